@@ -1,0 +1,463 @@
+"""Host-side mirror of aion's backend seam over libaion_cuda.
+
+aion's backends implement three Zig vtables; this module gives the same three roles in
+Python (the reference toolchain, Zig, is not available here), with the reference's
+names and argument meaning, so a test reads like the reference's own backend tests:
+
+  * `DeviceMemory`  - src/aion/runtime/device_memory.zig:36-112
+  * `DeviceStore`   - src/aion/runtime/device_store.zig:24-93 (TensorId -> meta + chunk)
+  * `CudaBackend` / `CudaSession` - src/aion/backend/backend.zig:24-107
+
+and the three step records of the hot path (src/aion/runtime/executable.zig:27,
+105-115, 217-223). `CudaSession.execute(program)` walks the steps exactly as
+`GpuSession.execute` does (src/aion/backend/gpu/backend.zig:551-662) and issues one C
+call per step. Errors surface as the reference's error names.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import dataclasses
+from typing import Optional, Sequence
+
+import numpy as np
+
+from . import capi
+
+# types.BackendKind (src/aion/backend/types.zig:4-11)
+BACKEND_KIND_CUDA = "cuda"
+
+DTYPE_BYTES = {capi.DTYPE_F32: 4, capi.DTYPE_F16: 2, capi.DTYPE_I8: 1, capi.DTYPE_I32: 4}
+BLOCK_BYTES = {capi.DTYPE_Q4_0: 18, capi.DTYPE_Q8_0: 34}
+ORDER_NAMES = ["row_major", "lanes4", "lanes8", "lanes16", "lanes32", "lanes32x16"]
+
+
+class BackendError(RuntimeError):
+    """`BackendError || StoreError` (src/aion/backend/types.zig:27, src/aion/runtime/tensor_store.zig:7)."""
+
+    NAMES = {1: "InvalidArgument", 2: "OutOfMemory", 3: "Unsupported", 4: "ExecutionFailed"}
+
+    def __init__(self, status: int, message: str):
+        self.status = status
+        self.name = self.NAMES.get(status, f"status{status}")
+        super().__init__(f"{self.name}: {message}")
+
+
+def _check(status: int) -> None:
+    if status != capi.OK:
+        raise BackendError(status, capi.last_error())
+
+
+class CudaBackend:
+    """One B200 behind `Backend.VTable` {kind, name, caps, deinit, createSession}."""
+
+    def __init__(self, ordinal: int = 0):
+        self._lib = capi.load()
+        h = C.c_void_p()
+        _check(self._lib.aion_cuda_device_create(ordinal, C.byref(h)))
+        self._h = h
+        info = capi.DeviceInfo()
+        _check(self._lib.aion_cuda_device_info(self._h, C.byref(info)))
+        self.info = info
+        self.device_memory = DeviceMemory(self)
+
+    # -- Backend.VTable ----------------------------------------------------------
+    def kind(self) -> str:
+        return BACKEND_KIND_CUDA
+
+    def name(self) -> str:
+        return f"cuda:{self.info.ordinal} {self.info.name.decode()}"
+
+    def caps(self) -> dict:
+        # BackendCaps (src/aion/backend/types.zig:13-25)
+        return {"simd": True, "threads": True, "fp16": True, "int8": True, "quant_q4": True, "quant_q8": True,
+                "strided_copy": False}
+
+    @property
+    def quant_block_order(self) -> int:
+        """The order the weight_layout pass should re-lay q8 [N,K] weights into."""
+        return int(self._lib.aion_cuda_quant_block_order(self._h))
+
+    def create_session(self, store: "DeviceStore") -> "CudaSession":
+        return CudaSession(self, store)
+
+    def deinit(self) -> None:
+        if self._h:
+            self._lib.aion_cuda_device_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.deinit()
+        except Exception:
+            pass
+
+    # -- stream plumbing (no reference counterpart) -------------------------------
+    def set_stream(self, cuda_stream: int | None) -> None:
+        _check(self._lib.aion_cuda_set_stream(self._h, C.c_void_p(cuda_stream or 0)))
+
+    def sync(self) -> None:
+        _check(self._lib.aion_cuda_sync(self._h))
+
+    @property
+    def handle(self):
+        return self._h
+
+
+class DeviceMemory:
+    """`DeviceMemory.VTable`: model, alloc, free, copyH2D, copyD2H, copyD2HMany, copyD2D, maxBindingBytes."""
+
+    def __init__(self, backend: CudaBackend):
+        self._b = backend
+        self._lib = backend._lib
+
+    def model(self) -> str:
+        return "discrete" if self._lib.aion_cuda_memory_model(self._b._h) == 0 else "unified"
+
+    def max_binding_bytes(self) -> int:
+        return int(self._lib.aion_cuda_max_binding_bytes(self._b._h))
+
+    def alloc(self, nbytes: int, alignment: int = 64) -> int:
+        h = C.c_uint64()
+        _check(self._lib.aion_cuda_alloc(self._b._h, nbytes, alignment, C.byref(h)))
+        return int(h.value)
+
+    def free(self, handle: int) -> None:
+        _check(self._lib.aion_cuda_free(self._b._h, handle))
+
+    def copy_h2d(self, handle: int, dst_offset: int, src: np.ndarray) -> None:
+        src = np.ascontiguousarray(src)
+        _check(self._lib.aion_cuda_h2d(self._b._h, handle, dst_offset, src.ctypes.data_as(C.c_void_p), src.nbytes))
+
+    def copy_d2h(self, dst: np.ndarray, handle: int, src_offset: int = 0) -> None:
+        assert dst.flags.c_contiguous and dst.flags.writeable
+        _check(self._lib.aion_cuda_d2h(self._b._h, dst.ctypes.data_as(C.c_void_p), handle, src_offset, dst.nbytes))
+
+    def copy_d2h_many(self, regions: Sequence[tuple[np.ndarray, int, int]]) -> None:
+        for dst, handle, off in regions:
+            self.copy_d2h(dst, handle, off)
+
+    def copy_d2d(self, dst: int, dst_offset: int, src: int, src_offset: int, nbytes: int) -> None:
+        _check(self._lib.aion_cuda_d2d(self._b._h, dst, dst_offset, src, src_offset, nbytes))
+
+    def memset(self, handle: int, offset: int, value: int, nbytes: int) -> None:
+        _check(self._lib.aion_cuda_memset(self._b._h, handle, offset, value, nbytes))
+
+
+@dataclasses.dataclass
+class TensorMeta:
+    """`TensorMeta` (src/aion/runtime/tensor_store.zig:22-32) plus the quant axis storage keeps beside it."""
+
+    dtype: int
+    shape: tuple
+    quant_axis: int = 0
+    block_order: int = capi.ORDER_ROW_MAJOR
+    # SequenceCachePolicyKind (src/aion/runtime/tensor_store.zig:9-13): "none" | "growable" | "rolling"
+    cache_policy: str = "none"
+
+    @property
+    def rank(self) -> int:
+        return len(self.shape)
+
+    def nbytes(self) -> int:
+        n = int(np.prod(self.shape, dtype=np.int64)) if self.shape else 1
+        if self.dtype in BLOCK_BYTES:
+            return n // 32 * BLOCK_BYTES[self.dtype]
+        return n * DTYPE_BYTES[self.dtype]
+
+
+@dataclasses.dataclass
+class Chunk:
+    """`Chunk{handle, offset, len}` (src/aion/runtime/device_store.zig:14-22)."""
+
+    handle: int
+    offset: int
+    len: int
+
+    def operand(self) -> capi.Operand:
+        return capi.Operand(self.handle, self.offset, self.len)
+
+
+class DeviceStore:
+    """A minimal tensor table: TensorId -> (meta, device chunk). Owns what it allocates."""
+
+    def __init__(self, memory: DeviceMemory):
+        self.memory = memory
+        self._meta: dict[int, TensorMeta] = {}
+        self._chunk: dict[int, Chunk] = {}
+        self._owned: list[int] = []
+        self._next = 0
+
+    def add(self, meta: TensorMeta, data: Optional[np.ndarray] = None) -> int:
+        """Allocate a tensor on the device (optionally filled from host bytes); returns its TensorId."""
+        nbytes = meta.nbytes()
+        h = self.memory.alloc(max(nbytes, 1), 64)
+        self._owned.append(h)
+        if data is not None:
+            data = np.ascontiguousarray(data)
+            if data.nbytes != nbytes:
+                raise BackendError(capi.INVALID_ARGUMENT, f"tensor holds {nbytes} bytes, data has {data.nbytes}")
+            self.memory.copy_h2d(h, 0, data)
+        return self.bind(meta, Chunk(h, 0, nbytes))
+
+    def bind(self, meta: TensorMeta, chunk: Chunk) -> int:
+        """Register memory the caller owns (a torch tensor's data_ptr, a slice of an arena)."""
+        tid = self._next
+        self._next += 1
+        self._meta[tid] = meta
+        self._chunk[tid] = chunk
+        return tid
+
+    def meta(self, tid: int) -> TensorMeta:
+        if tid not in self._meta:
+            raise BackendError(capi.INVALID_ARGUMENT, f"unknown TensorId {tid}")
+        return self._meta[tid]
+
+    def acquire_const(self, tid: int) -> Chunk:
+        self.meta(tid)
+        return self._chunk[tid]
+
+    acquire_mut = acquire_const
+
+    def sequence_cache_policy_info(self, tid: int) -> str:
+        return self.meta(tid).cache_policy
+
+    def read(self, tid: int) -> np.ndarray:
+        """Read a tensor back to the host (waits for the stream)."""
+        meta, ch = self.meta(tid), self._chunk[tid]
+        if meta.dtype in BLOCK_BYTES:
+            out = np.empty(meta.nbytes(), dtype=np.uint8)
+        else:
+            np_dt = {capi.DTYPE_F32: np.float32, capi.DTYPE_F16: np.float16, capi.DTYPE_I8: np.int8,
+                     capi.DTYPE_I32: np.int32}[meta.dtype]
+            out = np.empty(meta.shape, dtype=np_dt)
+        self.memory.copy_d2h(out, ch.handle, ch.offset)
+        return out
+
+    def write(self, tid: int, data: np.ndarray) -> None:
+        ch = self._chunk[tid]
+        self.memory.copy_h2d(ch.handle, ch.offset, data)
+
+    def deinit(self) -> None:
+        for h in self._owned:
+            self.memory.free(h)
+        self._owned.clear()
+
+
+# ---- step records (src/aion/runtime/executable.zig) ----------------------------------
+
+@dataclasses.dataclass
+class StepMatMul:
+    c: int
+    a: int
+    b: int
+    alpha: float = 1.0
+    beta: float = 0.0
+    flags: int = capi.MATMUL_AUTO
+
+
+@dataclasses.dataclass
+class StepMatMulNT:
+    c: int
+    a: int
+    b: int
+    alpha: float = 1.0
+    beta: float = 0.0
+    flags: int = capi.MATMUL_AUTO
+
+
+@dataclasses.dataclass
+class AttentionWindow:
+    """src/aion/graph/graph.zig:130-167."""
+
+    left: int = capi.WINDOW_UNBOUNDED
+    right: int = capi.WINDOW_UNBOUNDED
+    chunk: int = 0
+
+    @staticmethod
+    def causal() -> "AttentionWindow":
+        return AttentionWindow(right=0)
+
+    @staticmethod
+    def sliding(n: int, m: int) -> "AttentionWindow":
+        return AttentionWindow(left=n, right=m)
+
+    @staticmethod
+    def chunked(size: int, n: int) -> "AttentionWindow":
+        return AttentionWindow(left=n, right=0, chunk=size)
+
+
+@dataclasses.dataclass
+class StepAttention:
+    out: int
+    q: int
+    k: int
+    v: int
+    query_positions: Optional[int] = None
+    kv_lengths: Optional[int] = None
+    scale: float = 1.0
+    window: AttentionWindow = dataclasses.field(default_factory=AttentionWindow)
+    attn_logits_soft_cap: float = 0.0
+
+
+def _rows_of(shape: tuple) -> int:
+    """Leading dims folded into M (src/aion/backend/cpu/exec/matmul.zig:333-338)."""
+    m = 1
+    for d in shape[:-1]:
+        m *= d
+    return m
+
+
+class CudaSession:
+    """`Session.VTable` {execute, retireResources, deinit} bound to one `DeviceStore`."""
+
+    def __init__(self, backend: CudaBackend, store: DeviceStore):
+        self.backend = backend
+        self.store = store
+        self._lib = backend._lib
+
+    def execute(self, program: Sequence[object]) -> None:
+        """Run the steps in order; asynchronous, like the reference's device path."""
+        for step in program:
+            if isinstance(step, StepMatMul):
+                self._matmul(step)
+            elif isinstance(step, StepMatMulNT):
+                self._matmul_nt(step)
+            elif isinstance(step, StepAttention):
+                self._attention(step)
+            else:
+                # An unsupported step never falls back to the host
+                # (src/aion/runtime/executable.zig:355-357).
+                raise BackendError(capi.UNSUPPORTED, f"step {type(step).__name__} is outside this backend")
+
+    def retire_resources(self) -> None:
+        self.backend.sync()
+
+    def deinit(self) -> None:
+        self.retire_resources()
+
+    # ---------------------------------------------------------------------------
+    def _matmul(self, s: StepMatMul) -> None:
+        st = self.store
+        am, bm, cm = st.meta(s.a), st.meta(s.b), st.meta(s.c)
+        if am.dtype != capi.DTYPE_F32 or cm.dtype != capi.DTYPE_F32:
+            raise BackendError(capi.INVALID_ARGUMENT, "matmul: A and C must be f32")
+        if bm.rank != 2 or (bm.dtype in BLOCK_BYTES and bm.quant_axis != 0):
+            raise BackendError(capi.INVALID_ARGUMENT, "matmul: B must be [k, n] quantized along axis 0")
+        k, n = bm.shape
+        m = _rows_of(cm.shape)
+        if am.shape[-1] != k or cm.shape[-1] != n or _rows_of(am.shape) != m:
+            raise BackendError(capi.INVALID_ARGUMENT, "matmul: shapes do not agree")
+        rec = capi.MatMul(c=st.acquire_mut(s.c).operand(), a=st.acquire_const(s.a).operand(),
+                          b=st.acquire_const(s.b).operand(), b_dtype=bm.dtype, flags=s.flags, m=m, n=n, k=k,
+                          lda=0, ldb=0, ldc=0, alpha=s.alpha, beta=s.beta)
+        _check(self._lib.aion_cuda_matmul(self.backend._h, C.byref(rec)))
+
+    def _matmul_nt(self, s: StepMatMulNT) -> None:
+        st = self.store
+        am, bm, cm = st.meta(s.a), st.meta(s.b), st.meta(s.c)
+        if am.dtype != capi.DTYPE_F32 or cm.dtype != capi.DTYPE_F32:
+            raise BackendError(capi.INVALID_ARGUMENT, "matmul_nt: A and C must be f32")
+        # src/aion/runtime/executable.zig:210-216: B rank 2, quant_axis 1.
+        if bm.rank != 2 or (bm.dtype in BLOCK_BYTES and bm.quant_axis != 1):
+            raise BackendError(capi.INVALID_ARGUMENT, "matmul_nt: B must be [n, k] quantized along axis 1")
+        n, k = bm.shape
+        m = _rows_of(cm.shape)
+        if am.shape[-1] != k or cm.shape[-1] != n:
+            raise BackendError(capi.INVALID_ARGUMENT, "matmul_nt: shapes do not agree")
+        rec = capi.MatMulNT(c=st.acquire_mut(s.c).operand(), a=st.acquire_const(s.a).operand(),
+                            b=st.acquire_const(s.b).operand(), b_dtype=bm.dtype, block_order=bm.block_order,
+                            flags=s.flags, m=m, n=n, k=k, lda=0, ldc=0, c_off=0, alpha=s.alpha, beta=s.beta)
+        _check(self._lib.aion_cuda_matmul_nt(self.backend._h, C.byref(rec)))
+
+    def _attention(self, s: StepAttention) -> None:
+        st = self.store
+        qm, km, vm, om = st.meta(s.q), st.meta(s.k), st.meta(s.v), st.meta(s.out)
+        # src/aion/backend/cpu/exec/attention.zig:1461-1500
+        if qm.rank != 4 or km.rank != 4 or vm.rank != 4 or om.rank != 4:
+            raise BackendError(capi.INVALID_ARGUMENT, "attention: q, k, v, out must be rank 4")
+        if om.dtype != capi.DTYPE_F32:
+            raise BackendError(capi.INVALID_ARGUMENT, "attention: out must be f32")
+        B, L, Hq, Dk = qm.shape
+        _, T, Hkv, _ = km.shape
+        Dv = vm.shape[3]
+        if km.shape[0] != B or vm.shape[0] != B or km.shape[3] != Dk or vm.shape[1] != T or vm.shape[2] != Hkv:
+            raise BackendError(capi.INVALID_ARGUMENT, "attention: q/k/v shapes do not agree")
+        if tuple(om.shape) != (B, L, Hq, Dv):
+            raise BackendError(capi.INVALID_ARGUMENT, "attention: out shape")
+        none = capi.Operand(0, 0, 0)
+        pos = none
+        if s.query_positions is not None:
+            pm = st.meta(s.query_positions)
+            if pm.dtype != capi.DTYPE_I32 or tuple(pm.shape) != (B, L):
+                raise BackendError(capi.INVALID_ARGUMENT, "attention: query_positions must be i32 [B, L]")
+            pos = st.acquire_const(s.query_positions).operand()
+        lens = none
+        if s.kv_lengths is not None:
+            lm = st.meta(s.kv_lengths)
+            if lm.dtype != capi.DTYPE_I32 or tuple(lm.shape) != (B,):
+                raise BackendError(capi.INVALID_ARGUMENT, "attention: kv_lengths must be i32 [B]")
+            lens = st.acquire_const(s.kv_lengths).operand()
+        rolling = 1 if st.sequence_cache_policy_info(s.k) == "rolling" else 0
+        rec = capi.Attention(out=st.acquire_mut(s.out).operand(), q=st.acquire_const(s.q).operand(),
+                             k=st.acquire_const(s.k).operand(), v=st.acquire_const(s.v).operand(),
+                             query_positions=pos, kv_lengths=lens, q_dtype=qm.dtype, k_dtype=km.dtype,
+                             v_dtype=vm.dtype, rolling=rolling, batch=B, l_q=L, h_q=Hq, h_kv=Hkv, d_k=Dk, d_v=Dv,
+                             t_cap=T, scale=s.scale, soft_cap=s.attn_logits_soft_cap,
+                             window_left=s.window.left, window_right=s.window.right, window_chunk=s.window.chunk,
+                             flags=0)
+        _check(self._lib.aion_cuda_attention(self.backend._h, C.byref(rec)))
+
+
+# ---- storage-level helpers (Context.quantize / weight_layout on the device) -----------
+
+def quantize(backend: CudaBackend, dtype: int, values: np.ndarray, quant_axis: int) -> np.ndarray:
+    """Quantize an f32 host tensor on the device; returns the packed bytes (host)."""
+    v = np.ascontiguousarray(values, dtype=np.float32)
+    mem = backend.device_memory
+    nblocks = v.size // 32
+    out_bytes = nblocks * BLOCK_BYTES[dtype]
+    hv, ho = mem.alloc(max(v.nbytes, 1)), mem.alloc(max(out_bytes, 1))
+    try:
+        mem.copy_h2d(hv, 0, v)
+        shape = (C.c_uint64 * v.ndim)(*v.shape)
+        vo, oo = capi.Operand(hv, 0, v.nbytes), capi.Operand(ho, 0, out_bytes)
+        _check(backend._lib.aion_cuda_quantize(backend._h, dtype, C.byref(vo), shape, v.ndim, quant_axis, C.byref(oo)))
+        out = np.empty(out_bytes, dtype=np.uint8)
+        mem.copy_d2h(out, ho, 0)
+        return out
+    finally:
+        mem.free(hv)
+        mem.free(ho)
+
+
+def dequantize(backend: CudaBackend, dtype: int, blocks: np.ndarray) -> np.ndarray:
+    b = np.ascontiguousarray(blocks, dtype=np.uint8)
+    nblocks = b.size // BLOCK_BYTES[dtype]
+    mem = backend.device_memory
+    hb, ho = mem.alloc(max(b.nbytes, 1)), mem.alloc(max(nblocks * 128, 1))
+    try:
+        mem.copy_h2d(hb, 0, b)
+        bo, oo = capi.Operand(hb, 0, b.nbytes), capi.Operand(ho, 0, nblocks * 128)
+        _check(backend._lib.aion_cuda_dequantize(backend._h, dtype, C.byref(bo), nblocks, C.byref(oo)))
+        out = np.empty(nblocks * 32, dtype=np.float32)
+        mem.copy_d2h(out, ho, 0)
+        return out
+    finally:
+        mem.free(hb)
+        mem.free(ho)
+
+
+def relayout_q8(backend: CudaBackend, order: int, n: int, k: int, src: np.ndarray, inverse: bool = False) -> np.ndarray:
+    s = np.ascontiguousarray(src, dtype=np.uint8)
+    mem = backend.device_memory
+    hs, hd = mem.alloc(max(s.nbytes, 1)), mem.alloc(max(s.nbytes, 1))
+    try:
+        mem.copy_h2d(hs, 0, s)
+        so, do = capi.Operand(hs, 0, s.nbytes), capi.Operand(hd, 0, s.nbytes)
+        _check(backend._lib.aion_cuda_relayout_q8(backend._h, order, int(inverse), n, k, C.byref(so), C.byref(do)))
+        out = np.empty(s.nbytes, dtype=np.uint8)
+        mem.copy_d2h(out, hd, 0)
+        return out
+    finally:
+        mem.free(hs)
+        mem.free(hd)

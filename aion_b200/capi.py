@@ -1,0 +1,136 @@
+"""ctypes binding of libaion_cuda's C ABI (include/aion_cuda.h), one declaration per symbol.
+
+The library is the product; there is no Python or CPU fallback. Loading fails loudly
+when the shared object has not been built (`python -m aion_b200.build`).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+OK, INVALID_ARGUMENT, OUT_OF_MEMORY, UNSUPPORTED, INTERNAL_ERROR = range(5)
+STATUS_NAMES = {0: "OK", 1: "INVALID_ARGUMENT", 2: "OUT_OF_MEMORY", 3: "UNSUPPORTED", 4: "INTERNAL_ERROR"}
+
+DTYPE_F32, DTYPE_F16, DTYPE_I8, DTYPE_Q4_0, DTYPE_Q8_0, DTYPE_I32 = range(6)
+ORDER_ROW_MAJOR, ORDER_LANES4, ORDER_LANES8, ORDER_LANES16, ORDER_LANES32, ORDER_LANES32X16 = range(6)
+WINDOW_UNBOUNDED = 0xFFFFFFFF
+MATMUL_AUTO, MATMUL_FORCE_GENERIC, MATMUL_FORCE_GEMV, MATMUL_FORCE_GEMM = 0, 1, 2, 4
+GEMV_MAX_M = 16
+
+LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libaion_cuda.so")
+
+
+class Operand(C.Structure):
+    _fields_ = [("handle", C.c_uint64), ("offset", C.c_uint64), ("len", C.c_uint64)]
+
+
+class DeviceInfo(C.Structure):
+    _fields_ = [
+        ("name", C.c_char * 128),
+        ("ordinal", C.c_int32),
+        ("sm_count", C.c_int32),
+        ("cc_major", C.c_int32),
+        ("cc_minor", C.c_int32),
+        ("total_bytes", C.c_uint64),
+        ("l2_bytes", C.c_uint64),
+    ]
+
+
+class MatMul(C.Structure):
+    _fields_ = [
+        ("c", Operand), ("a", Operand), ("b", Operand),
+        ("b_dtype", C.c_uint32), ("flags", C.c_uint32),
+        ("m", C.c_uint64), ("n", C.c_uint64), ("k", C.c_uint64),
+        ("lda", C.c_uint64), ("ldb", C.c_uint64), ("ldc", C.c_uint64),
+        ("alpha", C.c_float), ("beta", C.c_float),
+    ]
+
+
+class MatMulNT(C.Structure):
+    _fields_ = [
+        ("c", Operand), ("a", Operand), ("b", Operand),
+        ("b_dtype", C.c_uint32), ("block_order", C.c_uint32), ("flags", C.c_uint32), ("reserved", C.c_uint32),
+        ("m", C.c_uint64), ("n", C.c_uint64), ("k", C.c_uint64),
+        ("lda", C.c_uint64), ("ldc", C.c_uint64), ("c_off", C.c_uint64),
+        ("alpha", C.c_float), ("beta", C.c_float),
+    ]
+
+
+class Attention(C.Structure):
+    _fields_ = [
+        ("out", Operand), ("q", Operand), ("k", Operand), ("v", Operand),
+        ("query_positions", Operand), ("kv_lengths", Operand),
+        ("q_dtype", C.c_uint32), ("k_dtype", C.c_uint32), ("v_dtype", C.c_uint32), ("rolling", C.c_uint32),
+        ("batch", C.c_uint64), ("l_q", C.c_uint64), ("h_q", C.c_uint64), ("h_kv", C.c_uint64),
+        ("d_k", C.c_uint64), ("d_v", C.c_uint64), ("t_cap", C.c_uint64),
+        ("scale", C.c_float), ("soft_cap", C.c_float),
+        ("window_left", C.c_uint32), ("window_right", C.c_uint32), ("window_chunk", C.c_uint32),
+        ("flags", C.c_uint32),
+    ]
+
+
+_DEV = C.c_void_p
+_OPP = C.POINTER(Operand)
+
+# name -> (restype, argtypes); every symbol include/aion_cuda.h declares.
+SIGNATURES = {
+    "aion_cuda_device_count": (C.c_int32, [C.POINTER(C.c_int32)]),
+    "aion_cuda_device_create": (C.c_int32, [C.c_int32, C.POINTER(_DEV)]),
+    "aion_cuda_device_destroy": (None, [_DEV]),
+    "aion_cuda_device_info": (C.c_int32, [_DEV, C.POINTER(DeviceInfo)]),
+    "aion_cuda_quant_block_order": (C.c_uint8, [_DEV]),
+    "aion_cuda_set_stream": (C.c_int32, [_DEV, C.c_void_p]),
+    "aion_cuda_get_stream": (C.c_void_p, [_DEV]),
+    "aion_cuda_sync": (C.c_int32, [_DEV]),
+    "aion_cuda_last_error": (C.c_int32, [C.c_char_p, C.c_size_t, C.POINTER(C.c_size_t)]),
+    "aion_cuda_memory_model": (C.c_int32, [_DEV]),
+    "aion_cuda_max_binding_bytes": (C.c_uint64, [_DEV]),
+    "aion_cuda_alloc": (C.c_int32, [_DEV, C.c_size_t, C.c_size_t, C.POINTER(C.c_uint64)]),
+    "aion_cuda_free": (C.c_int32, [_DEV, C.c_uint64]),
+    "aion_cuda_h2d": (C.c_int32, [_DEV, C.c_uint64, C.c_size_t, C.c_void_p, C.c_size_t]),
+    "aion_cuda_d2h": (C.c_int32, [_DEV, C.c_void_p, C.c_uint64, C.c_size_t, C.c_size_t]),
+    "aion_cuda_d2d": (C.c_int32, [_DEV, C.c_uint64, C.c_size_t, C.c_uint64, C.c_size_t, C.c_size_t]),
+    "aion_cuda_memset": (C.c_int32, [_DEV, C.c_uint64, C.c_size_t, C.c_int32, C.c_size_t]),
+    "aion_cuda_matmul": (C.c_int32, [_DEV, C.POINTER(MatMul)]),
+    "aion_cuda_matmul_nt": (C.c_int32, [_DEV, C.POINTER(MatMulNT)]),
+    "aion_cuda_attention": (C.c_int32, [_DEV, C.POINTER(Attention)]),
+    "aion_cuda_quantize": (C.c_int32, [_DEV, C.c_uint32, _OPP, C.POINTER(C.c_uint64), C.c_uint32, C.c_uint32, _OPP]),
+    "aion_cuda_dequantize": (C.c_int32, [_DEV, C.c_uint32, _OPP, C.c_uint64, _OPP]),
+    "aion_cuda_relayout_q8": (C.c_int32, [_DEV, C.c_uint32, C.c_uint32, C.c_uint64, C.c_uint64, _OPP, _OPP]),
+}
+
+_lib = None
+
+
+class AionCudaError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"{STATUS_NAMES.get(status, status)}: {message}")
+        self.status = status
+        self.message = message
+
+
+def load() -> C.CDLL:
+    """dlopen libaion_cuda.so and attach the signatures. Raises if it is not built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(
+                f"{LIB_PATH} is missing: build it with `python -m aion_b200.build` (there is no fallback path)")
+        lib = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+    return _lib
+
+
+def last_error() -> str:
+    buf = C.create_string_buffer(1024)
+    load().aion_cuda_last_error(buf, len(buf), None)
+    return buf.value.decode("utf-8", "replace")
+
+
+def check(status: int) -> None:
+    if status != OK:
+        raise AionCudaError(status, last_error())

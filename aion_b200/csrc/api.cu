@@ -1,0 +1,138 @@
+// Step entry points: argument checks and routing to a kernel family.
+#include <cmath>
+
+#include "common.cuh"
+
+using namespace aion;
+
+namespace {
+
+// Bytes a K-major quantized B of `kblocks` block-rows must hold
+// (src/aion/backend/cpu/kernels/matvec_q.zig:85).
+uint64_t kmajor_bytes(uint64_t kblocks, uint64_t ldb, uint64_t n, size_t bb) {
+  return kblocks == 0 ? 0 : ((kblocks - 1) * ldb + n) * bb;
+}
+
+int32_t route(AionCudaDevice* dev, const MatMulArgs& g, uint32_t flags, const char* what) {
+  if (flags & AION_CUDA_MATMUL_FORCE_GENERIC) return matmul_generic(dev, g);
+  if (flags & AION_CUDA_MATMUL_FORCE_GEMV) {
+    const int32_t st = gemv_mma(dev, g, false);
+    if (st == AION_CUDA_UNSUPPORTED) return fail(st, "%s: the tiled GEMV does not read this shape or alignment", what);
+    return st;
+  }
+  if (flags & AION_CUDA_MATMUL_FORCE_GEMM) {
+    const int32_t st = gemm_tcgen05(dev, g, false);
+    if (st == AION_CUDA_UNSUPPORTED) return fail(st, "%s: the tensor-core GEMM does not read this shape or alignment", what);
+    return st;
+  }
+  // Decode-sized m streams the weights once through the int8 GEMV; prefill-sized m is a
+  // dense contraction for the tensor cores. Either falls back to the any-shape kernel
+  // (still on the device) when the tiled kernel cannot read the operands.
+  if (g.m <= AION_CUDA_GEMV_MAX_M) {
+    const int32_t st = gemv_mma(dev, g, false);
+    if (st != AION_CUDA_UNSUPPORTED) return st;
+  } else {
+    const int32_t st = gemm_tcgen05(dev, g, false);
+    if (st != AION_CUDA_UNSUPPORTED) return st;
+  }
+  return matmul_generic(dev, g);
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t aion_cuda_matmul(AionCudaDevice* dev, const AionCudaMatMul* s) {
+  if (!dev || !s) return fail(AION_CUDA_INVALID_ARGUMENT, "matmul: null argument");
+  if (s->b_dtype == AION_CUDA_DTYPE_F32 || s->b_dtype == AION_CUDA_DTYPE_F16)
+    return fail(AION_CUDA_UNSUPPORTED, "matmul: float B is outside this backend (quantized q8_0 / q4_0 only)");
+  if (s->b_dtype != AION_CUDA_DTYPE_Q8_0 && s->b_dtype != AION_CUDA_DTYPE_Q4_0)
+    return fail(AION_CUDA_INVALID_ARGUMENT, "matmul: B dtype %u", s->b_dtype);
+  // Quantized B: K must be whole blocks (src/aion/graph/program/compiler.zig:189-239).
+  if (s->k % QK != 0) return fail(AION_CUDA_INVALID_ARGUMENT, "matmul: k = %llu is not a multiple of 32", (unsigned long long)s->k);
+  if (s->m == 0 || s->n == 0) return AION_CUDA_OK;
+  MatMulArgs g{};
+  g.dtype = s->b_dtype;
+  g.nt = false;
+  g.order = AION_CUDA_ORDER_ROW_MAJOR;
+  g.m = s->m;
+  g.n = s->n;
+  g.k = s->k;
+  g.lda = s->lda ? s->lda : s->k;
+  g.ldb = s->ldb ? s->ldb : s->n;
+  g.ldc = s->ldc ? s->ldc : s->n;
+  g.alpha = s->alpha;
+  g.beta = s->beta;
+  if (g.lda < g.k || g.ldb < g.n || g.ldc < g.n) return fail(AION_CUDA_INVALID_ARGUMENT, "matmul: a leading dimension is shorter than its row");
+  const size_t bb = block_bytes_of(g.dtype);
+  if (int32_t st = resolve(s->a, ((g.m - 1) * g.lda + g.k) * sizeof(float), "matmul.a", &g.a)) return st;
+  if (int32_t st = resolve(s->c, ((g.m - 1) * g.ldc + g.n) * sizeof(float), "matmul.c", &g.c)) return st;
+  if (g.k == 0) {
+    // An empty contraction still applies beta; the any-shape kernel handles it.
+    const uint8_t* none = nullptr;
+    g.b = none;
+  } else if (int32_t st = resolve(s->b, kmajor_bytes(g.k / QK, g.ldb, g.n, bb), "matmul.b", &g.b)) {
+    return st;
+  }
+  if ((reinterpret_cast<uintptr_t>(g.a) & 3) || (reinterpret_cast<uintptr_t>(g.c) & 3) || (reinterpret_cast<uintptr_t>(g.b) & 1))
+    return fail(AION_CUDA_INVALID_ARGUMENT, "matmul: A and C must be 4-byte aligned, B 2-byte aligned");
+  if (int32_t st = dev->make_current()) return st;
+  return route(dev, g, s->flags, "matmul");
+}
+
+int32_t aion_cuda_matmul_nt(AionCudaDevice* dev, const AionCudaMatMulNT* s) {
+  if (!dev || !s) return fail(AION_CUDA_INVALID_ARGUMENT, "matmul_nt: null argument");
+  if (s->b_dtype == AION_CUDA_DTYPE_F32)
+    return fail(AION_CUDA_UNSUPPORTED, "matmul_nt: f32 B is outside this backend (q8_0 only)");
+  // The NT lowering exists for q8_0 and f32 only (src/aion/graph/program/matmul_rows.zig:89-100).
+  if (s->b_dtype != AION_CUDA_DTYPE_Q8_0) return fail(AION_CUDA_INVALID_ARGUMENT, "matmul_nt: B dtype %u", s->b_dtype);
+  if (s->block_order > AION_CUDA_ORDER_LANES32X16) return fail(AION_CUDA_INVALID_ARGUMENT, "matmul_nt: block order %u", s->block_order);
+  if (s->k % QK != 0) return fail(AION_CUDA_INVALID_ARGUMENT, "matmul_nt: k = %llu is not a multiple of 32", (unsigned long long)s->k);
+  static const int group_of[6] = {1, 4, 8, 16, 32, 32};
+  if (s->n % group_of[s->block_order] != 0)
+    return fail(AION_CUDA_INVALID_ARGUMENT, "matmul_nt: n = %llu does not fill groups of %d rows", (unsigned long long)s->n,
+                group_of[s->block_order]);
+  if (s->m == 0 || s->n == 0) return AION_CUDA_OK;
+  MatMulArgs g{};
+  g.dtype = s->b_dtype;
+  g.nt = true;
+  g.order = s->block_order;
+  g.m = s->m;
+  g.n = s->n;
+  g.k = s->k;
+  g.lda = s->lda ? s->lda : s->k;
+  g.ldb = s->k / QK;
+  g.ldc = s->ldc ? s->ldc : s->n;
+  g.alpha = s->alpha;
+  g.beta = s->beta;
+  if (g.lda < g.k || g.ldc < s->c_off + g.n) return fail(AION_CUDA_INVALID_ARGUMENT, "matmul_nt: a leading dimension is shorter than its row");
+  if (int32_t st = resolve(s->a, ((g.m - 1) * g.lda + g.k) * sizeof(float), "matmul_nt.a", &g.a)) return st;
+  float* c0;
+  if (int32_t st = resolve(s->c, ((g.m - 1) * g.ldc + s->c_off + g.n) * sizeof(float), "matmul_nt.c", &c0)) return st;
+  g.c = c0 + s->c_off;
+  if (g.k == 0) g.b = nullptr;
+  else if (int32_t st = resolve(s->b, g.n * (g.k / QK) * Q8_BYTES, "matmul_nt.b", &g.b)) return st;
+  if ((reinterpret_cast<uintptr_t>(g.a) & 3) || (reinterpret_cast<uintptr_t>(g.c) & 3) || (reinterpret_cast<uintptr_t>(g.b) & 1))
+    return fail(AION_CUDA_INVALID_ARGUMENT, "matmul_nt: A and C must be 4-byte aligned, B 2-byte aligned");
+  if (int32_t st = dev->make_current()) return st;
+  return route(dev, g, s->flags, "matmul_nt");
+}
+
+int32_t aion_cuda_attention(AionCudaDevice* dev, const AionCudaAttention* s) {
+  if (!dev || !s) return fail(AION_CUDA_INVALID_ARGUMENT, "attention: null argument");
+  // src/aion/backend/cpu/exec/attention.zig:1452-1500.
+  if (!(s->scale > 0.0f) || !std::isfinite(s->scale)) return fail(AION_CUDA_INVALID_ARGUMENT, "attention: scale must be finite and positive");
+  if (!std::isfinite(s->soft_cap) || s->soft_cap < 0.0f) return fail(AION_CUDA_INVALID_ARGUMENT, "attention: soft cap must be finite and >= 0");
+  for (uint32_t dt : {s->q_dtype, s->k_dtype, s->v_dtype})
+    if (dt != AION_CUDA_DTYPE_F16 && dt != AION_CUDA_DTYPE_F32) return fail(AION_CUDA_INVALID_ARGUMENT, "attention: q/k/v dtype %u", dt);
+  if (s->h_kv == 0 || s->h_q == 0 || s->h_q % s->h_kv != 0)
+    return fail(AION_CUDA_INVALID_ARGUMENT, "attention: %llu query heads over %llu kv heads", (unsigned long long)s->h_q,
+                (unsigned long long)s->h_kv);
+  if (s->t_cap == 0) return fail(AION_CUDA_INVALID_ARGUMENT, "attention: empty K/V");
+  if (s->batch * s->l_q * s->h_q == 0) return AION_CUDA_OK;
+  if (s->d_k == 0 || s->d_v == 0) return fail(AION_CUDA_INVALID_ARGUMENT, "attention: zero head dimension");
+  if (int32_t st = dev->make_current()) return st;
+  return attention_launch(dev, s);
+}
+
+}  // extern "C"

@@ -1,0 +1,102 @@
+// Shared declarations of libaion_cuda: the device object, status plumbing and the
+// block-format helpers every kernel file uses.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdarg>
+#include <cstdio>
+
+#include "../../include/aion_cuda.h"
+
+namespace aion {
+
+constexpr int QK = 32;          // weights per quantized block
+constexpr int Q8_BYTES = 34;    // f16 scale + 32 int8
+constexpr int Q4_BYTES = 18;    // f16 scale + 16 nibble bytes
+
+// Codes a kernel can leave in the device status word; the host maps them to AionStatus.
+enum DeviceFault : int {
+  FAULT_NONE = 0,
+  FAULT_INVALID_ARGUMENT = 1,  // a negative position / length, a length beyond the cache
+  FAULT_WAIT_EXPIRED = 2,      // a bounded wait on an mbarrier gave up
+  FAULT_NONFINITE = 3,         // softmax denominator not finite and positive
+};
+
+void set_error(const char* fmt, ...);
+int32_t fail(int32_t status, const char* fmt, ...);
+int32_t cuda_fail(cudaError_t e, const char* what);
+
+#define AION_CUDA_TRY(expr)                                   \
+  do {                                                        \
+    cudaError_t _e = (expr);                                  \
+    if (_e != cudaSuccess) return ::aion::cuda_fail(_e, #expr); \
+  } while (0)
+
+inline __host__ __device__ size_t block_bytes_of(uint32_t dtype) {
+  return dtype == AION_CUDA_DTYPE_Q8_0 ? Q8_BYTES : Q4_BYTES;
+}
+
+inline uint64_t ceil_div(uint64_t a, uint64_t b) { return (a + b - 1) / b; }
+
+}  // namespace aion
+
+// The device object behind the C handle.
+struct AionCudaDevice {
+  int ordinal = 0;
+  cudaStream_t own_stream = nullptr;
+  cudaStream_t stream = nullptr;
+  cudaDeviceProp prop{};
+  int sm_count = 0;
+  // Device status word kernels write a DeviceFault into, and its pinned host mirror.
+  int* fault_dev = nullptr;
+  int* fault_host = nullptr;
+  // Kernel scratch (quantized activations of the any-shape path, split partials);
+  // grown on demand, never shrunk, freed with the device.
+  void* scratch = nullptr;
+  size_t scratch_bytes = 0;
+  // Tuning override (environment AION_CUDA_GEMV_SPLIT): K-split of the tiled GEMV, 0 = automatic.
+  uint32_t gemv_split_override = 0;
+
+  int32_t make_current() const;
+  int32_t reserve_scratch(size_t bytes);
+  // Reads the status word back (call after the stream has been synchronized).
+  int32_t check_fault();
+};
+
+namespace aion {
+
+// Resolve an operand to a typed device pointer after checking it covers `need` bytes.
+template <class T>
+inline int32_t resolve(const AionCudaOperand& op, size_t need, const char* name, T** out) {
+  if (op.handle == 0) return fail(AION_CUDA_INVALID_ARGUMENT, "%s: null handle", name);
+  if (op.len < need) return fail(AION_CUDA_INVALID_ARGUMENT, "%s: operand holds %llu bytes, step needs %llu", name,
+                                 (unsigned long long)op.len, (unsigned long long)need);
+  *out = reinterpret_cast<T*>(static_cast<uintptr_t>(op.handle + op.offset));
+  return AION_CUDA_OK;
+}
+
+// ---- step implementations, one per kernel file ------------------------------------
+int32_t quantize_activation_rows(AionCudaDevice* dev, const float* a, uint64_t m, uint64_t k, uint64_t lda,
+                                 int8_t* aq, float* ascale);
+
+struct MatMulArgs {
+  const float* a;
+  const uint8_t* b;
+  float* c;
+  uint32_t dtype;
+  bool nt;            // B is [n, k] (quant_axis 1) rather than K-major
+  uint32_t order;     // QuantBlockOrder, nt only
+  uint64_t m, n, k, lda, ldb, ldc;
+  float alpha, beta;
+};
+int32_t matmul_generic(AionCudaDevice* dev, const MatMulArgs& g);
+// Returns AION_CUDA_UNSUPPORTED (without setting an error) when the shape or the
+// alignment is outside what the tiled kernel reads; the caller then routes elsewhere.
+int32_t gemv_mma(AionCudaDevice* dev, const MatMulArgs& g, bool probe_only);
+int32_t gemm_tcgen05(AionCudaDevice* dev, const MatMulArgs& g, bool probe_only);
+int32_t attention_launch(AionCudaDevice* dev, const AionCudaAttention* s);
+
+}  // namespace aion

@@ -1,0 +1,251 @@
+// Device lifetime, the DeviceMemory entry points and the per-thread diagnostic.
+#include <cstdlib>
+#include <cstring>
+#include <new>
+#include <string>
+
+#include "common.cuh"
+
+namespace aion {
+
+static thread_local std::string g_last_error;
+
+void set_error(const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  g_last_error = buf;
+}
+
+int32_t fail(int32_t status, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  g_last_error = buf;
+  return status;
+}
+
+int32_t cuda_fail(cudaError_t e, const char* what) {
+  const int32_t st = (e == cudaErrorMemoryAllocation) ? AION_CUDA_OUT_OF_MEMORY : AION_CUDA_INTERNAL_ERROR;
+  return fail(st, "CUDA error %d (%s) in %s", (int)e, cudaGetErrorString(e), what);
+}
+
+}  // namespace aion
+
+using namespace aion;
+
+int32_t AionCudaDevice::make_current() const {
+  int cur = -1;
+  AION_CUDA_TRY(cudaGetDevice(&cur));
+  if (cur != ordinal) AION_CUDA_TRY(cudaSetDevice(ordinal));
+  return AION_CUDA_OK;
+}
+
+int32_t AionCudaDevice::reserve_scratch(size_t bytes) {
+  if (bytes <= scratch_bytes) return AION_CUDA_OK;
+  // Earlier launches may still read the old buffer.
+  AION_CUDA_TRY(cudaStreamSynchronize(stream));
+  if (scratch) AION_CUDA_TRY(cudaFree(scratch));
+  scratch = nullptr;
+  scratch_bytes = 0;
+  size_t want = bytes + (bytes >> 2);
+  want = (want + 255) & ~size_t(255);
+  AION_CUDA_TRY(cudaMalloc(&scratch, want));
+  scratch_bytes = want;
+  return AION_CUDA_OK;
+}
+
+int32_t AionCudaDevice::check_fault() {
+  // The stream is idle here, so a plain copy of one word is enough.
+  AION_CUDA_TRY(cudaMemcpy(fault_host, fault_dev, sizeof(int), cudaMemcpyDeviceToHost));
+  const int f = *fault_host;
+  if (f == FAULT_NONE) return AION_CUDA_OK;
+  AION_CUDA_TRY(cudaMemset(fault_dev, 0, sizeof(int)));
+  switch (f) {
+    case FAULT_INVALID_ARGUMENT:
+      return fail(AION_CUDA_INVALID_ARGUMENT,
+                  "a kernel rejected its inputs (negative position or length, or a length beyond the cache)");
+    case FAULT_WAIT_EXPIRED:
+      return fail(AION_CUDA_INTERNAL_ERROR, "a kernel gave up a bounded wait on a copy barrier");
+    case FAULT_NONFINITE:
+      return fail(AION_CUDA_INVALID_ARGUMENT, "attention: softmax denominator is not finite and positive");
+    default:
+      return fail(AION_CUDA_INTERNAL_ERROR, "kernel fault code %d", f);
+  }
+}
+
+extern "C" {
+
+int32_t aion_cuda_device_count(int32_t* out_count) {
+  if (!out_count) return fail(AION_CUDA_INVALID_ARGUMENT, "device_count: null out");
+  int n = 0;
+  cudaError_t e = cudaGetDeviceCount(&n);
+  if (e != cudaSuccess) {
+    *out_count = 0;
+    return cuda_fail(e, "cudaGetDeviceCount");
+  }
+  *out_count = n;
+  return AION_CUDA_OK;
+}
+
+int32_t aion_cuda_device_create(int32_t ordinal, AionCudaDevice** out) {
+  if (!out) return fail(AION_CUDA_INVALID_ARGUMENT, "device_create: null out");
+  *out = nullptr;
+  int n = 0;
+  AION_CUDA_TRY(cudaGetDeviceCount(&n));
+  if (ordinal < 0 || ordinal >= n) return fail(AION_CUDA_INVALID_ARGUMENT, "device_create: ordinal %d of %d", ordinal, n);
+  AionCudaDevice* d = new (std::nothrow) AionCudaDevice();
+  if (!d) return fail(AION_CUDA_OUT_OF_MEMORY, "device_create: host allocation failed");
+  d->ordinal = ordinal;
+  cudaError_t e = cudaSetDevice(ordinal);
+  if (e == cudaSuccess) e = cudaGetDeviceProperties(&d->prop, ordinal);
+  if (e == cudaSuccess && d->prop.major != 10) {
+    const int major = d->prop.major, minor = d->prop.minor;
+    delete d;
+    return fail(AION_CUDA_UNSUPPORTED, "device_create: device %d is sm_%d%d; this library holds sm_100a code only",
+                ordinal, major, minor);
+  }
+  if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&d->own_stream, cudaStreamNonBlocking);
+  if (e == cudaSuccess) e = cudaMalloc(&d->fault_dev, sizeof(int));
+  if (e == cudaSuccess) e = cudaMemset(d->fault_dev, 0, sizeof(int));
+  if (e == cudaSuccess) e = cudaMallocHost(&d->fault_host, sizeof(int));
+  if (e != cudaSuccess) {
+    const int32_t st = cuda_fail(e, "device_create");
+    aion_cuda_device_destroy(d);
+    return st;
+  }
+  d->stream = d->own_stream;
+  d->sm_count = d->prop.multiProcessorCount;
+  if (const char* e2 = std::getenv("AION_CUDA_GEMV_SPLIT")) {
+    const int v = std::atoi(e2);
+    if (v == 1 || v == 2 || v == 4 || v == 8) d->gemv_split_override = (uint32_t)v;
+  }
+  *out = d;
+  return AION_CUDA_OK;
+}
+
+void aion_cuda_device_destroy(AionCudaDevice* dev) {
+  if (!dev) return;
+  cudaSetDevice(dev->ordinal);
+  if (dev->own_stream) {
+    cudaStreamSynchronize(dev->own_stream);
+    cudaStreamDestroy(dev->own_stream);
+  }
+  if (dev->scratch) cudaFree(dev->scratch);
+  if (dev->fault_dev) cudaFree(dev->fault_dev);
+  if (dev->fault_host) cudaFreeHost(dev->fault_host);
+  delete dev;
+}
+
+int32_t aion_cuda_device_info(AionCudaDevice* dev, AionCudaDeviceInfo* out) {
+  if (!dev || !out) return fail(AION_CUDA_INVALID_ARGUMENT, "device_info: null argument");
+  std::memset(out, 0, sizeof *out);
+  std::strncpy(out->name, dev->prop.name, sizeof(out->name) - 1);
+  out->ordinal = dev->ordinal;
+  out->sm_count = dev->prop.multiProcessorCount;
+  out->cc_major = dev->prop.major;
+  out->cc_minor = dev->prop.minor;
+  out->total_bytes = dev->prop.totalGlobalMem;
+  out->l2_bytes = (uint64_t)dev->prop.l2CacheSize;
+  return AION_CUDA_OK;
+}
+
+uint8_t aion_cuda_quant_block_order(AionCudaDevice*) { return AION_CUDA_ORDER_ROW_MAJOR; }
+
+int32_t aion_cuda_set_stream(AionCudaDevice* dev, void* cuda_stream) {
+  if (!dev) return fail(AION_CUDA_INVALID_ARGUMENT, "set_stream: null device");
+  dev->stream = cuda_stream ? static_cast<cudaStream_t>(cuda_stream) : dev->own_stream;
+  return AION_CUDA_OK;
+}
+
+void* aion_cuda_get_stream(AionCudaDevice* dev) { return dev ? (void*)dev->stream : nullptr; }
+
+int32_t aion_cuda_sync(AionCudaDevice* dev) {
+  if (!dev) return fail(AION_CUDA_INVALID_ARGUMENT, "sync: null device");
+  if (int32_t st = dev->make_current()) return st;
+  AION_CUDA_TRY(cudaStreamSynchronize(dev->stream));
+  return dev->check_fault();
+}
+
+int32_t aion_cuda_last_error(char* buf, size_t cap, size_t* len) {
+  const std::string& s = g_last_error;
+  if (len) *len = s.size();
+  if (buf && cap > 0) {
+    const size_t n = s.size() < cap - 1 ? s.size() : cap - 1;
+    std::memcpy(buf, s.data(), n);
+    buf[n] = 0;
+  }
+  return AION_CUDA_OK;
+}
+
+int32_t aion_cuda_memory_model(AionCudaDevice*) { return 0; }
+uint64_t aion_cuda_max_binding_bytes(AionCudaDevice*) { return UINT64_MAX; }
+
+int32_t aion_cuda_alloc(AionCudaDevice* dev, size_t bytes, size_t alignment, uint64_t* out_handle) {
+  if (!dev || !out_handle) return fail(AION_CUDA_INVALID_ARGUMENT, "alloc: null argument");
+  *out_handle = 0;
+  // cudaMalloc returns 256-byte aligned addresses.
+  if (alignment > 256 || (alignment & (alignment - 1)) != 0)
+    return fail(AION_CUDA_INVALID_ARGUMENT, "alloc: alignment %llu is not a power of two <= 256", (unsigned long long)alignment);
+  if (int32_t st = dev->make_current()) return st;
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, bytes ? bytes : 1);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(AION_CUDA_OUT_OF_MEMORY, "alloc: %llu bytes: %s", (unsigned long long)bytes, cudaGetErrorString(e));
+  }
+  *out_handle = (uint64_t)(uintptr_t)p;
+  return AION_CUDA_OK;
+}
+
+int32_t aion_cuda_free(AionCudaDevice* dev, uint64_t handle) {
+  if (!dev) return fail(AION_CUDA_INVALID_ARGUMENT, "free: null device");
+  if (handle == 0) return AION_CUDA_OK;
+  if (int32_t st = dev->make_current()) return st;
+  // Work that still reads the buffer must finish first (cudaFree also synchronizes,
+  // but only implicitly).
+  AION_CUDA_TRY(cudaStreamSynchronize(dev->stream));
+  AION_CUDA_TRY(cudaFree((void*)(uintptr_t)handle));
+  return AION_CUDA_OK;
+}
+
+int32_t aion_cuda_h2d(AionCudaDevice* dev, uint64_t handle, size_t dst_offset, const void* src, size_t bytes) {
+  if (!dev || handle == 0 || (!src && bytes)) return fail(AION_CUDA_INVALID_ARGUMENT, "h2d: null argument");
+  if (bytes == 0) return AION_CUDA_OK;
+  if (int32_t st = dev->make_current()) return st;
+  AION_CUDA_TRY(cudaMemcpyAsync((void*)(uintptr_t)(handle + dst_offset), src, bytes, cudaMemcpyHostToDevice, dev->stream));
+  // The source may be pageable and reused by the caller right after return.
+  AION_CUDA_TRY(cudaStreamSynchronize(dev->stream));
+  return AION_CUDA_OK;
+}
+
+int32_t aion_cuda_d2h(AionCudaDevice* dev, void* dst, uint64_t handle, size_t src_offset, size_t bytes) {
+  if (!dev || handle == 0 || (!dst && bytes)) return fail(AION_CUDA_INVALID_ARGUMENT, "d2h: null argument");
+  if (int32_t st = dev->make_current()) return st;
+  if (bytes) AION_CUDA_TRY(cudaMemcpyAsync(dst, (const void*)(uintptr_t)(handle + src_offset), bytes, cudaMemcpyDeviceToHost, dev->stream));
+  AION_CUDA_TRY(cudaStreamSynchronize(dev->stream));
+  return dev->check_fault();
+}
+
+int32_t aion_cuda_d2d(AionCudaDevice* dev, uint64_t dst, size_t dst_offset, uint64_t src, size_t src_offset, size_t bytes) {
+  if (!dev || dst == 0 || src == 0) return fail(AION_CUDA_INVALID_ARGUMENT, "d2d: null argument");
+  if (bytes == 0) return AION_CUDA_OK;
+  if (int32_t st = dev->make_current()) return st;
+  AION_CUDA_TRY(cudaMemcpyAsync((void*)(uintptr_t)(dst + dst_offset), (const void*)(uintptr_t)(src + src_offset), bytes,
+                                cudaMemcpyDeviceToDevice, dev->stream));
+  return AION_CUDA_OK;
+}
+
+int32_t aion_cuda_memset(AionCudaDevice* dev, uint64_t handle, size_t offset, int32_t byte_value, size_t bytes) {
+  if (!dev || handle == 0) return fail(AION_CUDA_INVALID_ARGUMENT, "memset: null argument");
+  if (bytes == 0) return AION_CUDA_OK;
+  if (int32_t st = dev->make_current()) return st;
+  AION_CUDA_TRY(cudaMemsetAsync((void*)(uintptr_t)(handle + offset), byte_value, bytes, dev->stream));
+  return AION_CUDA_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,242 @@
+/* aion_cuda.h — C ABI of libaion_cuda, a B200 (sm_100a) device backend for aion's
+ * inference hot path: the q4_0 / q8_0 block-quantized `MatMul` / `MatMulNT` steps and
+ * the grouped-query `Attention` step.
+ *
+ * The header sits beside aion's own `include/aion.h`. aion has no C plugin ABI for
+ * backends: its seam is three Zig vtables (`Backend`, `Session`, `DeviceMemory`). Every
+ * entry point here is what a Zig `CudaBackend` implementing those vtables binds; the
+ * comment on each one names the reference interface it stands behind (paths relative
+ * to the aion project root).
+ *
+ * Conventions
+ *  - Every function returns an `AionStatus` value (aion `include/aion.h:62-68`):
+ *    0 OK, 1 INVALID_ARGUMENT, 2 OUT_OF_MEMORY, 3 UNSUPPORTED, 4 INTERNAL_ERROR.
+ *    Nothing throws. The only global state is a per-thread last-error string.
+ *  - A device handle (`uint64_t`) is a raw device address; 0 means "none"
+ *    (aion `src/aion/runtime/device_memory.zig:14`). An operand is (handle, byte
+ *    offset, byte length), exactly what `DeviceStore` resolves a `TensorId` chunk to
+ *    (aion `src/aion/runtime/device_store.zig:24-93`).
+ *  - Work is enqueued on the device's stream and is asynchronous; `aion_cuda_d2h` and
+ *    `aion_cuda_sync` wait for it. One thread drives a device at a time
+ *    (aion `src/aion/backend/backend.zig:28-40`: one `execute` per session at a time).
+ *  - There is no CPU path. A dtype / layout this library has no kernel for returns
+ *    UNSUPPORTED, never a host fallback (aion `src/aion/runtime/executable.zig:355-357`).
+ */
+#ifndef AION_CUDA_H
+#define AION_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define AION_CUDA_API __declspec(dllexport)
+#else
+#define AION_CUDA_API __attribute__((visibility("default")))
+#endif
+
+/* AionStatus values (aion include/aion.h:62-68). */
+#define AION_CUDA_OK 0
+#define AION_CUDA_INVALID_ARGUMENT 1
+#define AION_CUDA_OUT_OF_MEMORY 2
+#define AION_CUDA_UNSUPPORTED 3
+#define AION_CUDA_INTERNAL_ERROR 4
+
+/* AionDType values (aion include/aion.h:70-77; src/aion/backend/types.zig:29-41). */
+#define AION_CUDA_DTYPE_F32 0
+#define AION_CUDA_DTYPE_F16 1
+#define AION_CUDA_DTYPE_I8 2
+#define AION_CUDA_DTYPE_Q4_0 3 /* 18-byte blocks: f16 scale + 16 nibble bytes, 32 weights */
+#define AION_CUDA_DTYPE_Q8_0 4 /* 34-byte blocks: f16 scale + 32 int8, 32 weights */
+#define AION_CUDA_DTYPE_I32 5
+
+/* QuantBlockOrder values (aion src/aion/backend/types.zig:150-157). */
+#define AION_CUDA_ORDER_ROW_MAJOR 0
+#define AION_CUDA_ORDER_LANES4 1
+#define AION_CUDA_ORDER_LANES8 2
+#define AION_CUDA_ORDER_LANES16 3
+#define AION_CUDA_ORDER_LANES32 4
+#define AION_CUDA_ORDER_LANES32X16 5
+
+/* AttentionWindow "no limit" (aion src/aion/graph/graph.zig:134). */
+#define AION_CUDA_WINDOW_UNBOUNDED 0xFFFFFFFFu
+
+typedef struct AionCudaDevice AionCudaDevice;
+
+/* One resolved tensor chunk: `DeviceStore` Chunk{handle, offset, len}
+ * (aion src/aion/runtime/device_store.zig:24-37). */
+typedef struct AionCudaOperand {
+  uint64_t handle; /* device address of the buffer, 0 = absent */
+  uint64_t offset; /* byte offset of the tensor inside the buffer */
+  uint64_t len;    /* bytes of the tensor available from `offset` */
+} AionCudaOperand;
+
+typedef struct AionCudaDeviceInfo {
+  char name[128];
+  int32_t ordinal;
+  int32_t sm_count;
+  int32_t cc_major;
+  int32_t cc_minor;
+  uint64_t total_bytes;
+  uint64_t l2_bytes;
+} AionCudaDeviceInfo;
+
+/* ---------------------------------------------------------------------------------
+ * Backend lifetime. Stands behind `Backend.VTable` {kind, name, caps, deinit,
+ * createSession} (aion src/aion/backend/backend.zig:59-72) the way `GpuBackend.init`
+ * stands behind it for wgpu (aion src/aion/backend/gpu/backend.zig:85-268).
+ * A device owns one stream, its kernel scratch and nothing else.
+ * --------------------------------------------------------------------------------- */
+AION_CUDA_API int32_t aion_cuda_device_count(int32_t* out_count);
+AION_CUDA_API int32_t aion_cuda_device_create(int32_t ordinal, AionCudaDevice** out);
+AION_CUDA_API void aion_cuda_device_destroy(AionCudaDevice* dev);
+AION_CUDA_API int32_t aion_cuda_device_info(AionCudaDevice* dev, AionCudaDeviceInfo* out);
+/* The QuantBlockOrder this backend's NT q8 kernel reads fastest; the compile pass
+ * re-lays q8 weights into it (aion src/aion/backend/gpu/backend.zig:86-87,
+ * src/aion/graph/target.zig:33-35). Row-major: weights are read in place. */
+AION_CUDA_API uint8_t aion_cuda_quant_block_order(AionCudaDevice* dev);
+/* Run on a caller-owned CUDA stream (a `cudaStream_t` passed as void*) instead of the
+ * device's own; NULL restores the device's stream. No counterpart in the reference:
+ * it lets a host that already owns a stream (PyTorch, a graph capture) order work. */
+AION_CUDA_API int32_t aion_cuda_set_stream(AionCudaDevice* dev, void* cuda_stream);
+AION_CUDA_API void* aion_cuda_get_stream(AionCudaDevice* dev);
+/* `Session.retireResources` (aion src/aion/backend/backend.zig:34-36): wait for all
+ * submitted work. */
+AION_CUDA_API int32_t aion_cuda_sync(AionCudaDevice* dev);
+/* Per-thread diagnostic text of the last failing call on this thread
+ * (aion src/aion/diagnostic.zig:8-44; include/aion.h:117-140). Copies at most `cap`
+ * bytes, NUL-terminates when cap > 0, stores the full length in *len when non-NULL. */
+AION_CUDA_API int32_t aion_cuda_last_error(char* buf, size_t cap, size_t* len);
+
+/* ---------------------------------------------------------------------------------
+ * DeviceMemory.VTable (aion src/aion/runtime/device_memory.zig:40-73).
+ * model() is `.discrete`; maxBindingBytes() is unbounded, so no tensor is dim-0
+ * chunked (aion src/aion/storage/layout.zig:22-25); importHost is absent.
+ * --------------------------------------------------------------------------------- */
+AION_CUDA_API int32_t aion_cuda_memory_model(AionCudaDevice* dev); /* 0 = discrete */
+AION_CUDA_API uint64_t aion_cuda_max_binding_bytes(AionCudaDevice* dev);
+AION_CUDA_API int32_t aion_cuda_alloc(AionCudaDevice* dev, size_t bytes, size_t alignment, uint64_t* out_handle);
+AION_CUDA_API int32_t aion_cuda_free(AionCudaDevice* dev, uint64_t handle);
+AION_CUDA_API int32_t aion_cuda_h2d(AionCudaDevice* dev, uint64_t handle, size_t dst_offset, const void* src, size_t bytes);
+/* Waits for the stream, like the reference's readback (aion src/aion/backend/gpu/backend.zig:296-308). */
+AION_CUDA_API int32_t aion_cuda_d2h(AionCudaDevice* dev, void* dst, uint64_t handle, size_t src_offset, size_t bytes);
+AION_CUDA_API int32_t aion_cuda_d2d(AionCudaDevice* dev, uint64_t dst, size_t dst_offset, uint64_t src, size_t src_offset, size_t bytes);
+AION_CUDA_API int32_t aion_cuda_memset(AionCudaDevice* dev, uint64_t handle, size_t offset, int32_t byte_value, size_t bytes);
+
+/* ---------------------------------------------------------------------------------
+ * `MatMul` step: C[m,n] = alpha * A[m,k] @ B[k,n] + beta * C.
+ * `StepMatMul` (aion src/aion/runtime/executable.zig:27) executed by `execMatMul` /
+ * `gemm2D` (aion src/aion/backend/cpu/exec/matmul.zig:48-108, 243-296) with
+ * `MatMulParams` (aion src/aion/backend/types.zig:225-241).
+ *   A f32 row-major, row stride lda elements (0 = k); leading dims folded into m.
+ *   B q8_0 or q4_0, quant_axis 0: block (kb, j) at byte ((kb*ldb + j) * block_bytes),
+ *     ldb in blocks (0 = n); k % 32 == 0.
+ *   C f32, row stride ldc elements (0 = n).
+ * The activation is quantized to int8 per 32-block exactly as the reference CPU
+ * kernels do (aion src/aion/backend/cpu/kernels/matmul_q_i8.zig:187-203) for
+ * m <= AION_CUDA_GEMV_MAX_M; larger m runs the tensor-core prefill GEMM, which
+ * dequantizes B to bf16 and rounds A to bf16.
+ * f32 / f16 B return UNSUPPORTED.
+ * --------------------------------------------------------------------------------- */
+#define AION_CUDA_GEMV_MAX_M 16
+
+typedef struct AionCudaMatMul {
+  AionCudaOperand c, a, b;
+  uint32_t b_dtype; /* AION_CUDA_DTYPE_Q8_0 | AION_CUDA_DTYPE_Q4_0 */
+  uint32_t flags;   /* AION_CUDA_MATMUL_* */
+  uint64_t m, n, k;
+  uint64_t lda, ldb, ldc;
+  float alpha, beta;
+} AionCudaMatMul;
+
+/* Force a kernel family regardless of m; tests use these the way the reference's GPU
+ * tests pin a pipeline (aion src/aion/backend/gpu/test_gpu_backend.zig:403-422). */
+#define AION_CUDA_MATMUL_AUTO 0u
+#define AION_CUDA_MATMUL_FORCE_GENERIC 1u /* any-shape scalar kernel */
+#define AION_CUDA_MATMUL_FORCE_GEMV 2u    /* tiled int8 tensor-core GEMV */
+#define AION_CUDA_MATMUL_FORCE_GEMM 4u    /* tcgen05 prefill GEMM */
+
+AION_CUDA_API int32_t aion_cuda_matmul(AionCudaDevice* dev, const AionCudaMatMul* step);
+
+/* ---------------------------------------------------------------------------------
+ * `MatMulNT` step: C[m,n] = alpha * sum_k A[m,k] * B[n,k] + beta * C.
+ * `StepMatMulNT` (aion src/aion/runtime/executable.zig:217-223) executed by
+ * `execMatMulNT` (aion src/aion/backend/cpu/exec/matmul_nt.zig:87-174) over
+ * `matmulNtQ8_0(order)` (aion src/aion/backend/cpu/kernels/matmul_nt_q.zig:560-579).
+ *   B q8_0 [n,k], quant_axis 1, in `block_order`; a row is k/32 blocks.
+ *   c_off / ldc let one weight be issued as several N-chunks of one C, as the
+ *   reference's device path does (aion src/aion/backend/gpu/exec/matmul_nt.zig:151-160):
+ *   C element (r, j) is at c + (r*ldc + c_off + j) * 4.
+ * --------------------------------------------------------------------------------- */
+typedef struct AionCudaMatMulNT {
+  AionCudaOperand c, a, b;
+  uint32_t b_dtype;     /* AION_CUDA_DTYPE_Q8_0 */
+  uint32_t block_order; /* AION_CUDA_ORDER_* */
+  uint32_t flags;       /* AION_CUDA_MATMUL_* */
+  uint32_t reserved;
+  uint64_t m, n, k;
+  uint64_t lda, ldc, c_off;
+  float alpha, beta;
+} AionCudaMatMulNT;
+
+AION_CUDA_API int32_t aion_cuda_matmul_nt(AionCudaDevice* dev, const AionCudaMatMulNT* step);
+
+/* ---------------------------------------------------------------------------------
+ * `Attention` step. `StepAttention` (aion src/aion/runtime/executable.zig:105-115)
+ * executed by `execAttention` (aion src/aion/backend/cpu/exec/attention.zig:1444-1608).
+ *   q   [B, L, Hq, Dk]   f16 or f32
+ *   k   [B, T, Hkv, Dk]  f16 or f32       v [B, T, Hkv, Dv] f16 or f32
+ *   out [B, L, Hq, Dv]   f32
+ *   query_positions i32 [B, L] (absent: position = row l)
+ *   kv_lengths      i32 [B]    (absent: T)
+ *   window {left, right, chunk} (aion src/aion/graph/graph.zig:130-167), soft cap
+ *   (0 = off), rolling: K/V are a ring of T rows addressed t % T and only the last T
+ *   logical keys are visible (aion src/aion/backend/cpu/exec/attention.zig:1072-1075).
+ * Empty key range writes zeros. A negative position / length, or a length beyond T on
+ * a non-rolling cache, is detected on the device and reported by the next
+ * aion_cuda_sync / aion_cuda_d2h as INVALID_ARGUMENT.
+ * --------------------------------------------------------------------------------- */
+typedef struct AionCudaAttention {
+  AionCudaOperand out, q, k, v;
+  AionCudaOperand query_positions; /* handle 0 = absent */
+  AionCudaOperand kv_lengths;      /* handle 0 = absent */
+  uint32_t q_dtype, k_dtype, v_dtype;
+  uint32_t rolling;
+  uint64_t batch, l_q, h_q, h_kv, d_k, d_v, t_cap;
+  float scale;
+  float soft_cap;
+  uint32_t window_left, window_right, window_chunk;
+  uint32_t flags;
+} AionCudaAttention;
+
+AION_CUDA_API int32_t aion_cuda_attention(AionCudaDevice* dev, const AionCudaAttention* step);
+
+/* ---------------------------------------------------------------------------------
+ * Block quantizer on the device. `quantizeBlocks` (aion src/aion/storage/quantize.zig:31-103)
+ * for q8_0; for q4_0 the reference's only q4 packer (aion
+ * src/aion/backend/cpu/test_cpu_kernels.zig:490-523) under the same placement rule.
+ * `values` f32 row-major of `shape[rank]`; blocks along `quant_axis`; `out` row-major
+ * over the block-space shape. Byte-exact with the reference.
+ * --------------------------------------------------------------------------------- */
+AION_CUDA_API int32_t aion_cuda_quantize(AionCudaDevice* dev, uint32_t dtype, const AionCudaOperand* values,
+                                         const uint64_t* shape, uint32_t rank, uint32_t quant_axis,
+                                         const AionCudaOperand* out);
+/* w = f32(q) * f32(f16 scale) for `nblocks` consecutive blocks, 32 f32 per block
+ * (aion src/aion/backend/cpu/kernels/matmul_q_i8.zig:847-862, nibble decode :362-369).
+ * Bit-exact in f32. */
+AION_CUDA_API int32_t aion_cuda_dequantize(AionCudaDevice* dev, uint32_t dtype, const AionCudaOperand* blocks,
+                                           uint64_t nblocks, const AionCudaOperand* out);
+/* Re-lay a row-major q8_0 [n,k] tensor into `order` (inverse != 0: back to row-major).
+ * `QuantBlockOrder.storeBlock/loadBlock` (aion src/aion/backend/types.zig:206-222) as
+ * driven by the weight_layout pass (aion src/aion/graph/opt/weight_layout.zig:243-314),
+ * which creates the derived tensor directly on the device (:270-275). */
+AION_CUDA_API int32_t aion_cuda_relayout_q8(AionCudaDevice* dev, uint32_t order, uint32_t inverse, uint64_t n,
+                                            uint64_t k, const AionCudaOperand* src, const AionCudaOperand* dst);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AION_CUDA_H */

@@ -415,7 +415,7 @@ def quantize(backend: CudaBackend, dtype: int, values: np.ndarray, quant_axis: i
     v = np.ascontiguousarray(values, dtype=np.float32)
     mem = backend.device_memory
     nblocks = v.size // 32
-    out_bytes = nblocks * BLOCK_BYTES[dtype]
+    out_bytes = nblocks * BLOCK_BYTES.get(dtype, 34)  # an unknown dtype is rejected by the library
     hv, ho = mem.alloc(max(v.nbytes, 1)), mem.alloc(max(out_bytes, 1))
     try:
         mem.copy_h2d(hv, 0, v)

@@ -1,4 +1,636 @@
+// Grouped-query `Attention` step (src/aion/backend/cpu/exec/attention.zig:1444-1608).
+//
+// Semantics per output row (b, l, hq): keys [lo, hi) from the window
+// (src/aion/graph/graph.zig:160-167) clipped to the ring's retained span
+// (exec/attention.zig:1072-1075), logit = (q . k) * scale with optional soft cap,
+// softmax, out = sum p v / sum p, zeros for an empty range. The reference's softmax uses
+// a polynomial exp (kernels/fast_math.zig:79-92); this kernel uses the hardware exp2,
+// which is closer to the exact value than the polynomial is.
+//
+// Two kernels:
+//  * attn_decode_kernel — f16 K/V with Dk = Dv in {64, 128, 256}: the decode hot path.
+//    HBM-bound: K and V are read from global memory once per (b, l, kv head); the up to
+//    eight query heads of the group share them. A producer warp brings 64-key stages
+//    of K and V rows into shared memory with 1-D bulk (TMA) copies (row pitch padded by
+//    16 bytes so ldmatrix is conflict free); four consumer warps take 16 keys each.
+//    Both contractions run on the tensor cores in transposed form so that no
+//    accumulator row is padding: S^T[16 keys x 8 heads] = K . Q^T, then
+//    O^T[Dv x 8 heads] += V^T . P^T, with P^T obtained from the S^T fragment by one
+//    movmatrix transpose. An f32 q is split into two f16 terms so the logits keep f32
+//    accuracy. The context is split across CTAs (split-K); each writes an
+//    (unnormalised O, running max, sum) partial and the last CTA of a row to finish
+//    merges them by log-sum-exp — no second launch.
+//  * attn_generic_kernel — every other dtype / head size: one warp per key slice of a
+//    row, f32 arithmetic, same merge inside the CTA.
+#include <cfloat>
+
 #include "common.cuh"
+#include "ptx.cuh"
+
 namespace aion {
-int32_t attention_launch(AionCudaDevice*, const AionCudaAttention*) { return fail(AION_CUDA_UNSUPPORTED, "attention: not built yet"); }
+
+namespace {
+
+constexpr int KT = 64;              // keys per stage
+constexpr int CONSUMER_WARPS = 4;   // 16 keys each
+constexpr int THREADS = (CONSUMER_WARPS + 1) * 32;
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct AttnParams {
+  const void* q;
+  const void* k;
+  const void* v;
+  float* out;
+  const int32_t* positions;
+  const int32_t* lengths;
+  uint32_t B, L, Hq, Hkv, Dk, Dv, T;
+  uint32_t q_dtype, k_dtype, v_dtype;
+  uint32_t rolling;
+  uint32_t win_left, win_right, win_chunk;
+  float scale, soft_cap;
+  uint32_t splits;
+  uint32_t head_groups;  // ceil((Hq/Hkv) / 8)
+  float* partial;        // [unit][split][8 heads][Dv + 2]
+  int* tickets;          // [unit]
+  int* fault;
+};
+
+struct KeyRange {
+  uint32_t lo, hi;
+  bool bad;
+};
+
+// Window and ring clipping of one query row; flags inputs the reference rejects.
+__device__ __forceinline__ KeyRange key_range(const AttnParams& p, uint32_t b, uint32_t l) {
+  KeyRange r{0, 0, false};
+  int64_t valid_end = p.T;
+  if (p.lengths) {
+    const int32_t e = p.lengths[b];
+    if (e < 0) { r.bad = true; return r; }
+    valid_end = e;
+  }
+  if (!p.rolling && valid_end > (int64_t)p.T) { r.bad = true; return r; }
+  int64_t q_pos = l;
+  if (p.positions) {
+    const int32_t qp = p.positions[(uint64_t)b * p.L + l];
+    if (qp < 0) { r.bad = true; return r; }
+    q_pos = qp;
+  }
+  const int64_t anchor = p.win_chunk > 0 ? (q_pos / p.win_chunk) * p.win_chunk : q_pos;
+  const int64_t span = p.win_chunk > 0 ? p.win_chunk : 1;
+  int64_t lo = anchor - min(anchor, (int64_t)p.win_left);
+  int64_t hi = min(valid_end, anchor + span + (int64_t)p.win_right);
+  if (p.rolling && valid_end > (int64_t)p.T) lo = max(lo, valid_end - (int64_t)p.T);
+  if (hi > lo) {
+    r.lo = (uint32_t)lo;
+    r.hi = (uint32_t)hi;
+  }
+  return r;
+}
+
+__device__ __forceinline__ float soft_cap_logit(float x, float cap) { return cap > 0.0f ? cap * tanhf(x / cap) : x; }
+
+// ------------------------------------------------------------------------------------
+// tensor-core decode kernel
+// ------------------------------------------------------------------------------------
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                        uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+  uint32_t d;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+  return d;
+}
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+  const __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+template <int D>
+struct DecodeGeom {
+  static constexpr int PITCH = D * 2 + 16;            // bytes per K / V row in shared memory
+  static constexpr int TILE_BYTES = KT * PITCH;       // one of K, V
+  static constexpr int STAGE_BYTES = 2 * TILE_BYTES;  // K then V
+  static constexpr int QFRAG_BYTES = (D / 16) * 32 * 8;  // one of hi, lo
+  static constexpr int MERGE_BYTES = CONSUMER_WARPS * (8 * D + 16) * 4;
+  static constexpr int NS_MAX = (220 * 1024 - 2 * QFRAG_BYTES - 256) / STAGE_BYTES;
+  static constexpr int NS = NS_MAX > 4 ? 4 : NS_MAX;
+  static_assert(NS >= 2, "ring too small");
+  static_assert(MERGE_BYTES <= NS * STAGE_BYTES, "merge buffer reuses the ring");
+  static constexpr int OFF_QHI = NS * STAGE_BYTES;
+  static constexpr int OFF_QLO = OFF_QHI + QFRAG_BYTES;
+  static constexpr int OFF_BARS = OFF_QLO + QFRAG_BYTES;
+  static constexpr int SMEM_BYTES = OFF_BARS + 2 * NS * 8 + 32;
+};
+
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory"); }
+
+template <int D, bool QF32>
+__global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParams p) {
+  using G = DecodeGeom<D>;
+  constexpr int NS = G::NS;
+  extern __shared__ __align__(128) uint8_t smem[];
+  const uint32_t smem_base = ptx::smem_u32(smem);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, j = lane & 3;
+
+  // unit = (b, l, hkv, head group); split = blockIdx.y
+  uint32_t unit = blockIdx.x;
+  const uint32_t hg = unit % p.head_groups;
+  const uint32_t hkv = (unit / p.head_groups) % p.Hkv;
+  const uint32_t bl = unit / (p.head_groups * p.Hkv);
+  const uint32_t l = bl % p.L, b = bl / p.L;
+  const uint32_t split = blockIdx.y;
+  const uint32_t group = p.Hq / p.Hkv;
+  const uint32_t h0 = hkv * group + hg * 8;
+  const uint32_t nh = min(8u, group - hg * 8);
+
+  const uint32_t bar_full = smem_base + G::OFF_BARS;
+  const uint32_t bar_empty = bar_full + NS * 8;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + G::OFF_BARS + 2 * NS * 8);
+  int* last_flag = const_cast<int*>(abort_flag) + 1;
+
+  if (tid == 0) {
+    for (int s = 0; s < NS; s++) {
+      ptx::mbar_init(bar_full + 8 * s, 1);
+      ptx::mbar_init(bar_empty + 8 * s, CONSUMER_WARPS);
+    }
+    *abort_flag = 0;
+    *last_flag = 0;
+    ptx::fence_barrier_init();
+  }
+  __syncthreads();
+  ptx::pdl_launch_dependents();
+  // q, K, V, positions and lengths may all come from the previous kernel.
+  ptx::pdl_wait();
+
+  const KeyRange kr = key_range(p, b, l);
+  if (kr.bad && tid == 0) atomicExch(p.fault, FAULT_INVALID_ARGUMENT);
+  const uint32_t nkeys = kr.hi - kr.lo;
+  uint32_t per = (nkeys + p.splits - 1) / p.splits;
+  per = (per + 15) & ~15u;
+  const uint32_t my_lo = min(kr.hi, kr.lo + split * per);
+  const uint32_t my_hi = min(kr.hi, my_lo + per);
+  const uint32_t my_n = my_hi - my_lo;
+  const uint32_t ntiles = (my_n + KT - 1) / KT;
+
+  // running state of this lane's two heads (2j, 2j+1), log2 domain
+  float m_run[2] = {-INFINITY, -INFINITY};
+  float l_run[2] = {0.0f, 0.0f};
+  float acc[D / 16][4];
+#pragma unroll
+  for (int t = 0; t < D / 16; t++)
+#pragma unroll
+    for (int e = 0; e < 4; e++) acc[t][e] = 0.0f;
+
+  if (warp == CONSUMER_WARPS) {
+    // ---------------- producer ----------------
+    const __half* kbase = static_cast<const __half*>(p.k);
+    const __half* vbase = static_cast<const __half*>(p.v);
+    uint32_t issued = 0;
+    for (uint32_t it = 0; it < ntiles; it++) {
+      const uint32_t slot = it % NS;
+      if (*abort_flag) break;
+      if (it >= (uint32_t)NS && !ptx::mbar_wait_bounded(bar_empty + 8 * slot, ((it / NS) - 1) & 1)) {
+        if (lane == 0) {
+          atomicExch(p.fault, FAULT_WAIT_EXPIRED);
+          *abort_flag = 1;
+        }
+        break;
+      }
+      const uint32_t t0 = my_lo + it * KT;
+      const uint32_t cnt = min((uint32_t)KT, my_hi - t0);
+      const uint32_t full = bar_full + 8 * slot;
+      const uint32_t stage = smem_base + slot * G::STAGE_BYTES;
+      if (lane == 0) ptx::mbar_arrive_expect_tx(full, cnt * (uint32_t)(D * 2) * 2u);
+      __syncwarp();
+      for (uint32_t r = lane; r < cnt; r += 32) {
+        const uint32_t t = t0 + r;
+        const uint64_t row = ((uint64_t)b * p.T + (p.rolling ? t % p.T : t)) * p.Hkv + hkv;
+        ptx::bulk_g2s(stage + r * G::PITCH, kbase + row * D, D * 2, full);
+        ptx::bulk_g2s(stage + G::TILE_BYTES + r * G::PITCH, vbase + row * D, D * 2, full);
+      }
+      issued = it + 1;
+    }
+    if (*abort_flag)
+      for (uint32_t it = issued > (uint32_t)NS ? issued - NS : 0; it < issued; it++)
+        ptx::mbar_wait_bounded(bar_full + 8 * (it % NS), (it / NS) & 1, 1u << 16);
+  } else {
+    // ---------------- consumers ----------------
+    // Q^T fragments: for k-step s, lane (g, j) needs (q[g][16s+2j], q[g][16s+2j+1]) and
+    // the same at +8; rows g >= nh are zero. An f32 q is split hi + lo.
+    {
+      uint2* qhi = reinterpret_cast<uint2*>(smem + G::OFF_QHI);
+      uint2* qlo = reinterpret_cast<uint2*>(smem + G::OFF_QLO);
+      for (int i = tid; i < (D / 16) * 32; i += CONSUMER_WARPS * 32) {
+        const int s = i >> 5, ln = i & 31, gg = ln >> 2, jj = ln & 3;
+        float v[4] = {0, 0, 0, 0};
+        if ((uint32_t)gg < nh) {
+          const uint64_t off = (((uint64_t)b * p.L + l) * p.Hq + h0 + gg) * D + 16 * s + 2 * jj;
+          if (QF32) {
+            const float* qp = static_cast<const float*>(p.q) + off;
+            v[0] = qp[0]; v[1] = qp[1]; v[2] = qp[8]; v[3] = qp[9];
+          } else {
+            const __half* qp = static_cast<const __half*>(p.q) + off;
+            v[0] = __half2float(qp[0]); v[1] = __half2float(qp[1]); v[2] = __half2float(qp[8]); v[3] = __half2float(qp[9]);
+          }
+        }
+        const __half h0a = __float2half_rn(v[0]), h1a = __float2half_rn(v[1]), h2a = __float2half_rn(v[2]), h3a = __float2half_rn(v[3]);
+        qhi[i] = make_uint2(pack_half2(__half2float(h0a), __half2float(h1a)), pack_half2(__half2float(h2a), __half2float(h3a)));
+        if (QF32)
+          qlo[i] = make_uint2(pack_half2(v[0] - __half2float(h0a), v[1] - __half2float(h1a)),
+                              pack_half2(v[2] - __half2float(h2a), v[3] - __half2float(h3a)));
+      }
+    }
+    consumer_sync();
+
+    const float sc = (p.soft_cap > 0.0f) ? p.scale : p.scale * LOG2E;
+    bool ok = true;
+    for (uint32_t it = 0; it < ntiles; it++) {
+      const uint32_t slot = it % NS;
+      if (ok && (*abort_flag || !ptx::mbar_wait_bounded(bar_full + 8 * slot, (it / NS) & 1))) {
+        if (lane == 0 && !*abort_flag) {
+          atomicExch(p.fault, FAULT_WAIT_EXPIRED);
+          *abort_flag = 1;
+        }
+        ok = false;
+      }
+      const uint32_t t0 = my_lo + it * KT;
+      const uint32_t cnt = min((uint32_t)KT, my_hi - t0);
+      const uint32_t kst = smem_base + slot * G::STAGE_BYTES;
+      const uint32_t vst = kst + G::TILE_BYTES;
+      const uint32_t r0 = 16 * warp;
+      if (ok && r0 < cnt) {
+        const uint32_t valid = min(16u, cnt - r0);
+        if (valid < 16) {
+          // Rows past the range were not copied: clear them so stale bits cannot reach an MMA.
+          uint8_t* kt = smem + slot * G::STAGE_BYTES;
+          for (uint32_t i = lane; i < (16 - valid) * (D * 2 / 16); i += 32) {
+            const uint32_t rr = r0 + valid + i / (D * 2 / 16), cc = (i % (D * 2 / 16)) * 16;
+            *reinterpret_cast<uint4*>(kt + rr * G::PITCH + cc) = make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4*>(kt + G::TILE_BYTES + rr * G::PITCH + cc) = make_uint4(0, 0, 0, 0);
+          }
+          __syncwarp();
+        }
+        // ---- S^T[16 keys x 8 heads] = K . Q^T ----
+        float s[4] = {0, 0, 0, 0};
+        {
+          const uint32_t a_row = r0 + (lane & 7) + 8 * ((lane >> 3) & 1);
+          const uint32_t a_addr = kst + a_row * G::PITCH + (lane >> 4) * 16;
+          const uint2* qhi = reinterpret_cast<const uint2*>(smem + G::OFF_QHI);
+          const uint2* qlo = reinterpret_cast<const uint2*>(smem + G::OFF_QLO);
+#pragma unroll
+          for (int ks = 0; ks < D / 16; ks++) {
+            uint32_t a0, a1, a2, a3;
+            ldmatrix_x4(a_addr + ks * 32, a0, a1, a2, a3);
+            const uint2 bh = qhi[ks * 32 + lane];
+            mma_f16(s, a0, a1, a2, a3, bh.x, bh.y);
+            if (QF32) {
+              const uint2 bl2 = qlo[ks * 32 + lane];
+              mma_f16(s, a0, a1, a2, a3, bl2.x, bl2.y);
+            }
+          }
+        }
+        // s[0], s[1]: key g, heads 2j, 2j+1;  s[2], s[3]: key g+8.
+        const bool in0 = (uint32_t)g < valid, in1 = (uint32_t)(g + 8) < valid;
+        float lg[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+          float x = s[e] * sc;
+          if (p.soft_cap > 0.0f) x = soft_cap_logit(x, p.soft_cap) * LOG2E;
+          lg[e] = ((e < 2) ? in0 : in1) ? x : -INFINITY;
+        }
+        float mx[2] = {fmaxf(lg[0], lg[2]), fmaxf(lg[1], lg[3])};
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {
+          mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xFFFFFFFFu, mx[0], o));
+          mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xFFFFFFFFu, mx[1], o));
+        }
+        float alpha[2], pr[4];
+#pragma unroll
+        for (int hh = 0; hh < 2; hh++) {
+          const float m_new = fmaxf(m_run[hh], mx[hh]);  // finite: at least one key of the slice is valid
+          alpha[hh] = exp2f(m_run[hh] - m_new);           // exp2(-inf) = 0 on the first slice
+          m_run[hh] = m_new;
+        }
+        pr[0] = exp2f(lg[0] - m_run[0]);
+        pr[1] = exp2f(lg[1] - m_run[1]);
+        pr[2] = exp2f(lg[2] - m_run[0]);
+        pr[3] = exp2f(lg[3] - m_run[1]);
+        l_run[0] = l_run[0] * alpha[0] + pr[0] + pr[2];
+        l_run[1] = l_run[1] * alpha[1] + pr[1] + pr[3];
+        // P^T fragments (k = key, n = head) from the S^T accumulator layout by an 8x8 transpose.
+        const uint32_t pb0 = movmatrix_trans(pack_half2(pr[0], pr[1]));
+        const uint32_t pb1 = movmatrix_trans(pack_half2(pr[2], pr[3]));
+        // ---- O^T[Dv x 8 heads] = alpha * O^T + V^T . P^T ----
+        const uint32_t v_row = r0 + (lane & 7) + 8 * (lane >> 4);
+        const uint32_t v_addr = vst + v_row * G::PITCH + ((lane >> 3) & 1) * 16;
+#pragma unroll
+        for (int mt = 0; mt < D / 16; mt++) {
+          acc[mt][0] *= alpha[0];
+          acc[mt][1] *= alpha[1];
+          acc[mt][2] *= alpha[0];
+          acc[mt][3] *= alpha[1];
+          uint32_t a0, a1, a2, a3;
+          ldmatrix_x4_trans(v_addr + mt * 32, a0, a1, a2, a3);
+          mma_f16(acc[mt], a0, a1, a2, a3, pb0, pb1);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(bar_empty + 8 * slot);
+    }
+
+    // ---------------- fold the four warps (log-sum-exp), inside the drained ring ----------------
+#pragma unroll
+    for (int o = 4; o < 32; o <<= 1) {
+      l_run[0] += __shfl_xor_sync(0xFFFFFFFFu, l_run[0], o);
+      l_run[1] += __shfl_xor_sync(0xFFFFFFFFu, l_run[1], o);
+    }
+    consumer_sync();
+    float* mb = reinterpret_cast<float*>(smem) + (size_t)warp * (8 * D + 16);  // [8 heads][D] then m[8], l[8]
+#pragma unroll
+    for (int mt = 0; mt < D / 16; mt++) {
+      mb[(2 * j) * D + mt * 16 + g] = acc[mt][0];
+      mb[(2 * j + 1) * D + mt * 16 + g] = acc[mt][1];
+      mb[(2 * j) * D + mt * 16 + g + 8] = acc[mt][2];
+      mb[(2 * j + 1) * D + mt * 16 + g + 8] = acc[mt][3];
+    }
+    if (g == 0) {
+      mb[8 * D + 2 * j] = m_run[0];
+      mb[8 * D + 2 * j + 1] = m_run[1];
+      mb[8 * D + 8 + 2 * j] = l_run[0];
+      mb[8 * D + 8 + 2 * j + 1] = l_run[1];
+    }
+    consumer_sync();
+    const float* all = reinterpret_cast<const float*>(smem);
+    constexpr int WS = 8 * D + 16;
+    float* part = p.partial + ((uint64_t)unit * p.splits + split) * 8 * (D + 2);
+    float* orow = p.out + (((uint64_t)b * p.L + l) * p.Hq + h0) * D;
+    const bool direct = p.splits == 1;
+    for (int idx = tid; idx < 8 * D; idx += CONSUMER_WARPS * 32) {
+      const int h = idx / D, d = idx % D;
+      if ((uint32_t)h >= nh) continue;
+      float M = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < CONSUMER_WARPS; w++) M = fmaxf(M, all[w * WS + 8 * D + h]);
+      float o = 0.0f, lsum = 0.0f;
+#pragma unroll
+      for (int w = 0; w < CONSUMER_WARPS; w++) {
+        const float mw = all[w * WS + 8 * D + h];
+        const float f = (mw == -INFINITY) ? 0.0f : exp2f(mw - M);
+        o += all[w * WS + idx] * f;
+        lsum += all[w * WS + 8 * D + 8 + h] * f;
+      }
+      if (direct) {
+        if (lsum > 0.0f && isfinite(lsum)) orow[idx] = o / lsum;
+        else {
+          orow[idx] = 0.0f;
+          if (nkeys > 0 && !kr.bad && !*abort_flag) atomicExch(p.fault, FAULT_NONFINITE);
+        }
+      } else {
+        part[h * (D + 2) + d] = o;
+        if (d == 0) {
+          part[h * (D + 2) + D] = M;
+          part[h * (D + 2) + D + 1] = lsum;
+        }
+      }
+    }
+    if (!direct) {
+      // The last CTA of this row to arrive merges every split's partial.
+      __threadfence();
+      consumer_sync();
+      if (tid == 0) {
+        const int prev = atomicAdd(p.tickets + unit, 1);
+        const int last = (prev == (int)p.splits - 1);
+        if (last) p.tickets[unit] = 0;  // ready for the next launch
+        *last_flag = last;
+      }
+      consumer_sync();
+      if (*last_flag) {
+        __threadfence();
+        const float* pu = p.partial + (uint64_t)unit * p.splits * 8 * (D + 2);
+        for (int idx = tid; idx < 8 * D; idx += CONSUMER_WARPS * 32) {
+          const int h = idx / D, d = idx % D;
+          if ((uint32_t)h >= nh) continue;
+          float M = -INFINITY;
+          for (uint32_t s2 = 0; s2 < p.splits; s2++) M = fmaxf(M, __ldcg(pu + (s2 * 8 + h) * (D + 2) + D));
+          float o = 0.0f, lsum = 0.0f;
+          for (uint32_t s2 = 0; s2 < p.splits; s2++) {
+            const float* ps = pu + (s2 * 8 + h) * (D + 2);
+            const float ms = __ldcg(ps + D);
+            const float f = (ms == -INFINITY) ? 0.0f : exp2f(ms - M);
+            o += __ldcg(ps + d) * f;
+            lsum += __ldcg(ps + D + 1) * f;
+          }
+          if (lsum > 0.0f && isfinite(lsum)) orow[idx] = o / lsum;
+          else {
+            orow[idx] = 0.0f;
+            if (nkeys > 0 && !kr.bad) atomicExch(p.fault, FAULT_NONFINITE);
+          }
+        }
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// any-dtype, any-head-size kernel: one CTA per output row (b, l, hq), 4 warps stride the
+// keys, lanes stride the head dimension; per-warp online softmax, merged in shared memory.
+// ------------------------------------------------------------------------------------
+constexpr int GEN_WARPS = 4;
+constexpr int GEN_MAX_DV_PER_LANE = 32;  // Dv <= 1024
+
+__device__ __forceinline__ float load_as_float(const void* base, uint32_t dtype, uint64_t idx) {
+  return dtype == AION_CUDA_DTYPE_F32 ? static_cast<const float*>(base)[idx]
+                                      : __half2float(static_cast<const __half*>(base)[idx]);
+}
+
+__global__ void __launch_bounds__(GEN_WARPS * 32) attn_generic_kernel(const AttnParams p) {
+  extern __shared__ float gsm[];  // q[Dk], then per warp: acc[Dv], m, l
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t row = blockIdx.x;
+  const uint32_t hq = row % p.Hq;
+  const uint32_t l = (row / p.Hq) % p.L;
+  const uint32_t b = row / (p.Hq * p.L);
+  const uint32_t hkv = hq / (p.Hq / p.Hkv);
+  float* qs = gsm;
+  float* wbuf = gsm + p.Dk + (size_t)warp * (p.Dv + 2);
+
+  const KeyRange kr = key_range(p, b, l);
+  if (kr.bad && tid == 0) atomicExch(p.fault, FAULT_INVALID_ARGUMENT);
+  for (uint32_t i = tid; i < p.Dk; i += blockDim.x)
+    qs[i] = load_as_float(p.q, p.q_dtype, (((uint64_t)b * p.L + l) * p.Hq + hq) * p.Dk + i);
+  __syncthreads();
+
+  float m_run = -INFINITY, l_run = 0.0f;
+  float acc[GEN_MAX_DV_PER_LANE];
+#pragma unroll
+  for (int i = 0; i < GEN_MAX_DV_PER_LANE; i++) acc[i] = 0.0f;
+
+  for (uint32_t t = kr.lo + warp; t < kr.hi; t += GEN_WARPS) {
+    const uint64_t krow = ((uint64_t)b * p.T + (p.rolling ? t % p.T : t)) * p.Hkv + hkv;
+    float dot = 0.0f;
+    for (uint32_t i = lane; i < p.Dk; i += 32) dot = fmaf(qs[i], load_as_float(p.k, p.k_dtype, krow * p.Dk + i), dot);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xFFFFFFFFu, dot, o);
+    const float lg = soft_cap_logit(dot * p.scale, p.soft_cap) * LOG2E;
+    const float m_new = fmaxf(m_run, lg);
+    const float alpha = exp2f(m_run - m_new);
+    const float pr = exp2f(lg - m_new);
+    l_run = l_run * alpha + pr;
+    m_run = m_new;
+#pragma unroll
+    for (int i = 0; i < GEN_MAX_DV_PER_LANE; i++) {
+      const uint32_t d = lane + 32 * i;
+      if (d < p.Dv) acc[i] = acc[i] * alpha + pr * load_as_float(p.v, p.v_dtype, krow * p.Dv + d);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < GEN_MAX_DV_PER_LANE; i++) {
+    const uint32_t d = lane + 32 * i;
+    if (d < p.Dv) wbuf[d] = acc[i];
+  }
+  if (lane == 0) {
+    wbuf[p.Dv] = m_run;
+    wbuf[p.Dv + 1] = l_run;
+  }
+  __syncthreads();
+  float* orow = p.out + (((uint64_t)b * p.L + l) * p.Hq + hq) * p.Dv;
+  const float* base = gsm + p.Dk;
+  float M = -INFINITY;
+  for (int w = 0; w < GEN_WARPS; w++) M = fmaxf(M, base[(size_t)w * (p.Dv + 2) + p.Dv]);
+  float lsum = 0.0f;
+  for (int w = 0; w < GEN_WARPS; w++) {
+    const float mw = base[(size_t)w * (p.Dv + 2) + p.Dv];
+    lsum += (mw == -INFINITY) ? 0.0f : base[(size_t)w * (p.Dv + 2) + p.Dv + 1] * exp2f(mw - M);
+  }
+  const bool good = lsum > 0.0f && isfinite(lsum);
+  if (!good && kr.hi > kr.lo && !kr.bad && tid == 0) atomicExch(p.fault, FAULT_NONFINITE);
+  for (uint32_t d = tid; d < p.Dv; d += blockDim.x) {
+    float o = 0.0f;
+    for (int w = 0; w < GEN_WARPS; w++) {
+      const float mw = base[(size_t)w * (p.Dv + 2) + p.Dv];
+      if (mw != -INFINITY) o += base[(size_t)w * (p.Dv + 2) + d] * exp2f(mw - M);
+    }
+    orow[d] = good ? o / lsum : 0.0f;
+  }
+}
+
+template <int D, bool QF32>
+int32_t launch_decode(AionCudaDevice* dev, const AttnParams& p, uint32_t units) {
+  using G = DecodeGeom<D>;
+  auto kernel = attn_decode_kernel<D, QF32>;
+  static bool configured[16] = {};
+  if (!configured[dev->ordinal & 15]) {
+    AION_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM_BYTES));
+    configured[dev->ordinal & 15] = true;
+  }
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(units, p.splits);
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = G::SMEM_BYTES;
+  cfg.stream = dev->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  AION_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, p));
+  return AION_CUDA_OK;
+}
+
+}  // namespace
+
+int32_t attention_launch(AionCudaDevice* dev, const AionCudaAttention* s) {
+  AttnParams p{};
+  const uint64_t B = s->batch, L = s->l_q, Hq = s->h_q, Hkv = s->h_kv, Dk = s->d_k, Dv = s->d_v, T = s->t_cap;
+  if (B > 0x7FFFFFFF || L > 0x7FFFFFFF || Hq > 65535 || Dk > 65535 || Dv > 65535 || T > 0x7FFFFFFF || B * L * Hq > 0x7FFFFFFF)
+    return fail(AION_CUDA_UNSUPPORTED, "attention: a dimension is beyond what the kernels index");
+  auto esz = [](uint32_t dt) { return dt == AION_CUDA_DTYPE_F32 ? 4u : 2u; };
+  const uint8_t *q, *k, *v;
+  float* out;
+  if (int32_t st = resolve(s->q, B * L * Hq * Dk * esz(s->q_dtype), "attention.q", &q)) return st;
+  if (int32_t st = resolve(s->k, B * T * Hkv * Dk * esz(s->k_dtype), "attention.k", &k)) return st;
+  if (int32_t st = resolve(s->v, B * T * Hkv * Dv * esz(s->v_dtype), "attention.v", &v)) return st;
+  if (int32_t st = resolve(s->out, B * L * Hq * Dv * sizeof(float), "attention.out", &out)) return st;
+  p.q = q;
+  p.k = k;
+  p.v = v;
+  p.out = out;
+  if (s->query_positions.handle) {
+    if (int32_t st = resolve(s->query_positions, B * L * 4, "attention.query_positions", &p.positions)) return st;
+  }
+  if (s->kv_lengths.handle) {
+    if (int32_t st = resolve(s->kv_lengths, B * 4, "attention.kv_lengths", &p.lengths)) return st;
+  }
+  p.B = (uint32_t)B; p.L = (uint32_t)L; p.Hq = (uint32_t)Hq; p.Hkv = (uint32_t)Hkv;
+  p.Dk = (uint32_t)Dk; p.Dv = (uint32_t)Dv; p.T = (uint32_t)T;
+  p.q_dtype = s->q_dtype; p.k_dtype = s->k_dtype; p.v_dtype = s->v_dtype;
+  p.rolling = s->rolling ? 1u : 0u;
+  p.win_left = s->window_left; p.win_right = s->window_right; p.win_chunk = s->window_chunk;
+  p.scale = s->scale;
+  p.soft_cap = s->soft_cap;
+  p.fault = dev->fault_dev;
+
+  const bool f16kv = s->k_dtype == AION_CUDA_DTYPE_F16 && s->v_dtype == AION_CUDA_DTYPE_F16;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15) == 0 &&
+                       (reinterpret_cast<uintptr_t>(q) & 3) == 0;
+  const bool tensor_path = f16kv && aligned && Dk == Dv && (Dk == 64 || Dk == 128 || Dk == 256) && !(s->flags & 1u);
+  if (tensor_path) {
+    const uint32_t group = p.Hq / p.Hkv;
+    p.head_groups = (group + 7) / 8;
+    const uint64_t units = B * L * Hkv * p.head_groups;
+    if (units > 0x7FFFFFFF) return fail(AION_CUDA_UNSUPPORTED, "attention: too many rows");
+    // Split the context until the grid covers the SMs about twice; a split is at least 64 keys.
+    // Upper bound of any row's keys: the window span clipped to the cache (or ring) length.
+    uint64_t max_keys = T;
+    const uint64_t span = (uint64_t)(s->window_chunk ? s->window_chunk : 1) + s->window_left + s->window_right;
+    if (s->window_left != AION_CUDA_WINDOW_UNBOUNDED && s->window_right != AION_CUDA_WINDOW_UNBOUNDED && span < max_keys)
+      max_keys = span;
+    uint64_t splits = 1;
+    const uint64_t want = 2ull * dev->sm_count;
+    if (units < want) splits = (want + units - 1) / units;
+    const uint64_t max_splits = (max_keys + KT - 1) / KT;
+    if (splits > max_splits) splits = max_splits;
+    if (splits > 256) splits = 256;
+    if (splits < 1) splits = 1;
+    if (dev->attn_split_override) splits = dev->attn_split_override;
+    p.splits = (uint32_t)splits;
+    if (splits > 1) {
+      const size_t part_bytes = (size_t)units * splits * 8 * (Dk + 2) * sizeof(float);
+      if (int32_t st = dev->reserve_scratch(part_bytes)) return st;
+      if (int32_t st = dev->reserve_tickets(units)) return st;
+      p.partial = static_cast<float*>(dev->scratch);
+      p.tickets = dev->tickets;
+    }
+    const bool qf32 = s->q_dtype == AION_CUDA_DTYPE_F32;
+    switch (Dk) {
+      case 64: return qf32 ? launch_decode<64, true>(dev, p, (uint32_t)units) : launch_decode<64, false>(dev, p, (uint32_t)units);
+      case 128: return qf32 ? launch_decode<128, true>(dev, p, (uint32_t)units) : launch_decode<128, false>(dev, p, (uint32_t)units);
+      default: return qf32 ? launch_decode<256, true>(dev, p, (uint32_t)units) : launch_decode<256, false>(dev, p, (uint32_t)units);
+    }
+  }
+  if (Dv > 32 * GEN_MAX_DV_PER_LANE) return fail(AION_CUDA_UNSUPPORTED, "attention: Dv = %llu (any-shape kernel takes <= 1024)", (unsigned long long)Dv);
+  const size_t smem = (Dk + GEN_WARPS * (Dv + 2)) * sizeof(float);
+  if (smem > 48 * 1024) return fail(AION_CUDA_UNSUPPORTED, "attention: head dimensions %llu / %llu exceed the any-shape kernel", (unsigned long long)Dk, (unsigned long long)Dv);
+  p.splits = 1;
+  attn_generic_kernel<<<(unsigned)(B * L * Hq), GEN_WARPS * 32, smem, dev->stream>>>(p);
+  AION_CUDA_TRY(cudaGetLastError());
+  return AION_CUDA_OK;
+}
+
 }  // namespace aion

@@ -59,9 +59,15 @@ struct AionCudaDevice {
   size_t scratch_bytes = 0;
   // Tuning override (environment AION_CUDA_GEMV_SPLIT): K-split of the tiled GEMV, 0 = automatic.
   uint32_t gemv_split_override = 0;
+  // Same for the decode attention's context split (AION_CUDA_ATTN_SPLIT), 0 = automatic.
+  uint32_t attn_split_override = 0;
+  // One arrival counter per attention row for the split-K merge; zero between launches.
+  int* tickets = nullptr;
+  size_t tickets_cap = 0;
 
   int32_t make_current() const;
   int32_t reserve_scratch(size_t bytes);
+  int32_t reserve_tickets(size_t count);
   // Reads the status word back (call after the stream has been synchronized).
   int32_t check_fault();
 };

@@ -59,6 +59,19 @@ int32_t AionCudaDevice::reserve_scratch(size_t bytes) {
   return AION_CUDA_OK;
 }
 
+int32_t AionCudaDevice::reserve_tickets(size_t count) {
+  if (count <= tickets_cap) return AION_CUDA_OK;
+  AION_CUDA_TRY(cudaStreamSynchronize(stream));
+  if (tickets) AION_CUDA_TRY(cudaFree(tickets));
+  tickets = nullptr;
+  tickets_cap = 0;
+  size_t want = count < 1024 ? 1024 : count + (count >> 1);
+  AION_CUDA_TRY(cudaMalloc(&tickets, want * sizeof(int)));
+  AION_CUDA_TRY(cudaMemsetAsync(tickets, 0, want * sizeof(int), stream));
+  tickets_cap = want;
+  return AION_CUDA_OK;
+}
+
 int32_t AionCudaDevice::check_fault() {
   // The stream is idle here, so a plain copy of one word is enough.
   AION_CUDA_TRY(cudaMemcpy(fault_host, fault_dev, sizeof(int), cudaMemcpyDeviceToHost));
@@ -124,6 +137,10 @@ int32_t aion_cuda_device_create(int32_t ordinal, AionCudaDevice** out) {
     const int v = std::atoi(e2);
     if (v == 1 || v == 2 || v == 4 || v == 8) d->gemv_split_override = (uint32_t)v;
   }
+  if (const char* e3 = std::getenv("AION_CUDA_ATTN_SPLIT")) {
+    const int v = std::atoi(e3);
+    if (v >= 1 && v <= 256) d->attn_split_override = (uint32_t)v;
+  }
   *out = d;
   return AION_CUDA_OK;
 }
@@ -136,6 +153,7 @@ void aion_cuda_device_destroy(AionCudaDevice* dev) {
     cudaStreamDestroy(dev->own_stream);
   }
   if (dev->scratch) cudaFree(dev->scratch);
+  if (dev->tickets) cudaFree(dev->tickets);
   if (dev->fault_dev) cudaFree(dev->fault_dev);
   if (dev->fault_host) cudaFreeHost(dev->fault_host);
   delete dev;

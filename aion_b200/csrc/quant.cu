@@ -36,9 +36,8 @@ __global__ void quantize_blocks_kernel(const float* __restrict__ values, uint8_t
     // src/aion/storage/quantize.zig:83-103: codes are chosen against the stored f16 scale.
     const float scale = (absmax == 0.0f) ? 1.0f : __fdiv_rn(absmax, 127.0f);
     const __half sh = __float2half_rn(scale);
-    const uint16_t bits = __half_as_ushort(sh);
-    dst[0] = bits & 0xFF;
-    dst[1] = bits >> 8;
+    // Blocks are 2-byte aligned (even block sizes on an aligned tensor).
+    *reinterpret_cast<__half*>(dst) = sh;
     const float eff = __half2float(sh);
     const float inv = (absmax == 0.0f || eff == 0.0f) ? 0.0f : __fdiv_rn(1.0f, eff);
     for (int t = 0; t < QK; t++) {
@@ -49,9 +48,7 @@ __global__ void quantize_blocks_kernel(const float* __restrict__ values, uint8_t
   } else {
     // src/aion/backend/cpu/test_cpu_kernels.zig:490-523: divide by the unrounded scale.
     const float scale = (absmax == 0.0f) ? 1.0f : __fdiv_rn(absmax, 7.0f);
-    const uint16_t bits = __half_as_ushort(__float2half_rn(scale));
-    dst[0] = bits & 0xFF;
-    dst[1] = bits >> 8;
+    *reinterpret_cast<__half*>(dst) = __float2half_rn(scale);
     for (int i2 = 0; i2 < 16; i2++) {
       int lo = (int)roundf(__fdiv_rn(v[(2 * i2) * st], scale));
       int hi = (int)roundf(__fdiv_rn(v[(2 * i2 + 1) * st], scale));
@@ -172,6 +169,8 @@ int32_t aion_cuda_quantize(AionCudaDevice* dev, uint32_t dtype, const AionCudaOp
   uint8_t* o;
   if (int32_t st = resolve(*values, s * sizeof(float), "quantize.values", &v)) return st;
   if (int32_t st = resolve(*out, nblocks * block_bytes_of(dtype), "quantize.out", &o)) return st;
+  if ((reinterpret_cast<uintptr_t>(v) & 3) || (reinterpret_cast<uintptr_t>(o) & 1))
+    return fail(AION_CUDA_INVALID_ARGUMENT, "quantize: values must be 4-byte aligned, out 2-byte aligned");
   if (int32_t st = dev->make_current()) return st;
   const int threads = 128;
   const unsigned grid = (unsigned)ceil_div(nblocks, threads);

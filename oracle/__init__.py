@@ -157,3 +157,32 @@ def attention(q, k, v, *, scale, positions=None, kv_lengths=None, left=UNBOUNDED
         C.c_float(soft_cap), int(rolling), int(exact))
     _check(rc, "attention")
     return out
+
+
+# ---- timed CPU baseline (threaded port of the reference kernels) ------------------------
+def fast_has_vnni() -> bool:
+    return bool(lib().aion_oracle_fast_has_vnni())
+
+
+def fast_max_threads() -> int:
+    return int(lib().aion_oracle_fast_max_threads())
+
+
+def fast_matmul_q(dtype, a, b, m, n, k, *, alpha=1.0, beta=0.0, c=None, threads=0):
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    b = np.ascontiguousarray(b, dtype=np.uint8)
+    c = np.zeros(m * n, dtype=np.float32) if c is None else c
+    rc = lib().aion_oracle_fast_matmul_q(dtype, C.c_uint64(m), C.c_uint64(n), C.c_uint64(k), C.c_float(alpha),
+                                         C.c_float(beta), _p(c), _p(a), _p(b), threads)
+    _check(rc, "fast_matmul_q")
+    return c.reshape(m, n)
+
+
+def fast_matmul_nt_q8(a, b, m, n, k, *, alpha=1.0, beta=0.0, c=None, threads=0):
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    b = np.ascontiguousarray(b, dtype=np.uint8)
+    c = np.zeros(m * n, dtype=np.float32) if c is None else c
+    rc = lib().aion_oracle_fast_matmul_nt_q8(C.c_uint64(m), C.c_uint64(n), C.c_uint64(k), C.c_float(alpha),
+                                             C.c_float(beta), _p(c), _p(a), _p(b), threads)
+    _check(rc, "fast_matmul_nt_q8")
+    return c.reshape(m, n)

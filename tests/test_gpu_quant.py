@@ -1,0 +1,67 @@
+"""Device quantizer / dequantizer / re-layout against the oracle: byte- and bit-exact."""
+import numpy as np
+import pytest
+
+import oracle
+from aion_b200 import backend as ab
+from aion_b200 import capi
+from tests import refdata as rd
+
+pytestmark = pytest.mark.gpu
+
+
+def test_q8_reference_vector(backend):
+    vals, expect = rd.quantize_zig_q8_kn()  # src/aion/storage/quantize.zig:105-137
+    assert np.array_equal(ab.quantize(backend, capi.DTYPE_Q8_0, vals, 0), expect)
+
+
+@pytest.mark.parametrize("dtype", [capi.DTYPE_Q8_0, capi.DTYPE_Q4_0])
+@pytest.mark.parametrize("shape,axis", [((2048, 256), 0), ((256, 2048), 1), ((3, 64, 40), 1), ((32, 1), 0)])
+def test_quantize_bytes_equal_oracle(backend, dtype, shape, axis):
+    rng = np.random.default_rng(sum(shape) + axis)
+    w = (rng.standard_normal(shape) * 0.02).astype(np.float32)
+    w.reshape(-1)[: min(64, w.size)] = 0.0
+    # exact half-way quotients and the clamp edges
+    w.reshape(-1)[-1] = np.abs(w).max() * 2
+    got = ab.quantize(backend, dtype, w, axis)
+    assert np.array_equal(got, oracle.quantize(dtype, w, axis))
+
+
+@pytest.mark.parametrize("dtype", [capi.DTYPE_Q8_0, capi.DTYPE_Q4_0])
+def test_dequantize_bit_exact(backend, dtype):
+    w = rd.synth_weights(512, 2048)
+    packed = oracle.quantize(dtype, w, 1)
+    got = ab.dequantize(backend, dtype, packed)
+    want = oracle.dequant(dtype, packed)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def test_dequantize_every_code_and_scale_class(backend):
+    # every q8 code and every nibble against normal, subnormal and large f16 scales
+    for dtype, bb in ((capi.DTYPE_Q8_0, 34), (capi.DTYPE_Q4_0, 18)):
+        blocks = bytearray()
+        for sbits in (0x0001, 0x03FF, 0x0400, 0x211F, 0x3C00, 0x7BFF, 0x8001, 0xA11F):
+            for base in range(0, 256, 32):
+                payload = bytes((base + t) & 0xFF for t in range(bb - 2))
+                blocks += int(sbits).to_bytes(2, "little") + payload
+        packed = np.frombuffer(bytes(blocks), dtype=np.uint8)
+        got = ab.dequantize(backend, dtype, packed)
+        assert np.array_equal(got.view(np.uint32), oracle.dequant(dtype, packed).view(np.uint32))
+
+
+@pytest.mark.parametrize("order", range(1, 6))
+def test_relayout_matches_oracle_and_inverts(backend, order):
+    n, k = 96, 256
+    rows = oracle.quantize(oracle.Q8_0, rd.synth_weights(n, k), 1)
+    got = ab.relayout_q8(backend, order, n, k, rows)
+    assert np.array_equal(got, oracle.relayout_q8(order, n, k, rows))
+    assert np.array_equal(ab.relayout_q8(backend, order, n, k, got, inverse=True), rows)
+
+
+def test_quantize_rejects_bad_arguments(backend):
+    with pytest.raises(ab.BackendError) as e:
+        ab.quantize(backend, capi.DTYPE_Q8_0, np.zeros((33, 4), dtype=np.float32), 0)
+    assert e.value.name == "InvalidArgument"
+    with pytest.raises(ab.BackendError) as e:
+        ab.quantize(backend, capi.DTYPE_F16, np.zeros((32, 4), dtype=np.float32), 0)
+    assert e.value.name == "Unsupported"

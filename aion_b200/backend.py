@@ -329,6 +329,19 @@ class CudaSession:
                 # (src/aion/runtime/executable.zig:355-357).
                 raise BackendError(capi.UNSUPPORTED, f"step {type(step).__name__} is outside this backend")
 
+    def record(self, program: Sequence[object]) -> "RecordedProgram":
+        """Record the steps once into a replayable device program (one launch per replay).
+
+        Steps that need scratch must have executed once before (run `execute` first)."""
+        _check(self._lib.aion_cuda_record_begin(self.backend._h))
+        h = C.c_void_p()
+        try:
+            self.execute(program)
+        finally:
+            st = self._lib.aion_cuda_record_end(self.backend._h, C.byref(h))
+        _check(st)
+        return RecordedProgram(self.backend, h)
+
     def retire_resources(self) -> None:
         self.backend.sync()
 
@@ -406,6 +419,22 @@ class CudaSession:
                              window_left=s.window.left, window_right=s.window.right, window_chunk=s.window.chunk,
                              flags=0)
         _check(self._lib.aion_cuda_attention(self.backend._h, C.byref(rec)))
+
+
+class RecordedProgram:
+    """A recorded step list (a CUDA graph) bound to the buffers it was recorded with."""
+
+    def __init__(self, backend: CudaBackend, handle):
+        self.backend = backend
+        self._h = handle
+
+    def launch(self) -> None:
+        _check(self.backend._lib.aion_cuda_program_launch(self.backend._h, self._h))
+
+    def destroy(self) -> None:
+        if self._h:
+            self.backend._lib.aion_cuda_program_destroy(self.backend._h, self._h)
+            self._h = None
 
 
 # ---- storage-level helpers (Context.quantize / weight_layout on the device) -----------

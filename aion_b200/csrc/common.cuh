@@ -65,6 +65,9 @@ struct AionCudaDevice {
   int* tickets = nullptr;
   size_t tickets_cap = 0;
 
+  // Between aion_cuda_record_begin and aion_cuda_record_end.
+  bool recording = false;
+
   int32_t make_current() const;
   int32_t reserve_scratch(size_t bytes);
   int32_t reserve_tickets(size_t count);

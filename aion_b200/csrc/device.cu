@@ -47,6 +47,7 @@ int32_t AionCudaDevice::make_current() const {
 
 int32_t AionCudaDevice::reserve_scratch(size_t bytes) {
   if (bytes <= scratch_bytes) return AION_CUDA_OK;
+  if (recording) return fail(AION_CUDA_INVALID_ARGUMENT, "a recorded step needs %llu bytes of scratch that are not reserved yet: run it once before recording", (unsigned long long)bytes);
   // Earlier launches may still read the old buffer.
   AION_CUDA_TRY(cudaStreamSynchronize(stream));
   if (scratch) AION_CUDA_TRY(cudaFree(scratch));
@@ -61,6 +62,7 @@ int32_t AionCudaDevice::reserve_scratch(size_t bytes) {
 
 int32_t AionCudaDevice::reserve_tickets(size_t count) {
   if (count <= tickets_cap) return AION_CUDA_OK;
+  if (recording) return fail(AION_CUDA_INVALID_ARGUMENT, "a recorded attention step needs arrival counters that are not reserved yet: run it once before recording");
   AION_CUDA_TRY(cudaStreamSynchronize(stream));
   if (tickets) AION_CUDA_TRY(cudaFree(tickets));
   tickets = nullptr;
@@ -187,6 +189,66 @@ int32_t aion_cuda_sync(AionCudaDevice* dev) {
   if (int32_t st = dev->make_current()) return st;
   AION_CUDA_TRY(cudaStreamSynchronize(dev->stream));
   return dev->check_fault();
+}
+
+struct AionCudaProgram {
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+};
+
+int32_t aion_cuda_record_begin(AionCudaDevice* dev) {
+  if (!dev) return fail(AION_CUDA_INVALID_ARGUMENT, "record_begin: null device");
+  if (dev->recording) return fail(AION_CUDA_INVALID_ARGUMENT, "record_begin: already recording");
+  if (int32_t st = dev->make_current()) return st;
+  AION_CUDA_TRY(cudaStreamBeginCapture(dev->stream, cudaStreamCaptureModeThreadLocal));
+  dev->recording = true;
+  return AION_CUDA_OK;
+}
+
+int32_t aion_cuda_record_end(AionCudaDevice* dev, AionCudaProgram** out) {
+  if (!dev || !out) return fail(AION_CUDA_INVALID_ARGUMENT, "record_end: null argument");
+  *out = nullptr;
+  if (!dev->recording) return fail(AION_CUDA_INVALID_ARGUMENT, "record_end: not recording");
+  dev->recording = false;
+  cudaGraph_t graph = nullptr;
+  cudaError_t e = cudaStreamEndCapture(dev->stream, &graph);
+  if (e != cudaSuccess || !graph) {
+    cudaGetLastError();
+    return fail(AION_CUDA_INTERNAL_ERROR, "record_end: the recording was invalidated (%s); a recorded step may have "
+                "allocated or synchronized", cudaGetErrorString(e));
+  }
+  AionCudaProgram* p = new (std::nothrow) AionCudaProgram();
+  if (!p) {
+    cudaGraphDestroy(graph);
+    return fail(AION_CUDA_OUT_OF_MEMORY, "record_end: host allocation failed");
+  }
+  p->graph = graph;
+  e = cudaGraphInstantiate(&p->exec, graph, 0);
+  if (e != cudaSuccess) {
+    cudaGraphDestroy(graph);
+    delete p;
+    return cuda_fail(e, "cudaGraphInstantiate");
+  }
+  *out = p;
+  return AION_CUDA_OK;
+}
+
+int32_t aion_cuda_program_launch(AionCudaDevice* dev, AionCudaProgram* prog) {
+  if (!dev || !prog || !prog->exec) return fail(AION_CUDA_INVALID_ARGUMENT, "program_launch: null argument");
+  if (int32_t st = dev->make_current()) return st;
+  AION_CUDA_TRY(cudaGraphLaunch(prog->exec, dev->stream));
+  return AION_CUDA_OK;
+}
+
+void aion_cuda_program_destroy(AionCudaDevice* dev, AionCudaProgram* prog) {
+  if (!prog) return;
+  if (dev) {
+    cudaSetDevice(dev->ordinal);
+    cudaStreamSynchronize(dev->stream);
+  }
+  if (prog->exec) cudaGraphExecDestroy(prog->exec);
+  if (prog->graph) cudaGraphDestroy(prog->graph);
+  delete prog;
 }
 
 int32_t aion_cuda_last_error(char* buf, size_t cap, size_t* len) {

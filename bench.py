@@ -1,0 +1,355 @@
+#!/usr/bin/env python
+"""Benchmark of the decode GEMV hot path (the `MatMul` step with q4_0 weights).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (the q4 GEMV of the benchmark configurations): x f32 [M=1, K=2048] ~ N(0,1),
+W [K=2048, N=8192] ~ N(0,0.02) quantized to q4_0 [K/32][N] by the device quantizer
+(byte-exact with the reference's q4 packer), y = x . W. One weight matrix is 9.4 MB and
+would sit in the 126 MB L2, so a step walks COPIES = 256 distinct matrices (2.4 GB):
+every launch reads weights that are not cached. One step = one replay of a recorded
+program of 256 `aion_cuda_matmul` steps = one pass over the batch.
+
+Metric: GB/s of algorithmic bytes (weights once + x + y per launch) — higher is better.
+  value  : inputs resident in HBM, device-timed (CUDA events on the launching stream).
+  e2e    : the same pass driven through the C ABI from HOST buffers: per step one
+           aion_cuda_h2d of the batch's activations (pinned), the program, one
+           aion_cuda_d2h of the results.
+  N > 1  : replicas only (independent GEMVs share nothing): every rank runs the same
+           pass on its GPU, no collective on the data path; value = sum of the ranks'
+           bytes / max time.
+--impl reference times the reference's CPU path for the same step (a threaded port of its
+kernels: the reference is Zig and cannot be built here) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+M, N, K = 1, 8192, 2048
+COPIES = 256
+W_BYTES = (K // 32) * N * 18
+BYTES_PER_LAUNCH = W_BYTES + 4 * M * K + 4 * M * N
+WORKLOAD = f"q4_0 GEMV (MatMul step) M={M} N={N} K={K}, {COPIES} distinct weight matrices per step"
+METRIC = "q4 GEMV HBM GB/s"
+
+# DRAM bytes per launch of the GEMV kernel from an ncu capture of this workload
+# (dram__bytes_read.sum + dram__bytes_write.sum; summary under profiles/). None until captured.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def measured_peak_gbs():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU while a region runs (read-only NVML)."""
+
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+               0x80: "hw_power_brake_slowdown"}
+
+    def __init__(self, torch_device_index: int):
+        self.samples = []
+        self.reasons = set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        self._h = None
+        try:
+            import pynvml
+            import torch
+
+            pynvml.nvmlInit()
+            uuid = str(torch.cuda.get_device_properties(torch_device_index).uuid)
+            if not uuid.startswith("GPU-"):
+                uuid = "GPU-" + uuid
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode() if hasattr(uuid, "encode") else uuid)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self._h = None
+
+    def _run(self):
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
+                mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self._h))
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.01)
+
+    def __enter__(self):
+        if self._h is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": 0}
+        return {"sm_mhz": int(np.median(self.samples)), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from aion_b200 import capi
+    from aion_b200.backend import BackendError, CudaBackend
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    torch.cuda.set_device(local_rank)
+    backend = CudaBackend(local_rank)
+    lib, dev = backend._lib, backend.handle
+    mem = backend.device_memory
+
+    def chk(st):
+        if st != capi.OK:
+            raise BackendError(st, capi.last_error())
+
+    # ---- synthetic inputs, resident in HBM ------------------------------------------------
+    w_arena = mem.alloc(COPIES * W_BYTES, 256)
+    x_dev = mem.alloc(COPIES * M * K * 4, 256)
+    y_dev = mem.alloc(COPIES * M * N * 4, 256)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(1234 + rank)
+    shape = (C.c_uint64 * 2)(K, N)
+    for i in range(COPIES):
+        w = torch.randn((K, N), generator=gen, device="cuda", dtype=torch.float32) * 0.02
+        torch.cuda.synchronize()
+        src = capi.Operand(w.data_ptr(), 0, w.numel() * 4)
+        dst = capi.Operand(w_arena, i * W_BYTES, W_BYTES)
+        chk(lib.aion_cuda_quantize(dev, capi.DTYPE_Q4_0, C.byref(src), shape, 2, 0, C.byref(dst)))
+        backend.sync()
+    gen.manual_seed(5678 + rank)
+    x_host = torch.randn((COPIES, M, K), generator=torch.Generator().manual_seed(5678 + rank), dtype=torch.float32).pin_memory()
+    y_host = torch.empty((COPIES, M, N), dtype=torch.float32).pin_memory()
+    chk(lib.aion_cuda_h2d(dev, x_dev, 0, C.c_void_p(x_host.data_ptr()), x_host.numel() * 4))
+
+    steps_rec = []
+    for i in range(COPIES):
+        steps_rec.append(capi.MatMul(
+            c=capi.Operand(y_dev, i * M * N * 4, M * N * 4), a=capi.Operand(x_dev, i * M * K * 4, M * K * 4),
+            b=capi.Operand(w_arena, i * W_BYTES, W_BYTES), b_dtype=capi.DTYPE_Q4_0, flags=capi.MATMUL_AUTO,
+            m=M, n=N, k=K, lda=0, ldb=0, ldc=0, alpha=1.0, beta=0.0))
+
+    def issue_pass():
+        for rec in steps_rec:
+            chk(lib.aion_cuda_matmul(dev, C.byref(rec)))
+
+    issue_pass()  # first use of the kernels, outside any recording
+    backend.sync()
+    chk(lib.aion_cuda_record_begin(dev))
+    issue_pass()
+    prog = C.c_void_p()
+    chk(lib.aion_cuda_record_end(dev, C.byref(prog)))
+
+    stream = torch.cuda.ExternalStream(int(lib.aion_cuda_get_stream(dev)), device=torch.device("cuda", local_rank))
+    ev0 = torch.cuda.Event(enable_timing=True)
+    ev1 = torch.cuda.Event(enable_timing=True)
+
+    def barrier():
+        backend.sync()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+
+    for _ in range(max(args.warmup, 3)):
+        chk(lib.aion_cuda_program_launch(dev, prog))
+    barrier()
+    with ClockSampler(local_rank) as clocks:
+        ev0.record(stream)
+        for _ in range(args.steps):
+            chk(lib.aion_cuda_program_launch(dev, prog))
+        ev1.record(stream)
+        backend.sync()
+        torch.cuda.synchronize()
+    elapsed_ms = ev0.elapsed_time(ev1)
+    if world > 1:
+        t = torch.tensor([elapsed_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        max_ms = float(t.item())
+    else:
+        max_ms = elapsed_ms
+    ms_per_step = max_ms / args.steps
+    bytes_per_step = COPIES * BYTES_PER_LAUNCH
+    value = world * bytes_per_step / (ms_per_step * 1e-3) / 1e9
+
+    # ---- end to end from host buffers through the C ABI -------------------------------------
+    e2e_steps = max(3, min(args.steps, 200))
+    h2d_bytes = x_host.numel() * 4
+    d2h_bytes = y_host.numel() * 4
+
+    def e2e_step():
+        chk(lib.aion_cuda_h2d(dev, x_dev, 0, C.c_void_p(x_host.data_ptr()), h2d_bytes))
+        chk(lib.aion_cuda_program_launch(dev, prog))
+        chk(lib.aion_cuda_d2h(dev, C.c_void_p(y_host.data_ptr()), y_dev, 0, d2h_bytes))
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    backend.sync()
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e_value = world * bytes_per_step * e2e_steps / e2e_s / 1e9
+    finite = bool(torch.isfinite(y_host).all().item()) and float(y_host.abs().sum()) > 0.0
+
+    # ---- CPU baseline beside it (rank 0, one GPU only; bounded sample) ----------------------
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.skip_cpu_baseline:
+        import oracle
+
+        sample = 8
+        wh = np.empty(sample * W_BYTES, dtype=np.uint8)
+        mem.copy_d2h(wh, w_arena, 0)
+        xs = x_host.numpy()
+        cbuf = np.zeros(N * M, dtype=np.float32)
+        threads = oracle.fast_max_threads()
+        oracle.fast_matmul_q(oracle.Q4_0, xs[0], wh[:W_BYTES], M, N, K, c=cbuf)
+        t0 = time.perf_counter()
+        reps = 0
+        while time.perf_counter() - t0 < 8.0:
+            for i in range(sample):
+                oracle.fast_matmul_q(oracle.Q4_0, xs[i], wh[i * W_BYTES:(i + 1) * W_BYTES], M, N, K, c=cbuf)
+            reps += 1
+        dt = time.perf_counter() - t0
+        cpu_baseline = {"value": round(reps * sample * BYTES_PER_LAUNCH / dt / 1e9, 3), "unit": "GB/s", "cores": threads,
+                        "kind": "port",
+                        "sample": f"{sample} of the {COPIES} weight matrices, {reps} passes (~8 s), threaded port of the "
+                                  f"reference's packed int8 GEMM route for q4 (vnni={oracle.fast_has_vnni()})"}
+
+    peak, peak_kind = measured_peak_gbs()
+    achieved = BYTES_PER_LAUNCH / (elapsed_ms * 1e-3 / (args.steps * COPIES)) / 1e9
+    out = {
+        "metric": METRIC, "value": round(value, 2), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 5), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int8 x int4 -> int32, f32 scale/accumulate", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "l2": "inputs larger than L2: 2.4 GB of distinct weights per step",
+                   "parallelism": "replicas only" if world > 1 else "single GPU", "outputs_finite_nonzero": finite},
+        "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d_bytes,
+                "d2h_bytes_per_step": d2h_bytes, "steps": e2e_steps},
+        "gpu_launches": args.steps * COPIES,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
+                     "frac": round(achieved / peak, 4), "peak_kind": f"of {peak_kind}",
+                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "algorithmic_bytes_per_launch": BYTES_PER_LAUNCH},
+        "clocks": clocks.summary(),
+    }
+    if cpu_baseline is not None:
+        out["cpu_baseline"] = cpu_baseline
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    lib.aion_cuda_program_destroy(dev, prog)
+    for h in (w_arena, x_dev, y_dev):
+        mem.free(h)
+    backend.deinit()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_reference(args):
+    """The reference's CPU path for the same step, on this host's cores (rank 0 only)."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    import oracle
+
+    threads = oracle.fast_max_threads()
+    rng = np.random.default_rng(1234)
+    base = 4
+    mats = [oracle.quantize(oracle.Q4_0, (rng.standard_normal((K, N)) * 0.02).astype(np.float32), 0) for _ in range(base)]
+    copies = 64  # 604 MB of distinct weight bytes: beyond any last-level cache
+    arena = np.empty(copies * W_BYTES, dtype=np.uint8)
+    for i in range(copies):
+        arena[i * W_BYTES:(i + 1) * W_BYTES] = np.roll(mats[i % base], 18 * 8192 * (i // base))
+    xs = rng.standard_normal((copies, M, K)).astype(np.float32)
+    cbuf = np.zeros(M * N, dtype=np.float32)
+
+    def gemv(i):
+        oracle.fast_matmul_q(oracle.Q4_0, xs[i % copies], arena[(i % copies) * W_BYTES:(i % copies + 1) * W_BYTES], M, N, K, c=cbuf)
+
+    gemv(0)
+    t0 = time.perf_counter()
+    for i in range(8):
+        gemv(i)
+    t_one = (time.perf_counter() - t0) / 8
+    # A step is a bounded sample of the pass: as many of its GEMVs as keep the whole run near two minutes.
+    budget_s = 120.0
+    total_steps = args.steps + max(args.warmup, 3)
+    per_step = int(max(1, min(COPIES, budget_s / (total_steps * t_one))))
+    it = 0
+    for _ in range(max(args.warmup, 3)):
+        for _ in range(per_step):
+            gemv(it)
+            it += 1
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        for _ in range(per_step):
+            gemv(it)
+            it += 1
+    dt = time.perf_counter() - t0
+    value = args.steps * per_step * BYTES_PER_LAUNCH / dt / 1e9
+    sample = (f"{per_step} of the pass's {COPIES} GEMVs per step over {copies} distinct matrices; threaded port of the "
+              f"reference's CPU kernels (q4 takes its packed int8 GEMM route, re-packing B per call), vnni={oracle.fast_has_vnni()}")
+    out = {
+        "impl": "reference", "metric": METRIC, "value": round(value, 3), "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(dt / args.steps * 1e3, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8 x int4 -> int32, f32 scale/accumulate",
+        "data": "synthetic", "config": {"workload": WORKLOAD, "sample": sample},
+        "cpu_baseline": {"value": round(value, 3), "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": round(value, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(out), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--skip-cpu-baseline", action="store_true", help="leave the CPU leg out (profiling runs)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

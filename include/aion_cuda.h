@@ -106,6 +106,18 @@ AION_CUDA_API void* aion_cuda_get_stream(AionCudaDevice* dev);
 /* `Session.retireResources` (aion src/aion/backend/backend.zig:34-36): wait for all
  * submitted work. */
 AION_CUDA_API int32_t aion_cuda_sync(AionCudaDevice* dev);
+/* Record the steps issued between begin and end into a replayable device program (a
+ * CUDA graph) instead of running them, then replay it with one call. The reference's
+ * device path likewise records steps into a frame and submits them in bulk
+ * (aion src/aion/backend/gpu/backend.zig:551-662, src/aion/backend/gpu/frame.zig); here the
+ * recording also removes the per-launch host cost that decode-sized kernels cannot hide.
+ * Every buffer a recorded step names must stay allocated while the program is replayed.
+ * Steps that would allocate scratch must have run once before recording. */
+typedef struct AionCudaProgram AionCudaProgram;
+AION_CUDA_API int32_t aion_cuda_record_begin(AionCudaDevice* dev);
+AION_CUDA_API int32_t aion_cuda_record_end(AionCudaDevice* dev, AionCudaProgram** out);
+AION_CUDA_API int32_t aion_cuda_program_launch(AionCudaDevice* dev, AionCudaProgram* prog);
+AION_CUDA_API void aion_cuda_program_destroy(AionCudaDevice* dev, AionCudaProgram* prog);
 /* Per-thread diagnostic text of the last failing call on this thread
  * (aion src/aion/diagnostic.zig:8-44; include/aion.h:117-140). Copies at most `cap`
  * bytes, NUL-terminates when cap > 0, stores the full length in *len when non-NULL. */

@@ -2,6 +2,7 @@
 // block-format helpers every kernel file uses.
 #pragma once
 
+#include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -59,18 +60,30 @@ struct AionCudaDevice {
   size_t scratch_bytes = 0;
   // Tuning override (environment AION_CUDA_GEMV_SPLIT): K-split of the tiled GEMV, 0 = automatic.
   uint32_t gemv_split_override = 0;
+  // Tuning override (AION_CUDA_GEMV_TILE): columns per CTA of the tiled GEMV (16/32/64), 0 = automatic.
+  uint32_t gemv_tile_override = 0;
   // Same for the decode attention's context split (AION_CUDA_ATTN_SPLIT), 0 = automatic.
   uint32_t attn_split_override = 0;
   // One arrival counter per attention row for the split-K merge; zero between launches.
   int* tickets = nullptr;
   size_t tickets_cap = 0;
+  // The GEMV's split-tile partial sums and their arrival counters (same discipline).
+  float* gemv_partials = nullptr;
+  size_t gemv_partials_bytes = 0;
+  int* gemv_tickets = nullptr;
+  size_t gemv_tickets_cap = 0;
 
   // Between aion_cuda_record_begin and aion_cuda_record_end.
   bool recording = false;
 
+  // Tensor maps (TMA descriptors) already encoded for this device, keyed by view geometry.
+  struct TmapCache;
+  TmapCache* tmaps = nullptr;
+
   int32_t make_current() const;
   int32_t reserve_scratch(size_t bytes);
   int32_t reserve_tickets(size_t count);
+  int32_t reserve_gemv_fixup(size_t partial_bytes, size_t tickets);
   // Reads the status word back (call after the stream has been synchronized).
   int32_t check_fault();
 };
@@ -86,6 +99,14 @@ inline int32_t resolve(const AionCudaOperand& op, size_t need, const char* name,
   *out = reinterpret_cast<T*>(static_cast<uintptr_t>(op.handle + op.offset));
   return AION_CUDA_OK;
 }
+
+// A rank-2 or rank-3 byte view of device memory for tiled TMA loads. dims[0] is the
+// innermost extent in BYTES (a multiple of 8), dims[1..] are counts; strides[i] is the
+// byte distance between consecutive indices of dimension i+1 (multiples of 16); box[0] is
+// the innermost box extent in bytes (a multiple of 16, at most 2048), box[1..] counts
+// (at most 256). The descriptor is cached on the device.
+int32_t tensor_map_bytes(AionCudaDevice* dev, const void* base, uint32_t rank, const uint64_t* dims, const uint64_t* strides,
+                         const uint32_t* box, const CUtensorMap** out);
 
 // ---- step implementations, one per kernel file ------------------------------------
 int32_t quantize_activation_rows(AionCudaDevice* dev, const float* a, uint64_t m, uint64_t k, uint64_t lda,

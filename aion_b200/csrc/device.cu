@@ -3,6 +3,7 @@
 #include <cstring>
 #include <new>
 #include <string>
+#include <unordered_map>
 
 #include "common.cuh"
 
@@ -32,6 +33,72 @@ int32_t fail(int32_t status, const char* fmt, ...) {
 int32_t cuda_fail(cudaError_t e, const char* what) {
   const int32_t st = (e == cudaErrorMemoryAllocation) ? AION_CUDA_OUT_OF_MEMORY : AION_CUDA_INTERNAL_ERROR;
   return fail(st, "CUDA error %d (%s) in %s", (int)e, cudaGetErrorString(e), what);
+}
+
+}  // namespace aion
+
+struct AionCudaDevice::TmapCache {
+  struct Key {
+    uint64_t v[10];  // base, rank, dims[3], box[3], strides[2]
+    bool operator==(const Key& o) const {
+      for (int i = 0; i < 10; i++)
+        if (v[i] != o.v[i]) return false;
+      return true;
+    }
+  };
+  struct Hash {
+    size_t operator()(const Key& k) const {
+      uint64_t h = 0xCBF29CE484222325ull;
+      for (int i = 0; i < 10; i++) h = (h ^ k.v[i]) * 0x100000001B3ull;
+      return (size_t)(h ^ (h >> 29));
+    }
+  };
+  std::unordered_map<Key, CUtensorMap, Hash> map;
+};
+
+namespace aion {
+
+int32_t tensor_map_bytes(AionCudaDevice* dev, const void* base, uint32_t rank, const uint64_t* dim_bytes0_then_counts,
+                         const uint64_t* stride_bytes, const uint32_t* box, const CUtensorMap** out) {
+  if (!dev->tmaps) {
+    dev->tmaps = new (std::nothrow) AionCudaDevice::TmapCache();
+    if (!dev->tmaps) return fail(AION_CUDA_OUT_OF_MEMORY, "tensor map cache: host allocation failed");
+  }
+  AionCudaDevice::TmapCache::Key key{};
+  key.v[0] = (uint64_t)(uintptr_t)base;
+  key.v[1] = rank;
+  for (uint32_t i = 0; i < rank; i++) {
+    key.v[2 + i] = dim_bytes0_then_counts[i];
+    key.v[5 + i] = box[i];
+    if (i + 1 < rank) key.v[8 + i] = stride_bytes[i];
+  }
+  auto& m = dev->tmaps->map;
+  auto it = m.find(key);
+  if (it == m.end()) {
+    if (m.size() > 8192) m.clear();  // descriptors are cheap to rebuild; keep the table bounded
+    // Elements are 8-byte words so that a box row may hold up to 2048 bytes.
+    if (rank < 2 || rank > 3 || (dim_bytes0_then_counts[0] & 7) || (box[0] & 15) || box[0] / 8 > 256 || ((uintptr_t)base & 15))
+      return fail(AION_CUDA_INTERNAL_ERROR, "tensor map: view geometry is not TMA-addressable");
+    cuuint64_t gdim[3] = {dim_bytes0_then_counts[0] / 8, 1, 1};
+    cuuint64_t gstride[2] = {0, 0};
+    cuuint32_t bx[3] = {box[0] / 8, 1, 1};
+    const cuuint32_t estride[3] = {1, 1, 1};
+    for (uint32_t i = 1; i < rank; i++) {
+      gdim[i] = dim_bytes0_then_counts[i];
+      bx[i] = box[i];
+      gstride[i - 1] = stride_bytes[i - 1];
+      if ((stride_bytes[i - 1] & 15) || box[i] > 256)
+        return fail(AION_CUDA_INTERNAL_ERROR, "tensor map: view geometry is not TMA-addressable");
+    }
+    CUtensorMap tm;
+    const CUresult r = cuTensorMapEncodeTiled(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT64, rank, const_cast<void*>(base), gdim, gstride, bx,
+                                              estride, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(AION_CUDA_INTERNAL_ERROR, "cuTensorMapEncodeTiled failed with %d", (int)r);
+    it = m.emplace(key, tm).first;
+  }
+  *out = &it->second;
+  return AION_CUDA_OK;
 }
 
 }  // namespace aion
@@ -71,6 +138,31 @@ int32_t AionCudaDevice::reserve_tickets(size_t count) {
   AION_CUDA_TRY(cudaMalloc(&tickets, want * sizeof(int)));
   AION_CUDA_TRY(cudaMemsetAsync(tickets, 0, want * sizeof(int), stream));
   tickets_cap = want;
+  return AION_CUDA_OK;
+}
+
+int32_t AionCudaDevice::reserve_gemv_fixup(size_t partial_bytes, size_t ticket_count) {
+  if (partial_bytes > gemv_partials_bytes) {
+    if (recording) return fail(AION_CUDA_INVALID_ARGUMENT, "a recorded matmul step needs split-tile scratch that is not reserved yet: run it once before recording");
+    AION_CUDA_TRY(cudaStreamSynchronize(stream));
+    if (gemv_partials) AION_CUDA_TRY(cudaFree(gemv_partials));
+    gemv_partials = nullptr;
+    gemv_partials_bytes = 0;
+    const size_t want = (partial_bytes + (partial_bytes >> 2) + 255) & ~size_t(255);
+    AION_CUDA_TRY(cudaMalloc(&gemv_partials, want));
+    gemv_partials_bytes = want;
+  }
+  if (ticket_count > gemv_tickets_cap) {
+    if (recording) return fail(AION_CUDA_INVALID_ARGUMENT, "a recorded matmul step needs arrival counters that are not reserved yet: run it once before recording");
+    AION_CUDA_TRY(cudaStreamSynchronize(stream));
+    if (gemv_tickets) AION_CUDA_TRY(cudaFree(gemv_tickets));
+    gemv_tickets = nullptr;
+    gemv_tickets_cap = 0;
+    const size_t want = ticket_count < 4096 ? 4096 : ticket_count + (ticket_count >> 1);
+    AION_CUDA_TRY(cudaMalloc(&gemv_tickets, want * sizeof(int)));
+    AION_CUDA_TRY(cudaMemsetAsync(gemv_tickets, 0, want * sizeof(int), stream));
+    gemv_tickets_cap = want;
+  }
   return AION_CUDA_OK;
 }
 
@@ -139,6 +231,10 @@ int32_t aion_cuda_device_create(int32_t ordinal, AionCudaDevice** out) {
     const int v = std::atoi(e2);
     if (v == 1 || v == 2 || v == 4 || v == 8) d->gemv_split_override = (uint32_t)v;
   }
+  if (const char* e4 = std::getenv("AION_CUDA_GEMV_TILE")) {
+    const int v = std::atoi(e4);
+    if (v == 16 || v == 32 || v == 64) d->gemv_tile_override = (uint32_t)v;
+  }
   if (const char* e3 = std::getenv("AION_CUDA_ATTN_SPLIT")) {
     const int v = std::atoi(e3);
     if (v >= 1 && v <= 256) d->attn_split_override = (uint32_t)v;
@@ -156,6 +252,9 @@ void aion_cuda_device_destroy(AionCudaDevice* dev) {
   }
   if (dev->scratch) cudaFree(dev->scratch);
   if (dev->tickets) cudaFree(dev->tickets);
+  if (dev->gemv_partials) cudaFree(dev->gemv_partials);
+  if (dev->gemv_tickets) cudaFree(dev->gemv_tickets);
+  delete dev->tmaps;
   if (dev->fault_dev) cudaFree(dev->fault_dev);
   if (dev->fault_host) cudaFreeHost(dev->fault_host);
   delete dev;

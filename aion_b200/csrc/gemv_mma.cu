@@ -6,178 +6,216 @@
 // block contributes float(exact int dot) * (a_scale * w_scale), accumulated in f32.
 //
 // The kernel is HBM-bound: each weight byte is read from global memory exactly once.
-//   * A CTA owns a tile of 64 output columns and a contiguous range of K blocks. A
-//     producer warp streams the packed blocks, untouched, into a 4-stage shared-memory
-//     ring with 1-D bulk (TMA) copies that complete on mbarriers; four consumer warps
-//     drain it. Blocks are 18 / 34 bytes, so nothing inside a stage is 16-byte aligned
-//     except the copies themselves.
-//   * Consumers feed the int8 tensor-core MMA (m16n8k32): the 16 "rows" are 16 output
-//     columns of one K block, the 8 "columns" are up to 8 activation rows. q4 nibbles
-//     become int8 in two logic ops by placing the nibble in the high half of a byte
-//     (value 16*(nibble-8)); the 1/16 folds into the weight scale. One block's int32
-//     dot leaves the MMA and is scaled and accumulated in f32 registers.
-//   * Shared-memory reads are arranged so each load instruction is one wavefront:
-//     the 8 row groups of a fragment read 8 columns that are 8 apart (their starts are
-//     4 words apart modulo the 32 banks).
-//   * K is split across the CTAs of a thread-block cluster when the column tiles alone
-//     would not fill the GPU; partial sums meet in distributed shared memory in a fixed
-//     order, so results do not depend on scheduling.
-//   * With programmatic dependent launch the weight stream of the next GEMV starts
-//     while this one drains: only the activation read waits for the previous kernel.
+//   * Work is cut into units of (64 output columns) x (8 K blocks) = one shared-memory
+//     stage (9 KB of q4, 17 KB of q8). The grid is persistent — as many CTAs as are
+//     resident at once — and CTA c takes the contiguous unit range [c*U/G, (c+1)*U/G)
+//     in tile-major order ("stream-K"), so every SM streams the same number of bytes
+//     whatever the shape: no tail wave, and narrow matrices split along K for free.
+//   * A producer warp fills a 4-stage ring with ONE tiled TMA load per stage (the weight
+//     tensor viewed as bytes in 8-byte elements; one request per stage, because the copy
+//     engine takes about 50 ns per request and per-row bulk copies made that the
+//     bottleneck), completing on mbarriers. Blocks are 18 / 34 bytes, so nothing inside
+//     a stage is aligned except the stage itself.
+//   * Four consumer warps drain it, each owning 16 of the tile's 64 columns for all K, so
+//     no sums cross warps. They feed the int8 tensor-core MMA (m16n8k32): the 16 "rows"
+//     are 16 output columns of one K block, the 8 "columns" are up to 8 activation rows.
+//     q4 nibbles become int8 in three logic ops by placing the nibble in the high half of
+//     a byte (value 16*(nibble-8)); the 1/16 folds into the activation scale. One block's
+//     int32 dot leaves the MMA and is scaled and accumulated in f32 registers with
+//     packed f32x2 arithmetic.
+//   * Shared-memory reads are one wavefront each: the 8 row groups of a fragment read 8
+//     columns that are 8 apart (K-major: 4 words apart modulo the 32 banks) or 8
+//     consecutive weight rows 272 bytes apart (NT).
+//   * A tile whose K range is shared by several CTAs is finished by the last of them to
+//     arrive: each writes its partial sums to scratch, takes a ticket, and the last one
+//     adds the parts in CTA order (so results do not depend on timing) and stores C.
+//   * With programmatic dependent launch the next kernel's weight stream starts as this
+//     one's CTAs retire; only the activation read waits for the previous kernel.
 #include "common.cuh"
 #include "ptx.cuh"
 #include "quant_device.cuh"
 
 namespace aion {
 
+#ifdef AION_GEMV_TRACE
+unsigned long long* g_gemv_trace = nullptr;
+#endif
+
 namespace {
 
-constexpr int TN = 64;             // output columns per CTA
+constexpr int TN = 64;             // output columns per tile
 constexpr int KBT = 8;             // K blocks per stage
 constexpr int NS = 4;              // stages in the ring
-constexpr int CONSUMER_WARPS = 4;
+constexpr int CONSUMER_WARPS = 4;  // one per 16 columns
 constexpr int CONSUMER_THREADS = CONSUMER_WARPS * 32;
 constexpr int THREADS = CONSUMER_THREADS + 32;
-constexpr int ACT_STAGES = 8;      // stages whose activations are held quantized at once
-constexpr int ACT_KB = ACT_STAGES * KBT;
-constexpr int NT_ROW_PITCH = KBT * Q8_BYTES;  // 272 bytes: 16-byte multiple, 4 words mod 32 banks
+constexpr int NT_ROW_PITCH = KBT * Q8_BYTES;  // 272: 16-byte multiple, 4 words mod 32 banks
+constexpr size_t ACT_BUDGET_BYTES = 40 * 1024;  // quantized activations kept per CTA
+
+#ifdef AION_GEMV_TRACE
+#define GEMV_TRACE(slot)                                                          \
+  do {                                                                            \
+    if (p.trace && (threadIdx.x & 31) == 0) {                                     \
+      unsigned long long t_;                                                      \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                      \
+      p.trace[((size_t)blockIdx.x * 5 + (threadIdx.x >> 5)) * 8 + (slot)] = t_;   \
+    }                                                                             \
+  } while (0)
+#else
+#define GEMV_TRACE(slot) do {} while (0)
+#endif
 
 struct GemvParams {
-  const uint8_t* b;
   const float* a;
   float* c;
   uint32_t m, n, kblocks;
-  uint64_t lda, ldb, ldc;
+  uint32_t mp2;  // activation rows held in shared memory: m rounded up to even
+  uint64_t lda, ldc;
   float alpha, beta;
+  uint32_t tiles, stages_per_tile;
+  uint64_t units;
+  float* partials;  // [cta][2][TN * 8*MT]
+  int* tickets;     // [tile][warp]
   int* fault;
   uint32_t a_vec4;  // A rows may be read as float4
+#ifdef AION_GEMV_TRACE
+  unsigned long long* trace;
+#endif
 };
 
-template <int DT, bool NT, int MT>
+template <int DT, bool NT>
 struct Geom {
   static constexpr int BB = (DT == AION_CUDA_DTYPE_Q8_0) ? Q8_BYTES : Q4_BYTES;
   static constexpr int KM_PITCH = TN * BB;
   static constexpr int STAGE_BYTES = NT ? TN * NT_ROW_PITCH : KBT * KM_PITCH;
-  static constexpr int MP = 8 * MT;  // padded activation rows
-  static constexpr int PARTIAL_BYTES = CONSUMER_WARPS * TN * MP * 4;
   static constexpr int RING_BYTES = NS * STAGE_BYTES;
-  static_assert(PARTIAL_BYTES <= RING_BYTES, "partials reuse the ring");
-  static constexpr int OFF_ACTQ = RING_BYTES;
-  static constexpr int ACTQ_BYTES = ACT_KB * MP * 32;
-  static constexpr int OFF_ACTS = OFF_ACTQ + ACTQ_BYTES;
-  static constexpr int ACTS_BYTES = ACT_KB * MP * 4;
-  static constexpr int OFF_RED = OFF_ACTS + ACTS_BYTES;
-  static constexpr int RED_BYTES = TN * MP * 4;
-  static constexpr int OFF_BARS = OFF_RED + RED_BYTES;
-  static constexpr int SMEM_BYTES = OFF_BARS + 2 * NS * 8 + 16;
+  static constexpr int OFF_BARS = RING_BYTES;
+  static constexpr int OFF_ACT = OFF_BARS + 128;
+  static_assert(STAGE_BYTES % 128 == 0, "TMA destinations are 128-byte aligned");
 };
 
-__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_THREADS) : "memory"); }
+// Shared-memory bytes of the quantized activations: per K block, mp2 rows of 32 codes,
+// then mp2/2 scale quads (s_even, s_even, s_odd, s_odd).
+__host__ __device__ inline size_t act_bytes(uint32_t kb_pad, uint32_t mp2) { return (size_t)kb_pad * mp2 * 40 + 16; }
 
-// Position, inside the 32-byte quantized row of one K block, of the 4-byte word that
-// holds elements 4u..4u+3 (q8) — chosen so that MMA B-fragment lane j finds its two
-// registers as the 8 bytes at 8j.
-//   q8: b0 = k 4j..4j+3, b1 = k 16+4j..16+4j+3.
-//   q4: b0 = elements 8j+{0,2,4,6} (low nibbles of 4 bytes), b1 = 8j+{1,3,5,7}.
-template <int DT>
-__device__ __forceinline__ void store_act_quad(uint8_t* row32, int u, int q0, int q1, int q2, int q3) {
-  if (DT == AION_CUDA_DTYPE_Q8_0) {
-    const uint32_t w = (uint32_t)(q0 & 0xFF) | ((uint32_t)(q1 & 0xFF) << 8) | ((uint32_t)(q2 & 0xFF) << 16) |
-                       ((uint32_t)(q3 & 0xFF) << 24);
-    *reinterpret_cast<uint32_t*>(row32 + 8 * (u & 3) + 4 * (u >> 2)) = w;
-  } else {
-    const int j = u >> 1, odd = u & 1;
-    *reinterpret_cast<uint16_t*>(row32 + 8 * j + 2 * odd) = (uint16_t)((q0 & 0xFF) | ((q2 & 0xFF) << 8));
-    *reinterpret_cast<uint16_t*>(row32 + 8 * j + 4 + 2 * odd) = (uint16_t)((q1 & 0xFF) | ((q3 & 0xFF) << 8));
-  }
+// Shared-memory loads by 32-bit shared address. They are plain (non-volatile) asm so the
+// compiler may interleave the loads of independent K blocks; each takes its address from
+// a register the mbarrier wait has touched, which keeps it after the wait. Constant
+// offsets fold into the instruction.
+__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
+  uint32_t v;
+  asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ float lds_f16(uint32_t addr) {
+  unsigned short h;
+  asm("ld.shared.u16 %0, [%1];" : "=h"(h) : "r"(addr));
+  return __half2float(__ushort_as_half(h));
+}
+__device__ __forceinline__ uint2 lds_u64(uint32_t addr) {
+  uint2 v;
+  asm("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void lds_f32x4(uint32_t addr, uint64_t& lo, uint64_t& hi) {
+  asm("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(lo), "=l"(hi) : "r"(addr));
 }
 
 // The two A-fragment registers of one weight block for quad lane j. `aligned` says the
 // block's codes start on a 4-byte boundary (they start 2 bytes after the block does).
+// `blk` already includes the lane's 4*j.
 template <int DT>
-__device__ __forceinline__ void load_codes(uint32_t blk, bool aligned, int j, uint32_t& r_lo, uint32_t& r_hi) {
+__device__ __forceinline__ void load_codes(uint32_t blk, bool aligned, uint32_t& r_lo, uint32_t& r_hi) {
   if (DT == AION_CUDA_DTYPE_Q4_0) {
     uint32_t v;
     if (aligned) {
-      v = ptx::lds32(blk + 2 + 4 * j);
+      v = lds_u32(blk + 2);
     } else {
-      const uint32_t lo = ptx::lds32(blk + 4 * j), hi = ptx::lds32(blk + 4 * j + 4);
-      v = __funnelshift_r(lo, hi, 16);
+      v = __funnelshift_r(lds_u32(blk), lds_u32(blk + 4), 16);
     }
     // nibble -> signed byte 16*(nibble-8): move it to the high half, flip its top bit.
     r_lo = ((v << 4) & 0xF0F0F0F0u) ^ 0x80808080u;
     r_hi = (v & 0xF0F0F0F0u) ^ 0x80808080u;
   } else {
     if (aligned) {
-      r_lo = ptx::lds32(blk + 2 + 4 * j);
-      r_hi = ptx::lds32(blk + 18 + 4 * j);
+      r_lo = lds_u32(blk + 2);
+      r_hi = lds_u32(blk + 18);
     } else {
-      const uint32_t w0 = ptx::lds32(blk + 4 * j), w1 = ptx::lds32(blk + 4 * j + 4);
-      const uint32_t w2 = ptx::lds32(blk + 16 + 4 * j), w3 = ptx::lds32(blk + 20 + 4 * j);
-      r_lo = __funnelshift_r(w0, w1, 16);
-      r_hi = __funnelshift_r(w2, w3, 16);
+      r_lo = __funnelshift_r(lds_u32(blk), lds_u32(blk + 4), 16);
+      r_hi = __funnelshift_r(lds_u32(blk + 16), lds_u32(blk + 20), 16);
     }
   }
 }
 
-template <int DT>
-__device__ __forceinline__ float load_scale(uint32_t blk) {
-  const float s = __half2float(__ushort_as_half((unsigned short)ptx::lds16(blk)));
-  return DT == AION_CUDA_DTYPE_Q4_0 ? s * 0.0625f : s;  // undo the 16x of the nibble placement (exact)
+// Packed f32x2 helpers (two independent IEEE f32 operations per instruction).
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
 }
 
-template <int DT, bool NT, int MT>
-__global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p) {
-  using G = Geom<DT, NT, MT>;
+// CTA that owns unit u when G CTAs split U units as [c*U/G, (c+1)*U/G).
+__device__ __forceinline__ uint32_t unit_owner(uint64_t u, uint64_t U, uint64_t G) { return (uint32_t)(((u + 1) * G - 1) / U); }
+
+// DT: weight dtype; NT: weights are [n,k] row-major (else K-major); MT: 8-row activation
+// tiles (1 or 2); M1: exactly one activation row (skips the odd-row half of the epilogue).
+template <int DT, bool NT, int MT, bool M1>
+__global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tmap) {
+  using G = Geom<DT, NT>;
+  constexpr int MPA = 8 * MT;  // activation rows of the accumulator tile
+  constexpr uint32_t MP2 = M1 ? 2 : 8 * MT;  // activation rows held in shared memory
   extern __shared__ __align__(128) uint8_t smem[];
   const uint32_t smem_base = ptx::smem_u32(smem);
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, j = lane & 3;
 
-  const uint32_t S = ptx::cluster_nctarank();
-  const uint32_t rank = ptx::cluster_ctarank();
-  const uint32_t tile = blockIdx.x / S;
-  const uint32_t n0 = tile * TN;
-  const uint32_t cols = min((uint32_t)TN, p.n - n0);
-
-  const uint32_t stages_total = (p.kblocks + KBT - 1) / KBT;
-  const uint32_t s_begin = (uint32_t)((uint64_t)stages_total * rank / S);
-  const uint32_t s_end = (uint32_t)((uint64_t)stages_total * (rank + 1) / S);
-  const uint32_t my_stages = s_end - s_begin;
+  const uint64_t U = p.units, NG = gridDim.x;
+  const uint64_t u_begin = U * blockIdx.x / NG, u_end = U * (blockIdx.x + 1) / NG;
+  const uint32_t Sg = p.stages_per_tile;
 
   const uint32_t bar_full = smem_base + G::OFF_BARS;
   const uint32_t bar_empty = bar_full + NS * 8;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + G::OFF_BARS + 2 * NS * 8);
-
-  if (tid == 0) {
-    for (int s = 0; s < NS; s++) {
-      ptx::mbar_init(bar_full + 8 * s, 1);
-      ptx::mbar_init(bar_empty + 8 * s, CONSUMER_WARPS);
-    }
-    *abort_flag = 0;
-    ptx::fence_barrier_init();
-  }
-  __syncthreads();
-  // The next kernel in the stream may begin (its weight stream does not depend on us).
-  ptx::pdl_launch_dependents();
-
-  float acc[4][MT][4];
-#pragma unroll
-  for (int i = 0; i < 4; i++)
-#pragma unroll
-    for (int t = 0; t < MT; t++)
-#pragma unroll
-      for (int e = 0; e < 4; e++) acc[i][t][e] = 0.0f;
+  const uint32_t kb_pad = p.stages_per_tile * KBT;  // K blocks rounded up to whole stages
+  uint8_t* act_q = smem + G::OFF_ACT;
+  float* act_s = reinterpret_cast<float*>(act_q + (size_t)kb_pad * MP2 * 32);
+  GEMV_TRACE(0);
 
   if (warp == CONSUMER_WARPS) {
-    // ---------------- producer: stream packed weight blocks into the ring ----------------
-    uint32_t issued = 0;
-    for (uint32_t it = 0; it < my_stages; it++) {
-      const uint32_t slot = it % NS;
-      if (*abort_flag) break;
-      if (it >= NS) {
-        if (!ptx::mbar_wait_bounded(bar_empty + 8 * slot, ((it / NS) - 1) & 1)) {
+    // ---------------- producer: one tiled TMA load per stage ----------------
+    // It sets the barriers up itself and starts copying at once; the consumers meet it at
+    // the CTA barrier below before they first wait on one.
+    if (lane == 0) {
+      ptx::prefetch_tensormap(&tmap);
+      for (int s = 0; s < NS; s++) {
+        ptx::mbar_init(bar_full + 8 * s, 1);
+        ptx::mbar_init(bar_empty + 8 * s, CONSUMER_WARPS);
+      }
+      *abort_flag = 0;
+      ptx::fence_barrier_init();
+    }
+    __syncwarp();
+    const uint64_t n_units = u_end - u_begin;
+    uint64_t issued = 0;
+    uint32_t tile = (uint32_t)(u_begin / Sg), s = (uint32_t)(u_begin - (uint64_t)tile * Sg);
+    for (uint64_t it = 0; it < n_units; it++) {
+      const uint32_t slot = (uint32_t)(it % NS);
+      if (it == (uint64_t)NS) __syncthreads();  // CTA barrier #1 (see the consumers)
+      if (it >= (uint64_t)NS) {
+        if (*abort_flag) break;
+        if (!ptx::mbar_wait_bounded(bar_empty + 8 * slot, (uint32_t)((it / NS) - 1) & 1)) {
           if (lane == 0) {
             atomicExch(p.fault, FAULT_WAIT_EXPIRED);
             *abort_flag = 1;
@@ -185,232 +223,355 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p)
           break;
         }
       }
-      const uint32_t kb0 = (s_begin + it) * KBT;
-      const uint32_t nkb = min((uint32_t)KBT, p.kblocks - kb0);
-      const uint32_t stage = smem_base + slot * G::STAGE_BYTES;
-      const uint32_t full = bar_full + 8 * slot;
-      if (!NT) {
-        const uint32_t seg = cols * G::BB;
-        if (lane == 0) ptx::mbar_arrive_expect_tx(full, nkb * seg);
-        __syncwarp();
-        if ((uint32_t)lane < nkb)
-          ptx::bulk_g2s(stage + lane * G::KM_PITCH, p.b + ((uint64_t)(kb0 + lane) * p.ldb + n0) * G::BB, seg, full);
-      } else {
-        const uint32_t seg = nkb * Q8_BYTES;
-        if (lane == 0) ptx::mbar_arrive_expect_tx(full, cols * seg);
-        __syncwarp();
-        for (uint32_t r = lane; r < cols; r += 32)
-          ptx::bulk_g2s(stage + r * NT_ROW_PITCH, p.b + ((uint64_t)(n0 + r) * p.ldb + kb0) * Q8_BYTES, seg, full);
+      if (lane == 0) {
+        const uint32_t full = bar_full + 8 * slot;
+        const uint32_t stage = smem_base + slot * G::STAGE_BYTES;
+        // Rows or columns past the tensor arrive as zeros (a zero scale), and the whole
+        // box counts towards the barrier.
+        ptx::mbar_arrive_expect_tx(full, G::STAGE_BYTES);
+        if (!NT && DT == AION_CUDA_DTYPE_Q4_0) ptx::tma_load_2d(stage, &tmap, (int32_t)(tile * (TN * G::BB / 8)), (int32_t)(s * KBT), full);
+        else if (!NT) ptx::tma_load_3d(stage, &tmap, 0, (int32_t)(tile * (TN / 8)), (int32_t)(s * KBT), full);
+        else ptx::tma_load_2d(stage, &tmap, (int32_t)(s * KBT * Q8_BYTES / 8), (int32_t)(tile * TN), full);
       }
+      __syncwarp();
       issued = it + 1;
+      if (++s == Sg) {
+        s = 0;
+        tile++;
+      }
     }
+    if (n_units <= (uint64_t)NS) __syncthreads();  // CTA barrier #1 when the whole range fit the ring
     // After a failed wait nobody drains the ring: let the copies still in flight land
     // (bounded) before this CTA's shared memory can be handed to another CTA.
     if (*abort_flag)
-      for (uint32_t it = issued > NS ? issued - NS : 0; it < issued; it++)
-        ptx::mbar_wait_bounded(bar_full + 8 * (it % NS), (it / NS) & 1, 1u << 16);
+      for (uint64_t it = issued > (uint64_t)NS ? issued - NS : 0; it < issued; it++)
+        ptx::mbar_wait_bounded(bar_full + 8 * (uint32_t)(it % NS), (uint32_t)(it / NS) & 1, 1u << 16);
+    return;
+  }
+
+  // ---------------- consumers ----------------
+  // Scales start at zero: a pad row (m odd) and rows never written must contribute
+  // nothing, whatever their code bytes hold (an integer dot is always finite).
+  {
+    float4* z = reinterpret_cast<float4*>(act_s);
+    const uint32_t quads = kb_pad * (MP2 / 2) + 1;  // + the block of zeros absent rows read
+    for (uint32_t i = tid; i < quads; i += CONSUMER_THREADS) z[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  __syncthreads();  // CTA barrier #1: the producer has initialised the mbarriers
+  // The next kernel in the stream may begin: its weight stream does not depend on us.
+  ptx::pdl_launch_dependents();
+  GEMV_TRACE(1);
+  // Everything below reads what the previous kernel wrote (A, and C when beta != 0).
+  ptx::pdl_wait();
+  GEMV_TRACE(2);
+
+  {
+    // Quantize all of A, one thread per 32-block (no cross-lane traffic, 32 independent
+    // elements of instruction-level parallelism): the block's 128 bytes are one cache line.
+    const uint32_t items = p.m * p.kblocks;
+    const float fold = (DT == AION_CUDA_DTYPE_Q4_0) ? 0.0625f : 1.0f;  // undoes the 16x of the nibble placement (exact)
+    for (uint32_t item = tid; item < items; item += CONSUMER_THREADS) {
+      const uint32_t r = item / p.kblocks, kb = item - r * p.kblocks;
+      const float* src = p.a + (uint64_t)r * p.lda + (uint64_t)kb * QK;
+      float x[QK];
+      if (p.a_vec4) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          const float4 f = reinterpret_cast<const float4*>(src)[i];
+          x[4 * i] = f.x; x[4 * i + 1] = f.y; x[4 * i + 2] = f.z; x[4 * i + 3] = f.w;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < QK; i++) x[i] = src[i];
+      }
+      float am[8];
+#pragma unroll
+      for (int i = 0; i < 8; i++) am[i] = fmaxf(fmaxf(fabsf(x[4 * i]), fabsf(x[4 * i + 1])), fmaxf(fabsf(x[4 * i + 2]), fabsf(x[4 * i + 3])));
+      const float amax = fmaxf(fmaxf(fmaxf(am[0], am[1]), fmaxf(am[2], am[3])), fmaxf(fmaxf(am[4], am[5]), fmaxf(am[6], am[7])));
+      float scale, inv;
+      activation_block_scales(amax, &scale, &inv);
+      uint32_t w[8];
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        const uint32_t q0 = (uint32_t)quantize_activation_with_inv(x[4 * i], inv) & 0xFF;
+        const uint32_t q1 = (uint32_t)quantize_activation_with_inv(x[4 * i + 1], inv) & 0xFF;
+        const uint32_t q2 = (uint32_t)quantize_activation_with_inv(x[4 * i + 2], inv) & 0xFF;
+        const uint32_t q3 = (uint32_t)quantize_activation_with_inv(x[4 * i + 3], inv) & 0xFF;
+        w[i] = (DT == AION_CUDA_DTYPE_Q8_0) ? (q0 | (q1 << 8) | (q2 << 16) | (q3 << 24))    // elements in order
+                                             : (q0 | (q2 << 8) | (q1 << 16) | (q3 << 24));   // (e0, e2 | e1, e3)
+      }
+      // MMA B-fragment lane j finds its two registers as the 8 bytes at 8j.
+      //   q8: b0 = k 4j..4j+3, b1 = k 16+4j..16+4j+3            -> word 2j = w[j], word 2j+1 = w[4+j]
+      //   q4: b0 = elements 8j+{0,2,4,6}, b1 = elements 8j+{1,3,5,7} (low / high nibbles of 4 code bytes)
+      uint32_t o[8];
+#pragma unroll
+      for (int jj = 0; jj < 4; jj++) {
+        if (DT == AION_CUDA_DTYPE_Q8_0) {
+          o[2 * jj] = w[jj];
+          o[2 * jj + 1] = w[4 + jj];
+        } else {
+          o[2 * jj] = (w[2 * jj] & 0xFFFFu) | (w[2 * jj + 1] << 16);
+          o[2 * jj + 1] = (w[2 * jj] >> 16) | (w[2 * jj + 1] & 0xFFFF0000u);
+        }
+      }
+      uint4* dst = reinterpret_cast<uint4*>(act_q + ((size_t)kb * MP2 + r) * 32);
+      dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+      dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+      float* sq = act_s + ((size_t)kb * (MP2 / 2) + (r >> 1)) * 4 + 2 * (r & 1);
+      *reinterpret_cast<float2*>(sq) = make_float2(scale * fold, scale * fold);
+    }
+  }
+  GEMV_TRACE(3);
+  asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_THREADS) : "memory");
+  GEMV_TRACE(4);
+
+  // Per-lane constants: where this lane's two weight blocks (rows g and g+8 of the
+  // fragment) sit inside a stage, and where its activation fragments start. Lanes whose
+  // activation row does not exist read a block of zeros instead (no predicates in the loop).
+  uint32_t off0, off1;
+  if (!NT) {
+    off0 = (2 * warp + 8 * g) * G::BB;  // an even column: its codes start 2 bytes past a word boundary
+    off1 = off0 + G::BB;                // the odd column after it: codes word aligned
   } else {
-    // ---------------- consumers ----------------
-    // Rows of A beyond m are zero activations with zero scale.
-    if (p.m < (uint32_t)G::MP) {
-      for (int i = tid; i < ACT_KB * G::MP * 8; i += CONSUMER_THREADS) {
-        const int row = (i / 8) % G::MP;
-        if ((uint32_t)row >= p.m) reinterpret_cast<uint32_t*>(smem + G::OFF_ACTQ)[i] = 0u;
+    off0 = (16 * warp + g) * NT_ROW_PITCH;
+    off1 = off0 + 8 * NT_ROW_PITCH;
+  }
+  const int col0 = NT ? 16 * warp + g : 2 * warp + 8 * g;
+  const int col1 = NT ? col0 + 8 : col0 + 1;
+  constexpr uint32_t AQ_STRIDE = MP2 * 32, AS_STRIDE = MP2 * 8;  // bytes per K block
+  const uint32_t act_q_addr = smem_base + G::OFF_ACT;
+  const uint32_t act_s_addr = act_q_addr + kb_pad * AQ_STRIDE;
+  const uint32_t zero_addr = act_s_addr + kb_pad * AS_STRIDE;
+  uint32_t aq_lane[MT], as_lane[MT], aq_step[MT], as_step[MT];
+#pragma unroll
+  for (int t = 0; t < MT; t++) {
+    const bool row_ok = (t * 8 + g) < (int)MP2, pair_ok = (t * 8 + 2 * j) < (int)MP2;
+    aq_lane[t] = row_ok ? act_q_addr + (t * 8 + g) * 32 + 8 * j : zero_addr;
+    aq_step[t] = row_ok ? AQ_STRIDE : 0u;
+    as_lane[t] = pair_ok ? act_s_addr + (t * 4 + j) * 16 : zero_addr;
+    as_step[t] = pair_ok ? AS_STRIDE : 0u;
+  }
+
+  // acc[t][0] = (row g, row g+8) x activation row t*8+2j ; acc[t][1] = the same x row t*8+2j+1.
+  uint64_t acc[MT][2];
+#pragma unroll
+  for (int t = 0; t < MT; t++) acc[t][0] = acc[t][1] = 0ull;
+
+  const uint32_t first_tile = (uint32_t)(u_begin / Sg);
+  uint32_t tile = first_tile, s = (uint32_t)(u_begin - (uint64_t)first_tile * Sg);
+  bool ok = true;
+  uint64_t it = 0;
+  for (uint64_t uu = u_begin; uu < u_end; uu++, it++) {
+    const uint32_t slot = (uint32_t)(it % NS);
+    if (ok && (*abort_flag || !ptx::mbar_wait_bounded(bar_full + 8 * slot, (uint32_t)(it / NS) & 1))) {
+      if (lane == 0 && !*abort_flag) {
+        atomicExch(p.fault, FAULT_WAIT_EXPIRED);
+        *abort_flag = 1;
       }
-      for (int i = tid; i < ACT_KB * G::MP; i += CONSUMER_THREADS)
-        if ((uint32_t)(i % G::MP) >= p.m) reinterpret_cast<float*>(smem + G::OFF_ACTS)[i] = 0.0f;
+      ok = false;
     }
-    // Everything below reads what the previous kernel wrote (A, and C when beta != 0).
-    ptx::pdl_wait();
-
-    bool ok = true;
-    // A consumer that gives up a wait keeps walking the loops (without waiting or
-    // computing) so that every warp meets the same sequence of barriers.
-    for (uint32_t c0 = 0; c0 < my_stages; c0 += ACT_STAGES) {
-      const uint32_t nst = min((uint32_t)ACT_STAGES, my_stages - c0);
-      const uint32_t ckb0 = (s_begin + c0) * KBT;
-      const uint32_t cnkb = min(nst * KBT, p.kblocks - ckb0);
-      if (c0 > 0) consumer_sync();  // the previous chunk's activations are no longer read
-      {
-        // Quantize A[:, ckb0*32 .. (ckb0+cnkb)*32) : 8 lanes per 32-block, 4 elements each.
-        // The trip count is uniform inside an 8-lane group but not across a warp, so
-        // the shuffles name only their own group.
-        const int grp = tid >> 3, u = tid & 7;
-        const uint32_t gmask = 0xFFu << (lane & 24);
-        const uint32_t items = ok ? p.m * cnkb : 0u;
-        for (uint32_t item = grp; item < items; item += CONSUMER_THREADS / 8) {
-          const uint32_t r = item / cnkb, kb = item % cnkb;
-          const float* src = p.a + (uint64_t)r * p.lda + (uint64_t)(ckb0 + kb) * QK + 4 * u;
-          float4 v;
-          if (p.a_vec4) {
-            v = *reinterpret_cast<const float4*>(src);
-          } else {
-            v.x = src[0]; v.y = src[1]; v.z = src[2]; v.w = src[3];
-          }
-          float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
-          amax = fmaxf(amax, __shfl_xor_sync(gmask, amax, 4));
-          amax = fmaxf(amax, __shfl_xor_sync(gmask, amax, 2));
-          amax = fmaxf(amax, __shfl_xor_sync(gmask, amax, 1));
-          float scale, inv;
-          activation_block_scales(amax, &scale, &inv);
-          uint8_t* row32 = smem + G::OFF_ACTQ + ((size_t)kb * G::MP + r) * 32;
-          store_act_quad<DT>(row32, u, quantize_activation_with_inv(v.x, inv), quantize_activation_with_inv(v.y, inv),
-                             quantize_activation_with_inv(v.z, inv), quantize_activation_with_inv(v.w, inv));
-          if (u == 0) reinterpret_cast<float*>(smem + G::OFF_ACTS)[kb * G::MP + r] = scale;
-        }
-        __syncwarp();
-      }
-      consumer_sync();
-
-      for (uint32_t st = 0; st < nst; st++) {
-        const uint32_t it = c0 + st;
-        const uint32_t slot = it % NS;
-        if (ok && (*abort_flag || !ptx::mbar_wait_bounded(bar_full + 8 * slot, (it / NS) & 1))) {
-          if (lane == 0 && !*abort_flag) {
-            atomicExch(p.fault, FAULT_WAIT_EXPIRED);
-            *abort_flag = 1;
-          }
-          ok = false;
-        }
-        const uint32_t kb0 = (s_begin + it) * KBT;
-        const uint32_t nkb = ok ? min((uint32_t)KBT, p.kblocks - kb0) : 0u;
-        const uint32_t stage = smem_base + slot * G::STAGE_BYTES;
-        for (uint32_t kbl = warp; kbl < nkb; kbl += CONSUMER_WARPS) {
-          const uint32_t akb = st * KBT + kbl;  // K block index inside the activation chunk
-          uint32_t bq[MT][2];
-          float as[MT][2];
-#pragma unroll
-          for (int t = 0; t < MT; t++) {
-            const uint2 b2 = *reinterpret_cast<const uint2*>(smem + G::OFF_ACTQ + ((size_t)akb * G::MP + t * 8 + g) * 32 + 8 * j);
-            bq[t][0] = b2.x;
-            bq[t][1] = b2.y;
-            const float2 s2 = *reinterpret_cast<const float2*>(smem + G::OFF_ACTS + ((size_t)akb * G::MP + t * 8 + 2 * j) * 4);
-            as[t][0] = s2.x;
-            as[t][1] = s2.y;
-          }
-#pragma unroll
-          for (int i = 0; i < 4; i++) {
-            uint32_t blk0, blk1;
-            bool al0, al1;
-            if (!NT) {
-              // rows g -> column 2i + 8g (even: codes 2 bytes past a word boundary),
-              // rows g+8 -> column 2i + 1 + 8g (odd: codes word aligned).
-              blk0 = stage + kbl * G::KM_PITCH + (2 * i + 8 * g) * G::BB;
-              blk1 = blk0 + G::BB;
-              al0 = false;
-              al1 = true;
-            } else {
-              blk0 = stage + (16 * i + g) * NT_ROW_PITCH + kbl * Q8_BYTES;
-              blk1 = blk0 + 8 * NT_ROW_PITCH;
-              al0 = al1 = (kbl & 1) != 0;
-            }
-            uint32_t a0, a1, a2, a3;
-            load_codes<DT>(blk0, al0, j, a0, a2);
-            load_codes<DT>(blk1, al1, j, a1, a3);
-            const float ws0 = load_scale<DT>(blk0), ws1 = load_scale<DT>(blk1);
-#pragma unroll
-            for (int t = 0; t < MT; t++) {
-              int d[4];
-              ptx::mma_s8(d, a0, a1, a2, a3, bq[t][0], bq[t][1]);
-              acc[i][t][0] += (float)d[0] * (as[t][0] * ws0);
-              acc[i][t][1] += (float)d[1] * (as[t][1] * ws0);
-              acc[i][t][2] += (float)d[2] * (as[t][0] * ws1);
-              acc[i][t][3] += (float)d[3] * (as[t][1] * ws1);
-            }
-          }
-        }
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(bar_empty + 8 * slot);
-      }
-    }
-
-    // ---------------- fold the four warps' partial sums ----------------
-    consumer_sync();  // every consumer is past its last read of the ring
-    float* partial = reinterpret_cast<float*>(smem);  // [warp][col][MP], over the drained ring
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-      const int col0 = NT ? 16 * i + g : 2 * i + 8 * g;
-      const int col1 = NT ? col0 + 8 : col0 + 1;
+    if (ok) {
+      // K blocks past the end of K arrive as zero-filled weights against zero-scaled
+      // activations, so all 8 blocks of a stage are always processed.
+      uint32_t b0 = smem_base + slot * G::STAGE_BYTES + off0, b1 = smem_base + slot * G::STAGE_BYTES + off1;  // block starts
+      uint32_t w0 = b0 + 4 * j, w1 = b1 + 4 * j;  // this lane's code words
+      uint32_t aq[MT], as[MT];
 #pragma unroll
       for (int t = 0; t < MT; t++) {
-        float* p0 = partial + ((size_t)warp * TN + col0) * G::MP + t * 8 + 2 * j;
-        float* p1 = partial + ((size_t)warp * TN + col1) * G::MP + t * 8 + 2 * j;
-        *reinterpret_cast<float2*>(p0) = make_float2(acc[i][t][0], acc[i][t][1]);
-        *reinterpret_cast<float2*>(p1) = make_float2(acc[i][t][2], acc[i][t][3]);
+        aq[t] = aq_lane[t] + s * KBT * aq_step[t];
+        as[t] = as_lane[t] + s * KBT * as_step[t];
       }
-    }
-    consumer_sync();
-    float* red = reinterpret_cast<float*>(smem + G::OFF_RED);
-    for (int idx = tid; idx < TN * G::MP; idx += CONSUMER_THREADS) {
-      float s = partial[idx];
+      // Ties every load below to this point: they cannot move above the wait.
+      asm volatile("" : "+r"(w0), "+r"(w1), "+r"(b0), "+r"(b1)::"memory");
 #pragma unroll
-      for (int w = 1; w < CONSUMER_WARPS; w++) s += partial[(size_t)w * TN * G::MP + idx];
-      red[idx] = s;
-    }
-    consumer_sync();
-  }
-
-  // ---------------- meet the other K slices of the cluster, store ----------------
-  if (S > 1) ptx::cluster_sync_all();
-  if (warp < CONSUMER_WARPS && !*abort_flag) {
-    const uint32_t cpr = TN / S;  // columns this rank finishes
-    const uint32_t red_addr = smem_base + G::OFF_RED;
-    for (uint32_t idx = tid; idx < cpr * p.m; idx += CONSUMER_THREADS) {
-      const uint32_t col = rank * cpr + idx % cpr;
-      const uint32_t r = idx / cpr;
-      if (col >= cols) continue;
-      float s = 0.0f;
-      if (S == 1) {
-        s = reinterpret_cast<const float*>(smem + G::OFF_RED)[col * G::MP + r];
-      } else {
-        for (uint32_t q = 0; q < S; q++) s += ptx::ld_cluster_f32(ptx::map_to_rank(red_addr + (col * G::MP + r) * 4, q));
+      for (int kbl = 0; kbl < KBT; kbl++) {
+        constexpr int STEP = NT ? Q8_BYTES : G::KM_PITCH;
+        const bool al0 = NT ? (kbl & 1) != 0 : false;
+        const bool al1 = NT ? (kbl & 1) != 0 : true;
+        uint32_t a0, a1, a2, a3;
+        load_codes<DT>(w0 + kbl * STEP, al0, a0, a2);
+        load_codes<DT>(w1 + kbl * STEP, al1, a1, a3);
+        const uint64_t ws = pack2(lds_f16(b0 + kbl * STEP), lds_f16(b1 + kbl * STEP));
+#pragma unroll
+        for (int t = 0; t < MT; t++) {
+          const uint2 bq = lds_u64(aq[t] + kbl * aq_step[t]);
+          uint64_t as_even, as_odd;  // (s, s) of activation rows 2j and 2j+1
+          lds_f32x4(as[t] + kbl * as_step[t], as_even, as_odd);
+          int d[4];
+#ifdef AION_GEMV_NOMMA
+          d[0] = a0 ^ bq.x; d[1] = a1 ^ bq.y; d[2] = a2 + bq.x; d[3] = a3 + bq.y;  // lab only: timing without the MMA
+#else
+          ptx::mma_s8(d, a0, a1, a2, a3, bq.x, bq.y);
+#endif
+          // d[0], d[2]: rows g, g+8 against activation row 2j; d[1], d[3]: against row 2j+1.
+          acc[t][0] = fma2(mul2(pack2((float)d[0], (float)d[2]), ws), as_even, acc[t][0]);
+          if (!M1) acc[t][1] = fma2(mul2(pack2((float)d[1], (float)d[3]), ws), as_odd, acc[t][1]);
+        }
       }
-      float* cp = p.c + (uint64_t)r * p.ldc + n0 + col;
-      *cp = (p.beta == 0.0f) ? p.alpha * s : p.alpha * s + p.beta * *cp;
+    }
+    __syncwarp();
+    if (lane == 0) ptx::mbar_arrive(bar_empty + 8 * slot);
+
+    if (s == Sg - 1 || uu == u_end - 1) {
+      // ---------------- this CTA's share of `tile` is complete ----------------
+      GEMV_TRACE(5);
+      const uint64_t tile_u0 = (uint64_t)tile * Sg;
+      const bool whole = (uu + 1 - tile_u0 == Sg) && (tile_u0 >= u_begin);
+      const uint32_t n0 = tile * TN;
+      float v[MT][4];  // [t][0..3] = (row g, m 2j), (row g+8, m 2j), (row g, m 2j+1), (row g+8, m 2j+1)
+#pragma unroll
+      for (int t = 0; t < MT; t++) {
+        unpack2(acc[t][0], v[t][0], v[t][1]);
+        unpack2(acc[t][1], v[t][2], v[t][3]);
+        acc[t][0] = acc[t][1] = 0ull;
+      }
+      bool store = whole;
+      if (!whole) {
+        const uint32_t c_first = unit_owner(tile_u0, U, NG), c_last = unit_owner(tile_u0 + Sg - 1, U, NG);
+        const uint32_t nparts = c_last - c_first + 1;
+        float* mine = p.partials + ((size_t)blockIdx.x * 2 + (tile == first_tile ? 0 : 1)) * (TN * MPA);
+#pragma unroll
+        for (int t = 0; t < MT; t++) {
+          *reinterpret_cast<float2*>(mine + col0 * MPA + t * 8 + 2 * j) = make_float2(v[t][0], v[t][2]);
+          *reinterpret_cast<float2*>(mine + col1 * MPA + t * 8 + 2 * j) = make_float2(v[t][1], v[t][3]);
+        }
+        __threadfence();
+        __syncwarp();
+        int last = 0;
+        if (lane == 0) {
+          int* tk = p.tickets + (size_t)tile * CONSUMER_WARPS + warp;
+          last = (atomicAdd(tk, 1) == (int)nparts - 1);
+          if (last) *tk = 0;  // ready for the next launch
+        }
+        last = __shfl_sync(0xFFFFFFFFu, last, 0);
+        if (last) {
+          // The last part to arrive adds all of them in CTA order.
+          __threadfence();
+#pragma unroll
+          for (int t = 0; t < MT; t++) v[t][0] = v[t][1] = v[t][2] = v[t][3] = 0.0f;
+          for (uint32_t part = 0; part < nparts; part++) {
+            const uint32_t cc = c_first + part;
+            const uint32_t cc_first_tile = (uint32_t)((U * cc / NG) / Sg);
+            const float* src = p.partials + ((size_t)cc * 2 + (tile == cc_first_tile ? 0 : 1)) * (TN * MPA);
+#pragma unroll
+            for (int t = 0; t < MT; t++) {
+              const float2 x0 = __ldcg(reinterpret_cast<const float2*>(src + col0 * MPA + t * 8 + 2 * j));
+              const float2 x1 = __ldcg(reinterpret_cast<const float2*>(src + col1 * MPA + t * 8 + 2 * j));
+              v[t][0] += x0.x; v[t][2] += x0.y;
+              v[t][1] += x1.x; v[t][3] += x1.y;
+            }
+          }
+          store = true;
+        }
+      }
+      if (store && !*abort_flag) {
+#pragma unroll
+        for (int t = 0; t < MT; t++)
+#pragma unroll
+          for (int e = 0; e < 4; e++) {
+            const uint32_t mrow = t * 8 + 2 * j + (e >> 1);
+            const uint32_t col = n0 + ((e & 1) ? col1 : col0);
+            if (mrow < p.m && col < p.n) {
+              float* cp = p.c + (uint64_t)mrow * p.ldc + col;
+              *cp = (p.beta == 0.0f) ? p.alpha * v[t][e] : p.alpha * v[t][e] + p.beta * *cp;
+            }
+          }
+      }
+    }
+    if (++s == Sg) {
+      s = 0;
+      tile++;
     }
   }
-  // No CTA may exit while a peer still reads its shared memory.
-  if (S > 1) ptx::cluster_sync_all();
+  GEMV_TRACE(6);
 }
 
-template <int DT, bool NT, int MT>
-int32_t launch(AionCudaDevice* dev, const GemvParams& p, uint32_t split) {
-  using G = Geom<DT, NT, MT>;
-  auto kernel = gemv_q_mma_kernel<DT, NT, MT>;
-  static bool configured[16] = {};
-  if (!configured[dev->ordinal & 15]) {
-    AION_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM_BYTES));
-    configured[dev->ordinal & 15] = true;
+template <int DT, bool NT, int MT, bool M1>
+int32_t launch(AionCudaDevice* dev, GemvParams p, const uint8_t* b, uint64_t ldb) {
+  using G = Geom<DT, NT>;
+  auto kernel = gemv_q_mma_kernel<DT, NT, MT, M1>;
+  constexpr uint32_t MP2 = M1 ? 2 : 8 * MT;
+  const size_t smem = G::OFF_ACT + act_bytes(p.stages_per_tile * KBT, MP2);
+  // Kernel attributes and occupancy depend on the device and the dynamic size only.
+  static size_t configured_smem[16] = {};
+  static size_t occ_smem[16] = {};
+  static int occ_blocks[16] = {};
+  const int di = dev->ordinal & 15;
+  if (smem > configured_smem[di]) {
+    AION_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured_smem[di] = smem;
   }
-  const uint32_t tiles = (p.n + TN - 1) / TN;
+  if (occ_smem[di] != smem) {
+    int nb = 0;
+    AION_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, kernel, THREADS, smem));
+    if (nb < 1) return fail(AION_CUDA_INTERNAL_ERROR, "gemv: kernel does not fit an SM with %llu bytes of shared memory", (unsigned long long)smem);
+    occ_blocks[di] = nb;
+    occ_smem[di] = smem;
+  }
+  uint64_t grid = (uint64_t)occ_blocks[di] * dev->sm_count;
+  if (dev->gemv_split_override) grid = (uint64_t)dev->gemv_split_override * dev->sm_count;  // CTAs per SM, tuning only
+  if (grid > p.units) grid = p.units;
+
+  // Scratch for tiles shared by several CTAs: two partial slots per CTA, one ticket per (tile, warp).
+  constexpr int MPA = 8 * MT;
+  if (int32_t st = dev->reserve_gemv_fixup((size_t)grid * 2 * TN * MPA * sizeof(float), (size_t)p.tiles * CONSUMER_WARPS)) return st;
+  p.partials = dev->gemv_partials;
+  p.tickets = dev->gemv_tickets;
+
+  // The weight tensor as bytes in 8-byte elements.
+  const CUtensorMap* tm = nullptr;
+  if (!NT && DT == AION_CUDA_DTYPE_Q4_0) {
+    // [kblocks][n*18 bytes]: one box = 8 block rows x 64 blocks (1152 bytes, within the 2048-byte box row).
+    const uint64_t dims[2] = {(uint64_t)p.n * G::BB, p.kblocks};
+    const uint64_t strides[1] = {ldb * G::BB};
+    const uint32_t box[2] = {(uint32_t)TN * G::BB, KBT};
+    if (int32_t st = tensor_map_bytes(dev, b, 2, dims, strides, box, &tm)) return st;
+  } else if (!NT) {
+    // q8: 64 blocks side by side are 2176 bytes, more than a box row holds, so the row is
+    // viewed as [n/8 groups][8 blocks]: one box = 8 block rows x 8 groups = 64 columns.
+    const uint64_t dims[3] = {8ull * G::BB, p.n / 8, p.kblocks};
+    const uint64_t strides[2] = {8ull * G::BB, ldb * G::BB};
+    const uint32_t box[3] = {8u * G::BB, TN / 8, KBT};
+    if (int32_t st = tensor_map_bytes(dev, b, 3, dims, strides, box, &tm)) return st;
+  } else {
+    // [n rows][kblocks*34 bytes]: one box = 64 rows x 8 blocks.
+    const uint64_t dims[2] = {(uint64_t)p.kblocks * Q8_BYTES, p.n};
+    const uint64_t strides[1] = {ldb * Q8_BYTES};
+    const uint32_t box[2] = {NT_ROW_PITCH, TN};
+    if (int32_t st = tensor_map_bytes(dev, b, 2, dims, strides, box, &tm)) return st;
+  }
+
   cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3(tiles * split);
+  cfg.gridDim = dim3((unsigned)grid);
   cfg.blockDim = dim3(THREADS);
-  cfg.dynamicSmemBytes = G::SMEM_BYTES;
+  cfg.dynamicSmemBytes = smem;
   cfg.stream = dev->stream;
-  cudaLaunchAttribute attrs[2];
-  attrs[0].id = cudaLaunchAttributeClusterDimension;
-  attrs[0].val.clusterDim.x = split;
-  attrs[0].val.clusterDim.y = 1;
-  attrs[0].val.clusterDim.z = 1;
-  attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attrs[1].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attrs[1];
+  attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attrs[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attrs;
-  cfg.numAttrs = 2;
-  AION_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, p));
+  cfg.numAttrs = 1;
+  AION_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, p, *tm));
   return AION_CUDA_OK;
+}
+
+template <int DT, bool NT>
+int32_t launch_m(AionCudaDevice* dev, const GemvParams& p, const uint8_t* b, uint64_t ldb) {
+  if (p.m == 1) return launch<DT, NT, 1, true>(dev, p, b, ldb);
+  if (p.m <= 8) return launch<DT, NT, 1, false>(dev, p, b, ldb);
+  return launch<DT, NT, 2, false>(dev, p, b, ldb);
 }
 
 }  // namespace
 
 int32_t gemv_mma(AionCudaDevice* dev, const MatMulArgs& g, bool probe_only) {
   if (g.m > 16 || g.k == 0) return AION_CUDA_UNSUPPORTED;
-  if (g.n > 0xFFFFFFFFull - TN || g.k / QK > 0xFFFFFFFFull) return AION_CUDA_UNSUPPORTED;
+  if (g.n > 0x7FFFFFFFull - TN || g.k / QK > 0x7FFFFFFFull) return AION_CUDA_UNSUPPORTED;
   const uint64_t kblocks = g.k / QK;
   const uintptr_t baddr = reinterpret_cast<uintptr_t>(g.b);
   if (baddr & 15) return AION_CUDA_UNSUPPORTED;
   if (!g.nt) {
-    // Every 64-column segment of a block row must start and end on 16 bytes.
+    // Groups of 8 blocks (144 / 272 bytes) are the tensor map's innermost rows.
     if (g.n % 8 != 0 || g.ldb % 8 != 0) return AION_CUDA_UNSUPPORTED;
   } else {
     if (g.dtype != AION_CUDA_DTYPE_Q8_0 || g.order != AION_CUDA_ORDER_ROW_MAJOR) return AION_CUDA_UNSUPPORTED;
@@ -419,37 +580,45 @@ int32_t gemv_mma(AionCudaDevice* dev, const MatMulArgs& g, bool probe_only) {
   }
   if (probe_only) return AION_CUDA_OK;
 
-  GemvParams p{};
-  p.a = g.a;
-  p.b = g.b;
-  p.c = g.c;
-  p.m = (uint32_t)g.m;
-  p.n = (uint32_t)g.n;
-  p.kblocks = (uint32_t)kblocks;
-  p.lda = g.lda;
-  p.ldb = g.ldb;
-  p.ldc = g.ldc;
-  p.alpha = g.alpha;
-  p.beta = g.beta;
-  p.fault = dev->fault_dev;
-  p.a_vec4 = ((reinterpret_cast<uintptr_t>(g.a) & 15) == 0 && g.lda % 4 == 0) ? 1u : 0u;
+  const uint32_t mp2 = g.m == 1 ? 2u : (g.m <= 8 ? 8u : 16u);  // activation rows held per CTA (see MP2)
+  // K blocks whose quantized activations fit the per-CTA budget; a deeper K is issued as
+  // several launches that accumulate into C, like the reference's walk over K in chunks
+  // (src/aion/backend/cpu/exec/matmul.zig:431-434).
+  uint64_t kb_max = (ACT_BUDGET_BYTES / ((size_t)mp2 * 40)) / KBT * KBT;
+  if (kb_max < KBT) kb_max = KBT;
 
-  // Split K over a cluster until the grid covers the SMs about twice, as far as the
-  // stage count allows.
-  const uint32_t tiles = (p.n + TN - 1) / TN;
-  const uint32_t stages = (p.kblocks + KBT - 1) / KBT;
-  uint32_t split = 1;
-  while (split < 8 && tiles * split < (uint32_t)dev->sm_count * 3 / 2 && split * 2 <= stages) split *= 2;
-  if (dev->gemv_split_override) {
-    split = dev->gemv_split_override;
-    while (split > 1 && split > stages) split /= 2;
+  for (uint64_t kb0 = 0; kb0 < kblocks; kb0 += kb_max) {
+    const uint64_t nkb = kblocks - kb0 < kb_max ? kblocks - kb0 : kb_max;
+    GemvParams p{};
+    p.a = g.a + kb0 * QK;
+    p.c = g.c;
+    p.m = (uint32_t)g.m;
+    p.n = (uint32_t)g.n;
+    p.kblocks = (uint32_t)nkb;
+    p.mp2 = mp2;
+    p.lda = g.lda;
+    p.ldc = g.ldc;
+    p.alpha = g.alpha;
+    p.beta = kb0 == 0 ? g.beta : 1.0f;
+    p.tiles = (uint32_t)((g.n + TN - 1) / TN);
+    p.stages_per_tile = (uint32_t)((nkb + KBT - 1) / KBT);
+    p.units = (uint64_t)p.tiles * p.stages_per_tile;
+    p.fault = dev->fault_dev;
+    p.a_vec4 = ((reinterpret_cast<uintptr_t>(p.a) & 15) == 0 && g.lda % 4 == 0) ? 1u : 0u;
+#ifdef AION_GEMV_TRACE
+    p.trace = g_gemv_trace;
+#endif
+    int32_t st;
+    if (g.nt) {
+      st = launch_m<AION_CUDA_DTYPE_Q8_0, true>(dev, p, g.b + kb0 * Q8_BYTES, g.ldb);
+    } else if (g.dtype == AION_CUDA_DTYPE_Q8_0) {
+      st = launch_m<AION_CUDA_DTYPE_Q8_0, false>(dev, p, g.b + kb0 * g.ldb * Q8_BYTES, g.ldb);
+    } else {
+      st = launch_m<AION_CUDA_DTYPE_Q4_0, false>(dev, p, g.b + kb0 * g.ldb * Q4_BYTES, g.ldb);
+    }
+    if (st != AION_CUDA_OK) return st;
   }
-
-  const bool two = g.m > 8;
-  if (g.nt) return two ? launch<AION_CUDA_DTYPE_Q8_0, true, 2>(dev, p, split) : launch<AION_CUDA_DTYPE_Q8_0, true, 1>(dev, p, split);
-  if (g.dtype == AION_CUDA_DTYPE_Q8_0)
-    return two ? launch<AION_CUDA_DTYPE_Q8_0, false, 2>(dev, p, split) : launch<AION_CUDA_DTYPE_Q8_0, false, 1>(dev, p, split);
-  return two ? launch<AION_CUDA_DTYPE_Q4_0, false, 2>(dev, p, split) : launch<AION_CUDA_DTYPE_Q4_0, false, 1>(dev, p, split);
+  return AION_CUDA_OK;
 }
 
 }  // namespace aion

@@ -329,18 +329,58 @@ class CudaSession:
                 # (src/aion/runtime/executable.zig:355-357).
                 raise BackendError(capi.UNSUPPORTED, f"step {type(step).__name__} is outside this backend")
 
-    def record(self, program: Sequence[object]) -> "RecordedProgram":
+    @staticmethod
+    def _touches(step) -> tuple[set, set]:
+        """(tensors read, tensors written) of a step, by TensorId."""
+        if isinstance(step, (StepMatMul, StepMatMulNT)):
+            reads = {step.a, step.b} | ({step.c} if step.beta != 0.0 else set())
+            return reads, {step.c}
+        if isinstance(step, StepAttention):
+            reads = {step.q, step.k, step.v}
+            reads |= {t for t in (step.query_positions, step.kv_lengths) if t is not None}
+            return reads, {step.out}
+        return set(), set()
+
+    def record(self, program: Sequence[object], lanes: int = capi.RECORD_LANES) -> "RecordedProgram":
         """Record the steps once into a replayable device program (one launch per replay).
 
-        Steps that need scratch must have executed once before (run `execute` first)."""
-        _check(self._lib.aion_cuda_record_begin(self.backend._h))
-        h = C.c_void_p()
+        Steps that share no tensor are issued into parallel lanes, so the device may overlap
+        them; a step that depends on earlier ones follows them in the same lane, or after a
+        join when they sit in several lanes. Steps that need scratch must have executed once
+        before (run `execute` first)."""
+        lib, h = self._lib, self.backend._h
+        lanes = max(1, min(int(lanes), capi.RECORD_LANES))
+        _check(lib.aion_cuda_record_begin(h))
+        prog = C.c_void_p()
         try:
-            self.execute(program)
+            writer: dict[int, int] = {}            # tensor -> lane that last wrote it since the last join
+            readers: dict[int, set] = {}           # tensor -> lanes that read it since the last join
+            next_lane = 0
+            for step in program:
+                reads, writes = self._touches(step)
+                clash = {writer[t] for t in (reads | writes) if t in writer}
+                for t in writes:
+                    clash |= readers.get(t, set())
+                if not clash:
+                    lane = next_lane
+                    next_lane = (next_lane + 1) % lanes
+                elif len(clash) == 1:
+                    lane = next(iter(clash))
+                else:
+                    _check(lib.aion_cuda_record_join(h))
+                    writer.clear()
+                    readers.clear()
+                    lane, next_lane = 0, 1 % lanes
+                _check(lib.aion_cuda_record_lane(h, lane))
+                self.execute([step])
+                for t in writes:
+                    writer[t] = lane
+                for t in reads:
+                    readers.setdefault(t, set()).add(lane)
         finally:
-            st = self._lib.aion_cuda_record_end(self.backend._h, C.byref(h))
+            st = lib.aion_cuda_record_end(h, C.byref(prog))
         _check(st)
-        return RecordedProgram(self.backend, h)
+        return RecordedProgram(self.backend, prog)
 
     def retire_resources(self) -> None:
         self.backend.sync()

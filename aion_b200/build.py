@@ -59,7 +59,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     with cf.ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
         objs = list(ex.map(lambda s: _compile(s, verbose), srcs))
     if (not os.path.exists(LIB)) or any(os.path.getmtime(o) > os.path.getmtime(LIB) for o in objs):
-        cmd = ["nvcc", *ARCH, "-shared", "-o", LIB, *objs, "-lcuda"]
+        cmd = ["nvcc", *ARCH, "-shared", "-o", LIB, *objs]
         subprocess.run(cmd, check=True)
     return LIB
 

@@ -16,6 +16,7 @@ ORDER_ROW_MAJOR, ORDER_LANES4, ORDER_LANES8, ORDER_LANES16, ORDER_LANES32, ORDER
 WINDOW_UNBOUNDED = 0xFFFFFFFF
 MATMUL_AUTO, MATMUL_FORCE_GENERIC, MATMUL_FORCE_GEMV, MATMUL_FORCE_GEMM = 0, 1, 2, 4
 GEMV_MAX_M = 16
+RECORD_LANES = 8
 
 LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libaion_cuda.so")
 
@@ -83,6 +84,8 @@ SIGNATURES = {
     "aion_cuda_get_stream": (C.c_void_p, [_DEV]),
     "aion_cuda_sync": (C.c_int32, [_DEV]),
     "aion_cuda_record_begin": (C.c_int32, [_DEV]),
+    "aion_cuda_record_lane": (C.c_int32, [_DEV, C.c_uint32]),
+    "aion_cuda_record_join": (C.c_int32, [_DEV]),
     "aion_cuda_record_end": (C.c_int32, [_DEV, C.POINTER(C.c_void_p)]),
     "aion_cuda_program_launch": (C.c_int32, [_DEV, C.c_void_p]),
     "aion_cuda_program_destroy": (None, [_DEV, C.c_void_p]),

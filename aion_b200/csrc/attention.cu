@@ -614,8 +614,8 @@ int32_t attention_launch(AionCudaDevice* dev, const AionCudaAttention* s) {
       const size_t part_bytes = (size_t)units * splits * 8 * (Dk + 2) * sizeof(float);
       if (int32_t st = dev->reserve_scratch(part_bytes)) return st;
       if (int32_t st = dev->reserve_tickets(units)) return st;
-      p.partial = static_cast<float*>(dev->scratch);
-      p.tickets = dev->tickets;
+      p.partial = static_cast<float*>(dev->lane_scratch());
+      p.tickets = dev->lane_tickets();
     }
     const bool qf32 = s->q_dtype == AION_CUDA_DTYPE_F32;
     switch (Dk) {

@@ -54,8 +54,19 @@ struct AionCudaDevice {
   // Device status word kernels write a DeviceFault into, and its pinned host mirror.
   int* fault_dev = nullptr;
   int* fault_host = nullptr;
+  // While recording, independent steps may be issued into parallel lanes (branches of the
+  // recorded graph). Lane 0 is the device's stream; `stream` is always the lane in use.
+  static constexpr int LANES = 8;
+  cudaStream_t main_stream = nullptr;       // `stream` outside lanes
+  cudaStream_t lane_streams[LANES] = {};    // [0] unused
+  cudaEvent_t lane_events[LANES] = {};
+  cudaEvent_t fork_event = nullptr;
+  bool lane_forked[LANES] = {};
+  int cur_lane = 0;
   // Kernel scratch (quantized activations of the any-shape path, split partials);
-  // grown on demand, never shrunk, freed with the device.
+  // grown on demand, never shrunk, freed with the device. Every scratch buffer holds one
+  // slice per lane (`*_bytes` / `*_cap` are the size of one slice), so steps recorded in
+  // different lanes never share scratch.
   void* scratch = nullptr;
   size_t scratch_bytes = 0;
   // Tuning override (environment AION_CUDA_GEMV_SPLIT): K-split of the tiled GEMV, 0 = automatic.
@@ -84,6 +95,10 @@ struct AionCudaDevice {
   int32_t reserve_scratch(size_t bytes);
   int32_t reserve_tickets(size_t count);
   int32_t reserve_gemv_fixup(size_t partial_bytes, size_t tickets);
+  void* lane_scratch() const { return static_cast<uint8_t*>(scratch) + (size_t)cur_lane * scratch_bytes; }
+  int* lane_tickets() const { return tickets + (size_t)cur_lane * tickets_cap; }
+  float* lane_gemv_partials() const { return reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(gemv_partials) + (size_t)cur_lane * gemv_partials_bytes); }
+  int* lane_gemv_tickets() const { return gemv_tickets + (size_t)cur_lane * gemv_tickets_cap; }
   // Reads the status word back (call after the stream has been synchronized).
   int32_t check_fault();
 };

@@ -90,8 +90,21 @@ int32_t tensor_map_bytes(AionCudaDevice* dev, const void* base, uint32_t rank, c
       if ((stride_bytes[i - 1] & 15) || box[i] > 256)
         return fail(AION_CUDA_INTERNAL_ERROR, "tensor map: view geometry is not TMA-addressable");
     }
+    // The driver entry point is looked up through the runtime, so the library does not
+    // link libcuda and still loads on a machine without a driver.
+    typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                      const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                      CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeTiledFn encode = nullptr;
+    if (!encode) {
+      void* fn = nullptr;
+      cudaDriverEntryPointQueryResult qres;
+      AION_CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+      if (!fn || qres != cudaDriverEntryPointSuccess) return fail(AION_CUDA_INTERNAL_ERROR, "cuTensorMapEncodeTiled is not available from this driver");
+      encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
     CUtensorMap tm;
-    const CUresult r = cuTensorMapEncodeTiled(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT64, rank, const_cast<void*>(base), gdim, gstride, bx,
+    const CUresult r = encode(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT64, rank, const_cast<void*>(base), gdim, gstride, bx,
                                               estride, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
                                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(AION_CUDA_INTERNAL_ERROR, "cuTensorMapEncodeTiled failed with %d", (int)r);
@@ -122,7 +135,7 @@ int32_t AionCudaDevice::reserve_scratch(size_t bytes) {
   scratch_bytes = 0;
   size_t want = bytes + (bytes >> 2);
   want = (want + 255) & ~size_t(255);
-  AION_CUDA_TRY(cudaMalloc(&scratch, want));
+  AION_CUDA_TRY(cudaMalloc(&scratch, want * LANES));
   scratch_bytes = want;
   return AION_CUDA_OK;
 }
@@ -135,8 +148,8 @@ int32_t AionCudaDevice::reserve_tickets(size_t count) {
   tickets = nullptr;
   tickets_cap = 0;
   size_t want = count < 1024 ? 1024 : count + (count >> 1);
-  AION_CUDA_TRY(cudaMalloc(&tickets, want * sizeof(int)));
-  AION_CUDA_TRY(cudaMemsetAsync(tickets, 0, want * sizeof(int), stream));
+  AION_CUDA_TRY(cudaMalloc(&tickets, want * sizeof(int) * LANES));
+  AION_CUDA_TRY(cudaMemsetAsync(tickets, 0, want * sizeof(int) * LANES, stream));
   tickets_cap = want;
   return AION_CUDA_OK;
 }
@@ -149,7 +162,7 @@ int32_t AionCudaDevice::reserve_gemv_fixup(size_t partial_bytes, size_t ticket_c
     gemv_partials = nullptr;
     gemv_partials_bytes = 0;
     const size_t want = (partial_bytes + (partial_bytes >> 2) + 255) & ~size_t(255);
-    AION_CUDA_TRY(cudaMalloc(&gemv_partials, want));
+    AION_CUDA_TRY(cudaMalloc(&gemv_partials, want * LANES));
     gemv_partials_bytes = want;
   }
   if (ticket_count > gemv_tickets_cap) {
@@ -159,8 +172,8 @@ int32_t AionCudaDevice::reserve_gemv_fixup(size_t partial_bytes, size_t ticket_c
     gemv_tickets = nullptr;
     gemv_tickets_cap = 0;
     const size_t want = ticket_count < 4096 ? 4096 : ticket_count + (ticket_count >> 1);
-    AION_CUDA_TRY(cudaMalloc(&gemv_tickets, want * sizeof(int)));
-    AION_CUDA_TRY(cudaMemsetAsync(gemv_tickets, 0, want * sizeof(int), stream));
+    AION_CUDA_TRY(cudaMalloc(&gemv_tickets, want * sizeof(int) * LANES));
+    AION_CUDA_TRY(cudaMemsetAsync(gemv_tickets, 0, want * sizeof(int) * LANES, stream));
     gemv_tickets_cap = want;
   }
   return AION_CUDA_OK;
@@ -226,6 +239,7 @@ int32_t aion_cuda_device_create(int32_t ordinal, AionCudaDevice** out) {
     return st;
   }
   d->stream = d->own_stream;
+  d->main_stream = d->own_stream;
   d->sm_count = d->prop.multiProcessorCount;
   if (const char* e2 = std::getenv("AION_CUDA_GEMV_SPLIT")) {
     const int v = std::atoi(e2);
@@ -250,6 +264,11 @@ void aion_cuda_device_destroy(AionCudaDevice* dev) {
     cudaStreamSynchronize(dev->own_stream);
     cudaStreamDestroy(dev->own_stream);
   }
+  for (int l = 1; l < AionCudaDevice::LANES; l++) {
+    if (dev->lane_streams[l]) cudaStreamDestroy(dev->lane_streams[l]);
+    if (dev->lane_events[l]) cudaEventDestroy(dev->lane_events[l]);
+  }
+  if (dev->fork_event) cudaEventDestroy(dev->fork_event);
   if (dev->scratch) cudaFree(dev->scratch);
   if (dev->tickets) cudaFree(dev->tickets);
   if (dev->gemv_partials) cudaFree(dev->gemv_partials);
@@ -277,7 +296,9 @@ uint8_t aion_cuda_quant_block_order(AionCudaDevice*) { return AION_CUDA_ORDER_RO
 
 int32_t aion_cuda_set_stream(AionCudaDevice* dev, void* cuda_stream) {
   if (!dev) return fail(AION_CUDA_INVALID_ARGUMENT, "set_stream: null device");
+  if (dev->recording) return fail(AION_CUDA_INVALID_ARGUMENT, "set_stream: not while recording");
   dev->stream = cuda_stream ? static_cast<cudaStream_t>(cuda_stream) : dev->own_stream;
+  dev->main_stream = dev->stream;
   return AION_CUDA_OK;
 }
 
@@ -299,16 +320,63 @@ int32_t aion_cuda_record_begin(AionCudaDevice* dev) {
   if (!dev) return fail(AION_CUDA_INVALID_ARGUMENT, "record_begin: null device");
   if (dev->recording) return fail(AION_CUDA_INVALID_ARGUMENT, "record_begin: already recording");
   if (int32_t st = dev->make_current()) return st;
+  // Lane streams and events are created on first use (outside any capture).
+  for (int l = 1; l < AionCudaDevice::LANES; l++) {
+    if (!dev->lane_streams[l]) AION_CUDA_TRY(cudaStreamCreateWithFlags(&dev->lane_streams[l], cudaStreamNonBlocking));
+    if (!dev->lane_events[l]) AION_CUDA_TRY(cudaEventCreateWithFlags(&dev->lane_events[l], cudaEventDisableTiming));
+  }
+  if (!dev->fork_event) AION_CUDA_TRY(cudaEventCreateWithFlags(&dev->fork_event, cudaEventDisableTiming));
   AION_CUDA_TRY(cudaStreamBeginCapture(dev->stream, cudaStreamCaptureModeThreadLocal));
   dev->recording = true;
   return AION_CUDA_OK;
+}
+
+static int32_t join_lanes(AionCudaDevice* dev) {
+  for (int l = 1; l < AionCudaDevice::LANES; l++) {
+    if (!dev->lane_forked[l]) continue;
+    AION_CUDA_TRY(cudaEventRecord(dev->lane_events[l], dev->lane_streams[l]));
+    AION_CUDA_TRY(cudaStreamWaitEvent(dev->main_stream, dev->lane_events[l], 0));
+    dev->lane_forked[l] = false;
+  }
+  dev->cur_lane = 0;
+  dev->stream = dev->main_stream;
+  return AION_CUDA_OK;
+}
+
+int32_t aion_cuda_record_lane(AionCudaDevice* dev, uint32_t lane) {
+  if (!dev) return fail(AION_CUDA_INVALID_ARGUMENT, "record_lane: null device");
+  if (!dev->recording) return fail(AION_CUDA_INVALID_ARGUMENT, "record_lane: not recording");
+  if (lane >= (uint32_t)AionCudaDevice::LANES) return fail(AION_CUDA_INVALID_ARGUMENT, "record_lane: lane %u of %d", lane, AionCudaDevice::LANES);
+  if (lane != 0 && !dev->lane_forked[lane]) {
+    // The lane starts after everything recorded so far on the device's own stream.
+    AION_CUDA_TRY(cudaEventRecord(dev->fork_event, dev->main_stream));
+    AION_CUDA_TRY(cudaStreamWaitEvent(dev->lane_streams[lane], dev->fork_event, 0));
+    dev->lane_forked[lane] = true;
+  }
+  dev->cur_lane = (int)lane;
+  dev->stream = lane == 0 ? dev->main_stream : dev->lane_streams[lane];
+  return AION_CUDA_OK;
+}
+
+int32_t aion_cuda_record_join(AionCudaDevice* dev) {
+  if (!dev) return fail(AION_CUDA_INVALID_ARGUMENT, "record_join: null device");
+  if (!dev->recording) return fail(AION_CUDA_INVALID_ARGUMENT, "record_join: not recording");
+  return join_lanes(dev);
 }
 
 int32_t aion_cuda_record_end(AionCudaDevice* dev, AionCudaProgram** out) {
   if (!dev || !out) return fail(AION_CUDA_INVALID_ARGUMENT, "record_end: null argument");
   *out = nullptr;
   if (!dev->recording) return fail(AION_CUDA_INVALID_ARGUMENT, "record_end: not recording");
+  const int32_t jst = join_lanes(dev);
   dev->recording = false;
+  if (jst != AION_CUDA_OK) {
+    cudaGraph_t dead = nullptr;
+    cudaStreamEndCapture(dev->main_stream, &dead);
+    if (dead) cudaGraphDestroy(dead);
+    cudaGetLastError();
+    return jst;
+  }
   cudaGraph_t graph = nullptr;
   cudaError_t e = cudaStreamEndCapture(dev->stream, &graph);
   if (e != cudaSuccess || !graph) {

@@ -37,9 +37,6 @@
 
 namespace aion {
 
-#ifdef AION_GEMV_TRACE
-unsigned long long* g_gemv_trace = nullptr;
-#endif
 
 namespace {
 
@@ -52,18 +49,6 @@ constexpr int THREADS = CONSUMER_THREADS + 32;
 constexpr int NT_ROW_PITCH = KBT * Q8_BYTES;  // 272: 16-byte multiple, 4 words mod 32 banks
 constexpr size_t ACT_BUDGET_BYTES = 40 * 1024;  // quantized activations kept per CTA
 
-#ifdef AION_GEMV_TRACE
-#define GEMV_TRACE(slot)                                                          \
-  do {                                                                            \
-    if (p.trace && (threadIdx.x & 31) == 0) {                                     \
-      unsigned long long t_;                                                      \
-      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                      \
-      p.trace[((size_t)blockIdx.x * 5 + (threadIdx.x >> 5)) * 8 + (slot)] = t_;   \
-    }                                                                             \
-  } while (0)
-#else
-#define GEMV_TRACE(slot) do {} while (0)
-#endif
 
 struct GemvParams {
   const float* a;
@@ -78,9 +63,6 @@ struct GemvParams {
   int* tickets;     // [tile][warp]
   int* fault;
   uint32_t a_vec4;  // A rows may be read as float4
-#ifdef AION_GEMV_TRACE
-  unsigned long long* trace;
-#endif
 };
 
 template <int DT, bool NT>
@@ -96,53 +78,56 @@ struct Geom {
 
 // Shared-memory bytes of the quantized activations: per K block, mp2 rows of 32 codes,
 // then mp2/2 scale quads (s_even, s_even, s_odd, s_odd).
-__host__ __device__ inline size_t act_bytes(uint32_t kb_pad, uint32_t mp2) { return (size_t)kb_pad * mp2 * 40 + 16; }
+__host__ __device__ inline size_t act_bytes(uint32_t kb_pad, uint32_t mp2, uint32_t mt) {
+  return (size_t)kb_pad * (mp2 * 32 + (mp2 == 2 ? 16 : mt * 64));
+}
 
 // Shared-memory loads by 32-bit shared address. They are plain (non-volatile) asm so the
 // compiler may interleave the loads of independent K blocks; each takes its address from
 // a register the mbarrier wait has touched, which keeps it after the wait. Constant
 // offsets fold into the instruction.
+template <int OFF>
 __device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
   uint32_t v;
-  asm("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  asm("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(OFF));
   return v;
 }
+template <int OFF>
 __device__ __forceinline__ float lds_f16(uint32_t addr) {
   unsigned short h;
-  asm("ld.shared.u16 %0, [%1];" : "=h"(h) : "r"(addr));
+  asm("ld.shared.u16 %0, [%1+%2];" : "=h"(h) : "r"(addr), "n"(OFF));
   return __half2float(__ushort_as_half(h));
 }
+template <int OFF>
 __device__ __forceinline__ uint2 lds_u64(uint32_t addr) {
   uint2 v;
-  asm("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  asm("ld.shared.v2.u32 {%0, %1}, [%2+%3];" : "=r"(v.x), "=r"(v.y) : "r"(addr), "n"(OFF));
   return v;
 }
+template <int OFF>
 __device__ __forceinline__ void lds_f32x4(uint32_t addr, uint64_t& lo, uint64_t& hi) {
-  asm("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(lo), "=l"(hi) : "r"(addr));
+  asm("ld.shared.v2.b64 {%0, %1}, [%2+%3];" : "=l"(lo), "=l"(hi) : "r"(addr), "n"(OFF));
 }
 
 // The two A-fragment registers of one weight block for quad lane j. `aligned` says the
 // block's codes start on a 4-byte boundary (they start 2 bytes after the block does).
 // `blk` already includes the lane's 4*j.
-template <int DT>
-__device__ __forceinline__ void load_codes(uint32_t blk, bool aligned, uint32_t& r_lo, uint32_t& r_hi) {
+template <int DT, bool ALIGNED, int OFF>
+__device__ __forceinline__ void load_codes(uint32_t blk, uint32_t& r_lo, uint32_t& r_hi) {
   if (DT == AION_CUDA_DTYPE_Q4_0) {
     uint32_t v;
-    if (aligned) {
-      v = lds_u32(blk + 2);
-    } else {
-      v = __funnelshift_r(lds_u32(blk), lds_u32(blk + 4), 16);
-    }
+    if (ALIGNED) v = lds_u32<OFF + 2>(blk);
+    else v = __funnelshift_r(lds_u32<OFF>(blk), lds_u32<OFF + 4>(blk), 16);
     // nibble -> signed byte 16*(nibble-8): move it to the high half, flip its top bit.
     r_lo = ((v << 4) & 0xF0F0F0F0u) ^ 0x80808080u;
     r_hi = (v & 0xF0F0F0F0u) ^ 0x80808080u;
   } else {
-    if (aligned) {
-      r_lo = lds_u32(blk + 2);
-      r_hi = lds_u32(blk + 18);
+    if (ALIGNED) {
+      r_lo = lds_u32<OFF + 2>(blk);
+      r_hi = lds_u32<OFF + 18>(blk);
     } else {
-      r_lo = __funnelshift_r(lds_u32(blk), lds_u32(blk + 4), 16);
-      r_hi = __funnelshift_r(lds_u32(blk + 16), lds_u32(blk + 20), 16);
+      r_lo = __funnelshift_r(lds_u32<OFF>(blk), lds_u32<OFF + 4>(blk), 16);
+      r_hi = __funnelshift_r(lds_u32<OFF + 16>(blk), lds_u32<OFF + 20>(blk), 16);
     }
   }
 }
@@ -163,6 +148,45 @@ __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
   uint64_t r;
   asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
   return r;
+}
+
+// Everything one K block of a stage needs from shared memory, for one lane.
+template <int MT>
+struct BlockRegs {
+  uint32_t a0, a1, a2, a3;  // weight codes: rows g / g+8, low / high half of K
+  uint64_t ws;              // (scale of row g, scale of row g+8)
+  uint2 bq[MT];             // activation codes
+  uint64_t se[MT], so[MT];  // (s, s) of activation rows 2j and 2j+1
+};
+
+// K-major: rows g read an even column (codes 2 bytes past a word boundary), rows g+8 the
+// odd column after it (aligned). NT: both rows read block KBL of their weight row, whose
+// codes are aligned when KBL is odd.
+template <int DT, bool NT, int MT, int KBL, int STEP, int AQ_STRIDE, int AS_STRIDE>
+__device__ __forceinline__ void load_block(BlockRegs<MT>& r, uint32_t w0, uint32_t w1, uint32_t b0, uint32_t b1,
+                                           const uint32_t (&aq)[MT], const uint32_t (&as)[MT]) {
+  constexpr bool AL0 = NT ? (KBL & 1) != 0 : false;
+  constexpr bool AL1 = NT ? (KBL & 1) != 0 : true;
+  load_codes<DT, AL0, KBL * STEP>(w0, r.a0, r.a2);
+  load_codes<DT, AL1, KBL * STEP>(w1, r.a1, r.a3);
+  r.ws = pack2(lds_f16<KBL * STEP>(b0), lds_f16<KBL * STEP>(b1));
+#pragma unroll
+  for (int t = 0; t < MT; t++) {
+    r.bq[t] = lds_u64<KBL * AQ_STRIDE>(aq[t]);
+    lds_f32x4<KBL * AS_STRIDE>(as[t], r.se[t], r.so[t]);
+  }
+}
+
+template <int MT, bool M1>
+__device__ __forceinline__ void compute_block(const BlockRegs<MT>& r, uint64_t (&acc)[MT][2]) {
+#pragma unroll
+  for (int t = 0; t < MT; t++) {
+    int d[4];
+    ptx::mma_s8(d, r.a0, r.a1, r.a2, r.a3, r.bq[t].x, r.bq[t].y);
+    // d[0], d[2]: rows g, g+8 against activation row 2j; d[1], d[3]: against row 2j+1.
+    acc[t][0] = fma2(mul2(pack2((float)d[0], (float)d[2]), r.ws), r.se[t], acc[t][0]);
+    if (!M1) acc[t][1] = fma2(mul2(pack2((float)d[1], (float)d[3]), r.ws), r.so[t], acc[t][1]);
+  }
 }
 
 // CTA that owns unit u when G CTAs split U units as [c*U/G, (c+1)*U/G).
@@ -190,8 +214,8 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p,
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + G::OFF_BARS + 2 * NS * 8);
   const uint32_t kb_pad = p.stages_per_tile * KBT;  // K blocks rounded up to whole stages
   uint8_t* act_q = smem + G::OFF_ACT;
-  float* act_s = reinterpret_cast<float*>(act_q + (size_t)kb_pad * MP2 * 32);
-  GEMV_TRACE(0);
+  constexpr uint32_t QUADS = M1 ? 1 : 4 * MT;  // scale quads per K block
+  float* act_s = reinterpret_cast<float*>(act_q + (size_t)kb_pad * MP2 * 32);  // [kb][QUADS]
 
   if (warp == CONSUMER_WARPS) {
     // ---------------- producer: one tiled TMA load per stage ----------------
@@ -254,16 +278,14 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p,
   // nothing, whatever their code bytes hold (an integer dot is always finite).
   {
     float4* z = reinterpret_cast<float4*>(act_s);
-    const uint32_t quads = kb_pad * (MP2 / 2) + 1;  // + the block of zeros absent rows read
+    const uint32_t quads = kb_pad * QUADS;
     for (uint32_t i = tid; i < quads; i += CONSUMER_THREADS) z[i] = make_float4(0.f, 0.f, 0.f, 0.f);
   }
   __syncthreads();  // CTA barrier #1: the producer has initialised the mbarriers
   // The next kernel in the stream may begin: its weight stream does not depend on us.
   ptx::pdl_launch_dependents();
-  GEMV_TRACE(1);
   // Everything below reads what the previous kernel wrote (A, and C when beta != 0).
   ptx::pdl_wait();
-  GEMV_TRACE(2);
 
   {
     // Quantize all of A, one thread per 32-block (no cross-lane traffic, 32 independent
@@ -317,13 +339,11 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p,
       uint4* dst = reinterpret_cast<uint4*>(act_q + ((size_t)kb * MP2 + r) * 32);
       dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
       dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
-      float* sq = act_s + ((size_t)kb * (MP2 / 2) + (r >> 1)) * 4 + 2 * (r & 1);
+      float* sq = act_s + ((size_t)kb * QUADS + (r >> 1)) * 4 + 2 * (r & 1);
       *reinterpret_cast<float2*>(sq) = make_float2(scale * fold, scale * fold);
     }
   }
-  GEMV_TRACE(3);
   asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_THREADS) : "memory");
-  GEMV_TRACE(4);
 
   // Per-lane constants: where this lane's two weight blocks (rows g and g+8 of the
   // fragment) sit inside a stage, and where its activation fragments start. Lanes whose
@@ -338,18 +358,19 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p,
   }
   const int col0 = NT ? 16 * warp + g : 2 * warp + 8 * g;
   const int col1 = NT ? col0 + 8 : col0 + 1;
-  constexpr uint32_t AQ_STRIDE = MP2 * 32, AS_STRIDE = MP2 * 8;  // bytes per K block
+  // Bytes per K block: MP2 rows of codes; 4*MT scale quads (absent rows keep a zero
+  // scale, so whatever codes a lane of an absent row reads contribute nothing: such a
+  // lane simply reads an existing row).
+  // With a single activation row every lane reads the one scale quad: the outputs of the
+  // lanes that stand for absent rows are finite and never stored.
+  constexpr uint32_t AQ_STRIDE = MP2 * 32, AS_STRIDE = M1 ? 16 : MT * 64;
   const uint32_t act_q_addr = smem_base + G::OFF_ACT;
   const uint32_t act_s_addr = act_q_addr + kb_pad * AQ_STRIDE;
-  const uint32_t zero_addr = act_s_addr + kb_pad * AS_STRIDE;
-  uint32_t aq_lane[MT], as_lane[MT], aq_step[MT], as_step[MT];
+  uint32_t aq_lane[MT], as_lane[MT];
 #pragma unroll
   for (int t = 0; t < MT; t++) {
-    const bool row_ok = (t * 8 + g) < (int)MP2, pair_ok = (t * 8 + 2 * j) < (int)MP2;
-    aq_lane[t] = row_ok ? act_q_addr + (t * 8 + g) * 32 + 8 * j : zero_addr;
-    aq_step[t] = row_ok ? AQ_STRIDE : 0u;
-    as_lane[t] = pair_ok ? act_s_addr + (t * 4 + j) * 16 : zero_addr;
-    as_step[t] = pair_ok ? AS_STRIDE : 0u;
+    aq_lane[t] = act_q_addr + ((t * 8 + g) % MP2) * 32 + 8 * j;
+    as_lane[t] = act_s_addr + (M1 ? 0 : (t * 4 + j) * 16);
   }
 
   // acc[t][0] = (row g, row g+8) x activation row t*8+2j ; acc[t][1] = the same x row t*8+2j+1.
@@ -378,43 +399,35 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p,
       uint32_t aq[MT], as[MT];
 #pragma unroll
       for (int t = 0; t < MT; t++) {
-        aq[t] = aq_lane[t] + s * KBT * aq_step[t];
-        as[t] = as_lane[t] + s * KBT * as_step[t];
+        aq[t] = aq_lane[t] + s * (KBT * AQ_STRIDE);
+        as[t] = as_lane[t] + s * (KBT * AS_STRIDE);
       }
       // Ties every load below to this point: they cannot move above the wait.
       asm volatile("" : "+r"(w0), "+r"(w1), "+r"(b0), "+r"(b1)::"memory");
 #pragma unroll
-      for (int kbl = 0; kbl < KBT; kbl++) {
-        constexpr int STEP = NT ? Q8_BYTES : G::KM_PITCH;
-        const bool al0 = NT ? (kbl & 1) != 0 : false;
-        const bool al1 = NT ? (kbl & 1) != 0 : true;
-        uint32_t a0, a1, a2, a3;
-        load_codes<DT>(w0 + kbl * STEP, al0, a0, a2);
-        load_codes<DT>(w1 + kbl * STEP, al1, a1, a3);
-        const uint64_t ws = pack2(lds_f16(b0 + kbl * STEP), lds_f16(b1 + kbl * STEP));
-#pragma unroll
-        for (int t = 0; t < MT; t++) {
-          const uint2 bq = lds_u64(aq[t] + kbl * aq_step[t]);
-          uint64_t as_even, as_odd;  // (s, s) of activation rows 2j and 2j+1
-          lds_f32x4(as[t] + kbl * as_step[t], as_even, as_odd);
-          int d[4];
-#ifdef AION_GEMV_NOMMA
-          d[0] = a0 ^ bq.x; d[1] = a1 ^ bq.y; d[2] = a2 + bq.x; d[3] = a3 + bq.y;  // lab only: timing without the MMA
-#else
-          ptx::mma_s8(d, a0, a1, a2, a3, bq.x, bq.y);
-#endif
-          // d[0], d[2]: rows g, g+8 against activation row 2j; d[1], d[3]: against row 2j+1.
-          acc[t][0] = fma2(mul2(pack2((float)d[0], (float)d[2]), ws), as_even, acc[t][0]);
-          if (!M1) acc[t][1] = fma2(mul2(pack2((float)d[1], (float)d[3]), ws), as_odd, acc[t][1]);
-        }
-      }
+      for (int t = 0; t < MT; t++) asm volatile("" : "+r"(aq[t]), "+r"(as[t]));
+      constexpr int STEP = NT ? Q8_BYTES : G::KM_PITCH;
+      // Loads of four K blocks are issued before their arithmetic (and the next four
+      // before the first four finish), so shared-memory and MMA latencies overlap.
+      BlockRegs<MT> r[4];
+#define AION_LOAD(K, R) load_block<DT, NT, MT, K, STEP, (int)AQ_STRIDE, (int)AS_STRIDE>(r[R], w0, w1, b0, b1, aq, as)
+      AION_LOAD(0, 0); AION_LOAD(1, 1); AION_LOAD(2, 2); AION_LOAD(3, 3);
+      compute_block<MT, M1>(r[0], acc); AION_LOAD(4, 0);
+      compute_block<MT, M1>(r[1], acc); AION_LOAD(5, 1);
+      compute_block<MT, M1>(r[2], acc); AION_LOAD(6, 2);
+      compute_block<MT, M1>(r[3], acc); AION_LOAD(7, 3);
+      compute_block<MT, M1>(r[0], acc);
+      compute_block<MT, M1>(r[1], acc);
+      compute_block<MT, M1>(r[2], acc);
+      compute_block<MT, M1>(r[3], acc);
+#undef AION_LOAD
+      static_assert(KBT == 8, "eight K blocks per stage are spelled out above");
     }
     __syncwarp();
     if (lane == 0) ptx::mbar_arrive(bar_empty + 8 * slot);
 
     if (s == Sg - 1 || uu == u_end - 1) {
       // ---------------- this CTA's share of `tile` is complete ----------------
-      GEMV_TRACE(5);
       const uint64_t tile_u0 = (uint64_t)tile * Sg;
       const bool whole = (uu + 1 - tile_u0 == Sg) && (tile_u0 >= u_begin);
       const uint32_t n0 = tile * TN;
@@ -435,18 +448,20 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p,
           *reinterpret_cast<float2*>(mine + col0 * MPA + t * 8 + 2 * j) = make_float2(v[t][0], v[t][2]);
           *reinterpret_cast<float2*>(mine + col1 * MPA + t * 8 + 2 * j) = make_float2(v[t][1], v[t][3]);
         }
-        __threadfence();
+        // The warp's stores are ordered before lane 0's release by the warp barrier; the
+        // acquire side orders the last arriver's loads after every earlier release.
         __syncwarp();
         int last = 0;
         if (lane == 0) {
           int* tk = p.tickets + (size_t)tile * CONSUMER_WARPS + warp;
-          last = (atomicAdd(tk, 1) == (int)nparts - 1);
+          int prev;
+          asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(prev) : "l"(tk) : "memory");
+          last = (prev == (int)nparts - 1);
           if (last) *tk = 0;  // ready for the next launch
         }
         last = __shfl_sync(0xFFFFFFFFu, last, 0);
         if (last) {
           // The last part to arrive adds all of them in CTA order.
-          __threadfence();
 #pragma unroll
           for (int t = 0; t < MT; t++) v[t][0] = v[t][1] = v[t][2] = v[t][3] = 0.0f;
           for (uint32_t part = 0; part < nparts; part++) {
@@ -483,7 +498,6 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p,
       tile++;
     }
   }
-  GEMV_TRACE(6);
 }
 
 template <int DT, bool NT, int MT, bool M1>
@@ -491,7 +505,7 @@ int32_t launch(AionCudaDevice* dev, GemvParams p, const uint8_t* b, uint64_t ldb
   using G = Geom<DT, NT>;
   auto kernel = gemv_q_mma_kernel<DT, NT, MT, M1>;
   constexpr uint32_t MP2 = M1 ? 2 : 8 * MT;
-  const size_t smem = G::OFF_ACT + act_bytes(p.stages_per_tile * KBT, MP2);
+  const size_t smem = G::OFF_ACT + act_bytes(p.stages_per_tile * KBT, MP2, MT);
   // Kernel attributes and occupancy depend on the device and the dynamic size only.
   static size_t configured_smem[16] = {};
   static size_t occ_smem[16] = {};
@@ -511,12 +525,21 @@ int32_t launch(AionCudaDevice* dev, GemvParams p, const uint8_t* b, uint64_t ldb
   uint64_t grid = (uint64_t)occ_blocks[di] * dev->sm_count;
   if (dev->gemv_split_override) grid = (uint64_t)dev->gemv_split_override * dev->sm_count;  // CTAs per SM, tuning only
   if (grid > p.units) grid = p.units;
+  // Small problems: fewer, fuller CTAs (a CTA that owns a whole number of tiles needs no
+  // fix-up), but never fewer than one per SM.
+  if (!dev->gemv_split_override) {
+    const uint64_t sms = (uint64_t)dev->sm_count;
+    uint64_t want = p.units / 4;
+    if (want < sms) want = sms;
+    if (grid > want) grid = want;
+    if (grid > p.units) grid = p.units;
+  }
 
   // Scratch for tiles shared by several CTAs: two partial slots per CTA, one ticket per (tile, warp).
   constexpr int MPA = 8 * MT;
   if (int32_t st = dev->reserve_gemv_fixup((size_t)grid * 2 * TN * MPA * sizeof(float), (size_t)p.tiles * CONSUMER_WARPS)) return st;
-  p.partials = dev->gemv_partials;
-  p.tickets = dev->gemv_tickets;
+  p.partials = dev->lane_gemv_partials();
+  p.tickets = dev->lane_gemv_tickets();
 
   // The weight tensor as bytes in 8-byte elements.
   const CUtensorMap* tm = nullptr;
@@ -584,7 +607,7 @@ int32_t gemv_mma(AionCudaDevice* dev, const MatMulArgs& g, bool probe_only) {
   // K blocks whose quantized activations fit the per-CTA budget; a deeper K is issued as
   // several launches that accumulate into C, like the reference's walk over K in chunks
   // (src/aion/backend/cpu/exec/matmul.zig:431-434).
-  uint64_t kb_max = (ACT_BUDGET_BYTES / ((size_t)mp2 * 40)) / KBT * KBT;
+  uint64_t kb_max = (ACT_BUDGET_BYTES / ((size_t)mp2 * 32 + (g.m == 1 ? 16 : (g.m > 8 ? 128 : 64)))) / KBT * KBT;
   if (kb_max < KBT) kb_max = KBT;
 
   for (uint64_t kb0 = 0; kb0 < kblocks; kb0 += kb_max) {
@@ -605,9 +628,6 @@ int32_t gemv_mma(AionCudaDevice* dev, const MatMulArgs& g, bool probe_only) {
     p.units = (uint64_t)p.tiles * p.stages_per_tile;
     p.fault = dev->fault_dev;
     p.a_vec4 = ((reinterpret_cast<uintptr_t>(p.a) & 15) == 0 && g.lda % 4 == 0) ? 1u : 0u;
-#ifdef AION_GEMV_TRACE
-    p.trace = g_gemv_trace;
-#endif
     int32_t st;
     if (g.nt) {
       st = launch_m<AION_CUDA_DTYPE_Q8_0, true>(dev, p, g.b + kb0 * Q8_BYTES, g.ldb);

@@ -112,8 +112,8 @@ int32_t matmul_generic(AionCudaDevice* dev, const MatMulArgs& g) {
   const size_t aq_bytes = (g.m * g.k + 255) & ~size_t(255);
   const size_t as_bytes = g.m * kblocks * sizeof(float);
   if (int32_t st = dev->reserve_scratch(aq_bytes + as_bytes)) return st;
-  int8_t* aq = static_cast<int8_t*>(dev->scratch);
-  float* ascale = reinterpret_cast<float*>(static_cast<uint8_t*>(dev->scratch) + aq_bytes);
+  int8_t* aq = static_cast<int8_t*>(dev->lane_scratch());
+  float* ascale = reinterpret_cast<float*>(static_cast<uint8_t*>(dev->lane_scratch()) + aq_bytes);
   if (int32_t st = quantize_activation_rows(dev, g.a, g.m, g.k, g.lda, aq, ascale)) return st;
 
   BlockAddr ad{};

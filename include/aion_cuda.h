@@ -115,6 +115,15 @@ AION_CUDA_API int32_t aion_cuda_sync(AionCudaDevice* dev);
  * Steps that would allocate scratch must have run once before recording. */
 typedef struct AionCudaProgram AionCudaProgram;
 AION_CUDA_API int32_t aion_cuda_record_begin(AionCudaDevice* dev);
+/* While recording, steps that do not depend on one another may be issued into different
+ * lanes (0..7; lane 0 is the default): lanes become parallel branches of the recorded
+ * program and their kernels may overlap on the device. A lane starts after everything
+ * recorded on lane 0 before its first use; aion_cuda_record_join orders everything
+ * recorded so far before what follows (record_end joins too). The caller owns the
+ * dependency analysis, as the reference's compiler owns step order
+ * (aion src/aion/graph/program/compiler.zig:1052-1153). Each lane has its own kernel scratch. */
+AION_CUDA_API int32_t aion_cuda_record_lane(AionCudaDevice* dev, uint32_t lane);
+AION_CUDA_API int32_t aion_cuda_record_join(AionCudaDevice* dev);
 AION_CUDA_API int32_t aion_cuda_record_end(AionCudaDevice* dev, AionCudaProgram** out);
 AION_CUDA_API int32_t aion_cuda_program_launch(AionCudaDevice* dev, AionCudaProgram* prog);
 AION_CUDA_API void aion_cuda_program_destroy(AionCudaDevice* dev, AionCudaProgram* prog);

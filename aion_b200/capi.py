@@ -99,6 +99,7 @@ SIGNATURES = {
     "aion_cuda_d2d": (C.c_int32, [_DEV, C.c_uint64, C.c_size_t, C.c_uint64, C.c_size_t, C.c_size_t]),
     "aion_cuda_memset": (C.c_int32, [_DEV, C.c_uint64, C.c_size_t, C.c_int32, C.c_size_t]),
     "aion_cuda_matmul": (C.c_int32, [_DEV, C.POINTER(MatMul)]),
+    "aion_cuda_matmul_static_scratch": (C.c_int32, [_DEV, C.POINTER(MatMul)]),
     "aion_cuda_matmul_nt": (C.c_int32, [_DEV, C.POINTER(MatMulNT)]),
     "aion_cuda_attention": (C.c_int32, [_DEV, C.POINTER(Attention)]),
     "aion_cuda_quantize": (C.c_int32, [_DEV, C.c_uint32, _OPP, C.POINTER(C.c_uint64), C.c_uint32, C.c_uint32, _OPP]),

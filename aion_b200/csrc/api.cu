@@ -80,6 +80,38 @@ int32_t aion_cuda_matmul(AionCudaDevice* dev, const AionCudaMatMul* s) {
   return route(dev, g, s->flags, "matmul");
 }
 
+// The `MatMul` step for a caller that cannot allocate: same arguments and results as
+// aion_cuda_matmul for decode-sized m, with the kernel's scratch taken from an array
+// built into the library. See the header for who needs it and its limits.
+int32_t aion_cuda_matmul_static_scratch(AionCudaDevice* dev, const AionCudaMatMul* s) {
+  if (!dev || !s) return fail(AION_CUDA_INVALID_ARGUMENT, "matmul_static_scratch: null argument");
+  if (s->b_dtype != AION_CUDA_DTYPE_Q8_0 && s->b_dtype != AION_CUDA_DTYPE_Q4_0)
+    return fail(AION_CUDA_UNSUPPORTED, "matmul_static_scratch: B must be q8_0 or q4_0");
+  if (s->k % QK != 0) return fail(AION_CUDA_INVALID_ARGUMENT, "matmul_static_scratch: k = %llu is not a multiple of 32", (unsigned long long)s->k);
+  if (s->m == 0 || s->n == 0) return AION_CUDA_OK;
+  MatMulArgs g{};
+  g.dtype = s->b_dtype;
+  g.nt = false;
+  g.order = AION_CUDA_ORDER_ROW_MAJOR;
+  g.m = s->m;
+  g.n = s->n;
+  g.k = s->k;
+  g.lda = s->lda ? s->lda : s->k;
+  g.ldb = s->ldb ? s->ldb : s->n;
+  g.ldc = s->ldc ? s->ldc : s->n;
+  g.alpha = s->alpha;
+  g.beta = s->beta;
+  if (g.lda < g.k || g.ldb < g.n || g.ldc < g.n) return fail(AION_CUDA_INVALID_ARGUMENT, "matmul_static_scratch: a leading dimension is shorter than its row");
+  if (g.k == 0) return fail(AION_CUDA_UNSUPPORTED, "matmul_static_scratch: k = 0");
+  if (int32_t st = resolve(s->a, ((g.m - 1) * g.lda + g.k) * sizeof(float), "matmul_static_scratch.a", &g.a)) return st;
+  if (int32_t st = resolve(s->c, ((g.m - 1) * g.ldc + g.n) * sizeof(float), "matmul_static_scratch.c", &g.c)) return st;
+  if (int32_t st = resolve(s->b, kmajor_bytes(g.k / QK, g.ldb, g.n, block_bytes_of(g.dtype)), "matmul_static_scratch.b", &g.b)) return st;
+  if ((reinterpret_cast<uintptr_t>(g.a) & 3) || (reinterpret_cast<uintptr_t>(g.c) & 3))
+    return fail(AION_CUDA_INVALID_ARGUMENT, "matmul_static_scratch: A and C must be 4-byte aligned");
+  if (int32_t st = dev->make_current()) return st;
+  return gemv_mma_static_scratch(dev, g);
+}
+
 int32_t aion_cuda_matmul_nt(AionCudaDevice* dev, const AionCudaMatMulNT* s) {
   if (!dev || !s) return fail(AION_CUDA_INVALID_ARGUMENT, "matmul_nt: null argument");
   if (s->b_dtype == AION_CUDA_DTYPE_F32)

@@ -123,6 +123,11 @@ inline int32_t resolve(const AionCudaOperand& op, size_t need, const char* name,
 int32_t tensor_map_bytes(AionCudaDevice* dev, const void* base, uint32_t rank, const uint64_t* dims, const uint64_t* strides,
                          const uint32_t* box, const CUtensorMap** out);
 
+// The same descriptor written into caller storage, with no cache and no allocation of
+// any kind (for the entry point that must not allocate).
+int32_t tensor_map_encode(const void* base, uint32_t rank, const uint64_t* dims, const uint64_t* strides, const uint32_t* box,
+                          CUtensorMap* out);
+
 // ---- step implementations, one per kernel file ------------------------------------
 int32_t quantize_activation_rows(AionCudaDevice* dev, const float* a, uint64_t m, uint64_t k, uint64_t lda,
                                  int8_t* aq, float* ascale);
@@ -142,6 +147,7 @@ int32_t matmul_generic(AionCudaDevice* dev, const MatMulArgs& g);
 // alignment is outside what the tiled kernel reads; the caller then routes elsewhere.
 int32_t gemv_mma(AionCudaDevice* dev, const MatMulArgs& g, bool probe_only);
 int32_t gemm_tcgen05(AionCudaDevice* dev, const MatMulArgs& g, bool probe_only);
+int32_t gemv_mma_static_scratch(AionCudaDevice* dev, const MatMulArgs& g);
 int32_t attention_launch(AionCudaDevice* dev, const AionCudaAttention* s);
 
 }  // namespace aion

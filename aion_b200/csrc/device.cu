@@ -114,6 +114,38 @@ int32_t tensor_map_bytes(AionCudaDevice* dev, const void* base, uint32_t rank, c
   return AION_CUDA_OK;
 }
 
+int32_t tensor_map_encode(const void* base, uint32_t rank, const uint64_t* dims, const uint64_t* strides, const uint32_t* box,
+                          CUtensorMap* out) {
+  typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                    const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeTiledFn encode = nullptr;
+  if (!encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    AION_CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+    if (!fn || qres != cudaDriverEntryPointSuccess) return fail(AION_CUDA_INTERNAL_ERROR, "cuTensorMapEncodeTiled is not available from this driver");
+    encode = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  if (rank < 2 || rank > 3 || (dims[0] & 7) || (box[0] & 15) || box[0] / 8 > 256 || ((uintptr_t)base & 15))
+    return fail(AION_CUDA_INTERNAL_ERROR, "tensor map: view geometry is not TMA-addressable");
+  cuuint64_t gdim[3] = {dims[0] / 8, 1, 1};
+  cuuint64_t gstride[2] = {0, 0};
+  cuuint32_t bx[3] = {box[0] / 8, 1, 1};
+  const cuuint32_t estride[3] = {1, 1, 1};
+  for (uint32_t i = 1; i < rank; i++) {
+    gdim[i] = dims[i];
+    bx[i] = box[i];
+    gstride[i - 1] = strides[i - 1];
+    if ((strides[i - 1] & 15) || box[i] > 256) return fail(AION_CUDA_INTERNAL_ERROR, "tensor map: view geometry is not TMA-addressable");
+  }
+  const CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT64, rank, const_cast<void*>(base), gdim, gstride, bx, estride,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(AION_CUDA_INTERNAL_ERROR, "cuTensorMapEncodeTiled failed with %d", (int)r);
+  return AION_CUDA_OK;
+}
+
 }  // namespace aion
 
 using namespace aion;

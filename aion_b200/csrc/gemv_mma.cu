@@ -643,4 +643,121 @@ int32_t gemv_mma(AionCudaDevice* dev, const MatMulArgs& g, bool probe_only) {
   return AION_CUDA_OK;
 }
 
+// ------------------------------------------------------------------------------------
+// The same GEMV for callers that must not allocate (see aion_cuda_matmul_static_scratch
+// in the header). The split-tile partial sums and their arrival counters live in this
+// file-scope array instead of in memory the device object grows on demand. Every GPU that
+// loads the library holds the array until the process exits.
+// ------------------------------------------------------------------------------------
+namespace {
+
+constexpr uint32_t STATIC_MAX_CTAS = 512;    // grid is clamped to this
+constexpr uint32_t STATIC_MAX_TILES = 8192;  // n <= 524288
+constexpr size_t STATIC_PARTIAL_BYTES = (size_t)STATIC_MAX_CTAS * 2 * TN * 8 * sizeof(float);  // m <= 8
+constexpr size_t STATIC_TICKET_BYTES = (size_t)STATIC_MAX_TILES * CONSUMER_WARPS * sizeof(int);
+
+static __device__ __align__(256) unsigned char g_static_scratch[STATIC_PARTIAL_BYTES + STATIC_TICKET_BYTES];
+
+// In host code `g_static_scratch` is only a stand-in for the symbol, not a device
+// address: each device's address is looked up once, with that device current.
+unsigned char* g_static_scratch_addr[16] = {};
+
+template <int DT, bool NT, bool M1>
+int32_t launch_static(AionCudaDevice* dev, GemvParams p, const uint8_t* b, uint64_t ldb, unsigned char* scratch) {
+  using G = Geom<DT, NT>;
+  auto kernel = gemv_q_mma_kernel<DT, NT, 1, M1>;
+  constexpr uint32_t MP2 = M1 ? 2 : 8;
+  const size_t smem = G::OFF_ACT + act_bytes(p.stages_per_tile * KBT, MP2, 1);
+  AION_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  int nb = 0;
+  AION_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, kernel, THREADS, smem));
+  if (nb < 1) return fail(AION_CUDA_INTERNAL_ERROR, "gemv: kernel does not fit an SM with %llu bytes of shared memory", (unsigned long long)smem);
+  uint64_t grid = (uint64_t)nb * dev->sm_count;
+  if (grid > p.units) grid = p.units;
+  if (grid > STATIC_MAX_CTAS) grid = STATIC_MAX_CTAS;
+  p.partials = reinterpret_cast<float*>(scratch);
+  p.tickets = reinterpret_cast<int*>(scratch + STATIC_PARTIAL_BYTES);
+  // The counters must start at zero whatever an earlier call left behind.
+  AION_CUDA_TRY(cudaMemsetAsync(p.tickets, 0, (size_t)p.tiles * CONSUMER_WARPS * sizeof(int), dev->stream));
+
+  CUtensorMap tm;
+  if (!NT && DT == AION_CUDA_DTYPE_Q4_0) {
+    const uint64_t dims[2] = {(uint64_t)p.n * G::BB, p.kblocks};
+    const uint64_t strides[1] = {ldb * G::BB};
+    const uint32_t box[2] = {(uint32_t)TN * G::BB, KBT};
+    if (int32_t st = tensor_map_encode(b, 2, dims, strides, box, &tm)) return st;
+  } else if (!NT) {
+    const uint64_t dims[3] = {8ull * G::BB, p.n / 8, p.kblocks};
+    const uint64_t strides[2] = {8ull * G::BB, ldb * G::BB};
+    const uint32_t box[3] = {8u * G::BB, TN / 8, KBT};
+    if (int32_t st = tensor_map_encode(b, 3, dims, strides, box, &tm)) return st;
+  } else {
+    const uint64_t dims[2] = {(uint64_t)p.kblocks * Q8_BYTES, p.n};
+    const uint64_t strides[1] = {ldb * Q8_BYTES};
+    const uint32_t box[2] = {NT_ROW_PITCH, TN};
+    if (int32_t st = tensor_map_encode(b, 2, dims, strides, box, &tm)) return st;
+  }
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = dev->stream;
+  AION_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, p, tm));
+  return AION_CUDA_OK;
+}
+
+}  // namespace
+
+int32_t gemv_mma_static_scratch(AionCudaDevice* dev, const MatMulArgs& g) {
+  if (g.m == 0 || g.n == 0) return AION_CUDA_OK;
+  if (g.m > 8)
+    return fail(AION_CUDA_UNSUPPORTED, "matmul_static_scratch: m = %llu, the built-in scratch holds at most 8 rows", (unsigned long long)g.m);
+  if (g.k == 0 || g.k / QK > 0x7FFFFFFFull || g.n > (uint64_t)STATIC_MAX_TILES * TN)
+    return fail(AION_CUDA_UNSUPPORTED, "matmul_static_scratch: n = %llu, k = %llu are outside the built-in scratch (n <= %u, k >= 32)",
+                (unsigned long long)g.n, (unsigned long long)g.k, STATIC_MAX_TILES * TN);
+  const uint64_t kblocks = g.k / QK;
+  bool readable = (reinterpret_cast<uintptr_t>(g.b) & 15) == 0;
+  if (!g.nt) readable = readable && g.n % 8 == 0 && g.ldb % 8 == 0;
+  else readable = readable && g.dtype == AION_CUDA_DTYPE_Q8_0 && g.order == AION_CUDA_ORDER_ROW_MAJOR && kblocks % 8 == 0;
+  if (!readable) return fail(AION_CUDA_UNSUPPORTED, "matmul_static_scratch: the tiled GEMV does not read this shape or alignment");
+  const uint32_t mp2 = g.m == 1 ? 2u : 8u;
+  const uint64_t kb_max = (ACT_BUDGET_BYTES / ((size_t)mp2 * 32 + (g.m == 1 ? 16 : 64))) / KBT * KBT;
+  if (kblocks > kb_max)
+    return fail(AION_CUDA_UNSUPPORTED, "matmul_static_scratch: k = %llu with m = %llu exceeds one launch (k <= %llu)",
+                (unsigned long long)g.k, (unsigned long long)g.m, (unsigned long long)(kb_max * QK));
+
+  // First call on this device: find where the array lives on it.
+  const int di = dev->ordinal & 15;
+  if (!g_static_scratch_addr[di]) {
+    unsigned char* ptr = nullptr;
+    AION_CUDA_TRY(cudaGetSymbolAddress((void**)&ptr, g_static_scratch));
+    g_static_scratch_addr[di] = ptr;
+  }
+
+  GemvParams p{};
+  p.a = g.a;
+  p.c = g.c;
+  p.m = (uint32_t)g.m;
+  p.n = (uint32_t)g.n;
+  p.kblocks = (uint32_t)kblocks;
+  p.mp2 = mp2;
+  p.lda = g.lda;
+  p.ldc = g.ldc;
+  p.alpha = g.alpha;
+  p.beta = g.beta;
+  p.tiles = (uint32_t)((g.n + TN - 1) / TN);
+  p.stages_per_tile = (uint32_t)((kblocks + KBT - 1) / KBT);
+  p.units = (uint64_t)p.tiles * p.stages_per_tile;
+  p.fault = dev->fault_dev;
+  p.a_vec4 = ((reinterpret_cast<uintptr_t>(p.a) & 15) == 0 && g.lda % 4 == 0) ? 1u : 0u;
+  unsigned char* scratch = g_static_scratch_addr[di];
+  if (g.nt) return g.m == 1 ? launch_static<AION_CUDA_DTYPE_Q8_0, true, true>(dev, p, g.b, g.ldb, scratch)
+                            : launch_static<AION_CUDA_DTYPE_Q8_0, true, false>(dev, p, g.b, g.ldb, scratch);
+  if (g.dtype == AION_CUDA_DTYPE_Q8_0)
+    return g.m == 1 ? launch_static<AION_CUDA_DTYPE_Q8_0, false, true>(dev, p, g.b, g.ldb, scratch)
+                    : launch_static<AION_CUDA_DTYPE_Q8_0, false, false>(dev, p, g.b, g.ldb, scratch);
+  return g.m == 1 ? launch_static<AION_CUDA_DTYPE_Q4_0, false, true>(dev, p, g.b, g.ldb, scratch)
+                  : launch_static<AION_CUDA_DTYPE_Q4_0, false, false>(dev, p, g.b, g.ldb, scratch);
+}
+
 }  // namespace aion

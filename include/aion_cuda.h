@@ -182,6 +182,29 @@ typedef struct AionCudaMatMul {
 
 AION_CUDA_API int32_t aion_cuda_matmul(AionCudaDevice* dev, const AionCudaMatMul* step);
 
+/* No counterpart in the reference. The decode `MatMul` step (m <= 8, K-major q8_0 /
+ * q4_0 B) for callers that are not allowed to allocate device memory: code running
+ * inside someone else's memory pool or allocator callback, inside a region where the
+ * CUDA context's allocator must not be entered (a stream capture owned by the caller,
+ * a real-time audio or control loop that pre-allocates everything), or in a process
+ * whose device memory budget is fixed up front. aion_cuda_matmul grows the device's
+ * scratch with cudaMalloc the first time a shape needs it; this entry point never calls
+ * cudaMalloc, cudaFree or any allocating routine, on the host or on the device. The
+ * kernel's scratch (split-tile partial sums and their arrival counters) is a 2.1 MB
+ * array compiled into the library; every GPU that loads the library holds it until the
+ * process exits.
+ *  - Same arguments, arithmetic and results as aion_cuda_matmul (bitwise when both pick
+ *    the same grid; within f32 rounding otherwise).
+ *  - Limits: m <= 8; n <= 524288; n and ldb multiples of 8; B 16-byte aligned; k small
+ *    enough for one launch (k <= 16384 at m = 1, k <= 4096 at m = 2..8). Anything beyond
+ *    returns UNSUPPORTED with a message naming the limit.
+ *  - The first call on a device looks up where the array lives on that device
+ *    (cudaGetSymbolAddress); make that first call before beginning any stream capture.
+ *  - All calls share the one array: two calls whose kernels overlap on the GPU (different
+ *    streams, parallel recording lanes, several host threads) race on it. Issue them on
+ *    one stream, one at a time. The arrival counters are cleared by every call. */
+AION_CUDA_API int32_t aion_cuda_matmul_static_scratch(AionCudaDevice* dev, const AionCudaMatMul* step);
+
 /* ---------------------------------------------------------------------------------
  * `MatMulNT` step: C[m,n] = alpha * sum_k A[m,k] * B[n,k] + beta * C.
  * `StepMatMulNT` (aion src/aion/runtime/executable.zig:217-223) executed by

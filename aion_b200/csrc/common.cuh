@@ -128,6 +128,10 @@ int32_t tensor_map_bytes(AionCudaDevice* dev, const void* base, uint32_t rank, c
 int32_t tensor_map_encode(const void* base, uint32_t rank, const uint64_t* dims, const uint64_t* strides, const uint32_t* box,
                           CUtensorMap* out);
 
+// Row-major bf16 [rows, cols] view with a 128-byte swizzled box (tensor-core operand tiles).
+int32_t tensor_map_bf16_sw128(const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_bytes, uint32_t box_cols,
+                              uint32_t box_rows, CUtensorMap* out);
+
 // ---- step implementations, one per kernel file ------------------------------------
 int32_t quantize_activation_rows(AionCudaDevice* dev, const float* a, uint64_t m, uint64_t k, uint64_t lda,
                                  int8_t* aq, float* ascale);

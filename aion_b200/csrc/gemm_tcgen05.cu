@@ -1,6 +1,471 @@
-// Prefill GEMM placeholder: reports "not readable by this kernel" so callers route to
-// the any-shape path until the tensor-core kernel lands.
+// Prefill GEMM for q4_0 / q8_0 K-major weights on the 5th-generation tensor cores:
+// C[m,n] = alpha * A[m,k] . dequant(B)[k,n] + beta * C for m beyond the decode GEMV.
+//
+// This is the one dense contraction of the hot path, so unlike the GEMV it is tensor-pipe
+// bound. Arithmetic: A is rounded to bf16, B is dequantized to bf16 (w = (code) * scale),
+// products accumulate in f32 in tensor memory; against the reference's int8-activation
+// CPU arithmetic (src/aion/backend/cpu/kernels/matmul_q_i8.zig:385-497) that is a
+// different rounding of the same product, bounded by rel-L2 1e-2.
+//
+// Shape of the kernel (one persistent CTA per SM, 128 x 256 output tiles, K in steps of 64):
+//   warp 0      TMA producer: the bf16 activation tile (128B-swizzled, straight into the
+//               MMA operand layout) and the packed weight blocks of the stage, untouched.
+//   warps 2-5   dequantizers: packed blocks -> bf16 -> the 128B-swizzled K-major operand
+//               layout in shared memory (one generic-proxy pass; the packed bytes cannot be
+//               fed to the tensor core as they are), then a proxy fence and an arrive.
+//   warp 1      MMA issuer: one elected lane issues tcgen05.mma (M=128 tokens, N=256
+//               columns, K=16) four times per stage into one of two TMEM accumulators and
+//               commits to the stage's "empty" barrier; it also owns TMEM alloc / dealloc.
+//   warps 6-9   epilogue: tcgen05.ld the finished accumulator, alpha / beta in f32, store.
+// The activation is converted to bf16 once by a pre-pass (so every column tile re-reads
+// 2 bytes per element from L2 instead of converting 4), with the order of K inside each
+// group of 8 permuted for q4 to match the order in which a 32-bit word of nibbles
+// unpacks; a permutation of K applied to both operands does not change the product.
+// Every mbarrier wait is bounded; on expiry the kernel records a fault, stops issuing and
+// still frees its tensor memory.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <algorithm>
+
 #include "common.cuh"
+#include "ptx.cuh"
+#include "quant_device.cuh"
+
 namespace aion {
-int32_t gemm_tcgen05(AionCudaDevice*, const MatMulArgs&, bool) { return AION_CUDA_UNSUPPORTED; }
+
+namespace {
+
+constexpr int BM = 128;      // tokens per tile (UMMA M)
+constexpr int BN = 256;      // output columns per tile (UMMA N)
+constexpr int BK = 64;       // K per stage: one 128-byte swizzle row of bf16
+constexpr int UMMA_K = 16;
+constexpr int STAGES = 3;
+constexpr int KB_PER_STAGE = BK / QK;  // 2 quantized blocks of each column per stage
+constexpr int THREADS = 320;
+constexpr int DEQ_THREADS = 128;
+constexpr int A_TILE_BYTES = BM * BK * 2;   // 16 KB
+constexpr int B_TILE_BYTES = BN * BK * 2;   // 32 KB
+constexpr uint32_t TMEM_COLS = 512;         // two f32 accumulators of 256 columns
+
+struct GemmParams {
+  float* c;
+  uint32_t m, n, k;
+  uint64_t ldc;
+  float alpha, beta;
+  uint32_t m_tiles, n_tiles, k_stages;
+  int* fault;
+};
+
+template <int DT>
+struct GemmGeom {
+  static constexpr int BB = (DT == AION_CUDA_DTYPE_Q8_0) ? Q8_BYTES : Q4_BYTES;
+  static constexpr int PACKED_ROW = BN * BB;                       // one block row of the tile
+  static constexpr int PACKED_BYTES = KB_PER_STAGE * PACKED_ROW;   // 9216 (q4) / 17408 (q8)
+  static constexpr int PACKED_PAD = (PACKED_BYTES + 16 + 1023) / 1024 * 1024;  // +16: the unpacker reads one word past
+  static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES + PACKED_PAD;
+  static constexpr int OFF_A = 0;
+  static constexpr int OFF_B = A_TILE_BYTES;
+  static constexpr int OFF_PACKED = A_TILE_BYTES + B_TILE_BYTES;
+  static constexpr int OFF_BARS = STAGES * STAGE_BYTES;
+  static constexpr int SMEM_BYTES = OFF_BARS + 256 + 1024;  // + slack to align the base to 1024
+};
+
+// ---- f32 -> bf16 pre-pass ------------------------------------------------------------
+// Row-major [m, k] bf16 with k a multiple of 32. `permute`: inside every group of 8
+// consecutive k, position p holds element (p >> 1) + 4 * (p & 1), i.e. the order
+// e0 e4 e1 e5 e2 e6 e3 e7 in which a word of q4 nibbles unpacks two at a time.
+__global__ void convert_a_bf16_kernel(const float* __restrict__ a, uint64_t lda, __nv_bfloat16* __restrict__ out, uint32_t m,
+                                      uint32_t k, int permute) {
+  const uint64_t groups = (uint64_t)m * (k / 8);
+  for (uint64_t gi = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; gi < groups; gi += (uint64_t)gridDim.x * blockDim.x) {
+    const uint32_t r = (uint32_t)(gi / (k / 8)), g8 = (uint32_t)(gi % (k / 8));
+    const float* src = a + (uint64_t)r * lda + (uint64_t)g8 * 8;
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) v[i] = src[i];
+    __nv_bfloat162 o[4];
+    if (permute) {
+#pragma unroll
+      for (int i = 0; i < 4; i++) o[i] = __floats2bfloat162_rn(v[i], v[i + 4]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; i++) o[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    }
+    *reinterpret_cast<uint4*>(out + (uint64_t)r * k + (uint64_t)g8 * 8) = *reinterpret_cast<const uint4*>(o);
+  }
+}
+
+// ---- tcgen05 / TMEM wrappers ---------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// D[tmem] (+)= A[smem desc] . B[smem desc]^T, bf16 x bf16 -> f32, issued by one thread.
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// The mbarrier receives one arrival when every MMA issued so far by this thread is done.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory operand descriptor: K-major, 128-byte swizzle, rows of 128 bytes, groups of
+// 8 rows 1024 bytes apart. (Start address and offsets are in 16-byte units; bit 46 is the
+// descriptor version of this architecture; layout type 2 = 128-byte swizzle.)
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
+  return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+         ((uint64_t)2 << 61);
+}
+// Instruction descriptor: D f32, A and B bf16, both K-major, M = 128, N = 256.
+constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+// Byte offset of 16-byte chunk `c` (0..7) of row `r` inside a 128-byte-swizzled tile.
+__device__ __forceinline__ uint32_t sw128_offset(uint32_t r, uint32_t c) { return (r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4); }
+
+__device__ __forceinline__ uint32_t bf16x2_fma(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t d;
+  asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+__device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// Barrier block at the end of shared memory.
+struct Bars {
+  uint64_t full[STAGES];     // TMA landed the activation tile and the packed blocks
+  uint64_t bready[STAGES];   // the dequantized weight tile of the stage is written
+  uint64_t empty[STAGES];    // the MMAs that read the stage are done
+  uint64_t acc_full[2];      // an accumulator holds a finished tile
+  uint64_t acc_empty[2];     // the epilogue has drained it
+  uint32_t tmem_base;
+  uint32_t abort;
+};
+
+// Bounded wait that also gives up as soon as another role has aborted.
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
+  const uint32_t b = ptx::smem_u32(bar);
+  for (uint32_t i = 0; i < (1u << 18); i++) {
+    if (ptx::mbar_try_wait(b, parity)) return true;
+    if (*abort_flag) return false;
+  }
+  return false;
+}
+__device__ __noinline__ void raise_abort(int* fault, volatile uint32_t* abort_flag) {
+  *abort_flag = 1;
+  atomicCAS(fault, FAULT_NONE, FAULT_WAIT_EXPIRED);
+}
+
+// One q4_0 block (scale + 16 code bytes at a 2-byte aligned shared address) -> 32 bf16
+// weights, written as four 16-byte chunks of operand row `row`, chunks c0..c0+3. Word i of
+// the codes holds elements 8i..8i+7, one per nibble; they leave in the order
+// e0 e4 e1 e5 e2 e6 e3 e7 (the activation pre-pass applies the same order).
+__device__ __forceinline__ void dequant_q4_block(uint32_t blk, uint8_t* btile, uint32_t row, uint32_t c0) {
+  const float s = f16_bits_to_float((uint16_t)ptx::lds16(blk));
+  const uint32_t s2 = pack_bf16x2(s, s);
+  const uint32_t cb = blk + 2, al = cb & ~3u, sh = (cb & 3u) * 8;
+  uint32_t l[5];
+#pragma unroll
+  for (int i = 0; i < 5; i++) l[i] = ptx::lds32(al + 4 * i);
+  constexpr uint32_t MAGIC = 0x43004300u;   // bf16 128.0 twice: OR-ing a nibble gives 128 + nibble exactly
+  constexpr uint32_t ONE = 0x3F803F80u;     // 1.0
+  constexpr uint32_t NEG136 = 0xC308C308u;  // -(128 + 8)
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const uint32_t w = __funnelshift_r(l[i], l[i + 1], sh);
+    uint4 out;
+    out.x = bf16x2_mul(bf16x2_fma((w & 0x000F000Fu) | MAGIC, ONE, NEG136), s2);
+    out.y = bf16x2_mul(bf16x2_fma(((w >> 4) & 0x000F000Fu) | MAGIC, ONE, NEG136), s2);
+    out.z = bf16x2_mul(bf16x2_fma(((w >> 8) & 0x000F000Fu) | MAGIC, ONE, NEG136), s2);
+    out.w = bf16x2_mul(bf16x2_fma(((w >> 12) & 0x000F000Fu) | MAGIC, ONE, NEG136), s2);
+    *reinterpret_cast<uint4*>(btile + sw128_offset(row, c0 + i)) = out;
+  }
+}
+
+// One q8_0 block -> 32 bf16 weights in natural K order. A byte b becomes the f16 value
+// 1024 + (b ^ 0x80) by byte permutation, 1152 is subtracted exactly, the scale is applied
+// in f32 and the product rounded once to bf16.
+__device__ __forceinline__ void dequant_q8_block(uint32_t blk, uint8_t* btile, uint32_t row, uint32_t c0) {
+  const float s = f16_bits_to_float((uint16_t)ptx::lds16(blk));
+  const uint32_t cb = blk + 2, al = cb & ~3u, sh = (cb & 3u) * 8;
+  uint32_t l[9];
+#pragma unroll
+  for (int i = 0; i < 9; i++) l[i] = ptx::lds32(al + 4 * i);
+  const __half2 bias = __float2half2_rn(1152.0f);
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    uint32_t o[4];
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+      const uint32_t u = __funnelshift_r(l[2 * i + h], l[2 * i + h + 1], sh) ^ 0x80808080u;
+      const uint32_t h01 = __byte_perm(u, 0x64646464u, 0x5140);
+      const uint32_t h23 = __byte_perm(u, 0x64646464u, 0x7362);
+      const __half2 y01 = __hsub2(*reinterpret_cast<const __half2*>(&h01), bias);
+      const __half2 y23 = __hsub2(*reinterpret_cast<const __half2*>(&h23), bias);
+      o[2 * h] = pack_bf16x2(__low2float(y01) * s, __high2float(y01) * s);
+      o[2 * h + 1] = pack_bf16x2(__low2float(y23) * s, __high2float(y23) * s);
+    }
+    *reinterpret_cast<uint4*>(btile + sw128_offset(row, c0 + i)) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+template <int DT>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_q_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b) {
+  using G = GemmGeom<DT>;
+  extern __shared__ uint8_t smem_raw[];
+  // Swizzled operand tiles need 1024-byte alignment.
+  const uint32_t raw = ptx::smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* sm = smem_raw + (base - raw);
+  Bars* bars = reinterpret_cast<Bars*>(sm + G::OFF_BARS);
+  volatile uint32_t* abort_flag = &bars->abort;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) {
+      ptx::mbar_init(ptx::smem_u32(&bars->full[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&bars->bready[s]), DEQ_THREADS / 32);
+      ptx::mbar_init(ptx::smem_u32(&bars->empty[s]), 1);
+    }
+    for (int a = 0; a < 2; a++) {
+      ptx::mbar_init(ptx::smem_u32(&bars->acc_full[a]), 1);
+      ptx::mbar_init(ptx::smem_u32(&bars->acc_empty[a]), 4);
+    }
+    bars->abort = 0;
+    ptx::fence_barrier_init();
+    ptx::prefetch_tensormap(&tmap_a);
+    ptx::prefetch_tensormap(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(ptx::smem_u32(&bars->tmem_base), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = bars->tmem_base;
+  const uint32_t tiles = p.m_tiles * p.n_tiles;
+
+  if (warp == 0) {
+    // ---- TMA producer ----
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (uint32_t t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+        const int32_t m0 = (int32_t)((t % p.m_tiles) * BM), n0 = (int32_t)((t / p.m_tiles) * BN);
+        for (uint32_t ks = 0; ks < p.k_stages; ks++, it++) {
+          const uint32_t s = it % STAGES, use = it / STAGES;
+          if (use > 0 && !wait_or_abort(&bars->empty[s], (use - 1) & 1, abort_flag)) {
+            raise_abort(p.fault, abort_flag);
+            ok = false;
+            break;
+          }
+          const uint32_t stage = base + s * G::STAGE_BYTES, full = ptx::smem_u32(&bars->full[s]);
+          ptx::mbar_arrive_expect_tx(full, A_TILE_BYTES + G::PACKED_BYTES);
+          ptx::tma_load_2d(stage + G::OFF_A, &tmap_a, (int32_t)(ks * BK), m0, full);
+          ptx::tma_load_3d(stage + G::OFF_PACKED, &tmap_b, 0, n0 / 8, (int32_t)(ks * KB_PER_STAGE), full);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer ----
+    uint32_t it = 0, tile_iter = 0;
+    bool ok = true;
+    for (uint32_t t = blockIdx.x; t < tiles && ok; t += gridDim.x, tile_iter++) {
+      const uint32_t acc = tile_iter & 1, acc_use = tile_iter >> 1;
+      if (acc_use > 0 && !wait_or_abort(&bars->acc_empty[acc], (acc_use - 1) & 1, abort_flag)) {
+        if (lane == 0) raise_abort(p.fault, abort_flag);
+        break;
+      }
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + acc * BN;
+      for (uint32_t ks = 0; ks < p.k_stages; ks++, it++) {
+        const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+        if (!wait_or_abort(&bars->full[s], ph, abort_flag) || !wait_or_abort(&bars->bready[s], ph, abort_flag)) {
+          if (lane == 0) raise_abort(p.fault, abort_flag);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t stage = base + s * G::STAGE_BYTES;
+          const uint64_t a_desc = smem_desc_sw128(stage + G::OFF_A), b_desc = smem_desc_sw128(stage + G::OFF_B);
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; kk++)
+            umma_bf16(d_tmem, a_desc + (uint64_t)(kk * UMMA_K * 2 / 16), b_desc + (uint64_t)(kk * UMMA_K * 2 / 16), kInstrDesc,
+                      (ks | (uint32_t)kk) != 0);
+          umma_commit(ptx::smem_u32(&bars->empty[s]));
+        }
+        __syncwarp();
+      }
+      if (ok && lane == 0) umma_commit(ptx::smem_u32(&bars->acc_full[acc]));
+      __syncwarp();
+    }
+  } else if (warp < 2 + DEQ_THREADS / 32) {
+    // ---- dequantizers ----
+    const uint32_t d = threadIdx.x - 64;
+    uint32_t it = 0;
+    bool ok = true;
+    for (uint32_t t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+      for (uint32_t ks = 0; ks < p.k_stages; ks++, it++) {
+        const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+        if (!wait_or_abort(&bars->full[s], ph, abort_flag)) {
+          if (lane == 0) raise_abort(p.fault, abort_flag);
+          ok = false;
+          break;
+        }
+        const uint32_t packed = base + s * G::STAGE_BYTES + G::OFF_PACKED;
+        uint8_t* btile = sm + s * G::STAGE_BYTES + G::OFF_B;
+#pragma unroll
+        for (int half = 0; half < BN / DEQ_THREADS; half++) {
+          const uint32_t row = d + half * DEQ_THREADS;
+#pragma unroll
+          for (int kbl = 0; kbl < KB_PER_STAGE; kbl++) {
+            const uint32_t blk = packed + kbl * G::PACKED_ROW + row * G::BB;
+            if (DT == AION_CUDA_DTYPE_Q4_0) dequant_q4_block(blk, btile, row, kbl * 4);
+            else dequant_q8_block(blk, btile, row, kbl * 4);
+          }
+        }
+        ptx::fence_proxy_async();  // the tensor core reads this tile through the async proxy
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars->bready[s]));
+      }
+    }
+  } else {
+    // ---- epilogue: warp w may touch TMEM lanes 32*(w%4) .. +31 ----
+    const uint32_t quarter = warp & 3;
+    uint32_t tile_iter = 0;
+    for (uint32_t t = blockIdx.x; t < tiles; t += gridDim.x, tile_iter++) {
+      const uint32_t acc = tile_iter & 1, acc_use = tile_iter >> 1;
+      if (!wait_or_abort(&bars->acc_full[acc], acc_use & 1, abort_flag)) {
+        if (lane == 0) raise_abort(p.fault, abort_flag);
+        break;
+      }
+      tc_fence_after();
+      const uint32_t m0 = (t % p.m_tiles) * BM, n0 = (t / p.m_tiles) * BN;
+      const uint32_t row = m0 + quarter * 32 + lane;
+      float* crow = p.c + (uint64_t)row * p.ldc + n0;
+      const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + acc * BN;
+#pragma unroll 1
+      for (uint32_t c0 = 0; c0 < BN; c0 += 16) {
+        uint32_t r[16];
+        tmem_ld16(taddr + c0, r);
+        tmem_ld_wait();
+        if (row < p.m) {
+#pragma unroll
+          for (int q = 0; q < 4; q++) {
+            const uint32_t col = n0 + c0 + q * 4;
+            if (col < p.n) {  // n is a multiple of 8, so a group of 4 is in or out as a whole
+              float4 v = make_float4(__uint_as_float(r[4 * q]) * p.alpha, __uint_as_float(r[4 * q + 1]) * p.alpha,
+                                     __uint_as_float(r[4 * q + 2]) * p.alpha, __uint_as_float(r[4 * q + 3]) * p.alpha);
+              float4* dst = reinterpret_cast<float4*>(crow + c0 + q * 4);
+              if (p.beta != 0.0f) {
+                const float4 o = *dst;
+                v.x += p.beta * o.x, v.y += p.beta * o.y, v.z += p.beta * o.z, v.w += p.beta * o.w;
+              }
+              *dst = v;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars->acc_empty[acc]));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int DT>
+int32_t launch_gemm(AionCudaDevice* dev, const MatMulArgs& g, const __nv_bfloat16* a_bf16) {
+  using G = GemmGeom<DT>;
+  static bool configured[64] = {};
+  auto kernel = gemm_q_tcgen05_kernel<DT>;
+  if (dev->ordinal < 64 && !configured[dev->ordinal]) {
+    AION_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM_BYTES));
+    configured[dev->ordinal] = true;
+  }
+  const uint64_t kblocks = g.k / QK;
+  CUtensorMap tmap_a, tmap_b;
+  if (int32_t st = tensor_map_bf16_sw128(a_bf16, g.m, g.k, g.k * 2, BK, BM, &tmap_a)) return st;
+  {
+    // Packed weights as [K/32][ldb/8][8 blocks]: box = 2 block rows x 32 groups x 8 blocks.
+    const uint64_t dims[3] = {8ull * G::BB, g.n / 8, kblocks};
+    const uint64_t strides[2] = {8ull * G::BB, g.ldb * G::BB};
+    const uint32_t box[3] = {8u * G::BB, BN / 8, KB_PER_STAGE};
+    if (int32_t st = tensor_map_encode(g.b, 3, dims, strides, box, &tmap_b)) return st;
+  }
+  GemmParams p{};
+  p.c = g.c;
+  p.m = (uint32_t)g.m, p.n = (uint32_t)g.n, p.k = (uint32_t)g.k;
+  p.ldc = g.ldc;
+  p.alpha = g.alpha, p.beta = g.beta;
+  p.m_tiles = (uint32_t)ceil_div(g.m, (uint64_t)BM);
+  p.n_tiles = (uint32_t)ceil_div(g.n, (uint64_t)BN);
+  p.k_stages = (uint32_t)ceil_div(g.k, (uint64_t)BK);
+  p.fault = dev->fault_dev;
+  const uint32_t tiles = p.m_tiles * p.n_tiles;
+  const uint32_t grid = tiles < (uint32_t)dev->sm_count ? tiles : (uint32_t)dev->sm_count;
+  kernel<<<grid, THREADS, G::SMEM_BYTES, dev->stream>>>(p, tmap_a, tmap_b);
+  AION_CUDA_TRY(cudaGetLastError());
+  return AION_CUDA_OK;
+}
+
+}  // namespace
+
+// Returns UNSUPPORTED (without setting a message) for shapes this kernel does not read, so
+// the caller can route them to the any-shape kernel.
+int32_t gemm_tcgen05(AionCudaDevice* dev, const MatMulArgs& g, bool forced) {
+  (void)forced;
+  if (g.nt) return AION_CUDA_UNSUPPORTED;
+  if (g.dtype != AION_CUDA_DTYPE_Q4_0 && g.dtype != AION_CUDA_DTYPE_Q8_0) return AION_CUDA_UNSUPPORTED;
+  if (g.m == 0 || g.n == 0) return AION_CUDA_OK;
+  if ((g.n & 7) || (g.ldb & 7) || ((uintptr_t)g.b & 15) || ((uintptr_t)g.c & 15) || (g.ldc & 3)) return AION_CUDA_UNSUPPORTED;
+  if (g.m > (1u << 24) || g.n > (1u << 24) || g.k > (1u << 24)) return AION_CUDA_UNSUPPORTED;
+  // bf16 copy of the activation in lane scratch.
+  const size_t a_bytes = (size_t)g.m * g.k * sizeof(__nv_bfloat16);
+  if (int32_t st = dev->reserve_scratch(a_bytes)) return st;
+  __nv_bfloat16* a_bf16 = static_cast<__nv_bfloat16*>(dev->lane_scratch());
+  {
+    const uint64_t groups = g.m * (g.k / 8);
+    const unsigned blocks = (unsigned)std::min<uint64_t>(ceil_div(groups, (uint64_t)256), (uint64_t)dev->sm_count * 8);
+    convert_a_bf16_kernel<<<blocks, 256, 0, dev->stream>>>(g.a, g.lda, a_bf16, (uint32_t)g.m, (uint32_t)g.k,
+                                                           g.dtype == AION_CUDA_DTYPE_Q4_0 ? 1 : 0);
+    AION_CUDA_TRY(cudaGetLastError());
+  }
+  return g.dtype == AION_CUDA_DTYPE_Q4_0 ? launch_gemm<AION_CUDA_DTYPE_Q4_0>(dev, g, a_bf16)
+                                         : launch_gemm<AION_CUDA_DTYPE_Q8_0>(dev, g, a_bf16);
+}
+
 }  // namespace aion

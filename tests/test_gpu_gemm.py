@@ -1,0 +1,94 @@
+"""Prefill GEMM parity: the tcgen05 kernel through the C ABI against the oracle.
+
+The kernel rounds A to bf16 and dequantizes B to bf16, so the bound against the reference
+CPU arithmetic (int8 activations) is rel-L2 <= 1e-2, the tolerance stated for the path
+whose activations pass through bf16. Against f32-A x dequant(B) (the host reference of the
+reference's GPU tests, src/aion/backend/gpu/test_gpu_backend.zig:1325-1341) only the two
+bf16 roundings differ, so that distance is checked tighter (4e-3)."""
+import numpy as np
+import pytest
+
+import oracle
+from aion_b200 import capi
+from tests.gpu_util import run_matmul
+
+pytestmark = pytest.mark.gpu
+
+TOL_INT8A = 1e-2
+TOL_DEQ = 4e-3
+
+
+def rel_l2(got, want):
+    return float(np.linalg.norm(got.astype(np.float64) - want.astype(np.float64)) / max(np.linalg.norm(want.astype(np.float64)), 1e-30))
+
+
+def make(dtype, m, n, k, seed=0, ldb=0):
+    rng = np.random.default_rng(1234 + seed)
+    w = (rng.standard_normal((k, n)) * 0.02).astype(np.float32)
+    a = np.random.default_rng(5678 + seed).standard_normal((m, k)).astype(np.float32)
+    b = oracle.quantize(dtype, w, 0)
+    if ldb and ldb != n:
+        bb = oracle.BLOCK_BYTES[dtype]
+        rows = b.reshape(k // 32, n * bb)
+        wide = np.zeros((k // 32, ldb * bb), dtype=np.uint8)
+        wide[:, : n * bb] = rows
+        # the last block row holds only n blocks
+        b = wide.reshape(-1)[: ((k // 32 - 1) * ldb + n) * bb].copy()
+    return a, b
+
+
+@pytest.mark.parametrize("dtype", [capi.DTYPE_Q4_0, capi.DTYPE_Q8_0])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (33, 256, 128), (128, 256, 96), (200, 264, 256), (130, 512, 2048),
+                                   (64, 8, 32), (257, 776, 160)])
+def test_gemm_matches_oracle(backend, dtype, m, n, k):
+    a, b = make(dtype, m, n, k)
+    got = run_matmul(backend, dtype, a, b, m, n, k, flags=capi.MATMUL_FORCE_GEMM)
+    want_deq = oracle.matmul_deqf32(dtype, a, b, m, n, k).reshape(m, n)
+    want_i8 = oracle.matmul_q(dtype, a, b, m, n, k).reshape(m, n)
+    assert rel_l2(got, want_deq) <= TOL_DEQ
+    assert rel_l2(got, want_i8) <= TOL_INT8A
+
+
+@pytest.mark.parametrize("dtype", [capi.DTYPE_Q4_0, capi.DTYPE_Q8_0])
+def test_gemm_alpha_beta_and_leading_dims(backend, dtype):
+    m, n, k, lda, ldb, ldc = 150, 264, 192, 200, 272, 280
+    a, b = make(dtype, m, n, k, seed=3, ldb=ldb)
+    a_wide = np.zeros((m, lda), dtype=np.float32)
+    a_wide[:, :k] = a
+    c0 = np.random.default_rng(9).standard_normal(m * ldc).astype(np.float32)
+    got = run_matmul(backend, dtype, a_wide, b, m, n, k, lda=lda, ldb=ldb, ldc=ldc, alpha=0.5, beta=-1.25, c=c0,
+                     flags=capi.MATMUL_FORCE_GEMM)
+    want = oracle.matmul_deqf32(dtype, a_wide, b, m, n, k, lda=lda, ldb=ldb, ldc=ldc, alpha=0.5, beta=-1.25, c=c0).reshape(m, ldc)
+    assert rel_l2(got[:, :n], want[:, :n]) <= TOL_DEQ
+    # columns between n and ldc are not part of C and must be left alone
+    assert np.array_equal(got[:, n:], c0.reshape(m, ldc)[:, n:])
+
+
+@pytest.mark.parametrize("dtype", [capi.DTYPE_Q4_0, capi.DTYPE_Q8_0])
+def test_gemm_prefill_shape_auto_route(backend, dtype):
+    # BASELINE config 3, m = 512: routed to the tensor-core kernel by m alone.
+    m, n, k = 512, 8192, 2048
+    a, b = make(dtype, m, n, k, seed=7)
+    got = run_matmul(backend, dtype, a, b, m, n, k)
+    want_i8 = oracle.fast_matmul_q(dtype, a, b, m, n, k).reshape(m, n)
+    assert rel_l2(got, want_i8) <= TOL_INT8A
+    # linearity in alpha, exactly: the epilogue multiplies the same accumulators
+    got2 = run_matmul(backend, dtype, a, b, m, n, k, alpha=2.0)
+    assert np.array_equal(got2, 2.0 * got)
+
+
+def test_gemm_is_deterministic(backend):
+    m, n, k = 256, 1024, 512
+    a, b = make(capi.DTYPE_Q4_0, m, n, k, seed=11)
+    x = run_matmul(backend, capi.DTYPE_Q4_0, a, b, m, n, k, flags=capi.MATMUL_FORCE_GEMM)
+    y = run_matmul(backend, capi.DTYPE_Q4_0, a, b, m, n, k, flags=capi.MATMUL_FORCE_GEMM)
+    assert np.array_equal(x, y)
+
+
+def test_rows_between_gemv_and_gemm_keep_int8_arithmetic(backend):
+    # 17..32 rows run as GEMV passes of 16 rows: reference CPU arithmetic, tight bound.
+    m, n, k = 29, 264, 256
+    a, b = make(capi.DTYPE_Q4_0, m, n, k, seed=5)
+    got = run_matmul(backend, capi.DTYPE_Q4_0, a, b, m, n, k)
+    want = oracle.matmul_q(capi.DTYPE_Q4_0, a, b, m, n, k).reshape(m, n)
+    assert rel_l2(got, want) <= 2e-5

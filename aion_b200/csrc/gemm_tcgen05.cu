@@ -8,15 +8,15 @@
 // different rounding of the same product, bounded by rel-L2 1e-2.
 //
 // Shape of the kernel (one persistent CTA per SM, 128 x 256 output tiles, K in steps of 64):
-//   warp 0      TMA producer: the bf16 activation tile (128B-swizzled, straight into the
-//               MMA operand layout) and the packed weight blocks of the stage, untouched.
-//   warps 2-5   dequantizers: packed blocks -> bf16 -> the 128B-swizzled K-major operand
+//   warp 0      TMA producer of bf16 activation tiles (128B-swizzled, straight into the MMA
+//               operand layout); warp 2: TMA producer of the packed weight blocks, untouched.
+//   warps 3-8   dequantizers: packed blocks -> bf16 -> the 128B-swizzled K-major operand
 //               layout in shared memory (one generic-proxy pass; the packed bytes cannot be
 //               fed to the tensor core as they are), then a proxy fence and an arrive.
 //   warp 1      MMA issuer: one elected lane issues tcgen05.mma (M=128 tokens, N=256
 //               columns, K=16) four times per stage into one of two TMEM accumulators and
 //               commits to the stage's "empty" barrier; it also owns TMEM alloc / dealloc.
-//   warps 6-9   epilogue: tcgen05.ld the finished accumulator, alpha / beta in f32, store.
+//   warps 9-12  epilogue: tcgen05.ld the finished accumulator, alpha / beta in f32, store.
 // The activation is converted to bf16 once by a pre-pass (so every column tile re-reads
 // 2 bytes per element from L2 instead of converting 4), with the order of K inside each
 // group of 8 permuted for q4 to match the order in which a 32-bit word of nibbles
@@ -40,10 +40,13 @@ constexpr int BM = 128;      // tokens per tile (UMMA M)
 constexpr int BN = 256;      // output columns per tile (UMMA N)
 constexpr int BK = 64;       // K per stage: one 128-byte swizzle row of bf16
 constexpr int UMMA_K = 16;
-constexpr int STAGES = 3;
-constexpr int KB_PER_STAGE = BK / QK;  // 2 quantized blocks of each column per stage
-constexpr int THREADS = 320;
-constexpr int DEQ_THREADS = 128;
+constexpr int MAX_A_STAGES = 4, MAX_P_STAGES = 6, MAX_B_STAGES = 3;
+constexpr int KB_PER_STAGE = BK / QK;   // 2 quantized blocks of each column per stage
+constexpr int DEQ_GROUPS = 3;           // groups of dequantizer warps; group g unpacks k-stages g, g + 3, ...
+constexpr int DEQ_WARPS = 2 * DEQ_GROUPS;
+constexpr int DEQ_WARP0 = 3;            // warp 0: activation TMA, warp 1: MMA, warp 2: packed-block TMA
+constexpr int EPI_WARP0 = DEQ_WARP0 + DEQ_WARPS;
+constexpr int THREADS = (EPI_WARP0 + 4) * 32;
 constexpr int A_TILE_BYTES = BM * BK * 2;   // 16 KB
 constexpr int B_TILE_BYTES = BN * BK * 2;   // 32 KB
 constexpr uint32_t TMEM_COLS = 512;         // two f32 accumulators of 256 columns
@@ -63,12 +66,22 @@ struct GemmGeom {
   static constexpr int PACKED_ROW = BN * BB;                       // one block row of the tile
   static constexpr int PACKED_BYTES = KB_PER_STAGE * PACKED_ROW;   // 9216 (q4) / 17408 (q8)
   static constexpr int PACKED_PAD = (PACKED_BYTES + 16 + 1023) / 1024 * 1024;  // +16: the unpacker reads one word past
-  static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES + PACKED_PAD;
-  static constexpr int OFF_A = 0;
-  static constexpr int OFF_B = A_TILE_BYTES;
-  static constexpr int OFF_PACKED = A_TILE_BYTES + B_TILE_BYTES;
-  static constexpr int OFF_BARS = STAGES * STAGE_BYTES;
+  // Three rings, so each resource is released as early as its last reader allows: packed
+  // blocks after dequantization, activation tiles and dequantized tiles after their MMAs.
+  // B_STAGES equals the number of dequantizer groups and P_STAGES is a multiple of it, so
+  // every "free" barrier is waited on by one group only, use after use: a parity wait is
+  // only meaningful for a waiter that is at most one phase behind.
+  static constexpr int A_STAGES = 4;
+  static constexpr int P_STAGES = (DT == AION_CUDA_DTYPE_Q8_0) ? 3 : 6;
+  static constexpr int B_STAGES = DEQ_GROUPS;
+  static_assert(P_STAGES % DEQ_GROUPS == 0, "a packed stage belongs to one dequantizer group");
+  static constexpr int OFF_BRING = 0;
+  static constexpr int OFF_ARING = OFF_BRING + B_STAGES * B_TILE_BYTES;
+  static constexpr int OFF_PRING = OFF_ARING + A_STAGES * A_TILE_BYTES;
+  static constexpr int OFF_BARS = OFF_PRING + P_STAGES * PACKED_PAD;
   static constexpr int SMEM_BYTES = OFF_BARS + 256 + 1024;  // + slack to align the base to 1024
+  static_assert(A_STAGES <= MAX_A_STAGES && P_STAGES <= MAX_P_STAGES && B_STAGES <= MAX_B_STAGES, "barrier block");
+  static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 };
 
 // ---- f32 -> bf16 pre-pass ------------------------------------------------------------
@@ -157,21 +170,26 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 
 // Barrier block at the end of shared memory.
 struct Bars {
-  uint64_t full[STAGES];     // TMA landed the activation tile and the packed blocks
-  uint64_t bready[STAGES];   // the dequantized weight tile of the stage is written
-  uint64_t empty[STAGES];    // the MMAs that read the stage are done
-  uint64_t acc_full[2];      // an accumulator holds a finished tile
-  uint64_t acc_empty[2];     // the epilogue has drained it
+  uint64_t a_full[MAX_A_STAGES];   // TMA landed an activation tile
+  uint64_t a_empty[MAX_A_STAGES];  // the MMAs that read it are done
+  uint64_t p_full[MAX_P_STAGES];   // TMA landed a stage of packed blocks
+  uint64_t p_empty[MAX_P_STAGES];  // every dequantizer warp has read it
+  uint64_t bready[MAX_B_STAGES];   // a dequantized weight tile is written
+  uint64_t bfree[MAX_B_STAGES];    // the MMAs that read it are done
+  uint64_t acc_full[2];            // an accumulator holds a finished tile
+  uint64_t acc_empty[2];           // the epilogue has drained it
   uint32_t tmem_base;
   uint32_t abort;
 };
+static_assert(sizeof(Bars) <= 256, "barrier block");
 
 // Bounded wait that also gives up as soon as another role has aborted.
+template <bool SPIN = false>
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
   const uint32_t b = ptx::smem_u32(bar);
-  for (uint32_t i = 0; i < (1u << 18); i++) {
-    if (ptx::mbar_try_wait(b, parity)) return true;
-    if (*abort_flag) return false;
+  for (uint32_t i = 0; i < (SPIN ? (1u << 24) : (1u << 18)); i++) {
+    if (SPIN ? ptx::mbar_try_wait_spin(b, parity) : ptx::mbar_try_wait(b, parity)) return true;
+    if ((!SPIN || (i & 63) == 63) && *abort_flag) return false;
   }
   return false;
 }
@@ -246,11 +264,19 @@ gemm_q_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm
   volatile uint32_t* abort_flag = &bars->abort;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr uint32_t AS = G::A_STAGES, PS = G::P_STAGES, BS = G::B_STAGES;
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; s++) {
-      ptx::mbar_init(ptx::smem_u32(&bars->full[s]), 1);
-      ptx::mbar_init(ptx::smem_u32(&bars->bready[s]), DEQ_THREADS / 32);
-      ptx::mbar_init(ptx::smem_u32(&bars->empty[s]), 1);
+    for (int s = 0; s < (int)AS; s++) {
+      ptx::mbar_init(ptx::smem_u32(&bars->a_full[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&bars->a_empty[s]), 1);
+    }
+    for (int s = 0; s < (int)PS; s++) {
+      ptx::mbar_init(ptx::smem_u32(&bars->p_full[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&bars->p_empty[s]), DEQ_WARPS / DEQ_GROUPS);
+    }
+    for (int s = 0; s < (int)BS; s++) {
+      ptx::mbar_init(ptx::smem_u32(&bars->bready[s]), DEQ_WARPS / DEQ_GROUPS);
+      ptx::mbar_init(ptx::smem_u32(&bars->bfree[s]), 1);
     }
     for (int a = 0; a < 2; a++) {
       ptx::mbar_init(ptx::smem_u32(&bars->acc_full[a]), 1);
@@ -272,23 +298,42 @@ gemm_q_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm
   const uint32_t tiles = p.m_tiles * p.n_tiles;
 
   if (warp == 0) {
-    // ---- TMA producer ----
+    // ---- TMA producer of activation tiles ----
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
       for (uint32_t t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
-        const int32_t m0 = (int32_t)((t % p.m_tiles) * BM), n0 = (int32_t)((t / p.m_tiles) * BN);
+        const int32_t m0 = (int32_t)((t % p.m_tiles) * BM);
         for (uint32_t ks = 0; ks < p.k_stages; ks++, it++) {
-          const uint32_t s = it % STAGES, use = it / STAGES;
-          if (use > 0 && !wait_or_abort(&bars->empty[s], (use - 1) & 1, abort_flag)) {
+          const uint32_t s = it % AS, use = it / AS;
+          if (use > 0 && !wait_or_abort<true>(&bars->a_empty[s], (use - 1) & 1, abort_flag)) {
             raise_abort(p.fault, abort_flag);
             ok = false;
             break;
           }
-          const uint32_t stage = base + s * G::STAGE_BYTES, full = ptx::smem_u32(&bars->full[s]);
-          ptx::mbar_arrive_expect_tx(full, A_TILE_BYTES + G::PACKED_BYTES);
-          ptx::tma_load_2d(stage + G::OFF_A, &tmap_a, (int32_t)(ks * BK), m0, full);
-          ptx::tma_load_3d(stage + G::OFF_PACKED, &tmap_b, 0, n0 / 8, (int32_t)(ks * KB_PER_STAGE), full);
+          const uint32_t full = ptx::smem_u32(&bars->a_full[s]);
+          ptx::mbar_arrive_expect_tx(full, A_TILE_BYTES);
+          ptx::tma_load_2d(base + G::OFF_ARING + s * A_TILE_BYTES, &tmap_a, (int32_t)(ks * BK), m0, full);
+        }
+      }
+    }
+  } else if (warp == 2) {
+    // ---- TMA producer of packed weight blocks ----
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (uint32_t t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+        const int32_t n0 = (int32_t)((t / p.m_tiles) * BN);
+        for (uint32_t ks = 0; ks < p.k_stages; ks++, it++) {
+          const uint32_t s = it % PS, use = it / PS;
+          if (use > 0 && !wait_or_abort<true>(&bars->p_empty[s], (use - 1) & 1, abort_flag)) {
+            raise_abort(p.fault, abort_flag);
+            ok = false;
+            break;
+          }
+          const uint32_t full = ptx::smem_u32(&bars->p_full[s]);
+          ptx::mbar_arrive_expect_tx(full, G::PACKED_BYTES);
+          ptx::tma_load_3d(base + G::OFF_PRING + s * G::PACKED_PAD, &tmap_b, 0, n0 / 8, (int32_t)(ks * KB_PER_STAGE), full);
         }
       }
     }
@@ -298,52 +343,59 @@ gemm_q_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm
     bool ok = true;
     for (uint32_t t = blockIdx.x; t < tiles && ok; t += gridDim.x, tile_iter++) {
       const uint32_t acc = tile_iter & 1, acc_use = tile_iter >> 1;
-      if (acc_use > 0 && !wait_or_abort(&bars->acc_empty[acc], (acc_use - 1) & 1, abort_flag)) {
+      if (acc_use > 0 && !wait_or_abort<true>(&bars->acc_empty[acc], (acc_use - 1) & 1, abort_flag)) {
         if (lane == 0) raise_abort(p.fault, abort_flag);
         break;
       }
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + acc * BN;
       for (uint32_t ks = 0; ks < p.k_stages; ks++, it++) {
-        const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-        if (!wait_or_abort(&bars->full[s], ph, abort_flag) || !wait_or_abort(&bars->bready[s], ph, abort_flag)) {
+        const uint32_t sa = it % AS, pha = (it / AS) & 1, sb = it % BS, phb = (it / BS) & 1;
+        if (!wait_or_abort<true>(&bars->a_full[sa], pha, abort_flag) || !wait_or_abort<true>(&bars->bready[sb], phb, abort_flag)) {
           if (lane == 0) raise_abort(p.fault, abort_flag);
           ok = false;
           break;
         }
         tc_fence_after();
         if (lane == 0) {
-          const uint32_t stage = base + s * G::STAGE_BYTES;
-          const uint64_t a_desc = smem_desc_sw128(stage + G::OFF_A), b_desc = smem_desc_sw128(stage + G::OFF_B);
+          const uint64_t a_desc = smem_desc_sw128(base + G::OFF_ARING + sa * A_TILE_BYTES);
+          const uint64_t b_desc = smem_desc_sw128(base + G::OFF_BRING + sb * B_TILE_BYTES);
 #pragma unroll
           for (int kk = 0; kk < BK / UMMA_K; kk++)
             umma_bf16(d_tmem, a_desc + (uint64_t)(kk * UMMA_K * 2 / 16), b_desc + (uint64_t)(kk * UMMA_K * 2 / 16), kInstrDesc,
                       (ks | (uint32_t)kk) != 0);
-          umma_commit(ptx::smem_u32(&bars->empty[s]));
+          umma_commit(ptx::smem_u32(&bars->a_empty[sa]));
+          umma_commit(ptx::smem_u32(&bars->bfree[sb]));
         }
         __syncwarp();
       }
       if (ok && lane == 0) umma_commit(ptx::smem_u32(&bars->acc_full[acc]));
       __syncwarp();
     }
-  } else if (warp < 2 + DEQ_THREADS / 32) {
-    // ---- dequantizers ----
-    const uint32_t d = threadIdx.x - 64;
+  } else if (warp < EPI_WARP0) {
+    // ---- dequantizers: DEQ_GROUPS groups of warps take the k-stages in turn, so that
+    // several stages are being unpacked at once and one stage's wait / load / fence
+    // latency hides behind another's arithmetic. Thread j of a group owns weight
+    // columns (operand rows) j, j + GROUP_THREADS, ... of the tile.
+    constexpr uint32_t GROUP_WARPS = DEQ_WARPS / DEQ_GROUPS, GROUP_THREADS = GROUP_WARPS * 32;
+    const uint32_t dw = warp - DEQ_WARP0, group = dw / GROUP_WARPS, j0 = (dw % GROUP_WARPS) * 32 + lane;
     uint32_t it = 0;
     bool ok = true;
     for (uint32_t t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
       for (uint32_t ks = 0; ks < p.k_stages; ks++, it++) {
-        const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-        if (!wait_or_abort(&bars->full[s], ph, abort_flag)) {
+        if (it % DEQ_GROUPS != group) continue;
+        const uint32_t sp = it % PS, php = (it / PS) & 1, sb = it % BS, buse = it / BS;
+        if (!wait_or_abort<true>(&bars->p_full[sp], php, abort_flag) ||
+            (buse > 0 && !wait_or_abort<true>(&bars->bfree[sb], (buse - 1) & 1, abort_flag))) {
           if (lane == 0) raise_abort(p.fault, abort_flag);
           ok = false;
           break;
         }
-        const uint32_t packed = base + s * G::STAGE_BYTES + G::OFF_PACKED;
-        uint8_t* btile = sm + s * G::STAGE_BYTES + G::OFF_B;
+        const uint32_t packed = base + G::OFF_PRING + sp * G::PACKED_PAD;
+        uint8_t* btile = sm + G::OFF_BRING + sb * B_TILE_BYTES;
 #pragma unroll
-        for (int half = 0; half < BN / DEQ_THREADS; half++) {
-          const uint32_t row = d + half * DEQ_THREADS;
+        for (int rr = 0; rr < BN / (int)GROUP_THREADS; rr++) {
+          const uint32_t row = j0 + rr * GROUP_THREADS;
 #pragma unroll
           for (int kbl = 0; kbl < KB_PER_STAGE; kbl++) {
             const uint32_t blk = packed + kbl * G::PACKED_ROW + row * G::BB;
@@ -353,7 +405,10 @@ gemm_q_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm
         }
         ptx::fence_proxy_async();  // the tensor core reads this tile through the async proxy
         __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars->bready[s]));
+        if (lane == 0) {
+          ptx::mbar_arrive(ptx::smem_u32(&bars->p_empty[sp]));
+          ptx::mbar_arrive(ptx::smem_u32(&bars->bready[sb]));
+        }
       }
     }
   } else {

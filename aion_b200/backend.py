@@ -299,6 +299,69 @@ class StepAttention:
     attn_logits_soft_cap: float = 0.0
 
 
+@dataclasses.dataclass
+class StepRMSNorm:
+    """src/aion/runtime/executable.zig:94-101."""
+    out: int
+    x: int
+    gamma: int
+    beta: int
+    eps: float
+    residual: Optional[int] = None
+
+
+@dataclasses.dataclass
+class StepElemwiseBinary:
+    """src/aion/runtime/executable.zig:42-51; identical shapes only; op in {"add", "mul", "gate"} (gate act = gelu)."""
+    op: str
+    out: int
+    a: int
+    b: int
+
+
+@dataclasses.dataclass
+class StepRoPE1D:
+    """src/aion/runtime/executable.zig:163-170."""
+    out: int
+    x: int
+    positions: int
+    base_frequency: float
+    scale_factor: float = 1.0
+    rope_proportion: float = 1.0
+
+
+@dataclasses.dataclass
+class StepCast:
+    """src/aion/runtime/executable.zig:209."""
+    out: int
+    x: int
+    to_dtype: int
+
+
+@dataclasses.dataclass
+class StepSequenceAppend:
+    """src/aion/runtime/executable.zig:199-206."""
+    cache: int
+    new_kv: int
+    end_index: int
+
+
+@dataclasses.dataclass
+class StepGatherRows:
+    """src/aion/runtime/executable.zig:155; q8_0 table dequantized on read."""
+    out: int
+    table: int
+    indices: int
+
+
+@dataclasses.dataclass
+class StepArgMax:
+    """src/aion/runtime/executable.zig:140; last axis only."""
+    out: int
+    a: int
+    axis: int = -1
+
+
 def _rows_of(shape: tuple) -> int:
     """Leading dims folded into M (src/aion/backend/cpu/exec/matmul.zig:333-338)."""
     m = 1
@@ -324,6 +387,8 @@ class CudaSession:
                 self._matmul_nt(step)
             elif isinstance(step, StepAttention):
                 self._attention(step)
+            elif type(step) in self._GLUE:
+                getattr(self, self._GLUE[type(step)])(step)
             else:
                 # An unsupported step never falls back to the host
                 # (src/aion/runtime/executable.zig:355-357).
@@ -339,7 +404,27 @@ class CudaSession:
             reads = {step.q, step.k, step.v}
             reads |= {t for t in (step.query_positions, step.kv_lengths) if t is not None}
             return reads, {step.out}
+        if isinstance(step, StepRMSNorm):
+            reads = {step.x, step.gamma, step.beta} | ({step.residual} if step.residual is not None else set())
+            return reads, {step.out}
+        if isinstance(step, StepElemwiseBinary):
+            return {step.a, step.b}, {step.out}
+        if isinstance(step, StepRoPE1D):
+            return {step.x, step.positions}, {step.out}
+        if isinstance(step, StepCast):
+            return {step.x}, {step.out}
+        if isinstance(step, StepSequenceAppend):
+            return {step.new_kv, step.end_index, step.cache}, {step.cache}
+        if isinstance(step, StepGatherRows):
+            return {step.table, step.indices}, {step.out}
+        if isinstance(step, StepArgMax):
+            return {step.a}, {step.out}
         return set(), set()
+
+    def _span(self, tid: int) -> tuple:
+        """The device bytes a tensor occupies: views of one buffer must be seen as the same memory."""
+        ch = self.store.acquire_const(tid)
+        return (ch.handle, ch.offset, ch.offset + max(ch.len, 1))
 
     def record(self, program: Sequence[object], lanes: int = capi.RECORD_LANES) -> "RecordedProgram":
         """Record the steps once into a replayable device program (one launch per replay).
@@ -353,14 +438,19 @@ class CudaSession:
         _check(lib.aion_cuda_record_begin(h))
         prog = C.c_void_p()
         try:
-            writer: dict[int, int] = {}            # tensor -> lane that last wrote it since the last join
-            readers: dict[int, set] = {}           # tensor -> lanes that read it since the last join
+            writers: list[tuple] = []              # (span, lane) written since the last join
+            readers: list[tuple] = []              # (span, lane) read since the last join
             next_lane = 0
+
+            def overlaps(a, b):
+                return a[0] == b[0] and a[1] < b[2] and b[1] < a[2]
+
             for step in program:
                 reads, writes = self._touches(step)
-                clash = {writer[t] for t in (reads | writes) if t in writer}
-                for t in writes:
-                    clash |= readers.get(t, set())
+                rspans = [self._span(t) for t in reads]
+                wspans = [self._span(t) for t in writes]
+                clash = {ln for sp, ln in writers for q in rspans + wspans if overlaps(sp, q)}
+                clash |= {ln for sp, ln in readers for q in wspans if overlaps(sp, q)}
                 if not clash:
                     lane = next_lane
                     next_lane = (next_lane + 1) % lanes
@@ -368,15 +458,13 @@ class CudaSession:
                     lane = next(iter(clash))
                 else:
                     _check(lib.aion_cuda_record_join(h))
-                    writer.clear()
+                    writers.clear()
                     readers.clear()
                     lane, next_lane = 0, 1 % lanes
                 _check(lib.aion_cuda_record_lane(h, lane))
                 self.execute([step])
-                for t in writes:
-                    writer[t] = lane
-                for t in reads:
-                    readers.setdefault(t, set()).add(lane)
+                writers.extend((sp, lane) for sp in wspans)
+                readers.extend((sp, lane) for sp in rspans)
         finally:
             st = lib.aion_cuda_record_end(h, C.byref(prog))
         _check(st)
@@ -459,6 +547,122 @@ class CudaSession:
                              window_left=s.window.left, window_right=s.window.right, window_chunk=s.window.chunk,
                              flags=0)
         _check(self._lib.aion_cuda_attention(self.backend._h, C.byref(rec)))
+
+
+    # ---- decoder glue steps -------------------------------------------------------
+    def _need(self, tid: int, dtype: int, what: str) -> TensorMeta:
+        m = self.store.meta(tid)
+        if m.dtype != dtype:
+            raise BackendError(capi.INVALID_ARGUMENT, f"{what}: dtype {m.dtype}, expected {dtype}")
+        return m
+
+    def _rms_norm(self, s: StepRMSNorm) -> None:
+        st = self.store
+        om = st.meta(s.out)
+        if om.dtype == capi.DTYPE_F16:
+            raise BackendError(capi.UNSUPPORTED, "rms_norm: f16 tensors are outside this backend")
+        for t in (s.out, s.x, s.gamma, s.beta):
+            self._need(t, capi.DTYPE_F32, "rms_norm")
+        gm = st.meta(s.gamma)
+        # src/aion/backend/cpu/exec/layernorm.zig:74-79: gamma's shape is the trailing dims of out.
+        if gm.rank == 0 or gm.rank > om.rank or tuple(om.shape[om.rank - gm.rank:]) != tuple(gm.shape):
+            raise BackendError(capi.INVALID_ARGUMENT, "rms_norm: gamma must match the trailing dims of out")
+        cols = int(np.prod(gm.shape))
+        rows = int(np.prod(om.shape)) // cols
+        none = capi.Operand(0, 0, 0)
+        res = none
+        if s.residual is not None:
+            self._need(s.residual, capi.DTYPE_F32, "rms_norm.residual")
+            res = st.acquire_const(s.residual).operand()
+        rec = capi.RMSNorm(out=st.acquire_mut(s.out).operand(), x=st.acquire_const(s.x).operand(),
+                           gamma=st.acquire_const(s.gamma).operand(), beta=st.acquire_const(s.beta).operand(),
+                           residual=res, rows=rows, cols=cols, eps=s.eps, reserved=0)
+        _check(self._lib.aion_cuda_rms_norm(self.backend._h, C.byref(rec)))
+
+    def _elemwise(self, s: StepElemwiseBinary) -> None:
+        st = self.store
+        ops = {"add": capi.ELEMWISE_ADD, "mul": capi.ELEMWISE_MUL, "gate": capi.ELEMWISE_GATE_GELU}
+        if s.op not in ops:
+            raise BackendError(capi.UNSUPPORTED, f"elemwise: op {s.op!r} is outside this backend")
+        om = self._need(s.out, capi.DTYPE_F32, "elemwise")
+        for t in (s.a, s.b):
+            if tuple(self._need(t, capi.DTYPE_F32, "elemwise").shape) != tuple(om.shape):
+                raise BackendError(capi.UNSUPPORTED, "elemwise: only identical shapes are covered")
+        rec = capi.Elemwise(out=st.acquire_mut(s.out).operand(), a=st.acquire_const(s.a).operand(),
+                            b=st.acquire_const(s.b).operand(), count=int(np.prod(om.shape)), op=ops[s.op], reserved=0)
+        _check(self._lib.aion_cuda_elemwise(self.backend._h, C.byref(rec)))
+
+    def _rope(self, s: StepRoPE1D) -> None:
+        st = self.store
+        xm = self._need(s.x, capi.DTYPE_F32, "rope")
+        om = self._need(s.out, capi.DTYPE_F32, "rope")
+        pm = self._need(s.positions, capi.DTYPE_I32, "rope.positions")
+        if xm.rank != 4 or tuple(om.shape) != tuple(xm.shape) or tuple(pm.shape) != tuple(xm.shape[:2]):
+            raise BackendError(capi.INVALID_ARGUMENT, "rope: x, out [B, L, N, H] and positions [B, L]")
+        B, L, N, H = xm.shape
+        rec = capi.RoPE(out=st.acquire_mut(s.out).operand(), x=st.acquire_const(s.x).operand(),
+                        positions=st.acquire_const(s.positions).operand(), batch=B, len=L, heads=N, head_dim=H,
+                        base_frequency=s.base_frequency, scale_factor=s.scale_factor, proportion=s.rope_proportion,
+                        reserved=0)
+        _check(self._lib.aion_cuda_rope(self.backend._h, C.byref(rec)))
+
+    def _cast(self, s: StepCast) -> None:
+        st = self.store
+        xm, om = st.meta(s.x), st.meta(s.out)
+        if om.dtype != s.to_dtype or int(np.prod(xm.shape)) != int(np.prod(om.shape)):
+            raise BackendError(capi.INVALID_ARGUMENT, "cast: out does not match to_dtype / element count")
+        rec = capi.Cast(out=st.acquire_mut(s.out).operand(), in_=st.acquire_const(s.x).operand(),
+                        count=int(np.prod(xm.shape)), from_dtype=xm.dtype, to_dtype=om.dtype)
+        _check(self._lib.aion_cuda_cast(self.backend._h, C.byref(rec)))
+
+    def _sequence_append(self, s: StepSequenceAppend) -> None:
+        st = self.store
+        cm, nm = st.meta(s.cache), st.meta(s.new_kv)
+        im = self._need(s.end_index, capi.DTYPE_I32, "sequence_append.end_index")
+        # src/aion/backend/cpu/exec/sequence_append.zig:25-37
+        if cm.rank != 4 or nm.rank != 4 or im.rank != 1 or cm.dtype != nm.dtype:
+            raise BackendError(capi.INVALID_ARGUMENT, "sequence_append: ranks / dtypes")
+        if cm.shape[0] != nm.shape[0] or cm.shape[2] != nm.shape[2] or cm.shape[3] != nm.shape[3] or im.shape[0] != cm.shape[0]:
+            raise BackendError(capi.INVALID_ARGUMENT, "sequence_append: shapes do not agree")
+        policy = st.sequence_cache_policy_info(s.cache)
+        if policy == "growable":
+            raise BackendError(capi.UNSUPPORTED, "sequence_append: growable caches are settled by the storage layer, not here")
+        B, T, H, D = cm.shape
+        rec = capi.SequenceAppend(cache=st.acquire_mut(s.cache).operand(), new_kv=st.acquire_const(s.new_kv).operand(),
+                                  end_index=st.acquire_const(s.end_index).operand(), batch=B, t_cap=T, heads=H, head_dim=D,
+                                  new_len=nm.shape[1], dtype=cm.dtype, rolling=1 if policy == "rolling" else 0)
+        _check(self._lib.aion_cuda_sequence_append(self.backend._h, C.byref(rec)))
+
+    def _gather_rows(self, s: StepGatherRows) -> None:
+        st = self.store
+        tm, om = st.meta(s.table), self._need(s.out, capi.DTYPE_F32, "gather_rows.out")
+        im = self._need(s.indices, capi.DTYPE_I32, "gather_rows.indices")
+        if tm.dtype != capi.DTYPE_Q8_0 or tm.rank != 2 or tm.quant_axis != 1:
+            raise BackendError(capi.UNSUPPORTED, "gather_rows: only q8_0 [V, D] tables quantized along axis 1 are covered")
+        V, D = tm.shape
+        count = int(np.prod(im.shape))
+        if om.shape[-1] != D or int(np.prod(om.shape)) != count * D:
+            raise BackendError(capi.INVALID_ARGUMENT, "gather_rows: out must be indices.shape + [D]")
+        rec = capi.GatherRows(out=st.acquire_mut(s.out).operand(), table=st.acquire_const(s.table).operand(),
+                              indices=st.acquire_const(s.indices).operand(), table_rows=V, d=D, count=count,
+                              block_order=tm.block_order, reserved=0)
+        _check(self._lib.aion_cuda_gather_rows(self.backend._h, C.byref(rec)))
+
+    def _argmax(self, s: StepArgMax) -> None:
+        st = self.store
+        am = self._need(s.a, capi.DTYPE_F32, "argmax")
+        om = self._need(s.out, capi.DTYPE_I32, "argmax.out")
+        if s.axis not in (-1, am.rank - 1):
+            raise BackendError(capi.UNSUPPORTED, "argmax: only the last axis is covered")
+        n = am.shape[-1]
+        outer = int(np.prod(am.shape)) // n
+        if int(np.prod(om.shape)) != outer:
+            raise BackendError(capi.INVALID_ARGUMENT, "argmax: out shape")
+        rec = capi.ArgMax(out=st.acquire_mut(s.out).operand(), in_=st.acquire_const(s.a).operand(), outer=outer, n=n)
+        _check(self._lib.aion_cuda_argmax(self.backend._h, C.byref(rec)))
+
+    _GLUE = {StepRMSNorm: "_rms_norm", StepElemwiseBinary: "_elemwise", StepRoPE1D: "_rope", StepCast: "_cast",
+             StepSequenceAppend: "_sequence_append", StepGatherRows: "_gather_rows", StepArgMax: "_argmax"}
 
 
 class RecordedProgram:

@@ -19,7 +19,7 @@ INCLUDE = os.path.join(os.path.dirname(PKG), "include")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr"]
 # Files whose results must be byte-exact with the reference: no fused multiply-add.
-NO_FMA = {"quant.cu"}
+NO_FMA = {"quant.cu", "glue.cu"}
 
 
 def _sources() -> list[str]:

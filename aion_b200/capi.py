@@ -16,6 +16,8 @@ ORDER_ROW_MAJOR, ORDER_LANES4, ORDER_LANES8, ORDER_LANES16, ORDER_LANES32, ORDER
 WINDOW_UNBOUNDED = 0xFFFFFFFF
 MATMUL_AUTO, MATMUL_FORCE_GENERIC, MATMUL_FORCE_GEMV, MATMUL_FORCE_GEMM = 0, 1, 2, 4
 GEMV_MAX_M = 16
+GEMM_MIN_M = 33
+ELEMWISE_ADD, ELEMWISE_MUL, ELEMWISE_GATE_GELU = 0, 1, 2
 RECORD_LANES = 8
 
 LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libaion_cuda.so")
@@ -70,6 +72,44 @@ class Attention(C.Structure):
     ]
 
 
+class RMSNorm(C.Structure):
+    _fields_ = [("out", Operand), ("x", Operand), ("gamma", Operand), ("beta", Operand), ("residual", Operand),
+                ("rows", C.c_uint64), ("cols", C.c_uint64), ("eps", C.c_float), ("reserved", C.c_uint32)]
+
+
+class Elemwise(C.Structure):
+    _fields_ = [("out", Operand), ("a", Operand), ("b", Operand), ("count", C.c_uint64), ("op", C.c_uint32),
+                ("reserved", C.c_uint32)]
+
+
+class RoPE(C.Structure):
+    _fields_ = [("out", Operand), ("x", Operand), ("positions", Operand),
+                ("batch", C.c_uint64), ("len", C.c_uint64), ("heads", C.c_uint64), ("head_dim", C.c_uint64),
+                ("base_frequency", C.c_float), ("scale_factor", C.c_float), ("proportion", C.c_float),
+                ("reserved", C.c_uint32)]
+
+
+class Cast(C.Structure):
+    _fields_ = [("out", Operand), ("in_", Operand), ("count", C.c_uint64), ("from_dtype", C.c_uint32),
+                ("to_dtype", C.c_uint32)]
+
+
+class SequenceAppend(C.Structure):
+    _fields_ = [("cache", Operand), ("new_kv", Operand), ("end_index", Operand),
+                ("batch", C.c_uint64), ("t_cap", C.c_uint64), ("heads", C.c_uint64), ("head_dim", C.c_uint64),
+                ("new_len", C.c_uint64), ("dtype", C.c_uint32), ("rolling", C.c_uint32)]
+
+
+class GatherRows(C.Structure):
+    _fields_ = [("out", Operand), ("table", Operand), ("indices", Operand),
+                ("table_rows", C.c_uint64), ("d", C.c_uint64), ("count", C.c_uint64),
+                ("block_order", C.c_uint32), ("reserved", C.c_uint32)]
+
+
+class ArgMax(C.Structure):
+    _fields_ = [("out", Operand), ("in_", Operand), ("outer", C.c_uint64), ("n", C.c_uint64)]
+
+
 _DEV = C.c_void_p
 _OPP = C.POINTER(Operand)
 
@@ -102,6 +142,13 @@ SIGNATURES = {
     "aion_cuda_matmul_static_scratch": (C.c_int32, [_DEV, C.POINTER(MatMul)]),
     "aion_cuda_matmul_nt": (C.c_int32, [_DEV, C.POINTER(MatMulNT)]),
     "aion_cuda_attention": (C.c_int32, [_DEV, C.POINTER(Attention)]),
+    "aion_cuda_rms_norm": (C.c_int32, [_DEV, C.POINTER(RMSNorm)]),
+    "aion_cuda_elemwise": (C.c_int32, [_DEV, C.POINTER(Elemwise)]),
+    "aion_cuda_rope": (C.c_int32, [_DEV, C.POINTER(RoPE)]),
+    "aion_cuda_cast": (C.c_int32, [_DEV, C.POINTER(Cast)]),
+    "aion_cuda_sequence_append": (C.c_int32, [_DEV, C.POINTER(SequenceAppend)]),
+    "aion_cuda_gather_rows": (C.c_int32, [_DEV, C.POINTER(GatherRows)]),
+    "aion_cuda_argmax": (C.c_int32, [_DEV, C.POINTER(ArgMax)]),
     "aion_cuda_quantize": (C.c_int32, [_DEV, C.c_uint32, _OPP, C.POINTER(C.c_uint64), C.c_uint32, C.c_uint32, _OPP]),
     "aion_cuda_dequantize": (C.c_int32, [_DEV, C.c_uint32, _OPP, C.c_uint64, _OPP]),
     "aion_cuda_relayout_q8": (C.c_int32, [_DEV, C.c_uint32, C.c_uint32, C.c_uint64, C.c_uint64, _OPP, _OPP]),

@@ -249,7 +249,7 @@ int32_t AionCudaDevice::check_fault() {
   switch (f) {
     case FAULT_INVALID_ARGUMENT:
       return fail(AION_CUDA_INVALID_ARGUMENT,
-                  "a kernel rejected its inputs (negative position or length, or a length beyond the cache)");
+                  "a kernel rejected its inputs (a negative or out-of-range position, length or index, or a non-finite norm)");
     case FAULT_WAIT_EXPIRED:
       return fail(AION_CUDA_INTERNAL_ERROR, "a kernel gave up a bounded wait on a copy barrier");
     case FAULT_NONFINITE:

@@ -1,0 +1,376 @@
+// Decoder glue steps: RMSNorm (+residual), elementwise add / mul / GELU gate, RoPE,
+// f32 <-> f16 cast, SequenceAppend, GatherRows from a q8_0 table, ArgMax.
+//
+// These are the ops on either side of the matmul / attention path in a decode program
+// (src/bench/models.zig:364-540 in the reference shows the graph shape). Each is a small
+// HBM-bound pass; what matters is that they run on the device, in the session's stream,
+// so a token step never returns to the host. Arithmetic follows the reference CPU
+// executors operation by operation; this file is compiled without FMA contraction so a
+// multiply followed by an add rounds twice, as it does there.
+#include <cfloat>
+#include <cmath>
+
+#include "common.cuh"
+#include "quant_device.cuh"
+
+namespace aion {
+
+namespace {
+
+// ---- fast_math (src/aion/backend/cpu/kernels/fast_math.zig:53-141) -------------------
+__device__ __forceinline__ float clampf(float x, float lo, float hi) { return fmaxf(lo, fminf(hi, x)); }
+__device__ __forceinline__ float exp_approx(float x_in) {
+  const float x = clampf(x_in, -80.0f, 80.0f);
+  const float y = x * 1.4426950408889634f;
+  const int n = (int)floorf(y + 0.5f);
+  const float r = y - (float)n;
+  const float t = r * 0.6931471805599453f;
+  const float c4 = 1.0f / 24.0f, c3 = 1.0f / 6.0f, c2 = 0.5f;
+  const float poly = 1.0f + t * (1.0f + t * (c2 + t * (c3 + t * c4)));
+  return __uint_as_float((uint32_t)(n + 127) << 23) * poly;
+}
+__device__ __forceinline__ float sigmoid_approx(float x) {
+  float y;
+  if (x >= 0.0f) {
+    const float e = exp_approx(-x);
+    y = 1.0f / (1.0f + e);
+  } else {
+    const float e = exp_approx(x);
+    y = e / (1.0f + e);
+  }
+  return clampf(y, 0.0f, 1.0f);
+}
+__device__ __forceinline__ float tanh_approx(float x) { return clampf(2.0f * sigmoid_approx(2.0f * x) - 1.0f, -1.0f, 1.0f); }
+// src/aion/backend/cpu/kernels/gelu.zig:8-14
+__device__ __forceinline__ float gelu_approx(float x) {
+  const float x3 = x * x * x;
+  const float t = 0.7978845608028654f * (x + 0.044715f * x3);
+  return 0.5f * x * (1.0f + tanh_approx(t));
+}
+
+// ---- RMSNorm: one warp per row -------------------------------------------------------
+__global__ void rms_norm_kernel(float* out, const float* x, const float* __restrict__ gamma,
+                                const float* __restrict__ beta, const float* residual, uint64_t rows,
+                                uint64_t cols, float eps, int* fault) {
+  const int lane = threadIdx.x & 31;
+  const uint64_t r = blockIdx.x * (uint64_t)(blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= rows) return;
+  const float* xr = x + r * cols;
+  float sq = 0.0f;
+  for (uint64_t c = lane; c < cols; c += 32) {
+    const float v = xr[c];
+    sq += v * v;
+  }
+  for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xFFFFFFFFu, sq, o);
+  const float d = sq * (1.0f / (float)cols) + eps;
+  if (!(d > 0.0f) || !isfinite(d)) {
+    if (lane == 0) atomicCAS(fault, FAULT_NONE, FAULT_INVALID_ARGUMENT);
+    return;
+  }
+  const float inv = 1.0f / sqrtf(d);
+  for (uint64_t c = lane; c < cols; c += 32) {
+    float v = ((xr[c] * inv) * gamma[c]) + beta[c];
+    if (residual) v = v + residual[r * cols + c];
+    out[r * cols + c] = v;
+  }
+}
+
+// ---- elementwise ----------------------------------------------------------------------
+__global__ void elemwise_kernel(float* out, const float* a, const float* b, uint64_t n,
+                                uint32_t op) {
+  for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+    const float av = a[i], bv = b[i];
+    float v;
+    if (op == AION_CUDA_ELEMWISE_ADD) v = av + bv;
+    else if (op == AION_CUDA_ELEMWISE_MUL) v = av * bv;
+    else v = gelu_approx(av) * bv;
+    out[i] = v;
+  }
+}
+
+// ---- RoPE: one thread per (b, l, pair); the rotation is reused by every head ----------
+__global__ void rope_kernel(float* out, const float* x, const int32_t* __restrict__ pos, uint64_t bl,
+                            uint32_t heads, uint32_t d, uint32_t rope_pairs, float step, float scale_factor) {
+  const uint32_t pairs_total = d / 2;
+  const uint64_t idx = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x;
+  if (idx >= bl * pairs_total) return;
+  const uint64_t row = idx / pairs_total;
+  const uint32_t i = (uint32_t)(idx % pairs_total);
+  const float* xb = x + row * heads * d;
+  float* ob = out + row * heads * d;
+  if (i >= rope_pairs) {
+    for (uint32_t h = 0; h < heads; h++) {
+      const float lo = xb[h * d + i], hi = xb[h * d + pairs_total + i];
+      ob[h * d + i] = lo;
+      ob[h * d + pairs_total + i] = hi;
+    }
+    return;
+  }
+  // Frequency of pair i by repeated f32 multiplies, as the reference builds its table.
+  float f = scale_factor;
+  for (uint32_t j = 0; j < i; j++) f *= step;
+  const float ang = (float)pos[row] * f;
+  double sd, cd;
+  sincos((double)ang, &sd, &cd);
+  const float sn = (float)sd, cs = (float)cd;
+  for (uint32_t h = 0; h < heads; h++) {
+    const float xl = xb[h * d + i], xr = xb[h * d + pairs_total + i];
+    ob[h * d + i] = xl * cs - xr * sn;
+    ob[h * d + pairs_total + i] = xl * sn + xr * cs;
+  }
+}
+
+// ---- cast -----------------------------------------------------------------------------
+__global__ void cast_f32_f16_kernel(__half* __restrict__ out, const float* __restrict__ in, uint64_t n) {
+  for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x)
+    out[i] = __float2half_rn(in[i]);
+}
+__global__ void cast_f16_f32_kernel(float* __restrict__ out, const __half* __restrict__ in, uint64_t n) {
+  for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x)
+    out[i] = __half2float(in[i]);
+}
+
+// ---- SequenceAppend: one block per (request, new step), 2-byte units ---------------------
+__global__ void sequence_append_kernel(uint16_t* __restrict__ cache, const uint16_t* __restrict__ new_kv,
+                                       const int32_t* __restrict__ end_index, uint64_t t_cap, uint64_t row_units,
+                                       uint64_t new_len, int rolling, int* fault) {
+  const uint64_t b = blockIdx.x / new_len, t = blockIdx.x % new_len;
+  const int32_t e = end_index[b];
+  // The whole request is rejected if any of its steps is out of range, like the
+  // reference's check loop before the first write.
+  if (e < 0 || (!rolling && (uint64_t)e + new_len > t_cap)) {
+    if (threadIdx.x == 0) atomicCAS(fault, FAULT_NONE, FAULT_INVALID_ARGUMENT);
+    return;
+  }
+  const uint64_t logical = (uint64_t)e + t;
+  const uint64_t dst = rolling ? logical % t_cap : logical;
+  const uint16_t* src = new_kv + (b * new_len + t) * row_units;
+  uint16_t* dp = cache + (b * t_cap + dst) * row_units;
+  for (uint64_t i = threadIdx.x; i < row_units; i += blockDim.x) dp[i] = src[i];
+}
+
+// ---- GatherRows from a q8_0 table: one block per gathered row --------------------------
+__global__ void gather_rows_q8_kernel(float* __restrict__ out, const uint8_t* __restrict__ table,
+                                      const int32_t* __restrict__ indices, uint64_t table_rows, uint64_t d, int group, int chunk,
+                                      int* fault) {
+  const uint64_t i = blockIdx.x;
+  long long v = indices[i];
+  if (v < 0) v += (long long)table_rows;
+  if (v < 0 || v >= (long long)table_rows) {
+    if (threadIdx.x == 0) atomicCAS(fault, FAULT_NONE, FAULT_INVALID_ARGUMENT);
+    return;
+  }
+  const uint64_t r = (uint64_t)v, blocks = d / QK;
+  const int rg = (int)(r % group);
+  for (uint64_t e = threadIdx.x; e < d; e += blockDim.x) {
+    const uint64_t kb = e / QK;
+    const int t = (int)(e % QK);
+    // QuantBlockOrder addressing (src/aion/backend/types.zig:185-204).
+    const uint8_t* seg = table + ((r / group) * blocks + kb) * (uint64_t)group * Q8_BYTES;
+    const float scale = f16_bits_to_float(*reinterpret_cast<const uint16_t*>(seg + rg * 2));
+    const int8_t q = (int8_t)seg[2 * group + ((uint64_t)(t / chunk) * group + rg) * chunk + (t % chunk)];
+    out[i * d + e] = (float)q * scale;
+  }
+}
+
+// ---- ArgMax: one block per row; first maximum wins ------------------------------------
+__device__ __forceinline__ void argmax_take(float& bv, int& bi, float v, int i) {
+  if (v > bv || (v == bv && i < bi)) {
+    bv = v;
+    bi = i;
+  }
+}
+__global__ void argmax_kernel(int32_t* __restrict__ out, const float* __restrict__ in, uint64_t n) {
+  const float* row = in + blockIdx.x * n;
+  float bv = -INFINITY;
+  int bi = 0x7FFFFFFF;
+  for (uint64_t j = threadIdx.x; j < n; j += blockDim.x) argmax_take(bv, bi, row[j], (int)j);
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xFFFFFFFFu, bv, o);
+    const int oi = __shfl_xor_sync(0xFFFFFFFFu, bi, o);
+    argmax_take(bv, bi, ov, oi);
+  }
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) sv[warp] = bv, si[warp] = bi;
+  __syncthreads();
+  if (warp == 0) {
+    const int nw = blockDim.x >> 5;
+    bv = lane < nw ? sv[lane] : -INFINITY;
+    bi = lane < nw ? si[lane] : 0x7FFFFFFF;
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xFFFFFFFFu, bv, o);
+      const int oi = __shfl_xor_sync(0xFFFFFFFFu, bi, o);
+      argmax_take(bv, bi, ov, oi);
+    }
+    // A NaN in front can never be displaced in the reference's scan; a row of nothing but
+    // NaN (no candidate taken) answers 0 as well.
+    if (lane == 0) out[blockIdx.x] = (isnan(row[0]) || bi == 0x7FFFFFFF) ? 0 : bi;
+  }
+}
+
+unsigned grid_for(const AionCudaDevice* dev, uint64_t n, unsigned threads) {
+  const uint64_t want = ceil_div(n, (uint64_t)threads);
+  const uint64_t cap = (uint64_t)dev->sm_count * 16;
+  return (unsigned)(want < cap ? (want ? want : 1) : cap);
+}
+
+}  // namespace
+}  // namespace aion
+
+using namespace aion;
+
+extern "C" {
+
+int32_t aion_cuda_rms_norm(AionCudaDevice* dev, const AionCudaRMSNorm* s) {
+  if (!dev || !s) return fail(AION_CUDA_INVALID_ARGUMENT, "rms_norm: null argument");
+  if (!(s->eps > 0.0f) || !std::isfinite(s->eps)) return fail(AION_CUDA_INVALID_ARGUMENT, "rms_norm: eps must be finite and > 0");
+  if (s->rows == 0 || s->cols == 0) return AION_CUDA_OK;
+  if (int32_t st = dev->make_current()) return st;
+  const size_t bytes = s->rows * s->cols * sizeof(float);
+  float* out;
+  const float *x, *gamma, *beta, *res = nullptr;
+  if (int32_t st = resolve(s->out, bytes, "rms_norm.out", &out)) return st;
+  if (int32_t st = resolve(s->x, bytes, "rms_norm.x", &x)) return st;
+  if (int32_t st = resolve(s->gamma, s->cols * sizeof(float), "rms_norm.gamma", &gamma)) return st;
+  if (int32_t st = resolve(s->beta, s->cols * sizeof(float), "rms_norm.beta", &beta)) return st;
+  if (s->residual.handle)
+    if (int32_t st = resolve(s->residual, bytes, "rms_norm.residual", &res)) return st;
+  const int warps = 4;
+  rms_norm_kernel<<<(unsigned)ceil_div(s->rows, (uint64_t)warps), warps * 32, 0, dev->stream>>>(out, x, gamma, beta, res, s->rows,
+                                                                                                s->cols, s->eps, dev->fault_dev);
+  AION_CUDA_TRY(cudaGetLastError());
+  return AION_CUDA_OK;
+}
+
+int32_t aion_cuda_elemwise(AionCudaDevice* dev, const AionCudaElemwise* s) {
+  if (!dev || !s) return fail(AION_CUDA_INVALID_ARGUMENT, "elemwise: null argument");
+  if (s->op > AION_CUDA_ELEMWISE_GATE_GELU) return fail(AION_CUDA_INVALID_ARGUMENT, "elemwise: op %u", s->op);
+  if (s->count == 0) return AION_CUDA_OK;
+  if (int32_t st = dev->make_current()) return st;
+  const size_t bytes = s->count * sizeof(float);
+  float* out;
+  const float *a, *b;
+  if (int32_t st = resolve(s->out, bytes, "elemwise.out", &out)) return st;
+  if (int32_t st = resolve(s->a, bytes, "elemwise.a", &a)) return st;
+  if (int32_t st = resolve(s->b, bytes, "elemwise.b", &b)) return st;
+  elemwise_kernel<<<grid_for(dev, s->count, 256), 256, 0, dev->stream>>>(out, a, b, s->count, s->op);
+  AION_CUDA_TRY(cudaGetLastError());
+  return AION_CUDA_OK;
+}
+
+int32_t aion_cuda_rope(AionCudaDevice* dev, const AionCudaRoPE* s) {
+  if (!dev || !s) return fail(AION_CUDA_INVALID_ARGUMENT, "rope: null argument");
+  if (s->head_dim % 2 != 0 || s->head_dim == 0 || s->head_dim > (1u << 20) || s->heads > (1u << 20))
+    return fail(AION_CUDA_INVALID_ARGUMENT, "rope: head_dim = %llu", (unsigned long long)s->head_dim);
+  const uint64_t bl = s->batch * s->len;
+  if (bl == 0 || s->heads == 0) return AION_CUDA_OK;
+  if (int32_t st = dev->make_current()) return st;
+  // src/aion/backend/cpu/exec/rope.zig:43-50
+  const uint64_t pairs_total = s->head_dim / 2;
+  const float pf = std::floor(s->proportion * (float)pairs_total);
+  if (!(pf >= 0.0f)) return fail(AION_CUDA_INVALID_ARGUMENT, "rope: proportion %g", (double)s->proportion);
+  uint64_t rope_pairs = (uint64_t)pf;
+  if (rope_pairs > pairs_total) rope_pairs = pairs_total;
+  const float head_dim_f = (float)s->head_dim;
+  const float step = (float)std::pow((double)s->base_frequency, (double)(-2.0f / head_dim_f));
+  const size_t bytes = bl * s->heads * s->head_dim * sizeof(float);
+  float* out;
+  const float* x;
+  const int32_t* pos;
+  if (int32_t st = resolve(s->out, bytes, "rope.out", &out)) return st;
+  if (int32_t st = resolve(s->x, bytes, "rope.x", &x)) return st;
+  if (int32_t st = resolve(s->positions, bl * sizeof(int32_t), "rope.positions", &pos)) return st;
+  const uint64_t threads = bl * pairs_total;
+  rope_kernel<<<(unsigned)ceil_div(threads, (uint64_t)128), 128, 0, dev->stream>>>(out, x, pos, bl, (uint32_t)s->heads,
+                                                                                   (uint32_t)s->head_dim, (uint32_t)rope_pairs, step,
+                                                                                   s->scale_factor);
+  AION_CUDA_TRY(cudaGetLastError());
+  return AION_CUDA_OK;
+}
+
+int32_t aion_cuda_cast(AionCudaDevice* dev, const AionCudaCast* s) {
+  if (!dev || !s) return fail(AION_CUDA_INVALID_ARGUMENT, "cast: null argument");
+  if (s->count == 0) return AION_CUDA_OK;
+  if (int32_t st = dev->make_current()) return st;
+  if (s->from_dtype == AION_CUDA_DTYPE_F32 && s->to_dtype == AION_CUDA_DTYPE_F16) {
+    __half* out;
+    const float* in;
+    if (int32_t st = resolve(s->out, s->count * 2, "cast.out", &out)) return st;
+    if (int32_t st = resolve(s->in, s->count * 4, "cast.in", &in)) return st;
+    cast_f32_f16_kernel<<<grid_for(dev, s->count, 256), 256, 0, dev->stream>>>(out, in, s->count);
+  } else if (s->from_dtype == AION_CUDA_DTYPE_F16 && s->to_dtype == AION_CUDA_DTYPE_F32) {
+    float* out;
+    const __half* in;
+    if (int32_t st = resolve(s->out, s->count * 4, "cast.out", &out)) return st;
+    if (int32_t st = resolve(s->in, s->count * 2, "cast.in", &in)) return st;
+    cast_f16_f32_kernel<<<grid_for(dev, s->count, 256), 256, 0, dev->stream>>>(out, in, s->count);
+  } else {
+    return fail(AION_CUDA_UNSUPPORTED, "cast: only f32 <-> f16 is covered (got %u -> %u)", s->from_dtype, s->to_dtype);
+  }
+  AION_CUDA_TRY(cudaGetLastError());
+  return AION_CUDA_OK;
+}
+
+int32_t aion_cuda_sequence_append(AionCudaDevice* dev, const AionCudaSequenceAppend* s) {
+  if (!dev || !s) return fail(AION_CUDA_INVALID_ARGUMENT, "sequence_append: null argument");
+  if (s->dtype != AION_CUDA_DTYPE_F16 && s->dtype != AION_CUDA_DTYPE_F32)
+    return fail(AION_CUDA_INVALID_ARGUMENT, "sequence_append: cache dtype %u", s->dtype);
+  if (s->batch == 0 || s->new_len == 0 || s->heads == 0 || s->head_dim == 0) return AION_CUDA_OK;
+  if (s->t_cap == 0) return fail(AION_CUDA_INVALID_ARGUMENT, "sequence_append: empty cache");
+  if (int32_t st = dev->make_current()) return st;
+  const size_t eb = s->dtype == AION_CUDA_DTYPE_F16 ? 2 : 4;
+  const size_t row = s->heads * s->head_dim * eb;
+  uint16_t* cache;
+  const uint16_t* nk;
+  const int32_t* idx;
+  if (int32_t st = resolve(s->cache, s->batch * s->t_cap * row, "sequence_append.cache", &cache)) return st;
+  if (int32_t st = resolve(s->new_kv, s->batch * s->new_len * row, "sequence_append.new_kv", &nk)) return st;
+  if (int32_t st = resolve(s->end_index, s->batch * sizeof(int32_t), "sequence_append.end_index", &idx)) return st;
+  if (s->batch * s->new_len > 0x7FFFFFFFull) return fail(AION_CUDA_UNSUPPORTED, "sequence_append: too many rows for one launch");
+  sequence_append_kernel<<<(unsigned)(s->batch * s->new_len), 128, 0, dev->stream>>>(cache, nk, idx, s->t_cap, row / 2, s->new_len,
+                                                                                      s->rolling ? 1 : 0, dev->fault_dev);
+  AION_CUDA_TRY(cudaGetLastError());
+  return AION_CUDA_OK;
+}
+
+int32_t aion_cuda_gather_rows(AionCudaDevice* dev, const AionCudaGatherRows* s) {
+  if (!dev || !s) return fail(AION_CUDA_INVALID_ARGUMENT, "gather_rows: null argument");
+  if (s->d % QK != 0) return fail(AION_CUDA_INVALID_ARGUMENT, "gather_rows: d = %llu is not a multiple of 32", (unsigned long long)s->d);
+  int group = 1, chunk = 4;
+  if (!block_order_info(s->block_order, &group, &chunk)) return fail(AION_CUDA_INVALID_ARGUMENT, "gather_rows: unknown block order %u", s->block_order);
+  if (s->table_rows % (uint64_t)group != 0)
+    return fail(AION_CUDA_INVALID_ARGUMENT, "gather_rows: %llu rows is not a multiple of the order's group of %d",
+                (unsigned long long)s->table_rows, group);
+  if (s->count == 0 || s->d == 0) return AION_CUDA_OK;
+  if (int32_t st = dev->make_current()) return st;
+  float* out;
+  const uint8_t* table;
+  const int32_t* idx;
+  if (int32_t st = resolve(s->out, s->count * s->d * sizeof(float), "gather_rows.out", &out)) return st;
+  if (int32_t st = resolve(s->table, s->table_rows * (s->d / QK) * Q8_BYTES, "gather_rows.table", &table)) return st;
+  if (int32_t st = resolve(s->indices, s->count * sizeof(int32_t), "gather_rows.indices", &idx)) return st;
+  if (s->count > 0x7FFFFFFFull) return fail(AION_CUDA_UNSUPPORTED, "gather_rows: too many rows for one launch");
+  gather_rows_q8_kernel<<<(unsigned)s->count, 256, 0, dev->stream>>>(out, table, idx, s->table_rows, s->d, group, chunk,
+                                                                     dev->fault_dev);
+  AION_CUDA_TRY(cudaGetLastError());
+  return AION_CUDA_OK;
+}
+
+int32_t aion_cuda_argmax(AionCudaDevice* dev, const AionCudaArgMax* s) {
+  if (!dev || !s) return fail(AION_CUDA_INVALID_ARGUMENT, "argmax: null argument");
+  if (s->n == 0 || s->n > 0x7FFFFFFEull) return fail(AION_CUDA_INVALID_ARGUMENT, "argmax: n = %llu", (unsigned long long)s->n);
+  if (s->outer == 0) return AION_CUDA_OK;
+  if (int32_t st = dev->make_current()) return st;
+  int32_t* out;
+  const float* in;
+  if (int32_t st = resolve(s->out, s->outer * sizeof(int32_t), "argmax.out", &out)) return st;
+  if (int32_t st = resolve(s->in, s->outer * s->n * sizeof(float), "argmax.in", &in)) return st;
+  if (s->outer > 0x7FFFFFFFull) return fail(AION_CUDA_UNSUPPORTED, "argmax: too many rows for one launch");
+  argmax_kernel<<<(unsigned)s->outer, 1024, 0, dev->stream>>>(out, in, s->n);
+  AION_CUDA_TRY(cudaGetLastError());
+  return AION_CUDA_OK;
+}
+
+}  // extern "C"

@@ -261,6 +261,95 @@ typedef struct AionCudaAttention {
 AION_CUDA_API int32_t aion_cuda_attention(AionCudaDevice* dev, const AionCudaAttention* step);
 
 /* ---------------------------------------------------------------------------------
+ * Decoder glue steps: the ops on either side of the matmul / attention path in a decode
+ * program, so a whole token step stays on the device. All f32 unless stated.
+ * --------------------------------------------------------------------------------- */
+
+/* `RMSNorm` step with optional residual: `StepRMSNorm` executed by `execRMSNorm`
+ * (aion src/aion/backend/cpu/exec/layernorm.zig:41-154).
+ *   out[r, :] = (x[r, :] * inv_r) * gamma + beta (+ residual[r, :]),
+ *   inv_r = 1 / sqrt(mean(x[r, :]^2) + eps); eps must be finite and > 0.
+ * residual.handle == 0: absent. out may alias x or residual. */
+typedef struct AionCudaRMSNorm {
+  AionCudaOperand out, x, gamma, beta, residual;
+  uint64_t rows, cols;
+  float eps;
+  uint32_t reserved;
+} AionCudaRMSNorm;
+AION_CUDA_API int32_t aion_cuda_rms_norm(AionCudaDevice* dev, const AionCudaRMSNorm* step);
+
+/* `ElemwiseBinary` step over identical shapes (aion
+ * src/aion/backend/cpu/exec/elementwise.zig:18-45): add, mul, and `gate` = gelu(a) * b with
+ * the tanh-form GELU over the reference's tanhApprox (aion
+ * src/aion/backend/cpu/kernels/gelu.zig:8-14). out may alias a or b. */
+#define AION_CUDA_ELEMWISE_ADD 0u
+#define AION_CUDA_ELEMWISE_MUL 1u
+#define AION_CUDA_ELEMWISE_GATE_GELU 2u
+typedef struct AionCudaElemwise {
+  AionCudaOperand out, a, b;
+  uint64_t count;
+  uint32_t op;
+  uint32_t reserved;
+} AionCudaElemwise;
+AION_CUDA_API int32_t aion_cuda_elemwise(AionCudaDevice* dev, const AionCudaElemwise* step);
+
+/* `RoPE1D` step: x, out [B, L, H, D] f32, positions i32 [B, L]; pair i of a head is
+ * (x[i], x[D/2 + i]); the first floor(proportion * D/2) pairs rotate, the rest copy
+ * (aion src/aion/backend/cpu/exec/rope.zig:43-50, src/aion/backend/cpu/kernels/rope.zig:20-97).
+ * out may alias x. */
+typedef struct AionCudaRoPE {
+  AionCudaOperand out, x, positions;
+  uint64_t batch, len, heads, head_dim;
+  float base_frequency, scale_factor, proportion;
+  uint32_t reserved;
+} AionCudaRoPE;
+AION_CUDA_API int32_t aion_cuda_rope(AionCudaDevice* dev, const AionCudaRoPE* step);
+
+/* `Cast` step, f32 -> f16 (round to nearest even) or f16 -> f32 (aion
+ * src/aion/backend/cpu/exec/cast.zig:60-90). */
+typedef struct AionCudaCast {
+  AionCudaOperand out, in;
+  uint64_t count;
+  uint32_t from_dtype, to_dtype; /* AION_CUDA_DTYPE_F32 / AION_CUDA_DTYPE_F16 */
+} AionCudaCast;
+AION_CUDA_API int32_t aion_cuda_cast(AionCudaDevice* dev, const AionCudaCast* step);
+
+/* `SequenceAppend` step: writes new_kv [B, Ln, H, D] into cache [B, T, H, D] (same dtype,
+ * f16 or f32) at logical steps end_index[b] + t (aion
+ * src/aion/backend/cpu/exec/sequence_append.zig:12-104). rolling = 0: a step >= T is an
+ * error; rolling = 1: the step lands in row step % T. A negative index or an out-of-range
+ * step is detected on the device, nothing of that request is written, and the next
+ * aion_cuda_sync / aion_cuda_d2h reports INVALID_ARGUMENT. */
+typedef struct AionCudaSequenceAppend {
+  AionCudaOperand cache, new_kv, end_index;
+  uint64_t batch, t_cap, heads, head_dim, new_len;
+  uint32_t dtype;
+  uint32_t rolling;
+} AionCudaSequenceAppend;
+AION_CUDA_API int32_t aion_cuda_sequence_append(AionCudaDevice* dev, const AionCudaSequenceAppend* step);
+
+/* `GatherRows` step from a q8_0 [table_rows, d] table (quant_axis 1, any block order) to
+ * f32 [count, d] (aion src/aion/backend/cpu/exec/gather.zig:22-28, 57-87). Indices follow
+ * the ONNX rule: [-table_rows, table_rows - 1], negative counts from the end; anything else
+ * is reported like SequenceAppend's range error. */
+typedef struct AionCudaGatherRows {
+  AionCudaOperand out, table, indices;
+  uint64_t table_rows, d, count;
+  uint32_t block_order;
+  uint32_t reserved;
+} AionCudaGatherRows;
+AION_CUDA_API int32_t aion_cuda_gather_rows(AionCudaDevice* dev, const AionCudaGatherRows* step);
+
+/* `ArgMax` step over the last axis of f32 [outer, n] -> i32 [outer]; the first maximum
+ * wins, a NaN never beats a number, a row whose first element is NaN answers 0 (aion
+ * src/aion/backend/cpu/exec/argmax.zig:56-82). */
+typedef struct AionCudaArgMax {
+  AionCudaOperand out, in;
+  uint64_t outer, n;
+} AionCudaArgMax;
+AION_CUDA_API int32_t aion_cuda_argmax(AionCudaDevice* dev, const AionCudaArgMax* step);
+
+/* ---------------------------------------------------------------------------------
  * Block quantizer on the device. `quantizeBlocks` (aion src/aion/storage/quantize.zig:31-103)
  * for q8_0; for q4_0 the reference's only q4 packer (aion
  * src/aion/backend/cpu/test_cpu_kernels.zig:490-523) under the same placement rule.

@@ -186,3 +186,78 @@ def fast_matmul_nt_q8(a, b, m, n, k, *, alpha=1.0, beta=0.0, c=None, threads=0):
                                              C.c_float(beta), _p(c), _p(a), _p(b), threads)
     _check(rc, "fast_matmul_nt_q8")
     return c.reshape(m, n)
+
+
+# ---- decoder glue steps -----------------------------------------------------------------
+ELEMWISE_ADD, ELEMWISE_MUL, ELEMWISE_GATE_GELU = 0, 1, 2
+
+
+def rms_norm(x, gamma, beta, eps, residual=None):
+    """RMSNorm over the last axis (+ optional residual added after normalization)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    cols = x.shape[-1]
+    rows = x.size // cols
+    g = np.ascontiguousarray(gamma, dtype=np.float32)
+    b = np.ascontiguousarray(beta, dtype=np.float32)
+    r = None if residual is None else np.ascontiguousarray(residual, dtype=np.float32)
+    out = np.empty_like(x)
+    _check(lib().aion_oracle_rms_norm(_p(out), _p(x), _p(g), _p(b), _p(r), C.c_uint64(rows), C.c_uint64(cols), C.c_float(eps)),
+           "rms_norm")
+    return out
+
+
+def elemwise(op: int, a, b):
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    b = np.ascontiguousarray(b, dtype=np.float32)
+    out = np.empty_like(a)
+    _check(lib().aion_oracle_elemwise(op, _p(out), _p(a), _p(b), C.c_uint64(a.size)), "elemwise")
+    return out
+
+
+def rope(x, positions, base_frequency, scale_factor=1.0, proportion=1.0):
+    """RoPE1D over x [B, L, H, D] f32 with positions [B, L] i32."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    pos = np.ascontiguousarray(positions, dtype=np.int32)
+    B, L, H, D = x.shape
+    out = np.empty_like(x)
+    _check(lib().aion_oracle_rope(_p(out), _p(x), _p(pos), C.c_uint64(B), C.c_uint64(L), C.c_uint64(H), C.c_uint64(D),
+                                  C.c_float(base_frequency), C.c_float(scale_factor), C.c_float(proportion)), "rope")
+    return out
+
+
+def cast_f32_f16(x):
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    out = np.empty(x.shape, dtype=np.uint16)
+    _check(lib().aion_oracle_cast_f32_f16(_p(out), _p(x), C.c_uint64(x.size)), "cast")
+    return out.view(np.float16)
+
+
+def sequence_append(cache, new_kv, end_index, rolling=False):
+    """Returns a copy of cache [B, T, H, D] with new_kv [B, Ln, H, D] written at end_index[b] + t."""
+    cache = np.ascontiguousarray(cache).copy()
+    new_kv = np.ascontiguousarray(new_kv, dtype=cache.dtype)
+    idx = np.ascontiguousarray(end_index, dtype=np.int32)
+    B, T, H, D = cache.shape
+    _check(lib().aion_oracle_sequence_append(_p(cache), _p(new_kv), _p(idx), C.c_uint64(cache.itemsize), C.c_uint64(B),
+                                             C.c_uint64(T), C.c_uint64(H), C.c_uint64(D), C.c_uint64(new_kv.shape[1]),
+                                             int(rolling)), "sequence_append")
+    return cache
+
+
+def gather_rows_q8(table, table_rows, d, indices, order="row_major"):
+    table = np.ascontiguousarray(table, dtype=np.uint8)
+    idx = np.ascontiguousarray(indices, dtype=np.int32)
+    out = np.empty((idx.size, d), dtype=np.float32)
+    o = ORDERS[order] if isinstance(order, str) else int(order)
+    _check(lib().aion_oracle_gather_rows_q8(_p(out), _p(table), o, C.c_uint64(table_rows), C.c_uint64(d), _p(idx),
+                                            C.c_uint64(idx.size)), "gather_rows_q8")
+    return out
+
+
+def argmax(x):
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    n = x.shape[-1]
+    outer = x.size // n
+    out = np.empty(outer, dtype=np.int32)
+    _check(lib().aion_oracle_argmax(_p(out), _p(x), C.c_uint64(outer), C.c_uint64(n)), "argmax")
+    return out.reshape(x.shape[:-1])

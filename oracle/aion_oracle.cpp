@@ -714,3 +714,162 @@ ORC_API int aion_oracle_attention(float* out, const void* q, int q_dtype, const 
   }
   return kOk;
 }
+
+// =================================================================================
+// Decoder glue steps (the ops either side of the matmul / attention path).
+// =================================================================================
+
+// RMSNorm with optional residual: src/aion/backend/cpu/exec/layernorm.zig:41-154 and
+// src/aion/backend/cpu/kernels/layernorm.zig:7-107. Sum of squares in 16 lane partials
+// (the f32 vector width of a 512-bit host) reduced pairwise, tail added serially;
+// inv = 1 / sqrt(mean(x^2) + eps); out = (x * inv) * gamma + beta, then + residual.
+ORC_API int aion_oracle_rms_norm(float* out, const float* x, const float* gamma, const float* beta, const float* residual,
+                                 uint64_t rows, uint64_t cols, float eps) {
+  if (!(eps > 0.0f) || !std::isfinite(eps) || cols == 0) return kInvalid;
+  const size_t lanes = 16;
+  const float inv_denom = 1.0f / static_cast<float>(cols);
+  for (uint64_t r = 0; r < rows; r++) {
+    const float* xr = x + r * cols;
+    float part[16] = {0};
+    size_t c = 0;
+    const size_t vec_end = cols - (cols % lanes);
+    for (; c < vec_end; c += lanes)
+      for (size_t l = 0; l < lanes; l++) part[l] += xr[c + l] * xr[c + l];
+    for (size_t w = lanes / 2; w > 0; w /= 2)
+      for (size_t l = 0; l < w; l++) part[l] += part[l + w];
+    float sq = part[0];
+    for (; c < cols; c++) sq += xr[c] * xr[c];
+    const float d = sq * inv_denom + eps;
+    if (!(d > 0.0f) || !std::isfinite(d)) return kInvalid;
+    const float inv = 1.0f / std::sqrt(d);
+    for (size_t j = 0; j < cols; j++) {
+      float v = ((xr[j] * inv) * gamma[j]) + beta[j];
+      if (residual) v = v + residual[r * cols + j];
+      out[r * cols + j] = v;
+    }
+  }
+  return kOk;
+}
+
+// GELU (tanh form over tanhApprox): src/aion/backend/cpu/kernels/gelu.zig:8-14.
+inline float gelu_approx(float x) {
+  const float c = 0.044715f, k = 0.7978845608028654f;
+  const float x3 = x * x * x;
+  const float t = k * (x + c * x3);
+  return 0.5f * x * (1.0f + tanh_approx(t));
+}
+// op 0: a + b, 1: a * b, 2: gate = gelu(a) * b (src/aion/backend/cpu/exec/elementwise.zig:25-36).
+ORC_API int aion_oracle_elemwise(int op, float* out, const float* a, const float* b, uint64_t n) {
+  for (uint64_t i = 0; i < n; i++) {
+    switch (op) {
+      case 0: out[i] = a[i] + b[i]; break;
+      case 1: out[i] = a[i] * b[i]; break;
+      case 2: out[i] = gelu_approx(a[i]) * b[i]; break;
+      default: return kInvalid;
+    }
+  }
+  return kOk;
+}
+
+// RoPE1D over [B, L, H, D] f32 with positions i32 [B, L]:
+// src/aion/backend/cpu/exec/rope.zig:43-50 and src/aion/backend/cpu/kernels/rope.zig:20-97.
+// Pair i is (x[i], x[D/2 + i]); its frequency is scale * step^i by repeated f32 multiplies,
+// step = f32(base^(-2/D)) computed in f64; sin / cos in f64 of the f32 angle.
+ORC_API int aion_oracle_rope(float* out, const float* x, const int32_t* pos, uint64_t b, uint64_t l, uint64_t h, uint64_t d,
+                             float base_frequency, float scale_factor, float proportion) {
+  if (d % 2 != 0) return kInvalid;
+  const size_t pairs_total = d / 2;
+  const float pf = std::floor(proportion * static_cast<float>(pairs_total));
+  if (pf < 0.0f) return kInvalid;
+  size_t rope_pairs = static_cast<size_t>(pf);
+  if (rope_pairs > pairs_total) rope_pairs = pairs_total;
+  const float head_dim_f = static_cast<float>(d);
+  const float step = static_cast<float>(std::pow(static_cast<double>(base_frequency), static_cast<double>(-2.0f / head_dim_f)));
+  for (uint64_t bl = 0; bl < b * l; bl++) {
+    const float p = static_cast<float>(pos[bl]);
+    for (uint64_t hh = 0; hh < h; hh++) {
+      const float* xr = x + (bl * h + hh) * d;
+      float* orow = out + (bl * h + hh) * d;
+      std::memcpy(orow, xr, d * sizeof(float));
+      float f = scale_factor;
+      for (size_t i = 0; i < rope_pairs; i++) {
+        const float ang = p * f;
+        const float sn = static_cast<float>(std::sin(static_cast<double>(ang)));
+        const float cs = static_cast<float>(std::cos(static_cast<double>(ang)));
+        const float xl = xr[i], xrr = xr[pairs_total + i];
+        orow[i] = xl * cs - xrr * sn;
+        orow[pairs_total + i] = xl * sn + xrr * cs;
+        f *= step;
+      }
+    }
+  }
+  return kOk;
+}
+
+// Cast f32 -> f16 (round to nearest even), src/aion/backend/cpu/exec/cast.zig:67-76.
+ORC_API int aion_oracle_cast_f32_f16(uint16_t* out, const float* in, uint64_t n) {
+  for (uint64_t i = 0; i < n; i++) out[i] = f32_to_f16_bits(in[i]);
+  return kOk;
+}
+
+// SequenceAppend into a [B, T, H, D] cache at logical step end_index[b] + t:
+// src/aion/backend/cpu/exec/sequence_append.zig:12-104. A plain cache maps a logical step
+// to itself and rejects steps beyond T; a rolling cache maps it to step % T.
+ORC_API int aion_oracle_sequence_append(uint8_t* cache, const uint8_t* new_kv, const int32_t* end_index, uint64_t elem_bytes,
+                                        uint64_t b, uint64_t t_cap, uint64_t h, uint64_t d, uint64_t new_len, int rolling) {
+  const size_t row = h * d * elem_bytes;
+  for (uint64_t bb = 0; bb < b; bb++) {
+    if (end_index[bb] < 0) return kInvalid;
+    for (uint64_t t = 0; t < new_len; t++) {
+      const uint64_t logical = static_cast<uint64_t>(end_index[bb]) + t;
+      if (!rolling && logical >= t_cap) return kInvalid;
+    }
+  }
+  for (uint64_t bb = 0; bb < b; bb++)
+    for (uint64_t t = 0; t < new_len; t++) {
+      const uint64_t logical = static_cast<uint64_t>(end_index[bb]) + t;
+      const uint64_t dst = rolling ? logical % t_cap : logical;
+      std::memcpy(cache + (bb * t_cap + dst) * row, new_kv + (bb * new_len + t) * row, row);
+    }
+  return kOk;
+}
+
+// GatherRows from a q8_0 [rows, d] table (quant_axis 1, any block order) to f32:
+// src/aion/backend/cpu/exec/gather.zig:22-28, 57-87. Index in [-rows, rows-1].
+ORC_API int aion_oracle_gather_rows_q8(float* out, const uint8_t* table, int order, uint64_t table_rows, uint64_t d,
+                                       const int32_t* indices, uint64_t count) {
+  BlockOrder o;
+  if (!order_info(order, &o) || d % QK != 0) return kInvalid;
+  const size_t blocks = d / QK;
+  for (uint64_t i = 0; i < count; i++) {
+    int64_t v = indices[i];
+    if (v < 0) v += static_cast<int64_t>(table_rows);
+    if (v < 0 || v >= static_cast<int64_t>(table_rows)) return kInvalid;
+    for (size_t kb = 0; kb < blocks; kb++) {
+      uint8_t block[Q8_BYTES];
+      load_block(o, table, blocks, static_cast<size_t>(v), kb, block);
+      uint16_t sb;
+      std::memcpy(&sb, block, 2);
+      const float scale = f16_bits_to_f32(sb);
+      for (int t = 0; t < 32; t++) out[i * d + kb * QK + t] = static_cast<float>(static_cast<int8_t>(block[2 + t])) * scale;
+    }
+  }
+  return kOk;
+}
+
+// ArgMax over the last axis, first maximum wins: src/aion/backend/cpu/exec/argmax.zig:56-82.
+ORC_API int aion_oracle_argmax(int32_t* out, const float* in, uint64_t outer, uint64_t n) {
+  if (n == 0) return kInvalid;
+  for (uint64_t o = 0; o < outer; o++) {
+    const float* row = in + o * n;
+    size_t best_i = 0;
+    float best_v = row[0];
+    for (size_t j = 1; j < n; j++)
+      if (row[j] > best_v) {
+        best_v = row[j];
+        best_i = j;
+      }
+    out[o] = static_cast<int32_t>(best_i);
+  }
+  return kOk;
+}

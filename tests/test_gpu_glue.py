@@ -1,0 +1,160 @@
+"""Decoder glue steps: the CUDA kernels through `CudaSession` (C ABI) against the oracle.
+
+Elementwise, cast, append, gather and argmax are integer / per-element work: bit-exact.
+RMSNorm sums a row in a different order than the CPU's vector lanes: rel 1e-5. RoPE's
+sin / cos come from the device's f64 sincos instead of the host libm: abs 1e-6."""
+import numpy as np
+import pytest
+
+import oracle
+from aion_b200 import capi
+from aion_b200.backend import (BackendError, DeviceStore, StepArgMax, StepCast, StepElemwiseBinary, StepGatherRows,
+                               StepRMSNorm, StepRoPE1D, StepSequenceAppend, TensorMeta)
+
+pytestmark = pytest.mark.gpu
+
+F32, F16, I32, Q8 = capi.DTYPE_F32, capi.DTYPE_F16, capi.DTYPE_I32, capi.DTYPE_Q8_0
+
+
+@pytest.fixture()
+def sess(backend):
+    store = DeviceStore(backend.device_memory)
+    s = backend.create_session(store)
+    yield s, store
+    store.deinit()
+
+
+def put(store, arr, dtype):
+    return store.add(TensorMeta(dtype, tuple(arr.shape)), arr)
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 1536), (7, 256), (64, 1536), (3, 100), (520, 32)])
+@pytest.mark.parametrize("with_res", [False, True])
+def test_rms_norm(sess, rows, cols, with_res):
+    s, store = sess
+    rng = np.random.default_rng(rows * 1000 + cols)
+    x = rng.standard_normal((rows, cols)).astype(np.float32)
+    g = rng.standard_normal(cols).astype(np.float32)
+    b = rng.standard_normal(cols).astype(np.float32)
+    res = rng.standard_normal((rows, cols)).astype(np.float32) if with_res else None
+    tx, tg, tb = put(store, x, F32), put(store, g, F32), put(store, b, F32)
+    tr = put(store, res, F32) if with_res else None
+    to = store.add(TensorMeta(F32, (rows, cols)))
+    s.execute([StepRMSNorm(out=to, x=tx, gamma=tg, beta=tb, eps=1e-6, residual=tr)])
+    np.testing.assert_allclose(store.read(to), oracle.rms_norm(x, g, b, 1e-6, residual=res), rtol=1e-5, atol=1e-6)
+
+
+def test_rms_norm_in_place_and_bad_eps(sess):
+    s, store = sess
+    x = np.random.default_rng(0).standard_normal((4, 8, 256)).astype(np.float32)
+    g, b = np.ones(256, np.float32), np.zeros(256, np.float32)
+    tx, tg, tb = put(store, x, F32), put(store, g, F32), put(store, b, F32)
+    s.execute([StepRMSNorm(out=tx, x=tx, gamma=tg, beta=tb, eps=1e-6)])
+    np.testing.assert_allclose(store.read(tx), oracle.rms_norm(x, g, b, 1e-6), rtol=1e-5, atol=1e-6)
+    with pytest.raises(BackendError):
+        s.execute([StepRMSNorm(out=tx, x=tx, gamma=tg, beta=tb, eps=0.0)])
+
+
+@pytest.mark.parametrize("op,code", [("add", 0), ("mul", 1), ("gate", 2)])
+def test_elemwise_bit_exact(sess, op, code):
+    s, store = sess
+    rng = np.random.default_rng(code)
+    a = (rng.standard_normal(70001) * 4).astype(np.float32)
+    b = rng.standard_normal(70001).astype(np.float32)
+    a[:8] = [0.0, -0.0, 50.0, -50.0, 1e-30, 9.99, -9.99, 100.0]
+    ta, tb = put(store, a, F32), put(store, b, F32)
+    to = store.add(TensorMeta(F32, a.shape))
+    s.execute([StepElemwiseBinary(op=op, out=to, a=ta, b=tb)])
+    assert np.array_equal(store.read(to), oracle.elemwise(code, a, b))
+
+
+@pytest.mark.parametrize("shape,prop", [((2, 1, 8, 256), 1.0), ((3, 5, 1, 64), 1.0), ((1, 2, 4, 128), 0.25)])
+def test_rope(sess, shape, prop):
+    s, store = sess
+    rng = np.random.default_rng(4)
+    x = rng.standard_normal(shape).astype(np.float32)
+    pos = rng.integers(0, 4096, size=shape[:2]).astype(np.int32)
+    pos.flat[0] = 2047
+    tx, tp = put(store, x, F32), put(store, pos, I32)
+    to = store.add(TensorMeta(F32, shape))
+    s.execute([StepRoPE1D(out=to, x=tx, positions=tp, base_frequency=10000.0, rope_proportion=prop)])
+    np.testing.assert_allclose(store.read(to), oracle.rope(x, pos, 10000.0, proportion=prop), rtol=0, atol=1e-6)
+
+
+def test_cast_both_ways_bit_exact(sess):
+    s, store = sess
+    x = (np.random.default_rng(5).standard_normal(5000) * 100).astype(np.float32)
+    x[:6] = [1.00048828125, 65504.0, 1e-8, -2.5, 6.1e-5, 3.0e-8]
+    tx = put(store, x, F32)
+    th = store.add(TensorMeta(F16, x.shape))
+    tb = store.add(TensorMeta(F32, x.shape))
+    s.execute([StepCast(out=th, x=tx, to_dtype=F16), StepCast(out=tb, x=th, to_dtype=F32)])
+    want = oracle.cast_f32_f16(x)
+    assert np.array_equal(store.read(th).view(np.uint16), want.view(np.uint16))
+    assert np.array_equal(store.read(tb), want.astype(np.float32))
+
+
+@pytest.mark.parametrize("rolling", [False, True])
+def test_sequence_append(sess, rolling):
+    s, store = sess
+    rng = np.random.default_rng(6)
+    cache = rng.standard_normal((3, 16, 1, 256)).astype(np.float16)
+    new = rng.standard_normal((3, 2, 1, 256)).astype(np.float16)
+    idx = np.array([0, 14, 37 if rolling else 5], dtype=np.int32)
+    tc = store.add(TensorMeta(F16, cache.shape, cache_policy="rolling" if rolling else "none"), cache)
+    tn, ti = put(store, new, F16), put(store, idx, I32)
+    s.execute([StepSequenceAppend(cache=tc, new_kv=tn, end_index=ti)])
+    assert np.array_equal(store.read(tc).view(np.uint16), oracle.sequence_append(cache, new, idx, rolling=rolling).view(np.uint16))
+
+
+def test_sequence_append_out_of_range_is_reported(sess, backend):
+    s, store = sess
+    cache = np.zeros((2, 8, 1, 64), dtype=np.float16)
+    new = np.ones((2, 1, 1, 64), dtype=np.float16)
+    tc, tn = put(store, cache, F16), put(store, new, F16)
+    ti = put(store, np.array([3, 8], dtype=np.int32), I32)
+    s.execute([StepSequenceAppend(cache=tc, new_kv=tn, end_index=ti)])
+    with pytest.raises(BackendError):
+        backend.sync()
+    got = store.read(tc)
+    assert got[0, 3].sum() == 64 and got[1].sum() == 0   # the valid request was written, the bad one untouched
+
+
+@pytest.mark.parametrize("order", [capi.ORDER_ROW_MAJOR, capi.ORDER_LANES8, capi.ORDER_LANES32X16])
+def test_gather_rows_q8(sess, backend, order):
+    s, store = sess
+    rng = np.random.default_rng(7)
+    V, D = 128, 1536
+    w = rng.standard_normal((V, D)).astype(np.float32)
+    table = oracle.relayout_q8(order, V, D, oracle.quantize(oracle.Q8_0, w, 1))
+    idx = np.array([[0, 127, -1], [-128, 5, 64]], dtype=np.int32)
+    tt = store.add(TensorMeta(Q8, (V, D), quant_axis=1, block_order=order), table)
+    ti = put(store, idx, I32)
+    to = store.add(TensorMeta(F32, (2, 3, D)))
+    s.execute([StepGatherRows(out=to, table=tt, indices=ti)])
+    assert np.array_equal(store.read(to).reshape(6, D), oracle.gather_rows_q8(table, V, D, idx, order=order))
+    store.write(ti, np.array([[0, 128, 0], [0, 0, 0]], dtype=np.int32))
+    s.execute([StepGatherRows(out=to, table=tt, indices=ti)])
+    with pytest.raises(BackendError):
+        backend.sync()
+
+
+def test_argmax(sess):
+    s, store = sess
+    rng = np.random.default_rng(8)
+    x = rng.standard_normal((9, 262144)).astype(np.float32)
+    x[0, 100] = x[0, 200000] = 9.0           # tie: the first wins
+    x[1, 0] = np.nan                         # NaN in front answers 0
+    x[2, 5] = np.nan
+    x[2, 262143] = 11.0                      # NaN elsewhere is skipped
+    x[3, :] = -np.inf
+    ta = put(store, x, F32)
+    to = store.add(TensorMeta(I32, (9,)))
+    s.execute([StepArgMax(out=to, a=ta)])
+    got = store.read(to)
+    assert np.array_equal(got, oracle.argmax(x))
+    assert got[0] == 100 and got[1] == 0 and got[2] == 262143 and got[3] == 0
+    small = rng.standard_normal((5, 7)).astype(np.float32)
+    ts, t2 = put(store, small, F32), store.add(TensorMeta(I32, (5,)))
+    s.execute([StepArgMax(out=t2, a=ts)])
+    assert np.array_equal(store.read(t2), oracle.argmax(small))

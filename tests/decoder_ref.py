@@ -1,0 +1,52 @@
+"""The synthetic decoder's token step composed from oracle ops on the CPU (test helper).
+
+Mirrors aion_b200.decoder.SyntheticDecoder._build_steps op for op; state (KV caches) is kept
+in numpy arrays."""
+import numpy as np
+
+import oracle
+
+
+class OracleDecoder:
+    def __init__(self, cfg, requests, weights_f32, embedding_f32):
+        self.cfg, self.R = cfg, requests
+        dt = oracle.Q4_0 if cfg.weight_dtype == 3 else oracle.Q8_0
+        self.dt = dt
+        self.w = {name: oracle.quantize(dt, v, 0) for name, v in weights_f32.items()}
+        self.embed = oracle.quantize(oracle.Q8_0, embedding_f32, 1)
+        shape = (requests, cfg.ctx, cfg.kv_heads, cfg.head_dim)
+        self.k_cache = [np.zeros(shape, np.float16) for _ in range(cfg.layers)]
+        self.v_cache = [np.zeros(shape, np.float16) for _ in range(cfg.layers)]
+        self.gamma, self.beta = np.ones(cfg.hidden, np.float32), np.zeros(cfg.hidden, np.float32)
+
+    def _mm(self, a, name, k, n):
+        m = a.size // k
+        return oracle.matmul_q(self.dt, a.reshape(m, k), self.w[name], m, n, k).reshape(m, n)
+
+    def step(self, tokens, positions):
+        cfg, R = self.cfg, self.R
+        pos = np.asarray(positions, np.int32).reshape(R, 1)
+        rms = lambda v, res=None: oracle.rms_norm(v, self.gamma, self.beta, cfg.eps, residual=res)
+        x = oracle.gather_rows_q8(self.embed, cfg.vocab, cfg.hidden, np.asarray(tokens, np.int32)).reshape(R, cfg.hidden)
+        for l in range(cfg.layers):
+            xn = rms(x)
+            q = self._mm(xn, f"l{l}.wq", cfg.hidden, cfg.q_width).reshape(R, 1, cfg.heads, cfg.head_dim)
+            k = self._mm(xn, f"l{l}.wk", cfg.hidden, cfg.kv_width).reshape(R, 1, cfg.kv_heads, cfg.head_dim)
+            v = self._mm(xn, f"l{l}.wv", cfg.hidden, cfg.kv_width).reshape(R, 1, cfg.kv_heads, cfg.head_dim)
+            q = oracle.rope(q, pos, cfg.rope_base)
+            k = oracle.rope(k, pos, cfg.rope_base)
+            self.k_cache[l] = oracle.sequence_append(self.k_cache[l], oracle.cast_f32_f16(k), pos.reshape(R))
+            self.v_cache[l] = oracle.sequence_append(self.v_cache[l], oracle.cast_f32_f16(v), pos.reshape(R))
+            a = oracle.attention(q, self.k_cache[l], self.v_cache[l], scale=1.0 / np.sqrt(cfg.head_dim), positions=pos,
+                                 kv_lengths=(pos.reshape(R) + 1).astype(np.int32), right=0)
+            o = self._mm(a.reshape(R, cfg.q_width), f"l{l}.wo", cfg.q_width, cfg.hidden)
+            x = rms(o, res=x)
+            h = rms(x)
+            gate = self._mm(h, f"l{l}.wg", cfg.hidden, cfg.ffn)
+            up = self._mm(h, f"l{l}.wu", cfg.hidden, cfg.ffn)
+            act = oracle.elemwise(oracle.ELEMWISE_GATE_GELU, gate, up)
+            down = self._mm(act, f"l{l}.wd", cfg.ffn, cfg.hidden)
+            x = rms(down, res=x)
+        xf = rms(x)
+        logits = self._mm(xf, "head", cfg.hidden, cfg.vocab)
+        return x, logits, oracle.argmax(logits)

@@ -1,0 +1,304 @@
+"""Timed legs beyond the headline GEMV pass: the synthetic decoder (tokens/s), the prefill
+GEMM (TFLOP/s), decode attention (GB/s) and the column-split large layer with its NCCL
+all-gather. `bench.py` calls these; each returns a plain dict for its JSON line.
+
+torch is used for what it is here for: device RNG for synthetic inputs, CUDA events on the
+library's stream, and `torch.distributed` (NCCL) between ranks. All measured work runs in
+libaion_cuda through the C ABI.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import time
+
+import numpy as np
+
+from . import capi
+from .backend import BackendError, Chunk, CudaBackend
+from .decoder import DecoderConfig, SyntheticDecoder
+
+
+def _chk(st):
+    if st != capi.OK:
+        raise BackendError(st, capi.last_error())
+
+
+class _DevArray:
+    """Exposes a device allocation of the library to torch (zero copy) as a flat array."""
+
+    def __init__(self, handle: int, nbytes: int, typestr: str, itemsize: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes // itemsize,), "typestr": typestr, "data": (handle, False),
+                                         "version": 2}
+
+
+def _events(torch, backend, local_rank):
+    stream = torch.cuda.ExternalStream(int(backend._lib.aion_cuda_get_stream(backend.handle)),
+                                       device=torch.device("cuda", local_rank))
+    return stream, torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+
+def _max_over_ranks(torch, dist, world, value):
+    if world == 1:
+        return value
+    t = torch.tensor([value], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def decode_leg(torch, dist, backend: CudaBackend, rank: int, world: int, local_rank: int, requests_total: int, steps: int,
+               warmup: int, lanes: int, cfg: DecoderConfig | None = None, peak_gbs: float = 6552.3) -> dict:
+    """Decode tokens/s of the synthetic q4 decoder: `requests_total` concurrent requests at the far
+    end of the context window, split evenly over the ranks (replicated weights, no exchange)."""
+    cfg = cfg or DecoderConfig()
+    if requests_total % world != 0:
+        raise ValueError("requests must divide over the ranks")
+    R = requests_total // world
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(1234)  # every rank holds the same weights
+    keep = []
+
+    def weight_values(name, k, n):
+        w = torch.randn((k, n), generator=gen, device="cuda", dtype=torch.float32) * 0.02
+        torch.cuda.synchronize()
+        keep[:] = [w]
+        return Chunk(w.data_ptr(), 0, w.numel() * 4)
+
+    def embedding_values(v0, v1):
+        w = torch.randn((v1 - v0, cfg.hidden), generator=gen, device="cuda", dtype=torch.float32)
+        torch.cuda.synchronize()
+        keep[:] = [w]
+        return Chunk(w.data_ptr(), 0, w.numel() * 4)
+
+    t_build = time.perf_counter()
+    dec = SyntheticDecoder(backend, cfg, R, weight_values, embedding_values)
+    keep.clear()
+    # Caches full of plausible keys / values: every request sits at the last position of its window.
+    cgen = torch.Generator(device="cuda")
+    cgen.manual_seed(11 + rank)
+    for tid in dec.k_cache + dec.v_cache:
+        ch = dec.store.acquire_mut(tid)
+        t = torch.as_tensor(_DevArray(ch.handle + ch.offset, ch.len, "<f2", 2), device="cuda")
+        t.normal_(0.0, 1.0, generator=cgen)
+    torch.cuda.synchronize()
+    tokens = ((np.arange(R) + rank * R) * 7919 + 13) % cfg.vocab
+    positions = np.full(R, cfg.ctx - 1, np.int32)
+    dec.set_inputs(tokens, positions)
+    dec.execute()  # sizes scratch; also the un-recorded reference run
+    backend.sync()
+    first = dec.read_next_tokens().copy()
+    dec.record(lanes=lanes)
+    build_s = time.perf_counter() - t_build
+
+    stream, ev0, ev1 = _events(torch, backend, local_rank)
+
+    def barrier():
+        backend.sync()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+
+    for _ in range(max(warmup, 3)):
+        dec.launch()
+    barrier()
+    replay_same = bool(np.array_equal(dec.read_next_tokens(), first))
+    barrier()
+    ev0.record(stream)
+    for _ in range(steps):
+        dec.launch()
+    ev1.record(stream)
+    backend.sync()
+    torch.cuda.synchronize()
+    ms = _max_over_ranks(torch, dist, world, ev0.elapsed_time(ev1)) / steps
+
+    # end to end: per step the host sends token ids + positions and reads the next tokens back
+    tok_host = np.ascontiguousarray(tokens, dtype=np.int32).reshape(R, 1)
+    e2e_steps = max(3, min(steps, 50))
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        dec.set_inputs(tok_host, positions)
+        dec.launch()
+        tok_host = dec.read_next_tokens().reshape(R, 1) % cfg.vocab
+    e2e_s = _max_over_ranks(torch, dist, world, time.perf_counter() - t0)
+
+    step_bytes = cfg.weight_bytes_per_step() + R * cfg.kv_bytes_per_request_step()
+    out = {
+        "metric": "decode tokens/s", "value": round(requests_total / (ms * 1e-3), 1), "unit": "tokens/s",
+        "ms_per_step": round(ms, 4), "requests_total": requests_total, "requests_per_gpu": R, "n_gpus": world,
+        "scaling": "strong over requests (fixed total, batch-sharded, replicated weights, no collective)",
+        "e2e_tokens_per_s": round(requests_total * e2e_steps / e2e_s, 1),
+        "h2d_bytes_per_step": 4 * R * 4, "d2h_bytes_per_step": 4 * R,
+        "hbm_bytes_per_step_per_gpu": step_bytes,
+        "hbm_gbs_per_gpu": round(step_bytes / (ms * 1e-3) / 1e9, 1),
+        "hbm_frac_of_measured": round(step_bytes / (ms * 1e-3) / 1e9 / peak_gbs, 4),
+        "launches_per_step": len(dec.steps), "replay_matches_eager": replay_same, "build_s": round(build_s, 1),
+        "config": {"layers": cfg.layers, "hidden": cfg.hidden, "ffn": cfg.ffn, "heads": cfg.heads, "kv_heads": cfg.kv_heads,
+                   "head_dim": cfg.head_dim, "vocab": cfg.vocab, "ctx": cfg.ctx, "weights": "q4_0, N(0, 0.02), random init"},
+    }
+    dec.deinit()
+    return out
+
+
+def gemm_leg(torch, backend: CudaBackend, local_rank: int, dtype: int, m: int, n: int, k: int, iters: int = 20, copies: int = 8,
+             peak_tflops: float = 1622.7) -> dict:
+    """Prefill GEMM TFLOP/s: `copies` distinct weight matrices walked in turn, device-timed."""
+    lib, dev, mem = backend._lib, backend.handle, backend.device_memory
+    bb = 18 if dtype == capi.DTYPE_Q4_0 else 34
+    nb = (k // 32) * n * bb
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(1234)
+    shape = (C.c_uint64 * 2)(k, n)
+    hb = []
+    for _ in range(copies):
+        w = torch.randn((k, n), generator=gen, device="cuda", dtype=torch.float32) * 0.02
+        torch.cuda.synchronize()
+        h = mem.alloc(nb, 256)
+        src, dst = capi.Operand(w.data_ptr(), 0, w.numel() * 4), capi.Operand(h, 0, nb)
+        _chk(lib.aion_cuda_quantize(dev, dtype, C.byref(src), shape, 2, 0, C.byref(dst)))
+        backend.sync()
+        hb.append(h)
+    a = torch.randn((m, k), generator=torch.Generator().manual_seed(5678), dtype=torch.float32).numpy()
+    ha = mem.alloc(a.nbytes, 256)
+    mem.copy_h2d(ha, 0, a)
+    hc = mem.alloc(m * n * 4, 256)
+    recs = [capi.MatMul(c=capi.Operand(hc, 0, m * n * 4), a=capi.Operand(ha, 0, a.nbytes), b=capi.Operand(h, 0, nb),
+                        b_dtype=dtype, flags=capi.MATMUL_AUTO, m=m, n=n, k=k, lda=0, ldb=0, ldc=0, alpha=1.0, beta=0.0)
+            for h in hb]
+    for i in range(3):
+        _chk(lib.aion_cuda_matmul(dev, C.byref(recs[i % copies])))
+    backend.sync()
+    stream, ev0, ev1 = _events(torch, backend, local_rank)
+    ev0.record(stream)
+    for i in range(iters):
+        _chk(lib.aion_cuda_matmul(dev, C.byref(recs[i % copies])))
+    ev1.record(stream)
+    backend.sync()
+    torch.cuda.synchronize()
+    ms = ev0.elapsed_time(ev1) / iters
+    tf = 2.0 * m * n * k / (ms * 1e-3) / 1e12
+    for h in hb + [ha, hc]:
+        mem.free(h)
+    return {"dtype": "q4_0" if dtype == capi.DTYPE_Q4_0 else "q8_0", "m": m, "n": n, "k": k, "ms": round(ms, 4),
+            "tflops": round(tf, 1), "frac_of_measured_bf16_peak": round(tf / peak_tflops, 4),
+            "includes": "f32->bf16 activation pre-pass + GEMM kernel per call"}
+
+
+def attention_leg(torch, backend: CudaBackend, local_rank: int, batch: int, t_ctx: int, iters: int = 20,
+                  peak_gbs: float = 6552.3, heads: int = 8, kv_heads: int = 1, d: int = 256) -> dict:
+    """Decode attention GB/s of algorithmic bytes (K + V once per request + q + out)."""
+    lib, dev, mem = backend._lib, backend.handle, backend.device_memory
+    # enough distinct cache sets that consecutive launches do not find K/V in L2
+    kv_bytes = batch * t_ctx * kv_heads * d * 2
+    copies = max(2, min(16, int((512 << 20) // max(2 * kv_bytes, 1)) + 1))
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(12)
+    sets = []
+    for _ in range(copies):
+        hk, hv = mem.alloc(kv_bytes, 256), mem.alloc(kv_bytes, 256)
+        for h in (hk, hv):
+            torch.as_tensor(_DevArray(h, kv_bytes, "<f2", 2), device="cuda").normal_(0.0, 1.0, generator=gen)
+        sets.append((hk, hv))
+    torch.cuda.synchronize()
+    q = torch.randn((batch, 1, heads, d), generator=torch.Generator().manual_seed(11), dtype=torch.float32).to(torch.float16).numpy()
+    hq = mem.alloc(q.nbytes, 256)
+    mem.copy_h2d(hq, 0, q)
+    out_bytes = batch * heads * d * 4
+    ho = mem.alloc(out_bytes, 256)
+    pos = np.full((batch, 1), t_ctx - 1, np.int32)
+    lens = np.full(batch, t_ctx, np.int32)
+    hp, hl = mem.alloc(pos.nbytes, 64), mem.alloc(lens.nbytes, 64)
+    mem.copy_h2d(hp, 0, pos)
+    mem.copy_h2d(hl, 0, lens)
+    recs = [capi.Attention(out=capi.Operand(ho, 0, out_bytes), q=capi.Operand(hq, 0, q.nbytes), k=capi.Operand(hk, 0, kv_bytes),
+                           v=capi.Operand(hv, 0, kv_bytes), query_positions=capi.Operand(hp, 0, pos.nbytes),
+                           kv_lengths=capi.Operand(hl, 0, lens.nbytes), q_dtype=capi.DTYPE_F16, k_dtype=capi.DTYPE_F16,
+                           v_dtype=capi.DTYPE_F16, rolling=0, batch=batch, l_q=1, h_q=heads, h_kv=kv_heads, d_k=d, d_v=d,
+                           t_cap=t_ctx, scale=1.0 / float(np.sqrt(d)), soft_cap=0.0, window_left=capi.WINDOW_UNBOUNDED,
+                           window_right=0, window_chunk=0, flags=0) for hk, hv in sets]
+    for i in range(copies):
+        _chk(lib.aion_cuda_attention(dev, C.byref(recs[i])))
+    backend.sync()
+    # One recorded program = one launch over every cache set, so the host's per-call cost
+    # (two tensor-map encodes and a launch) stays out of the device-timed region.
+    _chk(lib.aion_cuda_record_begin(dev))
+    for i in range(copies):
+        _chk(lib.aion_cuda_attention(dev, C.byref(recs[i])))
+    prog = C.c_void_p()
+    _chk(lib.aion_cuda_record_end(dev, C.byref(prog)))
+    for _ in range(3):
+        _chk(lib.aion_cuda_program_launch(dev, prog))
+    backend.sync()
+    stream, ev0, ev1 = _events(torch, backend, local_rank)
+    ev0.record(stream)
+    for _ in range(iters):
+        _chk(lib.aion_cuda_program_launch(dev, prog))
+    ev1.record(stream)
+    backend.sync()
+    torch.cuda.synchronize()
+    ms = ev0.elapsed_time(ev1) / (iters * copies)
+    lib.aion_cuda_program_destroy(dev, prog)
+    alg = 2 * kv_bytes + q.nbytes + out_bytes
+    for hk, hv in sets:
+        mem.free(hk)
+        mem.free(hv)
+    for h in (hq, ho, hp, hl):
+        mem.free(h)
+    gbs = alg / (ms * 1e-3) / 1e9
+    return {"batch": batch, "context": t_ctx, "ms": round(ms, 4), "gbs": round(gbs, 1), "frac_of_measured_hbm": round(gbs / peak_gbs, 4),
+            "algorithmic_bytes": alg, "distinct_cache_sets": copies}
+
+
+def colsplit_leg(torch, dist, backend: CudaBackend, rank: int, world: int, local_rank: int, m: int, iters: int = 50,
+                 n: int = 28672, k: int = 8192) -> dict:
+    """The one large q4 layer column-split over the ranks: each rank computes y[:, n0:n1] straight
+    into its slot of the gather buffer, then one NCCL all-gather (in place) assembles y on every rank."""
+    lib, dev, mem = backend._lib, backend.handle, backend.device_memory
+    if n % (world * 8) != 0:
+        raise ValueError("n must split into multiples of 8 columns per rank")
+    n_loc = n // world
+    nb = (k // 32) * n_loc * 18
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(1234 + rank)
+    w = torch.randn((k, n_loc), generator=gen, device="cuda", dtype=torch.float32) * 0.02
+    torch.cuda.synchronize()
+    hw = mem.alloc(nb, 256)
+    shape = (C.c_uint64 * 2)(k, n_loc)
+    src, dst = capi.Operand(w.data_ptr(), 0, w.numel() * 4), capi.Operand(hw, 0, nb)
+    _chk(lib.aion_cuda_quantize(dev, capi.DTYPE_Q4_0, C.byref(src), shape, 2, 0, C.byref(dst)))
+    backend.sync()
+    del w
+    x = torch.randn((m, k), generator=torch.Generator().manual_seed(5678), dtype=torch.float32)
+    xd = x.cuda()
+    # gather buffer [world][m][n_loc]; rank r's matmul writes slot r (ldc = n_loc)
+    gather = torch.zeros((world, m, n_loc), device="cuda", dtype=torch.float32)
+    slot = gather[rank]
+    rec = capi.MatMul(c=capi.Operand(slot.data_ptr(), 0, m * n_loc * 4), a=capi.Operand(xd.data_ptr(), 0, xd.numel() * 4),
+                      b=capi.Operand(hw, 0, nb), b_dtype=capi.DTYPE_Q4_0, flags=capi.MATMUL_AUTO, m=m, n=n_loc, k=k,
+                      lda=0, ldb=0, ldc=0, alpha=1.0, beta=0.0)
+    stream, ev0, ev1 = _events(torch, backend, local_rank)
+
+    def step():
+        _chk(lib.aion_cuda_matmul(dev, C.byref(rec)))
+        if world > 1:
+            with torch.cuda.stream(stream):  # same stream as the kernel: ordered after it, no host sync
+                dist.all_gather_into_tensor(gather.view(-1), slot.reshape(-1))
+
+    for _ in range(5):
+        step()
+    backend.sync()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    ev0.record(stream)
+    for _ in range(iters):
+        step()
+    ev1.record(stream)
+    backend.sync()
+    torch.cuda.synchronize()
+    ms = _max_over_ranks(torch, dist, world, ev0.elapsed_time(ev1)) / iters
+    checksum = float(gather.double().sum().item())
+    mem.free(hw)
+    total_w = (k // 32) * n * 18
+    return {"m": m, "n": n, "k": k, "n_gpus": world, "columns_per_gpu": n_loc, "ms": round(ms, 4),
+            "aggregate_weight_gbs": round(total_w / (ms * 1e-3) / 1e9, 1),
+            "all_gather_bytes_per_rank": m * n_loc * 4, "checksum": checksum}

@@ -23,6 +23,7 @@
 //  * attn_generic_kernel — every other dtype / head size: one warp per key slice of a
 //    row, f32 arithmetic, same merge inside the CTA.
 #include <cfloat>
+#include <cmath>
 
 #include "common.cuh"
 #include "ptx.cuh"
@@ -120,9 +121,21 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
   return *reinterpret_cast<const uint32_t*>(&h);
 }
 
+// Two shared-memory layouts of a K / V tile of KT rows:
+//  * tiled (the usual case): the tile arrives as D/64 TMA boxes of 64 columns x KT rows with
+//    the 128-byte swizzle, so 16-byte chunk c of row r sits in column block c/8 at
+//    r*128 + ((c%8) ^ (r&7))*16 and ldmatrix is conflict free;
+//  * padded rows (rolling caches, whose rows wrap and so cannot be one box): one bulk copy
+//    per row at a pitch of D*2 + 16 bytes.
+template <int D, bool TILED>
+__device__ __forceinline__ uint32_t tile_off(uint32_t row, uint32_t chunk) {
+  if (TILED) return (chunk >> 3) * (KT * 128) + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
+  return row * (D * 2 + 16) + (chunk << 4);
+}
+
 template <int D>
 struct DecodeGeom {
-  static constexpr int PITCH = D * 2 + 16;            // bytes per K / V row in shared memory
+  static constexpr int PITCH = D * 2 + 16;            // bytes per K / V row in shared memory (padded layout)
   static constexpr int TILE_BYTES = KT * PITCH;       // one of K, V
   static constexpr int STAGE_BYTES = 2 * TILE_BYTES;  // K then V
   static constexpr int QFRAG_BYTES = (D / 16) * 32 * 8;  // one of hi, lo
@@ -139,11 +152,12 @@ struct DecodeGeom {
 
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory"); }
 
-template <int D, bool QF32>
-__global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParams p) {
+template <int D, bool QF32, bool TILED>
+__global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tmap_k,
+                                                                 const __grid_constant__ CUtensorMap tmap_v) {
   using G = DecodeGeom<D>;
   constexpr int NS = G::NS;
-  extern __shared__ __align__(128) uint8_t smem[];
+  extern __shared__ __align__(1024) uint8_t smem[];  // swizzled TMA tiles need 1024-byte alignment
   const uint32_t smem_base = ptx::smem_u32(smem);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, j = lane & 3;
@@ -216,13 +230,27 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParam
       const uint32_t cnt = min((uint32_t)KT, my_hi - t0);
       const uint32_t full = bar_full + 8 * slot;
       const uint32_t stage = smem_base + slot * G::STAGE_BYTES;
-      if (lane == 0) ptx::mbar_arrive_expect_tx(full, cnt * (uint32_t)(D * 2) * 2u);
-      __syncwarp();
-      for (uint32_t r = lane; r < cnt; r += 32) {
-        const uint32_t t = t0 + r;
-        const uint64_t row = ((uint64_t)b * p.T + (p.rolling ? t % p.T : t)) * p.Hkv + hkv;
-        ptx::bulk_g2s(stage + r * G::PITCH, kbase + row * D, D * 2, full);
-        ptx::bulk_g2s(stage + G::TILE_BYTES + r * G::PITCH, vbase + row * D, D * 2, full);
+      if (TILED) {
+        // Whole boxes always: rows past the range arrive too (later keys, the next request's
+        // rows or zeros past the tensor) and are cleared by the consumers before use.
+        if (lane == 0) {
+          ptx::mbar_arrive_expect_tx(full, 2u * KT * D * 2);
+          const int32_t y = (int32_t)(b * p.T + t0);
+#pragma unroll
+          for (int cb = 0; cb < D / 64; cb++) {
+            ptx::tma_load_2d(stage + cb * (KT * 128), &tmap_k, (int32_t)(hkv * D + cb * 64), y, full);
+            ptx::tma_load_2d(stage + G::TILE_BYTES + cb * (KT * 128), &tmap_v, (int32_t)(hkv * D + cb * 64), y, full);
+          }
+        }
+      } else {
+        if (lane == 0) ptx::mbar_arrive_expect_tx(full, cnt * (uint32_t)(D * 2) * 2u);
+        __syncwarp();
+        for (uint32_t r = lane; r < cnt; r += 32) {
+          const uint32_t t = t0 + r;
+          const uint64_t row = ((uint64_t)b * p.T + (p.rolling ? t % p.T : t)) * p.Hkv + hkv;
+          ptx::bulk_g2s(stage + r * G::PITCH, kbase + row * D, D * 2, full);
+          ptx::bulk_g2s(stage + G::TILE_BYTES + r * G::PITCH, vbase + row * D, D * 2, full);
+        }
       }
       issued = it + 1;
     }
@@ -280,9 +308,9 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParam
           // Rows past the range were not copied: clear them so stale bits cannot reach an MMA.
           uint8_t* kt = smem + slot * G::STAGE_BYTES;
           for (uint32_t i = lane; i < (16 - valid) * (D * 2 / 16); i += 32) {
-            const uint32_t rr = r0 + valid + i / (D * 2 / 16), cc = (i % (D * 2 / 16)) * 16;
-            *reinterpret_cast<uint4*>(kt + rr * G::PITCH + cc) = make_uint4(0, 0, 0, 0);
-            *reinterpret_cast<uint4*>(kt + G::TILE_BYTES + rr * G::PITCH + cc) = make_uint4(0, 0, 0, 0);
+            const uint32_t rr = r0 + valid + i / (D * 2 / 16), cc = i % (D * 2 / 16);
+            *reinterpret_cast<uint4*>(kt + tile_off<D, TILED>(rr, cc)) = make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4*>(kt + G::TILE_BYTES + tile_off<D, TILED>(rr, cc)) = make_uint4(0, 0, 0, 0);
           }
           __syncwarp();
         }
@@ -290,13 +318,13 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParam
         float s[4] = {0, 0, 0, 0};
         {
           const uint32_t a_row = r0 + (lane & 7) + 8 * ((lane >> 3) & 1);
-          const uint32_t a_addr = kst + a_row * G::PITCH + (lane >> 4) * 16;
+          const uint32_t a_chunk = lane >> 4;
           const uint2* qhi = reinterpret_cast<const uint2*>(smem + G::OFF_QHI);
           const uint2* qlo = reinterpret_cast<const uint2*>(smem + G::OFF_QLO);
 #pragma unroll
           for (int ks = 0; ks < D / 16; ks++) {
             uint32_t a0, a1, a2, a3;
-            ldmatrix_x4(a_addr + ks * 32, a0, a1, a2, a3);
+            ldmatrix_x4(kst + tile_off<D, TILED>(a_row, 2 * ks + a_chunk), a0, a1, a2, a3);
             const uint2 bh = qhi[ks * 32 + lane];
             mma_f16(s, a0, a1, a2, a3, bh.x, bh.y);
             if (QF32) {
@@ -338,7 +366,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParam
         const uint32_t pb1 = movmatrix_trans(pack_half2(pr[2], pr[3]));
         // ---- O^T[Dv x 8 heads] = alpha * O^T + V^T . P^T ----
         const uint32_t v_row = r0 + (lane & 7) + 8 * (lane >> 4);
-        const uint32_t v_addr = vst + v_row * G::PITCH + ((lane >> 3) & 1) * 16;
+        const uint32_t v_chunk = (lane >> 3) & 1;
 #pragma unroll
         for (int mt = 0; mt < D / 16; mt++) {
           acc[mt][0] *= alpha[0];
@@ -346,7 +374,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParam
           acc[mt][2] *= alpha[0];
           acc[mt][3] *= alpha[1];
           uint32_t a0, a1, a2, a3;
-          ldmatrix_x4_trans(v_addr + mt * 32, a0, a1, a2, a3);
+          ldmatrix_x4_trans(vst + tile_off<D, TILED>(v_row, 2 * mt + v_chunk), a0, a1, a2, a3);
           mma_f16(acc[mt], a0, a1, a2, a3, pb0, pb1);
         }
       }
@@ -422,20 +450,48 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParam
       consumer_sync();
       if (*last_flag) {
         __threadfence();
+        // Merge in two passes so that no thread walks the splits with dependent loads: first
+        // every split's (max, sum) pair becomes a scale factor in shared memory (the ring is
+        // drained, its space is free), then the weighted sums run over independent loads.
         const float* pu = p.partial + (uint64_t)unit * p.splits * 8 * (D + 2);
+        float* fac = reinterpret_cast<float*>(smem);          // [8][splits]
+        float* lsums = fac + 8 * p.splits;                    // [8]
+        for (uint32_t idx = tid; idx < 8 * p.splits; idx += CONSUMER_WARPS * 32) {
+          const uint32_t h = idx / p.splits, s2 = idx % p.splits;
+          fac[idx] = (h < nh) ? __ldcg(pu + (s2 * 8 + h) * (D + 2) + D) : -INFINITY;
+        }
+        consumer_sync();
+        for (uint32_t h = warp; h < 8; h += CONSUMER_WARPS) {
+          float M = -INFINITY;
+          for (uint32_t s2 = lane; s2 < p.splits; s2 += 32) M = fmaxf(M, fac[h * p.splits + s2]);
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xFFFFFFFFu, M, o));
+          float lsum = 0.0f;
+          for (uint32_t s2 = lane; s2 < p.splits; s2 += 32) {
+            const float ms = fac[h * p.splits + s2];
+            const float f = (ms == -INFINITY) ? 0.0f : exp2f(ms - M);
+            fac[h * p.splits + s2] = f;
+            if (h < nh) lsum += __ldcg(pu + (s2 * 8 + h) * (D + 2) + D + 1) * f;
+          }
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) lsum += __shfl_xor_sync(0xFFFFFFFFu, lsum, o);
+          if (lane == 0) lsums[h] = lsum;
+        }
+        consumer_sync();
         for (int idx = tid; idx < 8 * D; idx += CONSUMER_WARPS * 32) {
           const int h = idx / D, d = idx % D;
           if ((uint32_t)h >= nh) continue;
-          float M = -INFINITY;
-          for (uint32_t s2 = 0; s2 < p.splits; s2++) M = fmaxf(M, __ldcg(pu + (s2 * 8 + h) * (D + 2) + D));
-          float o = 0.0f, lsum = 0.0f;
-          for (uint32_t s2 = 0; s2 < p.splits; s2++) {
-            const float* ps = pu + (s2 * 8 + h) * (D + 2);
-            const float ms = __ldcg(ps + D);
-            const float f = (ms == -INFINITY) ? 0.0f : exp2f(ms - M);
-            o += __ldcg(ps + d) * f;
-            lsum += __ldcg(ps + D + 1) * f;
+          const float* col = pu + h * (D + 2) + d;
+          const float* fh = fac + h * p.splits;
+          float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
+          uint32_t s2 = 0;
+          for (; s2 + 4 <= p.splits; s2 += 4) {
+            const float v0 = __ldcg(col + (uint64_t)(s2 + 0) * 8 * (D + 2)), v1 = __ldcg(col + (uint64_t)(s2 + 1) * 8 * (D + 2));
+            const float v2 = __ldcg(col + (uint64_t)(s2 + 2) * 8 * (D + 2)), v3 = __ldcg(col + (uint64_t)(s2 + 3) * 8 * (D + 2));
+            o0 += v0 * fh[s2], o1 += v1 * fh[s2 + 1], o2 += v2 * fh[s2 + 2], o3 += v3 * fh[s2 + 3];
           }
+          for (; s2 < p.splits; s2++) o0 += __ldcg(col + (uint64_t)s2 * 8 * (D + 2)) * fh[s2];
+          const float o = (o0 + o1) + (o2 + o3), lsum = lsums[h];
           if (lsum > 0.0f && isfinite(lsum)) orow[idx] = o / lsum;
           else {
             orow[idx] = 0.0f;
@@ -530,10 +586,10 @@ __global__ void __launch_bounds__(GEN_WARPS * 32) attn_generic_kernel(const Attn
   }
 }
 
-template <int D, bool QF32>
-int32_t launch_decode(AionCudaDevice* dev, const AttnParams& p, uint32_t units) {
+template <int D, bool QF32, bool TILED>
+int32_t launch_decode_as(AionCudaDevice* dev, const AttnParams& p, uint32_t units, const CUtensorMap& tk, const CUtensorMap& tv) {
   using G = DecodeGeom<D>;
-  auto kernel = attn_decode_kernel<D, QF32>;
+  auto kernel = attn_decode_kernel<D, QF32, TILED>;
   static bool configured[16] = {};
   if (!configured[dev->ordinal & 15]) {
     AION_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM_BYTES));
@@ -549,8 +605,21 @@ int32_t launch_decode(AionCudaDevice* dev, const AttnParams& p, uint32_t units) 
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  AION_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, p));
+  AION_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, p, tk, tv));
   return AION_CUDA_OK;
+}
+
+template <int D, bool QF32>
+int32_t launch_decode(AionCudaDevice* dev, const AttnParams& p, uint32_t units) {
+  CUtensorMap tk{}, tv{};
+  // K and V as [B*T rows][Hkv*D columns] f16; a rolling cache's rows wrap, so it keeps row copies.
+  if (!p.rolling && (uint64_t)p.B * p.T < (1ull << 31)) {
+    const uint64_t rows = (uint64_t)p.B * p.T, cols = (uint64_t)p.Hkv * D;
+    if (int32_t st = tensor_map_16bit_sw128(p.k, false, rows, cols, cols * 2, 64, KT, &tk)) return st;
+    if (int32_t st = tensor_map_16bit_sw128(p.v, false, rows, cols, cols * 2, 64, KT, &tv)) return st;
+    return launch_decode_as<D, QF32, true>(dev, p, units, tk, tv);
+  }
+  return launch_decode_as<D, QF32, false>(dev, p, units, tk, tv);
 }
 
 }  // namespace
@@ -606,6 +675,10 @@ int32_t attention_launch(AionCudaDevice* dev, const AionCudaAttention* s) {
     if (units < want) splits = (want + units - 1) / units;
     const uint64_t max_splits = (max_keys + KT - 1) / KT;
     if (splits > max_splits) splits = max_splits;
+    // One CTA merges a row's partials (about 8 KB per split at D = 256, read through one SM),
+    // while a split's own work shrinks as 1/splits: the sum is least near sqrt(keys / 5).
+    const uint64_t merge_cap = (uint64_t)std::sqrt(0.2 * (double)max_keys) + 1;
+    if (splits > merge_cap) splits = merge_cap;
     if (splits > 256) splits = 256;
     if (splits < 1) splits = 1;
     if (dev->attn_split_override) splits = dev->attn_split_override;

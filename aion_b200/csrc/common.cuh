@@ -131,6 +131,9 @@ int32_t tensor_map_encode(const void* base, uint32_t rank, const uint64_t* dims,
 // Row-major bf16 [rows, cols] view with a 128-byte swizzled box (tensor-core operand tiles).
 int32_t tensor_map_bf16_sw128(const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_bytes, uint32_t box_cols,
                               uint32_t box_rows, CUtensorMap* out);
+// The same for either 16-bit float type (bf16 or f16).
+int32_t tensor_map_16bit_sw128(const void* base, bool bf16, uint64_t rows, uint64_t cols, uint64_t pitch_bytes, uint32_t box_cols,
+                               uint32_t box_rows, CUtensorMap* out);
 
 // ---- step implementations, one per kernel file ------------------------------------
 int32_t quantize_activation_rows(AionCudaDevice* dev, const float* a, uint64_t m, uint64_t k, uint64_t lda,

@@ -151,6 +151,11 @@ int32_t tensor_map_encode(const void* base, uint32_t rank, const uint64_t* dims,
 // descriptors read. Out-of-range rows and columns arrive as zeros.
 int32_t tensor_map_bf16_sw128(const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_bytes, uint32_t box_cols,
                               uint32_t box_rows, CUtensorMap* out) {
+  return tensor_map_16bit_sw128(base, true, rows, cols, pitch_bytes, box_cols, box_rows, out);
+}
+
+int32_t tensor_map_16bit_sw128(const void* base, bool bf16, uint64_t rows, uint64_t cols, uint64_t pitch_bytes, uint32_t box_cols,
+                               uint32_t box_rows, CUtensorMap* out) {
   typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                     const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                     CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -163,15 +168,15 @@ int32_t tensor_map_bf16_sw128(const void* base, uint64_t rows, uint64_t cols, ui
     encode = reinterpret_cast<EncodeTiledFn>(fn);
   }
   if (((uintptr_t)base & 15) || (pitch_bytes & 15) || box_cols * 2 != 128 || box_rows > 256)
-    return fail(AION_CUDA_INTERNAL_ERROR, "tensor map: bf16 view geometry is not TMA-addressable");
+    return fail(AION_CUDA_INTERNAL_ERROR, "tensor map: 16-bit view geometry is not TMA-addressable");
   const cuuint64_t gdim[2] = {cols, rows};
   const cuuint64_t gstride[1] = {pitch_bytes};
   const cuuint32_t bx[2] = {box_cols, box_rows};
   const cuuint32_t estride[2] = {1, 1};
-  const CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), gdim, gstride, bx, estride,
+  const CUresult r = encode(out, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), gdim, gstride, bx, estride,
                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(AION_CUDA_INTERNAL_ERROR, "cuTensorMapEncodeTiled (bf16) failed with %d", (int)r);
+  if (r != CUDA_SUCCESS) return fail(AION_CUDA_INTERNAL_ERROR, "cuTensorMapEncodeTiled (16-bit, swizzled) failed with %d", (int)r);
   return AION_CUDA_OK;
 }
 

@@ -48,27 +48,33 @@ __device__ __forceinline__ float gelu_approx(float x) {
   return 0.5f * x * (1.0f + tanh_approx(t));
 }
 
-// ---- RMSNorm: one warp per row -------------------------------------------------------
-__global__ void rms_norm_kernel(float* out, const float* x, const float* __restrict__ gamma,
-                                const float* __restrict__ beta, const float* residual, uint64_t rows,
-                                uint64_t cols, float eps, int* fault) {
-  const int lane = threadIdx.x & 31;
-  const uint64_t r = blockIdx.x * (uint64_t)(blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (r >= rows) return;
+// ---- RMSNorm: one block per row -----------------------------------------------------
+constexpr int RMS_THREADS = 128;
+__global__ void __launch_bounds__(RMS_THREADS) rms_norm_kernel(float* out, const float* x, const float* __restrict__ gamma,
+                                                               const float* __restrict__ beta, const float* residual,
+                                                               uint64_t cols, float eps, int* fault) {
+  const uint64_t r = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const float* xr = x + r * cols;
   float sq = 0.0f;
-  for (uint64_t c = lane; c < cols; c += 32) {
+  for (uint64_t c = threadIdx.x; c < cols; c += RMS_THREADS) {
     const float v = xr[c];
     sq += v * v;
   }
   for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xFFFFFFFFu, sq, o);
+  __shared__ float part[RMS_THREADS / 32];
+  if (lane == 0) part[warp] = sq;
+  __syncthreads();
+  sq = 0.0f;
+#pragma unroll
+  for (int w = 0; w < RMS_THREADS / 32; w++) sq += part[w];  // same order in every thread
   const float d = sq * (1.0f / (float)cols) + eps;
   if (!(d > 0.0f) || !isfinite(d)) {
-    if (lane == 0) atomicCAS(fault, FAULT_NONE, FAULT_INVALID_ARGUMENT);
+    if (threadIdx.x == 0) atomicCAS(fault, FAULT_NONE, FAULT_INVALID_ARGUMENT);
     return;
   }
   const float inv = 1.0f / sqrtf(d);
-  for (uint64_t c = lane; c < cols; c += 32) {
+  for (uint64_t c = threadIdx.x; c < cols; c += RMS_THREADS) {
     float v = ((xr[c] * inv) * gamma[c]) + beta[c];
     if (residual) v = v + residual[r * cols + c];
     out[r * cols + c] = v;
@@ -180,11 +186,8 @@ __device__ __forceinline__ void argmax_take(float& bv, int& bi, float v, int i) 
     bi = i;
   }
 }
-__global__ void argmax_kernel(int32_t* __restrict__ out, const float* __restrict__ in, uint64_t n) {
-  const float* row = in + blockIdx.x * n;
-  float bv = -INFINITY;
-  int bi = 0x7FFFFFFF;
-  for (uint64_t j = threadIdx.x; j < n; j += blockDim.x) argmax_take(bv, bi, row[j], (int)j);
+// Block-wide first-maximum of (bv, bi); the result is valid in warp 0, lane 0.
+__device__ __forceinline__ void argmax_block_reduce(float& bv, int& bi) {
   for (int o = 16; o > 0; o >>= 1) {
     const float ov = __shfl_xor_sync(0xFFFFFFFFu, bv, o);
     const int oi = __shfl_xor_sync(0xFFFFFFFFu, bi, o);
@@ -204,10 +207,40 @@ __global__ void argmax_kernel(int32_t* __restrict__ out, const float* __restrict
       const int oi = __shfl_xor_sync(0xFFFFFFFFu, bi, o);
       argmax_take(bv, bi, ov, oi);
     }
-    // A NaN in front can never be displaced in the reference's scan; a row of nothing but
-    // NaN (no candidate taken) answers 0 as well.
-    if (lane == 0) out[blockIdx.x] = (isnan(row[0]) || bi == 0x7FFFFFFF) ? 0 : bi;
   }
+}
+// grid (chunks, rows): every block scans one chunk of a row and leaves its candidate in
+// scratch; the last block of a row to finish (a ticket) picks among the candidates.
+__global__ void argmax_kernel(int32_t* __restrict__ out, const float* __restrict__ in, uint64_t n, uint64_t chunk_len,
+                              float* cand_v, int* cand_i, int* tickets) {
+  const uint64_t rowi = blockIdx.y;
+  const float* row = in + rowi * n;
+  const uint64_t lo = blockIdx.x * chunk_len, hi = min(n, lo + chunk_len);
+  float bv = -INFINITY;
+  int bi = 0x7FFFFFFF;
+  for (uint64_t j = lo + threadIdx.x; j < hi; j += blockDim.x) argmax_take(bv, bi, row[j], (int)j);
+  argmax_block_reduce(bv, bi);
+  __shared__ int last;
+  if (threadIdx.x == 0) {
+    cand_v[rowi * gridDim.x + blockIdx.x] = bv;
+    cand_i[rowi * gridDim.x + blockIdx.x] = bi;
+    __threadfence();
+    const int prev = atomicAdd(tickets + rowi, 1);
+    last = (prev == (int)gridDim.x - 1);
+    if (last) tickets[rowi] = 0;  // ready for the next launch
+  }
+  __syncthreads();
+  if (!last) return;
+  __threadfence();
+  bv = -INFINITY;
+  bi = 0x7FFFFFFF;
+  for (uint32_t c = threadIdx.x; c < gridDim.x; c += blockDim.x)
+    argmax_take(bv, bi, __ldcg(cand_v + rowi * gridDim.x + c), __ldcg(cand_i + rowi * gridDim.x + c));
+  __syncthreads();  // the reduction reuses its shared arrays
+  argmax_block_reduce(bv, bi);
+  // A NaN in front can never be displaced in the reference's scan; a row of nothing but
+  // NaN (no candidate taken) answers 0 as well.
+  if (threadIdx.x == 0) out[rowi] = (isnan(row[0]) || bi == 0x7FFFFFFF) ? 0 : bi;
 }
 
 unsigned grid_for(const AionCudaDevice* dev, uint64_t n, unsigned threads) {
@@ -237,9 +270,8 @@ int32_t aion_cuda_rms_norm(AionCudaDevice* dev, const AionCudaRMSNorm* s) {
   if (int32_t st = resolve(s->beta, s->cols * sizeof(float), "rms_norm.beta", &beta)) return st;
   if (s->residual.handle)
     if (int32_t st = resolve(s->residual, bytes, "rms_norm.residual", &res)) return st;
-  const int warps = 4;
-  rms_norm_kernel<<<(unsigned)ceil_div(s->rows, (uint64_t)warps), warps * 32, 0, dev->stream>>>(out, x, gamma, beta, res, s->rows,
-                                                                                                s->cols, s->eps, dev->fault_dev);
+  if (s->rows > 0x7FFFFFFFull) return fail(AION_CUDA_UNSUPPORTED, "rms_norm: too many rows for one launch");
+  rms_norm_kernel<<<(unsigned)s->rows, RMS_THREADS, 0, dev->stream>>>(out, x, gamma, beta, res, s->cols, s->eps, dev->fault_dev);
   AION_CUDA_TRY(cudaGetLastError());
   return AION_CUDA_OK;
 }
@@ -367,8 +399,20 @@ int32_t aion_cuda_argmax(AionCudaDevice* dev, const AionCudaArgMax* s) {
   const float* in;
   if (int32_t st = resolve(s->out, s->outer * sizeof(int32_t), "argmax.out", &out)) return st;
   if (int32_t st = resolve(s->in, s->outer * s->n * sizeof(float), "argmax.in", &in)) return st;
-  if (s->outer > 0x7FFFFFFFull) return fail(AION_CUDA_UNSUPPORTED, "argmax: too many rows for one launch");
-  argmax_kernel<<<(unsigned)s->outer, 1024, 0, dev->stream>>>(out, in, s->n);
+  if (s->outer > 65535) return fail(AION_CUDA_UNSUPPORTED, "argmax: at most 65535 rows per launch, got %llu", (unsigned long long)s->outer);
+  // Chunks of at least 4096 elements, enough of them to cover the SMs about twice.
+  uint64_t chunks = ceil_div(2ull * dev->sm_count, s->outer);
+  const uint64_t max_chunks = ceil_div(s->n, (uint64_t)4096);
+  if (chunks > max_chunks) chunks = max_chunks;
+  if (chunks < 1) chunks = 1;
+  const uint64_t chunk_len = ceil_div(s->n, chunks);
+  chunks = ceil_div(s->n, chunk_len);
+  if (int32_t st = dev->reserve_scratch(s->outer * chunks * 8)) return st;
+  if (int32_t st = dev->reserve_tickets(s->outer)) return st;
+  float* cand_v = static_cast<float*>(dev->lane_scratch());
+  int* cand_i = reinterpret_cast<int*>(cand_v + s->outer * chunks);
+  argmax_kernel<<<dim3((unsigned)chunks, (unsigned)s->outer), 256, 0, dev->stream>>>(out, in, s->n, chunk_len, cand_v, cand_i,
+                                                                                      dev->lane_tickets());
   AION_CUDA_TRY(cudaGetLastError());
   return AION_CUDA_OK;
 }

@@ -276,11 +276,64 @@ def run_ours(args):
     }
     if cpu_baseline is not None:
         out["cpu_baseline"] = cpu_baseline
-    if rank == 0:
-        print(json.dumps(out), flush=True)
     lib.aion_cuda_program_destroy(dev, prog)
     for h in (w_arena, x_dev, y_dev):
         mem.free(h)
+    if not args.no_decode:
+        # Second leg of the metric: decode tokens/s of the synthetic q4 decoder on the same GPUs.
+        from aion_b200 import benchmarks
+        from aion_b200.decoder import DecoderConfig
+
+        try:
+            out["decode"] = benchmarks.decode_leg(torch, dist, backend, rank, world, local_rank, args.decode_requests,
+                                                  args.decode_steps, 3, args.lanes, DecoderConfig(layers=args.decode_layers), peak)
+        except Exception as e:  # the headline line must still print
+            out["decode"] = {"error": f"{type(e).__name__}: {e}"}
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    backend.deinit()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_other(args):
+    """The other workloads of the benchmark configurations, one JSON line each."""
+    import torch
+    import torch.distributed as dist
+
+    from aion_b200 import benchmarks, capi
+    from aion_b200.backend import CudaBackend
+    from aion_b200.decoder import DecoderConfig
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    torch.cuda.set_device(local_rank)
+    backend = CudaBackend(local_rank)
+    peak, peak_kind = measured_peak_gbs()
+    with ClockSampler(local_rank) as clocks:
+        if args.workload == "decode":
+            out = benchmarks.decode_leg(torch, dist, backend, rank, world, local_rank, args.decode_requests, args.decode_steps,
+                                        max(args.warmup, 3), args.lanes, DecoderConfig(layers=args.decode_layers), peak)
+        elif args.workload == "gemm":
+            dt = capi.DTYPE_Q4_0 if args.gemm_dtype == "q4" else capi.DTYPE_Q8_0
+            out = {"metric": "prefill GEMM TFLOP/s", "n_gpus": 1,
+                   **benchmarks.gemm_leg(torch, backend, local_rank, dt, args.gemm_m, 8192, 2048, iters=max(3, min(args.steps, 50)))}
+        elif args.workload == "attention":
+            out = {"metric": "decode attention GB/s", "n_gpus": 1,
+                   **benchmarks.attention_leg(torch, backend, local_rank, args.attn_batch, args.attn_context,
+                                              iters=max(3, min(args.steps, 50)), peak_gbs=peak)}
+        else:
+            out = {"metric": "column-split q4 layer + all-gather",
+                   **benchmarks.colsplit_leg(torch, dist, backend, rank, world, local_rank, args.colsplit_m,
+                                             iters=max(3, min(args.steps, 100)))}
+    out["clocks"] = clocks.summary()
+    out["data"] = "synthetic"
+    if rank == 0:
+        print(json.dumps(out), flush=True)
     backend.deinit()
     if world > 1:
         dist.destroy_process_group()
@@ -348,11 +401,26 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--lanes", type=int, default=8, help="parallel lanes the independent steps are recorded into (1..8)")
     ap.add_argument("--skip-cpu-baseline", action="store_true", help="leave the CPU leg out (profiling runs)")
+    ap.add_argument("--workload", default="gemv", choices=["gemv", "decode", "gemm", "attention", "colsplit"],
+                    help="gemv: the headline pass (default; its line also carries the decode leg). The others print "
+                         "their own line: decode tokens/s, prefill GEMM TFLOP/s, decode attention GB/s, the "
+                         "column-split layer with its all-gather")
+    ap.add_argument("--no-decode", action="store_true", help="gemv workload: leave the decoder leg out")
+    ap.add_argument("--decode-requests", type=int, default=512, help="concurrent requests in total, split over the GPUs")
+    ap.add_argument("--decode-steps", type=int, default=20)
+    ap.add_argument("--decode-layers", type=int, default=30)
+    ap.add_argument("--gemm-m", type=int, default=2048)
+    ap.add_argument("--gemm-dtype", default="q4", choices=["q4", "q8"])
+    ap.add_argument("--attn-batch", type=int, default=64)
+    ap.add_argument("--attn-context", type=int, default=4096)
+    ap.add_argument("--colsplit-m", type=int, default=1)
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
-    else:
+    elif args.workload == "gemv":
         run_ours(args)
+    else:
+        run_other(args)
 
 
 if __name__ == "__main__":

@@ -16,6 +16,7 @@ import numpy as np
 from . import capi
 from .backend import BackendError, Chunk, CudaBackend
 from .decoder import DecoderConfig, SyntheticDecoder
+from .sharding import column_shard, request_shard
 
 
 def _chk(st):
@@ -50,9 +51,10 @@ def decode_leg(torch, dist, backend: CudaBackend, rank: int, world: int, local_r
     """Decode tokens/s of the synthetic q4 decoder: `requests_total` concurrent requests at the far
     end of the context window, split evenly over the ranks (replicated weights, no exchange)."""
     cfg = cfg or DecoderConfig()
-    if requests_total % world != 0:
-        raise ValueError("requests must divide over the ranks")
-    R = requests_total // world
+    mine = request_shard(requests_total, world, rank)
+    R = mine.stop - mine.start
+    if R == 0:
+        raise ValueError("fewer requests than ranks")
     gen = torch.Generator(device="cuda")
     gen.manual_seed(1234)  # every rank holds the same weights
     keep = []
@@ -80,7 +82,7 @@ def decode_leg(torch, dist, backend: CudaBackend, rank: int, world: int, local_r
         t = torch.as_tensor(_DevArray(ch.handle + ch.offset, ch.len, "<f2", 2), device="cuda")
         t.normal_(0.0, 1.0, generator=cgen)
     torch.cuda.synchronize()
-    tokens = ((np.arange(R) + rank * R) * 7919 + 13) % cfg.vocab
+    tokens = (np.arange(mine.start, mine.stop) * 7919 + 13) % cfg.vocab
     positions = np.full(R, cfg.ctx - 1, np.int32)
     dec.set_inputs(tokens, positions)
     dec.execute()  # sizes scratch; also the un-recorded reference run
@@ -253,9 +255,8 @@ def colsplit_leg(torch, dist, backend: CudaBackend, rank: int, world: int, local
     """The one large q4 layer column-split over the ranks: each rank computes y[:, n0:n1] straight
     into its slot of the gather buffer, then one NCCL all-gather (in place) assembles y on every rank."""
     lib, dev, mem = backend._lib, backend.handle, backend.device_memory
-    if n % (world * 8) != 0:
-        raise ValueError("n must split into multiples of 8 columns per rank")
-    n_loc = n // world
+    n0, n1 = column_shard(n, world, rank)
+    n_loc = n1 - n0
     nb = (k // 32) * n_loc * 18
     gen = torch.Generator(device="cuda")
     gen.manual_seed(1234 + rank)

@@ -45,8 +45,8 @@ WORKLOAD = f"q4_0 GEMV (MatMul step) M={M} N={N} K={K}, {COPIES} distinct weight
 METRIC = "q4 GEMV HBM GB/s"
 
 # DRAM bytes per launch of the GEMV kernel from an ncu capture of this workload
-# (dram__bytes_read.sum + dram__bytes_write.sum; summary under profiles/). None until captured.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# (dram__bytes_read.sum + dram__bytes_write.sum of one launch; summary under profiles/).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 9493248
 
 
 def measured_peak_gbs():

@@ -13,15 +13,6 @@ uint64_t kmajor_bytes(uint64_t kblocks, uint64_t ldb, uint64_t n, size_t bb) {
   return kblocks == 0 ? 0 : ((kblocks - 1) * ldb + n) * bb;
 }
 
-// Rows [r0, r0 + rows) of the step.
-MatMulArgs rows_of(const MatMulArgs& g, uint64_t r0, uint64_t rows) {
-  MatMulArgs h = g;
-  h.a = g.a + r0 * g.lda;
-  h.c = g.c + r0 * g.ldc;
-  h.m = rows;
-  return h;
-}
-
 int32_t route(AionCudaDevice* dev, const MatMulArgs& g, uint32_t flags, const char* what) {
   if (flags & AION_CUDA_MATMUL_FORCE_GENERIC) return matmul_generic(dev, g);
   if (flags & AION_CUDA_MATMUL_FORCE_GEMV) {
@@ -34,18 +25,14 @@ int32_t route(AionCudaDevice* dev, const MatMulArgs& g, uint32_t flags, const ch
     if (st == AION_CUDA_UNSUPPORTED) return fail(st, "%s: the tensor-core GEMM does not read this shape or alignment", what);
     return st;
   }
-  // Decode-sized m streams the weights through the int8 GEMV, 16 rows of A per pass, with
-  // the reference CPU kernels' arithmetic; beyond AION_CUDA_GEMM_MIN_M rows the step is a
-  // dense contraction for the tensor cores (bf16 operands). Either falls back to the
-  // any-shape kernel (still on the device) when the tiled kernel cannot read the operands.
+  // Decode-sized m streams the weights through the int8 GEMV (groups of 16 rows of A share
+  // one launch; the weights of the second and later groups come from L2), with the
+  // reference CPU kernels' arithmetic; from AION_CUDA_GEMM_MIN_M rows on the step is a dense
+  // contraction for the tensor cores (bf16 operands). Either falls back to the any-shape
+  // kernel (still on the device) when the tiled kernel cannot read the operands.
   if (g.m < AION_CUDA_GEMM_MIN_M) {
-    if (gemv_mma(dev, g.m <= AION_CUDA_GEMV_MAX_M ? g : rows_of(g, 0, AION_CUDA_GEMV_MAX_M), true) == AION_CUDA_OK) {
-      for (uint64_t r0 = 0; r0 < g.m; r0 += AION_CUDA_GEMV_MAX_M) {
-        const uint64_t rows = g.m - r0 < AION_CUDA_GEMV_MAX_M ? g.m - r0 : AION_CUDA_GEMV_MAX_M;
-        if (int32_t st = gemv_mma(dev, rows_of(g, r0, rows), false)) return st;
-      }
-      return AION_CUDA_OK;
-    }
+    const int32_t st = gemv_mma(dev, g, false);
+    if (st != AION_CUDA_UNSUPPORTED) return st;
   } else {
     const int32_t st = gemm_tcgen05(dev, g, false);
     if (st != AION_CUDA_UNSUPPORTED) return st;

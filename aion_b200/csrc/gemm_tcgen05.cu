@@ -57,6 +57,8 @@ struct GemmParams {
   uint64_t ldc;
   float alpha, beta;
   uint32_t m_tiles, n_tiles, k_stages;
+  uint32_t splits;    // K splits per tile (work unit = tile x split); > 1 goes through `partial`
+  float* partial;     // [tile][split][BM][BN] raw accumulators
   int* fault;
 };
 
@@ -251,6 +253,20 @@ __device__ __forceinline__ void dequant_q8_block(uint32_t blk, uint8_t* btile, u
   }
 }
 
+// Work unit u = tile * splits + split; the splits of a tile walk disjoint, nearly equal
+// ranges of the k-stages.
+struct Unit {
+  uint32_t tile, split, ks0, ks1;
+};
+__device__ __forceinline__ Unit unit_of(const GemmParams& p, uint32_t u) {
+  Unit w;
+  w.tile = u / p.splits;
+  w.split = u - w.tile * p.splits;
+  w.ks0 = (uint32_t)((uint64_t)p.k_stages * w.split / p.splits);
+  w.ks1 = (uint32_t)((uint64_t)p.k_stages * (w.split + 1) / p.splits);
+  return w;
+}
+
 template <int DT>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_q_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b) {
@@ -295,16 +311,17 @@ gemm_q_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
-  const uint32_t tiles = p.m_tiles * p.n_tiles;
+  const uint32_t units = p.m_tiles * p.n_tiles * p.splits;
 
   if (warp == 0) {
     // ---- TMA producer of activation tiles ----
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (uint32_t t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
-        const int32_t m0 = (int32_t)((t % p.m_tiles) * BM);
-        for (uint32_t ks = 0; ks < p.k_stages; ks++, it++) {
+      for (uint32_t u = blockIdx.x; u < units && ok; u += gridDim.x) {
+        const Unit w = unit_of(p, u);
+        const int32_t m0 = (int32_t)((w.tile % p.m_tiles) * BM);
+        for (uint32_t ks = w.ks0; ks < w.ks1; ks++, it++) {
           const uint32_t s = it % AS, use = it / AS;
           if (use > 0 && !wait_or_abort<true>(&bars->a_empty[s], (use - 1) & 1, abort_flag)) {
             raise_abort(p.fault, abort_flag);
@@ -322,9 +339,10 @@ gemm_q_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (uint32_t t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
-        const int32_t n0 = (int32_t)((t / p.m_tiles) * BN);
-        for (uint32_t ks = 0; ks < p.k_stages; ks++, it++) {
+      for (uint32_t u = blockIdx.x; u < units && ok; u += gridDim.x) {
+        const Unit w = unit_of(p, u);
+        const int32_t n0 = (int32_t)((w.tile / p.m_tiles) * BN);
+        for (uint32_t ks = w.ks0; ks < w.ks1; ks++, it++) {
           const uint32_t s = it % PS, use = it / PS;
           if (use > 0 && !wait_or_abort<true>(&bars->p_empty[s], (use - 1) & 1, abort_flag)) {
             raise_abort(p.fault, abort_flag);
@@ -341,7 +359,8 @@ gemm_q_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm
     // ---- MMA issuer ----
     uint32_t it = 0, tile_iter = 0;
     bool ok = true;
-    for (uint32_t t = blockIdx.x; t < tiles && ok; t += gridDim.x, tile_iter++) {
+    for (uint32_t u = blockIdx.x; u < units && ok; u += gridDim.x, tile_iter++) {
+      const Unit w = unit_of(p, u);
       const uint32_t acc = tile_iter & 1, acc_use = tile_iter >> 1;
       if (acc_use > 0 && !wait_or_abort<true>(&bars->acc_empty[acc], (acc_use - 1) & 1, abort_flag)) {
         if (lane == 0) raise_abort(p.fault, abort_flag);
@@ -349,7 +368,7 @@ gemm_q_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm
       }
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + acc * BN;
-      for (uint32_t ks = 0; ks < p.k_stages; ks++, it++) {
+      for (uint32_t ks = w.ks0; ks < w.ks1; ks++, it++) {
         const uint32_t sa = it % AS, pha = (it / AS) & 1, sb = it % BS, phb = (it / BS) & 1;
         if (!wait_or_abort<true>(&bars->a_full[sa], pha, abort_flag) || !wait_or_abort<true>(&bars->bready[sb], phb, abort_flag)) {
           if (lane == 0) raise_abort(p.fault, abort_flag);
@@ -363,7 +382,7 @@ gemm_q_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm
 #pragma unroll
           for (int kk = 0; kk < BK / UMMA_K; kk++)
             umma_bf16(d_tmem, a_desc + (uint64_t)(kk * UMMA_K * 2 / 16), b_desc + (uint64_t)(kk * UMMA_K * 2 / 16), kInstrDesc,
-                      (ks | (uint32_t)kk) != 0);
+                      ((ks - w.ks0) | (uint32_t)kk) != 0);
           umma_commit(ptx::smem_u32(&bars->a_empty[sa]));
           umma_commit(ptx::smem_u32(&bars->bfree[sb]));
         }
@@ -381,8 +400,9 @@ gemm_q_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm
     const uint32_t dw = warp - DEQ_WARP0, group = dw / GROUP_WARPS, j0 = (dw % GROUP_WARPS) * 32 + lane;
     uint32_t it = 0;
     bool ok = true;
-    for (uint32_t t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
-      for (uint32_t ks = 0; ks < p.k_stages; ks++, it++) {
+    for (uint32_t u = blockIdx.x; u < units && ok; u += gridDim.x) {
+      const Unit w = unit_of(p, u);
+      for (uint32_t ks = w.ks0; ks < w.ks1; ks++, it++) {
         if (it % DEQ_GROUPS != group) continue;
         const uint32_t sp = it % PS, php = (it / PS) & 1, sb = it % BS, buse = it / BS;
         if (!wait_or_abort<true>(&bars->p_full[sp], php, abort_flag) ||
@@ -415,37 +435,59 @@ gemm_q_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm
     // ---- epilogue: warp w may touch TMEM lanes 32*(w%4) .. +31 ----
     const uint32_t quarter = warp & 3;
     uint32_t tile_iter = 0;
-    for (uint32_t t = blockIdx.x; t < tiles; t += gridDim.x, tile_iter++) {
+    for (uint32_t u = blockIdx.x; u < units; u += gridDim.x, tile_iter++) {
+      const Unit w = unit_of(p, u);
       const uint32_t acc = tile_iter & 1, acc_use = tile_iter >> 1;
       if (!wait_or_abort(&bars->acc_full[acc], acc_use & 1, abort_flag)) {
         if (lane == 0) raise_abort(p.fault, abort_flag);
         break;
       }
       tc_fence_after();
-      const uint32_t m0 = (t % p.m_tiles) * BM, n0 = (t / p.m_tiles) * BN;
-      const uint32_t row = m0 + quarter * 32 + lane;
+      const uint32_t m0 = (w.tile % p.m_tiles) * BM, n0 = (w.tile / p.m_tiles) * BN;
+      const uint32_t trow = quarter * 32 + lane, row = m0 + trow;
       float* crow = p.c + (uint64_t)row * p.ldc + n0;
       const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + acc * BN;
+      if (p.splits == 1) {
+#pragma unroll 1
+        for (uint32_t c0 = 0; c0 < BN; c0 += 16) {
+          uint32_t r[16];
+          tmem_ld16(taddr + c0, r);
+          tmem_ld_wait();
+          if (row < p.m) {
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+              const uint32_t col = n0 + c0 + q * 4;
+              if (col < p.n) {  // n is a multiple of 8, so a group of 4 is in or out as a whole
+                float4 v = make_float4(__uint_as_float(r[4 * q]) * p.alpha, __uint_as_float(r[4 * q + 1]) * p.alpha,
+                                       __uint_as_float(r[4 * q + 2]) * p.alpha, __uint_as_float(r[4 * q + 3]) * p.alpha);
+                float4* dst = reinterpret_cast<float4*>(crow + c0 + q * 4);
+                if (p.beta != 0.0f) {
+                  const float4 o = *dst;
+                  v.x += p.beta * o.x, v.y += p.beta * o.y, v.z += p.beta * o.z, v.w += p.beta * o.w;
+                }
+                *dst = v;
+              }
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars->acc_empty[acc]));
+        continue;
+      }
+      // Split K: leave the raw accumulator in this unit's slot; a follow-up kernel adds the
+      // slots of every tile in split order, so the sum does not depend on timing.
+      float* slot = p.partial + ((size_t)w.tile * p.splits + w.split) * (BM * BN) + (size_t)trow * BN;
 #pragma unroll 1
       for (uint32_t c0 = 0; c0 < BN; c0 += 16) {
         uint32_t r[16];
         tmem_ld16(taddr + c0, r);
         tmem_ld_wait();
-        if (row < p.m) {
+        if (row < p.m && n0 + c0 < p.n) {
 #pragma unroll
-          for (int q = 0; q < 4; q++) {
-            const uint32_t col = n0 + c0 + q * 4;
-            if (col < p.n) {  // n is a multiple of 8, so a group of 4 is in or out as a whole
-              float4 v = make_float4(__uint_as_float(r[4 * q]) * p.alpha, __uint_as_float(r[4 * q + 1]) * p.alpha,
-                                     __uint_as_float(r[4 * q + 2]) * p.alpha, __uint_as_float(r[4 * q + 3]) * p.alpha);
-              float4* dst = reinterpret_cast<float4*>(crow + c0 + q * 4);
-              if (p.beta != 0.0f) {
-                const float4 o = *dst;
-                v.x += p.beta * o.x, v.y += p.beta * o.y, v.z += p.beta * o.z, v.w += p.beta * o.w;
-              }
-              *dst = v;
-            }
-          }
+          for (int q = 0; q < 4; q++)
+            __stcg(reinterpret_cast<float4*>(slot + c0 + q * 4), make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                                                               __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3])));
         }
       }
       tc_fence_before();
@@ -462,8 +504,43 @@ gemm_q_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm
   }
 }
 
+// C = alpha * sum over splits (in split order) + beta * C for the split-K path; one thread per
+// four adjacent columns, so both the partial reads and the C accesses are coalesced.
+__global__ void splitk_reduce_kernel(const GemmParams p) {
+  const uint64_t quads_per_row = p.n / 4, total = (uint64_t)p.m * quads_per_row;
+  const size_t slot = (size_t)BM * BN;
+  for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+    const uint32_t row = (uint32_t)(i / quads_per_row), col = (uint32_t)(i % quads_per_row) * 4;
+    const uint32_t tile = (row / BM) + (col / BN) * p.m_tiles;
+    const float* src = p.partial + (size_t)tile * p.splits * slot + (size_t)(row % BM) * BN + (col % BN);
+    float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    uint32_t sp = 0;
+    for (; sp + 4 <= p.splits; sp += 4) {  // four loads in flight, added in split order
+      const float4 x0 = __ldcg(reinterpret_cast<const float4*>(src + (size_t)(sp + 0) * slot));
+      const float4 x1 = __ldcg(reinterpret_cast<const float4*>(src + (size_t)(sp + 1) * slot));
+      const float4 x2 = __ldcg(reinterpret_cast<const float4*>(src + (size_t)(sp + 2) * slot));
+      const float4 x3 = __ldcg(reinterpret_cast<const float4*>(src + (size_t)(sp + 3) * slot));
+      v.x = (((v.x + x0.x) + x1.x) + x2.x) + x3.x;
+      v.y = (((v.y + x0.y) + x1.y) + x2.y) + x3.y;
+      v.z = (((v.z + x0.z) + x1.z) + x2.z) + x3.z;
+      v.w = (((v.w + x0.w) + x1.w) + x2.w) + x3.w;
+    }
+    for (; sp < p.splits; sp++) {
+      const float4 x = __ldcg(reinterpret_cast<const float4*>(src + (size_t)sp * slot));
+      v.x += x.x, v.y += x.y, v.z += x.z, v.w += x.w;
+    }
+    v.x *= p.alpha, v.y *= p.alpha, v.z *= p.alpha, v.w *= p.alpha;
+    float4* dst = reinterpret_cast<float4*>(p.c + (uint64_t)row * p.ldc + col);
+    if (p.beta != 0.0f) {
+      const float4 o = *dst;
+      v.x += p.beta * o.x, v.y += p.beta * o.y, v.z += p.beta * o.z, v.w += p.beta * o.w;
+    }
+    *dst = v;
+  }
+}
+
 template <int DT>
-int32_t launch_gemm(AionCudaDevice* dev, const MatMulArgs& g, const __nv_bfloat16* a_bf16) {
+int32_t launch_gemm(AionCudaDevice* dev, const MatMulArgs& g, const __nv_bfloat16* a_bf16, uint32_t splits, float* partial) {
   using G = GemmGeom<DT>;
   static bool configured[64] = {};
   auto kernel = gemm_q_tcgen05_kernel<DT>;
@@ -490,10 +567,18 @@ int32_t launch_gemm(AionCudaDevice* dev, const MatMulArgs& g, const __nv_bfloat1
   p.n_tiles = (uint32_t)ceil_div(g.n, (uint64_t)BN);
   p.k_stages = (uint32_t)ceil_div(g.k, (uint64_t)BK);
   p.fault = dev->fault_dev;
-  const uint32_t tiles = p.m_tiles * p.n_tiles;
-  const uint32_t grid = tiles < (uint32_t)dev->sm_count ? tiles : (uint32_t)dev->sm_count;
+  p.splits = splits;
+  p.partial = partial;
+  const uint32_t units = p.m_tiles * p.n_tiles * splits;
+  const uint32_t grid = units < (uint32_t)dev->sm_count ? units : (uint32_t)dev->sm_count;
   kernel<<<grid, THREADS, G::SMEM_BYTES, dev->stream>>>(p, tmap_a, tmap_b);
   AION_CUDA_TRY(cudaGetLastError());
+  if (splits > 1) {
+    const uint64_t quads = (uint64_t)g.m * (g.n / 4);
+    const unsigned blocks = (unsigned)std::min<uint64_t>(ceil_div(quads, (uint64_t)256), (uint64_t)dev->sm_count * 8);
+    splitk_reduce_kernel<<<blocks, 256, 0, dev->stream>>>(p);
+    AION_CUDA_TRY(cudaGetLastError());
+  }
   return AION_CUDA_OK;
 }
 
@@ -508,10 +593,22 @@ int32_t gemm_tcgen05(AionCudaDevice* dev, const MatMulArgs& g, bool forced) {
   if (g.m == 0 || g.n == 0) return AION_CUDA_OK;
   if ((g.n & 7) || (g.ldb & 7) || ((uintptr_t)g.b & 15) || ((uintptr_t)g.c & 15) || (g.ldc & 3)) return AION_CUDA_UNSUPPORTED;
   if (g.m > (1u << 24) || g.n > (1u << 24) || g.k > (1u << 24)) return AION_CUDA_UNSUPPORTED;
-  // bf16 copy of the activation in lane scratch.
-  const size_t a_bytes = (size_t)g.m * g.k * sizeof(__nv_bfloat16);
-  if (int32_t st = dev->reserve_scratch(a_bytes)) return st;
+  // Few output tiles (decode batches against narrow layers): split K so the SMs are covered.
+  // A split keeps at least two k-stages; its raw 128 x 256 accumulator goes through scratch.
+  const uint64_t tiles = ceil_div(g.m, (uint64_t)BM) * ceil_div(g.n, (uint64_t)BN), k_stages = ceil_div(g.k, (uint64_t)BK);
+  uint64_t splits = 1;
+  if (tiles * 2 <= (uint64_t)dev->sm_count) {
+    splits = (uint64_t)dev->sm_count / tiles;
+    if (splits > k_stages / 2) splits = k_stages / 2;
+    if (splits > 16) splits = 16;
+    if (splits < 1) splits = 1;
+  }
+  // Lane scratch: the bf16 copy of the activation, then the split partials.
+  const size_t a_bytes = ((size_t)g.m * g.k * sizeof(__nv_bfloat16) + 1023) & ~size_t(1023);
+  const size_t part_bytes = splits > 1 ? (size_t)tiles * splits * BM * BN * sizeof(float) : 0;
+  if (int32_t st = dev->reserve_scratch(a_bytes + part_bytes)) return st;
   __nv_bfloat16* a_bf16 = static_cast<__nv_bfloat16*>(dev->lane_scratch());
+  float* partial = reinterpret_cast<float*>(static_cast<uint8_t*>(dev->lane_scratch()) + a_bytes);
   {
     const uint64_t groups = g.m * (g.k / 8);
     const unsigned blocks = (unsigned)std::min<uint64_t>(ceil_div(groups, (uint64_t)256), (uint64_t)dev->sm_count * 8);
@@ -519,8 +616,8 @@ int32_t gemm_tcgen05(AionCudaDevice* dev, const MatMulArgs& g, bool forced) {
                                                            g.dtype == AION_CUDA_DTYPE_Q4_0 ? 1 : 0);
     AION_CUDA_TRY(cudaGetLastError());
   }
-  return g.dtype == AION_CUDA_DTYPE_Q4_0 ? launch_gemm<AION_CUDA_DTYPE_Q4_0>(dev, g, a_bf16)
-                                         : launch_gemm<AION_CUDA_DTYPE_Q8_0>(dev, g, a_bf16);
+  return g.dtype == AION_CUDA_DTYPE_Q4_0 ? launch_gemm<AION_CUDA_DTYPE_Q4_0>(dev, g, a_bf16, (uint32_t)splits, partial)
+                                         : launch_gemm<AION_CUDA_DTYPE_Q8_0>(dev, g, a_bf16, (uint32_t)splits, partial);
 }
 
 }  // namespace aion

@@ -195,9 +195,21 @@ __device__ __forceinline__ uint32_t unit_owner(uint64_t u, uint64_t U, uint64_t 
 // DT: weight dtype; NT: weights are [n,k] row-major (else K-major); MT: 8-row activation
 // tiles (1 or 2); M1: exactly one activation row (skips the odd-row half of the epilogue).
 template <int DT, bool NT, int MT, bool M1>
-__global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tmap) {
+__global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_in, const __grid_constant__ CUtensorMap tmap) {
   using G = Geom<DT, NT>;
   constexpr int MPA = 8 * MT;  // activation rows of the accumulator tile
+  // More than 8 * MT rows of A: blockIdx.y picks a group of 8 * MT rows. Every group streams
+  // the same weights (the second and later groups find them in L2), with its own slice of
+  // the fix-up scratch.
+  GemvParams p = p_in;
+  if (gridDim.y > 1) {
+    const uint32_t r0 = blockIdx.y * MPA;
+    p.a += (uint64_t)r0 * p.lda;
+    p.c += (uint64_t)r0 * p.ldc;
+    p.m = min((uint32_t)MPA, p.m - r0);
+    p.partials += (size_t)blockIdx.y * gridDim.x * 2 * TN * MPA;
+    p.tickets += (size_t)blockIdx.y * p.tiles * CONSUMER_WARPS;
+  }
   constexpr uint32_t MP2 = M1 ? 2 : 8 * MT;  // activation rows held in shared memory
   extern __shared__ __align__(128) uint8_t smem[];
   const uint32_t smem_base = ptx::smem_u32(smem);
@@ -537,9 +549,12 @@ int32_t launch(AionCudaDevice* dev, GemvParams p, const uint8_t* b, uint64_t ldb
     if (grid > p.units) grid = p.units;
   }
 
-  // Scratch for tiles shared by several CTAs: two partial slots per CTA, one ticket per (tile, warp).
+  // Scratch for tiles shared by several CTAs: two partial slots per CTA, one ticket per (tile, warp),
+  // times the groups of 8 * MT rows.
   constexpr int MPA = 8 * MT;
-  if (int32_t st = dev->reserve_gemv_fixup((size_t)grid * 2 * TN * MPA * sizeof(float), (size_t)p.tiles * CONSUMER_WARPS)) return st;
+  const uint64_t groups = M1 ? 1 : ceil_div((uint64_t)p.m, (uint64_t)MPA);
+  if (groups > 65535) return fail(AION_CUDA_UNSUPPORTED, "gemv: too many rows for one launch");
+  if (int32_t st = dev->reserve_gemv_fixup((size_t)groups * grid * 2 * TN * MPA * sizeof(float), (size_t)groups * p.tiles * CONSUMER_WARPS)) return st;
   p.partials = dev->lane_gemv_partials();
   p.tickets = dev->lane_gemv_tickets();
 
@@ -567,7 +582,7 @@ int32_t launch(AionCudaDevice* dev, GemvParams p, const uint8_t* b, uint64_t ldb
   }
 
   cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3((unsigned)grid);
+  cfg.gridDim = dim3((unsigned)grid, (unsigned)groups);
   cfg.blockDim = dim3(THREADS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = dev->stream;
@@ -590,7 +605,7 @@ int32_t launch_m(AionCudaDevice* dev, const GemvParams& p, const uint8_t* b, uin
 }  // namespace
 
 int32_t gemv_mma(AionCudaDevice* dev, const MatMulArgs& g, bool probe_only) {
-  if (g.m > 16 || g.k == 0) return AION_CUDA_UNSUPPORTED;
+  if (g.m > 16ull * 65535 || g.k == 0) return AION_CUDA_UNSUPPORTED;
   if (g.n > 0x7FFFFFFFull - TN || g.k / QK > 0x7FFFFFFFull) return AION_CUDA_UNSUPPORTED;
   const uint64_t kblocks = g.k / QK;
   const uintptr_t baddr = reinterpret_cast<uintptr_t>(g.b);

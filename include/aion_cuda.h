@@ -158,13 +158,13 @@ AION_CUDA_API int32_t aion_cuda_memset(AionCudaDevice* dev, uint64_t handle, siz
  *   C f32, row stride ldc elements (0 = n).
  * The activation is quantized to int8 per 32-block exactly as the reference CPU
  * kernels do (aion src/aion/backend/cpu/kernels/matmul_q_i8.zig:187-203) for
- * m < AION_CUDA_GEMM_MIN_M (in passes of AION_CUDA_GEMV_MAX_M rows); larger m runs the
+ * m < AION_CUDA_GEMM_MIN_M (in groups of AION_CUDA_GEMV_MAX_M rows inside one launch); larger m runs the
  * tensor-core prefill GEMM, which dequantizes B to bf16 and rounds A to bf16 (results
  * within rel-L2 1e-2 of the int8-activation arithmetic instead of 1e-3).
  * f32 / f16 B return UNSUPPORTED.
  * --------------------------------------------------------------------------------- */
-#define AION_CUDA_GEMV_MAX_M 16 /* rows of A one GEMV pass takes */
-#define AION_CUDA_GEMM_MIN_M 33 /* from this many rows on, the tensor-core GEMM (bf16 operands) runs */
+#define AION_CUDA_GEMV_MAX_M 16  /* rows of A one group of GEMV CTAs takes */
+#define AION_CUDA_GEMM_MIN_M 33  /* from this many rows on, the tensor-core GEMM (bf16 operands) runs */
 
 typedef struct AionCudaMatMul {
   AionCudaOperand c, a, b;

@@ -77,6 +77,19 @@ def test_gemm_prefill_shape_auto_route(backend, dtype):
     assert np.array_equal(got2, 2.0 * got)
 
 
+@pytest.mark.parametrize("dtype", [capi.DTYPE_Q4_0, capi.DTYPE_Q8_0])
+@pytest.mark.parametrize("m,n,k", [(64, 256, 1536), (40, 1536, 2048), (512, 256, 1536), (130, 264, 8192)])
+def test_gemm_split_k_shapes(backend, dtype, m, n, k):
+    # few output tiles: K is split over CTAs and reduced in split order
+    a, b = make(dtype, m, n, k, seed=21)
+    c0 = np.random.default_rng(3).standard_normal(m * n).astype(np.float32)
+    got = run_matmul(backend, dtype, a, b, m, n, k, alpha=0.75, beta=0.5, c=c0, flags=capi.MATMUL_FORCE_GEMM)
+    want = oracle.matmul_deqf32(dtype, a, b, m, n, k, alpha=0.75, beta=0.5, c=c0).reshape(m, n)
+    assert rel_l2(got, want) <= TOL_DEQ
+    again = run_matmul(backend, dtype, a, b, m, n, k, alpha=0.75, beta=0.5, c=c0, flags=capi.MATMUL_FORCE_GEMM)
+    assert np.array_equal(got, again)
+
+
 def test_gemm_is_deterministic(backend):
     m, n, k = 256, 1024, 512
     a, b = make(capi.DTYPE_Q4_0, m, n, k, seed=11)
@@ -85,9 +98,10 @@ def test_gemm_is_deterministic(backend):
     assert np.array_equal(x, y)
 
 
-def test_rows_between_gemv_and_gemm_keep_int8_arithmetic(backend):
-    # 17..32 rows run as GEMV passes of 16 rows: reference CPU arithmetic, tight bound.
-    m, n, k = 29, 264, 256
+@pytest.mark.parametrize("m", [17, 29, 32])
+def test_rows_between_gemv_and_gemm_keep_int8_arithmetic(backend, m):
+    # 17..32 rows run as two groups of 16 rows in one GEMV launch: reference CPU arithmetic, tight bound.
+    n, k = 264, 256
     a, b = make(capi.DTYPE_Q4_0, m, n, k, seed=5)
     got = run_matmul(backend, capi.DTYPE_Q4_0, a, b, m, n, k)
     want = oracle.matmul_q(capi.DTYPE_Q4_0, a, b, m, n, k).reshape(m, n)

@@ -46,8 +46,6 @@ def test_nt_grouped_fixture_every_order(backend, order, group, m):
 def test_weight_layout_arithmetic_fixture(backend, m, flags):
     # src/aion/graph/opt/test_opt.zig:1106-1175: NMSE < 1e-10 vs the f64 int8 reference
     m, n, k, a, w = rd.weight_layout_arith_case(m)
-    if flags == capi.MATMUL_FORCE_GEMV and m > capi.GEMV_MAX_M:
-        pytest.skip("the tiled GEMV takes m <= 16")
     b = oracle.quantize(oracle.Q8_0, w, 0)
     want = rd.int8_reference_f64(a, b, m, n, k, nt=False)
     got = run_matmul(backend, capi.DTYPE_Q8_0, a, b, m, n, k, flags=flags)

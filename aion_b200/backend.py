@@ -153,6 +153,9 @@ class TensorMeta:
     block_order: int = capi.ORDER_ROW_MAJOR
     # SequenceCachePolicyKind (src/aion/runtime/tensor_store.zig:9-13): "none" | "growable" | "rolling"
     cache_policy: str = "none"
+    # Elements between consecutive rows (rows = all leading dims folded) of a view whose rows
+    # are slices of a wider buffer; 0 = dense. Only the steps that say so accept such views.
+    row_stride: int = 0
 
     @property
     def rank(self) -> int:
@@ -160,6 +163,9 @@ class TensorMeta:
 
     def nbytes(self) -> int:
         n = int(np.prod(self.shape, dtype=np.int64)) if self.shape else 1
+        if self.row_stride and self.shape:
+            cols = int(self.shape[-1])
+            n = (n // cols - 1) * self.row_stride + cols
         if self.dtype in BLOCK_BYTES:
             return n // 32 * BLOCK_BYTES[self.dtype]
         return n * DTYPE_BYTES[self.dtype]
@@ -229,6 +235,13 @@ class DeviceStore:
         else:
             np_dt = {capi.DTYPE_F32: np.float32, capi.DTYPE_F16: np.float16, capi.DTYPE_I8: np.int8,
                      capi.DTYPE_I32: np.int32}[meta.dtype]
+            if meta.row_stride:
+                cols = int(meta.shape[-1])
+                rows = int(np.prod(meta.shape)) // cols
+                raw = np.empty((rows - 1) * meta.row_stride + cols, dtype=np_dt)
+                self.memory.copy_d2h(raw, ch.handle, ch.offset)
+                idx = (np.arange(rows)[:, None] * meta.row_stride + np.arange(cols)[None, :]).reshape(-1)
+                return raw[idx].reshape(meta.shape)
             out = np.empty(meta.shape, dtype=np_dt)
         self.memory.copy_d2h(out, ch.handle, ch.offset)
         return out
@@ -317,6 +330,36 @@ class StepElemwiseBinary:
     out: int
     a: int
     b: int
+
+
+@dataclasses.dataclass
+class StepRMSNormPair:
+    """Fusion of StepRMSNorm(out1, x, gamma1, beta1, eps1, residual) and StepRMSNorm(out2, out1, gamma2, beta2, eps2)."""
+    out1: int
+    out2: int
+    x: int
+    gamma1: int
+    beta1: int
+    gamma2: int
+    beta2: int
+    eps1: float
+    eps2: float
+    residual: Optional[int] = None
+
+
+@dataclasses.dataclass
+class StepRopeKVAppend:
+    """Fusion of RoPE1D(q), RoPE1D(k), Cast(k, v -> f16) and SequenceAppend of both, reading q | k | v
+    from one [B, L, (h_q + 2 h_kv) * head_dim] matmul output (possibly a strided view)."""
+    q_out: int
+    qkv: int
+    positions: int
+    end_index: int
+    k_cache: int
+    v_cache: int
+    base_frequency: float
+    scale_factor: float = 1.0
+    rope_proportion: float = 1.0
 
 
 @dataclasses.dataclass
@@ -409,6 +452,13 @@ class CudaSession:
             return reads, {step.out}
         if isinstance(step, StepElemwiseBinary):
             return {step.a, step.b}, {step.out}
+        if isinstance(step, StepRMSNormPair):
+            reads = {step.x, step.gamma1, step.beta1, step.gamma2, step.beta2}
+            reads |= {step.residual} if step.residual is not None else set()
+            return reads, {step.out1, step.out2}
+        if isinstance(step, StepRopeKVAppend):
+            return ({step.qkv, step.positions, step.end_index, step.k_cache, step.v_cache},
+                    {step.q_out, step.k_cache, step.v_cache})
         if isinstance(step, StepRoPE1D):
             return {step.x, step.positions}, {step.out}
         if isinstance(step, StepCast):
@@ -585,12 +635,60 @@ class CudaSession:
         if s.op not in ops:
             raise BackendError(capi.UNSUPPORTED, f"elemwise: op {s.op!r} is outside this backend")
         om = self._need(s.out, capi.DTYPE_F32, "elemwise")
+        metas = [om]
         for t in (s.a, s.b):
-            if tuple(self._need(t, capi.DTYPE_F32, "elemwise").shape) != tuple(om.shape):
+            m = self._need(t, capi.DTYPE_F32, "elemwise")
+            if tuple(m.shape) != tuple(om.shape):
                 raise BackendError(capi.UNSUPPORTED, "elemwise: only identical shapes are covered")
+            metas.append(m)
+        strided = any(m.row_stride for m in metas)
+        cols = int(om.shape[-1]) if strided else 0
         rec = capi.Elemwise(out=st.acquire_mut(s.out).operand(), a=st.acquire_const(s.a).operand(),
-                            b=st.acquire_const(s.b).operand(), count=int(np.prod(om.shape)), op=ops[s.op], reserved=0)
+                            b=st.acquire_const(s.b).operand(), count=int(np.prod(om.shape)), op=ops[s.op], reserved=0,
+                            cols=cols, ld_out=metas[0].row_stride, ld_a=metas[1].row_stride, ld_b=metas[2].row_stride)
         _check(self._lib.aion_cuda_elemwise(self.backend._h, C.byref(rec)))
+
+    def _rms_norm_pair(self, s: StepRMSNormPair) -> None:
+        st = self.store
+        for t in (s.out1, s.out2, s.x, s.gamma1, s.beta1, s.gamma2, s.beta2):
+            self._need(t, capi.DTYPE_F32, "rms_norm_pair")
+        om, gm = st.meta(s.out1), st.meta(s.gamma1)
+        if gm.rank == 0 or gm.rank > om.rank or tuple(om.shape[om.rank - gm.rank:]) != tuple(gm.shape) or \
+                tuple(st.meta(s.gamma2).shape) != tuple(gm.shape) or tuple(st.meta(s.out2).shape) != tuple(om.shape):
+            raise BackendError(capi.INVALID_ARGUMENT, "rms_norm_pair: shapes do not agree")
+        cols = int(np.prod(gm.shape))
+        rows = int(np.prod(om.shape)) // cols
+        res = capi.Operand(0, 0, 0)
+        if s.residual is not None:
+            self._need(s.residual, capi.DTYPE_F32, "rms_norm_pair.residual")
+            res = st.acquire_const(s.residual).operand()
+        op = lambda t: st.acquire_const(t).operand()
+        rec = capi.RMSNormPair(out1=op(s.out1), out2=op(s.out2), x=op(s.x), gamma1=op(s.gamma1), beta1=op(s.beta1), residual=res,
+                               gamma2=op(s.gamma2), beta2=op(s.beta2), rows=rows, cols=cols, eps1=s.eps1, eps2=s.eps2)
+        _check(self._lib.aion_cuda_rms_norm_pair(self.backend._h, C.byref(rec)))
+
+    def _rope_kv_append(self, s: StepRopeKVAppend) -> None:
+        st = self.store
+        qm = self._need(s.q_out, capi.DTYPE_F32, "rope_kv_append.q_out")
+        xm = self._need(s.qkv, capi.DTYPE_F32, "rope_kv_append.qkv")
+        pm = self._need(s.positions, capi.DTYPE_I32, "rope_kv_append.positions")
+        self._need(s.end_index, capi.DTYPE_I32, "rope_kv_append.end_index")
+        km, vm = self._need(s.k_cache, capi.DTYPE_F16, "rope_kv_append.k_cache"), self._need(s.v_cache, capi.DTYPE_F16, "rope_kv_append.v_cache")
+        if qm.rank != 4 or km.rank != 4 or tuple(km.shape) != tuple(vm.shape) or tuple(pm.shape) != tuple(qm.shape[:2]):
+            raise BackendError(capi.INVALID_ARGUMENT, "rope_kv_append: q_out [B, L, Hq, D], caches [B, T, Hkv, D], positions [B, L]")
+        B, L, Hq, D = qm.shape
+        _, T, Hkv, Dc = km.shape
+        if km.shape[0] != B or Dc != D or xm.shape[-1] != (Hq + 2 * Hkv) * D or int(np.prod(xm.shape[:-1])) != B * L:
+            raise BackendError(capi.INVALID_ARGUMENT, "rope_kv_append: qkv must hold q | k | v per (b, l)")
+        policy = st.sequence_cache_policy_info(s.k_cache)
+        if policy == "growable":
+            raise BackendError(capi.UNSUPPORTED, "rope_kv_append: growable caches are settled by the storage layer, not here")
+        op = lambda t: st.acquire_const(t).operand()
+        rec = capi.RopeKVAppend(q_out=op(s.q_out), qkv=op(s.qkv), positions=op(s.positions), end_index=op(s.end_index),
+                                k_cache=op(s.k_cache), v_cache=op(s.v_cache), batch=B, len=L, h_q=Hq, h_kv=Hkv, head_dim=D,
+                                ld_qkv=xm.row_stride, t_cap=T, base_frequency=s.base_frequency, scale_factor=s.scale_factor,
+                                proportion=s.rope_proportion, rolling=1 if policy == "rolling" else 0)
+        _check(self._lib.aion_cuda_rope_kv_append(self.backend._h, C.byref(rec)))
 
     def _rope(self, s: StepRoPE1D) -> None:
         st = self.store
@@ -661,7 +759,8 @@ class CudaSession:
         rec = capi.ArgMax(out=st.acquire_mut(s.out).operand(), in_=st.acquire_const(s.a).operand(), outer=outer, n=n)
         _check(self._lib.aion_cuda_argmax(self.backend._h, C.byref(rec)))
 
-    _GLUE = {StepRMSNorm: "_rms_norm", StepElemwiseBinary: "_elemwise", StepRoPE1D: "_rope", StepCast: "_cast",
+    _GLUE = {StepRMSNormPair: "_rms_norm_pair", StepRopeKVAppend: "_rope_kv_append",
+             StepRMSNorm: "_rms_norm", StepElemwiseBinary: "_elemwise", StepRoPE1D: "_rope", StepCast: "_cast",
              StepSequenceAppend: "_sequence_append", StepGatherRows: "_gather_rows", StepArgMax: "_argmax"}
 
 

@@ -79,7 +79,23 @@ class RMSNorm(C.Structure):
 
 class Elemwise(C.Structure):
     _fields_ = [("out", Operand), ("a", Operand), ("b", Operand), ("count", C.c_uint64), ("op", C.c_uint32),
-                ("reserved", C.c_uint32)]
+                ("reserved", C.c_uint32), ("cols", C.c_uint64), ("ld_out", C.c_uint64), ("ld_a", C.c_uint64),
+                ("ld_b", C.c_uint64)]
+
+
+class RMSNormPair(C.Structure):
+    _fields_ = [("out1", Operand), ("out2", Operand), ("x", Operand), ("gamma1", Operand), ("beta1", Operand),
+                ("residual", Operand), ("gamma2", Operand), ("beta2", Operand),
+                ("rows", C.c_uint64), ("cols", C.c_uint64), ("eps1", C.c_float), ("eps2", C.c_float)]
+
+
+class RopeKVAppend(C.Structure):
+    _fields_ = [("q_out", Operand), ("qkv", Operand), ("positions", Operand), ("end_index", Operand),
+                ("k_cache", Operand), ("v_cache", Operand),
+                ("batch", C.c_uint64), ("len", C.c_uint64), ("h_q", C.c_uint64), ("h_kv", C.c_uint64),
+                ("head_dim", C.c_uint64), ("ld_qkv", C.c_uint64), ("t_cap", C.c_uint64),
+                ("base_frequency", C.c_float), ("scale_factor", C.c_float), ("proportion", C.c_float),
+                ("rolling", C.c_uint32)]
 
 
 class RoPE(C.Structure):
@@ -149,6 +165,8 @@ SIGNATURES = {
     "aion_cuda_sequence_append": (C.c_int32, [_DEV, C.POINTER(SequenceAppend)]),
     "aion_cuda_gather_rows": (C.c_int32, [_DEV, C.POINTER(GatherRows)]),
     "aion_cuda_argmax": (C.c_int32, [_DEV, C.POINTER(ArgMax)]),
+    "aion_cuda_rms_norm_pair": (C.c_int32, [_DEV, C.POINTER(RMSNormPair)]),
+    "aion_cuda_rope_kv_append": (C.c_int32, [_DEV, C.POINTER(RopeKVAppend)]),
     "aion_cuda_quantize": (C.c_int32, [_DEV, C.c_uint32, _OPP, C.POINTER(C.c_uint64), C.c_uint32, C.c_uint32, _OPP]),
     "aion_cuda_dequantize": (C.c_int32, [_DEV, C.c_uint32, _OPP, C.c_uint64, _OPP]),
     "aion_cuda_relayout_q8": (C.c_int32, [_DEV, C.c_uint32, C.c_uint32, C.c_uint64, C.c_uint64, _OPP, _OPP]),

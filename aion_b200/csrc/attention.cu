@@ -604,7 +604,8 @@ int32_t launch_decode_as(AionCudaDevice* dev, const AttnParams& p, uint32_t unit
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  static const bool no_pdl_main = std::getenv("AION_CUDA_NO_PDL_MAIN") != nullptr;  // tuning only
+  cfg.numAttrs = no_pdl_main ? 0 : 1;
   AION_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, p, tk, tv));
   return AION_CUDA_OK;
 }

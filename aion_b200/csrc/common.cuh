@@ -2,6 +2,8 @@
 // block-format helpers every kernel file uses.
 #pragma once
 
+#include <cstdlib>
+
 #include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -134,6 +136,28 @@ int32_t tensor_map_bf16_sw128(const void* base, uint64_t rows, uint64_t cols, ui
 // The same for either 16-bit float type (bf16 or f16).
 int32_t tensor_map_16bit_sw128(const void* base, bool bf16, uint64_t rows, uint64_t cols, uint64_t pitch_bytes, uint32_t box_cols,
                                uint32_t box_rows, CUtensorMap* out);
+
+// Launch with programmatic stream serialization: the kernel may be scheduled while its
+// predecessor in the stream is still draining, which hides the launch latency of the chains
+// of small kernels a decode step is made of. Such a kernel calls ptx::pdl_wait() before it
+// reads anything an earlier kernel wrote (the wait returns when the predecessors have
+// completed and their writes are visible) and ptx::pdl_launch_dependents() to let its own
+// successor start early.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  static const bool plain = std::getenv("AION_CUDA_PDL_GLUE") == nullptr;  // tuning: set to overlap launches of the small kernels too
+  cfg.numAttrs = plain ? 0 : 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 // ---- step implementations, one per kernel file ------------------------------------
 int32_t quantize_activation_rows(AionCudaDevice* dev, const float* a, uint64_t m, uint64_t k, uint64_t lda,

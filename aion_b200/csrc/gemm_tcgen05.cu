@@ -92,6 +92,8 @@ struct GemmGeom {
 // e0 e4 e1 e5 e2 e6 e3 e7 in which a word of q4 nibbles unpacks two at a time.
 __global__ void convert_a_bf16_kernel(const float* __restrict__ a, uint64_t lda, __nv_bfloat16* __restrict__ out, uint32_t m,
                                       uint32_t k, int permute) {
+  ptx::pdl_launch_dependents();
+  ptx::pdl_wait();
   const uint64_t groups = (uint64_t)m * (k / 8);
   for (uint64_t gi = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; gi < groups; gi += (uint64_t)gridDim.x * blockDim.x) {
     const uint32_t r = (uint32_t)(gi / (k / 8)), g8 = (uint32_t)(gi % (k / 8));
@@ -310,6 +312,10 @@ gemm_q_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  // Everything above touched only this CTA's shared and tensor memory; the activation (and,
+  // in a recorded program, possibly C) comes from earlier kernels.
+  ptx::pdl_launch_dependents();
+  ptx::pdl_wait();
   const uint32_t tmem_base = bars->tmem_base;
   const uint32_t units = p.m_tiles * p.n_tiles * p.splits;
 
@@ -507,6 +513,8 @@ gemm_q_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm
 // C = alpha * sum over splits (in split order) + beta * C for the split-K path; one thread per
 // four adjacent columns, so both the partial reads and the C accesses are coalesced.
 __global__ void splitk_reduce_kernel(const GemmParams p) {
+  ptx::pdl_launch_dependents();
+  ptx::pdl_wait();
   const uint64_t quads_per_row = p.n / 4, total = (uint64_t)p.m * quads_per_row;
   const size_t slot = (size_t)BM * BN;
   for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
@@ -571,13 +579,11 @@ int32_t launch_gemm(AionCudaDevice* dev, const MatMulArgs& g, const __nv_bfloat1
   p.partial = partial;
   const uint32_t units = p.m_tiles * p.n_tiles * splits;
   const uint32_t grid = units < (uint32_t)dev->sm_count ? units : (uint32_t)dev->sm_count;
-  kernel<<<grid, THREADS, G::SMEM_BYTES, dev->stream>>>(p, tmap_a, tmap_b);
-  AION_CUDA_TRY(cudaGetLastError());
+  AION_CUDA_TRY(launch_pdl(kernel, dim3(grid), dim3(THREADS), (size_t)G::SMEM_BYTES, dev->stream, p, tmap_a, tmap_b));
   if (splits > 1) {
     const uint64_t quads = (uint64_t)g.m * (g.n / 4);
     const unsigned blocks = (unsigned)std::min<uint64_t>(ceil_div(quads, (uint64_t)256), (uint64_t)dev->sm_count * 8);
-    splitk_reduce_kernel<<<blocks, 256, 0, dev->stream>>>(p);
-    AION_CUDA_TRY(cudaGetLastError());
+    AION_CUDA_TRY(launch_pdl(splitk_reduce_kernel, dim3(blocks), dim3(256), 0, dev->stream, p));
   }
   return AION_CUDA_OK;
 }
@@ -612,9 +618,8 @@ int32_t gemm_tcgen05(AionCudaDevice* dev, const MatMulArgs& g, bool forced) {
   {
     const uint64_t groups = g.m * (g.k / 8);
     const unsigned blocks = (unsigned)std::min<uint64_t>(ceil_div(groups, (uint64_t)256), (uint64_t)dev->sm_count * 8);
-    convert_a_bf16_kernel<<<blocks, 256, 0, dev->stream>>>(g.a, g.lda, a_bf16, (uint32_t)g.m, (uint32_t)g.k,
-                                                           g.dtype == AION_CUDA_DTYPE_Q4_0 ? 1 : 0);
-    AION_CUDA_TRY(cudaGetLastError());
+    AION_CUDA_TRY(launch_pdl(convert_a_bf16_kernel, dim3(blocks), dim3(256), 0, dev->stream, g.a, g.lda, a_bf16, (uint32_t)g.m, (uint32_t)g.k,
+                             g.dtype == AION_CUDA_DTYPE_Q4_0 ? 1 : 0));
   }
   return g.dtype == AION_CUDA_DTYPE_Q4_0 ? launch_gemm<AION_CUDA_DTYPE_Q4_0>(dev, g, a_bf16, (uint32_t)splits, partial)
                                          : launch_gemm<AION_CUDA_DTYPE_Q8_0>(dev, g, a_bf16, (uint32_t)splits, partial);

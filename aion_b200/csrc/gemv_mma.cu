@@ -590,7 +590,8 @@ int32_t launch(AionCudaDevice* dev, GemvParams p, const uint8_t* b, uint64_t ldb
   attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attrs[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attrs;
-  cfg.numAttrs = 1;
+  static const bool no_pdl_main = std::getenv("AION_CUDA_NO_PDL_MAIN") != nullptr;  // tuning only
+  cfg.numAttrs = no_pdl_main ? 0 : 1;
   AION_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, p, *tm));
   return AION_CUDA_OK;
 }

@@ -11,6 +11,7 @@
 #include <cmath>
 
 #include "common.cuh"
+#include "ptx.cuh"
 #include "quant_device.cuh"
 
 namespace aion {
@@ -53,6 +54,8 @@ constexpr int RMS_THREADS = 128;
 __global__ void __launch_bounds__(RMS_THREADS) rms_norm_kernel(float* out, const float* x, const float* __restrict__ gamma,
                                                                const float* __restrict__ beta, const float* residual,
                                                                uint64_t cols, float eps, int* fault) {
+  ptx::pdl_launch_dependents();
+  ptx::pdl_wait();
   const uint64_t r = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const float* xr = x + r * cols;
@@ -82,21 +85,30 @@ __global__ void __launch_bounds__(RMS_THREADS) rms_norm_kernel(float* out, const
 }
 
 // ---- elementwise ----------------------------------------------------------------------
-__global__ void elemwise_kernel(float* out, const float* a, const float* b, uint64_t n,
-                                uint32_t op) {
+__global__ void elemwise_kernel(float* out, const float* a, const float* b, uint64_t n, uint32_t op, uint64_t cols, uint64_t ld_out,
+                                uint64_t ld_a, uint64_t ld_b) {
+  ptx::pdl_launch_dependents();
+  ptx::pdl_wait();
   for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
-    const float av = a[i], bv = b[i];
+    uint64_t io = i, ia = i, ib = i;
+    if (cols) {
+      const uint64_t r = i / cols, c = i - r * cols;
+      io = r * ld_out + c, ia = r * ld_a + c, ib = r * ld_b + c;
+    }
+    const float av = a[ia], bv = b[ib];
     float v;
     if (op == AION_CUDA_ELEMWISE_ADD) v = av + bv;
     else if (op == AION_CUDA_ELEMWISE_MUL) v = av * bv;
     else v = gelu_approx(av) * bv;
-    out[i] = v;
+    out[io] = v;
   }
 }
 
 // ---- RoPE: one thread per (b, l, pair); the rotation is reused by every head ----------
 __global__ void rope_kernel(float* out, const float* x, const int32_t* __restrict__ pos, uint64_t bl,
                             uint32_t heads, uint32_t d, uint32_t rope_pairs, float step, float scale_factor) {
+  ptx::pdl_launch_dependents();
+  ptx::pdl_wait();
   const uint32_t pairs_total = d / 2;
   const uint64_t idx = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x;
   if (idx >= bl * pairs_total) return;
@@ -128,10 +140,14 @@ __global__ void rope_kernel(float* out, const float* x, const int32_t* __restric
 
 // ---- cast -----------------------------------------------------------------------------
 __global__ void cast_f32_f16_kernel(__half* __restrict__ out, const float* __restrict__ in, uint64_t n) {
+  ptx::pdl_launch_dependents();
+  ptx::pdl_wait();
   for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x)
     out[i] = __float2half_rn(in[i]);
 }
 __global__ void cast_f16_f32_kernel(float* __restrict__ out, const __half* __restrict__ in, uint64_t n) {
+  ptx::pdl_launch_dependents();
+  ptx::pdl_wait();
   for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x)
     out[i] = __half2float(in[i]);
 }
@@ -140,6 +156,8 @@ __global__ void cast_f16_f32_kernel(float* __restrict__ out, const __half* __res
 __global__ void sequence_append_kernel(uint16_t* __restrict__ cache, const uint16_t* __restrict__ new_kv,
                                        const int32_t* __restrict__ end_index, uint64_t t_cap, uint64_t row_units,
                                        uint64_t new_len, int rolling, int* fault) {
+  ptx::pdl_launch_dependents();
+  ptx::pdl_wait();
   const uint64_t b = blockIdx.x / new_len, t = blockIdx.x % new_len;
   const int32_t e = end_index[b];
   // The whole request is rejected if any of its steps is out of range, like the
@@ -159,6 +177,8 @@ __global__ void sequence_append_kernel(uint16_t* __restrict__ cache, const uint1
 __global__ void gather_rows_q8_kernel(float* __restrict__ out, const uint8_t* __restrict__ table,
                                       const int32_t* __restrict__ indices, uint64_t table_rows, uint64_t d, int group, int chunk,
                                       int* fault) {
+  ptx::pdl_launch_dependents();
+  ptx::pdl_wait();
   const uint64_t i = blockIdx.x;
   long long v = indices[i];
   if (v < 0) v += (long long)table_rows;
@@ -213,6 +233,8 @@ __device__ __forceinline__ void argmax_block_reduce(float& bv, int& bi) {
 // scratch; the last block of a row to finish (a ticket) picks among the candidates.
 __global__ void argmax_kernel(int32_t* __restrict__ out, const float* __restrict__ in, uint64_t n, uint64_t chunk_len,
                               float* cand_v, int* cand_i, int* tickets) {
+  ptx::pdl_launch_dependents();
+  ptx::pdl_wait();
   const uint64_t rowi = blockIdx.y;
   const float* row = in + rowi * n;
   const uint64_t lo = blockIdx.x * chunk_len, hi = min(n, lo + chunk_len);
@@ -243,6 +265,106 @@ __global__ void argmax_kernel(int32_t* __restrict__ out, const float* __restrict
   if (threadIdx.x == 0) out[rowi] = (isnan(row[0]) || bi == 0x7FFFFFFF) ? 0 : bi;
 }
 
+// ---- RMSNorm(+residual) then RMSNorm of the result: one block per row ------------------
+__device__ __forceinline__ float rms_block_sum(float v, float* part) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+  __syncthreads();  // `part` may still be read from the previous reduction
+  if (lane == 0) part[warp] = v;
+  __syncthreads();
+  float s = 0.0f;
+#pragma unroll
+  for (int w = 0; w < RMS_THREADS / 32; w++) s += part[w];
+  return s;
+}
+__global__ void __launch_bounds__(RMS_THREADS) rms_norm_pair_kernel(float* out1, float* out2, const float* x,
+                                                                    const float* __restrict__ gamma1, const float* __restrict__ beta1,
+                                                                    const float* residual, const float* __restrict__ gamma2,
+                                                                    const float* __restrict__ beta2, uint64_t cols, float eps1,
+                                                                    float eps2, int* fault) {
+  ptx::pdl_launch_dependents();
+  ptx::pdl_wait();
+  __shared__ float part[RMS_THREADS / 32];
+  const uint64_t r = blockIdx.x;
+  const float* xr = x + r * cols;
+  float sq = 0.0f;
+  for (uint64_t c = threadIdx.x; c < cols; c += RMS_THREADS) {
+    const float v = xr[c];
+    sq += v * v;
+  }
+  const float d1 = rms_block_sum(sq, part) * (1.0f / (float)cols) + eps1;
+  if (!(d1 > 0.0f) || !isfinite(d1)) {
+    if (threadIdx.x == 0) atomicCAS(fault, FAULT_NONE, FAULT_INVALID_ARGUMENT);
+    return;
+  }
+  const float inv1 = 1.0f / sqrtf(d1);
+  sq = 0.0f;
+  for (uint64_t c = threadIdx.x; c < cols; c += RMS_THREADS) {
+    float v = ((xr[c] * inv1) * gamma1[c]) + beta1[c];
+    if (residual) v = v + residual[r * cols + c];
+    out1[r * cols + c] = v;
+    sq += v * v;
+  }
+  const float d2 = rms_block_sum(sq, part) * (1.0f / (float)cols) + eps2;
+  if (!(d2 > 0.0f) || !isfinite(d2)) {
+    if (threadIdx.x == 0) atomicCAS(fault, FAULT_NONE, FAULT_INVALID_ARGUMENT);
+    return;
+  }
+  const float inv2 = 1.0f / sqrtf(d2);
+  for (uint64_t c = threadIdx.x; c < cols; c += RMS_THREADS)  // each thread re-reads what it wrote itself
+    out2[r * cols + c] = ((out1[r * cols + c] * inv2) * gamma2[c]) + beta2[c];
+}
+
+// ---- RoPE(q), RoPE(k), f16 cast of k and v, append to both caches: one block per (b, l) ----
+__global__ void rope_kv_append_kernel(float* __restrict__ q_out, const float* __restrict__ qkv, const int32_t* __restrict__ pos,
+                                      const int32_t* __restrict__ end_index, __half* __restrict__ k_cache,
+                                      __half* __restrict__ v_cache, uint32_t len, uint32_t h_q, uint32_t h_kv, uint32_t d,
+                                      uint64_t ld, uint64_t t_cap, uint32_t rope_pairs, float step, float scale_factor, int rolling,
+                                      int* fault) {
+  ptx::pdl_launch_dependents();
+  ptx::pdl_wait();
+  const uint64_t row = blockIdx.x;  // (b, l)
+  const uint64_t b = row / len, l = row % len;
+  const int32_t e = end_index[b];
+  const bool bad = e < 0 || (!rolling && (uint64_t)e + len > t_cap);
+  if (bad && threadIdx.x == 0) atomicCAS(fault, FAULT_NONE, FAULT_INVALID_ARGUMENT);
+  const uint64_t logical = (uint64_t)(e < 0 ? 0 : e) + l;
+  const uint64_t dst_t = rolling ? logical % t_cap : logical;
+  const float* src = qkv + row * ld;
+  const float* ksrc = src + (uint64_t)h_q * d;
+  const float* vsrc = ksrc + (uint64_t)h_kv * d;
+  float* qo = q_out + row * (uint64_t)h_q * d;
+  __half* kd = k_cache + (b * t_cap + dst_t) * (uint64_t)h_kv * d;
+  __half* vd = v_cache + (b * t_cap + dst_t) * (uint64_t)h_kv * d;
+  const uint32_t pairs_total = d / 2;
+  const float p = (float)pos[row];
+  for (uint32_t i = threadIdx.x; i < pairs_total; i += blockDim.x) {
+    float sn = 0.0f, cs = 1.0f;
+    const bool rot = i < rope_pairs;
+    if (rot) {
+      float f = scale_factor;
+      for (uint32_t j = 0; j < i; j++) f *= step;
+      const float ang = p * f;
+      double sd, cd;
+      sincos((double)ang, &sd, &cd);
+      sn = (float)sd, cs = (float)cd;
+    }
+    for (uint32_t h = 0; h < h_q; h++) {
+      const float xl = src[h * d + i], xr = src[h * d + pairs_total + i];
+      qo[h * d + i] = rot ? xl * cs - xr * sn : xl;
+      qo[h * d + pairs_total + i] = rot ? xl * sn + xr * cs : xr;
+    }
+    if (!bad)
+      for (uint32_t h = 0; h < h_kv; h++) {
+        const float xl = ksrc[h * d + i], xr = ksrc[h * d + pairs_total + i];
+        kd[h * d + i] = __float2half_rn(rot ? xl * cs - xr * sn : xl);
+        kd[h * d + pairs_total + i] = __float2half_rn(rot ? xl * sn + xr * cs : xr);
+      }
+  }
+  if (!bad)
+    for (uint32_t i = threadIdx.x; i < h_kv * d; i += blockDim.x) vd[i] = __float2half_rn(vsrc[i]);
+}
+
 unsigned grid_for(const AionCudaDevice* dev, uint64_t n, unsigned threads) {
   const uint64_t want = ceil_div(n, (uint64_t)threads);
   const uint64_t cap = (uint64_t)dev->sm_count * 16;
@@ -271,8 +393,8 @@ int32_t aion_cuda_rms_norm(AionCudaDevice* dev, const AionCudaRMSNorm* s) {
   if (s->residual.handle)
     if (int32_t st = resolve(s->residual, bytes, "rms_norm.residual", &res)) return st;
   if (s->rows > 0x7FFFFFFFull) return fail(AION_CUDA_UNSUPPORTED, "rms_norm: too many rows for one launch");
-  rms_norm_kernel<<<(unsigned)s->rows, RMS_THREADS, 0, dev->stream>>>(out, x, gamma, beta, res, s->cols, s->eps, dev->fault_dev);
-  AION_CUDA_TRY(cudaGetLastError());
+  AION_CUDA_TRY(launch_pdl(rms_norm_kernel, dim3((unsigned)s->rows), dim3(RMS_THREADS), 0, dev->stream, out, x, gamma, beta, res, s->cols, s->eps,
+                           dev->fault_dev));
   return AION_CUDA_OK;
 }
 
@@ -281,14 +403,25 @@ int32_t aion_cuda_elemwise(AionCudaDevice* dev, const AionCudaElemwise* s) {
   if (s->op > AION_CUDA_ELEMWISE_GATE_GELU) return fail(AION_CUDA_INVALID_ARGUMENT, "elemwise: op %u", s->op);
   if (s->count == 0) return AION_CUDA_OK;
   if (int32_t st = dev->make_current()) return st;
-  const size_t bytes = s->count * sizeof(float);
   float* out;
   const float *a, *b;
-  if (int32_t st = resolve(s->out, bytes, "elemwise.out", &out)) return st;
-  if (int32_t st = resolve(s->a, bytes, "elemwise.a", &a)) return st;
-  if (int32_t st = resolve(s->b, bytes, "elemwise.b", &b)) return st;
-  elemwise_kernel<<<grid_for(dev, s->count, 256), 256, 0, dev->stream>>>(out, a, b, s->count, s->op);
-  AION_CUDA_TRY(cudaGetLastError());
+  uint64_t cols = s->cols, ldo = 0, lda = 0, ldb = 0;
+  size_t need_o = s->count * sizeof(float), need_a = need_o, need_b = need_o;
+  if (cols) {
+    if (s->count % cols != 0) return fail(AION_CUDA_INVALID_ARGUMENT, "elemwise: count is not a multiple of cols");
+    const uint64_t rows = s->count / cols;
+    ldo = s->ld_out ? s->ld_out : cols, lda = s->ld_a ? s->ld_a : cols, ldb = s->ld_b ? s->ld_b : cols;
+    if (ldo < cols || lda < cols || ldb < cols) return fail(AION_CUDA_INVALID_ARGUMENT, "elemwise: a row stride is shorter than a row");
+    need_o = ((rows - 1) * ldo + cols) * sizeof(float);
+    need_a = ((rows - 1) * lda + cols) * sizeof(float);
+    need_b = ((rows - 1) * ldb + cols) * sizeof(float);
+    if (ldo == cols && lda == cols && ldb == cols) cols = 0;  // dense after all
+  }
+  if (int32_t st = resolve(s->out, need_o, "elemwise.out", &out)) return st;
+  if (int32_t st = resolve(s->a, need_a, "elemwise.a", &a)) return st;
+  if (int32_t st = resolve(s->b, need_b, "elemwise.b", &b)) return st;
+  AION_CUDA_TRY(launch_pdl(elemwise_kernel, dim3(grid_for(dev, s->count, 256)), dim3(256), 0, dev->stream, out, a, b, s->count, s->op, cols,
+                           ldo, lda, ldb));
   return AION_CUDA_OK;
 }
 
@@ -315,10 +448,8 @@ int32_t aion_cuda_rope(AionCudaDevice* dev, const AionCudaRoPE* s) {
   if (int32_t st = resolve(s->x, bytes, "rope.x", &x)) return st;
   if (int32_t st = resolve(s->positions, bl * sizeof(int32_t), "rope.positions", &pos)) return st;
   const uint64_t threads = bl * pairs_total;
-  rope_kernel<<<(unsigned)ceil_div(threads, (uint64_t)128), 128, 0, dev->stream>>>(out, x, pos, bl, (uint32_t)s->heads,
-                                                                                   (uint32_t)s->head_dim, (uint32_t)rope_pairs, step,
-                                                                                   s->scale_factor);
-  AION_CUDA_TRY(cudaGetLastError());
+  AION_CUDA_TRY(launch_pdl(rope_kernel, dim3((unsigned)ceil_div(threads, (uint64_t)128)), dim3(128), 0, dev->stream, out, x, pos, bl,
+                           (uint32_t)s->heads, (uint32_t)s->head_dim, (uint32_t)rope_pairs, step, s->scale_factor));
   return AION_CUDA_OK;
 }
 
@@ -331,13 +462,13 @@ int32_t aion_cuda_cast(AionCudaDevice* dev, const AionCudaCast* s) {
     const float* in;
     if (int32_t st = resolve(s->out, s->count * 2, "cast.out", &out)) return st;
     if (int32_t st = resolve(s->in, s->count * 4, "cast.in", &in)) return st;
-    cast_f32_f16_kernel<<<grid_for(dev, s->count, 256), 256, 0, dev->stream>>>(out, in, s->count);
+    AION_CUDA_TRY(launch_pdl(cast_f32_f16_kernel, dim3(grid_for(dev, s->count, 256)), dim3(256), 0, dev->stream, out, in, s->count));
   } else if (s->from_dtype == AION_CUDA_DTYPE_F16 && s->to_dtype == AION_CUDA_DTYPE_F32) {
     float* out;
     const __half* in;
     if (int32_t st = resolve(s->out, s->count * 4, "cast.out", &out)) return st;
     if (int32_t st = resolve(s->in, s->count * 2, "cast.in", &in)) return st;
-    cast_f16_f32_kernel<<<grid_for(dev, s->count, 256), 256, 0, dev->stream>>>(out, in, s->count);
+    AION_CUDA_TRY(launch_pdl(cast_f16_f32_kernel, dim3(grid_for(dev, s->count, 256)), dim3(256), 0, dev->stream, out, in, s->count));
   } else {
     return fail(AION_CUDA_UNSUPPORTED, "cast: only f32 <-> f16 is covered (got %u -> %u)", s->from_dtype, s->to_dtype);
   }
@@ -361,9 +492,8 @@ int32_t aion_cuda_sequence_append(AionCudaDevice* dev, const AionCudaSequenceApp
   if (int32_t st = resolve(s->new_kv, s->batch * s->new_len * row, "sequence_append.new_kv", &nk)) return st;
   if (int32_t st = resolve(s->end_index, s->batch * sizeof(int32_t), "sequence_append.end_index", &idx)) return st;
   if (s->batch * s->new_len > 0x7FFFFFFFull) return fail(AION_CUDA_UNSUPPORTED, "sequence_append: too many rows for one launch");
-  sequence_append_kernel<<<(unsigned)(s->batch * s->new_len), 128, 0, dev->stream>>>(cache, nk, idx, s->t_cap, row / 2, s->new_len,
-                                                                                      s->rolling ? 1 : 0, dev->fault_dev);
-  AION_CUDA_TRY(cudaGetLastError());
+  AION_CUDA_TRY(launch_pdl(sequence_append_kernel, dim3((unsigned)(s->batch * s->new_len)), dim3(128), 0, dev->stream, cache, nk, idx,
+                           s->t_cap, (uint64_t)(row / 2), s->new_len, s->rolling ? 1 : 0, dev->fault_dev));
   return AION_CUDA_OK;
 }
 
@@ -384,9 +514,8 @@ int32_t aion_cuda_gather_rows(AionCudaDevice* dev, const AionCudaGatherRows* s) 
   if (int32_t st = resolve(s->table, s->table_rows * (s->d / QK) * Q8_BYTES, "gather_rows.table", &table)) return st;
   if (int32_t st = resolve(s->indices, s->count * sizeof(int32_t), "gather_rows.indices", &idx)) return st;
   if (s->count > 0x7FFFFFFFull) return fail(AION_CUDA_UNSUPPORTED, "gather_rows: too many rows for one launch");
-  gather_rows_q8_kernel<<<(unsigned)s->count, 256, 0, dev->stream>>>(out, table, idx, s->table_rows, s->d, group, chunk,
-                                                                     dev->fault_dev);
-  AION_CUDA_TRY(cudaGetLastError());
+  AION_CUDA_TRY(launch_pdl(gather_rows_q8_kernel, dim3((unsigned)s->count), dim3(256), 0, dev->stream, out, table, idx, s->table_rows,
+                           s->d, group, chunk, dev->fault_dev));
   return AION_CUDA_OK;
 }
 
@@ -411,9 +540,68 @@ int32_t aion_cuda_argmax(AionCudaDevice* dev, const AionCudaArgMax* s) {
   if (int32_t st = dev->reserve_tickets(s->outer)) return st;
   float* cand_v = static_cast<float*>(dev->lane_scratch());
   int* cand_i = reinterpret_cast<int*>(cand_v + s->outer * chunks);
-  argmax_kernel<<<dim3((unsigned)chunks, (unsigned)s->outer), 256, 0, dev->stream>>>(out, in, s->n, chunk_len, cand_v, cand_i,
-                                                                                      dev->lane_tickets());
-  AION_CUDA_TRY(cudaGetLastError());
+  AION_CUDA_TRY(launch_pdl(argmax_kernel, dim3((unsigned)chunks, (unsigned)s->outer), dim3(256), 0, dev->stream, out, in, s->n, chunk_len,
+                           cand_v, cand_i, dev->lane_tickets()));
+  return AION_CUDA_OK;
+}
+
+int32_t aion_cuda_rms_norm_pair(AionCudaDevice* dev, const AionCudaRMSNormPair* s) {
+  if (!dev || !s) return fail(AION_CUDA_INVALID_ARGUMENT, "rms_norm_pair: null argument");
+  if (!(s->eps1 > 0.0f) || !std::isfinite(s->eps1) || !(s->eps2 > 0.0f) || !std::isfinite(s->eps2))
+    return fail(AION_CUDA_INVALID_ARGUMENT, "rms_norm_pair: eps must be finite and > 0");
+  if (s->rows == 0 || s->cols == 0) return AION_CUDA_OK;
+  if (s->rows > 0x7FFFFFFFull) return fail(AION_CUDA_UNSUPPORTED, "rms_norm_pair: too many rows for one launch");
+  if (int32_t st = dev->make_current()) return st;
+  const size_t bytes = s->rows * s->cols * sizeof(float), vec = s->cols * sizeof(float);
+  float *out1, *out2;
+  const float *x, *g1, *b1, *g2, *b2, *res = nullptr;
+  if (int32_t st = resolve(s->out1, bytes, "rms_norm_pair.out1", &out1)) return st;
+  if (int32_t st = resolve(s->out2, bytes, "rms_norm_pair.out2", &out2)) return st;
+  if (int32_t st = resolve(s->x, bytes, "rms_norm_pair.x", &x)) return st;
+  if (int32_t st = resolve(s->gamma1, vec, "rms_norm_pair.gamma1", &g1)) return st;
+  if (int32_t st = resolve(s->beta1, vec, "rms_norm_pair.beta1", &b1)) return st;
+  if (int32_t st = resolve(s->gamma2, vec, "rms_norm_pair.gamma2", &g2)) return st;
+  if (int32_t st = resolve(s->beta2, vec, "rms_norm_pair.beta2", &b2)) return st;
+  if (s->residual.handle)
+    if (int32_t st = resolve(s->residual, bytes, "rms_norm_pair.residual", &res)) return st;
+  AION_CUDA_TRY(launch_pdl(rms_norm_pair_kernel, dim3((unsigned)s->rows), dim3(RMS_THREADS), 0, dev->stream, out1, out2, x, g1, b1, res, g2,
+                           b2, s->cols, s->eps1, s->eps2, dev->fault_dev));
+  return AION_CUDA_OK;
+}
+
+int32_t aion_cuda_rope_kv_append(AionCudaDevice* dev, const AionCudaRopeKVAppend* s) {
+  if (!dev || !s) return fail(AION_CUDA_INVALID_ARGUMENT, "rope_kv_append: null argument");
+  if (s->head_dim % 2 != 0 || s->head_dim == 0 || s->head_dim > (1u << 16) || s->h_q > (1u << 16) || s->h_kv > (1u << 16))
+    return fail(AION_CUDA_INVALID_ARGUMENT, "rope_kv_append: head geometry");
+  const uint64_t rows = s->batch * s->len;
+  if (rows == 0) return AION_CUDA_OK;
+  if (rows > 0x7FFFFFFFull || s->len > 0x7FFFFFFFull) return fail(AION_CUDA_UNSUPPORTED, "rope_kv_append: too many rows for one launch");
+  if (s->t_cap == 0) return fail(AION_CUDA_INVALID_ARGUMENT, "rope_kv_append: empty cache");
+  const uint64_t width = (s->h_q + 2 * s->h_kv) * s->head_dim;
+  const uint64_t ld = s->ld_qkv ? s->ld_qkv : width;
+  if (ld < width) return fail(AION_CUDA_INVALID_ARGUMENT, "rope_kv_append: ld_qkv is shorter than q | k | v");
+  if (int32_t st = dev->make_current()) return st;
+  const uint64_t pairs_total = s->head_dim / 2;
+  const float pf = std::floor(s->proportion * (float)pairs_total);
+  if (!(pf >= 0.0f)) return fail(AION_CUDA_INVALID_ARGUMENT, "rope_kv_append: proportion %g", (double)s->proportion);
+  uint64_t rope_pairs = (uint64_t)pf;
+  if (rope_pairs > pairs_total) rope_pairs = pairs_total;
+  const float head_dim_f = (float)s->head_dim;
+  const float step = (float)std::pow((double)s->base_frequency, (double)(-2.0f / head_dim_f));
+  float* q_out;
+  const float* qkv;
+  const int32_t *pos, *idx;
+  __half *kc, *vc;
+  const size_t cache_bytes = s->batch * s->t_cap * s->h_kv * s->head_dim * 2;
+  if (int32_t st = resolve(s->q_out, rows * s->h_q * s->head_dim * sizeof(float), "rope_kv_append.q_out", &q_out)) return st;
+  if (int32_t st = resolve(s->qkv, ((rows - 1) * ld + width) * sizeof(float), "rope_kv_append.qkv", &qkv)) return st;
+  if (int32_t st = resolve(s->positions, rows * sizeof(int32_t), "rope_kv_append.positions", &pos)) return st;
+  if (int32_t st = resolve(s->end_index, s->batch * sizeof(int32_t), "rope_kv_append.end_index", &idx)) return st;
+  if (int32_t st = resolve(s->k_cache, cache_bytes, "rope_kv_append.k_cache", &kc)) return st;
+  if (int32_t st = resolve(s->v_cache, cache_bytes, "rope_kv_append.v_cache", &vc)) return st;
+  AION_CUDA_TRY(launch_pdl(rope_kv_append_kernel, dim3((unsigned)rows), dim3(128), 0, dev->stream, q_out, qkv, pos, idx, kc, vc,
+                           (uint32_t)s->len, (uint32_t)s->h_q, (uint32_t)s->h_kv, (uint32_t)s->head_dim, ld, s->t_cap, (uint32_t)rope_pairs,
+                           step, s->scale_factor, s->rolling ? 1 : 0, dev->fault_dev));
   return AION_CUDA_OK;
 }
 

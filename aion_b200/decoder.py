@@ -13,6 +13,13 @@ to the benchmark's dense core: per layer
     x       = x + RMSNorm(MatMul(gelu(MatMul(h, Wg)) * MatMul(h, Wu), Wd))
 
 then `ArgMax(MatMul(RMSNorm(x), Whead))`, with x gathered from a q8_0 embedding table.
+
+`fused=True` (the default) issues the same arithmetic as fewer, fuller steps, the way a
+fusion pass would rewrite the graph: one matmul against [Wq | Wk | Wv] and one against
+[Wg | Wu] (column concatenation commutes with K-major block quantization, so the packed
+weights are the same bytes side by side), `StepRopeKVAppend` for RoPE + cast + append, and
+`StepRMSNormPair` for "x = x + RMSNorm(.)" followed by the next block's RMSNorm: 9 launches
+per layer instead of 19.
 Every request is independent of the others in its batch (all ops are row-wise), which is
 what lets a batch be split over GPUs with replicated weights and no exchange.
 
@@ -28,8 +35,8 @@ import numpy as np
 
 from . import capi
 from .backend import (AttentionWindow, Chunk, CudaBackend, CudaSession, DeviceStore, StepArgMax, StepAttention, StepCast,
-                      StepElemwiseBinary, StepGatherRows, StepMatMul, StepRMSNorm, StepRoPE1D, StepSequenceAppend,
-                      TensorMeta, _check)
+                      StepElemwiseBinary, StepGatherRows, StepMatMul, StepRMSNorm, StepRMSNormPair, StepRoPE1D,
+                      StepRopeKVAppend, StepSequenceAppend, TensorMeta, _check)
 
 F32, F16, I32, Q4, Q8 = capi.DTYPE_F32, capi.DTYPE_F16, capi.DTYPE_I32, capi.DTYPE_Q4_0, capi.DTYPE_Q8_0
 
@@ -91,13 +98,13 @@ class SyntheticDecoder:
 
     def __init__(self, backend: CudaBackend, cfg: DecoderConfig, requests: int,
                  weight_values: Callable[[str, int, int], object], embedding_values: Callable[[int, int], object],
-                 store: Optional[DeviceStore] = None):
-        self.backend, self.cfg, self.requests = backend, cfg, requests
+                 store: Optional[DeviceStore] = None, fused: bool = True):
+        self.backend, self.cfg, self.requests, self.fused = backend, cfg, requests, fused
         self.store = store or DeviceStore(backend.device_memory)
         self.session: CudaSession = backend.create_session(self.store)
         self._build_weights(weight_values, embedding_values)
         self._build_state()
-        self.steps = self._build_steps()
+        self.steps = self._build_steps_fused() if fused else self._build_steps()
         self.program = None
 
     # ---- weights -----------------------------------------------------------------------
@@ -123,10 +130,29 @@ class SyntheticDecoder:
     def _build_weights(self, weight_values, embedding_values) -> None:
         cfg, st = self.cfg, self.store
         self.w = []
+        shapes = cfg.layer_weights()
         for layer in range(cfg.layers):
             names = {}
-            for name, (k, n) in cfg.layer_weights().items():
-                names[name] = self._quantized(weight_values(f"l{layer}.{name}", k, n), (k, n), cfg.weight_dtype, 0)
+            if self.fused:
+                # [Wq | Wk | Wv] and [Wg | Wu] as single weights; host arrays are concatenated so the
+                # values stay those of the separate weights, device-side sources are asked directly.
+                for fused_name, parts in (("wqkv", ("wq", "wk", "wv")), ("wgu", ("wg", "wu"))):
+                    k = shapes[parts[0]][0]
+                    n = sum(shapes[p][1] for p in parts)
+                    first = weight_values(f"l{layer}.{parts[0]}", k, shapes[parts[0]][1])
+                    if isinstance(first, Chunk):
+                        vals = weight_values(f"l{layer}.{fused_name}", k, n)
+                    else:
+                        vals = np.concatenate([np.asarray(first, dtype=np.float32)] +
+                                              [np.asarray(weight_values(f"l{layer}.{p}", k, shapes[p][1]), dtype=np.float32)
+                                               for p in parts[1:]], axis=1)
+                    names[fused_name] = self._quantized(vals, (k, n), cfg.weight_dtype, 0)
+                for name in ("wo", "wd"):
+                    k, n = shapes[name]
+                    names[name] = self._quantized(weight_values(f"l{layer}.{name}", k, n), (k, n), cfg.weight_dtype, 0)
+            else:
+                for name, (k, n) in shapes.items():
+                    names[name] = self._quantized(weight_values(f"l{layer}.{name}", k, n), (k, n), cfg.weight_dtype, 0)
             self.w.append(names)
         self.w_head = self._quantized(weight_values("head", cfg.hidden, cfg.vocab), (cfg.hidden, cfg.vocab), cfg.weight_dtype, 0)
         # q8_0 [vocab, hidden] embedding table, quantized along hidden, filled in row slabs.
@@ -191,6 +217,15 @@ class SyntheticDecoder:
         self.up = f(R, 1, cfg.ffn)
         self.act = f(R, 1, cfg.ffn)
         self.down = f(R, 1, cfg.hidden)
+        if self.fused:
+            width = cfg.q_width + 2 * cfg.kv_width
+            self.qkv = f(R, 1, width)
+            self.q_rot = f(R, 1, cfg.heads, cfg.head_dim)
+            self.gu = f(R, 1, 2 * cfg.ffn)
+            ch = st.acquire_const(self.gu)
+            half = TensorMeta(F32, (R, 1, cfg.ffn), row_stride=2 * cfg.ffn)
+            self.gate_view = st.bind(half, Chunk(ch.handle, ch.offset, ch.len))
+            self.up_view = st.bind(half, Chunk(ch.handle, ch.offset + cfg.ffn * 4, ch.len - cfg.ffn * 4))
         self.logits = f(R, 1, cfg.vocab)
         self.next_token = st.add(TensorMeta(I32, (R, 1)))
 
@@ -229,6 +264,36 @@ class SyntheticDecoder:
             StepMatMul(c=self.logits, a=self.x_norm, b=self.w_head),
             StepArgMax(out=self.next_token, a=self.logits),
         ]
+        return steps
+
+    def _build_steps_fused(self) -> list:
+        cfg = self.cfg
+        g, b = self.gamma, self.beta
+        scale = 1.0 / float(np.sqrt(cfg.head_dim))
+        steps: list = [StepGatherRows(out=self.x, table=self.embed, indices=self.tokens),
+                       StepRMSNorm(out=self.x_norm, x=self.x, gamma=g, beta=b, eps=cfg.eps)]
+        for layer in range(cfg.layers):
+            w = self.w[layer]
+            steps += [
+                StepMatMul(c=self.qkv, a=self.x_norm, b=w["wqkv"]),
+                StepRopeKVAppend(q_out=self.q_rot, qkv=self.qkv, positions=self.positions, end_index=self.write_index,
+                                 k_cache=self.k_cache[layer], v_cache=self.v_cache[layer], base_frequency=cfg.rope_base),
+                StepAttention(out=self.attn, q=self.q_rot, k=self.k_cache[layer], v=self.v_cache[layer],
+                              query_positions=self.positions, kv_lengths=self.visible_end, scale=scale,
+                              window=AttentionWindow.causal()),
+                StepMatMul(c=self.o, a=self.attn2, b=w["wo"]),
+                # x = x + RMSNorm(o);  x_norm = RMSNorm(x)
+                StepRMSNormPair(out1=self.x, out2=self.x_norm, x=self.o, gamma1=g, beta1=b, gamma2=g, beta2=b, eps1=cfg.eps,
+                                eps2=cfg.eps, residual=self.x),
+                StepMatMul(c=self.gu, a=self.x_norm, b=w["wgu"]),
+                StepElemwiseBinary(op="gate", out=self.act, a=self.gate_view, b=self.up_view),
+                StepMatMul(c=self.down, a=self.act, b=w["wd"]),
+                # x = x + RMSNorm(down);  x_norm = RMSNorm(x): the next layer's input norm, or the final norm
+                StepRMSNormPair(out1=self.x, out2=self.x_norm, x=self.down, gamma1=g, beta1=b, gamma2=g, beta2=b, eps1=cfg.eps,
+                                eps2=cfg.eps, residual=self.x),
+            ]
+        steps += [StepMatMul(c=self.logits, a=self.x_norm, b=self.w_head),
+                  StepArgMax(out=self.next_token, a=self.logits)]
         return steps
 
     # ---- running -------------------------------------------------------------------------

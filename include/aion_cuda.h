@@ -290,6 +290,9 @@ typedef struct AionCudaElemwise {
   uint64_t count;
   uint32_t op;
   uint32_t reserved;
+  /* cols > 0: the operands are [count / cols, cols] matrices with these row strides in
+   * elements (0 = cols), e.g. the two halves of a [gate | up] matmul output. */
+  uint64_t cols, ld_out, ld_a, ld_b;
 } AionCudaElemwise;
 AION_CUDA_API int32_t aion_cuda_elemwise(AionCudaDevice* dev, const AionCudaElemwise* step);
 
@@ -348,6 +351,39 @@ typedef struct AionCudaArgMax {
   uint64_t outer, n;
 } AionCudaArgMax;
 AION_CUDA_API int32_t aion_cuda_argmax(AionCudaDevice* dev, const AionCudaArgMax* step);
+
+/* ---------------------------------------------------------------------------------
+ * Fused decoder steps. No counterpart step in the reference: each is the exact composition
+ * of reference steps that always follow one another in a decode program, issued as one
+ * kernel so a token step is fewer, fuller launches (the reference fuses in the same spirit:
+ * RMSNorm + residual, gate). Results equal the unfused sequences bit for bit (RoPE, cast,
+ * append) or to f32 summation order (norms).
+ * --------------------------------------------------------------------------------- */
+
+/* RMSNorm(+residual) followed by the RMSNorm of its result:
+ *   out1 = rms(x; gamma1, beta1, eps1) + residual     (residual.handle == 0: absent)
+ *   out2 = rms(out1; gamma2, beta2, eps2)
+ * out1 may alias x or residual. */
+typedef struct AionCudaRMSNormPair {
+  AionCudaOperand out1, out2, x, gamma1, beta1, residual, gamma2, beta2;
+  uint64_t rows, cols;
+  float eps1, eps2;
+} AionCudaRMSNormPair;
+AION_CUDA_API int32_t aion_cuda_rms_norm_pair(AionCudaDevice* dev, const AionCudaRMSNormPair* step);
+
+/* RoPE1D of q and k, Cast f32 -> f16 of k and v, SequenceAppend of both into their caches.
+ * qkv is one f32 row of ld_qkv elements per (b, l): q (h_q * head_dim) then k then v
+ * (h_kv * head_dim each) — the output of one matmul against [Wq | Wk | Wv].
+ *   q_out [B, L, h_q, head_dim] f32 = RoPE(q)
+ *   k_cache / v_cache [B, t_cap, h_kv, head_dim] f16: rows end_index[b] + l receive
+ *   f16(RoPE(k)) and f16(v); range rules and rolling as in aion_cuda_sequence_append. */
+typedef struct AionCudaRopeKVAppend {
+  AionCudaOperand q_out, qkv, positions, end_index, k_cache, v_cache;
+  uint64_t batch, len, h_q, h_kv, head_dim, ld_qkv, t_cap;
+  float base_frequency, scale_factor, proportion;
+  uint32_t rolling;
+} AionCudaRopeKVAppend;
+AION_CUDA_API int32_t aion_cuda_rope_kv_append(AionCudaDevice* dev, const AionCudaRopeKVAppend* step);
 
 /* ---------------------------------------------------------------------------------
  * Block quantizer on the device. `quantizeBlocks` (aion src/aion/storage/quantize.zig:31-103)

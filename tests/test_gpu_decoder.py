@@ -36,15 +36,16 @@ def rel_l2(a, b):
     return float(np.linalg.norm(a.astype(np.float64) - b) / max(np.linalg.norm(b.astype(np.float64)), 1e-30))
 
 
-def build(backend, cfg, R, w, emb):
-    return SyntheticDecoder(backend, cfg, R, lambda name, k, n: w[name], lambda v0, v1: emb[v0:v1])
+def build(backend, cfg, R, w, emb, fused=True):
+    return SyntheticDecoder(backend, cfg, R, lambda name, k, n: w[name], lambda v0, v1: emb[v0:v1], fused=fused)
 
 
+@pytest.mark.parametrize("fused", [False, True])
 @pytest.mark.parametrize("R", [1, 5])
-def test_decoder_steps_match_oracle(backend, R):
+def test_decoder_steps_match_oracle(backend, R, fused):
     cfg = SMALL
     w, emb = make_values(cfg)
-    dec = build(backend, cfg, R, w, emb)
+    dec = build(backend, cfg, R, w, emb, fused=fused)
     ref = OracleDecoder(cfg, R, w, emb)
     rng = np.random.default_rng(99)
     try:
@@ -68,6 +69,28 @@ def test_decoder_steps_match_oracle(backend, R):
                 assert rel_l2(kc[:, : t + 1], ref.k_cache[l][:, : t + 1].astype(np.float32)) <= CHAIN_TOL
     finally:
         dec.deinit()
+
+
+def test_fused_program_equals_step_by_step_program(backend):
+    """The fused steps are the same arithmetic: logits agree to f32 rounding of the matmul splits,
+    the caches hold the same bytes."""
+    cfg, R = SMALL, 4
+    w, emb = make_values(cfg, seed=5)
+    outs = {}
+    for fused in (False, True):
+        dec = build(backend, cfg, R, w, emb, fused=fused)
+        try:
+            for t in range(3):
+                dec.set_inputs(np.array([7, 8, 9, 10]) + t, np.full(R, t, np.int32))
+                dec.execute()
+            outs[fused] = (dec.store.read(dec.logits).copy(), dec.store.read(dec.k_cache[0]).copy(),
+                           dec.store.read(dec.v_cache[1]).copy(), dec.read_next_tokens().copy(), len(dec.steps))
+        finally:
+            dec.deinit()
+    assert rel_l2(outs[True][0], outs[False][0]) <= CHAIN_TOL
+    assert rel_l2(outs[True][1].astype(np.float32), outs[False][1].astype(np.float32)) <= CHAIN_TOL
+    assert rel_l2(outs[True][2].astype(np.float32), outs[False][2].astype(np.float32)) <= CHAIN_TOL
+    assert outs[True][4] < outs[False][4] // 2 + 4
 
 
 def test_recorded_program_replays_identically(backend):

@@ -158,3 +158,74 @@ def test_argmax(sess):
     ts, t2 = put(store, small, F32), store.add(TensorMeta(I32, (5,)))
     s.execute([StepArgMax(out=t2, a=ts)])
     assert np.array_equal(store.read(t2), oracle.argmax(small))
+
+
+# ---- fused steps against the unfused reference sequences --------------------------------
+from aion_b200.backend import StepRMSNormPair, StepRopeKVAppend, Chunk  # noqa: E402
+
+
+@pytest.mark.parametrize("with_res", [False, True])
+def test_rms_norm_pair_equals_two_norms(sess, with_res):
+    s, store = sess
+    rng = np.random.default_rng(31)
+    rows, cols = 9, 1536
+    x = rng.standard_normal((rows, cols)).astype(np.float32)
+    res = rng.standard_normal((rows, cols)).astype(np.float32) if with_res else None
+    g1, b1, g2, b2 = (rng.standard_normal(cols).astype(np.float32) for _ in range(4))
+    t = {k: put(store, v, F32) for k, v in dict(x=x, g1=g1, b1=b1, g2=g2, b2=b2).items()}
+    tr = put(store, res, F32) if with_res else None
+    o1, o2 = store.add(TensorMeta(F32, (rows, cols))), store.add(TensorMeta(F32, (rows, cols)))
+    s.execute([StepRMSNormPair(out1=o1, out2=o2, x=t["x"], gamma1=t["g1"], beta1=t["b1"], gamma2=t["g2"], beta2=t["b2"],
+                               eps1=1e-6, eps2=1e-5, residual=tr)])
+    want1 = oracle.rms_norm(x, g1, b1, 1e-6, residual=res)
+    want2 = oracle.rms_norm(want1, g2, b2, 1e-5)
+    np.testing.assert_allclose(store.read(o1), want1, rtol=1e-5, atol=1e-6)
+    np.testing.assert_allclose(store.read(o2), want2, rtol=2e-5, atol=2e-6)
+
+
+@pytest.mark.parametrize("rolling", [False, True])
+def test_rope_kv_append_equals_the_six_steps(sess, rolling):
+    s, store = sess
+    rng = np.random.default_rng(32)
+    B, L, Hq, Hkv, D, T = 3, 2, 4, 1, 64, 16
+    width = (Hq + 2 * Hkv) * D
+    ld = width + 32                                        # rows are slices of a wider buffer
+    buf = rng.standard_normal((B * L, ld)).astype(np.float32)
+    qkv = buf[:, :width]
+    pos = rng.integers(0, 500, size=(B, L)).astype(np.int32)
+    idx = np.array([0, 14, 33 if rolling else 7], dtype=np.int32)
+    kc0 = rng.standard_normal((B, T, Hkv, D)).astype(np.float16)
+    vc0 = rng.standard_normal((B, T, Hkv, D)).astype(np.float16)
+    tb = put(store, buf, F32)
+    ch = store.acquire_const(tb)
+    tq = store.bind(TensorMeta(F32, (B, L, width), row_stride=ld), Chunk(ch.handle, ch.offset, ch.len))
+    policy = "rolling" if rolling else "none"
+    tk = store.add(TensorMeta(F16, kc0.shape, cache_policy=policy), kc0)
+    tv = store.add(TensorMeta(F16, vc0.shape, cache_policy=policy), vc0)
+    tp, ti = put(store, pos, I32), put(store, idx, I32)
+    to = store.add(TensorMeta(F32, (B, L, Hq, D)))
+    s.execute([StepRopeKVAppend(q_out=to, qkv=tq, positions=tp, end_index=ti, k_cache=tk, v_cache=tv, base_frequency=10000.0)])
+    q = qkv[:, : Hq * D].reshape(B, L, Hq, D)
+    k = qkv[:, Hq * D:(Hq + Hkv) * D].reshape(B, L, Hkv, D)
+    v = qkv[:, (Hq + Hkv) * D:].reshape(B, L, Hkv, D)
+    np.testing.assert_allclose(store.read(to), oracle.rope(q, pos, 10000.0), rtol=0, atol=1e-6)
+    want_k = oracle.sequence_append(kc0, oracle.cast_f32_f16(oracle.rope(k, pos, 10000.0)), idx, rolling=rolling)
+    want_v = oracle.sequence_append(vc0, oracle.cast_f32_f16(v), idx, rolling=rolling)
+    got_k, got_v = store.read(tk), store.read(tv)
+    assert np.array_equal(got_v.view(np.uint16), want_v.view(np.uint16))
+    np.testing.assert_allclose(got_k.astype(np.float32), want_k.astype(np.float32), rtol=0, atol=2e-3)  # one f16 ulp where sincos differs
+
+
+def test_gate_on_strided_halves(sess):
+    s, store = sess
+    rng = np.random.default_rng(33)
+    R, F = 5, 512
+    gu = rng.standard_normal((R, 2 * F)).astype(np.float32)
+    tg = put(store, gu, F32)
+    ch = store.acquire_const(tg)
+    half = TensorMeta(F32, (R, F), row_stride=2 * F)
+    ta = store.bind(half, Chunk(ch.handle, ch.offset, ch.len))
+    tb = store.bind(half, Chunk(ch.handle, ch.offset + F * 4, ch.len - F * 4))
+    to = store.add(TensorMeta(F32, (R, F)))
+    s.execute([StepElemwiseBinary(op="gate", out=to, a=ta, b=tb)])
+    assert np.array_equal(store.read(to), oracle.elemwise(2, gu[:, :F], gu[:, F:]))

@@ -303,3 +303,74 @@ def colsplit_leg(torch, dist, backend: CudaBackend, rank: int, world: int, local
     return {"m": m, "n": n, "k": k, "n_gpus": world, "columns_per_gpu": n_loc, "ms": round(ms, 4),
             "aggregate_weight_gbs": round(total_w / (ms * 1e-3) / 1e9, 1),
             "all_gather_bytes_per_rank": m * n_loc * 4, "checksum": checksum}
+
+
+def matmul_leg(torch, backend: CudaBackend, local_rank: int, dtype: int, nt: bool, m: int, n: int, k: int, lanes: int = 8,
+               iters: int = 20, min_bytes: int = 512 << 20, peak_gbs: float = 6552.3) -> dict:
+    """Decode-sized matmul (`MatMul` K-major or `MatMulNT` row-major q8) GB/s of algorithmic bytes over
+    enough distinct weight copies (>= 512 MB) that no launch finds its weights in L2; one recorded
+    program per pass, its independent steps spread over `lanes` parallel lanes."""
+    lib, dev, mem = backend._lib, backend.handle, backend.device_memory
+    bb = 18 if dtype == capi.DTYPE_Q4_0 else 34
+    w_bytes = (k // 32) * n * bb
+    copies = max(8, min(256, -(-min_bytes // w_bytes)))
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(1234)
+    arena = mem.alloc(copies * w_bytes, 256)
+    shape = (C.c_uint64 * 2)(*((n, k) if nt else (k, n)))
+    for i in range(copies):
+        w = torch.randn((n, k) if nt else (k, n), generator=gen, device="cuda", dtype=torch.float32) * 0.02
+        torch.cuda.synchronize()
+        src, dst = capi.Operand(w.data_ptr(), 0, w.numel() * 4), capi.Operand(arena, i * w_bytes, w_bytes)
+        _chk(lib.aion_cuda_quantize(dev, dtype, C.byref(src), shape, 2, 1 if nt else 0, C.byref(dst)))
+        backend.sync()
+    x = torch.randn((copies, m, k), generator=torch.Generator().manual_seed(5678), dtype=torch.float32).numpy()
+    hx, hy = mem.alloc(x.nbytes, 256), mem.alloc(copies * m * n * 4, 256)
+    mem.copy_h2d(hx, 0, x)
+    recs = []
+    for i in range(copies):
+        c_op, a_op = capi.Operand(hy, i * m * n * 4, m * n * 4), capi.Operand(hx, i * m * k * 4, m * k * 4)
+        b_op = capi.Operand(arena, i * w_bytes, w_bytes)
+        if nt:
+            recs.append(capi.MatMulNT(c=c_op, a=a_op, b=b_op, b_dtype=dtype, block_order=capi.ORDER_ROW_MAJOR, flags=0, reserved=0,
+                                      m=m, n=n, k=k, lda=0, ldc=0, c_off=0, alpha=1.0, beta=0.0))
+        else:
+            recs.append(capi.MatMul(c=c_op, a=a_op, b=b_op, b_dtype=dtype, flags=0, m=m, n=n, k=k, lda=0, ldb=0, ldc=0,
+                                    alpha=1.0, beta=0.0))
+    call = lib.aion_cuda_matmul_nt if nt else lib.aion_cuda_matmul
+
+    def issue(nl):
+        for i, r in enumerate(recs):
+            if nl:
+                _chk(lib.aion_cuda_record_lane(dev, i % nl))
+            _chk(call(dev, C.byref(r)))
+
+    issue(0)
+    backend.sync()
+    out = {"dtype": "q4_0" if dtype == capi.DTYPE_Q4_0 else "q8_0", "layout": "[N,K] row-major (MatMulNT)" if nt else "[K/32][N] (MatMul)",
+           "m": m, "n": n, "k": k, "distinct_weight_copies": copies}
+    alg = w_bytes + 4 * m * k + 4 * m * n
+    stream, ev0, ev1 = _events(torch, backend, local_rank)
+    for name, nl in (("lanes", lanes), ("serial", 1)):
+        _chk(lib.aion_cuda_record_begin(dev))
+        issue(nl)
+        prog = C.c_void_p()
+        _chk(lib.aion_cuda_record_end(dev, C.byref(prog)))
+        for _ in range(3):
+            _chk(lib.aion_cuda_program_launch(dev, prog))
+        backend.sync()
+        ev0.record(stream)
+        for _ in range(iters):
+            _chk(lib.aion_cuda_program_launch(dev, prog))
+        ev1.record(stream)
+        backend.sync()
+        torch.cuda.synchronize()
+        us = ev0.elapsed_time(ev1) * 1e3 / (iters * copies)
+        gbs = alg / (us * 1e-6) / 1e9
+        out[f"us_per_launch_{name}"] = round(us, 2)
+        out[f"gbs_{name}"] = round(gbs, 1)
+        out[f"frac_of_measured_hbm_{name}"] = round(gbs / peak_gbs, 4)
+        lib.aion_cuda_program_destroy(dev, prog)
+    for h in (arena, hx, hy):
+        mem.free(h)
+    return out

@@ -326,6 +326,21 @@ def run_other(args):
             out = {"metric": "decode attention GB/s", "n_gpus": 1,
                    **benchmarks.attention_leg(torch, backend, local_rank, args.attn_batch, args.attn_context,
                                               iters=max(3, min(args.steps, 50)), peak_gbs=peak)}
+        elif args.workload == "sweep":
+            # The GEMV configurations of the benchmark: the single q8 NT op, then the q4 batch / shape sweep.
+            rows = [benchmarks.matmul_leg(torch, backend, local_rank, capi.DTYPE_Q8_0, True, 1, 8192, 2048, lanes=args.lanes, peak_gbs=peak)]
+            for (n, k) in ((2048, 2048), (8192, 2048), (2048, 8192)):
+                for m in (1, 2, 4, 8):
+                    rows.append(benchmarks.matmul_leg(torch, backend, local_rank, capi.DTYPE_Q4_0, False, m, n, k, lanes=args.lanes,
+                                                      peak_gbs=peak))
+            rows.append(benchmarks.matmul_leg(torch, backend, local_rank, capi.DTYPE_Q8_0, False, 1, 28672, 8192, lanes=args.lanes, peak_gbs=peak))
+            rows.append(benchmarks.matmul_leg(torch, backend, local_rank, capi.DTYPE_Q4_0, False, 1, 28672, 8192, lanes=args.lanes, peak_gbs=peak))
+            for dt in (capi.DTYPE_Q4_0, capi.DTYPE_Q8_0):
+                for m in (512, 2048):
+                    rows.append(benchmarks.gemm_leg(torch, backend, local_rank, dt, m, 8192, 2048))
+            for r in rows:
+                print(json.dumps(r), flush=True)
+            out = {"metric": "matmul sweep", "rows": len(rows)}
         else:
             out = {"metric": "column-split q4 layer + all-gather",
                    **benchmarks.colsplit_leg(torch, dist, backend, rank, world, local_rank, args.colsplit_m,
@@ -401,7 +416,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--lanes", type=int, default=8, help="parallel lanes the independent steps are recorded into (1..8)")
     ap.add_argument("--skip-cpu-baseline", action="store_true", help="leave the CPU leg out (profiling runs)")
-    ap.add_argument("--workload", default="gemv", choices=["gemv", "decode", "gemm", "attention", "colsplit"],
+    ap.add_argument("--workload", default="gemv", choices=["gemv", "decode", "gemm", "attention", "colsplit", "sweep"],
                     help="gemv: the headline pass (default; its line also carries the decode leg). The others print "
                          "their own line: decode tokens/s, prefill GEMM TFLOP/s, decode attention GB/s, the "
                          "column-split layer with its all-gather")

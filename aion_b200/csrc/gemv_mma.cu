@@ -42,7 +42,7 @@ namespace {
 
 constexpr int TN = 64;             // output columns per tile
 constexpr int KBT = 8;             // K blocks per stage
-constexpr int NS = 4;              // stages in the ring
+constexpr int NS = 2;              // stages in the ring: shallow, so that more CTAs (of concurrent launches) fit an SM
 constexpr int CONSUMER_WARPS = 4;  // one per 16 columns
 constexpr int CONSUMER_THREADS = CONSUMER_WARPS * 32;
 constexpr int THREADS = CONSUMER_THREADS + 32;
@@ -547,6 +547,16 @@ int32_t launch(AionCudaDevice* dev, GemvParams p, const uint8_t* b, uint64_t ldb
     if (want < sms) want = sms;
     if (grid > want) grid = want;
     if (grid > p.units) grid = p.units;
+    // Nearly one tile per CTA: give every CTA exactly one whole tile, so that no tile is shared
+    // and the partial-sum fix-up (two more L2 round trips at the end of a short kernel) is skipped.
+    // Only while independent steps are being recorded into parallel lanes: there other launches
+    // fill the idle SMs, whereas a lone launch on a critical path is shortest with every SM busy.
+    bool overlapped = false;
+    if (dev->recording) {
+      overlapped = dev->cur_lane != 0;
+      for (int l = 1; l < AionCudaDevice::LANES; l++) overlapped = overlapped || dev->lane_forked[l];
+    }
+    if (overlapped && (uint64_t)p.tiles <= grid && (uint64_t)p.tiles * 5 >= grid * 4) grid = p.tiles;
   }
 
   // Scratch for tiles shared by several CTAs: two partial slots per CTA, one ticket per (tile, warp),

@@ -36,7 +36,7 @@ namespace aion {
 
 namespace {
 
-constexpr int BM = 128;      // tokens per tile (UMMA M)
+constexpr int BM = 128;      // tokens per MMA (UMMA M); a tile holds MH of these halves (1 or 2)
 constexpr int BN = 256;      // output columns per tile (UMMA N)
 constexpr int BK = 64;       // K per stage: one 128-byte swizzle row of bf16
 constexpr int UMMA_K = 16;
@@ -47,7 +47,7 @@ constexpr int DEQ_WARPS = 2 * DEQ_GROUPS;
 constexpr int DEQ_WARP0 = 3;            // warp 0: activation TMA, warp 1: MMA, warp 2: packed-block TMA
 constexpr int EPI_WARP0 = DEQ_WARP0 + DEQ_WARPS;
 constexpr int THREADS = (EPI_WARP0 + 4) * 32;
-constexpr int A_TILE_BYTES = BM * BK * 2;   // 16 KB
+constexpr int A_HALF_BYTES = BM * BK * 2;   // 16 KB: activation rows of one MMA
 constexpr int B_TILE_BYTES = BN * BK * 2;   // 32 KB
 constexpr uint32_t TMEM_COLS = 512;         // two f32 accumulators of 256 columns
 
@@ -58,12 +58,14 @@ struct GemmParams {
   float alpha, beta;
   uint32_t m_tiles, n_tiles, k_stages;
   uint32_t splits;    // K splits per tile (work unit = tile x split); > 1 goes through `partial`
-  float* partial;     // [tile][split][BM][BN] raw accumulators
+  float* partial;     // [tile][split][BM * MH][BN] raw accumulators
+  uint32_t tile_rows; // BM * MH
   int* fault;
 };
 
-template <int DT>
+template <int DT, int MH>
 struct GemmGeom {
+  static constexpr int A_TILE_BYTES = MH * A_HALF_BYTES;
   static constexpr int BB = (DT == AION_CUDA_DTYPE_Q8_0) ? Q8_BYTES : Q4_BYTES;
   static constexpr int PACKED_ROW = BN * BB;                       // one block row of the tile
   static constexpr int PACKED_BYTES = KB_PER_STAGE * PACKED_ROW;   // 9216 (q4) / 17408 (q8)
@@ -73,8 +75,8 @@ struct GemmGeom {
   // B_STAGES equals the number of dequantizer groups and P_STAGES is a multiple of it, so
   // every "free" barrier is waited on by one group only, use after use: a parity wait is
   // only meaningful for a waiter that is at most one phase behind.
-  static constexpr int A_STAGES = 4;
-  static constexpr int P_STAGES = (DT == AION_CUDA_DTYPE_Q8_0) ? 3 : 6;
+  static constexpr int A_STAGES = MH == 1 ? 4 : (DT == AION_CUDA_DTYPE_Q8_0 ? 2 : 3);
+  static constexpr int P_STAGES = (DT == AION_CUDA_DTYPE_Q8_0 || MH == 2) ? 3 : 6;
   static constexpr int B_STAGES = DEQ_GROUPS;
   static_assert(P_STAGES % DEQ_GROUPS == 0, "a packed stage belongs to one dequantizer group");
   static constexpr int OFF_BRING = 0;
@@ -269,10 +271,15 @@ __device__ __forceinline__ Unit unit_of(const GemmParams& p, uint32_t u) {
   return w;
 }
 
-template <int DT>
+template <int DT, int MH>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_q_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b) {
-  using G = GemmGeom<DT>;
+  using G = GemmGeom<DT, MH>;
+  // MH == 1: two accumulators of 256 columns, so the epilogue of a tile overlaps the MMAs of
+  // the next. MH == 2: the two halves of one 256-token tile fill all 512 columns; one
+  // dequantized weight tile then feeds two MMAs, which halves the dequantizer work per flop.
+  constexpr uint32_t NACC = MH == 1 ? 2 : 1, ACC_COLS = MH * BN;
+  constexpr int A_TILE_BYTES = G::A_TILE_BYTES;
   extern __shared__ uint8_t smem_raw[];
   // Swizzled operand tiles need 1024-byte alignment.
   const uint32_t raw = ptx::smem_u32(smem_raw);
@@ -326,7 +333,7 @@ gemm_q_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm
       bool ok = true;
       for (uint32_t u = blockIdx.x; u < units && ok; u += gridDim.x) {
         const Unit w = unit_of(p, u);
-        const int32_t m0 = (int32_t)((w.tile % p.m_tiles) * BM);
+        const int32_t m0 = (int32_t)((w.tile % p.m_tiles) * (BM * MH));
         for (uint32_t ks = w.ks0; ks < w.ks1; ks++, it++) {
           const uint32_t s = it % AS, use = it / AS;
           if (use > 0 && !wait_or_abort<true>(&bars->a_empty[s], (use - 1) & 1, abort_flag)) {
@@ -367,13 +374,13 @@ gemm_q_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm
     bool ok = true;
     for (uint32_t u = blockIdx.x; u < units && ok; u += gridDim.x, tile_iter++) {
       const Unit w = unit_of(p, u);
-      const uint32_t acc = tile_iter & 1, acc_use = tile_iter >> 1;
+      const uint32_t acc = tile_iter % NACC, acc_use = tile_iter / NACC;
       if (acc_use > 0 && !wait_or_abort<true>(&bars->acc_empty[acc], (acc_use - 1) & 1, abort_flag)) {
         if (lane == 0) raise_abort(p.fault, abort_flag);
         break;
       }
       tc_fence_after();
-      const uint32_t d_tmem = tmem_base + acc * BN;
+      const uint32_t d_tmem = tmem_base + acc * ACC_COLS;
       for (uint32_t ks = w.ks0; ks < w.ks1; ks++, it++) {
         const uint32_t sa = it % AS, pha = (it / AS) & 1, sb = it % BS, phb = (it / BS) & 1;
         if (!wait_or_abort<true>(&bars->a_full[sa], pha, abort_flag) || !wait_or_abort<true>(&bars->bready[sb], phb, abort_flag)) {
@@ -387,8 +394,10 @@ gemm_q_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm
           const uint64_t b_desc = smem_desc_sw128(base + G::OFF_BRING + sb * B_TILE_BYTES);
 #pragma unroll
           for (int kk = 0; kk < BK / UMMA_K; kk++)
-            umma_bf16(d_tmem, a_desc + (uint64_t)(kk * UMMA_K * 2 / 16), b_desc + (uint64_t)(kk * UMMA_K * 2 / 16), kInstrDesc,
-                      ((ks - w.ks0) | (uint32_t)kk) != 0);
+#pragma unroll
+            for (int h = 0; h < MH; h++)
+              umma_bf16(d_tmem + h * BN, a_desc + (uint64_t)((h * A_HALF_BYTES + kk * UMMA_K * 2) / 16),
+                        b_desc + (uint64_t)(kk * UMMA_K * 2 / 16), kInstrDesc, ((ks - w.ks0) | (uint32_t)kk) != 0);
           umma_commit(ptx::smem_u32(&bars->a_empty[sa]));
           umma_commit(ptx::smem_u32(&bars->bfree[sb]));
         }
@@ -443,17 +452,21 @@ gemm_q_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm
     uint32_t tile_iter = 0;
     for (uint32_t u = blockIdx.x; u < units; u += gridDim.x, tile_iter++) {
       const Unit w = unit_of(p, u);
-      const uint32_t acc = tile_iter & 1, acc_use = tile_iter >> 1;
+      const uint32_t acc = tile_iter % NACC, acc_use = tile_iter / NACC;
       if (!wait_or_abort(&bars->acc_full[acc], acc_use & 1, abort_flag)) {
         if (lane == 0) raise_abort(p.fault, abort_flag);
         break;
       }
       tc_fence_after();
-      const uint32_t m0 = (w.tile % p.m_tiles) * BM, n0 = (w.tile / p.m_tiles) * BN;
-      const uint32_t trow = quarter * 32 + lane, row = m0 + trow;
-      float* crow = p.c + (uint64_t)row * p.ldc + n0;
-      const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + acc * BN;
-      if (p.splits == 1) {
+      const uint32_t m0 = (w.tile % p.m_tiles) * (BM * MH), n0 = (w.tile / p.m_tiles) * BN;
+#pragma unroll 1
+      for (int h = 0; h < MH; h++) {
+        const uint32_t trow = h * BM + quarter * 32 + lane, row = m0 + trow;
+        float* crow = p.c + (uint64_t)row * p.ldc + n0;
+        const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + acc * ACC_COLS + h * BN;
+        // Split K: the raw accumulator goes to this unit's slot; a follow-up kernel adds the slots
+        // of every tile in split order, so the sum does not depend on timing.
+        float* slot = p.partial + ((size_t)w.tile * p.splits + w.split) * ((size_t)BM * MH * BN) + (size_t)trow * BN;
 #pragma unroll 1
         for (uint32_t c0 = 0; c0 < BN; c0 += 16) {
           uint32_t r[16];
@@ -463,37 +476,22 @@ gemm_q_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm
 #pragma unroll
             for (int q = 0; q < 4; q++) {
               const uint32_t col = n0 + c0 + q * 4;
-              if (col < p.n) {  // n is a multiple of 8, so a group of 4 is in or out as a whole
-                float4 v = make_float4(__uint_as_float(r[4 * q]) * p.alpha, __uint_as_float(r[4 * q + 1]) * p.alpha,
-                                       __uint_as_float(r[4 * q + 2]) * p.alpha, __uint_as_float(r[4 * q + 3]) * p.alpha);
-                float4* dst = reinterpret_cast<float4*>(crow + c0 + q * 4);
-                if (p.beta != 0.0f) {
-                  const float4 o = *dst;
-                  v.x += p.beta * o.x, v.y += p.beta * o.y, v.z += p.beta * o.z, v.w += p.beta * o.w;
-                }
-                *dst = v;
+              if (col >= p.n) continue;  // n is a multiple of 8, so a group of 4 is in or out as a whole
+              float4 v = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]), __uint_as_float(r[4 * q + 2]),
+                                     __uint_as_float(r[4 * q + 3]));
+              if (p.splits > 1) {
+                __stcg(reinterpret_cast<float4*>(slot + c0 + q * 4), v);
+                continue;
               }
+              v.x *= p.alpha, v.y *= p.alpha, v.z *= p.alpha, v.w *= p.alpha;
+              float4* dst = reinterpret_cast<float4*>(crow + c0 + q * 4);
+              if (p.beta != 0.0f) {
+                const float4 o = *dst;
+                v.x += p.beta * o.x, v.y += p.beta * o.y, v.z += p.beta * o.z, v.w += p.beta * o.w;
+              }
+              *dst = v;
             }
           }
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars->acc_empty[acc]));
-        continue;
-      }
-      // Split K: leave the raw accumulator in this unit's slot; a follow-up kernel adds the
-      // slots of every tile in split order, so the sum does not depend on timing.
-      float* slot = p.partial + ((size_t)w.tile * p.splits + w.split) * (BM * BN) + (size_t)trow * BN;
-#pragma unroll 1
-      for (uint32_t c0 = 0; c0 < BN; c0 += 16) {
-        uint32_t r[16];
-        tmem_ld16(taddr + c0, r);
-        tmem_ld_wait();
-        if (row < p.m && n0 + c0 < p.n) {
-#pragma unroll
-          for (int q = 0; q < 4; q++)
-            __stcg(reinterpret_cast<float4*>(slot + c0 + q * 4), make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
-                                                                               __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3])));
         }
       }
       tc_fence_before();
@@ -516,11 +514,11 @@ __global__ void splitk_reduce_kernel(const GemmParams p) {
   ptx::pdl_launch_dependents();
   ptx::pdl_wait();
   const uint64_t quads_per_row = p.n / 4, total = (uint64_t)p.m * quads_per_row;
-  const size_t slot = (size_t)BM * BN;
+  const size_t slot = (size_t)p.tile_rows * BN;
   for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
     const uint32_t row = (uint32_t)(i / quads_per_row), col = (uint32_t)(i % quads_per_row) * 4;
-    const uint32_t tile = (row / BM) + (col / BN) * p.m_tiles;
-    const float* src = p.partial + (size_t)tile * p.splits * slot + (size_t)(row % BM) * BN + (col % BN);
+    const uint32_t tile = (row / p.tile_rows) + (col / BN) * p.m_tiles;
+    const float* src = p.partial + (size_t)tile * p.splits * slot + (size_t)(row % p.tile_rows) * BN + (col % BN);
     float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     uint32_t sp = 0;
     for (; sp + 4 <= p.splits; sp += 4) {  // four loads in flight, added in split order
@@ -547,18 +545,18 @@ __global__ void splitk_reduce_kernel(const GemmParams p) {
   }
 }
 
-template <int DT>
+template <int DT, int MH>
 int32_t launch_gemm(AionCudaDevice* dev, const MatMulArgs& g, const __nv_bfloat16* a_bf16, uint32_t splits, float* partial) {
-  using G = GemmGeom<DT>;
+  using G = GemmGeom<DT, MH>;
   static bool configured[64] = {};
-  auto kernel = gemm_q_tcgen05_kernel<DT>;
+  auto kernel = gemm_q_tcgen05_kernel<DT, MH>;
   if (dev->ordinal < 64 && !configured[dev->ordinal]) {
     AION_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM_BYTES));
     configured[dev->ordinal] = true;
   }
   const uint64_t kblocks = g.k / QK;
   CUtensorMap tmap_a, tmap_b;
-  if (int32_t st = tensor_map_bf16_sw128(a_bf16, g.m, g.k, g.k * 2, BK, BM, &tmap_a)) return st;
+  if (int32_t st = tensor_map_bf16_sw128(a_bf16, g.m, g.k, g.k * 2, BK, BM * MH, &tmap_a)) return st;
   {
     // Packed weights as [K/32][ldb/8][8 blocks]: box = 2 block rows x 32 groups x 8 blocks.
     const uint64_t dims[3] = {8ull * G::BB, g.n / 8, kblocks};
@@ -571,7 +569,8 @@ int32_t launch_gemm(AionCudaDevice* dev, const MatMulArgs& g, const __nv_bfloat1
   p.m = (uint32_t)g.m, p.n = (uint32_t)g.n, p.k = (uint32_t)g.k;
   p.ldc = g.ldc;
   p.alpha = g.alpha, p.beta = g.beta;
-  p.m_tiles = (uint32_t)ceil_div(g.m, (uint64_t)BM);
+  p.m_tiles = (uint32_t)ceil_div(g.m, (uint64_t)(BM * MH));
+  p.tile_rows = BM * MH;
   p.n_tiles = (uint32_t)ceil_div(g.n, (uint64_t)BN);
   p.k_stages = (uint32_t)ceil_div(g.k, (uint64_t)BK);
   p.fault = dev->fault_dev;
@@ -601,7 +600,11 @@ int32_t gemm_tcgen05(AionCudaDevice* dev, const MatMulArgs& g, bool forced) {
   if (g.m > (1u << 24) || g.n > (1u << 24) || g.k > (1u << 24)) return AION_CUDA_UNSUPPORTED;
   // Few output tiles (decode batches against narrow layers): split K so the SMs are covered.
   // A split keeps at least two k-stages; its raw 128 x 256 accumulator goes through scratch.
-  const uint64_t tiles = ceil_div(g.m, (uint64_t)BM) * ceil_div(g.n, (uint64_t)BN), k_stages = ceil_div(g.k, (uint64_t)BK);
+  // 256-token tiles (one dequantized weight tile feeds two MMAs) once there are enough of them
+  // to fill the SMs; 128-token tiles with a double-buffered accumulator otherwise.
+  const uint64_t tiles256 = ceil_div(g.m, (uint64_t)(2 * BM)) * ceil_div(g.n, (uint64_t)BN);
+  const int mh = (g.m > BM && tiles256 >= (uint64_t)dev->sm_count) ? 2 : 1;
+  const uint64_t tiles = ceil_div(g.m, (uint64_t)(BM * mh)) * ceil_div(g.n, (uint64_t)BN), k_stages = ceil_div(g.k, (uint64_t)BK);
   uint64_t splits = 1;
   if (tiles * 2 <= (uint64_t)dev->sm_count) {
     splits = (uint64_t)dev->sm_count / tiles;
@@ -611,7 +614,7 @@ int32_t gemm_tcgen05(AionCudaDevice* dev, const MatMulArgs& g, bool forced) {
   }
   // Lane scratch: the bf16 copy of the activation, then the split partials.
   const size_t a_bytes = ((size_t)g.m * g.k * sizeof(__nv_bfloat16) + 1023) & ~size_t(1023);
-  const size_t part_bytes = splits > 1 ? (size_t)tiles * splits * BM * BN * sizeof(float) : 0;
+  const size_t part_bytes = splits > 1 ? (size_t)tiles * splits * BM * mh * BN * sizeof(float) : 0;
   if (int32_t st = dev->reserve_scratch(a_bytes + part_bytes)) return st;
   __nv_bfloat16* a_bf16 = static_cast<__nv_bfloat16*>(dev->lane_scratch());
   float* partial = reinterpret_cast<float*>(static_cast<uint8_t*>(dev->lane_scratch()) + a_bytes);
@@ -621,8 +624,11 @@ int32_t gemm_tcgen05(AionCudaDevice* dev, const MatMulArgs& g, bool forced) {
     AION_CUDA_TRY(launch_pdl(convert_a_bf16_kernel, dim3(blocks), dim3(256), 0, dev->stream, g.a, g.lda, a_bf16, (uint32_t)g.m, (uint32_t)g.k,
                              g.dtype == AION_CUDA_DTYPE_Q4_0 ? 1 : 0));
   }
-  return g.dtype == AION_CUDA_DTYPE_Q4_0 ? launch_gemm<AION_CUDA_DTYPE_Q4_0>(dev, g, a_bf16, (uint32_t)splits, partial)
-                                         : launch_gemm<AION_CUDA_DTYPE_Q8_0>(dev, g, a_bf16, (uint32_t)splits, partial);
+  if (g.dtype == AION_CUDA_DTYPE_Q4_0)
+    return mh == 2 ? launch_gemm<AION_CUDA_DTYPE_Q4_0, 2>(dev, g, a_bf16, (uint32_t)splits, partial)
+                   : launch_gemm<AION_CUDA_DTYPE_Q4_0, 1>(dev, g, a_bf16, (uint32_t)splits, partial);
+  return mh == 2 ? launch_gemm<AION_CUDA_DTYPE_Q8_0, 2>(dev, g, a_bf16, (uint32_t)splits, partial)
+                 : launch_gemm<AION_CUDA_DTYPE_Q8_0, 1>(dev, g, a_bf16, (uint32_t)splits, partial);
 }
 
 }  // namespace aion

@@ -671,17 +671,29 @@ int32_t attention_launch(AionCudaDevice* dev, const AionCudaAttention* s) {
     const uint64_t span = (uint64_t)(s->window_chunk ? s->window_chunk : 1) + s->window_left + s->window_right;
     if (s->window_left != AION_CUDA_WINDOW_UNBOUNDED && s->window_right != AION_CUDA_WINDOW_UNBOUNDED && span < max_keys)
       max_keys = span;
+    // Choose the number of context splits by a small cost model: CTAs run in waves of one per
+    // SM (the ring fills shared memory), a CTA costs its 64-key stages plus a fixed ramp
+    // (first TMA round trip, fold, output) of about four stages, two more when it leaves a partial
+    // behind (write, fence, ticket), and the merge of a
+    // row's partials by one CTA grows with the splits (so they are capped near sqrt(keys / 5),
+    // where split work and merge cost balance).
+    const uint64_t sms = (uint64_t)dev->sm_count;
+    const uint64_t stages_total = (max_keys + KT - 1) / KT;
+    uint64_t cap = (uint64_t)std::sqrt(0.2 * (double)max_keys) + 1;
+    if (cap > stages_total) cap = stages_total;
+    if (cap > 256) cap = 256;
+    if (cap < 1) cap = 1;
     uint64_t splits = 1;
-    const uint64_t want = 2ull * dev->sm_count;
-    if (units < want) splits = (want + units - 1) / units;
-    const uint64_t max_splits = (max_keys + KT - 1) / KT;
-    if (splits > max_splits) splits = max_splits;
-    // One CTA merges a row's partials (about 8 KB per split at D = 256, read through one SM),
-    // while a split's own work shrinks as 1/splits: the sum is least near sqrt(keys / 5).
-    const uint64_t merge_cap = (uint64_t)std::sqrt(0.2 * (double)max_keys) + 1;
-    if (splits > merge_cap) splits = merge_cap;
-    if (splits > 256) splits = 256;
-    if (splits < 1) splits = 1;
+    double best = 1e30;
+    for (uint64_t sp = 1; sp <= cap; sp++) {
+      const uint64_t waves = (units * sp + sms - 1) / sms;
+      const double per_cta = (double)((stages_total + sp - 1) / sp) + 4.0 + (sp > 1 ? 2.0 + 0.1 * (double)sp : 0.0);
+      const double cost = (double)waves * per_cta;
+      if (cost < best * 0.999) {
+        best = cost;
+        splits = sp;
+      }
+    }
     if (dev->attn_split_override) splits = dev->attn_split_override;
     p.splits = (uint32_t)splits;
     if (splits > 1) {

@@ -194,22 +194,26 @@ __device__ __forceinline__ uint32_t unit_owner(uint64_t u, uint64_t U, uint64_t 
 
 // DT: weight dtype; NT: weights are [n,k] row-major (else K-major); MT: 8-row activation
 // tiles (1 or 2); M1: exactly one activation row (skips the odd-row half of the epilogue).
-template <int DT, bool NT, int MT, bool M1>
+template <int DT, bool NT, int MT, bool M1, bool RG = false>
 __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_in, const __grid_constant__ CUtensorMap tmap) {
   using G = Geom<DT, NT>;
   constexpr int MPA = 8 * MT;  // activation rows of the accumulator tile
   // More than 8 * MT rows of A: blockIdx.y picks a group of 8 * MT rows. Every group streams
   // the same weights (the second and later groups find them in L2), with its own slice of
   // the fix-up scratch.
-  GemvParams p = p_in;
-  if (gridDim.y > 1) {
+  // (RG, row groups, is a template parameter so that the usual kernel keeps reading its
+  // parameters from the constant bank instead of holding an adjusted copy in registers.)
+  GemvParams p_rows;
+  if (RG) {
+    p_rows = p_in;
     const uint32_t r0 = blockIdx.y * MPA;
-    p.a += (uint64_t)r0 * p.lda;
-    p.c += (uint64_t)r0 * p.ldc;
-    p.m = min((uint32_t)MPA, p.m - r0);
-    p.partials += (size_t)blockIdx.y * gridDim.x * 2 * TN * MPA;
-    p.tickets += (size_t)blockIdx.y * p.tiles * CONSUMER_WARPS;
+    p_rows.a += (uint64_t)r0 * p_in.lda;
+    p_rows.c += (uint64_t)r0 * p_in.ldc;
+    p_rows.m = min((uint32_t)MPA, p_in.m - r0);
+    p_rows.partials += (size_t)blockIdx.y * gridDim.x * 2 * TN * MPA;
+    p_rows.tickets += (size_t)blockIdx.y * p_in.tiles * CONSUMER_WARPS;
   }
+  const GemvParams& p = RG ? p_rows : p_in;
   constexpr uint32_t MP2 = M1 ? 2 : 8 * MT;  // activation rows held in shared memory
   extern __shared__ __align__(128) uint8_t smem[];
   const uint32_t smem_base = ptx::smem_u32(smem);
@@ -512,10 +516,10 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_
   }
 }
 
-template <int DT, bool NT, int MT, bool M1>
+template <int DT, bool NT, int MT, bool M1, bool RG = false>
 int32_t launch(AionCudaDevice* dev, GemvParams p, const uint8_t* b, uint64_t ldb) {
   using G = Geom<DT, NT>;
-  auto kernel = gemv_q_mma_kernel<DT, NT, MT, M1>;
+  auto kernel = gemv_q_mma_kernel<DT, NT, MT, M1, RG>;
   constexpr uint32_t MP2 = M1 ? 2 : 8 * MT;
   const size_t smem = G::OFF_ACT + act_bytes(p.stages_per_tile * KBT, MP2, MT);
   // Kernel attributes and occupancy depend on the device and the dynamic size only.
@@ -562,7 +566,7 @@ int32_t launch(AionCudaDevice* dev, GemvParams p, const uint8_t* b, uint64_t ldb
   // Scratch for tiles shared by several CTAs: two partial slots per CTA, one ticket per (tile, warp),
   // times the groups of 8 * MT rows.
   constexpr int MPA = 8 * MT;
-  const uint64_t groups = M1 ? 1 : ceil_div((uint64_t)p.m, (uint64_t)MPA);
+  const uint64_t groups = RG ? ceil_div((uint64_t)p.m, (uint64_t)MPA) : 1;
   if (groups > 65535) return fail(AION_CUDA_UNSUPPORTED, "gemv: too many rows for one launch");
   if (int32_t st = dev->reserve_gemv_fixup((size_t)groups * grid * 2 * TN * MPA * sizeof(float), (size_t)groups * p.tiles * CONSUMER_WARPS)) return st;
   p.partials = dev->lane_gemv_partials();
@@ -610,7 +614,8 @@ template <int DT, bool NT>
 int32_t launch_m(AionCudaDevice* dev, const GemvParams& p, const uint8_t* b, uint64_t ldb) {
   if (p.m == 1) return launch<DT, NT, 1, true>(dev, p, b, ldb);
   if (p.m <= 8) return launch<DT, NT, 1, false>(dev, p, b, ldb);
-  return launch<DT, NT, 2, false>(dev, p, b, ldb);
+  if (p.m <= 16) return launch<DT, NT, 2, false>(dev, p, b, ldb);
+  return launch<DT, NT, 2, false, true>(dev, p, b, ldb);  // groups of 16 rows
 }
 
 }  // namespace

@@ -94,6 +94,9 @@ struct AionCudaDevice {
   TmapCache* tmaps = nullptr;
 
   int32_t make_current() const;
+  // Recorded programs hold the addresses of the scratch buffers they were recorded with, so
+  // the buffers may not be re-allocated while one is alive.
+  int live_programs = 0;
   int32_t reserve_scratch(size_t bytes);
   int32_t reserve_tickets(size_t count);
   int32_t reserve_gemv_fixup(size_t partial_bytes, size_t tickets);

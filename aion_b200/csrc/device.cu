@@ -194,6 +194,7 @@ int32_t AionCudaDevice::make_current() const {
 int32_t AionCudaDevice::reserve_scratch(size_t bytes) {
   if (bytes <= scratch_bytes) return AION_CUDA_OK;
   if (recording) return fail(AION_CUDA_INVALID_ARGUMENT, "a recorded step needs %llu bytes of scratch that are not reserved yet: run it once before recording", (unsigned long long)bytes);
+  if (live_programs > 0) return fail(AION_CUDA_INVALID_ARGUMENT, "this step needs more device scratch than is reserved, and a recorded program still uses the current buffers: destroy the program, or run the largest step once before recording");
   // Earlier launches may still read the old buffer.
   AION_CUDA_TRY(cudaStreamSynchronize(stream));
   if (scratch) AION_CUDA_TRY(cudaFree(scratch));
@@ -209,6 +210,7 @@ int32_t AionCudaDevice::reserve_scratch(size_t bytes) {
 int32_t AionCudaDevice::reserve_tickets(size_t count) {
   if (count <= tickets_cap) return AION_CUDA_OK;
   if (recording) return fail(AION_CUDA_INVALID_ARGUMENT, "a recorded attention step needs arrival counters that are not reserved yet: run it once before recording");
+  if (live_programs > 0) return fail(AION_CUDA_INVALID_ARGUMENT, "this step needs more device scratch than is reserved, and a recorded program still uses the current buffers: destroy the program, or run the largest step once before recording");
   AION_CUDA_TRY(cudaStreamSynchronize(stream));
   if (tickets) AION_CUDA_TRY(cudaFree(tickets));
   tickets = nullptr;
@@ -223,6 +225,7 @@ int32_t AionCudaDevice::reserve_tickets(size_t count) {
 int32_t AionCudaDevice::reserve_gemv_fixup(size_t partial_bytes, size_t ticket_count) {
   if (partial_bytes > gemv_partials_bytes) {
     if (recording) return fail(AION_CUDA_INVALID_ARGUMENT, "a recorded matmul step needs split-tile scratch that is not reserved yet: run it once before recording");
+    if (live_programs > 0) return fail(AION_CUDA_INVALID_ARGUMENT, "this step needs more device scratch than is reserved, and a recorded program still uses the current buffers: destroy the program, or run the largest step once before recording");
     AION_CUDA_TRY(cudaStreamSynchronize(stream));
     if (gemv_partials) AION_CUDA_TRY(cudaFree(gemv_partials));
     gemv_partials = nullptr;
@@ -233,6 +236,7 @@ int32_t AionCudaDevice::reserve_gemv_fixup(size_t partial_bytes, size_t ticket_c
   }
   if (ticket_count > gemv_tickets_cap) {
     if (recording) return fail(AION_CUDA_INVALID_ARGUMENT, "a recorded matmul step needs arrival counters that are not reserved yet: run it once before recording");
+    if (live_programs > 0) return fail(AION_CUDA_INVALID_ARGUMENT, "this step needs more device scratch than is reserved, and a recorded program still uses the current buffers: destroy the program, or run the largest step once before recording");
     AION_CUDA_TRY(cudaStreamSynchronize(stream));
     if (gemv_tickets) AION_CUDA_TRY(cudaFree(gemv_tickets));
     gemv_tickets = nullptr;
@@ -462,6 +466,7 @@ int32_t aion_cuda_record_end(AionCudaDevice* dev, AionCudaProgram** out) {
     delete p;
     return cuda_fail(e, "cudaGraphInstantiate");
   }
+  dev->live_programs++;
   *out = p;
   return AION_CUDA_OK;
 }
@@ -478,6 +483,7 @@ void aion_cuda_program_destroy(AionCudaDevice* dev, AionCudaProgram* prog) {
   if (dev) {
     cudaSetDevice(dev->ordinal);
     cudaStreamSynchronize(dev->stream);
+    if (dev->live_programs > 0) dev->live_programs--;
   }
   if (prog->exec) cudaGraphExecDestroy(prog->exec);
   if (prog->graph) cudaGraphDestroy(prog->graph);

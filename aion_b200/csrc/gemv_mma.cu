@@ -1,4 +1,5 @@
-// Decode GEMV for q4_0 / q8_0 weights: C[m,n] = alpha * A[m,k] . W + beta * C, m <= 16.
+// Decode GEMV for q4_0 / q8_0 weights: C[m,n] = alpha * A[m,k] . W + beta * C, m <= 16 per
+// group of CTAs (blockIdx.y walks further groups of 16 rows over the same weights).
 //
 // Arithmetic is the reference CPU kernels' (src/aion/backend/cpu/kernels/matvec_q.zig:62-160,
 // src/aion/backend/cpu/kernels/matmul_nt_q.zig:74-95, src/aion/backend/cpu/kernels/matmul_q_i8.zig:385-497):
@@ -11,7 +12,8 @@
 //     resident at once — and CTA c takes the contiguous unit range [c*U/G, (c+1)*U/G)
 //     in tile-major order ("stream-K"), so every SM streams the same number of bytes
 //     whatever the shape: no tail wave, and narrow matrices split along K for free.
-//   * A producer warp fills a 4-stage ring with ONE tiled TMA load per stage (the weight
+//   * A producer warp fills a 2-stage ring (shallow on purpose: concurrent launches overlap
+//     as far as CTAs fit an SM) with ONE tiled TMA load per stage (the weight
 //     tensor viewed as bytes in 8-byte elements; one request per stage, because the copy
 //     engine takes about 50 ns per request and per-row bulk copies made that the
 //     bottleneck), completing on mbarriers. Blocks are 18 / 34 bytes, so nothing inside
@@ -28,7 +30,9 @@
 //     consecutive weight rows 272 bytes apart (NT).
 //   * A tile whose K range is shared by several CTAs is finished by the last of them to
 //     arrive: each writes its partial sums to scratch, takes a ticket, and the last one
-//     adds the parts in CTA order (so results do not depend on timing) and stores C.
+//     adds the parts in CTA order (so results do not depend on timing) and stores C. While
+//     independent launches are recorded into parallel lanes and there is about one tile per
+//     SM, each CTA takes exactly one whole tile instead and this step is skipped.
 //   * With programmatic dependent launch the next kernel's weight stream starts as this
 //     one's CTAs retire; only the activation read waits for the previous kernel.
 #include "common.cuh"

@@ -62,6 +62,23 @@ def _worker(rank: int, world: int, port: int, tmp: str):
     dist.all_gather(parts, torch.from_numpy(part))
     whole = oracle.matmul_q(oracle.Q4_0, xs, full, total, n, k).reshape(total, n)
     assert np.array_equal(torch.cat(parts).numpy(), whole)
+    # the decoder itself: every op is row-wise, so a request decodes to the same tokens in any shard
+    from aion_b200.decoder import DecoderConfig
+    from tests.decoder_ref import OracleDecoder
+
+    cfg = DecoderConfig(layers=1, hidden=64, ffn=128, heads=2, kv_heads=1, head_dim=32, vocab=96, ctx=8)
+    drng = np.random.default_rng(7)
+    wts = {f"l0.{nm}": (drng.standard_normal(shape) * 0.05).astype(np.float32) for nm, shape in cfg.layer_weights().items()}
+    wts["head"] = (drng.standard_normal((cfg.hidden, cfg.vocab)) * 0.05).astype(np.float32)
+    emb = drng.standard_normal((cfg.vocab, cfg.hidden)).astype(np.float32)
+    tokens = np.array([3, 17, 40, 5, 77, 90], np.int32)
+    sl = sharding.request_shard(len(tokens), world, rank)
+    mine_dec = OracleDecoder(cfg, sl.stop - sl.start, wts, emb)
+    full_dec = OracleDecoder(cfg, len(tokens), wts, emb)
+    for t in range(3):
+        _, lg_mine, nx_mine = mine_dec.step(tokens[sl] + t, np.full(sl.stop - sl.start, t, np.int32))
+        _, lg_full, nx_full = full_dec.step(tokens + t, np.full(len(tokens), t, np.int32))
+        assert np.array_equal(lg_mine, lg_full[sl]) and np.array_equal(nx_mine, nx_full[sl])
     dist.barrier()
     dist.destroy_process_group()
     open(os.path.join(tmp, f"ok{rank}"), "w").close()

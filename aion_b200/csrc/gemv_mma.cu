@@ -67,6 +67,10 @@ struct GemvParams {
   int* tickets;     // [tile][warp]
   int* fault;
   uint32_t a_vec4;  // A rows may be read as float4
+  // Pre-quantized activations (m >= 2): the shared-memory image of one group of rows,
+  // `act_image_bytes` per group, written by gemv_act_image_kernel.
+  const uint8_t* act_image;
+  uint32_t act_image_bytes;
 };
 
 template <int DT, bool NT>
@@ -196,9 +200,81 @@ __device__ __forceinline__ void compute_block(const BlockRegs<MT>& r, uint64_t (
 // CTA that owns unit u when G CTAs split U units as [c*U/G, (c+1)*U/G).
 __device__ __forceinline__ uint32_t unit_owner(uint64_t u, uint64_t U, uint64_t G) { return (uint32_t)(((u + 1) * G - 1) / U); }
 
+// One 32-block of activations -> the 8 words the MMA B fragments read (lane j finds its two
+// registers as the 8 bytes at 8j) and the block's scale, with the q4 nibble placement's 16x
+// folded in.
+//   q8: b0 = k 4j..4j+3, b1 = k 16+4j..16+4j+3            -> word 2j = w[j], word 2j+1 = w[4+j]
+//   q4: b0 = elements 8j+{0,2,4,6}, b1 = elements 8j+{1,3,5,7} (low / high nibbles of 4 code bytes)
+template <int DT>
+__device__ __forceinline__ float quantize_act_block(const float* __restrict__ src, bool vec4, uint32_t (&o)[8]) {
+  float x[QK];
+  if (vec4) {
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      const float4 f = reinterpret_cast<const float4*>(src)[i];
+      x[4 * i] = f.x; x[4 * i + 1] = f.y; x[4 * i + 2] = f.z; x[4 * i + 3] = f.w;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < QK; i++) x[i] = src[i];
+  }
+  float am[8];
+#pragma unroll
+  for (int i = 0; i < 8; i++) am[i] = fmaxf(fmaxf(fabsf(x[4 * i]), fabsf(x[4 * i + 1])), fmaxf(fabsf(x[4 * i + 2]), fabsf(x[4 * i + 3])));
+  const float amax = fmaxf(fmaxf(fmaxf(am[0], am[1]), fmaxf(am[2], am[3])), fmaxf(fmaxf(am[4], am[5]), fmaxf(am[6], am[7])));
+  float scale, inv;
+  activation_block_scales(amax, &scale, &inv);
+  uint32_t w[8];
+#pragma unroll
+  for (int i = 0; i < 8; i++) {
+    const uint32_t q0 = (uint32_t)quantize_activation_with_inv(x[4 * i], inv) & 0xFF;
+    const uint32_t q1 = (uint32_t)quantize_activation_with_inv(x[4 * i + 1], inv) & 0xFF;
+    const uint32_t q2 = (uint32_t)quantize_activation_with_inv(x[4 * i + 2], inv) & 0xFF;
+    const uint32_t q3 = (uint32_t)quantize_activation_with_inv(x[4 * i + 3], inv) & 0xFF;
+    w[i] = (DT == AION_CUDA_DTYPE_Q8_0) ? (q0 | (q1 << 8) | (q2 << 16) | (q3 << 24))    // elements in order
+                                         : (q0 | (q2 << 8) | (q1 << 16) | (q3 << 24));   // (e0, e2 | e1, e3)
+  }
+#pragma unroll
+  for (int jj = 0; jj < 4; jj++) {
+    if (DT == AION_CUDA_DTYPE_Q8_0) {
+      o[2 * jj] = w[jj];
+      o[2 * jj + 1] = w[4 + jj];
+    } else {
+      o[2 * jj] = (w[2 * jj] & 0xFFFFu) | (w[2 * jj + 1] << 16);
+      o[2 * jj + 1] = (w[2 * jj] >> 16) | (w[2 * jj + 1] & 0xFFFF0000u);
+    }
+  }
+  const float fold = (DT == AION_CUDA_DTYPE_Q4_0) ? 0.0625f : 1.0f;  // undoes the 16x of the nibble placement (exact)
+  return scale * fold;
+}
+
+// Quantizes A once per launch into the image the GEMV CTAs copy into shared memory: for
+// every group of `mpa` rows, per K block `mpa` rows of 32 codes, then per K block `quads`
+// scale quads (s_even, s_even, s_odd, s_odd). Rows past m and blocks past kblocks are
+// written as zeros (a zero scale contributes nothing). One thread per (group, block, row).
+template <int DT>
+__global__ void gemv_act_image_kernel(const float* __restrict__ a, uint64_t lda, uint32_t m, uint32_t kblocks, uint32_t kb_pad,
+                                      uint32_t mpa, uint32_t quads, uint32_t groups, uint8_t* __restrict__ image,
+                                      uint32_t group_bytes, uint32_t a_vec4) {
+  const uint32_t items = groups * kb_pad * mpa;
+  const uint32_t item = blockIdx.x * blockDim.x + threadIdx.x;
+  if (item >= items) return;
+  const uint32_t r = item % mpa, kb = (item / mpa) % kb_pad, g = item / (mpa * kb_pad);
+  const uint32_t row = g * mpa + r;
+  uint32_t o[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  float sc = 0.0f;
+  if (row < m && kb < kblocks) sc = quantize_act_block<DT>(a + (uint64_t)row * lda + (uint64_t)kb * QK, a_vec4 != 0, o);
+  uint8_t* base = image + (size_t)g * group_bytes;
+  uint4* dst = reinterpret_cast<uint4*>(base + ((size_t)kb * mpa + r) * 32);
+  dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+  dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+  float* act_s = reinterpret_cast<float*>(base + (size_t)kb_pad * mpa * 32);
+  *reinterpret_cast<float2*>(act_s + ((size_t)kb * quads + (r >> 1)) * 4 + 2 * (r & 1)) = make_float2(sc, sc);
+}
+
 // DT: weight dtype; NT: weights are [n,k] row-major (else K-major); MT: 8-row activation
 // tiles (1 or 2); M1: exactly one activation row (skips the odd-row half of the epilogue).
-template <int DT, bool NT, int MT, bool M1, bool RG = false>
+template <int DT, bool NT, int MT, bool M1, bool RG = false, bool PREQ = false>
 __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_in, const __grid_constant__ CUtensorMap tmap) {
   using G = Geom<DT, NT>;
   constexpr int MPA = 8 * MT;  // activation rows of the accumulator tile
@@ -232,6 +308,8 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_
   const uint32_t bar_full = smem_base + G::OFF_BARS;
   const uint32_t bar_empty = bar_full + NS * 8;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + G::OFF_BARS + 2 * NS * 8);
+  const uint32_t bar_act = smem_base + G::OFF_BARS + 64;  // the activation image has landed (PREQ)
+  static_assert(2 * NS * 8 + 4 <= 64, "barrier block layout");
   const uint32_t kb_pad = p.stages_per_tile * KBT;  // K blocks rounded up to whole stages
   uint8_t* act_q = smem + G::OFF_ACT;
   constexpr uint32_t QUADS = M1 ? 1 : 4 * MT;  // scale quads per K block
@@ -247,6 +325,7 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_
         ptx::mbar_init(bar_full + 8 * s, 1);
         ptx::mbar_init(bar_empty + 8 * s, CONSUMER_WARPS);
       }
+      if (PREQ) ptx::mbar_init(bar_act, 1);
       *abort_flag = 0;
       ptx::fence_barrier_init();
     }
@@ -296,7 +375,7 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_
   // ---------------- consumers ----------------
   // Scales start at zero: a pad row (m odd) and rows never written must contribute
   // nothing, whatever their code bytes hold (an integer dot is always finite).
-  {
+  if (!PREQ) {
     float4* z = reinterpret_cast<float4*>(act_s);
     const uint32_t quads = kb_pad * QUADS;
     for (uint32_t i = tid; i < quads; i += CONSUMER_THREADS) z[i] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -307,60 +386,31 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_
   // Everything below reads what the previous kernel wrote (A, and C when beta != 0).
   ptx::pdl_wait();
 
-  {
+  if (PREQ) {
+    // A was quantized once for all CTAs: one bulk copy brings this group's image in.
+    if (tid == 0) {
+      ptx::mbar_arrive_expect_tx(bar_act, p.act_image_bytes);
+      ptx::bulk_g2s(smem_base + G::OFF_ACT, p.act_image + (size_t)(RG ? blockIdx.y : 0) * p.act_image_bytes, p.act_image_bytes, bar_act);
+    }
+    if (!ptx::mbar_wait_bounded(bar_act, 0)) {
+      if (lane == 0) {
+        atomicExch(p.fault, FAULT_WAIT_EXPIRED);
+        *abort_flag = 1;
+      }
+    }
+  } else {
     // Quantize all of A, one thread per 32-block (no cross-lane traffic, 32 independent
     // elements of instruction-level parallelism): the block's 128 bytes are one cache line.
     const uint32_t items = p.m * p.kblocks;
-    const float fold = (DT == AION_CUDA_DTYPE_Q4_0) ? 0.0625f : 1.0f;  // undoes the 16x of the nibble placement (exact)
     for (uint32_t item = tid; item < items; item += CONSUMER_THREADS) {
       const uint32_t r = item / p.kblocks, kb = item - r * p.kblocks;
-      const float* src = p.a + (uint64_t)r * p.lda + (uint64_t)kb * QK;
-      float x[QK];
-      if (p.a_vec4) {
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-          const float4 f = reinterpret_cast<const float4*>(src)[i];
-          x[4 * i] = f.x; x[4 * i + 1] = f.y; x[4 * i + 2] = f.z; x[4 * i + 3] = f.w;
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < QK; i++) x[i] = src[i];
-      }
-      float am[8];
-#pragma unroll
-      for (int i = 0; i < 8; i++) am[i] = fmaxf(fmaxf(fabsf(x[4 * i]), fabsf(x[4 * i + 1])), fmaxf(fabsf(x[4 * i + 2]), fabsf(x[4 * i + 3])));
-      const float amax = fmaxf(fmaxf(fmaxf(am[0], am[1]), fmaxf(am[2], am[3])), fmaxf(fmaxf(am[4], am[5]), fmaxf(am[6], am[7])));
-      float scale, inv;
-      activation_block_scales(amax, &scale, &inv);
-      uint32_t w[8];
-#pragma unroll
-      for (int i = 0; i < 8; i++) {
-        const uint32_t q0 = (uint32_t)quantize_activation_with_inv(x[4 * i], inv) & 0xFF;
-        const uint32_t q1 = (uint32_t)quantize_activation_with_inv(x[4 * i + 1], inv) & 0xFF;
-        const uint32_t q2 = (uint32_t)quantize_activation_with_inv(x[4 * i + 2], inv) & 0xFF;
-        const uint32_t q3 = (uint32_t)quantize_activation_with_inv(x[4 * i + 3], inv) & 0xFF;
-        w[i] = (DT == AION_CUDA_DTYPE_Q8_0) ? (q0 | (q1 << 8) | (q2 << 16) | (q3 << 24))    // elements in order
-                                             : (q0 | (q2 << 8) | (q1 << 16) | (q3 << 24));   // (e0, e2 | e1, e3)
-      }
-      // MMA B-fragment lane j finds its two registers as the 8 bytes at 8j.
-      //   q8: b0 = k 4j..4j+3, b1 = k 16+4j..16+4j+3            -> word 2j = w[j], word 2j+1 = w[4+j]
-      //   q4: b0 = elements 8j+{0,2,4,6}, b1 = elements 8j+{1,3,5,7} (low / high nibbles of 4 code bytes)
       uint32_t o[8];
-#pragma unroll
-      for (int jj = 0; jj < 4; jj++) {
-        if (DT == AION_CUDA_DTYPE_Q8_0) {
-          o[2 * jj] = w[jj];
-          o[2 * jj + 1] = w[4 + jj];
-        } else {
-          o[2 * jj] = (w[2 * jj] & 0xFFFFu) | (w[2 * jj + 1] << 16);
-          o[2 * jj + 1] = (w[2 * jj] >> 16) | (w[2 * jj + 1] & 0xFFFF0000u);
-        }
-      }
+      const float sc = quantize_act_block<DT>(p.a + (uint64_t)r * p.lda + (uint64_t)kb * QK, p.a_vec4 != 0, o);
       uint4* dst = reinterpret_cast<uint4*>(act_q + ((size_t)kb * MP2 + r) * 32);
       dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
       dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
       float* sq = act_s + ((size_t)kb * QUADS + (r >> 1)) * 4 + 2 * (r & 1);
-      *reinterpret_cast<float2*>(sq) = make_float2(scale * fold, scale * fold);
+      *reinterpret_cast<float2*>(sq) = make_float2(sc, sc);
     }
   }
   asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_THREADS) : "memory");
@@ -520,10 +570,10 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_
   }
 }
 
-template <int DT, bool NT, int MT, bool M1, bool RG = false>
+template <int DT, bool NT, int MT, bool M1, bool RG = false, bool PREQ = false>
 int32_t launch(AionCudaDevice* dev, GemvParams p, const uint8_t* b, uint64_t ldb) {
   using G = Geom<DT, NT>;
-  auto kernel = gemv_q_mma_kernel<DT, NT, MT, M1, RG>;
+  auto kernel = gemv_q_mma_kernel<DT, NT, MT, M1, RG, PREQ>;
   constexpr uint32_t MP2 = M1 ? 2 : 8 * MT;
   const size_t smem = G::OFF_ACT + act_bytes(p.stages_per_tile * KBT, MP2, MT);
   // Kernel attributes and occupancy depend on the device and the dynamic size only.
@@ -576,6 +626,20 @@ int32_t launch(AionCudaDevice* dev, GemvParams p, const uint8_t* b, uint64_t ldb
   p.partials = dev->lane_gemv_partials();
   p.tickets = dev->lane_gemv_tickets();
 
+  if (PREQ) {
+    // Quantize A once, into lane scratch, in the layout the CTAs copy into shared memory.
+    const uint32_t kb_pad = p.stages_per_tile * KBT;
+    const size_t image_bytes = act_bytes(kb_pad, MP2, MT);
+    if (int32_t st = dev->reserve_scratch(groups * image_bytes)) return st;
+    uint8_t* image = static_cast<uint8_t*>(dev->lane_scratch());
+    const uint32_t items = (uint32_t)(groups * kb_pad * MPA);
+    gemv_act_image_kernel<DT><<<(items + 127) / 128, 128, 0, dev->stream>>>(p.a, p.lda, p.m, p.kblocks, kb_pad, (uint32_t)MPA, (uint32_t)(4 * MT),
+                                                                          (uint32_t)groups, image, (uint32_t)image_bytes, p.a_vec4);
+    AION_CUDA_TRY(cudaGetLastError());
+    p.act_image = image;
+    p.act_image_bytes = (uint32_t)image_bytes;
+  }
+
   // The weight tensor as bytes in 8-byte elements.
   const CUtensorMap* tm = nullptr;
   if (!NT && DT == AION_CUDA_DTYPE_Q4_0) {
@@ -616,10 +680,11 @@ int32_t launch(AionCudaDevice* dev, GemvParams p, const uint8_t* b, uint64_t ldb
 
 template <int DT, bool NT>
 int32_t launch_m(AionCudaDevice* dev, const GemvParams& p, const uint8_t* b, uint64_t ldb) {
+  // m >= 2: A is quantized once by a small kernel instead of by every CTA.
   if (p.m == 1) return launch<DT, NT, 1, true>(dev, p, b, ldb);
-  if (p.m <= 8) return launch<DT, NT, 1, false>(dev, p, b, ldb);
-  if (p.m <= 16) return launch<DT, NT, 2, false>(dev, p, b, ldb);
-  return launch<DT, NT, 2, false, true>(dev, p, b, ldb);  // groups of 16 rows
+  if (p.m <= 8) return launch<DT, NT, 1, false, false, true>(dev, p, b, ldb);
+  if (p.m <= 16) return launch<DT, NT, 2, false, false, true>(dev, p, b, ldb);
+  return launch<DT, NT, 2, false, true, true>(dev, p, b, ldb);  // groups of 16 rows
 }
 
 }  // namespace

@@ -529,8 +529,9 @@ int32_t aion_cuda_argmax(AionCudaDevice* dev, const AionCudaArgMax* s) {
   if (int32_t st = resolve(s->out, s->outer * sizeof(int32_t), "argmax.out", &out)) return st;
   if (int32_t st = resolve(s->in, s->outer * s->n * sizeof(float), "argmax.in", &in)) return st;
   if (s->outer > 65535) return fail(AION_CUDA_UNSUPPORTED, "argmax: at most 65535 rows per launch, got %llu", (unsigned long long)s->outer);
-  // Chunks of at least 4096 elements, enough of them to cover the SMs about twice.
-  uint64_t chunks = ceil_div(2ull * dev->sm_count, s->outer);
+  // Chunks of at least 4096 elements, enough of them for about eight blocks per SM (a block
+  // is one pass of dependent loads, so many small blocks hide the latency better than few).
+  uint64_t chunks = ceil_div(8ull * dev->sm_count, s->outer);
   const uint64_t max_chunks = ceil_div(s->n, (uint64_t)4096);
   if (chunks > max_chunks) chunks = max_chunks;
   if (chunks < 1) chunks = 1;

@@ -545,6 +545,30 @@ __global__ void splitk_reduce_kernel(const GemmParams p) {
   }
 }
 
+// `MatMulNT` weights, q8_0 [n][k/32] blocks in any QuantBlockOrder (src/aion/backend/types.zig:185-204),
+// re-laid as K-major [k/32][n] blocks for the GEMM. Both layouts quantize along K, so a block
+// holds the same 34 bytes either way: this is a permutation of blocks. One thread per block,
+// n fastest, so the K-major writes are contiguous.
+__global__ void nt_to_kmajor_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, uint64_t n, uint64_t kblocks,
+                                    int group, int chunk) {
+  ptx::pdl_launch_dependents();
+  ptx::pdl_wait();
+  const uint64_t total = n * kblocks;
+  for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+    const uint64_t kb = i / n, r = i % n;
+    const uint8_t* seg = src + ((r / group) * kblocks + kb) * (uint64_t)group * Q8_BYTES;
+    const int rg = (int)(r % group);
+    uint16_t* out = reinterpret_cast<uint16_t*>(dst + i * Q8_BYTES);  // blocks are 2-byte aligned
+    out[0] = *reinterpret_cast<const uint16_t*>(seg + rg * 2);
+    const uint8_t* quants = seg + 2 * group;
+#pragma unroll
+    for (int t = 0; t < 16; t++) {
+      const int e = 2 * t;  // a pair of codes never straddles a chunk (chunks are 4 or 16 bytes)
+      out[1 + t] = *reinterpret_cast<const uint16_t*>(quants + ((uint64_t)(e / chunk) * group + rg) * chunk + (e % chunk));
+    }
+  }
+}
+
 template <int DT, int MH>
 int32_t launch_gemm(AionCudaDevice* dev, const MatMulArgs& g, const __nv_bfloat16* a_bf16, uint32_t splits, float* partial) {
   using G = GemmGeom<DT, MH>;
@@ -591,18 +615,33 @@ int32_t launch_gemm(AionCudaDevice* dev, const MatMulArgs& g, const __nv_bfloat1
 
 // Returns UNSUPPORTED (without setting a message) for shapes this kernel does not read, so
 // the caller can route them to the any-shape kernel.
-int32_t gemm_tcgen05(AionCudaDevice* dev, const MatMulArgs& g, bool forced) {
+int32_t gemm_tcgen05(AionCudaDevice* dev, const MatMulArgs& g_in, bool forced) {
   (void)forced;
-  if (g.nt) return AION_CUDA_UNSUPPORTED;
+  MatMulArgs g = g_in;
   if (g.dtype != AION_CUDA_DTYPE_Q4_0 && g.dtype != AION_CUDA_DTYPE_Q8_0) return AION_CUDA_UNSUPPORTED;
   if (g.m == 0 || g.n == 0) return AION_CUDA_OK;
-  if ((g.n & 7) || (g.ldb & 7) || ((uintptr_t)g.b & 15) || ((uintptr_t)g.c & 15) || (g.ldc & 3)) return AION_CUDA_UNSUPPORTED;
+  // `MatMulNT`: the same kernel after a block permutation of the weights into lane scratch
+  // (the reference's weight-layout pass does the equivalent once per model; here it costs one
+  // pass over the weight per call, a few percent of a prefill GEMM).
+  size_t relaid_bytes = 0;
+  int nt_group = 1, nt_chunk = 4;
+  if (g.nt) {
+    if (g.dtype != AION_CUDA_DTYPE_Q8_0 || !block_order_info(g.order, &nt_group, &nt_chunk)) return AION_CUDA_UNSUPPORTED;
+    if ((g.n & 7) || ((uintptr_t)g.b & 1)) return AION_CUDA_UNSUPPORTED;
+    relaid_bytes = ((size_t)g.n * (g.k / QK) * Q8_BYTES + 1023) & ~size_t(1023);
+    g.ldb = g.n;
+  } else if ((g.ldb & 7) || ((uintptr_t)g.b & 15)) {
+    return AION_CUDA_UNSUPPORTED;
+  }
+  if ((g.n & 7) || ((uintptr_t)g.c & 15) || (g.ldc & 3)) return AION_CUDA_UNSUPPORTED;
   if (g.m > (1u << 24) || g.n > (1u << 24) || g.k > (1u << 24)) return AION_CUDA_UNSUPPORTED;
   // Few output tiles (decode batches against narrow layers): split K so the SMs are covered.
   // A split keeps at least two k-stages; its raw 128 x 256 accumulator goes through scratch.
   // 256-token tiles (one dequantized weight tile feeds two MMAs) once there are enough of them
   // to fill the SMs; 128-token tiles with a double-buffered accumulator otherwise.
   const uint64_t tiles256 = ceil_div(g.m, (uint64_t)(2 * BM)) * ceil_div(g.n, (uint64_t)BN);
+  // (fewer 256-token tiles with a K split to fill the SMs measured slower: m = 512 x 8192 columns
+  // took 47 us that way against 39 us with 128-token tiles)
   const int mh = (g.m > BM && tiles256 >= (uint64_t)dev->sm_count) ? 2 : 1;
   const uint64_t tiles = ceil_div(g.m, (uint64_t)(BM * mh)) * ceil_div(g.n, (uint64_t)BN), k_stages = ceil_div(g.k, (uint64_t)BK);
   uint64_t splits = 1;
@@ -615,9 +654,17 @@ int32_t gemm_tcgen05(AionCudaDevice* dev, const MatMulArgs& g, bool forced) {
   // Lane scratch: the bf16 copy of the activation, then the split partials.
   const size_t a_bytes = ((size_t)g.m * g.k * sizeof(__nv_bfloat16) + 1023) & ~size_t(1023);
   const size_t part_bytes = splits > 1 ? (size_t)tiles * splits * BM * mh * BN * sizeof(float) : 0;
-  if (int32_t st = dev->reserve_scratch(a_bytes + part_bytes)) return st;
-  __nv_bfloat16* a_bf16 = static_cast<__nv_bfloat16*>(dev->lane_scratch());
-  float* partial = reinterpret_cast<float*>(static_cast<uint8_t*>(dev->lane_scratch()) + a_bytes);
+  if (int32_t st = dev->reserve_scratch(relaid_bytes + a_bytes + part_bytes)) return st;
+  uint8_t* scratch = static_cast<uint8_t*>(dev->lane_scratch());
+  if (g.nt) {
+    const uint64_t total = g.n * (g.k / QK);
+    const unsigned blocks = (unsigned)std::min<uint64_t>(ceil_div(total, (uint64_t)256), (uint64_t)dev->sm_count * 16);
+    AION_CUDA_TRY(launch_pdl(nt_to_kmajor_kernel, dim3(blocks), dim3(256), 0, dev->stream, g.b, scratch, g.n, g.k / QK, nt_group, nt_chunk));
+    g.b = scratch;
+    g.nt = false;
+  }
+  __nv_bfloat16* a_bf16 = reinterpret_cast<__nv_bfloat16*>(scratch + relaid_bytes);
+  float* partial = reinterpret_cast<float*>(scratch + relaid_bytes + a_bytes);
   {
     const uint64_t groups = g.m * (g.k / 8);
     const unsigned blocks = (unsigned)std::min<uint64_t>(ceil_div(groups, (uint64_t)256), (uint64_t)dev->sm_count * 8);

@@ -106,3 +106,21 @@ def test_rows_between_gemv_and_gemm_keep_int8_arithmetic(backend, m):
     got = run_matmul(backend, capi.DTYPE_Q4_0, a, b, m, n, k)
     want = oracle.matmul_q(capi.DTYPE_Q4_0, a, b, m, n, k).reshape(m, n)
     assert rel_l2(got, want) <= 2e-5
+
+
+@pytest.mark.parametrize("order", [capi.ORDER_ROW_MAJOR, capi.ORDER_LANES8, capi.ORDER_LANES32X16])
+@pytest.mark.parametrize("m,n,k", [(64, 256, 256), (300, 512, 2048)])
+def test_gemm_nt_q8_prefill(backend, order, m, n, k):
+    # MatMulNT with prefill-sized m: the weights are permuted to K-major on the device, then the same GEMM
+    from tests.gpu_util import run_matmul_nt
+    rng = np.random.default_rng(77)
+    w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    rows = oracle.quantize(oracle.Q8_0, w, 1)
+    tile = oracle.relayout_q8(order, n, k, rows)
+    got = run_matmul_nt(backend, a, tile, m, n, k, order=order)
+    want_i8 = oracle.matmul_nt_q8(a, rows, m, n, k).reshape(m, n)
+    kmajor = oracle.quantize(oracle.Q8_0, np.ascontiguousarray(w.T), 0)
+    want_deq = oracle.matmul_deqf32(oracle.Q8_0, a, kmajor, m, n, k).reshape(m, n)
+    assert rel_l2(got, want_i8) <= TOL_INT8A
+    assert rel_l2(got, want_deq) <= TOL_DEQ

@@ -247,26 +247,31 @@ def test_argument_errors(backend):
     assert backend.quant_block_order == capi.ORDER_ROW_MAJOR
 
 
-def test_scratch_cannot_move_under_a_recorded_program(backend):
+def test_scratch_cannot_move_under_a_recorded_program():
     """A recorded program holds scratch addresses: a later, larger step must be refused, not re-allocate."""
     import ctypes as C
-    lib, dev = backend._lib, backend.handle
-    rng = np.random.default_rng(0)
-    k, n = 64, 8
-    a = rng.standard_normal((1, k)).astype(np.float32)
-    b = oracle.quantize(oracle.Q4_0, (rng.standard_normal((k, n)) * 0.02).astype(np.float32), 0)
-    run_matmul(backend, capi.DTYPE_Q4_0, a, b, 1, n, k, flags=capi.MATMUL_FORCE_GENERIC)  # sizes scratch for this shape
-    assert lib.aion_cuda_record_begin(dev) == capi.OK
-    prog = C.c_void_p()
-    assert lib.aion_cuda_record_end(dev, C.byref(prog)) == capi.OK
+    backend = CudaBackend(0)  # its own device object, so its scratch starts empty whatever ran before
     try:
-        big_m = 4096  # the any-shape kernel's activation scratch grows with m * k
-        a_big = rng.standard_normal((big_m, 8192)).astype(np.float32)
-        b_big = oracle.quantize(oracle.Q8_0, (rng.standard_normal((8192, n)) * 0.02).astype(np.float32), 0)
-        with pytest.raises(BackendError) as e:
-            run_matmul(backend, capi.DTYPE_Q8_0, a_big, b_big, big_m, n, 8192, flags=capi.MATMUL_FORCE_GENERIC)
-        assert e.value.status == capi.INVALID_ARGUMENT
+        lib, dev = backend._lib, backend.handle
+        rng = np.random.default_rng(0)
+        k, n = 64, 8
+        a = rng.standard_normal((1, k)).astype(np.float32)
+        b = oracle.quantize(oracle.Q4_0, (rng.standard_normal((k, n)) * 0.02).astype(np.float32), 0)
+        run_matmul(backend, capi.DTYPE_Q4_0, a, b, 1, n, k, flags=capi.MATMUL_FORCE_GENERIC)  # sizes scratch for this shape
+        assert lib.aion_cuda_record_begin(dev) == capi.OK
+        prog = C.c_void_p()
+        assert lib.aion_cuda_record_end(dev, C.byref(prog)) == capi.OK
+        big_m, big_k = 512, 4096  # the any-shape kernel's activation scratch grows with m * k
+        a_big = rng.standard_normal((big_m, big_k)).astype(np.float32)
+        b_big = oracle.quantize(oracle.Q8_0, (rng.standard_normal((big_k, n)) * 0.02).astype(np.float32), 0)
+        try:
+            with pytest.raises(BackendError) as e:
+                run_matmul(backend, capi.DTYPE_Q8_0, a_big, b_big, big_m, n, big_k, flags=capi.MATMUL_FORCE_GENERIC)
+            assert e.value.status == capi.INVALID_ARGUMENT
+        finally:
+            lib.aion_cuda_program_destroy(dev, prog)
+        got = run_matmul(backend, capi.DTYPE_Q8_0, a_big, b_big, big_m, n, big_k, flags=capi.MATMUL_FORCE_GENERIC)
+        want = oracle.matmul_q(oracle.Q8_0, a_big, b_big, big_m, n, big_k).reshape(big_m, n)
+        assert np.sum((got - want) ** 2) / np.sum(want ** 2) < 1e-10
     finally:
-        lib.aion_cuda_program_destroy(dev, prog)
-    got = run_matmul(backend, capi.DTYPE_Q8_0, a_big, b_big, big_m, n, 8192, flags=capi.MATMUL_FORCE_GENERIC)
-    assert np.isfinite(got).all()
+        backend.deinit()

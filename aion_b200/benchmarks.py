@@ -142,37 +142,45 @@ def decode_leg(torch, dist, backend: CudaBackend, rank: int, world: int, local_r
 
 
 def gemm_leg(torch, backend: CudaBackend, local_rank: int, dtype: int, m: int, n: int, k: int, iters: int = 20, copies: int = 8,
-             peak_tflops: float = 1622.7) -> dict:
-    """Prefill GEMM TFLOP/s: `copies` distinct weight matrices walked in turn, device-timed."""
+             peak_tflops: float = 1622.7, nt: bool = False) -> dict:
+    """Prefill GEMM TFLOP/s: `copies` distinct weight matrices walked in turn, device-timed.
+    nt: the `MatMulNT` step (q8_0 [n, k] row-major weights) instead of `MatMul`."""
     lib, dev, mem = backend._lib, backend.handle, backend.device_memory
     bb = 18 if dtype == capi.DTYPE_Q4_0 else 34
     nb = (k // 32) * n * bb
     gen = torch.Generator(device="cuda")
     gen.manual_seed(1234)
-    shape = (C.c_uint64 * 2)(k, n)
+    shape = (C.c_uint64 * 2)(*((n, k) if nt else (k, n)))
     hb = []
     for _ in range(copies):
-        w = torch.randn((k, n), generator=gen, device="cuda", dtype=torch.float32) * 0.02
+        w = torch.randn((n, k) if nt else (k, n), generator=gen, device="cuda", dtype=torch.float32) * 0.02
         torch.cuda.synchronize()
         h = mem.alloc(nb, 256)
         src, dst = capi.Operand(w.data_ptr(), 0, w.numel() * 4), capi.Operand(h, 0, nb)
-        _chk(lib.aion_cuda_quantize(dev, dtype, C.byref(src), shape, 2, 0, C.byref(dst)))
+        _chk(lib.aion_cuda_quantize(dev, dtype, C.byref(src), shape, 2, 1 if nt else 0, C.byref(dst)))
         backend.sync()
         hb.append(h)
     a = torch.randn((m, k), generator=torch.Generator().manual_seed(5678), dtype=torch.float32).numpy()
     ha = mem.alloc(a.nbytes, 256)
     mem.copy_h2d(ha, 0, a)
     hc = mem.alloc(m * n * 4, 256)
-    recs = [capi.MatMul(c=capi.Operand(hc, 0, m * n * 4), a=capi.Operand(ha, 0, a.nbytes), b=capi.Operand(h, 0, nb),
-                        b_dtype=dtype, flags=capi.MATMUL_AUTO, m=m, n=n, k=k, lda=0, ldb=0, ldc=0, alpha=1.0, beta=0.0)
-            for h in hb]
+    if nt:
+        recs = [capi.MatMulNT(c=capi.Operand(hc, 0, m * n * 4), a=capi.Operand(ha, 0, a.nbytes), b=capi.Operand(h, 0, nb),
+                              b_dtype=dtype, block_order=capi.ORDER_ROW_MAJOR, flags=0, reserved=0, m=m, n=n, k=k, lda=0, ldc=0,
+                              c_off=0, alpha=1.0, beta=0.0) for h in hb]
+        call = lib.aion_cuda_matmul_nt
+    else:
+        recs = [capi.MatMul(c=capi.Operand(hc, 0, m * n * 4), a=capi.Operand(ha, 0, a.nbytes), b=capi.Operand(h, 0, nb),
+                            b_dtype=dtype, flags=capi.MATMUL_AUTO, m=m, n=n, k=k, lda=0, ldb=0, ldc=0, alpha=1.0, beta=0.0)
+                for h in hb]
+        call = lib.aion_cuda_matmul
     for i in range(3):
-        _chk(lib.aion_cuda_matmul(dev, C.byref(recs[i % copies])))
+        _chk(call(dev, C.byref(recs[i % copies])))
     backend.sync()
     stream, ev0, ev1 = _events(torch, backend, local_rank)
     ev0.record(stream)
     for i in range(iters):
-        _chk(lib.aion_cuda_matmul(dev, C.byref(recs[i % copies])))
+        _chk(call(dev, C.byref(recs[i % copies])))
     ev1.record(stream)
     backend.sync()
     torch.cuda.synchronize()
@@ -180,9 +188,10 @@ def gemm_leg(torch, backend: CudaBackend, local_rank: int, dtype: int, m: int, n
     tf = 2.0 * m * n * k / (ms * 1e-3) / 1e12
     for h in hb + [ha, hc]:
         mem.free(h)
-    return {"dtype": "q4_0" if dtype == capi.DTYPE_Q4_0 else "q8_0", "m": m, "n": n, "k": k, "ms": round(ms, 4),
-            "tflops": round(tf, 1), "frac_of_measured_bf16_peak": round(tf / peak_tflops, 4),
-            "includes": "f32->bf16 activation pre-pass + GEMM kernel per call"}
+    return {"dtype": "q4_0" if dtype == capi.DTYPE_Q4_0 else "q8_0", "step": "MatMulNT [n,k]" if nt else "MatMul [k/32][n]",
+            "m": m, "n": n, "k": k, "ms": round(ms, 4), "tflops": round(tf, 1),
+            "frac_of_measured_bf16_peak": round(tf / peak_tflops, 4),
+            "includes": ("block permutation to K-major + " if nt else "") + "f32->bf16 activation pre-pass + GEMM kernel per call"}
 
 
 def attention_leg(torch, backend: CudaBackend, local_rank: int, batch: int, t_ctx: int, iters: int = 20,

@@ -569,6 +569,31 @@ __global__ void nt_to_kmajor_kernel(const uint8_t* __restrict__ src, uint8_t* __
   }
 }
 
+// The same permutation for the row-major order, through a shared-memory tile so that both the
+// reads (16 blocks of a row are 544 contiguous bytes) and the writes (64 blocks of a block row
+// are 2176 contiguous bytes) are coalesced. Tile = 64 rows x 16 blocks, moved as 2-byte units.
+constexpr int RT_ROWS = 64, RT_KB = 16, RT_UNITS = Q8_BYTES / 2, RT_PITCH = RT_KB * RT_UNITS + 1;
+__global__ void __launch_bounds__(256) nt_rowmajor_to_kmajor_kernel(const uint16_t* __restrict__ src, uint16_t* __restrict__ dst,
+                                                                    uint64_t n, uint64_t kblocks) {
+  ptx::pdl_launch_dependents();
+  ptx::pdl_wait();
+  __shared__ uint16_t tile[RT_ROWS * RT_PITCH];
+  const uint64_t r0 = (uint64_t)blockIdx.x * RT_ROWS, kb0 = (uint64_t)blockIdx.y * RT_KB;
+  const uint32_t rows = (uint32_t)min((uint64_t)RT_ROWS, n - r0), kbs = (uint32_t)min((uint64_t)RT_KB, kblocks - kb0);
+  const uint32_t row_units = kbs * RT_UNITS;
+  for (uint32_t i = threadIdx.x; i < rows * row_units; i += 256) {
+    const uint32_t r = i / row_units, u = i - r * row_units;
+    tile[r * RT_PITCH + u] = src[((r0 + r) * kblocks + kb0) * RT_UNITS + u];
+  }
+  __syncthreads();
+  const uint32_t col_units = rows * RT_UNITS;
+  for (uint32_t i = threadIdx.x; i < kbs * col_units; i += 256) {
+    const uint32_t kb = i / col_units, u = i - kb * col_units;
+    const uint32_t r = u / RT_UNITS, w = u - r * RT_UNITS;
+    dst[((kb0 + kb) * n + r0) * RT_UNITS + u] = tile[r * RT_PITCH + kb * RT_UNITS + w];
+  }
+}
+
 template <int DT, int MH>
 int32_t launch_gemm(AionCudaDevice* dev, const MatMulArgs& g, const __nv_bfloat16* a_bf16, uint32_t splits, float* partial) {
   using G = GemmGeom<DT, MH>;
@@ -657,9 +682,15 @@ int32_t gemm_tcgen05(AionCudaDevice* dev, const MatMulArgs& g_in, bool forced) {
   if (int32_t st = dev->reserve_scratch(relaid_bytes + a_bytes + part_bytes)) return st;
   uint8_t* scratch = static_cast<uint8_t*>(dev->lane_scratch());
   if (g.nt) {
-    const uint64_t total = g.n * (g.k / QK);
-    const unsigned blocks = (unsigned)std::min<uint64_t>(ceil_div(total, (uint64_t)256), (uint64_t)dev->sm_count * 16);
-    AION_CUDA_TRY(launch_pdl(nt_to_kmajor_kernel, dim3(blocks), dim3(256), 0, dev->stream, g.b, scratch, g.n, g.k / QK, nt_group, nt_chunk));
+    const uint64_t kblocks = g.k / QK, total = g.n * kblocks;
+    if (g.order == AION_CUDA_ORDER_ROW_MAJOR && ceil_div(kblocks, (uint64_t)RT_KB) <= 65535) {
+      const dim3 grid((unsigned)ceil_div(g.n, (uint64_t)RT_ROWS), (unsigned)ceil_div(kblocks, (uint64_t)RT_KB));
+      AION_CUDA_TRY(launch_pdl(nt_rowmajor_to_kmajor_kernel, grid, dim3(256), 0, dev->stream, reinterpret_cast<const uint16_t*>(g.b),
+                               reinterpret_cast<uint16_t*>(scratch), g.n, kblocks));
+    } else {
+      const unsigned blocks = (unsigned)std::min<uint64_t>(ceil_div(total, (uint64_t)256), (uint64_t)dev->sm_count * 16);
+      AION_CUDA_TRY(launch_pdl(nt_to_kmajor_kernel, dim3(blocks), dim3(256), 0, dev->stream, g.b, scratch, g.n, kblocks, nt_group, nt_chunk));
+    }
     g.b = scratch;
     g.nt = false;
   }

@@ -338,6 +338,8 @@ def run_other(args):
             for dt in (capi.DTYPE_Q4_0, capi.DTYPE_Q8_0):
                 for m in (512, 2048):
                     rows.append(benchmarks.gemm_leg(torch, backend, local_rank, dt, m, 8192, 2048))
+            for m in (512, 2048):
+                rows.append(benchmarks.gemm_leg(torch, backend, local_rank, capi.DTYPE_Q8_0, m, 8192, 2048, nt=True))
             for r in rows:
                 print(json.dumps(r), flush=True)
             out = {"metric": "matmul sweep", "rows": len(rows)}

@@ -124,3 +124,12 @@ def test_gemm_nt_q8_prefill(backend, order, m, n, k):
     want_deq = oracle.matmul_deqf32(oracle.Q8_0, a, kmajor, m, n, k).reshape(m, n)
     assert rel_l2(got, want_i8) <= TOL_INT8A
     assert rel_l2(got, want_deq) <= TOL_DEQ
+
+
+@pytest.mark.parametrize("m,n,k", [(33, 8, 32), (129, 16, 64), (256, 256, 32)])
+def test_gemm_smallest_and_ragged_shapes(backend, m, n, k):
+    # the smallest m the GEMM is routed, a single K block, n far below a tile
+    a, b = make(capi.DTYPE_Q8_0, m, n, k, seed=41)
+    got = run_matmul(backend, capi.DTYPE_Q8_0, a, b, m, n, k)
+    want = oracle.matmul_deqf32(capi.DTYPE_Q8_0, a, b, m, n, k).reshape(m, n)
+    assert rel_l2(got, want) <= TOL_DEQ

@@ -229,3 +229,44 @@ def test_gate_on_strided_halves(sess):
     to = store.add(TensorMeta(F32, (R, F)))
     s.execute([StepElemwiseBinary(op="gate", out=to, a=ta, b=tb)])
     assert np.array_equal(store.read(to), oracle.elemwise(2, gu[:, :F], gu[:, F:]))
+
+
+# ---- edge cases ----------------------------------------------------------------------------
+def test_empty_steps_are_no_ops(sess, backend):
+    s, store = sess
+    z = store.add(TensorMeta(F32, (0, 64)))
+    g = put(store, np.ones(64, np.float32), F32)
+    b = put(store, np.zeros(64, np.float32), F32)
+    zi = store.add(TensorMeta(I32, (0,)))
+    zo = store.add(TensorMeta(I32, (0,)))
+    zl = store.add(TensorMeta(F32, (0, 7)))
+    s.execute([StepRMSNorm(out=z, x=z, gamma=g, beta=b, eps=1e-6), StepElemwiseBinary(op="add", out=z, a=z, b=z),
+               StepArgMax(out=zo, a=zl)])
+    backend.sync()
+    assert store.read(z).shape == (0, 64) and zi is not None
+
+
+def test_argmax_single_column_and_rope_without_rotation(sess):
+    s, store = sess
+    x = np.array([[3.0], [np.nan], [-np.inf]], np.float32)
+    ta, to = put(store, x, F32), store.add(TensorMeta(I32, (3,)))
+    s.execute([StepArgMax(out=to, a=ta)])
+    assert store.read(to).tolist() == [0, 0, 0]
+    q = np.random.default_rng(1).standard_normal((1, 2, 3, 32)).astype(np.float32)
+    pos = np.array([[9, 1000]], np.int32)
+    tq, tp = put(store, q, F32), put(store, pos, I32)
+    tr = store.add(TensorMeta(F32, q.shape))
+    s.execute([StepRoPE1D(out=tr, x=tq, positions=tp, base_frequency=10000.0, rope_proportion=0.0)])
+    assert np.array_equal(store.read(tr), q)  # no pair rotates: a copy
+
+
+def test_rms_norm_non_finite_row_is_reported(sess, backend):
+    s, store = sess
+    x = np.ones((2, 64), np.float32)
+    x[1, 3] = np.inf
+    tx = put(store, x, F32)
+    g, b = put(store, np.ones(64, np.float32), F32), put(store, np.zeros(64, np.float32), F32)
+    to = store.add(TensorMeta(F32, (2, 64)))
+    s.execute([StepRMSNorm(out=to, x=tx, gamma=g, beta=b, eps=1e-6)])
+    with pytest.raises(BackendError):   # the reference rejects a non-finite mean square (layernorm.zig:131-133)
+        backend.sync()

@@ -308,8 +308,6 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_
   const uint32_t bar_full = smem_base + G::OFF_BARS;
   const uint32_t bar_empty = bar_full + NS * 8;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + G::OFF_BARS + 2 * NS * 8);
-  const uint32_t bar_act = smem_base + G::OFF_BARS + 64;  // the activation image has landed (PREQ)
-  static_assert(2 * NS * 8 + 4 <= 64, "barrier block layout");
   const uint32_t kb_pad = p.stages_per_tile * KBT;  // K blocks rounded up to whole stages
   uint8_t* act_q = smem + G::OFF_ACT;
   constexpr uint32_t QUADS = M1 ? 1 : 4 * MT;  // scale quads per K block
@@ -325,7 +323,6 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_
         ptx::mbar_init(bar_full + 8 * s, 1);
         ptx::mbar_init(bar_empty + 8 * s, CONSUMER_WARPS);
       }
-      if (PREQ) ptx::mbar_init(bar_act, 1);
       *abort_flag = 0;
       ptx::fence_barrier_init();
     }
@@ -333,9 +330,29 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_
     const uint64_t n_units = u_end - u_begin;
     uint64_t issued = 0;
     uint32_t tile = (uint32_t)(u_begin / Sg), s = (uint32_t)(u_begin - (uint64_t)tile * Sg);
+    // PREQ: every stage also brings its 8 K blocks of the pre-quantized activation image (codes,
+    // then scale quads) into the stage's slot of the activation ring. The image comes from the
+    // previous kernel, so those copies wait for it; the weight copies of the first NS stages
+    // do not, and start at once.
+    constexpr uint32_t AQ_SLICE = KBT * (M1 ? 2 : 8 * MT) * 32, AS_SLICE = KBT * (M1 ? 16 : MT * 64);
+    const uint8_t* image = PREQ ? p.act_image + (size_t)(RG ? blockIdx.y : 0) * p.act_image_bytes : nullptr;
+    auto issue_acts = [&](uint32_t slot_, uint32_t s_) {
+      const uint32_t dst = smem_base + G::OFF_ACT + slot_ * (AQ_SLICE + AS_SLICE), full = bar_full + 8 * slot_;
+      ptx::bulk_g2s(dst, image + (size_t)s_ * AQ_SLICE, AQ_SLICE, full);
+      ptx::bulk_g2s(dst + AQ_SLICE, image + (size_t)kb_pad * (AQ_SLICE / KBT) + (size_t)s_ * AS_SLICE, AS_SLICE, full);
+    };
+    uint32_t pend_s[NS];
+    uint32_t npend = 0;
+    bool acts_open = !PREQ;
     for (uint64_t it = 0; it < n_units; it++) {
       const uint32_t slot = (uint32_t)(it % NS);
       if (it == (uint64_t)NS) __syncthreads();  // CTA barrier #1 (see the consumers)
+      if (PREQ && !acts_open && it == (uint64_t)NS) {
+        ptx::pdl_wait();
+        if (lane == 0)
+          for (uint32_t i = 0; i < npend; i++) issue_acts(i, pend_s[i]);
+        acts_open = true;
+      }
       if (it >= (uint64_t)NS) {
         if (*abort_flag) break;
         if (!ptx::mbar_wait_bounded(bar_empty + 8 * slot, (uint32_t)((it / NS) - 1) & 1)) {
@@ -351,11 +368,16 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_
         const uint32_t stage = smem_base + slot * G::STAGE_BYTES;
         // Rows or columns past the tensor arrive as zeros (a zero scale), and the whole
         // box counts towards the barrier.
-        ptx::mbar_arrive_expect_tx(full, G::STAGE_BYTES);
+        ptx::mbar_arrive_expect_tx(full, G::STAGE_BYTES + (PREQ ? AQ_SLICE + AS_SLICE : 0));
         if (!NT && DT == AION_CUDA_DTYPE_Q4_0) ptx::tma_load_2d(stage, &tmap, (int32_t)(tile * (TN * G::BB / 8)), (int32_t)(s * KBT), full);
         else if (!NT) ptx::tma_load_3d(stage, &tmap, 0, (int32_t)(tile * (TN / 8)), (int32_t)(s * KBT), full);
         else ptx::tma_load_2d(stage, &tmap, (int32_t)(s * KBT * Q8_BYTES / 8), (int32_t)(tile * TN), full);
+        if (PREQ) {
+          if (acts_open) issue_acts(slot, s);
+          else pend_s[npend] = s;
+        }
       }
+      if (PREQ && !acts_open) npend++;
       __syncwarp();
       issued = it + 1;
       if (++s == Sg) {
@@ -364,6 +386,11 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_
       }
     }
     if (n_units <= (uint64_t)NS) __syncthreads();  // CTA barrier #1 when the whole range fit the ring
+    if (PREQ && !acts_open) {
+      ptx::pdl_wait();
+      if (lane == 0)
+        for (uint32_t i = 0; i < npend; i++) issue_acts(i, pend_s[i]);
+    }
     // After a failed wait nobody drains the ring: let the copies still in flight land
     // (bounded) before this CTA's shared memory can be handed to another CTA.
     if (*abort_flag)
@@ -387,17 +414,7 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_
   ptx::pdl_wait();
 
   if (PREQ) {
-    // A was quantized once for all CTAs: one bulk copy brings this group's image in.
-    if (tid == 0) {
-      ptx::mbar_arrive_expect_tx(bar_act, p.act_image_bytes);
-      ptx::bulk_g2s(smem_base + G::OFF_ACT, p.act_image + (size_t)(RG ? blockIdx.y : 0) * p.act_image_bytes, p.act_image_bytes, bar_act);
-    }
-    if (!ptx::mbar_wait_bounded(bar_act, 0)) {
-      if (lane == 0) {
-        atomicExch(p.fault, FAULT_WAIT_EXPIRED);
-        *abort_flag = 1;
-      }
-    }
+    // A was quantized once for all CTAs; its blocks arrive with the weight stages.
   } else {
     // Quantize all of A, one thread per 32-block (no cross-lane traffic, 32 independent
     // elements of instruction-level parallelism): the block's 128 bytes are one cache line.
@@ -435,7 +452,7 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_
   // lanes that stand for absent rows are finite and never stored.
   constexpr uint32_t AQ_STRIDE = MP2 * 32, AS_STRIDE = M1 ? 16 : MT * 64;
   const uint32_t act_q_addr = smem_base + G::OFF_ACT;
-  const uint32_t act_s_addr = act_q_addr + kb_pad * AQ_STRIDE;
+  const uint32_t act_s_addr = act_q_addr + (PREQ ? KBT : kb_pad) * AQ_STRIDE;  // PREQ: inside a ring slot
   uint32_t aq_lane[MT], as_lane[MT];
 #pragma unroll
   for (int t = 0; t < MT; t++) {
@@ -469,8 +486,8 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_
       uint32_t aq[MT], as[MT];
 #pragma unroll
       for (int t = 0; t < MT; t++) {
-        aq[t] = aq_lane[t] + s * (KBT * AQ_STRIDE);
-        as[t] = as_lane[t] + s * (KBT * AS_STRIDE);
+        aq[t] = aq_lane[t] + (PREQ ? slot * (KBT * (AQ_STRIDE + AS_STRIDE)) : s * (KBT * AQ_STRIDE));
+        as[t] = as_lane[t] + (PREQ ? slot * (KBT * (AQ_STRIDE + AS_STRIDE)) : s * (KBT * AS_STRIDE));
       }
       // Ties every load below to this point: they cannot move above the wait.
       asm volatile("" : "+r"(w0), "+r"(w1), "+r"(b0), "+r"(b1)::"memory");
@@ -575,7 +592,7 @@ int32_t launch(AionCudaDevice* dev, GemvParams p, const uint8_t* b, uint64_t ldb
   using G = Geom<DT, NT>;
   auto kernel = gemv_q_mma_kernel<DT, NT, MT, M1, RG, PREQ>;
   constexpr uint32_t MP2 = M1 ? 2 : 8 * MT;
-  const size_t smem = G::OFF_ACT + act_bytes(p.stages_per_tile * KBT, MP2, MT);
+  const size_t smem = G::OFF_ACT + (PREQ ? (size_t)NS * act_bytes(KBT, MP2, MT) : act_bytes(p.stages_per_tile * KBT, MP2, MT));
   // Kernel attributes and occupancy depend on the device and the dynamic size only.
   static size_t configured_smem[16] = {};
   static size_t occ_smem[16] = {};
@@ -711,6 +728,7 @@ int32_t gemv_mma(AionCudaDevice* dev, const MatMulArgs& g, bool probe_only) {
   // (src/aion/backend/cpu/exec/matmul.zig:431-434).
   uint64_t kb_max = (ACT_BUDGET_BYTES / ((size_t)mp2 * 32 + (g.m == 1 ? 16 : (g.m > 8 ? 128 : 64)))) / KBT * KBT;
   if (kb_max < KBT) kb_max = KBT;
+  if (g.m >= 2) kb_max = (kblocks + KBT - 1) / KBT * KBT;  // the activation streams with the weights: any depth in one launch
 
   for (uint64_t kb0 = 0; kb0 < kblocks; kb0 += kb_max) {
     const uint64_t nkb = kblocks - kb0 < kb_max ? kblocks - kb0 : kb_max;

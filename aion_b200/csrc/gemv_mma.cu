@@ -649,8 +649,8 @@ int32_t launch(AionCudaDevice* dev, GemvParams p, const uint8_t* b, uint64_t ldb
     const size_t image_bytes = act_bytes(kb_pad, MP2, MT);
     if (int32_t st = dev->reserve_scratch(groups * image_bytes)) return st;
     uint8_t* image = static_cast<uint8_t*>(dev->lane_scratch());
-    const uint32_t items = (uint32_t)(groups * kb_pad * MPA);
-    gemv_act_image_kernel<DT><<<(items + 127) / 128, 128, 0, dev->stream>>>(p.a, p.lda, p.m, p.kblocks, kb_pad, (uint32_t)MPA, (uint32_t)(4 * MT),
+    const uint32_t items = (uint32_t)(groups * kb_pad * MP2);
+    gemv_act_image_kernel<DT><<<(items + 127) / 128, 128, 0, dev->stream>>>(p.a, p.lda, p.m, p.kblocks, kb_pad, MP2, (uint32_t)(M1 ? 1 : 4 * MT),
                                                                           (uint32_t)groups, image, (uint32_t)image_bytes, p.a_vec4);
     AION_CUDA_TRY(cudaGetLastError());
     p.act_image = image;
@@ -698,7 +698,9 @@ int32_t launch(AionCudaDevice* dev, GemvParams p, const uint8_t* b, uint64_t ldb
 template <int DT, bool NT>
 int32_t launch_m(AionCudaDevice* dev, const GemvParams& p, const uint8_t* b, uint64_t ldb) {
   // m >= 2: A is quantized once by a small kernel instead of by every CTA.
-  if (p.m == 1) return launch<DT, NT, 1, true>(dev, p, b, ldb);
+  // (m = 1 quantizes its one row inside the kernel unless K is deep: past about 3000 the small
+  // kernel is cheaper than 148 CTAs each quantizing the whole row.)
+  if (p.m == 1) return p.kblocks > 96 ? launch<DT, NT, 1, true, false, true>(dev, p, b, ldb) : launch<DT, NT, 1, true>(dev, p, b, ldb);
   if (p.m <= 8) return launch<DT, NT, 1, false, false, true>(dev, p, b, ldb);
   if (p.m <= 16) return launch<DT, NT, 2, false, false, true>(dev, p, b, ldb);
   return launch<DT, NT, 2, false, true, true>(dev, p, b, ldb);  // groups of 16 rows
@@ -728,7 +730,7 @@ int32_t gemv_mma(AionCudaDevice* dev, const MatMulArgs& g, bool probe_only) {
   // (src/aion/backend/cpu/exec/matmul.zig:431-434).
   uint64_t kb_max = (ACT_BUDGET_BYTES / ((size_t)mp2 * 32 + (g.m == 1 ? 16 : (g.m > 8 ? 128 : 64)))) / KBT * KBT;
   if (kb_max < KBT) kb_max = KBT;
-  if (g.m >= 2) kb_max = (kblocks + KBT - 1) / KBT * KBT;  // the activation streams with the weights: any depth in one launch
+  if (g.m >= 2 || kblocks > 96) kb_max = (kblocks + KBT - 1) / KBT * KBT;  // the activation streams with the weights: any depth in one launch
 
   for (uint64_t kb0 = 0; kb0 < kblocks; kb0 += kb_max) {
     const uint64_t nkb = kblocks - kb0 < kb_max ? kblocks - kb0 : kb_max;

@@ -1,5 +1,6 @@
 // Step entry points: argument checks and routing to a kernel family.
 #include <cmath>
+#include <cstdlib>
 
 #include "common.cuh"
 
@@ -30,7 +31,12 @@ int32_t route(AionCudaDevice* dev, const MatMulArgs& g, uint32_t flags, const ch
   // reference CPU kernels' arithmetic; from AION_CUDA_GEMM_MIN_M rows on the step is a dense
   // contraction for the tensor cores (bf16 operands). Either falls back to the any-shape
   // kernel (still on the device) when the tiled kernel cannot read the operands.
-  if (g.m < AION_CUDA_GEMM_MIN_M) {
+  static const uint64_t gemm_min_m = [] {
+    const char* e = std::getenv("AION_CUDA_GEMM_MIN_M");  // tuning: where the int8 GEMV hands over to the bf16 GEMM
+    const long v = e ? std::atol(e) : 0;
+    return v > 0 ? (uint64_t)v : (uint64_t)AION_CUDA_GEMM_MIN_M;
+  }();
+  if (g.m < gemm_min_m) {
     const int32_t st = gemv_mma(dev, g, false);
     if (st != AION_CUDA_UNSUPPORTED) return st;
   } else {

@@ -12,7 +12,8 @@ program of 256 `aion_cuda_matmul` steps = one pass over the batch.
 
 Metric: GB/s of algorithmic bytes (weights once + x + y per launch) — higher is better.
   value  : inputs resident in HBM, device-timed (CUDA events on the launching stream).
-  e2e    : the same pass driven through the C ABI from HOST buffers: per step one
+  e2e    : the same pass driven through the C ABI from HOST buffers (two sessions on two host
+           threads, so one session's copies overlap the other's kernels): per step one
            aion_cuda_h2d of the batch's activations (pinned), the program, one
            aion_cuda_d2h of the results.
   N > 1  : replicas only (independent GEMVs share nothing): every rank runs the same
@@ -213,19 +214,77 @@ def run_ours(args):
     h2d_bytes = x_host.numel() * 4
     d2h_bytes = y_host.numel() * 4
 
-    def e2e_step():
-        chk(lib.aion_cuda_h2d(dev, x_dev, 0, C.c_void_p(x_host.data_ptr()), h2d_bytes))
-        chk(lib.aion_cuda_program_launch(dev, prog))
-        chk(lib.aion_cuda_d2h(dev, C.c_void_p(y_host.data_ptr()), y_dev, 0, d2h_bytes))
+    # Two sessions (two device objects, each with its own stream, activation / result buffers
+    # and recorded program over the shared weights) driven by two host threads, the way a
+    # server overlaps requests: one session's copies run under the other's kernels. Every step
+    # of either session is h2d of its inputs, the program, d2h of its results.
+    class E2ESession:
+        def __init__(self, be, xd, yd, pg, owned):
+            self.be, self.xd, self.yd, self.pg, self.owned = be, xd, yd, pg, owned
+            self.y = y_host if not owned else torch.empty_like(y_host).pin_memory()
 
-    for _ in range(3):
-        e2e_step()
+        def step(self):
+            lb, dv = self.be._lib, self.be.handle
+            chk(lb.aion_cuda_h2d(dv, self.xd, 0, C.c_void_p(x_host.data_ptr()), h2d_bytes))
+            chk(lb.aion_cuda_program_launch(dv, self.pg))
+            chk(lb.aion_cuda_d2h(dv, C.c_void_p(self.y.data_ptr()), self.yd, 0, d2h_bytes))
+
+    sessions = [E2ESession(backend, x_dev, y_dev, prog, False)]
+    if args.e2e_sessions > 1:
+        be2 = CudaBackend(local_rank)
+        x2 = be2.device_memory.alloc(COPIES * M * K * 4, 256)
+        y2 = be2.device_memory.alloc(COPIES * M * N * 4, 256)
+        recs2 = [capi.MatMul(c=capi.Operand(y2, i * M * N * 4, M * N * 4), a=capi.Operand(x2, i * M * K * 4, M * K * 4),
+                             b=capi.Operand(w_arena, i * W_BYTES, W_BYTES), b_dtype=capi.DTYPE_Q4_0, flags=capi.MATMUL_AUTO,
+                             m=M, n=N, k=K, lda=0, ldb=0, ldc=0, alpha=1.0, beta=0.0) for i in range(COPIES)]
+        chk(be2._lib.aion_cuda_h2d(be2.handle, x2, 0, C.c_void_p(x_host.data_ptr()), h2d_bytes))
+        for r2 in recs2:
+            chk(be2._lib.aion_cuda_matmul(be2.handle, C.byref(r2)))
+        be2.sync()
+        chk(be2._lib.aion_cuda_record_begin(be2.handle))
+        for i, r2 in enumerate(recs2):
+            chk(be2._lib.aion_cuda_record_lane(be2.handle, i % args.lanes))
+            chk(be2._lib.aion_cuda_matmul(be2.handle, C.byref(r2)))
+        prog2 = C.c_void_p()
+        chk(be2._lib.aion_cuda_record_end(be2.handle, C.byref(prog2)))
+        sessions.append(E2ESession(be2, x2, y2, prog2, True))
+
+    for sn in sessions:
+        for _ in range(3):
+            sn.step()
     barrier()
+    per_session = max(2, e2e_steps // len(sessions))
+    e2e_steps = per_session * len(sessions)
+    errors = []
+
+    def drive(sn):
+        try:
+            for _ in range(per_session):
+                sn.step()
+        except Exception as ex:  # surfaced after the join
+            errors.append(ex)
+
+    threads_ = [threading.Thread(target=drive, args=(sn,)) for sn in sessions[1:]]
     t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        e2e_step()
-    backend.sync()
+    for th in threads_:
+        th.start()
+    drive(sessions[0])
+    for th in threads_:
+        th.join()
+    for sn in sessions:
+        sn.be.sync()
     e2e_s = time.perf_counter() - t0
+    if errors:
+        raise errors[0]
+    if len(sessions) > 1:
+        same = bool(torch.equal(sessions[1].y, y_host))
+        sn = sessions[1]
+        sn.be._lib.aion_cuda_program_destroy(sn.be.handle, sn.pg)
+        sn.be.device_memory.free(sn.xd)
+        sn.be.device_memory.free(sn.yd)
+        sn.be.deinit()
+    else:
+        same = True
     if world > 1:
         t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -267,7 +326,9 @@ def run_ours(args):
                    "parallelism": "replicas only" if world > 1 else "single GPU",
                    "program": f"one recorded program per step; its 256 independent steps sit in {args.lanes} parallel lanes", "outputs_finite_nonzero": finite},
         "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d_bytes,
-                "d2h_bytes_per_step": d2h_bytes, "steps": e2e_steps},
+                "d2h_bytes_per_step": d2h_bytes, "steps": e2e_steps, "sessions": len(sessions),
+                "how": "host threads, one per session; a step = aion_cuda_h2d + aion_cuda_program_launch + aion_cuda_d2h",
+                "sessions_agree": same},
         "gpu_launches": args.steps * COPIES,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
                      "frac": round(achieved / peak, 4), "peak_kind": f"of {peak_kind}",
@@ -423,6 +484,8 @@ def main():
                          "their own line: decode tokens/s, prefill GEMM TFLOP/s, decode attention GB/s, the "
                          "column-split layer with its all-gather")
     ap.add_argument("--no-decode", action="store_true", help="gemv workload: leave the decoder leg out")
+    ap.add_argument("--e2e-sessions", type=int, default=2, choices=[1, 2],
+                    help="sessions (device objects + host threads) the end-to-end leg drives concurrently")
     ap.add_argument("--decode-requests", type=int, default=512, help="concurrent requests in total, split over the GPUs")
     ap.add_argument("--decode-steps", type=int, default=20)
     ap.add_argument("--decode-layers", type=int, default=30)

@@ -51,7 +51,7 @@ struct AttnParams {
   float scale, soft_cap;
   uint32_t splits;
   uint32_t head_groups;  // ceil((Hq/Hkv) / 8)
-  float* partial;        // [unit][split][8 heads][Dv + 2]
+  float* partial;        // [unit][split][8 heads][Dv + 4]: sums, max, sum of weights, pad
   int* tickets;          // [unit]
   int* fault;
 };
@@ -406,7 +406,10 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParam
     consumer_sync();
     const float* all = reinterpret_cast<const float*>(smem);
     constexpr int WS = 8 * D + 16;
-    float* part = p.partial + ((uint64_t)unit * p.splits + split) * 8 * (D + 2);
+    // A partial row is D sums, then (max, sum of weights), padded to a 16-byte multiple so
+    // that the merge reads it in float4s.
+    constexpr int PP = D + 4;
+    float* part = p.partial + ((uint64_t)unit * p.splits + split) * 8 * PP;
     float* orow = p.out + (((uint64_t)b * p.L + l) * p.Hq + h0) * D;
     const bool direct = p.splits == 1;
     for (int idx = tid; idx < 8 * D; idx += CONSUMER_WARPS * 32) {
@@ -430,11 +433,8 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParam
           if (nkeys > 0 && !kr.bad && !*abort_flag) atomicExch(p.fault, FAULT_NONFINITE);
         }
       } else {
-        part[h * (D + 2) + d] = o;
-        if (d == 0) {
-          part[h * (D + 2) + D] = M;
-          part[h * (D + 2) + D + 1] = lsum;
-        }
+        part[h * PP + d] = o;
+        if (d == 0) *reinterpret_cast<float2*>(part + h * PP + D) = make_float2(M, lsum);
       }
     }
     if (!direct) {
@@ -450,15 +450,20 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParam
       consumer_sync();
       if (*last_flag) {
         __threadfence();
-        // Merge in two passes so that no thread walks the splits with dependent loads: first
-        // every split's (max, sum) pair becomes a scale factor in shared memory (the ring is
-        // drained, its space is free), then the weighted sums run over independent loads.
-        const float* pu = p.partial + (uint64_t)unit * p.splits * 8 * (D + 2);
-        float* fac = reinterpret_cast<float*>(smem);          // [8][splits]
-        float* lsums = fac + 8 * p.splits;                    // [8]
+        // The merge is a chain of L2 round trips on one CTA, so it keeps them few: one pass
+        // fetches every split's (max, sum) pair into shared memory (the ring is drained, its
+        // space is free), the factors come from there, and the weighted sums then run over
+        // float4 loads issued sixteen at a time per thread.
+        const float* pu = p.partial + (uint64_t)unit * p.splits * 8 * PP;
+        float* fac = reinterpret_cast<float*>(smem);  // [8][splits]: max, then factor
+        float* wsum = fac + 8 * p.splits;             // [8][splits]: sum of weights
+        float* lsums = wsum + 8 * p.splits;           // [8]
         for (uint32_t idx = tid; idx < 8 * p.splits; idx += CONSUMER_WARPS * 32) {
           const uint32_t h = idx / p.splits, s2 = idx % p.splits;
-          fac[idx] = (h < nh) ? __ldcg(pu + (s2 * 8 + h) * (D + 2) + D) : -INFINITY;
+          float2 ml = make_float2(-INFINITY, 0.0f);
+          if (h < nh) ml = __ldcg(reinterpret_cast<const float2*>(pu + (size_t)(s2 * 8 + h) * PP + D));
+          fac[idx] = ml.x;
+          wsum[idx] = ml.y;
         }
         consumer_sync();
         for (uint32_t h = warp; h < 8; h += CONSUMER_WARPS) {
@@ -471,30 +476,63 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParam
             const float ms = fac[h * p.splits + s2];
             const float f = (ms == -INFINITY) ? 0.0f : exp2f(ms - M);
             fac[h * p.splits + s2] = f;
-            if (h < nh) lsum += __ldcg(pu + (s2 * 8 + h) * (D + 2) + D + 1) * f;
+            lsum += wsum[h * p.splits + s2] * f;
           }
 #pragma unroll
           for (int o = 16; o > 0; o >>= 1) lsum += __shfl_xor_sync(0xFFFFFFFFu, lsum, o);
           if (lane == 0) lsums[h] = lsum;
         }
         consumer_sync();
-        for (int idx = tid; idx < 8 * D; idx += CONSUMER_WARPS * 32) {
-          const int h = idx / D, d = idx % D;
-          if ((uint32_t)h >= nh) continue;
-          const float* col = pu + h * (D + 2) + d;
-          const float* fh = fac + h * p.splits;
-          float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
-          uint32_t s2 = 0;
-          for (; s2 + 4 <= p.splits; s2 += 4) {
-            const float v0 = __ldcg(col + (uint64_t)(s2 + 0) * 8 * (D + 2)), v1 = __ldcg(col + (uint64_t)(s2 + 1) * 8 * (D + 2));
-            const float v2 = __ldcg(col + (uint64_t)(s2 + 2) * 8 * (D + 2)), v3 = __ldcg(col + (uint64_t)(s2 + 3) * 8 * (D + 2));
-            o0 += v0 * fh[s2], o1 += v1 * fh[s2 + 1], o2 += v2 * fh[s2 + 2], o3 += v3 * fh[s2 + 3];
-          }
-          for (; s2 < p.splits; s2++) o0 += __ldcg(col + (uint64_t)s2 * 8 * (D + 2)) * fh[s2];
-          const float o = (o0 + o1) + (o2 + o3), lsum = lsums[h];
-          if (lsum > 0.0f && isfinite(lsum)) orow[idx] = o / lsum;
-          else {
-            orow[idx] = 0.0f;
+        // Thread t owns the float4 columns t, t + 128, ... of the row's [8 heads][D] outputs.
+        constexpr int C4 = (8 * D / 4) / (CONSUMER_WARPS * 32);
+        static_assert(C4 >= 1 && C4 * CONSUMER_WARPS * 32 * 4 == 8 * D, "whole float4 columns per thread");
+        const float* colp[C4];
+        const float* fh[C4];
+        bool live[C4];
+        float4 o[C4];
+#pragma unroll
+        for (int c = 0; c < C4; c++) {
+          const uint32_t idx4 = tid + c * (CONSUMER_WARPS * 32), h = idx4 / (D / 4), d4 = idx4 % (D / 4);
+          live[c] = h < nh;
+          colp[c] = pu + (size_t)h * PP + 4 * d4;
+          fh[c] = fac + h * p.splits;
+          o[c] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
+        for (uint32_t s2 = 0; s2 < p.splits; s2 += 4) {
+          float4 v[C4][4];
+          float f[C4][4];
+#pragma unroll
+          for (int c = 0; c < C4; c++)
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+              const uint32_t ss = s2 + k;
+              const bool on = live[c] && ss < p.splits;
+              v[c][k] = on ? __ldcg(reinterpret_cast<const float4*>(colp[c] + (size_t)ss * 8 * PP)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+              f[c][k] = on ? fh[c][ss] : 0.0f;
+            }
+#pragma unroll
+          for (int c = 0; c < C4; c++)
+#pragma unroll
+            for (int k = 0; k < 4; k++) {  // splits in order
+              o[c].x += v[c][k].x * f[c][k];
+              o[c].y += v[c][k].y * f[c][k];
+              o[c].z += v[c][k].z * f[c][k];
+              o[c].w += v[c][k].w * f[c][k];
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < C4; c++) {
+          if (!live[c]) continue;
+          const uint32_t idx4 = tid + c * (CONSUMER_WARPS * 32), h = idx4 / (D / 4);
+          const float lsum = lsums[h];
+          float* dst = orow + 4 * idx4;
+          if (lsum > 0.0f && isfinite(lsum)) {
+            dst[0] = o[c].x / lsum;
+            dst[1] = o[c].y / lsum;
+            dst[2] = o[c].z / lsum;
+            dst[3] = o[c].w / lsum;
+          } else {
+            dst[0] = dst[1] = dst[2] = dst[3] = 0.0f;
             if (nkeys > 0 && !kr.bad) atomicExch(p.fault, FAULT_NONFINITE);
           }
         }
@@ -697,7 +735,7 @@ int32_t attention_launch(AionCudaDevice* dev, const AionCudaAttention* s) {
     if (dev->attn_split_override) splits = dev->attn_split_override;
     p.splits = (uint32_t)splits;
     if (splits > 1) {
-      const size_t part_bytes = (size_t)units * splits * 8 * (Dk + 2) * sizeof(float);
+      const size_t part_bytes = (size_t)units * splits * 8 * (Dk + 4) * sizeof(float);
       if (int32_t st = dev->reserve_scratch(part_bytes)) return st;
       if (int32_t st = dev->reserve_tickets(units)) return st;
       p.partial = static_cast<float*>(dev->lane_scratch());

@@ -315,6 +315,114 @@ __global__ void __launch_bounds__(RMS_THREADS) rms_norm_pair_kernel(float* out1,
     out2[r * cols + c] = ((out1[r * cols + c] * inv2) * gamma2[c]) + beta2[c];
 }
 
+// ---- RMSNorm (single or pair) for rows that fit registers: one block per row ------------
+// The two kernels above walk a row element by element, several dependent cache round trips
+// per thread; on a decode step (a handful of rows) that latency is the whole cost. Here every
+// operand of the row is fetched up front as float4s (one round trip), the row stays in
+// registers between the sum of squares and the scaling, and the element arithmetic keeps
+// the reference's order ((x * inv) * gamma) + beta [+ residual].
+constexpr int RMSF_THREADS = 256;
+__device__ __forceinline__ float rmsf_block_sum(float v, float* part) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, o);
+  __syncthreads();  // `part` may still be read from the previous reduction
+  if (lane == 0) part[warp] = v;
+  __syncthreads();
+  float s = 0.0f;
+#pragma unroll
+  for (int w = 0; w < RMSF_THREADS / 32; w++) s += part[w];  // same order in every thread
+  return s;
+}
+// CH: float4 chunks per thread (cols <= CH * 4 * RMSF_THREADS); PAIR: also out2 = RMSNorm(out1).
+// out1 may alias x or residual: a thread reads its own elements before it writes them.
+template <int CH, bool PAIR>
+__global__ void __launch_bounds__(RMSF_THREADS) rms_norm_regs_kernel(float* out1, float* out2, const float* x,
+                                                                     const float* __restrict__ gamma1, const float* __restrict__ beta1,
+                                                                     const float* residual, const float* __restrict__ gamma2,
+                                                                     const float* __restrict__ beta2, uint32_t cols, float eps1, float eps2,
+                                                                     int* fault) {
+  ptx::pdl_launch_dependents();
+  __shared__ float part[RMSF_THREADS / 32];
+  const uint32_t n4 = cols / 4;
+  const uint64_t row4 = (uint64_t)blockIdx.x * n4;
+  const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  float4 g1[CH], b1[CH], g2[CH], b2[CH], xv[CH], rs[CH];
+  ptx::pdl_wait();
+#pragma unroll
+  for (int c = 0; c < CH; c++) {
+    const uint32_t i = threadIdx.x + c * RMSF_THREADS;
+    const bool on = i < n4;
+    g1[c] = on ? reinterpret_cast<const float4*>(gamma1)[i] : zero;
+    b1[c] = on ? reinterpret_cast<const float4*>(beta1)[i] : zero;
+    if (PAIR) {
+      g2[c] = on ? reinterpret_cast<const float4*>(gamma2)[i] : zero;
+      b2[c] = on ? reinterpret_cast<const float4*>(beta2)[i] : zero;
+    }
+    xv[c] = on ? reinterpret_cast<const float4*>(x)[row4 + i] : zero;
+    rs[c] = (on && residual) ? reinterpret_cast<const float4*>(residual)[row4 + i] : zero;
+  }
+  float sq = 0.0f;
+#pragma unroll
+  for (int c = 0; c < CH; c++) sq += ((xv[c].x * xv[c].x + xv[c].y * xv[c].y) + xv[c].z * xv[c].z) + xv[c].w * xv[c].w;
+  const float d1 = rmsf_block_sum(sq, part) * (1.0f / (float)cols) + eps1;
+  if (!(d1 > 0.0f) || !isfinite(d1)) {
+    if (threadIdx.x == 0) atomicCAS(fault, FAULT_NONE, FAULT_INVALID_ARGUMENT);
+    return;
+  }
+  const float inv1 = 1.0f / sqrtf(d1);
+  sq = 0.0f;
+#pragma unroll
+  for (int c = 0; c < CH; c++) {
+    const uint32_t i = threadIdx.x + c * RMSF_THREADS;
+    float4 v;
+    v.x = ((xv[c].x * inv1) * g1[c].x) + b1[c].x;
+    v.y = ((xv[c].y * inv1) * g1[c].y) + b1[c].y;
+    v.z = ((xv[c].z * inv1) * g1[c].z) + b1[c].z;
+    v.w = ((xv[c].w * inv1) * g1[c].w) + b1[c].w;
+    if (residual) v.x = v.x + rs[c].x, v.y = v.y + rs[c].y, v.z = v.z + rs[c].z, v.w = v.w + rs[c].w;
+    if (i < n4) reinterpret_cast<float4*>(out1)[row4 + i] = v;
+    else v = zero;
+    xv[c] = v;
+    sq += ((v.x * v.x + v.y * v.y) + v.z * v.z) + v.w * v.w;
+  }
+  if (!PAIR) return;
+  const float d2 = rmsf_block_sum(sq, part) * (1.0f / (float)cols) + eps2;
+  if (!(d2 > 0.0f) || !isfinite(d2)) {
+    if (threadIdx.x == 0) atomicCAS(fault, FAULT_NONE, FAULT_INVALID_ARGUMENT);
+    return;
+  }
+  const float inv2 = 1.0f / sqrtf(d2);
+#pragma unroll
+  for (int c = 0; c < CH; c++) {
+    const uint32_t i = threadIdx.x + c * RMSF_THREADS;
+    float4 v;
+    v.x = ((xv[c].x * inv2) * g2[c].x) + b2[c].x;
+    v.y = ((xv[c].y * inv2) * g2[c].y) + b2[c].y;
+    v.z = ((xv[c].z * inv2) * g2[c].z) + b2[c].z;
+    v.w = ((xv[c].w * inv2) * g2[c].w) + b2[c].w;
+    if (i < n4) reinterpret_cast<float4*>(out2)[row4 + i] = v;
+  }
+}
+
+// Launches the register-resident kernel when the row fits and everything is float4-readable.
+// Returns false when the caller should use the element-wise kernel instead.
+template <bool PAIR>
+bool launch_rms_regs(AionCudaDevice* dev, cudaError_t* err, unsigned rows, float* out1, float* out2, const float* x, const float* g1,
+                     const float* b1, const float* res, const float* g2, const float* b2, uint64_t cols, float eps1, float eps2) {
+  const uintptr_t bits = reinterpret_cast<uintptr_t>(out1) | reinterpret_cast<uintptr_t>(out2) | reinterpret_cast<uintptr_t>(x) |
+                         reinterpret_cast<uintptr_t>(g1) | reinterpret_cast<uintptr_t>(b1) | reinterpret_cast<uintptr_t>(res) |
+                         reinterpret_cast<uintptr_t>(g2) | reinterpret_cast<uintptr_t>(b2);
+  if ((bits & 15) != 0 || cols % 4 != 0 || cols > 4ull * 4 * RMSF_THREADS) return false;
+  const uint32_t c32 = (uint32_t)cols;
+  if (cols <= 2ull * 4 * RMSF_THREADS)
+    *err = launch_pdl(rms_norm_regs_kernel<2, PAIR>, dim3(rows), dim3(RMSF_THREADS), 0, dev->stream, out1, out2, x, g1, b1, res, g2, b2, c32,
+                      eps1, eps2, dev->fault_dev);
+  else
+    *err = launch_pdl(rms_norm_regs_kernel<4, PAIR>, dim3(rows), dim3(RMSF_THREADS), 0, dev->stream, out1, out2, x, g1, b1, res, g2, b2, c32,
+                      eps1, eps2, dev->fault_dev);
+  return true;
+}
+
 // ---- RoPE(q), RoPE(k), f16 cast of k and v, append to both caches: one block per (b, l) ----
 __global__ void rope_kv_append_kernel(float* __restrict__ q_out, const float* __restrict__ qkv, const int32_t* __restrict__ pos,
                                       const int32_t* __restrict__ end_index, __half* __restrict__ k_cache,
@@ -338,9 +446,25 @@ __global__ void rope_kv_append_kernel(float* __restrict__ q_out, const float* __
   __half* vd = v_cache + (b * t_cap + dst_t) * (uint64_t)h_kv * d;
   const uint32_t pairs_total = d / 2;
   const float p = (float)pos[row];
+  // Loads first, eight heads at a time, so that they are all in flight while the angle is
+  // computed: on a decode step this kernel is a chain of cache round trips and nothing else.
+  constexpr uint32_t HC = 8;
   for (uint32_t i = threadIdx.x; i < pairs_total; i += blockDim.x) {
-    float sn = 0.0f, cs = 1.0f;
     const bool rot = i < rope_pairs;
+    float xl[HC], xr[HC], kl[HC], kr[HC];
+#pragma unroll
+    for (uint32_t u = 0; u < HC; u++) {
+      const bool on = u < h_q;
+      xl[u] = on ? src[u * d + i] : 0.0f;
+      xr[u] = on ? src[u * d + pairs_total + i] : 0.0f;
+    }
+#pragma unroll
+    for (uint32_t u = 0; u < HC; u++) {
+      const bool on = !bad && u < h_kv;
+      kl[u] = on ? ksrc[u * d + i] : 0.0f;
+      kr[u] = on ? ksrc[u * d + pairs_total + i] : 0.0f;
+    }
+    float sn = 0.0f, cs = 1.0f;
     if (rot) {
       float f = scale_factor;
       for (uint32_t j = 0; j < i; j++) f *= step;
@@ -349,16 +473,40 @@ __global__ void rope_kv_append_kernel(float* __restrict__ q_out, const float* __
       sincos((double)ang, &sd, &cd);
       sn = (float)sd, cs = (float)cd;
     }
-    for (uint32_t h = 0; h < h_q; h++) {
-      const float xl = src[h * d + i], xr = src[h * d + pairs_total + i];
-      qo[h * d + i] = rot ? xl * cs - xr * sn : xl;
-      qo[h * d + pairs_total + i] = rot ? xl * sn + xr * cs : xr;
+    for (uint32_t h0q = 0; h0q < h_q; h0q += HC) {
+      if (h0q > 0) {
+#pragma unroll
+        for (uint32_t u = 0; u < HC; u++) {
+          const bool on = h0q + u < h_q;
+          xl[u] = on ? src[(h0q + u) * d + i] : 0.0f;
+          xr[u] = on ? src[(h0q + u) * d + pairs_total + i] : 0.0f;
+        }
+      }
+#pragma unroll
+      for (uint32_t u = 0; u < HC; u++) {
+        const uint32_t h = h0q + u;
+        if (h >= h_q) break;
+        qo[h * d + i] = rot ? xl[u] * cs - xr[u] * sn : xl[u];
+        qo[h * d + pairs_total + i] = rot ? xl[u] * sn + xr[u] * cs : xr[u];
+      }
     }
     if (!bad)
-      for (uint32_t h = 0; h < h_kv; h++) {
-        const float xl = ksrc[h * d + i], xr = ksrc[h * d + pairs_total + i];
-        kd[h * d + i] = __float2half_rn(rot ? xl * cs - xr * sn : xl);
-        kd[h * d + pairs_total + i] = __float2half_rn(rot ? xl * sn + xr * cs : xr);
+      for (uint32_t h0k = 0; h0k < h_kv; h0k += HC) {
+        if (h0k > 0) {
+#pragma unroll
+          for (uint32_t u = 0; u < HC; u++) {
+            const bool on = h0k + u < h_kv;
+            kl[u] = on ? ksrc[(h0k + u) * d + i] : 0.0f;
+            kr[u] = on ? ksrc[(h0k + u) * d + pairs_total + i] : 0.0f;
+          }
+        }
+#pragma unroll
+        for (uint32_t u = 0; u < HC; u++) {
+          const uint32_t h = h0k + u;
+          if (h >= h_kv) break;
+          kd[h * d + i] = __float2half_rn(rot ? kl[u] * cs - kr[u] * sn : kl[u]);
+          kd[h * d + pairs_total + i] = __float2half_rn(rot ? kl[u] * sn + kr[u] * cs : kr[u]);
+        }
       }
   }
   if (!bad)
@@ -393,6 +541,11 @@ int32_t aion_cuda_rms_norm(AionCudaDevice* dev, const AionCudaRMSNorm* s) {
   if (s->residual.handle)
     if (int32_t st = resolve(s->residual, bytes, "rms_norm.residual", &res)) return st;
   if (s->rows > 0x7FFFFFFFull) return fail(AION_CUDA_UNSUPPORTED, "rms_norm: too many rows for one launch");
+  cudaError_t err = cudaSuccess;
+  if (launch_rms_regs<false>(dev, &err, (unsigned)s->rows, out, nullptr, x, gamma, beta, res, nullptr, nullptr, s->cols, s->eps, s->eps)) {
+    AION_CUDA_TRY(err);
+    return AION_CUDA_OK;
+  }
   AION_CUDA_TRY(launch_pdl(rms_norm_kernel, dim3((unsigned)s->rows), dim3(RMS_THREADS), 0, dev->stream, out, x, gamma, beta, res, s->cols, s->eps,
                            dev->fault_dev));
   return AION_CUDA_OK;
@@ -565,6 +718,11 @@ int32_t aion_cuda_rms_norm_pair(AionCudaDevice* dev, const AionCudaRMSNormPair* 
   if (int32_t st = resolve(s->beta2, vec, "rms_norm_pair.beta2", &b2)) return st;
   if (s->residual.handle)
     if (int32_t st = resolve(s->residual, bytes, "rms_norm_pair.residual", &res)) return st;
+  cudaError_t err = cudaSuccess;
+  if (launch_rms_regs<true>(dev, &err, (unsigned)s->rows, out1, out2, x, g1, b1, res, g2, b2, s->cols, s->eps1, s->eps2)) {
+    AION_CUDA_TRY(err);
+    return AION_CUDA_OK;
+  }
   AION_CUDA_TRY(launch_pdl(rms_norm_pair_kernel, dim3((unsigned)s->rows), dim3(RMS_THREADS), 0, dev->stream, out1, out2, x, g1, b1, res, g2,
                            b2, s->cols, s->eps1, s->eps2, dev->fault_dev));
   return AION_CUDA_OK;

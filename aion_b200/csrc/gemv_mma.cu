@@ -256,6 +256,11 @@ template <int DT>
 __global__ void gemv_act_image_kernel(const float* __restrict__ a, uint64_t lda, uint32_t m, uint32_t kblocks, uint32_t kb_pad,
                                       uint32_t mpa, uint32_t quads, uint32_t groups, uint8_t* __restrict__ image,
                                       uint32_t group_bytes, uint32_t a_vec4) {
+  // The GEMV that follows may start now: its weight stream does not depend on this kernel,
+  // and it waits for this kernel to finish before it copies the image. A comes from the
+  // previous kernel, and the image buffer may still be read by an earlier GEMV until then.
+  ptx::pdl_launch_dependents();
+  ptx::pdl_wait();
   const uint32_t items = groups * kb_pad * mpa;
   const uint32_t item = blockIdx.x * blockDim.x + threadIdx.x;
   if (item >= items) return;
@@ -650,9 +655,18 @@ int32_t launch(AionCudaDevice* dev, GemvParams p, const uint8_t* b, uint64_t ldb
     if (int32_t st = dev->reserve_scratch(groups * image_bytes)) return st;
     uint8_t* image = static_cast<uint8_t*>(dev->lane_scratch());
     const uint32_t items = (uint32_t)(groups * kb_pad * MP2);
-    gemv_act_image_kernel<DT><<<(items + 127) / 128, 128, 0, dev->stream>>>(p.a, p.lda, p.m, p.kblocks, kb_pad, MP2, (uint32_t)(M1 ? 1 : 4 * MT),
-                                                                          (uint32_t)groups, image, (uint32_t)image_bytes, p.a_vec4);
-    AION_CUDA_TRY(cudaGetLastError());
+    cudaLaunchConfig_t icfg{};
+    icfg.gridDim = dim3((items + 127) / 128);
+    icfg.blockDim = dim3(128);
+    icfg.stream = dev->stream;
+    cudaLaunchAttribute iattrs[1];
+    iattrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    iattrs[0].val.programmaticStreamSerializationAllowed = 1;
+    icfg.attrs = iattrs;
+    static const bool no_pdl_image = std::getenv("AION_CUDA_NO_PDL_MAIN") != nullptr;  // tuning only
+    icfg.numAttrs = no_pdl_image ? 0 : 1;
+    AION_CUDA_TRY(cudaLaunchKernelEx(&icfg, gemv_act_image_kernel<DT>, p.a, p.lda, p.m, p.kblocks, kb_pad, (uint32_t)MP2, (uint32_t)(M1 ? 1 : 4 * MT),
+                                     (uint32_t)groups, image, (uint32_t)image_bytes, p.a_vec4));
     p.act_image = image;
     p.act_image_bytes = (uint32_t)image_bytes;
   }

@@ -315,8 +315,12 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParam
           __syncwarp();
         }
         // ---- S^T[16 keys x 8 heads] = K . Q^T ----
+        // Four accumulators (even / odd k-steps, high / low half of an f32 q) keep the chain of
+        // dependent MMAs a quarter as long; a CTA works on one tile at a time, so nothing else
+        // would hide that latency.
         float s[4] = {0, 0, 0, 0};
         {
+          float sa[4] = {0, 0, 0, 0}, sb[4] = {0, 0, 0, 0}, sc[4] = {0, 0, 0, 0}, sd[4] = {0, 0, 0, 0};
           const uint32_t a_row = r0 + (lane & 7) + 8 * ((lane >> 3) & 1);
           const uint32_t a_chunk = lane >> 4;
           const uint2* qhi = reinterpret_cast<const uint2*>(smem + G::OFF_QHI);
@@ -326,12 +330,14 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParam
             uint32_t a0, a1, a2, a3;
             ldmatrix_x4(kst + tile_off<D, TILED>(a_row, 2 * ks + a_chunk), a0, a1, a2, a3);
             const uint2 bh = qhi[ks * 32 + lane];
-            mma_f16(s, a0, a1, a2, a3, bh.x, bh.y);
+            mma_f16((ks & 1) ? sb : sa, a0, a1, a2, a3, bh.x, bh.y);
             if (QF32) {
               const uint2 bl2 = qlo[ks * 32 + lane];
-              mma_f16(s, a0, a1, a2, a3, bl2.x, bl2.y);
+              mma_f16((ks & 1) ? sd : sc, a0, a1, a2, a3, bl2.x, bl2.y);
             }
           }
+#pragma unroll
+          for (int e = 0; e < 4; e++) s[e] = (sa[e] + sb[e]) + (sc[e] + sd[e]);
         }
         // s[0], s[1]: key g, heads 2j, 2j+1;  s[2], s[3]: key g+8.
         const bool in0 = (uint32_t)g < valid, in1 = (uint32_t)(g + 8) < valid;

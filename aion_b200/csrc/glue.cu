@@ -240,7 +240,18 @@ __global__ void argmax_kernel(int32_t* __restrict__ out, const float* __restrict
   const uint64_t lo = blockIdx.x * chunk_len, hi = min(n, lo + chunk_len);
   float bv = -INFINITY;
   int bi = 0x7FFFFFFF;
-  for (uint64_t j = lo + threadIdx.x; j < hi; j += blockDim.x) argmax_take(bv, bi, row[j], (int)j);
+  // Eight independent loads per thread are in flight before the first comparison; the
+  // candidates are still taken in index order.
+  uint64_t j = lo + threadIdx.x;
+  const uint64_t bd = blockDim.x;
+  for (; j + 7 * bd < hi; j += 8 * bd) {
+    float v[8];
+#pragma unroll
+    for (int u = 0; u < 8; u++) v[u] = row[j + u * bd];
+#pragma unroll
+    for (int u = 0; u < 8; u++) argmax_take(bv, bi, v[u], (int)(j + u * bd));
+  }
+  for (; j < hi; j += bd) argmax_take(bv, bi, row[j], (int)j);
   argmax_block_reduce(bv, bi);
   __shared__ int last;
   if (threadIdx.x == 0) {

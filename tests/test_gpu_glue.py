@@ -28,7 +28,10 @@ def put(store, arr, dtype):
     return store.add(TensorMeta(dtype, tuple(arr.shape)), arr)
 
 
-@pytest.mark.parametrize("rows,cols", [(1, 1536), (7, 256), (64, 1536), (3, 100), (520, 32)])
+# Rows of up to 4096 columns (a multiple of 4) take the register-resident kernel, two or four
+# float4 chunks per thread; wider or ragged rows the element-wise one.
+@pytest.mark.parametrize("rows,cols", [(1, 1536), (7, 256), (64, 1536), (3, 100), (520, 32), (5, 4096), (3, 3000), (2, 8200),
+                                       (3, 1023)])
 @pytest.mark.parametrize("with_res", [False, True])
 def test_rms_norm(sess, rows, cols, with_res):
     s, store = sess
@@ -180,6 +183,25 @@ def test_rms_norm_pair_equals_two_norms(sess, with_res):
     want1 = oracle.rms_norm(x, g1, b1, 1e-6, residual=res)
     want2 = oracle.rms_norm(want1, g2, b2, 1e-5)
     np.testing.assert_allclose(store.read(o1), want1, rtol=1e-5, atol=1e-6)
+    np.testing.assert_allclose(store.read(o2), want2, rtol=2e-5, atol=2e-6)
+
+
+@pytest.mark.parametrize("cols", [1536, 4096, 4100])
+def test_rms_norm_pair_in_place_on_the_residual(sess, cols):
+    """The decoder's use: x = x + RMSNorm(o), x_norm = RMSNorm(x), with out1 and residual the same tensor."""
+    s, store = sess
+    rng = np.random.default_rng(cols)
+    rows = 6
+    o = rng.standard_normal((rows, cols)).astype(np.float32)
+    x = rng.standard_normal((rows, cols)).astype(np.float32)
+    g1, b1, g2, b2 = (rng.standard_normal(cols).astype(np.float32) for _ in range(4))
+    t = {k: put(store, v, F32) for k, v in dict(o=o, x=x, g1=g1, b1=b1, g2=g2, b2=b2).items()}
+    o2 = store.add(TensorMeta(F32, (rows, cols)))
+    s.execute([StepRMSNormPair(out1=t["x"], out2=o2, x=t["o"], gamma1=t["g1"], beta1=t["b1"], gamma2=t["g2"], beta2=t["b2"],
+                               eps1=1e-6, eps2=1e-6, residual=t["x"])])
+    want1 = oracle.rms_norm(o, g1, b1, 1e-6, residual=x)
+    want2 = oracle.rms_norm(want1, g2, b2, 1e-6)
+    np.testing.assert_allclose(store.read(t["x"]), want1, rtol=1e-5, atol=1e-6)
     np.testing.assert_allclose(store.read(o2), want2, rtol=2e-5, atol=2e-6)
 
 

@@ -104,6 +104,34 @@ __global__ void elemwise_kernel(float* out, const float* a, const float* b, uint
   }
 }
 
+// The same over float4s (rows and row strides are multiples of 4 elements, pointers 16-byte
+// aligned): a quarter of the index arithmetic and of the load / store instructions per element;
+// each element goes through exactly the arithmetic above.
+__device__ __forceinline__ float elemwise_one(float av, float bv, uint32_t op) {
+  if (op == AION_CUDA_ELEMWISE_ADD) return av + bv;
+  if (op == AION_CUDA_ELEMWISE_MUL) return av * bv;
+  return gelu_approx(av) * bv;
+}
+__global__ void elemwise4_kernel(float4* out, const float4* a, const float4* b, uint64_t n4, uint32_t op, uint64_t cols4, uint64_t ld_out4,
+                                 uint64_t ld_a4, uint64_t ld_b4) {
+  ptx::pdl_launch_dependents();
+  ptx::pdl_wait();
+  for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < n4; i += (uint64_t)gridDim.x * blockDim.x) {
+    uint64_t io = i, ia = i, ib = i;
+    if (cols4) {
+      const uint64_t r = i / cols4, c = i - r * cols4;
+      io = r * ld_out4 + c, ia = r * ld_a4 + c, ib = r * ld_b4 + c;
+    }
+    const float4 av = a[ia], bv = b[ib];
+    float4 v;
+    v.x = elemwise_one(av.x, bv.x, op);
+    v.y = elemwise_one(av.y, bv.y, op);
+    v.z = elemwise_one(av.z, bv.z, op);
+    v.w = elemwise_one(av.w, bv.w, op);
+    out[io] = v;
+  }
+}
+
 // ---- RoPE: one thread per (b, l, pair); the rotation is reused by every head ----------
 __global__ void rope_kernel(float* out, const float* x, const int32_t* __restrict__ pos, uint64_t bl,
                             uint32_t heads, uint32_t d, uint32_t rope_pairs, float step, float scale_factor) {
@@ -584,6 +612,13 @@ int32_t aion_cuda_elemwise(AionCudaDevice* dev, const AionCudaElemwise* s) {
   if (int32_t st = resolve(s->out, need_o, "elemwise.out", &out)) return st;
   if (int32_t st = resolve(s->a, need_a, "elemwise.a", &a)) return st;
   if (int32_t st = resolve(s->b, need_b, "elemwise.b", &b)) return st;
+  const uintptr_t bits = reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b);
+  if ((bits & 15) == 0 && s->count % 4 == 0 && cols % 4 == 0 && ldo % 4 == 0 && lda % 4 == 0 && ldb % 4 == 0) {
+    AION_CUDA_TRY(launch_pdl(elemwise4_kernel, dim3(grid_for(dev, s->count / 4, 256)), dim3(256), 0, dev->stream, reinterpret_cast<float4*>(out),
+                             reinterpret_cast<const float4*>(a), reinterpret_cast<const float4*>(b), s->count / 4, s->op, cols / 4, ldo / 4,
+                             lda / 4, ldb / 4));
+    return AION_CUDA_OK;
+  }
   AION_CUDA_TRY(launch_pdl(elemwise_kernel, dim3(grid_for(dev, s->count, 256)), dim3(256), 0, dev->stream, out, a, b, s->count, s->op, cols,
                            ldo, lda, ldb));
   return AION_CUDA_OK;

@@ -59,11 +59,12 @@ def test_rms_norm_in_place_and_bad_eps(sess):
 
 
 @pytest.mark.parametrize("op,code", [("add", 0), ("mul", 1), ("gate", 2)])
-def test_elemwise_bit_exact(sess, op, code):
+@pytest.mark.parametrize("n", [70001, 65536])  # element by element; as float4s
+def test_elemwise_bit_exact(sess, op, code, n):
     s, store = sess
     rng = np.random.default_rng(code)
-    a = (rng.standard_normal(70001) * 4).astype(np.float32)
-    b = rng.standard_normal(70001).astype(np.float32)
+    a = (rng.standard_normal(n) * 4).astype(np.float32)
+    b = rng.standard_normal(n).astype(np.float32)
     a[:8] = [0.0, -0.0, 50.0, -50.0, 1e-30, 9.99, -9.99, 100.0]
     ta, tb = put(store, a, F32), put(store, b, F32)
     to = store.add(TensorMeta(F32, a.shape))
@@ -238,10 +239,10 @@ def test_rope_kv_append_equals_the_six_steps(sess, rolling):
     np.testing.assert_allclose(got_k.astype(np.float32), want_k.astype(np.float32), rtol=0, atol=2e-3)  # one f16 ulp where sincos differs
 
 
-def test_gate_on_strided_halves(sess):
+@pytest.mark.parametrize("R,F", [(5, 512), (3, 510)])  # rows readable as float4s; rows that are not
+def test_gate_on_strided_halves(sess, R, F):
     s, store = sess
     rng = np.random.default_rng(33)
-    R, F = 5, 512
     gu = rng.standard_normal((R, 2 * F)).astype(np.float32)
     tg = put(store, gu, F32)
     ch = store.acquire_const(tg)

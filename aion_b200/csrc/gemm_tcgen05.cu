@@ -10,13 +10,13 @@
 // Shape of the kernel (one persistent CTA per SM, 128 x 256 output tiles, K in steps of 64):
 //   warp 0      TMA producer of bf16 activation tiles (128B-swizzled, straight into the MMA
 //               operand layout); warp 2: TMA producer of the packed weight blocks, untouched.
-//   warps 3-8   dequantizers: packed blocks -> bf16 -> the 128B-swizzled K-major operand
+//   warps 3-14  dequantizers: packed blocks -> bf16 -> the 128B-swizzled K-major operand
 //               layout in shared memory (one generic-proxy pass; the packed bytes cannot be
 //               fed to the tensor core as they are), then a proxy fence and an arrive.
 //   warp 1      MMA issuer: one elected lane issues tcgen05.mma (M=128 tokens, N=256
 //               columns, K=16) four times per stage into one of two TMEM accumulators and
 //               commits to the stage's "empty" barrier; it also owns TMEM alloc / dealloc.
-//   warps 9-12  epilogue: tcgen05.ld the finished accumulator, alpha / beta in f32, store.
+//   warps 15-18 epilogue: tcgen05.ld the finished accumulator, alpha / beta in f32, store.
 // The activation is converted to bf16 once by a pre-pass (so every column tile re-reads
 // 2 bytes per element from L2 instead of converting 4), with the order of K inside each
 // group of 8 permuted for q4 to match the order in which a 32-bit word of nibbles
@@ -43,7 +43,7 @@ constexpr int UMMA_K = 16;
 constexpr int MAX_A_STAGES = 4, MAX_P_STAGES = 6, MAX_B_STAGES = 3;
 constexpr int KB_PER_STAGE = BK / QK;   // 2 quantized blocks of each column per stage
 constexpr int DEQ_GROUPS = 3;           // groups of dequantizer warps; group g unpacks k-stages g, g + 3, ...
-constexpr int DEQ_WARPS = 2 * DEQ_GROUPS;
+constexpr int DEQ_WARPS = 4 * DEQ_GROUPS;   // 12: measured against 6 (slower: each warp is a latency chain) and 24 (no faster)
 constexpr int DEQ_WARP0 = 3;            // warp 0: activation TMA, warp 1: MMA, warp 2: packed-block TMA
 constexpr int EPI_WARP0 = DEQ_WARP0 + DEQ_WARPS;
 constexpr int THREADS = (EPI_WARP0 + 4) * 32;

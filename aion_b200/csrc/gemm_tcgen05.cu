@@ -627,11 +627,11 @@ int32_t launch_gemm(AionCudaDevice* dev, const MatMulArgs& g, const __nv_bfloat1
   p.partial = partial;
   const uint32_t units = p.m_tiles * p.n_tiles * splits;
   const uint32_t grid = units < (uint32_t)dev->sm_count ? units : (uint32_t)dev->sm_count;
-  AION_CUDA_TRY(launch_pdl(kernel, dim3(grid), dim3(THREADS), (size_t)G::SMEM_BYTES, dev->stream, p, tmap_a, tmap_b));
+  AION_CUDA_TRY(launch_pdl_main(kernel, dim3(grid), dim3(THREADS), (size_t)G::SMEM_BYTES, dev->stream, p, tmap_a, tmap_b));
   if (splits > 1) {
     const uint64_t quads = (uint64_t)g.m * (g.n / 4);
     const unsigned blocks = (unsigned)std::min<uint64_t>(ceil_div(quads, (uint64_t)256), (uint64_t)dev->sm_count * 8);
-    AION_CUDA_TRY(launch_pdl(splitk_reduce_kernel, dim3(blocks), dim3(256), 0, dev->stream, p));
+    AION_CUDA_TRY(launch_pdl_main(splitk_reduce_kernel, dim3(blocks), dim3(256), 0, dev->stream, p));
   }
   return AION_CUDA_OK;
 }
@@ -685,11 +685,11 @@ int32_t gemm_tcgen05(AionCudaDevice* dev, const MatMulArgs& g_in, bool forced) {
     const uint64_t kblocks = g.k / QK, total = g.n * kblocks;
     if (g.order == AION_CUDA_ORDER_ROW_MAJOR && ceil_div(kblocks, (uint64_t)RT_KB) <= 65535) {
       const dim3 grid((unsigned)ceil_div(g.n, (uint64_t)RT_ROWS), (unsigned)ceil_div(kblocks, (uint64_t)RT_KB));
-      AION_CUDA_TRY(launch_pdl(nt_rowmajor_to_kmajor_kernel, grid, dim3(256), 0, dev->stream, reinterpret_cast<const uint16_t*>(g.b),
+      AION_CUDA_TRY(launch_pdl_main(nt_rowmajor_to_kmajor_kernel, grid, dim3(256), 0, dev->stream, reinterpret_cast<const uint16_t*>(g.b),
                                reinterpret_cast<uint16_t*>(scratch), g.n, kblocks));
     } else {
       const unsigned blocks = (unsigned)std::min<uint64_t>(ceil_div(total, (uint64_t)256), (uint64_t)dev->sm_count * 16);
-      AION_CUDA_TRY(launch_pdl(nt_to_kmajor_kernel, dim3(blocks), dim3(256), 0, dev->stream, g.b, scratch, g.n, kblocks, nt_group, nt_chunk));
+      AION_CUDA_TRY(launch_pdl_main(nt_to_kmajor_kernel, dim3(blocks), dim3(256), 0, dev->stream, g.b, scratch, g.n, kblocks, nt_group, nt_chunk));
     }
     g.b = scratch;
     g.nt = false;
@@ -699,7 +699,7 @@ int32_t gemm_tcgen05(AionCudaDevice* dev, const MatMulArgs& g_in, bool forced) {
   {
     const uint64_t groups = g.m * (g.k / 8);
     const unsigned blocks = (unsigned)std::min<uint64_t>(ceil_div(groups, (uint64_t)256), (uint64_t)dev->sm_count * 8);
-    AION_CUDA_TRY(launch_pdl(convert_a_bf16_kernel, dim3(blocks), dim3(256), 0, dev->stream, g.a, g.lda, a_bf16, (uint32_t)g.m, (uint32_t)g.k,
+    AION_CUDA_TRY(launch_pdl_main(convert_a_bf16_kernel, dim3(blocks), dim3(256), 0, dev->stream, g.a, g.lda, a_bf16, (uint32_t)g.m, (uint32_t)g.k,
                              g.dtype == AION_CUDA_DTYPE_Q4_0 ? 1 : 0));
   }
   if (g.dtype == AION_CUDA_DTYPE_Q4_0)

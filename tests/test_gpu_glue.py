@@ -59,7 +59,7 @@ def test_rms_norm_in_place_and_bad_eps(sess):
 
 
 @pytest.mark.parametrize("op,code", [("add", 0), ("mul", 1), ("gate", 2)])
-@pytest.mark.parametrize("n", [70001, 65536])  # element by element; as float4s
+@pytest.mark.parametrize("n", [70001, 1 << 21])  # element by element; as float4s (large, aligned counts)
 def test_elemwise_bit_exact(sess, op, code, n):
     s, store = sess
     rng = np.random.default_rng(code)
@@ -239,7 +239,7 @@ def test_rope_kv_append_equals_the_six_steps(sess, rolling):
     np.testing.assert_allclose(got_k.astype(np.float32), want_k.astype(np.float32), rtol=0, atol=2e-3)  # one f16 ulp where sincos differs
 
 
-@pytest.mark.parametrize("R,F", [(5, 512), (3, 510)])  # rows readable as float4s; rows that are not
+@pytest.mark.parametrize("R,F", [(5, 512), (3, 510), (520, 2048)])  # small; ragged rows; large enough for the float4 kernel
 def test_gate_on_strided_halves(sess, R, F):
     s, store = sess
     rng = np.random.default_rng(33)

@@ -302,13 +302,13 @@ def run_ours(args):
         mem.copy_d2h(wh, w_arena, 0)
         xs = x_host.numpy()
         cbuf = np.zeros(N * M, dtype=np.float32)
-        threads = oracle.fast_max_threads()
-        oracle.fast_matmul_q(oracle.Q4_0, xs[0], wh[:W_BYTES], M, N, K, c=cbuf)
+        threads = host_threads()
+        oracle.fast_matmul_q(oracle.Q4_0, xs[0], wh[:W_BYTES], M, N, K, c=cbuf, threads=threads)
         t0 = time.perf_counter()
         reps = 0
         while time.perf_counter() - t0 < 8.0:
             for i in range(sample):
-                oracle.fast_matmul_q(oracle.Q4_0, xs[i], wh[i * W_BYTES:(i + 1) * W_BYTES], M, N, K, c=cbuf)
+                oracle.fast_matmul_q(oracle.Q4_0, xs[i], wh[i * W_BYTES:(i + 1) * W_BYTES], M, N, K, c=cbuf, threads=threads)
             reps += 1
         dt = time.perf_counter() - t0
         cpu_baseline = {"value": round(reps * sample * BYTES_PER_LAUNCH / dt / 1e9, 3), "unit": "GB/s", "cores": threads,
@@ -417,13 +417,22 @@ def run_other(args):
         dist.destroy_process_group()
 
 
+def host_threads() -> int:
+    """Cores this process may run on. The launcher for several ranks sets OMP_NUM_THREADS=1, so the
+    OpenMP default is not the answer: the CPU legs pass this count to the kernels explicitly."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def run_reference(args):
     """The reference's CPU path for the same step, on this host's cores (rank 0 only)."""
     if int(os.environ.get("RANK", "0")) != 0:
         return
     import oracle
 
-    threads = oracle.fast_max_threads()
+    threads = host_threads()
     rng = np.random.default_rng(1234)
     base = 4
     mats = [oracle.quantize(oracle.Q4_0, (rng.standard_normal((K, N)) * 0.02).astype(np.float32), 0) for _ in range(base)]
@@ -435,7 +444,8 @@ def run_reference(args):
     cbuf = np.zeros(M * N, dtype=np.float32)
 
     def gemv(i):
-        oracle.fast_matmul_q(oracle.Q4_0, xs[i % copies], arena[(i % copies) * W_BYTES:(i % copies + 1) * W_BYTES], M, N, K, c=cbuf)
+        oracle.fast_matmul_q(oracle.Q4_0, xs[i % copies], arena[(i % copies) * W_BYTES:(i % copies + 1) * W_BYTES], M, N, K, c=cbuf,
+                             threads=threads)
 
     gemv(0)
     t0 = time.perf_counter()

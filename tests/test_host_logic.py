@@ -121,3 +121,13 @@ def test_views_of_one_buffer_are_seen_as_the_same_memory():
     sess.record([StepMatMul(c=gu, a=x, b=w), StepElemwiseBinary(op="gate", out=act, a=gate, b=up)], lanes=4)
     got = _lanes(be._lib.calls)
     assert got[0][1] == got[1][1], "the gate reads the matmul's output through views: it must follow it in the same lane"
+
+
+def test_cpu_legs_use_the_hosts_cores_whatever_the_launcher_sets(monkeypatch):
+    """The multi-rank launcher exports OMP_NUM_THREADS=1; bench.py's CPU legs must still pass the
+    cores this process may run on to the threaded oracle port, explicitly."""
+    import os
+    import bench
+    monkeypatch.setenv("OMP_NUM_THREADS", "1")
+    want = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    assert bench.host_threads() == max(1, want)

@@ -156,6 +156,9 @@ class TensorMeta:
     # Elements between consecutive rows (rows = all leading dims folded) of a view whose rows
     # are slices of a wider buffer; 0 = dense. Only the steps that say so accept such views.
     row_stride: int = 0
+    # For a quantized-activation image (an i8 byte buffer made by `act_image_meta`): the weight
+    # dtype it is laid out for; None for ordinary tensors.
+    image_for: Optional[int] = None
 
     @property
     def rank(self) -> int:
@@ -183,6 +186,14 @@ class Chunk:
         return capi.Operand(self.handle, self.offset, self.len)
 
 
+def act_image_meta(m: int, k: int, weight_dtype: int) -> TensorMeta:
+    """Meta of the quantized image of an [m, k] activation for a matmul against `weight_dtype` weights
+    (`aion_cuda_act_image_bytes`): a zero-filled byte buffer a producing step writes and the matmul reads."""
+    n = C.c_uint64()
+    _check(capi.load().aion_cuda_act_image_bytes(m, k, C.byref(n)))
+    return TensorMeta(capi.DTYPE_I8, (int(n.value),), image_for=weight_dtype)
+
+
 class DeviceStore:
     """A minimal tensor table: TensorId -> (meta, device chunk). Owns what it allocates."""
 
@@ -203,6 +214,8 @@ class DeviceStore:
             if data.nbytes != nbytes:
                 raise BackendError(capi.INVALID_ARGUMENT, f"tensor holds {nbytes} bytes, data has {data.nbytes}")
             self.memory.copy_h2d(h, 0, data)
+        elif meta.image_for is not None:
+            self.memory.memset(h, 0, 0, max(nbytes, 1))  # an image's padding must read as zeros
         return self.bind(meta, Chunk(h, 0, nbytes))
 
     def bind(self, meta: TensorMeta, chunk: Chunk) -> int:
@@ -266,6 +279,9 @@ class StepMatMul:
     alpha: float = 1.0
     beta: float = 0.0
     flags: int = capi.MATMUL_AUTO
+    # TensorId of the quantized image of A that the producing step wrote (no counterpart in the
+    # reference; see `ActImage`), or None.
+    a_image: Optional[int] = None
 
 
 @dataclasses.dataclass
@@ -276,6 +292,7 @@ class StepMatMulNT:
     alpha: float = 1.0
     beta: float = 0.0
     flags: int = capi.MATMUL_AUTO
+    a_image: Optional[int] = None
 
 
 @dataclasses.dataclass
@@ -310,6 +327,7 @@ class StepAttention:
     scale: float = 1.0
     window: AttentionWindow = dataclasses.field(default_factory=AttentionWindow)
     attn_logits_soft_cap: float = 0.0
+    image: Optional[int] = None       # also write the quantized image of `out` (see `ActImage`)
 
 
 @dataclasses.dataclass
@@ -321,6 +339,7 @@ class StepRMSNorm:
     beta: int
     eps: float
     residual: Optional[int] = None
+    image: Optional[int] = None
 
 
 @dataclasses.dataclass
@@ -330,6 +349,7 @@ class StepElemwiseBinary:
     out: int
     a: int
     b: int
+    image: Optional[int] = None
 
 
 @dataclasses.dataclass
@@ -345,6 +365,7 @@ class StepRMSNormPair:
     eps1: float
     eps2: float
     residual: Optional[int] = None
+    image: Optional[int] = None       # the quantized image of out2
 
 
 @dataclasses.dataclass
@@ -440,22 +461,23 @@ class CudaSession:
     @staticmethod
     def _touches(step) -> tuple[set, set]:
         """(tensors read, tensors written) of a step, by TensorId."""
+        img = lambda t: {t} if t is not None else set()
         if isinstance(step, (StepMatMul, StepMatMulNT)):
-            reads = {step.a, step.b} | ({step.c} if step.beta != 0.0 else set())
+            reads = {step.a, step.b} | ({step.c} if step.beta != 0.0 else set()) | img(step.a_image)
             return reads, {step.c}
         if isinstance(step, StepAttention):
             reads = {step.q, step.k, step.v}
             reads |= {t for t in (step.query_positions, step.kv_lengths) if t is not None}
-            return reads, {step.out}
+            return reads, {step.out} | img(step.image)
         if isinstance(step, StepRMSNorm):
             reads = {step.x, step.gamma, step.beta} | ({step.residual} if step.residual is not None else set())
-            return reads, {step.out}
+            return reads, {step.out} | img(step.image)
         if isinstance(step, StepElemwiseBinary):
-            return {step.a, step.b}, {step.out}
+            return {step.a, step.b}, {step.out} | img(step.image)
         if isinstance(step, StepRMSNormPair):
             reads = {step.x, step.gamma1, step.beta1, step.gamma2, step.beta2}
             reads |= {step.residual} if step.residual is not None else set()
-            return reads, {step.out1, step.out2}
+            return reads, {step.out1, step.out2} | img(step.image)
         if isinstance(step, StepRopeKVAppend):
             return ({step.qkv, step.positions, step.end_index, step.k_cache, step.v_cache},
                     {step.q_out, step.k_cache, step.v_cache})
@@ -523,6 +545,15 @@ class CudaSession:
     def retire_resources(self) -> None:
         self.backend.sync()
 
+    def _image(self, tid: Optional[int], what: str) -> tuple:
+        """(operand, weight dtype) of an optional activation image."""
+        if tid is None:
+            return capi.Operand(0, 0, 0), 0
+        m = self.store.meta(tid)
+        if m.image_for is None:
+            raise BackendError(capi.INVALID_ARGUMENT, f"{what}: tensor {tid} is not an activation image")
+        return self.store.acquire_mut(tid).operand(), m.image_for
+
     def deinit(self) -> None:
         self.retire_resources()
 
@@ -538,9 +569,12 @@ class CudaSession:
         m = _rows_of(cm.shape)
         if am.shape[-1] != k or cm.shape[-1] != n or _rows_of(am.shape) != m:
             raise BackendError(capi.INVALID_ARGUMENT, "matmul: shapes do not agree")
+        img, img_dt = self._image(s.a_image, "matmul.a_image")
+        if s.a_image is not None and img_dt != bm.dtype:
+            raise BackendError(capi.INVALID_ARGUMENT, "matmul: the image of A was laid out for another weight dtype")
         rec = capi.MatMul(c=st.acquire_mut(s.c).operand(), a=st.acquire_const(s.a).operand(),
                           b=st.acquire_const(s.b).operand(), b_dtype=bm.dtype, flags=s.flags, m=m, n=n, k=k,
-                          lda=0, ldb=0, ldc=0, alpha=s.alpha, beta=s.beta)
+                          lda=0, ldb=0, ldc=0, alpha=s.alpha, beta=s.beta, a_image=img)
         _check(self._lib.aion_cuda_matmul(self.backend._h, C.byref(rec)))
 
     def _matmul_nt(self, s: StepMatMulNT) -> None:
@@ -555,9 +589,12 @@ class CudaSession:
         m = _rows_of(cm.shape)
         if am.shape[-1] != k or cm.shape[-1] != n:
             raise BackendError(capi.INVALID_ARGUMENT, "matmul_nt: shapes do not agree")
+        img, img_dt = self._image(s.a_image, "matmul_nt.a_image")
+        if s.a_image is not None and img_dt != bm.dtype:
+            raise BackendError(capi.INVALID_ARGUMENT, "matmul_nt: the image of A was laid out for another weight dtype")
         rec = capi.MatMulNT(c=st.acquire_mut(s.c).operand(), a=st.acquire_const(s.a).operand(),
                             b=st.acquire_const(s.b).operand(), b_dtype=bm.dtype, block_order=bm.block_order,
-                            flags=s.flags, m=m, n=n, k=k, lda=0, ldc=0, c_off=0, alpha=s.alpha, beta=s.beta)
+                            flags=s.flags, m=m, n=n, k=k, lda=0, ldc=0, c_off=0, alpha=s.alpha, beta=s.beta, a_image=img)
         _check(self._lib.aion_cuda_matmul_nt(self.backend._h, C.byref(rec)))
 
     def _attention(self, s: StepAttention) -> None:
@@ -589,7 +626,8 @@ class CudaSession:
                 raise BackendError(capi.INVALID_ARGUMENT, "attention: kv_lengths must be i32 [B]")
             lens = st.acquire_const(s.kv_lengths).operand()
         rolling = 1 if st.sequence_cache_policy_info(s.k) == "rolling" else 0
-        rec = capi.Attention(out=st.acquire_mut(s.out).operand(), q=st.acquire_const(s.q).operand(),
+        img, img_dt = self._image(s.image, "attention.image")
+        rec = capi.Attention(image=img, image_dtype=img_dt, out=st.acquire_mut(s.out).operand(), q=st.acquire_const(s.q).operand(),
                              k=st.acquire_const(s.k).operand(), v=st.acquire_const(s.v).operand(),
                              query_positions=pos, kv_lengths=lens, q_dtype=qm.dtype, k_dtype=km.dtype,
                              v_dtype=vm.dtype, rolling=rolling, batch=B, l_q=L, h_q=Hq, h_kv=Hkv, d_k=Dk, d_v=Dv,
@@ -624,9 +662,10 @@ class CudaSession:
         if s.residual is not None:
             self._need(s.residual, capi.DTYPE_F32, "rms_norm.residual")
             res = st.acquire_const(s.residual).operand()
+        img, img_dt = self._image(s.image, "rms_norm.image")
         rec = capi.RMSNorm(out=st.acquire_mut(s.out).operand(), x=st.acquire_const(s.x).operand(),
                            gamma=st.acquire_const(s.gamma).operand(), beta=st.acquire_const(s.beta).operand(),
-                           residual=res, rows=rows, cols=cols, eps=s.eps, reserved=0)
+                           residual=res, rows=rows, cols=cols, eps=s.eps, image_dtype=img_dt, image=img)
         _check(self._lib.aion_cuda_rms_norm(self.backend._h, C.byref(rec)))
 
     def _elemwise(self, s: StepElemwiseBinary) -> None:
@@ -642,10 +681,12 @@ class CudaSession:
                 raise BackendError(capi.UNSUPPORTED, "elemwise: only identical shapes are covered")
             metas.append(m)
         strided = any(m.row_stride for m in metas)
-        cols = int(om.shape[-1]) if strided else 0
+        img, img_dt = self._image(s.image, "elemwise.image")
+        cols = int(om.shape[-1]) if (strided or s.image is not None) else 0
         rec = capi.Elemwise(out=st.acquire_mut(s.out).operand(), a=st.acquire_const(s.a).operand(),
                             b=st.acquire_const(s.b).operand(), count=int(np.prod(om.shape)), op=ops[s.op], reserved=0,
-                            cols=cols, ld_out=metas[0].row_stride, ld_a=metas[1].row_stride, ld_b=metas[2].row_stride)
+                            cols=cols, ld_out=metas[0].row_stride, ld_a=metas[1].row_stride, ld_b=metas[2].row_stride,
+                            image=img, image_dtype=img_dt, reserved2=0)
         _check(self._lib.aion_cuda_elemwise(self.backend._h, C.byref(rec)))
 
     def _rms_norm_pair(self, s: StepRMSNormPair) -> None:
@@ -663,8 +704,10 @@ class CudaSession:
             self._need(s.residual, capi.DTYPE_F32, "rms_norm_pair.residual")
             res = st.acquire_const(s.residual).operand()
         op = lambda t: st.acquire_const(t).operand()
+        img, img_dt = self._image(s.image, "rms_norm_pair.image")
         rec = capi.RMSNormPair(out1=op(s.out1), out2=op(s.out2), x=op(s.x), gamma1=op(s.gamma1), beta1=op(s.beta1), residual=res,
-                               gamma2=op(s.gamma2), beta2=op(s.beta2), rows=rows, cols=cols, eps1=s.eps1, eps2=s.eps2)
+                               gamma2=op(s.gamma2), beta2=op(s.beta2), rows=rows, cols=cols, eps1=s.eps1, eps2=s.eps2,
+                               image=img, image_dtype=img_dt, reserved=0)
         _check(self._lib.aion_cuda_rms_norm_pair(self.backend._h, C.byref(rec)))
 
     def _rope_kv_append(self, s: StepRopeKVAppend) -> None:

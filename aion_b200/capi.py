@@ -15,8 +15,9 @@ DTYPE_F32, DTYPE_F16, DTYPE_I8, DTYPE_Q4_0, DTYPE_Q8_0, DTYPE_I32 = range(6)
 ORDER_ROW_MAJOR, ORDER_LANES4, ORDER_LANES8, ORDER_LANES16, ORDER_LANES32, ORDER_LANES32X16 = range(6)
 WINDOW_UNBOUNDED = 0xFFFFFFFF
 MATMUL_AUTO, MATMUL_FORCE_GENERIC, MATMUL_FORCE_GEMV, MATMUL_FORCE_GEMM = 0, 1, 2, 4
-GEMV_MAX_M = 16
-GEMM_MIN_M = 33
+INT8_GROUP_ROWS = 64
+GEMM_MIN_M = 513
+KERNEL_GENERIC, KERNEL_INT8, KERNEL_GEMM = 1, 2, 3
 ELEMWISE_ADD, ELEMWISE_MUL, ELEMWISE_GATE_GELU = 0, 1, 2
 RECORD_LANES = 8
 
@@ -46,7 +47,13 @@ class MatMul(C.Structure):
         ("m", C.c_uint64), ("n", C.c_uint64), ("k", C.c_uint64),
         ("lda", C.c_uint64), ("ldb", C.c_uint64), ("ldc", C.c_uint64),
         ("alpha", C.c_float), ("beta", C.c_float),
+        ("a_image", Operand),
     ]
+
+
+class MatMulPlan(C.Structure):
+    _fields_ = [("kernel", C.c_uint32), ("tile_rows", C.c_uint32), ("tile_cols", C.c_uint32), ("k_splits", C.c_uint32),
+                ("grid", C.c_uint32), ("reserved", C.c_uint32 * 3)]
 
 
 class MatMulNT(C.Structure):
@@ -56,6 +63,7 @@ class MatMulNT(C.Structure):
         ("m", C.c_uint64), ("n", C.c_uint64), ("k", C.c_uint64),
         ("lda", C.c_uint64), ("ldc", C.c_uint64), ("c_off", C.c_uint64),
         ("alpha", C.c_float), ("beta", C.c_float),
+        ("a_image", Operand),
     ]
 
 
@@ -69,24 +77,27 @@ class Attention(C.Structure):
         ("scale", C.c_float), ("soft_cap", C.c_float),
         ("window_left", C.c_uint32), ("window_right", C.c_uint32), ("window_chunk", C.c_uint32),
         ("flags", C.c_uint32),
+        ("image", Operand), ("image_dtype", C.c_uint32), ("reserved", C.c_uint32),
     ]
 
 
 class RMSNorm(C.Structure):
     _fields_ = [("out", Operand), ("x", Operand), ("gamma", Operand), ("beta", Operand), ("residual", Operand),
-                ("rows", C.c_uint64), ("cols", C.c_uint64), ("eps", C.c_float), ("reserved", C.c_uint32)]
+                ("rows", C.c_uint64), ("cols", C.c_uint64), ("eps", C.c_float), ("image_dtype", C.c_uint32),
+                ("image", Operand)]
 
 
 class Elemwise(C.Structure):
     _fields_ = [("out", Operand), ("a", Operand), ("b", Operand), ("count", C.c_uint64), ("op", C.c_uint32),
                 ("reserved", C.c_uint32), ("cols", C.c_uint64), ("ld_out", C.c_uint64), ("ld_a", C.c_uint64),
-                ("ld_b", C.c_uint64)]
+                ("ld_b", C.c_uint64), ("image", Operand), ("image_dtype", C.c_uint32), ("reserved2", C.c_uint32)]
 
 
 class RMSNormPair(C.Structure):
     _fields_ = [("out1", Operand), ("out2", Operand), ("x", Operand), ("gamma1", Operand), ("beta1", Operand),
                 ("residual", Operand), ("gamma2", Operand), ("beta2", Operand),
-                ("rows", C.c_uint64), ("cols", C.c_uint64), ("eps1", C.c_float), ("eps2", C.c_float)]
+                ("rows", C.c_uint64), ("cols", C.c_uint64), ("eps1", C.c_float), ("eps2", C.c_float),
+                ("image", Operand), ("image_dtype", C.c_uint32), ("reserved", C.c_uint32)]
 
 
 class RopeKVAppend(C.Structure):
@@ -156,6 +167,9 @@ SIGNATURES = {
     "aion_cuda_memset": (C.c_int32, [_DEV, C.c_uint64, C.c_size_t, C.c_int32, C.c_size_t]),
     "aion_cuda_matmul": (C.c_int32, [_DEV, C.POINTER(MatMul)]),
     "aion_cuda_matmul_static_scratch": (C.c_int32, [_DEV, C.POINTER(MatMul)]),
+    "aion_cuda_matmul_plan": (C.c_int32, [_DEV, C.POINTER(MatMul), C.POINTER(MatMulPlan)]),
+    "aion_cuda_act_image_bytes": (C.c_int32, [C.c_uint64, C.c_uint64, C.POINTER(C.c_uint64)]),
+    "aion_cuda_act_image": (C.c_int32, [_DEV, C.c_uint32, _OPP, C.c_uint64, C.c_uint64, C.c_uint64, _OPP]),
     "aion_cuda_matmul_nt": (C.c_int32, [_DEV, C.POINTER(MatMulNT)]),
     "aion_cuda_attention": (C.c_int32, [_DEV, C.POINTER(Attention)]),
     "aion_cuda_rms_norm": (C.c_int32, [_DEV, C.POINTER(RMSNorm)]),

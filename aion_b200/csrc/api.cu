@@ -2,6 +2,7 @@
 #include <cmath>
 #include <cstdlib>
 
+#include "act_image.cuh"
 #include "common.cuh"
 
 using namespace aion;
@@ -14,51 +15,64 @@ uint64_t kmajor_bytes(uint64_t kblocks, uint64_t ldb, uint64_t n, size_t bb) {
   return kblocks == 0 ? 0 : ((kblocks - 1) * ldb + n) * bb;
 }
 
+// Rows of A from which the step is a dense contraction for the tensor cores (bf16 operands);
+// below, the int8 kernel streams the weights with the reference CPU kernels' arithmetic.
+uint64_t gemm_min_m() {
+  static const uint64_t v = [] {
+    const char* e = std::getenv("AION_CUDA_GEMM_MIN_M");  // tuning: where the int8 kernel hands over to the bf16 GEMM
+    const long x = e ? std::atol(e) : 0;
+    return x > 0 ? (uint64_t)x : (uint64_t)AION_CUDA_GEMM_MIN_M;
+  }();
+  return v;
+}
+
 int32_t route(AionCudaDevice* dev, const MatMulArgs& g, uint32_t flags, const char* what) {
   if (flags & AION_CUDA_MATMUL_FORCE_GENERIC) return matmul_generic(dev, g);
   if (flags & AION_CUDA_MATMUL_FORCE_GEMV) {
     const int32_t st = gemv_mma(dev, g, false);
-    if (st == AION_CUDA_UNSUPPORTED) return fail(st, "%s: the tiled GEMV does not read this shape or alignment", what);
+    if (st == AION_CUDA_UNSUPPORTED) return fail(st, "%s: the tiled int8 kernel does not read this shape or alignment", what);
     return st;
   }
   if (flags & AION_CUDA_MATMUL_FORCE_GEMM) {
-    const int32_t st = gemm_tcgen05(dev, g, false);
+    const int32_t st = gemm_tcgen05(dev, g);
     if (st == AION_CUDA_UNSUPPORTED) return fail(st, "%s: the tensor-core GEMM does not read this shape or alignment", what);
     return st;
   }
-  // Decode-sized m streams the weights through the int8 GEMV (groups of 16 rows of A share
-  // one launch; the weights of the second and later groups come from L2), with the
-  // reference CPU kernels' arithmetic; from AION_CUDA_GEMM_MIN_M rows on the step is a dense
-  // contraction for the tensor cores (bf16 operands). Either falls back to the any-shape
-  // kernel (still on the device) when the tiled kernel cannot read the operands.
-  static const uint64_t gemm_min_m = [] {
-    const char* e = std::getenv("AION_CUDA_GEMM_MIN_M");  // tuning: where the int8 GEMV hands over to the bf16 GEMM
-    const long v = e ? std::atol(e) : 0;
-    return v > 0 ? (uint64_t)v : (uint64_t)AION_CUDA_GEMM_MIN_M;
-  }();
-  if (g.m < gemm_min_m) {
+  // Either family falls back to the any-shape kernel (still on the device) when the tiled
+  // kernel cannot read the operands.
+  if (g.m < gemm_min_m()) {
     const int32_t st = gemv_mma(dev, g, false);
     if (st != AION_CUDA_UNSUPPORTED) return st;
   } else {
-    const int32_t st = gemm_tcgen05(dev, g, false);
+    const int32_t st = gemm_tcgen05(dev, g);
     if (st != AION_CUDA_UNSUPPORTED) return st;
   }
   return matmul_generic(dev, g);
 }
 
-}  // namespace
+// Resolves the optional activation image of a matmul step.
+int32_t resolve_image(const AionCudaOperand& op, uint64_t m, uint64_t k, const char* name, const uint8_t** out) {
+  *out = nullptr;
+  if (op.handle == 0) return AION_CUDA_OK;
+  const size_t need = act_image_total_bytes(act_image_layout(m, k / QK));
+  if (int32_t st = resolve(op, need, name, out)) return st;
+  if (reinterpret_cast<uintptr_t>(*out) & 15) return fail(AION_CUDA_INVALID_ARGUMENT, "%s: the image must be 16-byte aligned", name);
+  return AION_CUDA_OK;
+}
 
-extern "C" {
-
-int32_t aion_cuda_matmul(AionCudaDevice* dev, const AionCudaMatMul* s) {
-  if (!dev || !s) return fail(AION_CUDA_INVALID_ARGUMENT, "matmul: null argument");
+// Fills MatMulArgs from a `MatMul` step after checking it. *empty: nothing to do.
+int32_t matmul_args(const AionCudaMatMul* s, MatMulArgs* out, bool* empty) {
+  *empty = false;
   if (s->b_dtype == AION_CUDA_DTYPE_F32 || s->b_dtype == AION_CUDA_DTYPE_F16)
     return fail(AION_CUDA_UNSUPPORTED, "matmul: float B is outside this backend (quantized q8_0 / q4_0 only)");
   if (s->b_dtype != AION_CUDA_DTYPE_Q8_0 && s->b_dtype != AION_CUDA_DTYPE_Q4_0)
     return fail(AION_CUDA_INVALID_ARGUMENT, "matmul: B dtype %u", s->b_dtype);
   // Quantized B: K must be whole blocks (src/aion/graph/program/compiler.zig:189-239).
   if (s->k % QK != 0) return fail(AION_CUDA_INVALID_ARGUMENT, "matmul: k = %llu is not a multiple of 32", (unsigned long long)s->k);
-  if (s->m == 0 || s->n == 0) return AION_CUDA_OK;
+  if (s->m == 0 || s->n == 0) {
+    *empty = true;
+    return AION_CUDA_OK;
+  }
   MatMulArgs g{};
   g.dtype = s->b_dtype;
   g.nt = false;
@@ -77,15 +91,83 @@ int32_t aion_cuda_matmul(AionCudaDevice* dev, const AionCudaMatMul* s) {
   if (int32_t st = resolve(s->c, ((g.m - 1) * g.ldc + g.n) * sizeof(float), "matmul.c", &g.c)) return st;
   if (g.k == 0) {
     // An empty contraction still applies beta; the any-shape kernel handles it.
-    const uint8_t* none = nullptr;
-    g.b = none;
+    g.b = nullptr;
   } else if (int32_t st = resolve(s->b, kmajor_bytes(g.k / QK, g.ldb, g.n, bb), "matmul.b", &g.b)) {
     return st;
   }
   if ((reinterpret_cast<uintptr_t>(g.a) & 3) || (reinterpret_cast<uintptr_t>(g.c) & 3) || (reinterpret_cast<uintptr_t>(g.b) & 1))
     return fail(AION_CUDA_INVALID_ARGUMENT, "matmul: A and C must be 4-byte aligned, B 2-byte aligned");
+  if (g.k > 0)
+    if (int32_t st = resolve_image(s->a_image, g.m, g.k, "matmul.a_image", &g.a_image)) return st;
+  *out = g;
+  return AION_CUDA_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t aion_cuda_matmul(AionCudaDevice* dev, const AionCudaMatMul* s) {
+  if (!dev || !s) return fail(AION_CUDA_INVALID_ARGUMENT, "matmul: null argument");
+  MatMulArgs g{};
+  bool empty = false;
+  if (int32_t st = matmul_args(s, &g, &empty)) return st;
+  if (empty) return AION_CUDA_OK;
   if (int32_t st = dev->make_current()) return st;
   return route(dev, g, s->flags, "matmul");
+}
+
+int32_t aion_cuda_matmul_plan(AionCudaDevice* dev, const AionCudaMatMul* s, AionCudaMatMulPlan* out) {
+  if (!dev || !s || !out) return fail(AION_CUDA_INVALID_ARGUMENT, "matmul_plan: null argument");
+  *out = AionCudaMatMulPlan{};
+  MatMulArgs g{};
+  bool empty = false;
+  if (int32_t st = matmul_args(s, &g, &empty)) return st;
+  if (empty) return AION_CUDA_OK;
+  const bool want_gemm = (s->flags & AION_CUDA_MATMUL_FORCE_GEMM) || (!(s->flags & (AION_CUDA_MATMUL_FORCE_GEMV | AION_CUDA_MATMUL_FORCE_GENERIC)) && g.m >= gemm_min_m());
+  GemmPlan gp{};
+  if (s->flags & AION_CUDA_MATMUL_FORCE_GENERIC) {
+    out->kernel = AION_CUDA_KERNEL_GENERIC;
+  } else if (want_gemm && gemm_tcgen05_plan(dev, g, &gp)) {
+    out->kernel = AION_CUDA_KERNEL_GEMM;
+    out->tile_rows = gp.tile_rows;
+    out->tile_cols = 256;
+    out->k_splits = gp.splits;
+    out->grid = gp.grid;
+  } else if (!want_gemm && g.k > 0 && gemv_mma(dev, g, true) == AION_CUDA_OK) {
+    out->kernel = AION_CUDA_KERNEL_INT8;
+    out->tile_rows = g.m <= 8 ? 8u : (g.m <= 16 ? 16u : (g.m <= 32 ? 32u : (uint32_t)AION_CUDA_INT8_GROUP_ROWS));
+    out->tile_cols = g.m <= 16 ? 64u : 128u;
+    out->k_splits = 1;
+  } else {
+    out->kernel = AION_CUDA_KERNEL_GENERIC;
+  }
+  return AION_CUDA_OK;
+}
+
+int32_t aion_cuda_act_image_bytes(uint64_t m, uint64_t k, uint64_t* out_bytes) {
+  if (!out_bytes) return fail(AION_CUDA_INVALID_ARGUMENT, "act_image_bytes: null out");
+  if (k % QK != 0) return fail(AION_CUDA_INVALID_ARGUMENT, "act_image_bytes: k = %llu is not a multiple of 32", (unsigned long long)k);
+  if (m > (1ull << 22) || k > (1ull << 26)) return fail(AION_CUDA_UNSUPPORTED, "act_image_bytes: shape beyond what the matmul kernels index");
+  *out_bytes = m == 0 ? 0 : act_image_total_bytes(act_image_layout(m, k / QK));
+  return AION_CUDA_OK;
+}
+
+int32_t aion_cuda_act_image(AionCudaDevice* dev, uint32_t b_dtype, const AionCudaOperand* a, uint64_t m, uint64_t k, uint64_t lda,
+                            const AionCudaOperand* image) {
+  if (!dev || !a || !image) return fail(AION_CUDA_INVALID_ARGUMENT, "act_image: null argument");
+  if (b_dtype != AION_CUDA_DTYPE_Q8_0 && b_dtype != AION_CUDA_DTYPE_Q4_0) return fail(AION_CUDA_INVALID_ARGUMENT, "act_image: weight dtype %u", b_dtype);
+  if (k % QK != 0 || k == 0) return fail(AION_CUDA_INVALID_ARGUMENT, "act_image: k = %llu must be a positive multiple of 32", (unsigned long long)k);
+  if (m == 0) return AION_CUDA_OK;
+  if (m > (1ull << 22) || k > (1ull << 26)) return fail(AION_CUDA_UNSUPPORTED, "act_image: shape beyond what the matmul kernels index");
+  const uint64_t ld = lda ? lda : k;
+  if (ld < k) return fail(AION_CUDA_INVALID_ARGUMENT, "act_image: lda is shorter than a row");
+  const float* ap;
+  const uint8_t* ip;
+  if (int32_t st = resolve(*a, ((m - 1) * ld + k) * sizeof(float), "act_image.a", &ap)) return st;
+  if (int32_t st = resolve_image(*image, m, k, "act_image.image", &ip)) return st;
+  if (int32_t st = dev->make_current()) return st;
+  return act_image_from_f32(dev, b_dtype, ap, m, k, ld, const_cast<uint8_t*>(ip));
 }
 
 // The `MatMul` step for a caller that cannot allocate: same arguments and results as
@@ -154,6 +236,8 @@ int32_t aion_cuda_matmul_nt(AionCudaDevice* dev, const AionCudaMatMulNT* s) {
   else if (int32_t st = resolve(s->b, g.n * (g.k / QK) * Q8_BYTES, "matmul_nt.b", &g.b)) return st;
   if ((reinterpret_cast<uintptr_t>(g.a) & 3) || (reinterpret_cast<uintptr_t>(g.c) & 3) || (reinterpret_cast<uintptr_t>(g.b) & 1))
     return fail(AION_CUDA_INVALID_ARGUMENT, "matmul_nt: A and C must be 4-byte aligned, B 2-byte aligned");
+  if (g.k > 0)
+    if (int32_t st = resolve_image(s->a_image, g.m, g.k, "matmul_nt.a_image", &g.a_image)) return st;
   if (int32_t st = dev->make_current()) return st;
   return route(dev, g, s->flags, "matmul_nt");
 }

@@ -24,7 +24,9 @@
 //    row, f32 arithmetic, same merge inside the CTA.
 #include <cfloat>
 #include <cmath>
+#include <mutex>
 
+#include "act_image.cuh"
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -54,6 +56,11 @@ struct AttnParams {
   float* partial;        // [unit][split][8 heads][Dv + 4]: sums, max, sum of weights, pad
   int* tickets;          // [unit]
   int* fault;
+  // Optional: the quantized image of `out` as [B*L, Hq*Dv] rows (act_image.cuh), for the matmul
+  // that consumes the attention output.
+  uint8_t* image;
+  ActImageLayout image_layout;
+  uint32_t image_dtype;
 };
 
 struct KeyRange {
@@ -418,28 +425,40 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParam
     float* part = p.partial + ((uint64_t)unit * p.splits + split) * 8 * PP;
     float* orow = p.out + (((uint64_t)b * p.L + l) * p.Hq + h0) * D;
     const bool direct = p.splits == 1;
-    for (int idx = tid; idx < 8 * D; idx += CONSUMER_WARPS * 32) {
-      const int h = idx / D, d = idx % D;
-      if ((uint32_t)h >= nh) continue;
+    // Thread t owns the float4 columns t, t + 128, ... of the row's [8 heads][D] outputs: eight
+    // consecutive lanes hold one 32-block of the output row.
+    constexpr int C4 = (8 * D / 4) / (CONSUMER_WARPS * 32);
+    static_assert(C4 >= 1 && C4 * CONSUMER_WARPS * 32 * 4 == 8 * D, "whole float4 columns per thread");
+    const uint32_t out_row = b * p.L + l;
+#pragma unroll
+    for (int c = 0; c < C4; c++) {
+      const uint32_t idx4 = tid + c * (CONSUMER_WARPS * 32), h = idx4 / (D / 4), d = 4 * (idx4 % (D / 4));
+      const bool on = h < nh;
       float M = -INFINITY;
 #pragma unroll
       for (int w = 0; w < CONSUMER_WARPS; w++) M = fmaxf(M, all[w * WS + 8 * D + h]);
-      float o = 0.0f, lsum = 0.0f;
+      float4 o = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      float lsum = 0.0f;
 #pragma unroll
       for (int w = 0; w < CONSUMER_WARPS; w++) {
         const float mw = all[w * WS + 8 * D + h];
         const float f = (mw == -INFINITY) ? 0.0f : exp2f(mw - M);
-        o += all[w * WS + idx] * f;
+        const float4 x = *reinterpret_cast<const float4*>(all + w * WS + 4 * idx4);
+        o.x += x.x * f; o.y += x.y * f; o.z += x.z * f; o.w += x.w * f;
         lsum += all[w * WS + 8 * D + 8 + h] * f;
       }
       if (direct) {
-        if (lsum > 0.0f && isfinite(lsum)) orow[idx] = o / lsum;
-        else {
-          orow[idx] = 0.0f;
-          if (nkeys > 0 && !kr.bad && !*abort_flag) atomicExch(p.fault, FAULT_NONFINITE);
+        float4 r = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (lsum > 0.0f && isfinite(lsum)) r = make_float4(o.x / lsum, o.y / lsum, o.z / lsum, o.w / lsum);
+        else if (on && nkeys > 0 && !kr.bad && !*abort_flag) atomicExch(p.fault, FAULT_NONFINITE);
+        if (on) *reinterpret_cast<float4*>(orow + 4 * idx4) = r;
+        if (p.image) {
+          const uint32_t col4 = (h0 * D) / 4 + idx4;
+          if (p.image_dtype == AION_CUDA_DTYPE_Q8_0) quantize_store_block_8lanes<AION_CUDA_DTYPE_Q8_0>(r, col4 & 7, on, p.image, p.image_layout, out_row, col4 >> 3);
+          else quantize_store_block_8lanes<AION_CUDA_DTYPE_Q4_0>(r, col4 & 7, on, p.image, p.image_layout, out_row, col4 >> 3);
         }
-      } else {
-        part[h * PP + d] = o;
+      } else if (on) {
+        *reinterpret_cast<float4*>(part + h * PP + d) = o;
         if (d == 0) *reinterpret_cast<float2*>(part + h * PP + D) = make_float2(M, lsum);
       }
     }
@@ -489,9 +508,6 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParam
           if (lane == 0) lsums[h] = lsum;
         }
         consumer_sync();
-        // Thread t owns the float4 columns t, t + 128, ... of the row's [8 heads][D] outputs.
-        constexpr int C4 = (8 * D / 4) / (CONSUMER_WARPS * 32);
-        static_assert(C4 >= 1 && C4 * CONSUMER_WARPS * 32 * 4 == 8 * D, "whole float4 columns per thread");
         const float* colp[C4];
         const float* fh[C4];
         bool live[C4];
@@ -528,18 +544,16 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParam
         }
 #pragma unroll
         for (int c = 0; c < C4; c++) {
-          if (!live[c]) continue;
           const uint32_t idx4 = tid + c * (CONSUMER_WARPS * 32), h = idx4 / (D / 4);
-          const float lsum = lsums[h];
-          float* dst = orow + 4 * idx4;
-          if (lsum > 0.0f && isfinite(lsum)) {
-            dst[0] = o[c].x / lsum;
-            dst[1] = o[c].y / lsum;
-            dst[2] = o[c].z / lsum;
-            dst[3] = o[c].w / lsum;
-          } else {
-            dst[0] = dst[1] = dst[2] = dst[3] = 0.0f;
-            if (nkeys > 0 && !kr.bad) atomicExch(p.fault, FAULT_NONFINITE);
+          const float lsum = lsums[h & 7];
+          float4 r = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+          if (lsum > 0.0f && isfinite(lsum)) r = make_float4(o[c].x / lsum, o[c].y / lsum, o[c].z / lsum, o[c].w / lsum);
+          else if (live[c] && nkeys > 0 && !kr.bad) atomicExch(p.fault, FAULT_NONFINITE);
+          if (live[c]) *reinterpret_cast<float4*>(orow + 4 * idx4) = r;
+          if (p.image) {
+            const uint32_t col4 = (h0 * D) / 4 + idx4;
+            if (p.image_dtype == AION_CUDA_DTYPE_Q8_0) quantize_store_block_8lanes<AION_CUDA_DTYPE_Q8_0>(r, col4 & 7, live[c], p.image, p.image_layout, out_row, col4 >> 3);
+            else quantize_store_block_8lanes<AION_CUDA_DTYPE_Q4_0>(r, col4 & 7, live[c], p.image, p.image_layout, out_row, col4 >> 3);
           }
         }
       }
@@ -634,10 +648,15 @@ template <int D, bool QF32, bool TILED>
 int32_t launch_decode_as(AionCudaDevice* dev, const AttnParams& p, uint32_t units, const CUtensorMap& tk, const CUtensorMap& tv) {
   using G = DecodeGeom<D>;
   auto kernel = attn_decode_kernel<D, QF32, TILED>;
-  static bool configured[16] = {};
-  if (!configured[dev->ordinal & 15]) {
-    AION_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM_BYTES));
-    configured[dev->ordinal & 15] = true;
+  {
+    // Once per device and instantiation; several host threads may drive devices at once.
+    static std::mutex mu;
+    static bool configured[64] = {};
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev->ordinal < 0 || dev->ordinal >= 64 || !configured[dev->ordinal]) {
+      AION_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM_BYTES));
+      if (dev->ordinal >= 0 && dev->ordinal < 64) configured[dev->ordinal] = true;
+    }
   }
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(units, p.splits);
@@ -701,9 +720,18 @@ int32_t attention_launch(AionCudaDevice* dev, const AionCudaAttention* s) {
   p.fault = dev->fault_dev;
 
   const bool f16kv = s->k_dtype == AION_CUDA_DTYPE_F16 && s->v_dtype == AION_CUDA_DTYPE_F16;
-  const bool aligned = ((reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15) == 0 &&
+  const bool aligned = ((reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(out)) & 15) == 0 &&
                        (reinterpret_cast<uintptr_t>(q) & 3) == 0;
   const bool tensor_path = f16kv && aligned && Dk == Dv && (Dk == 64 || Dk == 128 || Dk == 256) && !(s->flags & 1u);
+  if (s->image.handle) {
+    if (!tensor_path) return fail(AION_CUDA_UNSUPPORTED, "attention: the output image is written by the f16 tensor-core kernel only (Dk = Dv in {64, 128, 256}, aligned operands)");
+    if (s->image_dtype != AION_CUDA_DTYPE_Q8_0 && s->image_dtype != AION_CUDA_DTYPE_Q4_0)
+      return fail(AION_CUDA_INVALID_ARGUMENT, "attention: image dtype %u", s->image_dtype);
+    p.image_layout = act_image_layout(B * L, Hq * Dv / QK);
+    if (int32_t st = resolve(s->image, act_image_total_bytes(p.image_layout), "attention.image", &p.image)) return st;
+    if (reinterpret_cast<uintptr_t>(p.image) & 15) return fail(AION_CUDA_INVALID_ARGUMENT, "attention.image: the image must be 16-byte aligned");
+    p.image_dtype = s->image_dtype;
+  }
   if (tensor_path) {
     const uint32_t group = p.Hq / p.Hkv;
     p.head_groups = (group + 7) / 8;

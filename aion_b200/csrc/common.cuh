@@ -73,8 +73,6 @@ struct AionCudaDevice {
   size_t scratch_bytes = 0;
   // Tuning override (environment AION_CUDA_GEMV_SPLIT): K-split of the tiled GEMV, 0 = automatic.
   uint32_t gemv_split_override = 0;
-  // Tuning override (AION_CUDA_GEMV_TILE): columns per CTA of the tiled GEMV (16/32/64), 0 = automatic.
-  uint32_t gemv_tile_override = 0;
   // Same for the decode attention's context split (AION_CUDA_ATTN_SPLIT), 0 = automatic.
   uint32_t attn_split_override = 0;
   // One arrival counter per attention row for the split-K merge; zero between launches.
@@ -189,13 +187,23 @@ struct MatMulArgs {
   uint32_t order;     // QuantBlockOrder, nt only
   uint64_t m, n, k, lda, ldb, ldc;
   float alpha, beta;
+  // The quantized image of A written by the kernel that produced A (act_image.cuh), or null:
+  // the int8 matmul then reads it instead of quantizing A itself.
+  const uint8_t* a_image = nullptr;
 };
 int32_t matmul_generic(AionCudaDevice* dev, const MatMulArgs& g);
 // Returns AION_CUDA_UNSUPPORTED (without setting an error) when the shape or the
 // alignment is outside what the tiled kernel reads; the caller then routes elsewhere.
 int32_t gemv_mma(AionCudaDevice* dev, const MatMulArgs& g, bool probe_only);
-int32_t gemm_tcgen05(AionCudaDevice* dev, const MatMulArgs& g, bool probe_only);
+int32_t gemm_tcgen05(AionCudaDevice* dev, const MatMulArgs& g);
 int32_t gemv_mma_static_scratch(AionCudaDevice* dev, const MatMulArgs& g);
+// Quantizes f32 rows into an activation image (act_image.cuh) for weights of `dtype`.
+int32_t act_image_from_f32(AionCudaDevice* dev, uint32_t dtype, const float* a, uint64_t m, uint64_t k, uint64_t lda, uint8_t* image);
+// What the prefill GEMM would do with this shape: rows per tile (128 or 256), K splits, CTAs.
+struct GemmPlan {
+  uint32_t tile_rows, splits, grid;
+};
+bool gemm_tcgen05_plan(const AionCudaDevice* dev, const MatMulArgs& g, GemmPlan* out);
 int32_t attention_launch(AionCudaDevice* dev, const AionCudaAttention* s);
 
 }  // namespace aion

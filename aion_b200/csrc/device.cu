@@ -315,10 +315,6 @@ int32_t aion_cuda_device_create(int32_t ordinal, AionCudaDevice** out) {
     const int v = std::atoi(e2);
     if (v == 1 || v == 2 || v == 4 || v == 8) d->gemv_split_override = (uint32_t)v;
   }
-  if (const char* e4 = std::getenv("AION_CUDA_GEMV_TILE")) {
-    const int v = std::atoi(e4);
-    if (v == 16 || v == 32 || v == 64) d->gemv_tile_override = (uint32_t)v;
-  }
   if (const char* e3 = std::getenv("AION_CUDA_ATTN_SPLIT")) {
     const int v = std::atoi(e3);
     if (v >= 1 && v <= 256) d->attn_split_override = (uint32_t)v;

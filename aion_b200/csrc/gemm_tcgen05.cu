@@ -27,6 +27,7 @@
 #include <cuda_fp16.h>
 
 #include <algorithm>
+#include <mutex>
 
 #include "common.cuh"
 #include "ptx.cuh"
@@ -597,11 +598,16 @@ __global__ void __launch_bounds__(256) nt_rowmajor_to_kmajor_kernel(const uint16
 template <int DT, int MH>
 int32_t launch_gemm(AionCudaDevice* dev, const MatMulArgs& g, const __nv_bfloat16* a_bf16, uint32_t splits, float* partial) {
   using G = GemmGeom<DT, MH>;
-  static bool configured[64] = {};
   auto kernel = gemm_q_tcgen05_kernel<DT, MH>;
-  if (dev->ordinal < 64 && !configured[dev->ordinal]) {
-    AION_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM_BYTES));
-    configured[dev->ordinal] = true;
+  {
+    // Once per device and instantiation; several host threads may drive devices at once.
+    static std::mutex mu;
+    static bool configured[64] = {};
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev->ordinal < 0 || dev->ordinal >= 64 || !configured[dev->ordinal]) {
+      AION_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM_BYTES));
+      if (dev->ordinal >= 0 && dev->ordinal < 64) configured[dev->ordinal] = true;
+    }
   }
   const uint64_t kblocks = g.k / QK;
   CUtensorMap tmap_a, tmap_b;
@@ -638,43 +644,63 @@ int32_t launch_gemm(AionCudaDevice* dev, const MatMulArgs& g, const __nv_bfloat1
 
 }  // namespace
 
-// Returns UNSUPPORTED (without setting a message) for shapes this kernel does not read, so
-// the caller can route them to the any-shape kernel.
-int32_t gemm_tcgen05(AionCudaDevice* dev, const MatMulArgs& g_in, bool forced) {
-  (void)forced;
-  MatMulArgs g = g_in;
-  if (g.dtype != AION_CUDA_DTYPE_Q4_0 && g.dtype != AION_CUDA_DTYPE_Q8_0) return AION_CUDA_UNSUPPORTED;
-  if (g.m == 0 || g.n == 0) return AION_CUDA_OK;
-  // `MatMulNT`: the same kernel after a block permutation of the weights into lane scratch
-  // (the reference's weight-layout pass does the equivalent once per model; here it costs one
-  // pass over the weight per call, a few percent of a prefill GEMM).
-  size_t relaid_bytes = 0;
-  int nt_group = 1, nt_chunk = 4;
+// Whether this kernel reads the step's operands, and how it would tile them.
+static bool plan_gemm(const AionCudaDevice* dev, const MatMulArgs& g, GemmPlan* out) {
+  if (g.dtype != AION_CUDA_DTYPE_Q4_0 && g.dtype != AION_CUDA_DTYPE_Q8_0) return false;
+  if (g.m == 0 || g.n == 0 || g.k == 0) return false;
   if (g.nt) {
-    if (g.dtype != AION_CUDA_DTYPE_Q8_0 || !block_order_info(g.order, &nt_group, &nt_chunk)) return AION_CUDA_UNSUPPORTED;
-    if ((g.n & 7) || ((uintptr_t)g.b & 1)) return AION_CUDA_UNSUPPORTED;
-    relaid_bytes = ((size_t)g.n * (g.k / QK) * Q8_BYTES + 1023) & ~size_t(1023);
-    g.ldb = g.n;
+    int group, chunk;
+    if (g.dtype != AION_CUDA_DTYPE_Q8_0 || !block_order_info(g.order, &group, &chunk)) return false;
+    if ((g.n & 7) || ((uintptr_t)g.b & 1)) return false;
   } else if ((g.ldb & 7) || ((uintptr_t)g.b & 15)) {
-    return AION_CUDA_UNSUPPORTED;
+    return false;
   }
-  if ((g.n & 7) || ((uintptr_t)g.c & 15) || (g.ldc & 3)) return AION_CUDA_UNSUPPORTED;
-  if (g.m > (1u << 24) || g.n > (1u << 24) || g.k > (1u << 24)) return AION_CUDA_UNSUPPORTED;
-  // Few output tiles (decode batches against narrow layers): split K so the SMs are covered.
-  // A split keeps at least two k-stages; its raw 128 x 256 accumulator goes through scratch.
+  if ((g.n & 7) || ((uintptr_t)g.c & 15) || (g.ldc & 3)) return false;
+  if (g.m > (1u << 24) || g.n > (1u << 24) || g.k > (1u << 24)) return false;
   // 256-token tiles (one dequantized weight tile feeds two MMAs) once there are enough of them
   // to fill the SMs; 128-token tiles with a double-buffered accumulator otherwise.
-  const uint64_t tiles256 = ceil_div(g.m, (uint64_t)(2 * BM)) * ceil_div(g.n, (uint64_t)BN);
   // (fewer 256-token tiles with a K split to fill the SMs measured slower: m = 512 x 8192 columns
   // took 47 us that way against 39 us with 128-token tiles)
-  const int mh = (g.m > BM && tiles256 >= (uint64_t)dev->sm_count) ? 2 : 1;
+  const uint64_t tiles256 = ceil_div(g.m, (uint64_t)(2 * BM)) * ceil_div(g.n, (uint64_t)BN);
+  const uint32_t mh = (g.m > BM && tiles256 >= (uint64_t)dev->sm_count) ? 2 : 1;
   const uint64_t tiles = ceil_div(g.m, (uint64_t)(BM * mh)) * ceil_div(g.n, (uint64_t)BN), k_stages = ceil_div(g.k, (uint64_t)BK);
+  // Few output tiles (narrow layers): split K so the SMs are covered. A split keeps at least
+  // two k-stages; its raw accumulator goes through scratch.
   uint64_t splits = 1;
   if (tiles * 2 <= (uint64_t)dev->sm_count) {
     splits = (uint64_t)dev->sm_count / tiles;
     if (splits > k_stages / 2) splits = k_stages / 2;
     if (splits > 16) splits = 16;
     if (splits < 1) splits = 1;
+  }
+  out->tile_rows = BM * mh;
+  out->splits = (uint32_t)splits;
+  const uint64_t units = tiles * splits;
+  out->grid = (uint32_t)(units < (uint64_t)dev->sm_count ? units : (uint64_t)dev->sm_count);
+  return true;
+}
+
+bool gemm_tcgen05_plan(const AionCudaDevice* dev, const MatMulArgs& g, GemmPlan* out) { return plan_gemm(dev, g, out); }
+
+// Returns UNSUPPORTED (without setting a message) for shapes this kernel does not read, so
+// the caller can route them to the any-shape kernel.
+int32_t gemm_tcgen05(AionCudaDevice* dev, const MatMulArgs& g_in) {
+  MatMulArgs g = g_in;
+  if (g.dtype != AION_CUDA_DTYPE_Q4_0 && g.dtype != AION_CUDA_DTYPE_Q8_0) return AION_CUDA_UNSUPPORTED;
+  if (g.m == 0 || g.n == 0) return AION_CUDA_OK;
+  GemmPlan plan{};
+  if (!plan_gemm(dev, g, &plan)) return AION_CUDA_UNSUPPORTED;
+  const int mh = (int)(plan.tile_rows / BM);
+  const uint64_t splits = plan.splits;
+  const uint64_t tiles = ceil_div(g.m, (uint64_t)plan.tile_rows) * ceil_div(g.n, (uint64_t)BN);
+  // `MatMulNT`: the same kernel after a block permutation of the weights into lane scratch
+  // (the reference's weight-layout pass does the equivalent once per model).
+  size_t relaid_bytes = 0;
+  int nt_group = 1, nt_chunk = 4;
+  if (g.nt) {
+    block_order_info(g.order, &nt_group, &nt_chunk);
+    relaid_bytes = ((size_t)g.n * (g.k / QK) * Q8_BYTES + 1023) & ~size_t(1023);
+    g.ldb = g.n;
   }
   // Lane scratch: the bf16 copy of the activation, then the split partials.
   const size_t a_bytes = ((size_t)g.m * g.k * sizeof(__nv_bfloat16) + 1023) & ~size_t(1023);

@@ -1,94 +1,100 @@
-// Decode GEMV for q4_0 / q8_0 weights: C[m,n] = alpha * A[m,k] . W + beta * C, m <= 16 per
-// group of CTAs (blockIdx.y walks further groups of 16 rows over the same weights).
+// Decode matmul for q4_0 / q8_0 weights with the reference's int8-activation arithmetic:
+// C[m,n] = alpha * A[m,k] . W + beta * C for the batch sizes of decoding (one row to a few
+// hundred rows of A). The weights are streamed from global memory exactly once per group of
+// up to 64 rows of A (blockIdx.y walks further groups of 64 rows; they find the weights in L2).
 //
 // Arithmetic is the reference CPU kernels' (src/aion/backend/cpu/kernels/matvec_q.zig:62-160,
 // src/aion/backend/cpu/kernels/matmul_nt_q.zig:74-95, src/aion/backend/cpu/kernels/matmul_q_i8.zig:385-497):
-// the activation is quantized to int8 per 32-block inside the kernel, every weight
-// block contributes float(exact int dot) * (a_scale * w_scale), accumulated in f32.
+// the activation is quantized to int8 per 32-block, every weight block contributes
+// float(exact int dot) * w_scale * a_scale, accumulated in f32 in K order.
 //
-// The kernel is HBM-bound: each weight byte is read from global memory exactly once.
-//   * Work is cut into units of (64 output columns) x (8 K blocks) = one shared-memory
-//     stage (9 KB of q4, 17 KB of q8). The grid is persistent — as many CTAs as are
-//     resident at once — and CTA c takes the contiguous unit range [c*U/G, (c+1)*U/G)
-//     in tile-major order ("stream-K"), so every SM streams the same number of bytes
-//     whatever the shape: no tail wave, and narrow matrices split along K for free.
-//   * A producer warp fills a 2-stage ring (shallow on purpose: concurrent launches overlap
-//     as far as CTAs fit an SM) with ONE tiled TMA load per stage (the weight
-//     tensor viewed as bytes in 8-byte elements; one request per stage, because the copy
-//     engine takes about 50 ns per request and per-row bulk copies made that the
-//     bottleneck), completing on mbarriers. Blocks are 18 / 34 bytes, so nothing inside
-//     a stage is aligned except the stage itself.
-//   * Four consumer warps drain it, each owning 16 of the tile's 64 columns for all K, so
-//     no sums cross warps. They feed the int8 tensor-core MMA (m16n8k32): the 16 "rows"
-//     are 16 output columns of one K block, the 8 "columns" are up to 8 activation rows.
+// The kernel is HBM-bound at small m and bound by instruction issue (the per-block scaling,
+// which has to run on the ordinary f32 pipes) at large m:
+//   * Work is cut into units of (TN output columns) x (8 K blocks) = one shared-memory stage,
+//     TN = 64 (up to 16 rows of A) or 128 (more). The grid is persistent and CTA c takes the
+//     contiguous unit range [c*U/G, (c+1)*U/G) in tile-major order ("stream-K"), so every SM
+//     streams the same number of bytes whatever the shape; when there are at least as many
+//     tiles as CTAs the ranges are rounded to whole tiles and no tile is shared.
+//   * A producer warp fills a 2-stage ring with ONE tiled TMA load per stage (the weight tensor
+//     viewed as bytes in 8-byte elements: blocks are 18 / 34 bytes, so nothing inside a stage
+//     is aligned except the stage itself), completing on mbarriers. With a pre-quantized
+//     activation image (m >= 2, deep K, or an image handed in by the producer of A) the
+//     stage's 8 K blocks of the image arrive with it as two more bulk copies.
+//   * Four consumer warps drain it, each owning 16 (or 2 x 16) of the tile's columns for all K,
+//     so no sums cross warps. They feed the int8 tensor-core MMA (m16n8k32): the 16 "rows"
+//     are 16 output columns of one K block, the 8 "columns" are 8 activation rows; a weight
+//     fragment is unpacked once and used for every group of 8 activation rows.
 //     q4 nibbles become int8 in three logic ops by placing the nibble in the high half of
-//     a byte (value 16*(nibble-8)); the 1/16 folds into the activation scale. One block's
-//     int32 dot leaves the MMA and is scaled and accumulated in f32 registers with
-//     packed f32x2 arithmetic.
-//   * Shared-memory reads are one wavefront each: the 8 row groups of a fragment read 8
-//     columns that are 8 apart (K-major: 4 words apart modulo the 32 banks) or 8
-//     consecutive weight rows 272 bytes apart (NT).
+//     a byte (value 16*(nibble-8)); the 1/16 folds into the activation scale.
+//   * int32 -> f32 without a conversion instruction: the MMA's accumulator input is the bit
+//     pattern of 1.5 * 2^23, so the result read as f32 is 12582912 + dot exactly, and one
+//     fused multiply-add (x * w_scale - 12582912 * w_scale, a single rounding of dot * w_scale)
+//     removes the offset while applying the weight scale. A second one applies the activation
+//     scale and accumulates. Both are packed f32x2 instructions over the MMA's natural
+//     register pairs (one weight column, two activation rows).
 //   * A tile whose K range is shared by several CTAs is finished by the last of them to
 //     arrive: each writes its partial sums to scratch, takes a ticket, and the last one
-//     adds the parts in CTA order (so results do not depend on timing) and stores C. While
-//     independent launches are recorded into parallel lanes and there is about one tile per
-//     SM, each CTA takes exactly one whole tile instead and this step is skipped.
+//     adds the parts in CTA order (so results do not depend on timing) and stores C.
 //   * With programmatic dependent launch the next kernel's weight stream starts as this
 //     one's CTAs retire; only the activation read waits for the previous kernel.
+#include <mutex>
+
+#include "act_image.cuh"
 #include "common.cuh"
 #include "ptx.cuh"
 #include "quant_device.cuh"
 
 namespace aion {
 
-
 namespace {
 
-constexpr int TN = 64;             // output columns per tile
 constexpr int KBT = 8;             // K blocks per stage
 constexpr int NS = 2;              // stages in the ring: shallow, so that more CTAs (of concurrent launches) fit an SM
-constexpr int CONSUMER_WARPS = 4;  // one per 16 columns
+constexpr int CONSUMER_WARPS = 4;
 constexpr int CONSUMER_THREADS = CONSUMER_WARPS * 32;
 constexpr int THREADS = CONSUMER_THREADS + 32;
 constexpr int NT_ROW_PITCH = KBT * Q8_BYTES;  // 272: 16-byte multiple, 4 words mod 32 banks
-constexpr size_t ACT_BUDGET_BYTES = 40 * 1024;  // quantized activations kept per CTA
-
+constexpr size_t ACT_BUDGET_BYTES = 40 * 1024;  // quantized activations kept per CTA when it quantizes them itself
+constexpr uint32_t MAGIC_BITS = 0x4B400000u;    // 1.5 * 2^23 as f32
+constexpr float MAGIC = 12582912.0f;
 
 struct GemvParams {
   const float* a;
   float* c;
   uint32_t m, n, kblocks;
-  uint32_t mp2;  // activation rows held in shared memory: m rounded up to even
   uint64_t lda, ldc;
   float alpha, beta;
   uint32_t tiles, stages_per_tile;
   uint64_t units;
-  float* partials;  // [cta][2][TN * 8*MT]
-  int* tickets;     // [tile][warp]
+  uint32_t whole_tiles;  // CTA ranges are rounded to tile boundaries: no tile is shared
+  float* partials;       // [group][cta][2][TN * rows]
+  int* tickets;          // [group][tile][warp]
   int* fault;
-  uint32_t a_vec4;  // A rows may be read as float4
-  // Pre-quantized activations (m >= 2): the shared-memory image of one group of rows,
-  // `act_image_bytes` per group, written by gemv_act_image_kernel.
+  uint32_t a_vec4;       // A rows may be read as float4
+  uint32_t c_vec2;       // C may be written as float2 (even ldc, 8-byte aligned base)
+  // Pre-quantized activations: `act_image_bytes` per group of rows (see act_image.cuh).
   const uint8_t* act_image;
   uint32_t act_image_bytes;
 };
 
-template <int DT, bool NT>
+// CG: groups of 16 columns per consumer warp (1: 64-column tiles, 2: 128-column tiles).
+template <int DT, bool NT, int CG>
 struct Geom {
   static constexpr int BB = (DT == AION_CUDA_DTYPE_Q8_0) ? Q8_BYTES : Q4_BYTES;
+  static constexpr int TN = 64 * CG;
   static constexpr int KM_PITCH = TN * BB;
   static constexpr int STAGE_BYTES = NT ? TN * NT_ROW_PITCH : KBT * KM_PITCH;
   static constexpr int RING_BYTES = NS * STAGE_BYTES;
   static constexpr int OFF_BARS = RING_BYTES;
   static constexpr int OFF_ACT = OFF_BARS + 128;
+  // Distance between a warp's first and second group of 16 columns inside a stage.
+  static constexpr int CG_STRIDE = NT ? 64 * NT_ROW_PITCH : 64 * BB;
   static_assert(STAGE_BYTES % 128 == 0, "TMA destinations are 128-byte aligned");
 };
 
-// Shared-memory bytes of the quantized activations: per K block, mp2 rows of 32 codes,
-// then mp2/2 scale quads (s_even, s_even, s_odd, s_odd).
-__host__ __device__ inline size_t act_bytes(uint32_t kb_pad, uint32_t mp2, uint32_t mt) {
-  return (size_t)kb_pad * (mp2 * 32 + (mp2 == 2 ? 16 : mt * 64));
-}
+// Shared-memory bytes of the quantized activations of `kb` K blocks and `rows` rows:
+// 32 code bytes and one f32 scale per (block, row).
+__host__ __device__ inline size_t act_bytes(uint32_t kb, uint32_t rows) { return (size_t)kb * rows * 36; }
 
 // Shared-memory loads by 32-bit shared address. They are plain (non-volatile) asm so the
 // compiler may interleave the loads of independent K blocks; each takes its address from
@@ -113,8 +119,10 @@ __device__ __forceinline__ uint2 lds_u64(uint32_t addr) {
   return v;
 }
 template <int OFF>
-__device__ __forceinline__ void lds_f32x4(uint32_t addr, uint64_t& lo, uint64_t& hi) {
-  asm("ld.shared.v2.b64 {%0, %1}, [%2+%3];" : "=l"(lo), "=l"(hi) : "r"(addr), "n"(OFF));
+__device__ __forceinline__ uint64_t lds_b64(uint32_t addr) {
+  uint64_t v;
+  asm("ld.shared.b64 %0, [%1+%2];" : "=l"(v) : "r"(addr), "n"(OFF));
+  return v;
 }
 
 // The two A-fragment registers of one weight block for quad lane j. `aligned` says the
@@ -146,157 +154,122 @@ __device__ __forceinline__ uint64_t pack2(float lo, float hi) {
   asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
   return r;
 }
-__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
-__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+__device__ __forceinline__ uint64_t pack2i(int lo, int hi) {
   uint64_t r;
-  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
   return r;
 }
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
 __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
   uint64_t r;
   asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
   return r;
 }
 
-// Everything one K block of a stage needs from shared memory, for one lane.
-template <int MT>
-struct BlockRegs {
-  uint32_t a0, a1, a2, a3;  // weight codes: rows g / g+8, low / high half of K
-  uint64_t ws;              // (scale of row g, scale of row g+8)
-  uint2 bq[MT];             // activation codes
-  uint64_t se[MT], so[MT];  // (s, s) of activation rows 2j and 2j+1
+// D(16x8, s32) = A(16x32, s8 row) * B(32x8, s8 col) + the bit pattern of 1.5 * 2^23 in every
+// element: read as f32 the result is 12582912 + dot, exactly (|dot| <= 32 * 128 * 127 < 2^22).
+__device__ __forceinline__ void mma_s8_biased(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(MAGIC_BITS));
+}
+
+// The weight side of one K block for one group of 16 columns: the MMA A fragment and, per
+// fragment row (column g / column g+8 of the group), the scale pair (s, s) and (-M s, -M s).
+struct WeightRegs {
+  uint32_t a0, a1, a2, a3;
+  uint64_t s0, s1, n0, n1;
 };
 
 // K-major: rows g read an even column (codes 2 bytes past a word boundary), rows g+8 the
 // odd column after it (aligned). NT: both rows read block KBL of their weight row, whose
 // codes are aligned when KBL is odd.
-template <int DT, bool NT, int MT, int KBL, int STEP, int AQ_STRIDE, int AS_STRIDE>
-__device__ __forceinline__ void load_block(BlockRegs<MT>& r, uint32_t w0, uint32_t w1, uint32_t b0, uint32_t b1,
-                                           const uint32_t (&aq)[MT], const uint32_t (&as)[MT]) {
+template <int DT, bool NT, int KBL, int STEP, int OFF>
+__device__ __forceinline__ void load_weights(WeightRegs& r, uint32_t w0, uint32_t w1, uint32_t b0, uint32_t b1) {
   constexpr bool AL0 = NT ? (KBL & 1) != 0 : false;
   constexpr bool AL1 = NT ? (KBL & 1) != 0 : true;
-  load_codes<DT, AL0, KBL * STEP>(w0, r.a0, r.a2);
-  load_codes<DT, AL1, KBL * STEP>(w1, r.a1, r.a3);
-  r.ws = pack2(lds_f16<KBL * STEP>(b0), lds_f16<KBL * STEP>(b1));
-#pragma unroll
-  for (int t = 0; t < MT; t++) {
-    r.bq[t] = lds_u64<KBL * AQ_STRIDE>(aq[t]);
-    lds_f32x4<KBL * AS_STRIDE>(as[t], r.se[t], r.so[t]);
-  }
+  load_codes<DT, AL0, KBL * STEP + OFF>(w0, r.a0, r.a2);
+  load_codes<DT, AL1, KBL * STEP + OFF>(w1, r.a1, r.a3);
+  const float s0 = lds_f16<KBL * STEP + OFF>(b0), s1 = lds_f16<KBL * STEP + OFF>(b1);
+  const float m0 = s0 * -MAGIC, m1 = s1 * -MAGIC;  // exact: an f16 value times 3 * 2^22
+  r.s0 = pack2(s0, s0);
+  r.s1 = pack2(s1, s1);
+  r.n0 = pack2(m0, m0);
+  r.n1 = pack2(m1, m1);
 }
 
-template <int MT, bool M1>
-__device__ __forceinline__ void compute_block(const BlockRegs<MT>& r, uint64_t (&acc)[MT][2]) {
+// One K block of a stage: every group of 8 activation rows against every group of 16 columns.
+// acc[t][c][0] = (column g of group c) x (activation rows t*8+2j, t*8+2j+1); [1]: column g+8.
+template <int DT, bool NT, int MT, int CG, int KBL, int STEP, int CGS, int AQ_STRIDE, int AS_STRIDE>
+__device__ __forceinline__ void block_step(uint32_t w0, uint32_t w1, uint32_t b0, uint32_t b1, uint32_t aq, uint32_t as,
+                                           uint64_t (&acc)[MT][CG][2]) {
+  WeightRegs w[CG];
+#pragma unroll
+  for (int c = 0; c < CG; c++) load_weights<DT, NT, KBL, STEP, 0>(w[c], w0 + c * CGS, w1 + c * CGS, b0 + c * CGS, b1 + c * CGS);
 #pragma unroll
   for (int t = 0; t < MT; t++) {
-    int d[4];
-    ptx::mma_s8(d, r.a0, r.a1, r.a2, r.a3, r.bq[t].x, r.bq[t].y);
-    // d[0], d[2]: rows g, g+8 against activation row 2j; d[1], d[3]: against row 2j+1.
-    acc[t][0] = fma2(mul2(pack2((float)d[0], (float)d[2]), r.ws), r.se[t], acc[t][0]);
-    if (!M1) acc[t][1] = fma2(mul2(pack2((float)d[1], (float)d[3]), r.ws), r.so[t], acc[t][1]);
+    // (MT > 1 implies at least 8 rows per K block, so row tile t starts 256 bytes / 8 scales further.)
+    const uint2 bq = lds_u64<KBL * AQ_STRIDE>(aq + t * 256);
+    const uint64_t sc = lds_b64<KBL * AS_STRIDE>(as + t * 32);
+#pragma unroll
+    for (int c = 0; c < CG; c++) {
+      int d[4];
+      mma_s8_biased(d, w[c].a0, w[c].a1, w[c].a2, w[c].a3, bq.x, bq.y);
+      acc[t][c][0] = fma2(fma2(pack2i(d[0], d[1]), w[c].s0, w[c].n0), sc, acc[t][c][0]);
+      acc[t][c][1] = fma2(fma2(pack2i(d[2], d[3]), w[c].s1, w[c].n1), sc, acc[t][c][1]);
+    }
   }
 }
 
 // CTA that owns unit u when G CTAs split U units as [c*U/G, (c+1)*U/G).
 __device__ __forceinline__ uint32_t unit_owner(uint64_t u, uint64_t U, uint64_t G) { return (uint32_t)(((u + 1) * G - 1) / U); }
 
-// One 32-block of activations -> the 8 words the MMA B fragments read (lane j finds its two
-// registers as the 8 bytes at 8j) and the block's scale, with the q4 nibble placement's 16x
-// folded in.
-//   q8: b0 = k 4j..4j+3, b1 = k 16+4j..16+4j+3            -> word 2j = w[j], word 2j+1 = w[4+j]
-//   q4: b0 = elements 8j+{0,2,4,6}, b1 = elements 8j+{1,3,5,7} (low / high nibbles of 4 code bytes)
+// Quantizes A once per launch into its image (act_image.cuh). Rows past m and blocks past
+// kblocks are written as zeros. One thread per (group, block, row).
 template <int DT>
-__device__ __forceinline__ float quantize_act_block(const float* __restrict__ src, bool vec4, uint32_t (&o)[8]) {
-  float x[QK];
-  if (vec4) {
-#pragma unroll
-    for (int i = 0; i < 8; i++) {
-      const float4 f = reinterpret_cast<const float4*>(src)[i];
-      x[4 * i] = f.x; x[4 * i + 1] = f.y; x[4 * i + 2] = f.z; x[4 * i + 3] = f.w;
-    }
-  } else {
-#pragma unroll
-    for (int i = 0; i < QK; i++) x[i] = src[i];
-  }
-  float am[8];
-#pragma unroll
-  for (int i = 0; i < 8; i++) am[i] = fmaxf(fmaxf(fabsf(x[4 * i]), fabsf(x[4 * i + 1])), fmaxf(fabsf(x[4 * i + 2]), fabsf(x[4 * i + 3])));
-  const float amax = fmaxf(fmaxf(fmaxf(am[0], am[1]), fmaxf(am[2], am[3])), fmaxf(fmaxf(am[4], am[5]), fmaxf(am[6], am[7])));
-  float scale, inv;
-  activation_block_scales(amax, &scale, &inv);
-  uint32_t w[8];
-#pragma unroll
-  for (int i = 0; i < 8; i++) {
-    const uint32_t q0 = (uint32_t)quantize_activation_with_inv(x[4 * i], inv) & 0xFF;
-    const uint32_t q1 = (uint32_t)quantize_activation_with_inv(x[4 * i + 1], inv) & 0xFF;
-    const uint32_t q2 = (uint32_t)quantize_activation_with_inv(x[4 * i + 2], inv) & 0xFF;
-    const uint32_t q3 = (uint32_t)quantize_activation_with_inv(x[4 * i + 3], inv) & 0xFF;
-    w[i] = (DT == AION_CUDA_DTYPE_Q8_0) ? (q0 | (q1 << 8) | (q2 << 16) | (q3 << 24))    // elements in order
-                                         : (q0 | (q2 << 8) | (q1 << 16) | (q3 << 24));   // (e0, e2 | e1, e3)
-  }
-#pragma unroll
-  for (int jj = 0; jj < 4; jj++) {
-    if (DT == AION_CUDA_DTYPE_Q8_0) {
-      o[2 * jj] = w[jj];
-      o[2 * jj + 1] = w[4 + jj];
-    } else {
-      o[2 * jj] = (w[2 * jj] & 0xFFFFu) | (w[2 * jj + 1] << 16);
-      o[2 * jj + 1] = (w[2 * jj] >> 16) | (w[2 * jj + 1] & 0xFFFF0000u);
-    }
-  }
-  const float fold = (DT == AION_CUDA_DTYPE_Q4_0) ? 0.0625f : 1.0f;  // undoes the 16x of the nibble placement (exact)
-  return scale * fold;
-}
-
-// Quantizes A once per launch into the image the GEMV CTAs copy into shared memory: for
-// every group of `mpa` rows, per K block `mpa` rows of 32 codes, then per K block `quads`
-// scale quads (s_even, s_even, s_odd, s_odd). Rows past m and blocks past kblocks are
-// written as zeros (a zero scale contributes nothing). One thread per (group, block, row).
-template <int DT>
-__global__ void gemv_act_image_kernel(const float* __restrict__ a, uint64_t lda, uint32_t m, uint32_t kblocks, uint32_t kb_pad,
-                                      uint32_t mpa, uint32_t quads, uint32_t groups, uint8_t* __restrict__ image,
-                                      uint32_t group_bytes, uint32_t a_vec4) {
-  // The GEMV that follows may start now: its weight stream does not depend on this kernel,
+__global__ void gemv_act_image_kernel(const float* __restrict__ a, uint64_t lda, uint32_t m, uint32_t kblocks, ActImageLayout L,
+                                      uint8_t* __restrict__ image, uint32_t a_vec4) {
+  // The matmul that follows may start now: its weight stream does not depend on this kernel,
   // and it waits for this kernel to finish before it copies the image. A comes from the
-  // previous kernel, and the image buffer may still be read by an earlier GEMV until then.
+  // previous kernel, and the image buffer may still be read by an earlier matmul until then.
   ptx::pdl_launch_dependents();
   ptx::pdl_wait();
-  const uint32_t items = groups * kb_pad * mpa;
+  const uint32_t items = L.groups * L.kb_pad * L.rows_per_group;
   const uint32_t item = blockIdx.x * blockDim.x + threadIdx.x;
   if (item >= items) return;
-  const uint32_t r = item % mpa, kb = (item / mpa) % kb_pad, g = item / (mpa * kb_pad);
-  const uint32_t row = g * mpa + r;
+  const uint32_t r = item % L.rows_per_group, kb = (item / L.rows_per_group) % L.kb_pad, g = item / (L.rows_per_group * L.kb_pad);
+  const uint32_t row = g * L.rows_per_group + r;
   uint32_t o[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   float sc = 0.0f;
   if (row < m && kb < kblocks) sc = quantize_act_block<DT>(a + (uint64_t)row * lda + (uint64_t)kb * QK, a_vec4 != 0, o);
-  uint8_t* base = image + (size_t)g * group_bytes;
-  uint4* dst = reinterpret_cast<uint4*>(base + ((size_t)kb * mpa + r) * 32);
+  uint4* dst = reinterpret_cast<uint4*>(act_image_codes(image, L, row, kb));
   dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
   dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
-  float* act_s = reinterpret_cast<float*>(base + (size_t)kb_pad * mpa * 32);
-  *reinterpret_cast<float2*>(act_s + ((size_t)kb * quads + (r >> 1)) * 4 + 2 * (r & 1)) = make_float2(sc, sc);
+  *act_image_scale(image, L, row, kb) = sc;
 }
 
-// DT: weight dtype; NT: weights are [n,k] row-major (else K-major); MT: 8-row activation
-// tiles (1 or 2); M1: exactly one activation row (skips the odd-row half of the epilogue).
-template <int DT, bool NT, int MT, bool M1, bool RG = false, bool PREQ = false>
+// DT: weight dtype; NT: weights are [n,k] row-major (else K-major); MT: groups of 8 activation
+// rows per CTA (1, 2, 4, 8); M1: exactly one activation row; RG: blockIdx.y picks a group of
+// 8 * MT rows; PREQ: the activation arrives as a pre-quantized image; CG: 16-column groups per warp.
+template <int DT, bool NT, int MT, bool M1, bool RG, bool PREQ, int CG>
 __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_in, const __grid_constant__ CUtensorMap tmap) {
-  using G = Geom<DT, NT>;
+  using G = Geom<DT, NT, CG>;
+  constexpr int TN = G::TN;
   constexpr int MPA = 8 * MT;  // activation rows of the accumulator tile
-  // More than 8 * MT rows of A: blockIdx.y picks a group of 8 * MT rows. Every group streams
-  // the same weights (the second and later groups find them in L2), with its own slice of
-  // the fix-up scratch.
-  // (RG, row groups, is a template parameter so that the usual kernel keeps reading its
-  // parameters from the constant bank instead of holding an adjusted copy in registers.)
+  // (RG is a template parameter so that the usual kernel keeps reading its parameters from
+  // the constant bank instead of holding an adjusted copy in registers.)
+  // With row groups the group index is the fastest-varying block index, so that the CTAs that
+  // stream the same weight range run next to one another and all but the first find it in L2.
+  const uint32_t cta = RG ? blockIdx.y : blockIdx.x, n_ctas = RG ? gridDim.y : gridDim.x, row_group = RG ? blockIdx.x : 0;
   GemvParams p_rows;
   if (RG) {
     p_rows = p_in;
-    const uint32_t r0 = blockIdx.y * MPA;
+    const uint32_t r0 = row_group * MPA;
     p_rows.a += (uint64_t)r0 * p_in.lda;
     p_rows.c += (uint64_t)r0 * p_in.ldc;
     p_rows.m = min((uint32_t)MPA, p_in.m - r0);
-    p_rows.partials += (size_t)blockIdx.y * gridDim.x * 2 * TN * MPA;
-    p_rows.tickets += (size_t)blockIdx.y * p_in.tiles * CONSUMER_WARPS;
+    p_rows.partials += (size_t)row_group * n_ctas * 2 * TN * MPA;
+    p_rows.tickets += (size_t)row_group * p_in.tiles * CONSUMER_WARPS;
   }
   const GemvParams& p = RG ? p_rows : p_in;
   constexpr uint32_t MP2 = M1 ? 2 : 8 * MT;  // activation rows held in shared memory
@@ -306,17 +279,24 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_
   const int warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, j = lane & 3;
 
-  const uint64_t U = p.units, NG = gridDim.x;
-  const uint64_t u_begin = U * blockIdx.x / NG, u_end = U * (blockIdx.x + 1) / NG;
+  const uint64_t U = p.units, NG = n_ctas;
   const uint32_t Sg = p.stages_per_tile;
+  uint64_t u_begin, u_end;
+  if (p.whole_tiles) {
+    u_begin = ((uint64_t)p.tiles * cta / NG) * Sg;
+    u_end = ((uint64_t)p.tiles * (cta + 1) / NG) * Sg;
+  } else {
+    u_begin = U * cta / NG;
+    u_end = U * (cta + 1) / NG;
+  }
 
   const uint32_t bar_full = smem_base + G::OFF_BARS;
   const uint32_t bar_empty = bar_full + NS * 8;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + G::OFF_BARS + 2 * NS * 8);
   const uint32_t kb_pad = p.stages_per_tile * KBT;  // K blocks rounded up to whole stages
   uint8_t* act_q = smem + G::OFF_ACT;
-  constexpr uint32_t QUADS = M1 ? 1 : 4 * MT;  // scale quads per K block
-  float* act_s = reinterpret_cast<float*>(act_q + (size_t)kb_pad * MP2 * 32);  // [kb][QUADS]
+  float* act_s = reinterpret_cast<float*>(act_q + (size_t)kb_pad * MP2 * 32);  // [kb][MP2] (when the CTA quantizes A itself)
+  constexpr uint32_t AQ_SLICE = KBT * MP2 * 32, AS_SLICE = KBT * MP2 * 4;  // one stage's codes / scales of the image
 
   if (warp == CONSUMER_WARPS) {
     // ---------------- producer: one tiled TMA load per stage ----------------
@@ -335,16 +315,15 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_
     const uint64_t n_units = u_end - u_begin;
     uint64_t issued = 0;
     uint32_t tile = (uint32_t)(u_begin / Sg), s = (uint32_t)(u_begin - (uint64_t)tile * Sg);
-    // PREQ: every stage also brings its 8 K blocks of the pre-quantized activation image (codes,
-    // then scale quads) into the stage's slot of the activation ring. The image comes from the
-    // previous kernel, so those copies wait for it; the weight copies of the first NS stages
-    // do not, and start at once.
-    constexpr uint32_t AQ_SLICE = KBT * (M1 ? 2 : 8 * MT) * 32, AS_SLICE = KBT * (M1 ? 16 : MT * 64);
-    const uint8_t* image = PREQ ? p.act_image + (size_t)(RG ? blockIdx.y : 0) * p.act_image_bytes : nullptr;
+    // PREQ: every stage also brings its 8 K blocks of the activation image (codes, then scales)
+    // into the stage's slot of the activation ring. The image comes from the previous kernel,
+    // so those copies wait for it; the weight copies of the first NS stages do not, and start
+    // at once.
+    const uint8_t* image = PREQ ? p.act_image + (size_t)row_group * p.act_image_bytes : nullptr;
     auto issue_acts = [&](uint32_t slot_, uint32_t s_) {
       const uint32_t dst = smem_base + G::OFF_ACT + slot_ * (AQ_SLICE + AS_SLICE), full = bar_full + 8 * slot_;
       ptx::bulk_g2s(dst, image + (size_t)s_ * AQ_SLICE, AQ_SLICE, full);
-      ptx::bulk_g2s(dst + AQ_SLICE, image + (size_t)kb_pad * (AQ_SLICE / KBT) + (size_t)s_ * AS_SLICE, AS_SLICE, full);
+      ptx::bulk_g2s(dst + AQ_SLICE, image + (size_t)kb_pad * (MP2 * 32) + (size_t)s_ * AS_SLICE, AS_SLICE, full);
     };
     uint32_t pend_s[NS];
     uint32_t npend = 0;
@@ -374,7 +353,7 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_
         // Rows or columns past the tensor arrive as zeros (a zero scale), and the whole
         // box counts towards the barrier.
         ptx::mbar_arrive_expect_tx(full, G::STAGE_BYTES + (PREQ ? AQ_SLICE + AS_SLICE : 0));
-        if (!NT && DT == AION_CUDA_DTYPE_Q4_0) ptx::tma_load_2d(stage, &tmap, (int32_t)(tile * (TN * G::BB / 8)), (int32_t)(s * KBT), full);
+        if (!NT && DT == AION_CUDA_DTYPE_Q4_0 && CG == 1) ptx::tma_load_2d(stage, &tmap, (int32_t)(tile * (TN * G::BB / 8)), (int32_t)(s * KBT), full);
         else if (!NT) ptx::tma_load_3d(stage, &tmap, 0, (int32_t)(tile * (TN / 8)), (int32_t)(s * KBT), full);
         else ptx::tma_load_2d(stage, &tmap, (int32_t)(s * KBT * Q8_BYTES / 8), (int32_t)(tile * TN), full);
         if (PREQ) {
@@ -408,9 +387,9 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_
   // Scales start at zero: a pad row (m odd) and rows never written must contribute
   // nothing, whatever their code bytes hold (an integer dot is always finite).
   if (!PREQ) {
-    float4* z = reinterpret_cast<float4*>(act_s);
-    const uint32_t quads = kb_pad * QUADS;
-    for (uint32_t i = tid; i < quads; i += CONSUMER_THREADS) z[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    float* z = act_s;
+    const uint32_t count = kb_pad * MP2;
+    for (uint32_t i = tid; i < count; i += CONSUMER_THREADS) z[i] = 0.0f;
   }
   __syncthreads();  // CTA barrier #1: the producer has initialised the mbarriers
   // The next kernel in the stream may begin: its weight stream does not depend on us.
@@ -418,9 +397,7 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_
   // Everything below reads what the previous kernel wrote (A, and C when beta != 0).
   ptx::pdl_wait();
 
-  if (PREQ) {
-    // A was quantized once for all CTAs; its blocks arrive with the weight stages.
-  } else {
+  if (!PREQ) {
     // Quantize all of A, one thread per 32-block (no cross-lane traffic, 32 independent
     // elements of instruction-level parallelism): the block's 128 bytes are one cache line.
     const uint32_t items = p.m * p.kblocks;
@@ -431,15 +408,13 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_
       uint4* dst = reinterpret_cast<uint4*>(act_q + ((size_t)kb * MP2 + r) * 32);
       dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
       dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
-      float* sq = act_s + ((size_t)kb * QUADS + (r >> 1)) * 4 + 2 * (r & 1);
-      *reinterpret_cast<float2*>(sq) = make_float2(sc, sc);
+      act_s[(size_t)kb * MP2 + r] = sc;
     }
   }
   asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_THREADS) : "memory");
 
   // Per-lane constants: where this lane's two weight blocks (rows g and g+8 of the
-  // fragment) sit inside a stage, and where its activation fragments start. Lanes whose
-  // activation row does not exist read a block of zeros instead (no predicates in the loop).
+  // fragment) sit inside a stage, and where its activation fragments start.
   uint32_t off0, off1;
   if (!NT) {
     off0 = (2 * warp + 8 * g) * G::BB;  // an even column: its codes start 2 bytes past a word boundary
@@ -450,25 +425,21 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_
   }
   const int col0 = NT ? 16 * warp + g : 2 * warp + 8 * g;
   const int col1 = NT ? col0 + 8 : col0 + 1;
-  // Bytes per K block: MP2 rows of codes; 4*MT scale quads (absent rows keep a zero
-  // scale, so whatever codes a lane of an absent row reads contribute nothing: such a
-  // lane simply reads an existing row).
-  // With a single activation row every lane reads the one scale quad: the outputs of the
-  // lanes that stand for absent rows are finite and never stored.
-  constexpr uint32_t AQ_STRIDE = MP2 * 32, AS_STRIDE = M1 ? 16 : MT * 64;
+  // Bytes per K block: MP2 rows of codes, MP2 scales. A lane supplies the codes of activation
+  // row t*8+g (absent rows are zero codes with a zero scale) and applies the scales of rows
+  // t*8+2j and t*8+2j+1. With a single activation row every lane reads row g % 2 and scale
+  // pair 0: the outputs of lanes that stand for absent rows are finite and never stored.
+  constexpr uint32_t AQ_STRIDE = MP2 * 32, AS_STRIDE = MP2 * 4;
   const uint32_t act_q_addr = smem_base + G::OFF_ACT;
   const uint32_t act_s_addr = act_q_addr + (PREQ ? KBT : kb_pad) * AQ_STRIDE;  // PREQ: inside a ring slot
-  uint32_t aq_lane[MT], as_lane[MT];
-#pragma unroll
-  for (int t = 0; t < MT; t++) {
-    aq_lane[t] = act_q_addr + ((t * 8 + g) % MP2) * 32 + 8 * j;
-    as_lane[t] = act_s_addr + (M1 ? 0 : (t * 4 + j) * 16);
-  }
+  const uint32_t aq_lane = act_q_addr + (g % MP2) * 32 + 8 * j;
+  const uint32_t as_lane = act_s_addr + (M1 ? 0 : j * 8);
 
-  // acc[t][0] = (row g, row g+8) x activation row t*8+2j ; acc[t][1] = the same x row t*8+2j+1.
-  uint64_t acc[MT][2];
+  uint64_t acc[MT][CG][2];
 #pragma unroll
-  for (int t = 0; t < MT; t++) acc[t][0] = acc[t][1] = 0ull;
+  for (int t = 0; t < MT; t++)
+#pragma unroll
+    for (int c = 0; c < CG; c++) acc[t][c][0] = acc[t][c][1] = 0ull;
 
   const uint32_t first_tile = (uint32_t)(u_begin / Sg);
   uint32_t tile = first_tile, s = (uint32_t)(u_begin - (uint64_t)first_tile * Sg);
@@ -488,31 +459,15 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_
       // activations, so all 8 blocks of a stage are always processed.
       uint32_t b0 = smem_base + slot * G::STAGE_BYTES + off0, b1 = smem_base + slot * G::STAGE_BYTES + off1;  // block starts
       uint32_t w0 = b0 + 4 * j, w1 = b1 + 4 * j;  // this lane's code words
-      uint32_t aq[MT], as[MT];
-#pragma unroll
-      for (int t = 0; t < MT; t++) {
-        aq[t] = aq_lane[t] + (PREQ ? slot * (KBT * (AQ_STRIDE + AS_STRIDE)) : s * (KBT * AQ_STRIDE));
-        as[t] = as_lane[t] + (PREQ ? slot * (KBT * (AQ_STRIDE + AS_STRIDE)) : s * (KBT * AS_STRIDE));
-      }
+      uint32_t aq = aq_lane + (PREQ ? slot * (KBT * (AQ_STRIDE + AS_STRIDE)) : s * (KBT * AQ_STRIDE));
+      uint32_t as = as_lane + (PREQ ? slot * (KBT * (AQ_STRIDE + AS_STRIDE)) : s * (KBT * AS_STRIDE));
       // Ties every load below to this point: they cannot move above the wait.
-      asm volatile("" : "+r"(w0), "+r"(w1), "+r"(b0), "+r"(b1)::"memory");
-#pragma unroll
-      for (int t = 0; t < MT; t++) asm volatile("" : "+r"(aq[t]), "+r"(as[t]));
+      asm volatile("" : "+r"(w0), "+r"(w1), "+r"(b0), "+r"(b1), "+r"(aq), "+r"(as)::"memory");
       constexpr int STEP = NT ? Q8_BYTES : G::KM_PITCH;
-      // Loads of four K blocks are issued before their arithmetic (and the next four
-      // before the first four finish), so shared-memory and MMA latencies overlap.
-      BlockRegs<MT> r[4];
-#define AION_LOAD(K, R) load_block<DT, NT, MT, K, STEP, (int)AQ_STRIDE, (int)AS_STRIDE>(r[R], w0, w1, b0, b1, aq, as)
-      AION_LOAD(0, 0); AION_LOAD(1, 1); AION_LOAD(2, 2); AION_LOAD(3, 3);
-      compute_block<MT, M1>(r[0], acc); AION_LOAD(4, 0);
-      compute_block<MT, M1>(r[1], acc); AION_LOAD(5, 1);
-      compute_block<MT, M1>(r[2], acc); AION_LOAD(6, 2);
-      compute_block<MT, M1>(r[3], acc); AION_LOAD(7, 3);
-      compute_block<MT, M1>(r[0], acc);
-      compute_block<MT, M1>(r[1], acc);
-      compute_block<MT, M1>(r[2], acc);
-      compute_block<MT, M1>(r[3], acc);
-#undef AION_LOAD
+#define AION_BLOCK(K) block_step<DT, NT, MT, CG, K, STEP, G::CG_STRIDE, (int)AQ_STRIDE, (int)AS_STRIDE>(w0, w1, b0, b1, aq, as, acc)
+      AION_BLOCK(0); AION_BLOCK(1); AION_BLOCK(2); AION_BLOCK(3);
+      AION_BLOCK(4); AION_BLOCK(5); AION_BLOCK(6); AION_BLOCK(7);
+#undef AION_BLOCK
       static_assert(KBT == 8, "eight K blocks per stage are spelled out above");
     }
     __syncwarp();
@@ -523,23 +478,28 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_
       const uint64_t tile_u0 = (uint64_t)tile * Sg;
       const bool whole = (uu + 1 - tile_u0 == Sg) && (tile_u0 >= u_begin);
       const uint32_t n0 = tile * TN;
-      float v[MT][4];  // [t][0..3] = (row g, m 2j), (row g+8, m 2j), (row g, m 2j+1), (row g+8, m 2j+1)
+      // v[t][c][0..3] = (col0, row 2j), (col0, row 2j+1), (col1, row 2j), (col1, row 2j+1)
+      float v[MT][CG][4];
 #pragma unroll
-      for (int t = 0; t < MT; t++) {
-        unpack2(acc[t][0], v[t][0], v[t][1]);
-        unpack2(acc[t][1], v[t][2], v[t][3]);
-        acc[t][0] = acc[t][1] = 0ull;
-      }
+      for (int t = 0; t < MT; t++)
+#pragma unroll
+        for (int c = 0; c < CG; c++) {
+          unpack2(acc[t][c][0], v[t][c][0], v[t][c][1]);
+          unpack2(acc[t][c][1], v[t][c][2], v[t][c][3]);
+          acc[t][c][0] = acc[t][c][1] = 0ull;
+        }
       bool store = whole;
       if (!whole) {
         const uint32_t c_first = unit_owner(tile_u0, U, NG), c_last = unit_owner(tile_u0 + Sg - 1, U, NG);
         const uint32_t nparts = c_last - c_first + 1;
-        float* mine = p.partials + ((size_t)blockIdx.x * 2 + (tile == first_tile ? 0 : 1)) * (TN * MPA);
+        float* mine = p.partials + ((size_t)cta * 2 + (tile == first_tile ? 0 : 1)) * (TN * MPA);
 #pragma unroll
-        for (int t = 0; t < MT; t++) {
-          *reinterpret_cast<float2*>(mine + col0 * MPA + t * 8 + 2 * j) = make_float2(v[t][0], v[t][2]);
-          *reinterpret_cast<float2*>(mine + col1 * MPA + t * 8 + 2 * j) = make_float2(v[t][1], v[t][3]);
-        }
+        for (int t = 0; t < MT; t++)
+#pragma unroll
+          for (int c = 0; c < CG; c++) {
+            *reinterpret_cast<float2*>(mine + (col0 + 64 * c) * MPA + t * 8 + 2 * j) = make_float2(v[t][c][0], v[t][c][1]);
+            *reinterpret_cast<float2*>(mine + (col1 + 64 * c) * MPA + t * 8 + 2 * j) = make_float2(v[t][c][2], v[t][c][3]);
+          }
         // The warp's stores are ordered before lane 0's release by the warp barrier; the
         // acquire side orders the last arriver's loads after every earlier release.
         __syncwarp();
@@ -555,18 +515,22 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_
         if (last) {
           // The last part to arrive adds all of them in CTA order.
 #pragma unroll
-          for (int t = 0; t < MT; t++) v[t][0] = v[t][1] = v[t][2] = v[t][3] = 0.0f;
+          for (int t = 0; t < MT; t++)
+#pragma unroll
+            for (int c = 0; c < CG; c++) v[t][c][0] = v[t][c][1] = v[t][c][2] = v[t][c][3] = 0.0f;
           for (uint32_t part = 0; part < nparts; part++) {
             const uint32_t cc = c_first + part;
             const uint32_t cc_first_tile = (uint32_t)((U * cc / NG) / Sg);
             const float* src = p.partials + ((size_t)cc * 2 + (tile == cc_first_tile ? 0 : 1)) * (TN * MPA);
 #pragma unroll
-            for (int t = 0; t < MT; t++) {
-              const float2 x0 = __ldcg(reinterpret_cast<const float2*>(src + col0 * MPA + t * 8 + 2 * j));
-              const float2 x1 = __ldcg(reinterpret_cast<const float2*>(src + col1 * MPA + t * 8 + 2 * j));
-              v[t][0] += x0.x; v[t][2] += x0.y;
-              v[t][1] += x1.x; v[t][3] += x1.y;
-            }
+            for (int t = 0; t < MT; t++)
+#pragma unroll
+              for (int c = 0; c < CG; c++) {
+                const float2 x0 = __ldcg(reinterpret_cast<const float2*>(src + (col0 + 64 * c) * MPA + t * 8 + 2 * j));
+                const float2 x1 = __ldcg(reinterpret_cast<const float2*>(src + (col1 + 64 * c) * MPA + t * 8 + 2 * j));
+                v[t][c][0] += x0.x; v[t][c][1] += x0.y;
+                v[t][c][2] += x1.x; v[t][c][3] += x1.y;
+              }
           }
           store = true;
         }
@@ -575,14 +539,22 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_
 #pragma unroll
         for (int t = 0; t < MT; t++)
 #pragma unroll
-          for (int e = 0; e < 4; e++) {
-            const uint32_t mrow = t * 8 + 2 * j + (e >> 1);
-            const uint32_t col = n0 + ((e & 1) ? col1 : col0);
-            if (mrow < p.m && col < p.n) {
-              float* cp = p.c + (uint64_t)mrow * p.ldc + col;
-              *cp = (p.beta == 0.0f) ? p.alpha * v[t][e] : p.alpha * v[t][e] + p.beta * *cp;
+          for (int c = 0; c < CG; c++)
+#pragma unroll
+            for (int rr = 0; rr < 2; rr++) {
+              const uint32_t mrow = t * 8 + 2 * j + rr;
+              if (mrow >= p.m) continue;
+              const uint32_t ca = n0 + col0 + 64 * c, cb = n0 + col1 + 64 * c;
+              float* row = p.c + (uint64_t)mrow * p.ldc;
+              const float va = v[t][c][rr], vb = v[t][c][2 + rr];
+              if (!NT && p.c_vec2 && p.beta == 0.0f && cb < p.n) {
+                // K-major tiles: the lane's two columns are neighbours, the first one even.
+                *reinterpret_cast<float2*>(row + ca) = make_float2(p.alpha * va, p.alpha * vb);
+              } else {
+                if (ca < p.n) row[ca] = (p.beta == 0.0f) ? p.alpha * va : p.alpha * va + p.beta * row[ca];
+                if (cb < p.n) row[cb] = (p.beta == 0.0f) ? p.alpha * vb : p.alpha * vb + p.beta * row[cb];
+              }
             }
-          }
       }
     }
     if (++s == Sg) {
@@ -592,29 +564,85 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_
   }
 }
 
-template <int DT, bool NT, int MT, bool M1, bool RG = false, bool PREQ = false>
-int32_t launch(AionCudaDevice* dev, GemvParams p, const uint8_t* b, uint64_t ldb) {
-  using G = Geom<DT, NT>;
-  auto kernel = gemv_q_mma_kernel<DT, NT, MT, M1, RG, PREQ>;
-  constexpr uint32_t MP2 = M1 ? 2 : 8 * MT;
-  const size_t smem = G::OFF_ACT + (PREQ ? (size_t)NS * act_bytes(KBT, MP2, MT) : act_bytes(p.stages_per_tile * KBT, MP2, MT));
-  // Kernel attributes and occupancy depend on the device and the dynamic size only.
-  static size_t configured_smem[16] = {};
-  static size_t occ_smem[16] = {};
-  static int occ_blocks[16] = {};
-  const int di = dev->ordinal & 15;
-  if (smem > configured_smem[di]) {
+// Per device and kernel instantiation: the largest dynamic shared-memory size the kernel has
+// been allowed so far (the attribute is only ever raised) and the occupancy found for the
+// last size asked. Shared by every launch path of the instantiation and safe to call from
+// several host threads.
+struct KernelSetup {
+  std::mutex mu;
+  size_t configured_smem[64] = {};
+  size_t occ_smem[64] = {};
+  int occ_blocks[64] = {};
+};
+
+template <typename Kernel>
+int32_t kernel_occupancy(KernelSetup& ks, Kernel kernel, AionCudaDevice* dev, size_t smem, int* blocks_per_sm) {
+  if (dev->ordinal < 0 || dev->ordinal >= 64) return fail(AION_CUDA_UNSUPPORTED, "gemv: device ordinal %d is beyond the 64 this library keeps state for", dev->ordinal);
+  std::lock_guard<std::mutex> lock(ks.mu);
+  const int di = dev->ordinal;
+  if (smem > ks.configured_smem[di]) {
     AION_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured_smem[di] = smem;
+    ks.configured_smem[di] = smem;
   }
-  if (occ_smem[di] != smem) {
+  if (ks.occ_smem[di] != smem) {
     int nb = 0;
     AION_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, kernel, THREADS, smem));
     if (nb < 1) return fail(AION_CUDA_INTERNAL_ERROR, "gemv: kernel does not fit an SM with %llu bytes of shared memory", (unsigned long long)smem);
-    occ_blocks[di] = nb;
-    occ_smem[di] = smem;
+    ks.occ_blocks[di] = nb;
+    ks.occ_smem[di] = smem;
   }
-  uint64_t grid = (uint64_t)occ_blocks[di] * dev->sm_count;
+  *blocks_per_sm = ks.occ_blocks[di];
+  return AION_CUDA_OK;
+}
+
+template <int DT, bool NT, int MT, bool M1, bool RG, bool PREQ, int CG>
+KernelSetup& setup_of() {
+  static KernelSetup ks;
+  return ks;
+}
+
+template <int DT, bool NT, int CG>
+int32_t encode_weight_map(const uint8_t* b, uint64_t ldb, uint32_t n, uint32_t kblocks, AionCudaDevice* cache_dev, CUtensorMap* local,
+                          const CUtensorMap** out) {
+  using G = Geom<DT, NT, CG>;
+  uint64_t dims[3], strides[2];
+  uint32_t box[3], rank;
+  if (!NT && DT == AION_CUDA_DTYPE_Q4_0 && CG == 1) {
+    // [kblocks][n*18 bytes]: one box = 8 block rows x 64 blocks (1152 bytes, within the 2048-byte box row).
+    rank = 2;
+    dims[0] = (uint64_t)n * G::BB, dims[1] = kblocks;
+    strides[0] = ldb * G::BB;
+    box[0] = (uint32_t)G::TN * G::BB, box[1] = KBT;
+  } else if (!NT) {
+    // A row of TN blocks can exceed what a box row holds (2048 bytes), so the row is viewed as
+    // [n/8 groups][8 blocks]: one box = 8 block rows x TN/8 groups.
+    rank = 3;
+    dims[0] = 8ull * G::BB, dims[1] = n / 8, dims[2] = kblocks;
+    strides[0] = 8ull * G::BB, strides[1] = ldb * G::BB;
+    box[0] = 8u * G::BB, box[1] = G::TN / 8, box[2] = KBT;
+  } else {
+    // [n rows][kblocks*34 bytes]: one box = TN rows x 8 blocks.
+    rank = 2;
+    dims[0] = (uint64_t)kblocks * Q8_BYTES, dims[1] = n;
+    strides[0] = ldb * Q8_BYTES;
+    box[0] = NT_ROW_PITCH, box[1] = G::TN;
+  }
+  if (cache_dev) return tensor_map_bytes(cache_dev, b, rank, dims, strides, box, out);
+  if (int32_t st = tensor_map_encode(b, rank, dims, strides, box, local)) return st;
+  *out = local;
+  return AION_CUDA_OK;
+}
+
+template <int DT, bool NT, int MT, bool M1, bool RG, bool PREQ, int CG>
+int32_t launch(AionCudaDevice* dev, GemvParams p, const uint8_t* b, uint64_t ldb, const uint8_t* given_image) {
+  using G = Geom<DT, NT, CG>;
+  constexpr int TN = G::TN;
+  auto kernel = gemv_q_mma_kernel<DT, NT, MT, M1, RG, PREQ, CG>;
+  constexpr uint32_t MP2 = M1 ? 2 : 8 * MT;
+  const size_t smem = G::OFF_ACT + (PREQ ? (size_t)NS * act_bytes(KBT, MP2) : act_bytes(p.stages_per_tile * KBT, MP2));
+  int per_sm = 0;
+  if (int32_t st = kernel_occupancy(setup_of<DT, NT, MT, M1, RG, PREQ, CG>(), kernel, dev, smem, &per_sm)) return st;
+  uint64_t grid = (uint64_t)per_sm * dev->sm_count;
   if (dev->gemv_split_override) grid = (uint64_t)dev->gemv_split_override * dev->sm_count;  // CTAs per SM, tuning only
   if (grid > p.units) grid = p.units;
   // Small problems: fewer, fuller CTAs — about eight stages each, but never fewer than one
@@ -627,10 +655,8 @@ int32_t launch(AionCudaDevice* dev, GemvParams p, const uint8_t* b, uint64_t ldb
     if (want < sms) want = sms;
     if (grid > want) grid = want;
     if (grid > p.units) grid = p.units;
-    // Nearly one tile per CTA: give every CTA exactly one whole tile, so that no tile is shared
-    // and the partial-sum fix-up (two more L2 round trips at the end of a short kernel) is skipped.
-    // Only while independent steps are being recorded into parallel lanes: there other launches
-    // fill the idle SMs, whereas a lone launch on a critical path is shortest with every SM busy.
+    // Nearly one tile per CTA while independent steps are being recorded into parallel lanes:
+    // give every CTA exactly one whole tile (other launches fill the idle SMs).
     bool overlapped = false;
     if (dev->recording) {
       overlapped = dev->cur_lane != 0;
@@ -638,64 +664,56 @@ int32_t launch(AionCudaDevice* dev, GemvParams p, const uint8_t* b, uint64_t ldb
     }
     if (overlapped && (uint64_t)p.tiles <= grid && (uint64_t)p.tiles * 5 >= grid * 4) grid = p.tiles;
   }
+  // At least as many tiles as CTAs: hand out whole tiles, so that no tile is shared and the
+  // partial-sum fix-up (two more L2 round trips at the end of a short kernel) is skipped —
+  // unless rounding to tiles would leave the busiest CTA more than a fifth above the average.
+  p.whole_tiles = 0;
+  if ((uint64_t)p.tiles >= grid) {
+    const uint64_t most = ceil_div((uint64_t)p.tiles, grid);
+    if (most * grid * 5 <= (uint64_t)p.tiles * 6) p.whole_tiles = 1;
+  }
 
   // Scratch for tiles shared by several CTAs: two partial slots per CTA, one ticket per (tile, warp),
   // times the groups of 8 * MT rows.
   constexpr int MPA = 8 * MT;
   const uint64_t groups = RG ? ceil_div((uint64_t)p.m, (uint64_t)MPA) : 1;
-  if (groups > 65535) return fail(AION_CUDA_UNSUPPORTED, "gemv: too many rows for one launch");
+  if (groups > 0x7FFFFFFFull || grid > 65535) return fail(AION_CUDA_UNSUPPORTED, "gemv: too many rows for one launch");
   if (int32_t st = dev->reserve_gemv_fixup((size_t)groups * grid * 2 * TN * MPA * sizeof(float), (size_t)groups * p.tiles * CONSUMER_WARPS)) return st;
   p.partials = dev->lane_gemv_partials();
   p.tickets = dev->lane_gemv_tickets();
 
+  static const bool no_pdl_main = std::getenv("AION_CUDA_NO_PDL_MAIN") != nullptr;  // tuning only
   if (PREQ) {
-    // Quantize A once, into lane scratch, in the layout the CTAs copy into shared memory.
-    const uint32_t kb_pad = p.stages_per_tile * KBT;
-    const size_t image_bytes = act_bytes(kb_pad, MP2, MT);
-    if (int32_t st = dev->reserve_scratch(groups * image_bytes)) return st;
-    uint8_t* image = static_cast<uint8_t*>(dev->lane_scratch());
-    const uint32_t items = (uint32_t)(groups * kb_pad * MP2);
-    cudaLaunchConfig_t icfg{};
-    icfg.gridDim = dim3((items + 127) / 128);
-    icfg.blockDim = dim3(128);
-    icfg.stream = dev->stream;
-    cudaLaunchAttribute iattrs[1];
-    iattrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    iattrs[0].val.programmaticStreamSerializationAllowed = 1;
-    icfg.attrs = iattrs;
-    static const bool no_pdl_image = std::getenv("AION_CUDA_NO_PDL_MAIN") != nullptr;  // tuning only
-    icfg.numAttrs = no_pdl_image ? 0 : 1;
-    AION_CUDA_TRY(cudaLaunchKernelEx(&icfg, gemv_act_image_kernel<DT>, p.a, p.lda, p.m, p.kblocks, kb_pad, (uint32_t)MP2, (uint32_t)(M1 ? 1 : 4 * MT),
-                                     (uint32_t)groups, image, (uint32_t)image_bytes, p.a_vec4));
-    p.act_image = image;
-    p.act_image_bytes = (uint32_t)image_bytes;
+    const ActImageLayout L = act_image_layout(p.m, p.kblocks);
+    if (L.rows_per_group != MP2 || L.groups != groups || L.kb_pad != p.stages_per_tile * KBT)
+      return fail(AION_CUDA_INTERNAL_ERROR, "gemv: activation image layout does not match the kernel chosen");
+    if (given_image) {
+      p.act_image = given_image;
+    } else {
+      // Quantize A once, into lane scratch, in the layout the CTAs copy into shared memory.
+      if (int32_t st = dev->reserve_scratch(act_image_total_bytes(L))) return st;
+      uint8_t* image = static_cast<uint8_t*>(dev->lane_scratch());
+      const uint32_t items = L.groups * L.kb_pad * L.rows_per_group;
+      cudaLaunchConfig_t icfg{};
+      icfg.gridDim = dim3((items + 127) / 128);
+      icfg.blockDim = dim3(128);
+      icfg.stream = dev->stream;
+      cudaLaunchAttribute iattrs[1];
+      iattrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      iattrs[0].val.programmaticStreamSerializationAllowed = 1;
+      icfg.attrs = iattrs;
+      icfg.numAttrs = no_pdl_main ? 0 : 1;
+      AION_CUDA_TRY(cudaLaunchKernelEx(&icfg, gemv_act_image_kernel<DT>, p.a, p.lda, p.m, p.kblocks, L, image, p.a_vec4));
+      p.act_image = image;
+    }
+    p.act_image_bytes = L.group_bytes;
   }
 
-  // The weight tensor as bytes in 8-byte elements.
   const CUtensorMap* tm = nullptr;
-  if (!NT && DT == AION_CUDA_DTYPE_Q4_0) {
-    // [kblocks][n*18 bytes]: one box = 8 block rows x 64 blocks (1152 bytes, within the 2048-byte box row).
-    const uint64_t dims[2] = {(uint64_t)p.n * G::BB, p.kblocks};
-    const uint64_t strides[1] = {ldb * G::BB};
-    const uint32_t box[2] = {(uint32_t)TN * G::BB, KBT};
-    if (int32_t st = tensor_map_bytes(dev, b, 2, dims, strides, box, &tm)) return st;
-  } else if (!NT) {
-    // q8: 64 blocks side by side are 2176 bytes, more than a box row holds, so the row is
-    // viewed as [n/8 groups][8 blocks]: one box = 8 block rows x 8 groups = 64 columns.
-    const uint64_t dims[3] = {8ull * G::BB, p.n / 8, p.kblocks};
-    const uint64_t strides[2] = {8ull * G::BB, ldb * G::BB};
-    const uint32_t box[3] = {8u * G::BB, TN / 8, KBT};
-    if (int32_t st = tensor_map_bytes(dev, b, 3, dims, strides, box, &tm)) return st;
-  } else {
-    // [n rows][kblocks*34 bytes]: one box = 64 rows x 8 blocks.
-    const uint64_t dims[2] = {(uint64_t)p.kblocks * Q8_BYTES, p.n};
-    const uint64_t strides[1] = {ldb * Q8_BYTES};
-    const uint32_t box[2] = {NT_ROW_PITCH, TN};
-    if (int32_t st = tensor_map_bytes(dev, b, 2, dims, strides, box, &tm)) return st;
-  }
+  if (int32_t st = encode_weight_map<DT, NT, CG>(b, ldb, p.n, p.kblocks, dev, nullptr, &tm)) return st;
 
   cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3((unsigned)grid, (unsigned)groups);
+  cfg.gridDim = RG ? dim3((unsigned)groups, (unsigned)grid) : dim3((unsigned)grid);
   cfg.blockDim = dim3(THREADS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = dev->stream;
@@ -703,28 +721,30 @@ int32_t launch(AionCudaDevice* dev, GemvParams p, const uint8_t* b, uint64_t ldb
   attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attrs[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attrs;
-  static const bool no_pdl_main = std::getenv("AION_CUDA_NO_PDL_MAIN") != nullptr;  // tuning only
   cfg.numAttrs = no_pdl_main ? 0 : 1;
   AION_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, p, *tm));
   return AION_CUDA_OK;
 }
 
 template <int DT, bool NT>
-int32_t launch_m(AionCudaDevice* dev, const GemvParams& p, const uint8_t* b, uint64_t ldb) {
-  // m >= 2: A is quantized once by a small kernel instead of by every CTA.
-  // (m = 1 quantizes its one row inside the kernel unless K is deep: past about 3000 the small
-  // kernel is cheaper than 148 CTAs each quantizing the whole row.)
-  if (p.m == 1) return p.kblocks > 96 ? launch<DT, NT, 1, true, false, true>(dev, p, b, ldb) : launch<DT, NT, 1, true>(dev, p, b, ldb);
-  if (p.m <= 8) return launch<DT, NT, 1, false, false, true>(dev, p, b, ldb);
-  if (p.m <= 16) return launch<DT, NT, 2, false, false, true>(dev, p, b, ldb);
-  return launch<DT, NT, 2, false, true, true>(dev, p, b, ldb);  // groups of 16 rows
+int32_t launch_m(AionCudaDevice* dev, const GemvParams& p, const uint8_t* b, uint64_t ldb, const uint8_t* image) {
+  // m >= 2: A is quantized once by a small kernel (or by the kernel that produced A) instead of
+  // by every CTA. m = 1 quantizes its one row inside the kernel unless K is deep: past about
+  // 3000 the small kernel is cheaper than 148 CTAs each quantizing the whole row.
+  if (p.m == 1) return (image || p.kblocks > 96) ? launch<DT, NT, 1, true, false, true, 1>(dev, p, b, ldb, image)
+                                                 : launch<DT, NT, 1, true, false, false, 1>(dev, p, b, ldb, nullptr);
+  if (p.m <= 8) return launch<DT, NT, 1, false, false, true, 1>(dev, p, b, ldb, image);
+  if (p.m <= 16) return launch<DT, NT, 2, false, false, true, 1>(dev, p, b, ldb, image);
+  if (p.m <= 32) return launch<DT, NT, 4, false, false, true, 2>(dev, p, b, ldb, image);
+  if (p.m <= 64) return launch<DT, NT, 8, false, false, true, 2>(dev, p, b, ldb, image);
+  return launch<DT, NT, 8, false, true, true, 2>(dev, p, b, ldb, image);  // groups of 64 rows
 }
 
 }  // namespace
 
 int32_t gemv_mma(AionCudaDevice* dev, const MatMulArgs& g, bool probe_only) {
-  if (g.m > 16ull * 65535 || g.k == 0) return AION_CUDA_UNSUPPORTED;
-  if (g.n > 0x7FFFFFFFull - TN || g.k / QK > 0x7FFFFFFFull) return AION_CUDA_UNSUPPORTED;
+  if (g.m > 64ull * 65535 || g.k == 0) return AION_CUDA_UNSUPPORTED;
+  if (g.n > 0x7FFFFFFFull - 128 || g.k / QK > 0x7FFFFFFFull) return AION_CUDA_UNSUPPORTED;
   const uint64_t kblocks = g.k / QK;
   const uintptr_t baddr = reinterpret_cast<uintptr_t>(g.b);
   if (baddr & 15) return AION_CUDA_UNSUPPORTED;
@@ -738,13 +758,12 @@ int32_t gemv_mma(AionCudaDevice* dev, const MatMulArgs& g, bool probe_only) {
   }
   if (probe_only) return AION_CUDA_OK;
 
-  const uint32_t mp2 = g.m == 1 ? 2u : (g.m <= 8 ? 8u : 16u);  // activation rows held per CTA (see MP2)
-  // K blocks whose quantized activations fit the per-CTA budget; a deeper K is issued as
-  // several launches that accumulate into C, like the reference's walk over K in chunks
-  // (src/aion/backend/cpu/exec/matmul.zig:431-434).
-  uint64_t kb_max = (ACT_BUDGET_BYTES / ((size_t)mp2 * 32 + (g.m == 1 ? 16 : (g.m > 8 ? 128 : 64)))) / KBT * KBT;
-  if (kb_max < KBT) kb_max = KBT;
-  if (g.m >= 2 || kblocks > 96) kb_max = (kblocks + KBT - 1) / KBT * KBT;  // the activation streams with the weights: any depth in one launch
+  // m = 1 with a shallow K quantizes its row inside the kernel, in K chunks that fit the per-CTA
+  // budget, issued as several launches that accumulate into C, like the reference's walk over
+  // K in chunks (src/aion/backend/cpu/exec/matmul.zig:431-434). Every other case streams the
+  // activation image with the weights: any depth in one launch.
+  uint64_t kb_max = (ACT_BUDGET_BYTES / 72) / KBT * KBT;
+  if (g.m >= 2 || kblocks > 96 || g.a_image) kb_max = (kblocks + KBT - 1) / KBT * KBT;
 
   for (uint64_t kb0 = 0; kb0 < kblocks; kb0 += kb_max) {
     const uint64_t nkb = kblocks - kb0 < kb_max ? kblocks - kb0 : kb_max;
@@ -754,31 +773,47 @@ int32_t gemv_mma(AionCudaDevice* dev, const MatMulArgs& g, bool probe_only) {
     p.m = (uint32_t)g.m;
     p.n = (uint32_t)g.n;
     p.kblocks = (uint32_t)nkb;
-    p.mp2 = mp2;
     p.lda = g.lda;
     p.ldc = g.ldc;
     p.alpha = g.alpha;
     p.beta = kb0 == 0 ? g.beta : 1.0f;
-    p.tiles = (uint32_t)((g.n + TN - 1) / TN);
+    const uint32_t tn = g.m > 16 ? 128u : 64u;
+    p.tiles = (uint32_t)((g.n + tn - 1) / tn);
     p.stages_per_tile = (uint32_t)((nkb + KBT - 1) / KBT);
     p.units = (uint64_t)p.tiles * p.stages_per_tile;
     p.fault = dev->fault_dev;
-    p.a_vec4 = ((reinterpret_cast<uintptr_t>(p.a) & 15) == 0 && g.lda % 4 == 0) ? 1u : 0u;
+    p.a_vec4 = (g.a && (reinterpret_cast<uintptr_t>(p.a) & 15) == 0 && g.lda % 4 == 0) ? 1u : 0u;
+    p.c_vec2 = ((reinterpret_cast<uintptr_t>(p.c) & 7) == 0 && g.ldc % 2 == 0) ? 1u : 0u;
     int32_t st;
     if (g.nt) {
-      st = launch_m<AION_CUDA_DTYPE_Q8_0, true>(dev, p, g.b + kb0 * Q8_BYTES, g.ldb);
+      st = launch_m<AION_CUDA_DTYPE_Q8_0, true>(dev, p, g.b + kb0 * Q8_BYTES, g.ldb, g.a_image);
     } else if (g.dtype == AION_CUDA_DTYPE_Q8_0) {
-      st = launch_m<AION_CUDA_DTYPE_Q8_0, false>(dev, p, g.b + kb0 * g.ldb * Q8_BYTES, g.ldb);
+      st = launch_m<AION_CUDA_DTYPE_Q8_0, false>(dev, p, g.b + kb0 * g.ldb * Q8_BYTES, g.ldb, g.a_image);
     } else {
-      st = launch_m<AION_CUDA_DTYPE_Q4_0, false>(dev, p, g.b + kb0 * g.ldb * Q4_BYTES, g.ldb);
+      st = launch_m<AION_CUDA_DTYPE_Q4_0, false>(dev, p, g.b + kb0 * g.ldb * Q4_BYTES, g.ldb, g.a_image);
     }
     if (st != AION_CUDA_OK) return st;
   }
   return AION_CUDA_OK;
 }
 
+// Fills an activation image from f32 rows (the library's own producer of images; the fused
+// producers in the other files write the same bytes).
+int32_t act_image_from_f32(AionCudaDevice* dev, uint32_t dtype, const float* a, uint64_t m, uint64_t k, uint64_t lda, uint8_t* image) {
+  const ActImageLayout L = act_image_layout(m, k / QK);
+  const uint32_t items = L.groups * L.kb_pad * L.rows_per_group;
+  const uint32_t vec4 = ((reinterpret_cast<uintptr_t>(a) & 15) == 0 && lda % 4 == 0) ? 1u : 0u;
+  if (dtype == AION_CUDA_DTYPE_Q8_0)
+    AION_CUDA_TRY(launch_pdl_main(gemv_act_image_kernel<AION_CUDA_DTYPE_Q8_0>, dim3((items + 127) / 128), dim3(128), 0, dev->stream, a, lda,
+                                  (uint32_t)m, (uint32_t)(k / QK), L, image, vec4));
+  else
+    AION_CUDA_TRY(launch_pdl_main(gemv_act_image_kernel<AION_CUDA_DTYPE_Q4_0>, dim3((items + 127) / 128), dim3(128), 0, dev->stream, a, lda,
+                                  (uint32_t)m, (uint32_t)(k / QK), L, image, vec4));
+  return AION_CUDA_OK;
+}
+
 // ------------------------------------------------------------------------------------
-// The same GEMV for callers that must not allocate (see aion_cuda_matmul_static_scratch
+// The same matmul for callers that must not allocate (see aion_cuda_matmul_static_scratch
 // in the header). The split-tile partial sums and their arrival counters live in this
 // file-scope array instead of in memory the device object grows on demand. Every GPU that
 // loads the library holds the array until the process exits.
@@ -787,56 +822,42 @@ namespace {
 
 constexpr uint32_t STATIC_MAX_CTAS = 512;    // grid is clamped to this
 constexpr uint32_t STATIC_MAX_TILES = 8192;  // n <= 524288
-constexpr size_t STATIC_PARTIAL_BYTES = (size_t)STATIC_MAX_CTAS * 2 * TN * 8 * sizeof(float);  // m <= 8
+constexpr size_t STATIC_PARTIAL_BYTES = (size_t)STATIC_MAX_CTAS * 2 * 64 * 8 * sizeof(float);  // m <= 8
 constexpr size_t STATIC_TICKET_BYTES = (size_t)STATIC_MAX_TILES * CONSUMER_WARPS * sizeof(int);
 
 static __device__ __align__(256) unsigned char g_static_scratch[STATIC_PARTIAL_BYTES + STATIC_TICKET_BYTES];
 
 // In host code `g_static_scratch` is only a stand-in for the symbol, not a device
 // address: each device's address is looked up once, with that device current.
-unsigned char* g_static_scratch_addr[16] = {};
+std::mutex g_static_scratch_mu;
+unsigned char* g_static_scratch_addr[64] = {};
 
-template <int DT, bool NT, bool M1>
+template <int DT, bool M1>
 int32_t launch_static(AionCudaDevice* dev, GemvParams p, const uint8_t* b, uint64_t ldb, unsigned char* scratch) {
-  using G = Geom<DT, NT>;
-  auto kernel = gemv_q_mma_kernel<DT, NT, 1, M1>;
+  using G = Geom<DT, false, 1>;
+  // The same instantiation aion_cuda_matmul uses for these shapes: they share its set-up state.
+  auto kernel = gemv_q_mma_kernel<DT, false, 1, M1, false, false, 1>;
   constexpr uint32_t MP2 = M1 ? 2 : 8;
-  const size_t smem = G::OFF_ACT + act_bytes(p.stages_per_tile * KBT, MP2, 1);
-  AION_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  int nb = 0;
-  AION_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, kernel, THREADS, smem));
-  if (nb < 1) return fail(AION_CUDA_INTERNAL_ERROR, "gemv: kernel does not fit an SM with %llu bytes of shared memory", (unsigned long long)smem);
-  uint64_t grid = (uint64_t)nb * dev->sm_count;
+  const size_t smem = G::OFF_ACT + act_bytes(p.stages_per_tile * KBT, MP2);
+  int per_sm = 0;
+  if (int32_t st = kernel_occupancy(setup_of<DT, false, 1, M1, false, false, 1>(), kernel, dev, smem, &per_sm)) return st;
+  uint64_t grid = (uint64_t)per_sm * dev->sm_count;
   if (grid > p.units) grid = p.units;
   if (grid > STATIC_MAX_CTAS) grid = STATIC_MAX_CTAS;
+  p.whole_tiles = 0;
   p.partials = reinterpret_cast<float*>(scratch);
   p.tickets = reinterpret_cast<int*>(scratch + STATIC_PARTIAL_BYTES);
   // The counters must start at zero whatever an earlier call left behind.
   AION_CUDA_TRY(cudaMemsetAsync(p.tickets, 0, (size_t)p.tiles * CONSUMER_WARPS * sizeof(int), dev->stream));
-
-  CUtensorMap tm;
-  if (!NT && DT == AION_CUDA_DTYPE_Q4_0) {
-    const uint64_t dims[2] = {(uint64_t)p.n * G::BB, p.kblocks};
-    const uint64_t strides[1] = {ldb * G::BB};
-    const uint32_t box[2] = {(uint32_t)TN * G::BB, KBT};
-    if (int32_t st = tensor_map_encode(b, 2, dims, strides, box, &tm)) return st;
-  } else if (!NT) {
-    const uint64_t dims[3] = {8ull * G::BB, p.n / 8, p.kblocks};
-    const uint64_t strides[2] = {8ull * G::BB, ldb * G::BB};
-    const uint32_t box[3] = {8u * G::BB, TN / 8, KBT};
-    if (int32_t st = tensor_map_encode(b, 3, dims, strides, box, &tm)) return st;
-  } else {
-    const uint64_t dims[2] = {(uint64_t)p.kblocks * Q8_BYTES, p.n};
-    const uint64_t strides[1] = {ldb * Q8_BYTES};
-    const uint32_t box[2] = {NT_ROW_PITCH, TN};
-    if (int32_t st = tensor_map_encode(b, 2, dims, strides, box, &tm)) return st;
-  }
+  CUtensorMap local;
+  const CUtensorMap* tm = nullptr;
+  if (int32_t st = encode_weight_map<DT, false, 1>(b, ldb, p.n, p.kblocks, nullptr, &local, &tm)) return st;
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3((unsigned)grid);
   cfg.blockDim = dim3(THREADS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = dev->stream;
-  AION_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, p, tm));
+  AION_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, p, *tm));
   return AION_CUDA_OK;
 }
 
@@ -846,26 +867,32 @@ int32_t gemv_mma_static_scratch(AionCudaDevice* dev, const MatMulArgs& g) {
   if (g.m == 0 || g.n == 0) return AION_CUDA_OK;
   if (g.m > 8)
     return fail(AION_CUDA_UNSUPPORTED, "matmul_static_scratch: m = %llu, the built-in scratch holds at most 8 rows", (unsigned long long)g.m);
-  if (g.k == 0 || g.k / QK > 0x7FFFFFFFull || g.n > (uint64_t)STATIC_MAX_TILES * TN)
+  if (g.k == 0 || g.k / QK > 0x7FFFFFFFull || g.n > (uint64_t)STATIC_MAX_TILES * 64)
     return fail(AION_CUDA_UNSUPPORTED, "matmul_static_scratch: n = %llu, k = %llu are outside the built-in scratch (n <= %u, k >= 32)",
-                (unsigned long long)g.n, (unsigned long long)g.k, STATIC_MAX_TILES * TN);
+                (unsigned long long)g.n, (unsigned long long)g.k, STATIC_MAX_TILES * 64);
   const uint64_t kblocks = g.k / QK;
-  bool readable = (reinterpret_cast<uintptr_t>(g.b) & 15) == 0;
-  if (!g.nt) readable = readable && g.n % 8 == 0 && g.ldb % 8 == 0;
-  else readable = readable && g.dtype == AION_CUDA_DTYPE_Q8_0 && g.order == AION_CUDA_ORDER_ROW_MAJOR && kblocks % 8 == 0;
-  if (!readable) return fail(AION_CUDA_UNSUPPORTED, "matmul_static_scratch: the tiled GEMV does not read this shape or alignment");
-  const uint32_t mp2 = g.m == 1 ? 2u : 8u;
-  const uint64_t kb_max = (ACT_BUDGET_BYTES / ((size_t)mp2 * 32 + (g.m == 1 ? 16 : 64))) / KBT * KBT;
+  if (g.nt || (reinterpret_cast<uintptr_t>(g.b) & 15) != 0 || g.n % 8 != 0 || g.ldb % 8 != 0)
+    return fail(AION_CUDA_UNSUPPORTED, "matmul_static_scratch: the tiled kernel does not read this shape or alignment");
+  // One launch holds the whole quantized activation in shared memory: 16384 columns of K for one
+  // row, 4096 for up to eight.
+  const uint64_t kb_max = g.m == 1 ? 512 : 128;
+  static_assert(512 * 2 * 36 <= ACT_BUDGET_BYTES && 128 * 8 * 36 <= ACT_BUDGET_BYTES, "static-scratch K limits fit the activation budget");
   if (kblocks > kb_max)
     return fail(AION_CUDA_UNSUPPORTED, "matmul_static_scratch: k = %llu with m = %llu exceeds one launch (k <= %llu)",
                 (unsigned long long)g.k, (unsigned long long)g.m, (unsigned long long)(kb_max * QK));
+  if (dev->ordinal < 0 || dev->ordinal >= 64)
+    return fail(AION_CUDA_UNSUPPORTED, "matmul_static_scratch: device ordinal %d is beyond the 64 this library keeps state for", dev->ordinal);
 
   // First call on this device: find where the array lives on it.
-  const int di = dev->ordinal & 15;
-  if (!g_static_scratch_addr[di]) {
-    unsigned char* ptr = nullptr;
-    AION_CUDA_TRY(cudaGetSymbolAddress((void**)&ptr, g_static_scratch));
-    g_static_scratch_addr[di] = ptr;
+  unsigned char* scratch;
+  {
+    std::lock_guard<std::mutex> lock(g_static_scratch_mu);
+    if (!g_static_scratch_addr[dev->ordinal]) {
+      unsigned char* ptr = nullptr;
+      AION_CUDA_TRY(cudaGetSymbolAddress((void**)&ptr, g_static_scratch));
+      g_static_scratch_addr[dev->ordinal] = ptr;
+    }
+    scratch = g_static_scratch_addr[dev->ordinal];
   }
 
   GemvParams p{};
@@ -874,24 +901,21 @@ int32_t gemv_mma_static_scratch(AionCudaDevice* dev, const MatMulArgs& g) {
   p.m = (uint32_t)g.m;
   p.n = (uint32_t)g.n;
   p.kblocks = (uint32_t)kblocks;
-  p.mp2 = mp2;
   p.lda = g.lda;
   p.ldc = g.ldc;
   p.alpha = g.alpha;
   p.beta = g.beta;
-  p.tiles = (uint32_t)((g.n + TN - 1) / TN);
+  p.tiles = (uint32_t)((g.n + 63) / 64);
   p.stages_per_tile = (uint32_t)((kblocks + KBT - 1) / KBT);
   p.units = (uint64_t)p.tiles * p.stages_per_tile;
   p.fault = dev->fault_dev;
   p.a_vec4 = ((reinterpret_cast<uintptr_t>(p.a) & 15) == 0 && g.lda % 4 == 0) ? 1u : 0u;
-  unsigned char* scratch = g_static_scratch_addr[di];
-  if (g.nt) return g.m == 1 ? launch_static<AION_CUDA_DTYPE_Q8_0, true, true>(dev, p, g.b, g.ldb, scratch)
-                            : launch_static<AION_CUDA_DTYPE_Q8_0, true, false>(dev, p, g.b, g.ldb, scratch);
+  p.c_vec2 = ((reinterpret_cast<uintptr_t>(p.c) & 7) == 0 && g.ldc % 2 == 0) ? 1u : 0u;
   if (g.dtype == AION_CUDA_DTYPE_Q8_0)
-    return g.m == 1 ? launch_static<AION_CUDA_DTYPE_Q8_0, false, true>(dev, p, g.b, g.ldb, scratch)
-                    : launch_static<AION_CUDA_DTYPE_Q8_0, false, false>(dev, p, g.b, g.ldb, scratch);
-  return g.m == 1 ? launch_static<AION_CUDA_DTYPE_Q4_0, false, true>(dev, p, g.b, g.ldb, scratch)
-                  : launch_static<AION_CUDA_DTYPE_Q4_0, false, false>(dev, p, g.b, g.ldb, scratch);
+    return g.m == 1 ? launch_static<AION_CUDA_DTYPE_Q8_0, true>(dev, p, g.b, g.ldb, scratch)
+                    : launch_static<AION_CUDA_DTYPE_Q8_0, false>(dev, p, g.b, g.ldb, scratch);
+  return g.m == 1 ? launch_static<AION_CUDA_DTYPE_Q4_0, true>(dev, p, g.b, g.ldb, scratch)
+                  : launch_static<AION_CUDA_DTYPE_Q4_0, false>(dev, p, g.b, g.ldb, scratch);
 }
 
 }  // namespace aion

@@ -10,6 +10,7 @@
 #include <cfloat>
 #include <cmath>
 
+#include "act_image.cuh"
 #include "common.cuh"
 #include "ptx.cuh"
 #include "quant_device.cuh"
@@ -130,6 +131,31 @@ __global__ void elemwise4_kernel(float4* out, const float4* a, const float4* b, 
     v.w = elemwise_one(av.w, bv.w, op);
     out[io] = v;
   }
+}
+
+// The same, one float4 per thread over [rows, cols] matrices, also writing the quantized image
+// of the result for the matmul that consumes it (act_image.cuh): the eight threads that hold
+// one 32-block of a row quantize it together. cols % 32 == 0.
+__global__ void __launch_bounds__(256) elemwise4_image_kernel(float4* out, const float4* a, const float4* b, uint64_t n4, uint32_t op,
+                                                              uint32_t cols4, uint64_t ld_out4, uint64_t ld_a4, uint64_t ld_b4,
+                                                              uint8_t* image, ActImageLayout L, uint32_t image_dtype) {
+  ptx::pdl_launch_dependents();
+  ptx::pdl_wait();
+  const uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x;
+  const bool on = i < n4;
+  const uint64_t ii = on ? i : 0;
+  const uint32_t r = (uint32_t)(ii / cols4), c = (uint32_t)(ii - (uint64_t)r * cols4);
+  float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  if (on) {
+    const float4 av = a[(uint64_t)r * ld_a4 + c], bv = b[(uint64_t)r * ld_b4 + c];
+    v.x = elemwise_one(av.x, bv.x, op);
+    v.y = elemwise_one(av.y, bv.y, op);
+    v.z = elemwise_one(av.z, bv.z, op);
+    v.w = elemwise_one(av.w, bv.w, op);
+    out[(uint64_t)r * ld_out4 + c] = v;
+  }
+  if (image_dtype == AION_CUDA_DTYPE_Q8_0) quantize_store_block_8lanes<AION_CUDA_DTYPE_Q8_0>(v, c & 7, on, image, L, r, c >> 3);
+  else quantize_store_block_8lanes<AION_CUDA_DTYPE_Q4_0>(v, c & 7, on, image, L, r, c >> 3);
 }
 
 // ---- RoPE: one thread per (b, l, pair); the rotation is reused by every head ----------
@@ -374,12 +400,15 @@ __device__ __forceinline__ float rmsf_block_sum(float v, float* part) {
 }
 // CH: float4 chunks per thread (cols <= CH * 4 * RMSF_THREADS); PAIR: also out2 = RMSNorm(out1).
 // out1 may alias x or residual: a thread reads its own elements before it writes them.
+// image != null: also the quantized image (act_image.cuh) of the last output (out2 of a pair,
+// out1 otherwise) for the matmul that consumes it; cols % 32 == 0 then, so the eight threads
+// that hold one 32-block are eight consecutive lanes.
 template <int CH, bool PAIR>
 __global__ void __launch_bounds__(RMSF_THREADS) rms_norm_regs_kernel(float* out1, float* out2, const float* x,
                                                                      const float* __restrict__ gamma1, const float* __restrict__ beta1,
                                                                      const float* residual, const float* __restrict__ gamma2,
                                                                      const float* __restrict__ beta2, uint32_t cols, float eps1, float eps2,
-                                                                     int* fault) {
+                                                                     int* fault, uint8_t* image, ActImageLayout L, uint32_t image_dtype) {
   ptx::pdl_launch_dependents();
   __shared__ float part[RMSF_THREADS / 32];
   const uint32_t n4 = cols / 4;
@@ -424,7 +453,17 @@ __global__ void __launch_bounds__(RMSF_THREADS) rms_norm_regs_kernel(float* out1
     xv[c] = v;
     sq += ((v.x * v.x + v.y * v.y) + v.z * v.z) + v.w * v.w;
   }
-  if (!PAIR) return;
+  if (!PAIR) {
+    if (image) {
+#pragma unroll
+      for (int c = 0; c < CH; c++) {
+        const uint32_t i = threadIdx.x + c * RMSF_THREADS;
+        if (image_dtype == AION_CUDA_DTYPE_Q8_0) quantize_store_block_8lanes<AION_CUDA_DTYPE_Q8_0>(xv[c], i & 7, i < n4, image, L, blockIdx.x, i >> 3);
+        else quantize_store_block_8lanes<AION_CUDA_DTYPE_Q4_0>(xv[c], i & 7, i < n4, image, L, blockIdx.x, i >> 3);
+      }
+    }
+    return;
+  }
   const float d2 = rmsf_block_sum(sq, part) * (1.0f / (float)cols) + eps2;
   if (!(d2 > 0.0f) || !isfinite(d2)) {
     if (threadIdx.x == 0) atomicCAS(fault, FAULT_NONE, FAULT_INVALID_ARGUMENT);
@@ -440,6 +479,10 @@ __global__ void __launch_bounds__(RMSF_THREADS) rms_norm_regs_kernel(float* out1
     v.z = ((xv[c].z * inv2) * g2[c].z) + b2[c].z;
     v.w = ((xv[c].w * inv2) * g2[c].w) + b2[c].w;
     if (i < n4) reinterpret_cast<float4*>(out2)[row4 + i] = v;
+    if (image) {
+      if (image_dtype == AION_CUDA_DTYPE_Q8_0) quantize_store_block_8lanes<AION_CUDA_DTYPE_Q8_0>(v, i & 7, i < n4, image, L, blockIdx.x, i >> 3);
+      else quantize_store_block_8lanes<AION_CUDA_DTYPE_Q4_0>(v, i & 7, i < n4, image, L, blockIdx.x, i >> 3);
+    }
   }
 }
 
@@ -447,18 +490,21 @@ __global__ void __launch_bounds__(RMSF_THREADS) rms_norm_regs_kernel(float* out1
 // Returns false when the caller should use the element-wise kernel instead.
 template <bool PAIR>
 bool launch_rms_regs(AionCudaDevice* dev, cudaError_t* err, unsigned rows, float* out1, float* out2, const float* x, const float* g1,
-                     const float* b1, const float* res, const float* g2, const float* b2, uint64_t cols, float eps1, float eps2) {
+                     const float* b1, const float* res, const float* g2, const float* b2, uint64_t cols, float eps1, float eps2,
+                     uint8_t* image, uint32_t image_dtype) {
   const uintptr_t bits = reinterpret_cast<uintptr_t>(out1) | reinterpret_cast<uintptr_t>(out2) | reinterpret_cast<uintptr_t>(x) |
                          reinterpret_cast<uintptr_t>(g1) | reinterpret_cast<uintptr_t>(b1) | reinterpret_cast<uintptr_t>(res) |
                          reinterpret_cast<uintptr_t>(g2) | reinterpret_cast<uintptr_t>(b2);
   if ((bits & 15) != 0 || cols % 4 != 0 || cols > 4ull * 4 * RMSF_THREADS) return false;
+  if (image && cols % QK != 0) return false;
   const uint32_t c32 = (uint32_t)cols;
+  const ActImageLayout L = act_image_layout(rows, cols / QK);
   if (cols <= 2ull * 4 * RMSF_THREADS)
     *err = launch_pdl(rms_norm_regs_kernel<2, PAIR>, dim3(rows), dim3(RMSF_THREADS), 0, dev->stream, out1, out2, x, g1, b1, res, g2, b2, c32,
-                      eps1, eps2, dev->fault_dev);
+                      eps1, eps2, dev->fault_dev, image, L, image_dtype);
   else
     *err = launch_pdl(rms_norm_regs_kernel<4, PAIR>, dim3(rows), dim3(RMSF_THREADS), 0, dev->stream, out1, out2, x, g1, b1, res, g2, b2, c32,
-                      eps1, eps2, dev->fault_dev);
+                      eps1, eps2, dev->fault_dev, image, L, image_dtype);
   return true;
 }
 
@@ -552,6 +598,18 @@ __global__ void rope_kv_append_kernel(float* __restrict__ q_out, const float* __
     for (uint32_t i = threadIdx.x; i < h_kv * d; i += blockDim.x) vd[i] = __float2half_rn(vsrc[i]);
 }
 
+// The optional image operand of a producer step: null when absent.
+int32_t resolve_out_image(const AionCudaOperand& op, uint32_t dtype, uint64_t rows, uint64_t cols, const char* name, uint8_t** out) {
+  *out = nullptr;
+  if (op.handle == 0) return AION_CUDA_OK;
+  if (dtype != AION_CUDA_DTYPE_Q8_0 && dtype != AION_CUDA_DTYPE_Q4_0) return fail(AION_CUDA_INVALID_ARGUMENT, "%s: image dtype %u", name, dtype);
+  if (cols % QK != 0) return fail(AION_CUDA_INVALID_ARGUMENT, "%s: an image needs rows of whole 32-blocks, got %llu columns", name, (unsigned long long)cols);
+  if (rows > (1ull << 22) || cols > (1ull << 26)) return fail(AION_CUDA_UNSUPPORTED, "%s: shape beyond what the matmul kernels index", name);
+  if (int32_t st = resolve(op, act_image_total_bytes(act_image_layout(rows, cols / QK)), name, out)) return st;
+  if (reinterpret_cast<uintptr_t>(*out) & 15) return fail(AION_CUDA_INVALID_ARGUMENT, "%s: the image must be 16-byte aligned", name);
+  return AION_CUDA_OK;
+}
+
 unsigned grid_for(const AionCudaDevice* dev, uint64_t n, unsigned threads) {
   const uint64_t want = ceil_div(n, (uint64_t)threads);
   const uint64_t cap = (uint64_t)dev->sm_count * 16;
@@ -580,11 +638,15 @@ int32_t aion_cuda_rms_norm(AionCudaDevice* dev, const AionCudaRMSNorm* s) {
   if (s->residual.handle)
     if (int32_t st = resolve(s->residual, bytes, "rms_norm.residual", &res)) return st;
   if (s->rows > 0x7FFFFFFFull) return fail(AION_CUDA_UNSUPPORTED, "rms_norm: too many rows for one launch");
+  uint8_t* image;
+  if (int32_t st = resolve_out_image(s->image, s->image_dtype, s->rows, s->cols, "rms_norm.image", &image)) return st;
   cudaError_t err = cudaSuccess;
-  if (launch_rms_regs<false>(dev, &err, (unsigned)s->rows, out, nullptr, x, gamma, beta, res, nullptr, nullptr, s->cols, s->eps, s->eps)) {
+  if (launch_rms_regs<false>(dev, &err, (unsigned)s->rows, out, nullptr, x, gamma, beta, res, nullptr, nullptr, s->cols, s->eps, s->eps, image,
+                             s->image_dtype)) {
     AION_CUDA_TRY(err);
     return AION_CUDA_OK;
   }
+  if (image) return fail(AION_CUDA_UNSUPPORTED, "rms_norm: an image needs rows of at most 4096 columns and 16-byte aligned operands");
   AION_CUDA_TRY(launch_pdl(rms_norm_kernel, dim3((unsigned)s->rows), dim3(RMS_THREADS), 0, dev->stream, out, x, gamma, beta, res, s->cols, s->eps,
                            dev->fault_dev));
   return AION_CUDA_OK;
@@ -613,6 +675,22 @@ int32_t aion_cuda_elemwise(AionCudaDevice* dev, const AionCudaElemwise* s) {
   if (int32_t st = resolve(s->a, need_a, "elemwise.a", &a)) return st;
   if (int32_t st = resolve(s->b, need_b, "elemwise.b", &b)) return st;
   const uintptr_t bits = reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b);
+  if (s->image.handle) {
+    // s->cols, not `cols`: a dense matrix still has rows for the image.
+    const uint64_t icols = s->cols;
+    if (icols == 0) return fail(AION_CUDA_INVALID_ARGUMENT, "elemwise: an image needs cols > 0");
+    const uint64_t rows = s->count / icols;
+    uint8_t* image;
+    if (int32_t st = resolve_out_image(s->image, s->image_dtype, rows, icols, "elemwise.image", &image)) return st;
+    const uint64_t lo = ldo ? ldo : icols, la = lda ? lda : icols, lb = ldb ? ldb : icols;
+    if ((bits & 15) != 0 || lo % 4 != 0 || la % 4 != 0 || lb % 4 != 0 || s->count / 4 > 0x7FFFFFFFull * 256)
+      return fail(AION_CUDA_UNSUPPORTED, "elemwise: an image needs 16-byte aligned operands and row strides that are multiples of 4");
+    const uint64_t n4 = s->count / 4;
+    AION_CUDA_TRY(launch_pdl(elemwise4_image_kernel, dim3((unsigned)ceil_div(n4, (uint64_t)256)), dim3(256), 0, dev->stream,
+                             reinterpret_cast<float4*>(out), reinterpret_cast<const float4*>(a), reinterpret_cast<const float4*>(b), n4, s->op,
+                             (uint32_t)(icols / 4), lo / 4, la / 4, lb / 4, image, act_image_layout(rows, icols / QK), s->image_dtype));
+    return AION_CUDA_OK;
+  }
   // Float4s pay once the element-per-thread grid is saturated anyway (decode of 512 requests:
   // 11.11 -> 10.90 ms); on small steps they only make fewer, longer threads (16 requests:
   // 2.46 -> 2.61 ms), so those stay element by element.
@@ -767,11 +845,14 @@ int32_t aion_cuda_rms_norm_pair(AionCudaDevice* dev, const AionCudaRMSNormPair* 
   if (int32_t st = resolve(s->beta2, vec, "rms_norm_pair.beta2", &b2)) return st;
   if (s->residual.handle)
     if (int32_t st = resolve(s->residual, bytes, "rms_norm_pair.residual", &res)) return st;
+  uint8_t* image;
+  if (int32_t st = resolve_out_image(s->image, s->image_dtype, s->rows, s->cols, "rms_norm_pair.image", &image)) return st;
   cudaError_t err = cudaSuccess;
-  if (launch_rms_regs<true>(dev, &err, (unsigned)s->rows, out1, out2, x, g1, b1, res, g2, b2, s->cols, s->eps1, s->eps2)) {
+  if (launch_rms_regs<true>(dev, &err, (unsigned)s->rows, out1, out2, x, g1, b1, res, g2, b2, s->cols, s->eps1, s->eps2, image, s->image_dtype)) {
     AION_CUDA_TRY(err);
     return AION_CUDA_OK;
   }
+  if (image) return fail(AION_CUDA_UNSUPPORTED, "rms_norm_pair: an image needs rows of at most 4096 columns and 16-byte aligned operands");
   AION_CUDA_TRY(launch_pdl(rms_norm_pair_kernel, dim3((unsigned)s->rows), dim3(RMS_THREADS), 0, dev->stream, out1, out2, x, g1, b1, res, g2,
                            b2, s->cols, s->eps1, s->eps2, dev->fault_dev));
   return AION_CUDA_OK;

@@ -1,5 +1,4 @@
-// Thin inline-PTX wrappers: mbarriers, 1-D bulk (TMA) copies, cluster addressing,
-// programmatic dependent launch and the int8 tensor-core MMA.
+// Thin inline-PTX wrappers: mbarriers, bulk and tiled TMA copies and programmatic dependent launch.
 #pragma once
 
 #include <stdint.h>
@@ -84,46 +83,10 @@ __device__ __forceinline__ void prefetch_tensormap(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
 
-// Thread-block cluster helpers.
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ uint32_t cluster_nctarank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
-  return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// Address of `local_smem` (a shared::cta address in this CTA) inside CTA `rank` of the cluster.
-__device__ __forceinline__ uint32_t map_to_rank(uint32_t local_smem, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_smem), "r"(rank));
-  return r;
-}
-__device__ __forceinline__ float ld_cluster_f32(uint32_t addr) {
-  float v;
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
-  return v;
-}
-
 // Programmatic dependent launch: let the next kernel in the stream start its
 // prologue, and wait for the previous kernel's results before touching them.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-
-// D(16x8, s32) = A(16x32, s8 row) * B(32x8, s8 col), fresh accumulator.
-__device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                       uint32_t b1) {
-  // Not volatile: a pure function of its operands, so independent MMAs may be interleaved.
-  asm(
-      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
-      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
-}
 
 __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
   uint32_t v;

@@ -19,7 +19,9 @@ fusion pass would rewrite the graph: one matmul against [Wq | Wk | Wv] and one a
 [Wg | Wu] (column concatenation commutes with K-major block quantization, so the packed
 weights are the same bytes side by side), `StepRopeKVAppend` for RoPE + cast + append, and
 `StepRMSNormPair` for "x = x + RMSNorm(.)" followed by the next block's RMSNorm: 9 launches
-per layer instead of 19.
+per layer instead of 19. With `images=True` (the default) every step that produces a matmul's
+activation (the norms, the GELU gate, attention) also writes its quantized image, so no matmul
+launches a quantization kernel of its own; the codes are the ones the matmul would compute.
 Every request is independent of the others in its batch (all ops are row-wise), which is
 what lets a batch be split over GPUs with replicated weights and no exchange.
 
@@ -36,7 +38,7 @@ import numpy as np
 from . import capi
 from .backend import (AttentionWindow, Chunk, CudaBackend, CudaSession, DeviceStore, StepArgMax, StepAttention, StepCast,
                       StepElemwiseBinary, StepGatherRows, StepMatMul, StepRMSNorm, StepRMSNormPair, StepRoPE1D,
-                      StepRopeKVAppend, StepSequenceAppend, TensorMeta, _check)
+                      StepRopeKVAppend, StepSequenceAppend, TensorMeta, _check, act_image_meta)
 
 F32, F16, I32, Q4, Q8 = capi.DTYPE_F32, capi.DTYPE_F16, capi.DTYPE_I32, capi.DTYPE_Q4_0, capi.DTYPE_Q8_0
 
@@ -98,8 +100,12 @@ class SyntheticDecoder:
 
     def __init__(self, backend: CudaBackend, cfg: DecoderConfig, requests: int,
                  weight_values: Callable[[str, int, int], object], embedding_values: Callable[[int, int], object],
-                 store: Optional[DeviceStore] = None, fused: bool = True):
+                 store: Optional[DeviceStore] = None, fused: bool = True, images: bool = True):
         self.backend, self.cfg, self.requests, self.fused = backend, cfg, requests, fused
+        # Images ride on the fused steps, on rows the register-resident norm kernel takes, and only
+        # where the int8 kernel (which reads them) runs.
+        self.images = bool(images and fused and cfg.hidden % 32 == 0 and cfg.hidden <= 4096 and cfg.ffn % 32 == 0
+                           and cfg.head_dim in (64, 128, 256) and requests < capi.GEMM_MIN_M)
         self.store = store or DeviceStore(backend.device_memory)
         self.session: CudaSession = backend.create_session(self.store)
         self._build_weights(weight_values, embedding_values)
@@ -228,6 +234,11 @@ class SyntheticDecoder:
             self.up_view = st.bind(half, Chunk(ch.handle, ch.offset + cfg.ffn * 4, ch.len - cfg.ffn * 4))
         self.logits = f(R, 1, cfg.vocab)
         self.next_token = st.add(TensorMeta(I32, (R, 1)))
+        self.img_xn = self.img_attn = self.img_act = None
+        if self.images:
+            self.img_xn = st.add(act_image_meta(R, cfg.hidden, cfg.weight_dtype))
+            self.img_attn = st.add(act_image_meta(R, cfg.q_width, cfg.weight_dtype))
+            self.img_act = st.add(act_image_meta(R, cfg.ffn, cfg.weight_dtype))
 
     def _build_steps(self) -> list:
         cfg = self.cfg
@@ -269,30 +280,31 @@ class SyntheticDecoder:
     def _build_steps_fused(self) -> list:
         cfg = self.cfg
         g, b = self.gamma, self.beta
+        ixn, iat, iac = self.img_xn, self.img_attn, self.img_act
         scale = 1.0 / float(np.sqrt(cfg.head_dim))
         steps: list = [StepGatherRows(out=self.x, table=self.embed, indices=self.tokens),
-                       StepRMSNorm(out=self.x_norm, x=self.x, gamma=g, beta=b, eps=cfg.eps)]
+                       StepRMSNorm(out=self.x_norm, x=self.x, gamma=g, beta=b, eps=cfg.eps, image=ixn)]
         for layer in range(cfg.layers):
             w = self.w[layer]
             steps += [
-                StepMatMul(c=self.qkv, a=self.x_norm, b=w["wqkv"]),
+                StepMatMul(c=self.qkv, a=self.x_norm, b=w["wqkv"], a_image=ixn),
                 StepRopeKVAppend(q_out=self.q_rot, qkv=self.qkv, positions=self.positions, end_index=self.write_index,
                                  k_cache=self.k_cache[layer], v_cache=self.v_cache[layer], base_frequency=cfg.rope_base),
                 StepAttention(out=self.attn, q=self.q_rot, k=self.k_cache[layer], v=self.v_cache[layer],
                               query_positions=self.positions, kv_lengths=self.visible_end, scale=scale,
-                              window=AttentionWindow.causal()),
-                StepMatMul(c=self.o, a=self.attn2, b=w["wo"]),
+                              window=AttentionWindow.causal(), image=iat),
+                StepMatMul(c=self.o, a=self.attn2, b=w["wo"], a_image=iat),
                 # x = x + RMSNorm(o);  x_norm = RMSNorm(x)
                 StepRMSNormPair(out1=self.x, out2=self.x_norm, x=self.o, gamma1=g, beta1=b, gamma2=g, beta2=b, eps1=cfg.eps,
-                                eps2=cfg.eps, residual=self.x),
-                StepMatMul(c=self.gu, a=self.x_norm, b=w["wgu"]),
-                StepElemwiseBinary(op="gate", out=self.act, a=self.gate_view, b=self.up_view),
-                StepMatMul(c=self.down, a=self.act, b=w["wd"]),
+                                eps2=cfg.eps, residual=self.x, image=ixn),
+                StepMatMul(c=self.gu, a=self.x_norm, b=w["wgu"], a_image=ixn),
+                StepElemwiseBinary(op="gate", out=self.act, a=self.gate_view, b=self.up_view, image=iac),
+                StepMatMul(c=self.down, a=self.act, b=w["wd"], a_image=iac),
                 # x = x + RMSNorm(down);  x_norm = RMSNorm(x): the next layer's input norm, or the final norm
                 StepRMSNormPair(out1=self.x, out2=self.x_norm, x=self.down, gamma1=g, beta1=b, gamma2=g, beta2=b, eps1=cfg.eps,
-                                eps2=cfg.eps, residual=self.x),
+                                eps2=cfg.eps, residual=self.x, image=ixn),
             ]
-        steps += [StepMatMul(c=self.logits, a=self.x_norm, b=self.w_head),
+        steps += [StepMatMul(c=self.logits, a=self.x_norm, b=self.w_head, a_image=ixn),
                   StepArgMax(out=self.next_token, a=self.logits)]
         return steps
 

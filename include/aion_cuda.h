@@ -158,13 +158,18 @@ AION_CUDA_API int32_t aion_cuda_memset(AionCudaDevice* dev, uint64_t handle, siz
  *   C f32, row stride ldc elements (0 = n).
  * The activation is quantized to int8 per 32-block exactly as the reference CPU
  * kernels do (aion src/aion/backend/cpu/kernels/matmul_q_i8.zig:187-203) for
- * m < AION_CUDA_GEMM_MIN_M (in groups of AION_CUDA_GEMV_MAX_M rows inside one launch); larger m runs the
- * tensor-core prefill GEMM, which dequantizes B to bf16 and rounds A to bf16 (results
- * within rel-L2 1e-2 of the int8-activation arithmetic instead of 1e-3).
+ * m < AION_CUDA_GEMM_MIN_M — every decode batch size: one launch streams the weights once per
+ * AION_CUDA_INT8_GROUP_ROWS rows of A, so a request's result does not depend on how many
+ * requests share its step; larger m (prefill) runs the tensor-core GEMM, which dequantizes B
+ * to bf16 and rounds A to bf16 (results within rel-L2 1e-2 of the int8-activation arithmetic
+ * instead of 1e-3).
  * f32 / f16 B return UNSUPPORTED.
+ *   a_image (handle 0 = absent): the quantized image of A that the step producing A wrote
+ *     (see aion_cuda_act_image_bytes); the int8 kernels then read it instead of quantizing A.
+ *     Ignored by the tensor-core GEMM and the any-shape kernel, which read A itself.
  * --------------------------------------------------------------------------------- */
-#define AION_CUDA_GEMV_MAX_M 16  /* rows of A one group of GEMV CTAs takes */
-#define AION_CUDA_GEMM_MIN_M 33  /* from this many rows on, the tensor-core GEMM (bf16 operands) runs */
+#define AION_CUDA_INT8_GROUP_ROWS 64 /* rows of A that share one pass over the weights */
+#define AION_CUDA_GEMM_MIN_M 513     /* from this many rows on, the tensor-core GEMM (bf16 operands) runs */
 
 typedef struct AionCudaMatMul {
   AionCudaOperand c, a, b;
@@ -173,16 +178,50 @@ typedef struct AionCudaMatMul {
   uint64_t m, n, k;
   uint64_t lda, ldb, ldc;
   float alpha, beta;
+  AionCudaOperand a_image; /* handle 0 = absent */
 } AionCudaMatMul;
 
 /* Force a kernel family regardless of m; tests use these the way the reference's GPU
  * tests pin a pipeline (aion src/aion/backend/gpu/test_gpu_backend.zig:403-422). */
 #define AION_CUDA_MATMUL_AUTO 0u
 #define AION_CUDA_MATMUL_FORCE_GENERIC 1u /* any-shape scalar kernel */
-#define AION_CUDA_MATMUL_FORCE_GEMV 2u    /* tiled int8 tensor-core GEMV */
+#define AION_CUDA_MATMUL_FORCE_GEMV 2u    /* tiled int8 tensor-core kernel (decode) */
 #define AION_CUDA_MATMUL_FORCE_GEMM 4u    /* tcgen05 prefill GEMM */
 
 AION_CUDA_API int32_t aion_cuda_matmul(AionCudaDevice* dev, const AionCudaMatMul* step);
+
+/* Which kernel aion_cuda_matmul would run for this step and how it would tile it, without
+ * running anything. No counterpart in the reference; the tests use it to show that a case
+ * reaches the kernel variant it is meant to cover, the way the reference's device tests pin
+ * a pipeline (aion src/aion/backend/gpu/test_gpu_backend.zig:403-422). */
+#define AION_CUDA_KERNEL_GENERIC 1u /* any-shape scalar kernel */
+#define AION_CUDA_KERNEL_INT8 2u    /* tiled int8 tensor-core kernel */
+#define AION_CUDA_KERNEL_GEMM 3u    /* tcgen05 prefill GEMM */
+typedef struct AionCudaMatMulPlan {
+  uint32_t kernel;    /* AION_CUDA_KERNEL_* */
+  uint32_t tile_rows; /* rows of A per tile (GEMM: 128 or 256) or per pass over the weights (int8) */
+  uint32_t tile_cols; /* output columns per tile */
+  uint32_t k_splits;  /* GEMM: CTAs that share one tile's K range (1 = none) */
+  uint32_t grid;      /* GEMM: CTAs launched; 0 where the choice is made at launch */
+  uint32_t reserved[3];
+} AionCudaMatMulPlan;
+AION_CUDA_API int32_t aion_cuda_matmul_plan(AionCudaDevice* dev, const AionCudaMatMul* step, AionCudaMatMulPlan* out);
+
+/* The quantized-activation image. No counterpart in the reference, whose CPU kernels quantize
+ * A at the start of every matmul (aion src/aion/backend/cpu/kernels/matmul_q_i8.zig:237-246):
+ * here the step that PRODUCES an activation (RMSNorm, the GELU gate, Attention) can write, next
+ * to its f32 output, the int8 codes and block scales of that output in the order the int8
+ * matmul kernel reads them, and the matmul that consumes it takes the image through `a_image`.
+ * A decode layer then runs without a quantization kernel between its steps. The codes and
+ * scales are exactly those the matmul would compute from the f32 values.
+ *   aion_cuda_act_image_bytes: size of the image of an [m, k] activation (k % 32 == 0).
+ *   aion_cuda_act_image: writes the image of f32 rows (row stride lda elements, 0 = k) for
+ *     weights of `b_dtype` (q4_0 and q8_0 weights read their codes in different orders).
+ * A producer writes only the blocks of rows < m and K blocks < k/32: zero the image buffer
+ * once (aion_cuda_memset) before its first use with a given shape, the padding must read as zeros. */
+AION_CUDA_API int32_t aion_cuda_act_image_bytes(uint64_t m, uint64_t k, uint64_t* out_bytes);
+AION_CUDA_API int32_t aion_cuda_act_image(AionCudaDevice* dev, uint32_t b_dtype, const AionCudaOperand* a, uint64_t m, uint64_t k,
+                                          uint64_t lda, const AionCudaOperand* image);
 
 /* No counterpart in the reference. The decode `MatMul` step (m <= 8, K-major q8_0 /
  * q4_0 B) for callers that are not allowed to allocate device memory: code running
@@ -192,7 +231,7 @@ AION_CUDA_API int32_t aion_cuda_matmul(AionCudaDevice* dev, const AionCudaMatMul
  * whose device memory budget is fixed up front. aion_cuda_matmul grows the device's
  * scratch with cudaMalloc the first time a shape needs it; this entry point never calls
  * cudaMalloc, cudaFree or any allocating routine, on the host or on the device. The
- * kernel's scratch (split-tile partial sums and their arrival counters) is a 2.1 MB
+ * kernel's scratch (split-tile partial sums and their arrival counters) is a 2.23 MB
  * array compiled into the library; every GPU that loads the library holds it until the
  * process exits.
  *  - Same arguments, arithmetic and results as aion_cuda_matmul (bitwise when both pick
@@ -226,6 +265,7 @@ typedef struct AionCudaMatMulNT {
   uint64_t m, n, k;
   uint64_t lda, ldc, c_off;
   float alpha, beta;
+  AionCudaOperand a_image; /* as in AionCudaMatMul; handle 0 = absent */
 } AionCudaMatMulNT;
 
 AION_CUDA_API int32_t aion_cuda_matmul_nt(AionCudaDevice* dev, const AionCudaMatMulNT* step);
@@ -256,6 +296,12 @@ typedef struct AionCudaAttention {
   float soft_cap;
   uint32_t window_left, window_right, window_chunk;
   uint32_t flags;
+  /* Optional (handle 0 = absent): the quantized image of `out` seen as [B*L, Hq*Dv] rows, for the
+   * matmul against weights of image_dtype that consumes it (aion_cuda_act_image_bytes). Written
+   * by the tensor-core decode kernel; other shapes return UNSUPPORTED when it is asked for. */
+  AionCudaOperand image;
+  uint32_t image_dtype;
+  uint32_t reserved;
 } AionCudaAttention;
 
 AION_CUDA_API int32_t aion_cuda_attention(AionCudaDevice* dev, const AionCudaAttention* step);
@@ -269,12 +315,15 @@ AION_CUDA_API int32_t aion_cuda_attention(AionCudaDevice* dev, const AionCudaAtt
  * (aion src/aion/backend/cpu/exec/layernorm.zig:41-154).
  *   out[r, :] = (x[r, :] * inv_r) * gamma + beta (+ residual[r, :]),
  *   inv_r = 1 / sqrt(mean(x[r, :]^2) + eps); eps must be finite and > 0.
- * residual.handle == 0: absent. out may alias x or residual. */
+ * residual.handle == 0: absent. out may alias x or residual.
+ * image (handle 0 = absent): also write the quantized image of `out` for a matmul against
+ * weights of image_dtype (cols % 32 == 0, cols <= 4096 and 16-byte aligned operands). */
 typedef struct AionCudaRMSNorm {
   AionCudaOperand out, x, gamma, beta, residual;
   uint64_t rows, cols;
   float eps;
-  uint32_t reserved;
+  uint32_t image_dtype;
+  AionCudaOperand image;
 } AionCudaRMSNorm;
 AION_CUDA_API int32_t aion_cuda_rms_norm(AionCudaDevice* dev, const AionCudaRMSNorm* step);
 
@@ -293,6 +342,11 @@ typedef struct AionCudaElemwise {
   /* cols > 0: the operands are [count / cols, cols] matrices with these row strides in
    * elements (0 = cols), e.g. the two halves of a [gate | up] matmul output. */
   uint64_t cols, ld_out, ld_a, ld_b;
+  /* Optional (handle 0 = absent): the quantized image of `out` as [count / cols, cols] rows for a
+   * matmul against weights of image_dtype; needs cols > 0, cols % 32 == 0 and 16-byte aligned rows. */
+  AionCudaOperand image;
+  uint32_t image_dtype;
+  uint32_t reserved2;
 } AionCudaElemwise;
 AION_CUDA_API int32_t aion_cuda_elemwise(AionCudaDevice* dev, const AionCudaElemwise* step);
 
@@ -368,6 +422,9 @@ typedef struct AionCudaRMSNormPair {
   AionCudaOperand out1, out2, x, gamma1, beta1, residual, gamma2, beta2;
   uint64_t rows, cols;
   float eps1, eps2;
+  AionCudaOperand image; /* optional: the quantized image of out2, as in AionCudaRMSNorm */
+  uint32_t image_dtype;
+  uint32_t reserved;
 } AionCudaRMSNormPair;
 AION_CUDA_API int32_t aion_cuda_rms_norm_pair(AionCudaDevice* dev, const AionCudaRMSNormPair* step);
 

@@ -8,8 +8,8 @@ import oracle
 
 
 class OracleDecoder:
-    def __init__(self, cfg, requests, weights_f32, embedding_f32):
-        self.cfg, self.R = cfg, requests
+    def __init__(self, cfg, requests, weights_f32, embedding_f32, fast=False):
+        self.cfg, self.R, self.fast = cfg, requests, fast
         dt = oracle.Q4_0 if cfg.weight_dtype == 3 else oracle.Q8_0
         self.dt = dt
         self.w = {name: oracle.quantize(dt, v, 0) for name, v in weights_f32.items()}
@@ -21,6 +21,8 @@ class OracleDecoder:
 
     def _mm(self, a, name, k, n):
         m = a.size // k
+        if self.fast:  # the threaded port of the same kernels (tests/test_oracle_fast.py holds it to the scalar oracle)
+            return oracle.fast_matmul_q(self.dt, np.ascontiguousarray(a.reshape(m, k)), self.w[name], m, n, k).reshape(m, n)
         return oracle.matmul_q(self.dt, a.reshape(m, k), self.w[name], m, n, k).reshape(m, n)
 
     def step(self, tokens, positions):

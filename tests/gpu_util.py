@@ -42,9 +42,39 @@ def _raise(status: int):
         raise BackendError(status, capi.last_error())
 
 
+def image_bytes(m: int, k: int) -> int:
+    n = C.c_uint64()
+    _raise(capi.load().aion_cuda_act_image_bytes(m, k, C.byref(n)))
+    return int(n.value)
+
+
+def make_image(backend: CudaBackend, dtype: int, a_buf: "DevBuf", m: int, k: int, lda: int = 0) -> "DevBuf":
+    """The quantized image of the f32 rows in `a_buf`, made by aion_cuda_act_image (zero-filled first)."""
+    img = DevBuf(backend, np.zeros(image_bytes(m, k), dtype=np.uint8))
+    a_op, i_op = a_buf.operand(), img.operand()
+    _raise(backend._lib.aion_cuda_act_image(backend.handle, dtype, C.byref(a_op), m, k, lda, C.byref(i_op)))
+    return img
+
+
+def matmul_plan(backend: CudaBackend, dtype: int, m: int, n: int, k: int, flags=capi.MATMUL_AUTO) -> capi.MatMulPlan:
+    """aion_cuda_matmul_plan for dense operands of this shape (placeholder buffers of the right sizes)."""
+    bb = 18 if dtype == capi.DTYPE_Q4_0 else 34
+    bufs = [DevBuf(backend, nbytes=m * k * 4), DevBuf(backend, nbytes=(k // 32) * n * bb), DevBuf(backend, nbytes=m * n * 4)]
+    try:
+        rec = capi.MatMul(c=bufs[2].operand(), a=bufs[0].operand(), b=bufs[1].operand(), b_dtype=dtype, flags=flags, m=m, n=n,
+                          k=k, lda=0, ldb=0, ldc=0, alpha=1.0, beta=0.0)
+        plan = capi.MatMulPlan()
+        _raise(backend._lib.aion_cuda_matmul_plan(backend.handle, C.byref(rec), C.byref(plan)))
+        return plan
+    finally:
+        for x in bufs:
+            x.free()
+
+
 def run_matmul(backend: CudaBackend, dtype: int, a: np.ndarray, b: np.ndarray, m: int, n: int, k: int, *, lda=0, ldb=0,
-               ldc=0, alpha=1.0, beta=0.0, c: np.ndarray | None = None, flags=capi.MATMUL_AUTO, canary=True):
-    """aion_cuda_matmul on host arrays; returns C as [m, ldc or n]. Checks a canary past the end of C."""
+               ldc=0, alpha=1.0, beta=0.0, c: np.ndarray | None = None, flags=capi.MATMUL_AUTO, canary=True, image=False):
+    """aion_cuda_matmul on host arrays; returns C as [m, ldc or n]. Checks a canary past the end of C.
+    image: hand the step the quantized image of A (made by aion_cuda_act_image) as well."""
     width = ldc if ldc else n
     c_host = np.zeros(m * width, dtype=np.float32) if c is None else np.asarray(c, dtype=np.float32).reshape(-1).copy()
     tail = np.full(64, CANARY, dtype=np.float32)
@@ -52,8 +82,13 @@ def run_matmul(backend: CudaBackend, dtype: int, a: np.ndarray, b: np.ndarray, m
             DevBuf(backend, np.concatenate([c_host, tail]))]
     try:
         need_c = ((m - 1) * width + n) * 4 if m else 0
+        img_op = capi.Operand(0, 0, 0)
+        if image:
+            bufs.append(make_image(backend, dtype, bufs[0], m, k, lda))
+            img_op = bufs[-1].operand()
         rec = capi.MatMul(c=bufs[2].operand(0, max(need_c, c_host.nbytes)), a=bufs[0].operand(), b=bufs[1].operand(),
-                          b_dtype=dtype, flags=flags, m=m, n=n, k=k, lda=lda, ldb=ldb, ldc=ldc, alpha=alpha, beta=beta)
+                          b_dtype=dtype, flags=flags, m=m, n=n, k=k, lda=lda, ldb=ldb, ldc=ldc, alpha=alpha, beta=beta,
+                          a_image=img_op)
         _raise(backend._lib.aion_cuda_matmul(backend.handle, C.byref(rec)))
         out = bufs[2].read(np.float32)
         if canary:
@@ -65,16 +100,20 @@ def run_matmul(backend: CudaBackend, dtype: int, a: np.ndarray, b: np.ndarray, m
 
 
 def run_matmul_nt(backend: CudaBackend, a: np.ndarray, b: np.ndarray, m: int, n: int, k: int, *, order=capi.ORDER_ROW_MAJOR,
-                  lda=0, ldc=0, c_off=0, alpha=1.0, beta=0.0, c: np.ndarray | None = None, flags=capi.MATMUL_AUTO):
+                  lda=0, ldc=0, c_off=0, alpha=1.0, beta=0.0, c: np.ndarray | None = None, flags=capi.MATMUL_AUTO, image=False):
     width = ldc if ldc else n
     c_host = np.zeros(m * width, dtype=np.float32) if c is None else np.asarray(c, dtype=np.float32).reshape(-1).copy()
     tail = np.full(64, CANARY, dtype=np.float32)
     bufs = [DevBuf(backend, np.ascontiguousarray(a, dtype=np.float32)), DevBuf(backend, np.ascontiguousarray(b, dtype=np.uint8)),
             DevBuf(backend, np.concatenate([c_host, tail]))]
     try:
+        img_op = capi.Operand(0, 0, 0)
+        if image:
+            bufs.append(make_image(backend, capi.DTYPE_Q8_0, bufs[0], m, k, lda))
+            img_op = bufs[-1].operand()
         rec = capi.MatMulNT(c=bufs[2].operand(0, c_host.nbytes), a=bufs[0].operand(), b=bufs[1].operand(),
                             b_dtype=capi.DTYPE_Q8_0, block_order=order, flags=flags, m=m, n=n, k=k, lda=lda, ldc=ldc,
-                            c_off=c_off, alpha=alpha, beta=beta)
+                            c_off=c_off, alpha=alpha, beta=beta, a_image=img_op)
         _raise(backend._lib.aion_cuda_matmul_nt(backend.handle, C.byref(rec)))
         out = bufs[2].read(np.float32)
         assert np.array_equal(out[c_host.size:], tail), "kernel wrote past the end of C"

@@ -4,6 +4,7 @@ for those that fail before any CUDA call)."""
 import ctypes as C
 import os
 import re
+import subprocess
 
 from aion_b200 import capi
 
@@ -27,11 +28,36 @@ def test_library_exports_every_declared_symbol():
         assert hasattr(lib, name), name
 
 
-def test_struct_sizes_match_the_header_layout():
-    assert C.sizeof(capi.Operand) == 24
-    assert C.sizeof(capi.MatMul) == 3 * 24 + 8 + 6 * 8 + 8
-    assert C.sizeof(capi.MatMulNT) == 3 * 24 + 16 + 6 * 8 + 8
-    assert C.sizeof(capi.Attention) == 6 * 24 + 16 + 7 * 8 + 8 + 16
+STRUCTS = {"AionCudaOperand": capi.Operand, "AionCudaDeviceInfo": capi.DeviceInfo, "AionCudaMatMul": capi.MatMul,
+           "AionCudaMatMulPlan": capi.MatMulPlan, "AionCudaMatMulNT": capi.MatMulNT, "AionCudaAttention": capi.Attention,
+           "AionCudaRMSNorm": capi.RMSNorm, "AionCudaElemwise": capi.Elemwise, "AionCudaRoPE": capi.RoPE,
+           "AionCudaCast": capi.Cast, "AionCudaSequenceAppend": capi.SequenceAppend, "AionCudaGatherRows": capi.GatherRows,
+           "AionCudaArgMax": capi.ArgMax, "AionCudaRMSNormPair": capi.RMSNormPair, "AionCudaRopeKVAppend": capi.RopeKVAppend}
+
+
+def test_struct_layouts_match_the_header(tmp_path):
+    """Every struct the header declares, compiled by the C compiler, has the size and the field
+    offsets of its ctypes mirror."""
+    text = open(os.path.join(ROOT, "include", "aion_cuda.h")).read()
+    declared = set(re.findall(r"typedef struct \w+ \{[^}]*\} (\w+);", text))
+    assert declared == set(STRUCTS), declared ^ set(STRUCTS)
+    lines = ['#include <stdio.h>', '#include <stddef.h>', f'#include "{os.path.join(ROOT, "include", "aion_cuda.h")}"',
+             "int main(void) {"]
+    for name, ct in STRUCTS.items():
+        lines.append(f'printf("{name} %zu\\n", sizeof({name}));')
+        for field, _ in ct._fields_:
+            cfield = field[:-1] if field.endswith("_") and field != "_" else field  # `in_` mirrors the C field `in`
+            lines.append(f'printf("{name}.{field} %zu\\n", offsetof({name}, {cfield}));')
+    lines.append("return 0; }")
+    src = tmp_path / "layout.c"
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "layout"
+    subprocess.run(["gcc", "-std=c11", "-o", str(exe), str(src)], check=True)
+    out = dict(line.split() for line in subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.splitlines())
+    for name, ct in STRUCTS.items():
+        assert int(out[name]) == C.sizeof(ct), name
+        for field, _ in ct._fields_:
+            assert int(out[f"{name}.{field}"]) == getattr(ct, field).offset, f"{name}.{field}"
 
 
 def test_null_arguments_are_rejected_with_a_message():

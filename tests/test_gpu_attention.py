@@ -55,7 +55,7 @@ def test_plain_sequence_equals_cache_with_implied_indices(backend):
 
 
 # ---- benchmark configuration 4 (seeded synthetic inputs of that shape) -------------------
-@pytest.mark.parametrize("B,T", [(1, 1024), (8, 1024), (1, 4096), (3, 4096), (2, 16384)])
+@pytest.mark.parametrize("B,T", [(1, 1024), (8, 1024), (64, 1024), (1, 4096), (3, 4096), (2, 16384)])
 def test_config4_decode(backend, B, T):
     q, k, v = _qkv(B, 1, 8, 1, T, 256, 256, np.float16, np.float16, seed=T + B)
     pos = np.full((B, 1), T - 1, dtype=np.int32)
@@ -182,5 +182,43 @@ def test_session_attention_step(backend):
         want = oracle.attention(q, k, v, scale=0.125, positions=np.array([[99], [127]]), kv_lengths=np.array([100, 128]),
                                 right=0)
         assert rd.rel_l2(got, want) < TOL
+    finally:
+        store.deinit()
+
+
+@pytest.mark.parametrize("dtype", [capi.DTYPE_Q4_0, capi.DTYPE_Q8_0])
+@pytest.mark.parametrize("B,T,qdt", [(1, 48, np.float32), (8, 2048, np.float32), (70, 300, np.float16)])
+def test_attention_writes_the_image_of_its_output(backend, dtype, B, T, qdt):
+    """The decode kernel (one pass per row, and split contexts merged by the last CTA) also writes the
+    quantized image of out [B, Hq*Dv] that the output projection reads."""
+    from aion_b200.backend import act_image_meta
+    from tests.gpu_util import DevBuf, make_image
+
+    Hq, D = 8, 256
+    q, k, v = _qkv(B, 1, Hq, 1, T, D, D, qdt, np.float16, seed=B)
+    lens = np.random.default_rng(1).integers(1, T + 1, B).astype(np.int32)
+    pos = (lens - 1).reshape(B, 1).astype(np.int32)
+    store = DeviceStore(backend.device_memory)
+    try:
+        f = {np.float32: capi.DTYPE_F32, np.float16: capi.DTYPE_F16}
+        tq = store.add(TensorMeta(f[qdt], q.shape), q)
+        tk = store.add(TensorMeta(capi.DTYPE_F16, k.shape), k)
+        tv = store.add(TensorMeta(capi.DTYPE_F16, v.shape), v)
+        tp = store.add(TensorMeta(capi.DTYPE_I32, pos.shape), pos)
+        tl = store.add(TensorMeta(capi.DTYPE_I32, lens.shape), lens)
+        to = store.add(TensorMeta(capi.DTYPE_F32, (B, 1, Hq, D)))
+        ti = store.add(act_image_meta(B, Hq * D, dtype))
+        sess = backend.create_session(store)
+        sess.execute([StepAttention(out=to, q=tq, k=tk, v=tv, query_positions=tp, kv_lengths=tl, scale=1.0 / 16.0,
+                                    window=AttentionWindow.causal(), image=ti)])
+        got = store.read(to)
+        assert rd.rel_l2(got, oracle.attention(q, k, v, scale=1.0 / 16.0, positions=pos, kv_lengths=lens, right=0)) < TOL
+        a = DevBuf(backend, got.reshape(B, Hq * D))
+        img = make_image(backend, dtype, a, B, Hq * D)
+        try:
+            assert np.array_equal(store.read(ti).view(np.uint8), img.read(np.uint8))
+        finally:
+            a.free()
+            img.free()
     finally:
         store.deinit()

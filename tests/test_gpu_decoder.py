@@ -134,3 +134,98 @@ def test_request_result_is_independent_of_its_batch(backend):
     top2 = np.sort(outs["all"][0], axis=-1)[:, -2:]
     clear = (top2[:, 1] - top2[:, 0]) > 4 * CHAIN_TOL * np.abs(outs["all"][0]).max()
     assert np.array_equal(outs["all"][1][clear], split_next[clear])
+
+
+# ---- the benchmark decoder's real widths -------------------------------------------------------
+REAL = DecoderConfig(layers=1, hidden=1536, ffn=8192, heads=8, kv_heads=1, head_dim=256, vocab=4096, ctx=512)
+# One layer at real widths, fed identical inputs on both sides: four matmuls, each re-quantizing an
+# activation that differs from the CPU's in the last bits, so a few int8 roundings flip.
+REAL_TOL = 5e-3
+
+
+def _prefill(dec, ref, cfg, R, filled, seed, total=None):
+    """The same random f16 keys / values in both caches for positions < filled; with `total`, request r
+    gets the rows it would get in a batch of `total` requests."""
+    rng = np.random.default_rng(seed)
+    total = total or R
+    for l in range(cfg.layers):
+        for dev_t, host in ((dec.k_cache[l], ref.k_cache[l] if ref else None), (dec.v_cache[l], ref.v_cache[l] if ref else None)):
+            vals = np.zeros((R, cfg.ctx, cfg.kv_heads, cfg.head_dim), np.float16)
+            vals[:, :filled] = rng.standard_normal((total, filled, cfg.kv_heads, cfg.head_dim)).astype(np.float16)[:R]
+            dec.store.write(dev_t, vals)
+            if ref is not None:
+                host[:] = vals
+
+
+@pytest.mark.parametrize("R", [8, 64])
+def test_decoder_layer_at_real_widths_matches_oracle(backend, R):
+    """Hidden 1536, FFN 8192, 8 query heads / 1 kv head x 256, 500 cached positions, a 4096-column slice of
+    the head: 8 requests (8-row tiles) and 64 requests (64-row groups, 128-column tiles, split contexts in
+    attention), every activation image written by its producer. Against the graph composed from oracle ops."""
+    cfg = REAL
+    w, emb = make_values(cfg, seed=21)
+    dec = build(backend, cfg, R, w, emb)
+    assert dec.images
+    ref = OracleDecoder(cfg, R, w, emb, fast=True)
+    try:
+        _prefill(dec, ref, cfg, R, 500, seed=R)
+        rng = np.random.default_rng(5)
+        worst = {"hidden": 0.0, "logits": 0.0}
+        for t in (500, 501):
+            tokens = rng.integers(0, cfg.vocab, R).astype(np.int32)
+            pos = np.full(R, t, np.int32)
+            dec.set_inputs(tokens, pos)
+            dec.execute()
+            x_ref, logits_ref, next_ref = ref.step(tokens, pos)
+            x = dec.store.read(dec.x).reshape(R, cfg.hidden)
+            logits = dec.store.read(dec.logits).reshape(R, cfg.vocab)
+            worst["hidden"] = max(worst["hidden"], rel_l2(x, x_ref))
+            worst["logits"] = max(worst["logits"], rel_l2(logits, logits_ref))
+            top2 = np.sort(logits_ref, axis=-1)[:, -2:]
+            clear = (top2[:, 1] - top2[:, 0]) > 4 * REAL_TOL * np.abs(logits_ref).max()
+            assert np.array_equal(dec.read_next_tokens()[clear], next_ref[clear])
+        print(f"\nreal-width decoder layer, R={R}: rel-L2 hidden {worst['hidden']:.3e}, logits {worst['logits']:.3e}")
+        assert worst["hidden"] <= REAL_TOL and worst["logits"] <= REAL_TOL
+    finally:
+        dec.deinit()
+
+
+def test_a_request_decodes_the_same_alone_in_8_and_in_64(backend):
+    """Batch sharding over GPUs changes how many requests share a step. Every batch size below the
+    prefill threshold runs the same int8 arithmetic, so a request's logits agree across batch sizes to
+    f32 summation order (plus the odd flipped activation rounding that follows from it)."""
+    cfg = REAL
+    w, emb = make_values(cfg, seed=22)
+    tokens = (np.arange(64) * 37 + 11) % cfg.vocab
+    outs = {}
+    for R in (1, 8, 64):
+        dec = build(backend, cfg, R, w, emb)
+        try:
+            _prefill(dec, None, cfg, R, 300, seed=3, total=64)  # request r gets the same cache rows in every batch size
+            dec.set_inputs(tokens[:R], np.full(R, 300, np.int32))
+            dec.execute()
+            outs[R] = dec.store.read(dec.logits).reshape(R, cfg.vocab).copy()
+        finally:
+            dec.deinit()
+    d8, d1 = rel_l2(outs[64][:8], outs[8]), rel_l2(outs[64][:1], outs[1])
+    print(f"\nsame request across batch sizes: 64 vs 8 rel-L2 {d8:.3e}, 64 vs 1 {d1:.3e}")
+    assert d8 <= 1e-3 and d1 <= 1e-3
+
+
+def test_images_do_not_change_a_decoder_step(backend):
+    """Producers writing the activation images against every matmul quantizing for itself: the codes are
+    the same, so the logits are bit-equal (8 requests: both forms run the same matmul kernel)."""
+    cfg, R = SMALL, 8
+    w, emb = make_values(cfg, seed=31)
+    outs = []
+    for images in (False, True):
+        dec = SyntheticDecoder(backend, cfg, R, lambda name, k, n: w[name], lambda v0, v1: emb[v0:v1], images=images)
+        try:
+            assert dec.images == images
+            for t in range(3):
+                dec.set_inputs(np.arange(R) + t, np.full(R, t, np.int32))
+                dec.execute()
+            outs.append(dec.store.read(dec.logits).copy())
+        finally:
+            dec.deinit()
+    assert np.array_equal(outs[0], outs[1])

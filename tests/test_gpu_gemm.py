@@ -10,7 +10,7 @@ import pytest
 
 import oracle
 from aion_b200 import capi
-from tests.gpu_util import run_matmul
+from tests.gpu_util import matmul_plan, run_matmul
 
 pytestmark = pytest.mark.gpu
 
@@ -65,16 +65,53 @@ def test_gemm_alpha_beta_and_leading_dims(backend, dtype):
 
 
 @pytest.mark.parametrize("dtype", [capi.DTYPE_Q4_0, capi.DTYPE_Q8_0])
-def test_gemm_prefill_shape_auto_route(backend, dtype):
-    # BASELINE config 3, m = 512: routed to the tensor-core kernel by m alone.
+def test_gemm_prefill_m512(backend, dtype):
+    # The prefill configuration with m = 512 on the tensor-core kernel (128-token tiles: 256 of them).
     m, n, k = 512, 8192, 2048
     a, b = make(dtype, m, n, k, seed=7)
-    got = run_matmul(backend, dtype, a, b, m, n, k)
+    plan = matmul_plan(backend, dtype, m, n, k, flags=capi.MATMUL_FORCE_GEMM)
+    assert plan.kernel == capi.KERNEL_GEMM and plan.tile_rows == 128 and plan.k_splits == 1
+    got = run_matmul(backend, dtype, a, b, m, n, k, flags=capi.MATMUL_FORCE_GEMM)
     want_i8 = oracle.fast_matmul_q(dtype, a, b, m, n, k).reshape(m, n)
     assert rel_l2(got, want_i8) <= TOL_INT8A
     # linearity in alpha, exactly: the epilogue multiplies the same accumulators
-    got2 = run_matmul(backend, dtype, a, b, m, n, k, alpha=2.0)
+    got2 = run_matmul(backend, dtype, a, b, m, n, k, alpha=2.0, flags=capi.MATMUL_FORCE_GEMM)
     assert np.array_equal(got2, 2.0 * got)
+
+
+@pytest.mark.parametrize("dtype", [capi.DTYPE_Q4_0, capi.DTYPE_Q8_0])
+def test_gemm_prefill_m2048_takes_256_token_tiles(backend, dtype):
+    """The prefill configuration with m = 2048, routed by m alone: 8 x 32 = 256 tiles of 256 tokens, at
+    least one per SM, so the kernel variant whose dequantized weight tile feeds two MMAs runs."""
+    m, n, k = 2048, 8192, 2048
+    plan = matmul_plan(backend, dtype, m, n, k)
+    assert plan.kernel == capi.KERNEL_GEMM and plan.tile_rows == 256 and plan.k_splits == 1
+    a, b = make(dtype, m, n, k, seed=8)
+    got = run_matmul(backend, dtype, a, b, m, n, k)
+    want_i8 = oracle.fast_matmul_q(dtype, a, b, m, n, k).reshape(m, n)
+    assert rel_l2(got, want_i8) <= TOL_INT8A
+    # a slice of the f32-activation reference (the scalar oracle is slow at this size): rows from every tile row
+    rows = np.concatenate([np.arange(0, 8), np.arange(250, 262), np.arange(1020, 1030), np.arange(2040, 2048)])
+    want_deq = oracle.matmul_deqf32(dtype, a[rows], b, len(rows), n, k).reshape(len(rows), n)
+    assert rel_l2(got[rows], want_deq) <= TOL_DEQ
+
+
+@pytest.mark.parametrize("dtype", [capi.DTYPE_Q4_0, capi.DTYPE_Q8_0])
+def test_gemm_256_token_tiles_ragged_alpha_beta_ldc(backend, dtype):
+    """256-token tiles with a ragged last tile row (m = 300 = 256 + 44), alpha / beta and a C wider than n."""
+    m, n, k, ldc = 300, 38400, 256, 38400 + 8
+    plan = matmul_plan(backend, dtype, m, n, k, flags=capi.MATMUL_FORCE_GEMM)
+    assert plan.kernel == capi.KERNEL_GEMM and plan.tile_rows == 256
+    a, b = make(dtype, m, n, k, seed=9)
+    c0 = np.random.default_rng(4).standard_normal(m * ldc).astype(np.float32)
+    got = run_matmul(backend, dtype, a, b, m, n, k, ldc=ldc, alpha=0.5, beta=-1.25, c=c0, flags=capi.MATMUL_FORCE_GEMM)
+    c0m = c0.reshape(m, ldc)
+    want_i8 = 0.5 * oracle.fast_matmul_q(dtype, a, b, m, n, k).reshape(m, n) - 1.25 * c0m[:, :n]
+    assert rel_l2(got[:, :n], want_i8) <= TOL_INT8A
+    rows = np.concatenate([np.arange(0, 6), np.arange(252, 260), np.arange(294, 300)])
+    want_deq = 0.5 * oracle.matmul_deqf32(dtype, a[rows], b, len(rows), n, k).reshape(len(rows), n) - 1.25 * c0m[rows][:, :n]
+    assert rel_l2(got[rows][:, :n], want_deq) <= TOL_DEQ
+    assert np.array_equal(got[:, n:], c0m[:, n:])
 
 
 @pytest.mark.parametrize("dtype", [capi.DTYPE_Q4_0, capi.DTYPE_Q8_0])
@@ -100,7 +137,7 @@ def test_gemm_is_deterministic(backend):
 
 @pytest.mark.parametrize("m", [17, 29, 32])
 def test_rows_between_gemv_and_gemm_keep_int8_arithmetic(backend, m):
-    # 17..32 rows run as two groups of 16 rows in one GEMV launch: reference CPU arithmetic, tight bound.
+    # 17..32 rows run as one group of 32 rows of the int8 kernel: reference CPU arithmetic, tight bound.
     n, k = 264, 256
     a, b = make(capi.DTYPE_Q4_0, m, n, k, seed=5)
     got = run_matmul(backend, capi.DTYPE_Q4_0, a, b, m, n, k)
@@ -118,7 +155,7 @@ def test_gemm_nt_q8_prefill(backend, order, m, n, k):
     a = rng.standard_normal((m, k)).astype(np.float32)
     rows = oracle.quantize(oracle.Q8_0, w, 1)
     tile = oracle.relayout_q8(order, n, k, rows)
-    got = run_matmul_nt(backend, a, tile, m, n, k, order=order)
+    got = run_matmul_nt(backend, a, tile, m, n, k, order=order, flags=capi.MATMUL_FORCE_GEMM)
     want_i8 = oracle.matmul_nt_q8(a, rows, m, n, k).reshape(m, n)
     kmajor = oracle.quantize(oracle.Q8_0, np.ascontiguousarray(w.T), 0)
     want_deq = oracle.matmul_deqf32(oracle.Q8_0, a, kmajor, m, n, k).reshape(m, n)
@@ -128,8 +165,8 @@ def test_gemm_nt_q8_prefill(backend, order, m, n, k):
 
 @pytest.mark.parametrize("m,n,k", [(33, 8, 32), (129, 16, 64), (256, 256, 32)])
 def test_gemm_smallest_and_ragged_shapes(backend, m, n, k):
-    # the smallest m the GEMM is routed, a single K block, n far below a tile
+    # small m, a single K block, n far below a tile
     a, b = make(capi.DTYPE_Q8_0, m, n, k, seed=41)
-    got = run_matmul(backend, capi.DTYPE_Q8_0, a, b, m, n, k)
+    got = run_matmul(backend, capi.DTYPE_Q8_0, a, b, m, n, k, flags=capi.MATMUL_FORCE_GEMM)
     want = oracle.matmul_deqf32(capi.DTYPE_Q8_0, a, b, m, n, k).reshape(m, n)
     assert rel_l2(got, want) <= TOL_DEQ

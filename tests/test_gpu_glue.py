@@ -9,7 +9,8 @@ import pytest
 import oracle
 from aion_b200 import capi
 from aion_b200.backend import (BackendError, DeviceStore, StepArgMax, StepCast, StepElemwiseBinary, StepGatherRows,
-                               StepRMSNorm, StepRoPE1D, StepSequenceAppend, TensorMeta)
+                               StepRMSNorm, StepRMSNormPair, StepRoPE1D, StepSequenceAppend, TensorMeta, act_image_meta)
+from tests.gpu_util import DevBuf, make_image
 
 pytestmark = pytest.mark.gpu
 
@@ -70,6 +71,65 @@ def test_elemwise_bit_exact(sess, op, code, n):
     to = store.add(TensorMeta(F32, a.shape))
     s.execute([StepElemwiseBinary(op=op, out=to, a=ta, b=tb)])
     assert np.array_equal(store.read(to), oracle.elemwise(code, a, b))
+
+
+# ---- producers that also write the quantized image of their output ---------------------------
+def _image_of(backend, store, tid, rows, cols, dtype):
+    """The image aion_cuda_act_image makes of a tensor's f32 values: what a fused producer must equal."""
+    vals = store.read(tid).reshape(rows, cols)
+    a = DevBuf(backend, vals)
+    img = make_image(backend, dtype, a, rows, cols)
+    try:
+        return img.read(np.uint8)
+    finally:
+        a.free()
+        img.free()
+
+
+@pytest.mark.parametrize("dtype", [capi.DTYPE_Q4_0, capi.DTYPE_Q8_0])
+@pytest.mark.parametrize("rows,cols", [(1, 1536), (8, 1536), (20, 256), (64, 1536), (70, 4096), (3, 2080)])
+def test_rms_norm_writes_the_image_of_its_output(sess, backend, dtype, rows, cols):
+    s, store = sess
+    rng = np.random.default_rng(rows + cols)
+    x = rng.standard_normal((rows, cols)).astype(np.float32)
+    g = rng.standard_normal(cols).astype(np.float32)
+    b = rng.standard_normal(cols).astype(np.float32)
+    res = rng.standard_normal((rows, cols)).astype(np.float32)
+    tx, tg, tb, tr = put(store, x, F32), put(store, g, F32), put(store, b, F32), put(store, res, F32)
+    to, to2 = store.add(TensorMeta(F32, (rows, cols))), store.add(TensorMeta(F32, (rows, cols)))
+    ti = store.add(act_image_meta(rows, cols, dtype))
+    s.execute([StepRMSNorm(out=to, x=tx, gamma=tg, beta=tb, eps=1e-6, image=ti)])
+    assert np.array_equal(store.read(ti).view(np.uint8), _image_of(backend, store, to, rows, cols, dtype))
+    np.testing.assert_allclose(store.read(to), oracle.rms_norm(x, g, b, 1e-6), rtol=1e-5, atol=1e-6)
+    # the pair: the image is that of the second output
+    s.execute([StepRMSNormPair(out1=to, out2=to2, x=tx, gamma1=tg, beta1=tb, gamma2=tg, beta2=tb, eps1=1e-6, eps2=1e-5,
+                               residual=tr, image=ti)])
+    assert np.array_equal(store.read(ti).view(np.uint8), _image_of(backend, store, to2, rows, cols, dtype))
+    first = oracle.rms_norm(x, g, b, 1e-6, residual=res)
+    np.testing.assert_allclose(store.read(to), first, rtol=1e-5, atol=1e-6)
+    np.testing.assert_allclose(store.read(to2), oracle.rms_norm(first, g, b, 1e-5), rtol=2e-5, atol=2e-6)
+
+
+@pytest.mark.parametrize("dtype", [capi.DTYPE_Q4_0, capi.DTYPE_Q8_0])
+@pytest.mark.parametrize("rows,cols", [(1, 8192), (8, 8192), (65, 512), (3, 96)])
+def test_gate_writes_the_image_of_its_output(sess, backend, dtype, rows, cols):
+    # the two halves of a [gate | up] matmul output, as the fused decoder reads them
+    s, store = sess
+    rng = np.random.default_rng(cols)
+    gu = (rng.standard_normal((rows, 2 * cols)) * 3).astype(np.float32)
+    tgu = put(store, gu, F32)
+    ch = store.acquire_const(tgu)
+    half = TensorMeta(F32, (rows, cols), row_stride=2 * cols)
+    from aion_b200.backend import Chunk
+
+    tgate = store.bind(half, Chunk(ch.handle, ch.offset, ch.len))
+    tup = store.bind(half, Chunk(ch.handle, ch.offset + cols * 4, ch.len - cols * 4))
+    to = store.add(TensorMeta(F32, (rows, cols)))
+    ti = store.add(act_image_meta(rows, cols, dtype))
+    s.execute([StepElemwiseBinary(op="gate", out=to, a=tgate, b=tup, image=ti)])
+    want = oracle.elemwise(2, np.ascontiguousarray(gu[:, :cols]), np.ascontiguousarray(gu[:, cols:]))
+    assert np.array_equal(store.read(to), want)
+    assert np.array_equal(store.read(ti).view(np.uint8), _image_of(backend, store, to, rows, cols, dtype))
 
 
 @pytest.mark.parametrize("shape,prop", [((2, 1, 8, 256), 1.0), ((3, 5, 1, 64), 1.0), ((1, 2, 4, 128), 0.25)])

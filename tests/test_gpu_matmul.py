@@ -12,7 +12,7 @@ import oracle
 from aion_b200 import capi
 from aion_b200.backend import (BackendError, CudaBackend, DeviceStore, StepMatMul, StepMatMulNT, TensorMeta)
 from tests import refdata as rd
-from tests.gpu_util import run_matmul, run_matmul_nt
+from tests.gpu_util import DevBuf, image_bytes, make_image, matmul_plan, run_matmul, run_matmul_nt
 
 pytestmark = pytest.mark.gpu
 
@@ -95,6 +95,165 @@ def test_kmajor_gemv_all_m(backend, dtype, m):
     want = oracle.matmul_q(dtype, x, b, m, n, k)
     got = run_matmul(backend, dtype, x, b, m, n, k, flags=capi.MATMUL_FORCE_GEMV)
     assert rd.rel_l2(got, want) < TIGHT
+
+
+# ---- decode batches beyond 16 rows: the same int8 arithmetic, weights streamed once per 64 rows ----
+@pytest.mark.parametrize("dtype", [capi.DTYPE_Q8_0, capi.DTYPE_Q4_0])
+@pytest.mark.parametrize("m", [17, 29, 32, 33, 48, 64, 65, 100, 128, 200, 512])
+def test_decode_batches_keep_int8_arithmetic(backend, dtype, m):
+    # 128-column tiles (two tiles and a tail of 8 columns), a K that is not whole stages
+    n, k = 264, 2080
+    x = rd.synth_acts(m, k, seed=m)
+    b = oracle.quantize(dtype, rd.synth_weights(k, n, seed=7), 0)
+    want = oracle.fast_matmul_q(dtype, x, b, m, n, k)
+    plan = matmul_plan(backend, dtype, m, n, k)
+    assert plan.kernel == capi.KERNEL_INT8 and plan.tile_cols == 128 and plan.tile_rows == (32 if m <= 32 else 64)
+    got = run_matmul(backend, dtype, x, b, m, n, k)
+    assert rd.rel_l2(got, want) < TIGHT
+
+
+@pytest.mark.parametrize("m", [24, 64, 130])
+def test_decode_batches_nt(backend, m):
+    n, k = 328, 1024
+    x = rd.synth_acts(m, k, seed=m)
+    b = oracle.quantize(oracle.Q8_0, rd.synth_weights(n, k, seed=3), 1)
+    want = oracle.fast_matmul_nt_q8(x, b, m, n, k)
+    assert rd.rel_l2(run_matmul_nt(backend, x, b, m, n, k), want) < TIGHT
+
+
+@pytest.mark.parametrize("dtype", [capi.DTYPE_Q8_0, capi.DTYPE_Q4_0])
+def test_decode_batch_at_decoder_widths_alpha_beta_ldc(backend, dtype):
+    # the synthetic decoder's gate/up projection for 64 requests, written into a wider C
+    m, n, k, ldc = 64, 16384, 1536, 16384 + 8
+    x = rd.synth_acts(m, k, seed=1)
+    b = oracle.quantize(dtype, rd.synth_weights(k, n, seed=2), 0)
+    c0 = rd.synth_acts(m, ldc, seed=3)
+    want = oracle.fast_matmul_q(dtype, x, b, m, n, k)
+    got = run_matmul(backend, dtype, x, b, m, n, k, ldc=ldc, alpha=0.5, beta=-2.0, c=c0)
+    assert rd.rel_l2(got[:, :n], 0.5 * want - 2.0 * c0[:, :n]) < TIGHT
+    assert np.array_equal(got[:, n:], c0[:, n:])
+
+
+def test_a_request_does_not_depend_on_its_batch(backend):
+    """Rows decoded alone, in a batch of 8 and in a batch of 64 take different kernel variants
+    (8-, 64-row groups; different K splits) but the same arithmetic: equal to f32 summation order."""
+    n, k = 1536, 2048
+    x = rd.synth_acts(64, k, seed=9)
+    b = oracle.quantize(oracle.Q4_0, rd.synth_weights(k, n, seed=10), 0)
+    full = run_matmul(backend, capi.DTYPE_Q4_0, x, b, 64, n, k)
+    eight = run_matmul(backend, capi.DTYPE_Q4_0, x[:8], b, 8, n, k)
+    one = run_matmul(backend, capi.DTYPE_Q4_0, x[:1], b, 1, n, k)
+    assert rd.rel_l2(full[:8], eight) < TIGHT
+    assert rd.rel_l2(full[:1], one) < TIGHT
+
+
+# ---- the quantized-activation image ---------------------------------------------------------
+def _oracle_image_blocks(x, dtype):
+    """(codes int8 [m, k], scales f32 [m, k/32]) of the reference activation quantizer."""
+    m, k = x.shape
+    q, s = oracle.quantize_activation(x)
+    return q.reshape(m, k), s.reshape(m, k // 32)
+
+
+def _decode_image(raw, m, k, dtype):
+    """Undo the image layout (groups of rows, padded K blocks, fragment order): codes [m, k], scales [m, k/32]."""
+    kb = k // 32
+    kb_pad = (kb + 7) // 8 * 8
+    rpg = 2 if m <= 1 else 8 if m <= 8 else 16 if m <= 16 else 32 if m <= 32 else 64
+    groups = 1 if m <= 64 else (m + 63) // 64
+    gbytes = kb_pad * rpg * 36
+    assert raw.size == groups * gbytes
+    codes = np.zeros((m, k), np.int8)
+    scales = np.zeros((m, kb), np.float32)
+    for g in range(groups):
+        blob = raw[g * gbytes:(g + 1) * gbytes]
+        cq = blob[: kb_pad * rpg * 32].view(np.int8).reshape(kb_pad, rpg, 8, 4)
+        cs = blob[kb_pad * rpg * 32:].view(np.float32).reshape(kb_pad, rpg)
+        for r in range(rpg):
+            row = g * rpg + r
+            if row >= m:
+                assert not cq[:, r].any() and not cs[:, r].any()
+                continue
+            assert not cq[kb:, r].any() and not cs[kb:, r].any()
+            w = cq[:kb, r]  # [kb, 8 words, 4 bytes]
+            if dtype == capi.DTYPE_Q8_0:
+                # word 2j = codes 4j..4j+3, word 2j+1 = codes 16+4j..
+                lo = w[:, 0::2].reshape(kb, 16)
+                hi = w[:, 1::2].reshape(kb, 16)
+                codes[row] = np.concatenate([lo, hi], axis=1).reshape(-1)
+            else:
+                # word 2j = elements 8j+{0,2,4,6}, word 2j+1 = elements 8j+{1,3,5,7}
+                blk = np.zeros((kb, 32), np.int8)
+                for j in range(4):
+                    blk[:, 8 * j + 0:8 * j + 8:2] = w[:, 2 * j]
+                    blk[:, 8 * j + 1:8 * j + 8:2] = w[:, 2 * j + 1]
+                codes[row] = blk.reshape(-1)
+            scales[row] = cs[:kb, r] * (16.0 if dtype == capi.DTYPE_Q4_0 else 1.0)
+    return codes, scales
+
+
+@pytest.mark.parametrize("dtype", [capi.DTYPE_Q8_0, capi.DTYPE_Q4_0])
+@pytest.mark.parametrize("m,k", [(1, 96), (5, 2080), (16, 256), (40, 512), (64, 1536), (130, 320)])
+def test_act_image_holds_the_reference_quantization(backend, dtype, m, k):
+    x = rd.synth_acts(m, k, seed=m + k)
+    x[0, :32] = 0.0  # a zero block: zero codes, zero scale
+    a = DevBuf(backend, x)
+    img = make_image(backend, dtype, a, m, k)
+    try:
+        raw = img.read(np.uint8)
+        assert raw.size == image_bytes(m, k)
+        codes, scales = _decode_image(raw, m, k, dtype)
+        want_q, want_s = _oracle_image_blocks(x, dtype)
+        assert np.array_equal(codes, want_q)
+        assert np.array_equal(scales, want_s)
+    finally:
+        a.free()
+        img.free()
+
+
+@pytest.mark.parametrize("dtype", [capi.DTYPE_Q8_0, capi.DTYPE_Q4_0])
+@pytest.mark.parametrize("m", [1, 5, 16, 40, 64, 130])
+def test_matmul_with_image_equals_matmul_without(backend, dtype, m):
+    n, k = 520, 1024
+    x = rd.synth_acts(m, k, seed=m)
+    b = oracle.quantize(dtype, rd.synth_weights(k, n, seed=5), 0)
+    plain = run_matmul(backend, dtype, x, b, m, n, k)
+    with_image = run_matmul(backend, dtype, x, b, m, n, k, image=True)
+    if m == 1:  # alone, a single row is quantized inside the matmul and K may be split differently
+        assert rd.rel_l2(with_image, plain) < TIGHT
+    else:
+        assert np.array_equal(with_image, plain)
+    assert rd.rel_l2(with_image, oracle.fast_matmul_q(dtype, x, b, m, n, k)) < TIGHT
+
+
+def test_matmul_nt_with_image(backend):
+    m, n, k = 6, 256, 512
+    x = rd.synth_acts(m, k)
+    b = oracle.quantize(oracle.Q8_0, rd.synth_weights(n, k), 1)
+    assert np.array_equal(run_matmul_nt(backend, x, b, m, n, k, image=True), run_matmul_nt(backend, x, b, m, n, k))
+
+
+def test_image_operand_is_checked(backend):
+    m, n, k = 4, 64, 128
+    x = rd.synth_acts(m, k)
+    b = oracle.quantize(oracle.Q8_0, rd.synth_weights(k, n), 0)
+    bufs = [DevBuf(backend, x), DevBuf(backend, b), DevBuf(backend, nbytes=m * n * 4), DevBuf(backend, nbytes=image_bytes(m, k) - 16)]
+    try:
+        rec = capi.MatMul(c=bufs[2].operand(), a=bufs[0].operand(), b=bufs[1].operand(), b_dtype=capi.DTYPE_Q8_0, flags=0, m=m, n=n,
+                          k=k, lda=0, ldb=0, ldc=0, alpha=1.0, beta=0.0, a_image=bufs[3].operand())
+        assert backend._lib.aion_cuda_matmul(backend.handle, C.byref(rec)) == capi.INVALID_ARGUMENT  # image too short
+    finally:
+        for x_ in bufs:
+            x_.free()
+
+
+def test_plan_names_the_kernel(backend):
+    assert matmul_plan(backend, capi.DTYPE_Q4_0, 1, 8192, 2048).kernel == capi.KERNEL_INT8
+    assert matmul_plan(backend, capi.DTYPE_Q4_0, 512, 8192, 2048).kernel == capi.KERNEL_INT8
+    p = matmul_plan(backend, capi.DTYPE_Q4_0, 2048, 8192, 2048)
+    assert p.kernel == capi.KERNEL_GEMM and p.tile_cols == 256
+    assert matmul_plan(backend, capi.DTYPE_Q4_0, 3, 5, 64).kernel == capi.KERNEL_GENERIC  # n not a multiple of 8
+    assert matmul_plan(backend, capi.DTYPE_Q8_0, 64, 256, 256, flags=capi.MATMUL_FORCE_GEMM).kernel == capi.KERNEL_GEMM
 
 
 # ---- edges: tails, strides, epilogue -------------------------------------------------

@@ -70,3 +70,47 @@ def test_static_scratch_rejects_what_it_cannot_hold(backend):
         _run(backend, "aion_cuda_matmul_static_scratch", capi.DTYPE_Q4_0, rd.synth_acts(4, kk), bb, 4, 64, kk,
              np.zeros((4, 64), dtype=np.float32), 1.0, 0.0)
     assert e.value.name == "Unsupported" and "one launch" in str(e.value)
+
+
+@pytest.mark.parametrize("dtype", [capi.DTYPE_Q4_0, capi.DTYPE_Q8_0])
+def test_static_scratch_does_not_disturb_the_allocating_entry_point(backend, dtype):
+    """Both entry points run the same kernel for one row; the shared-memory allowance one of them
+    raised must survive a smaller call through the other."""
+    n = 512
+    big_k, small_k = 3072, 256
+    a_big, a_small = rd.synth_acts(1, big_k, seed=1), rd.synth_acts(1, small_k, seed=2)
+    b_big = _quantize(backend, dtype, rd.synth_weights(big_k, n, seed=3))
+    b_small = _quantize(backend, dtype, rd.synth_weights(small_k, n, seed=4))
+    c0 = np.zeros((1, n), dtype=np.float32)
+    first = _run(backend, "aion_cuda_matmul", dtype, a_big, b_big, 1, n, big_k, c0, 1.0, 0.0)
+    _run(backend, "aion_cuda_matmul_static_scratch", dtype, a_small, b_small, 1, n, small_k, c0, 1.0, 0.0)
+    again = _run(backend, "aion_cuda_matmul", dtype, a_big, b_big, 1, n, big_k, c0, 1.0, 0.0)
+    assert np.array_equal(again, first)
+
+
+def test_static_scratch_at_its_limits_and_leaves_device_memory_alone(backend):
+    """A grid that is clamped to the built-in scratch (more units than its 512 CTA slots), the deepest K of
+    one row, and no change in free device memory across a call on a shape this device has not seen."""
+    import torch
+
+    cases = [(capi.DTYPE_Q4_0, 1, 8192, 2048), (capi.DTYPE_Q8_0, 1, 256, 16384), (capi.DTYPE_Q4_0, 8, 4096, 4096)]
+    for dtype, m, n, k in cases:
+        a = rd.synth_acts(m, k, seed=k)
+        b = _quantize(backend, dtype, rd.synth_weights(k, n, seed=n))
+        c0 = np.zeros((m, n), dtype=np.float32)
+        bufs = [DevBuf(backend, a), DevBuf(backend, b), DevBuf(backend, c0)]
+        try:
+            rec = capi.MatMul(c=bufs[2].operand(), a=bufs[0].operand(), b=bufs[1].operand(), b_dtype=dtype, flags=0, m=m, n=n, k=k,
+                              lda=0, ldb=0, ldc=0, alpha=1.0, beta=0.0)
+            backend.sync()
+            free_before = torch.cuda.mem_get_info(0)[0]
+            assert backend._lib.aion_cuda_matmul_static_scratch(backend.handle, C.byref(rec)) == capi.OK
+            backend.sync()
+            assert torch.cuda.mem_get_info(0)[0] == free_before
+            got = bufs[2].read(np.float32).reshape(m, n)
+        finally:
+            for x in bufs:
+                x.free()
+        import oracle
+
+        assert rd.rel_l2(got, oracle.fast_matmul_q(dtype, a, b, m, n, k)) < TIGHT

@@ -142,9 +142,11 @@ def decode_leg(torch, dist, backend: CudaBackend, rank: int, world: int, local_r
 
 
 def gemm_leg(torch, backend: CudaBackend, local_rank: int, dtype: int, m: int, n: int, k: int, iters: int = 20, copies: int = 8,
-             peak_tflops: float = 1622.7, nt: bool = False) -> dict:
+             peak_tflops: float = 1622.7, nt: bool = False, kernel: str = "gemm") -> dict:
     """Prefill GEMM TFLOP/s: `copies` distinct weight matrices walked in turn, device-timed.
-    nt: the `MatMulNT` step (q8_0 [n, k] row-major weights) instead of `MatMul`."""
+    nt: the `MatMulNT` step (q8_0 [n, k] row-major weights) instead of `MatMul`.
+    kernel: "gemm" = the tcgen05 kernel (bf16 operands), "int8" = the int8-activation kernel, "auto" = by m."""
+    flags = {"gemm": capi.MATMUL_FORCE_GEMM, "int8": capi.MATMUL_FORCE_GEMV, "auto": capi.MATMUL_AUTO}[kernel]
     lib, dev, mem = backend._lib, backend.handle, backend.device_memory
     bb = 18 if dtype == capi.DTYPE_Q4_0 else 34
     nb = (k // 32) * n * bb
@@ -166,12 +168,12 @@ def gemm_leg(torch, backend: CudaBackend, local_rank: int, dtype: int, m: int, n
     hc = mem.alloc(m * n * 4, 256)
     if nt:
         recs = [capi.MatMulNT(c=capi.Operand(hc, 0, m * n * 4), a=capi.Operand(ha, 0, a.nbytes), b=capi.Operand(h, 0, nb),
-                              b_dtype=dtype, block_order=capi.ORDER_ROW_MAJOR, flags=0, reserved=0, m=m, n=n, k=k, lda=0, ldc=0,
+                              b_dtype=dtype, block_order=capi.ORDER_ROW_MAJOR, flags=flags, reserved=0, m=m, n=n, k=k, lda=0, ldc=0,
                               c_off=0, alpha=1.0, beta=0.0) for h in hb]
         call = lib.aion_cuda_matmul_nt
     else:
         recs = [capi.MatMul(c=capi.Operand(hc, 0, m * n * 4), a=capi.Operand(ha, 0, a.nbytes), b=capi.Operand(h, 0, nb),
-                            b_dtype=dtype, flags=capi.MATMUL_AUTO, m=m, n=n, k=k, lda=0, ldb=0, ldc=0, alpha=1.0, beta=0.0)
+                            b_dtype=dtype, flags=flags, m=m, n=n, k=k, lda=0, ldb=0, ldc=0, alpha=1.0, beta=0.0)
                 for h in hb]
         call = lib.aion_cuda_matmul
     for i in range(3):
@@ -189,9 +191,10 @@ def gemm_leg(torch, backend: CudaBackend, local_rank: int, dtype: int, m: int, n
     for h in hb + [ha, hc]:
         mem.free(h)
     return {"dtype": "q4_0" if dtype == capi.DTYPE_Q4_0 else "q8_0", "step": "MatMulNT [n,k]" if nt else "MatMul [k/32][n]",
-            "m": m, "n": n, "k": k, "ms": round(ms, 4), "tflops": round(tf, 1),
+            "kernel": kernel, "m": m, "n": n, "k": k, "ms": round(ms, 4), "tflops": round(tf, 1),
             "frac_of_measured_bf16_peak": round(tf / peak_tflops, 4),
-            "includes": ("block permutation to K-major + " if nt else "") + "f32->bf16 activation pre-pass + GEMM kernel per call"}
+            "includes": ("activation quantization + int8 kernel per call" if kernel == "int8" else
+                         ("block permutation to K-major + " if nt else "") + "f32->bf16 activation pre-pass + GEMM kernel per call")}
 
 
 def attention_leg(torch, backend: CudaBackend, local_rank: int, batch: int, t_ctx: int, iters: int = 20,

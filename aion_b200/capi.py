@@ -16,7 +16,7 @@ ORDER_ROW_MAJOR, ORDER_LANES4, ORDER_LANES8, ORDER_LANES16, ORDER_LANES32, ORDER
 WINDOW_UNBOUNDED = 0xFFFFFFFF
 MATMUL_AUTO, MATMUL_FORCE_GENERIC, MATMUL_FORCE_GEMV, MATMUL_FORCE_GEMM = 0, 1, 2, 4
 INT8_GROUP_ROWS = 64
-GEMM_MIN_M = 513
+GEMM_MIN_M = 33
 KERNEL_GENERIC, KERNEL_INT8, KERNEL_GEMM = 1, 2, 3
 ELEMWISE_ADD, ELEMWISE_MUL, ELEMWISE_GATE_GELU = 0, 1, 2
 RECORD_LANES = 8

@@ -2,10 +2,11 @@
 // C[m,n] = alpha * A[m,k] . dequant(B)[k,n] + beta * C for m beyond the decode GEMV.
 //
 // This is the one dense contraction of the hot path, so unlike the GEMV it is tensor-pipe
-// bound. Arithmetic: A is rounded to bf16, B is dequantized to bf16 (w = (code) * scale),
-// products accumulate in f32 in tensor memory; against the reference's int8-activation
-// CPU arithmetic (src/aion/backend/cpu/kernels/matmul_q_i8.zig:385-497) that is a
-// different rounding of the same product, bounded by rel-L2 1e-2.
+// bound. Arithmetic: A is quantized to int8 per 32-block as the reference does and its
+// dequantized value rounded to bf16, B is dequantized to bf16 (w = code * scale), products
+// accumulate in f32 in tensor memory; against the reference's int8-activation CPU arithmetic
+// (src/aion/backend/cpu/kernels/matmul_q_i8.zig:385-497) that is the same product with both
+// factors rounded to bf16, bounded by rel-L2 1e-2 (observed about 2e-3).
 //
 // Shape of the kernel (one persistent CTA per SM, 128 x 256 output tiles, K in steps of 64):
 //   warp 0      TMA producer of bf16 activation tiles (128B-swizzled, straight into the MMA
@@ -89,21 +90,39 @@ struct GemmGeom {
   static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 };
 
-// ---- f32 -> bf16 pre-pass ------------------------------------------------------------
-// Row-major [m, k] bf16 with k a multiple of 32. `permute`: inside every group of 8
-// consecutive k, position p holds element (p >> 1) + 4 * (p & 1), i.e. the order
-// e0 e4 e1 e5 e2 e6 e3 e7 in which a word of q4 nibbles unpacks two at a time.
-__global__ void convert_a_bf16_kernel(const float* __restrict__ a, uint64_t lda, __nv_bfloat16* __restrict__ out, uint32_t m,
-                                      uint32_t k, int permute) {
+// ---- activation pre-pass: f32 -> the reference's int8 quantization -> bf16 ---------------
+// Row-major [m, k] bf16 with k a multiple of 32. Every 32-block of A is quantized to int8 exactly
+// as the reference CPU kernels quantize it (src/aion/backend/cpu/kernels/matmul_q_i8.zig:187-203)
+// and the value written is code * scale rounded to bf16: the GEMM then multiplies the operands
+// the reference multiplies, and differs from it only by the bf16 rounding of both. (Rounding the
+// raw activation to bf16 instead leaves the whole int8 quantization error, about 5e-3, between
+// the two.) Four consecutive threads hold one block, eight elements each.
+// `permute`: inside every group of 8 consecutive k, position p holds element (p >> 1) + 4 * (p & 1),
+// i.e. the order e0 e4 e1 e5 e2 e6 e3 e7 in which a word of q4 nibbles unpacks two at a time.
+__global__ void __launch_bounds__(256) convert_a_bf16_kernel(const float* __restrict__ a, uint64_t lda, __nv_bfloat16* __restrict__ out, uint32_t m,
+                                                             uint32_t k, int permute) {
   ptx::pdl_launch_dependents();
   ptx::pdl_wait();
-  const uint64_t groups = (uint64_t)m * (k / 8);
-  for (uint64_t gi = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; gi < groups; gi += (uint64_t)gridDim.x * blockDim.x) {
-    const uint32_t r = (uint32_t)(gi / (k / 8)), g8 = (uint32_t)(gi % (k / 8));
+  const uint64_t groups = (uint64_t)m * (k / 8), stride = (uint64_t)gridDim.x * blockDim.x;
+  const uint64_t trips = (groups + stride - 1) / stride;
+  uint64_t gi = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x;
+  for (uint64_t trip = 0; trip < trips; trip++, gi += stride) {  // every lane makes every trip: the shuffles need whole warps
+    const bool on = gi < groups;
+    const uint64_t gq = on ? gi : 0;
+    const uint32_t r = (uint32_t)(gq / (k / 8)), g8 = (uint32_t)(gq % (k / 8));
     const float* src = a + (uint64_t)r * lda + (uint64_t)g8 * 8;
     float v[8];
 #pragma unroll
-    for (int i = 0; i < 8; i++) v[i] = src[i];
+    for (int i = 0; i < 8; i++) v[i] = on ? src[i] : 0.0f;
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(v[i]));
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));
+    float scale, inv;
+    activation_block_scales(amax, &scale, &inv);
+#pragma unroll
+    for (int i = 0; i < 8; i++) v[i] = __fmul_rn((float)quantize_activation_with_inv(v[i], inv), scale);
     __nv_bfloat162 o[4];
     if (permute) {
 #pragma unroll
@@ -112,7 +131,7 @@ __global__ void convert_a_bf16_kernel(const float* __restrict__ a, uint64_t lda,
 #pragma unroll
       for (int i = 0; i < 4; i++) o[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
     }
-    *reinterpret_cast<uint4*>(out + (uint64_t)r * k + (uint64_t)g8 * 8) = *reinterpret_cast<const uint4*>(o);
+    if (on) *reinterpret_cast<uint4*>(out + (uint64_t)r * k + (uint64_t)g8 * 8) = *reinterpret_cast<const uint4*>(o);
   }
 }
 

@@ -1,7 +1,7 @@
 // Decode matmul for q4_0 / q8_0 weights with the reference's int8-activation arithmetic:
 // C[m,n] = alpha * A[m,k] . W + beta * C for the batch sizes of decoding (one row to a few
 // hundred rows of A). The weights are streamed from global memory exactly once per group of
-// up to 64 rows of A (blockIdx.y walks further groups of 64 rows; they find the weights in L2).
+// up to 64 rows of A (further groups of 64 rows are further tiles; they find the weights in L2).
 //
 // Arithmetic is the reference CPU kernels' (src/aion/backend/cpu/kernels/matvec_q.zig:62-160,
 // src/aion/backend/cpu/kernels/matmul_nt_q.zig:74-95, src/aion/backend/cpu/kernels/matmul_q_i8.zig:385-497):
@@ -50,9 +50,8 @@ namespace {
 
 constexpr int KBT = 8;             // K blocks per stage
 constexpr int NS = 2;              // stages in the ring: shallow, so that more CTAs (of concurrent launches) fit an SM
-constexpr int CONSUMER_WARPS = 4;
-constexpr int CONSUMER_THREADS = CONSUMER_WARPS * 32;
-constexpr int THREADS = CONSUMER_THREADS + 32;
+constexpr int COL_WARPS = 4;                    // consumer warps side by side over a tile's columns
+constexpr int threads_of(int rw) { return (COL_WARPS * rw + 1) * 32; }
 constexpr int NT_ROW_PITCH = KBT * Q8_BYTES;  // 272: 16-byte multiple, 4 words mod 32 banks
 constexpr size_t ACT_BUDGET_BYTES = 40 * 1024;  // quantized activations kept per CTA when it quantizes them itself
 constexpr uint32_t MAGIC_BITS = 0x4B400000u;    // 1.5 * 2^23 as f32
@@ -64,11 +63,11 @@ struct GemvParams {
   uint32_t m, n, kblocks;
   uint64_t lda, ldc;
   float alpha, beta;
-  uint32_t tiles, stages_per_tile;
+  uint32_t tiles, col_tiles, stages_per_tile;  // tiles = col_tiles x groups of rows, group-major
   uint64_t units;
   uint32_t whole_tiles;  // CTA ranges are rounded to tile boundaries: no tile is shared
-  float* partials;       // [group][cta][2][TN * rows]
-  int* tickets;          // [group][tile][warp]
+  float* partials;       // [cta][2][TN * rows]
+  int* tickets;          // [tile][consumer warp]
   int* fault;
   uint32_t a_vec4;       // A rows may be read as float4
   uint32_t c_vec2;       // C may be written as float2 (even ldc, 8-byte aligned base)
@@ -249,35 +248,30 @@ __global__ void gemv_act_image_kernel(const float* __restrict__ a, uint64_t lda,
 }
 
 // DT: weight dtype; NT: weights are [n,k] row-major (else K-major); MT: groups of 8 activation
-// rows per CTA (1, 2, 4, 8); M1: exactly one activation row; RG: blockIdx.y picks a group of
-// 8 * MT rows; PREQ: the activation arrives as a pre-quantized image; CG: 16-column groups per warp.
-template <int DT, bool NT, int MT, bool M1, bool RG, bool PREQ, int CG>
-__global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_in, const __grid_constant__ CUtensorMap tmap) {
+// rows per tile (1, 2, 4, 8); M1: exactly one activation row; RG: A has several groups of
+// 8 * MT rows; PREQ: the activation arrives as a pre-quantized image; CG: 16-column groups
+// per warp; RW: consumer warps stacked over the activation rows (1: four warps take all MT row
+// groups, 2: eight warps, each MT / 2 of them — the warps a scheduler needs to hide the latency
+// of the MMA and shared-memory loads once there is this much arithmetic per weight byte).
+template <int DT, bool NT, int MT, bool M1, bool RG, bool PREQ, int CG, int RW>
+__global__ void __launch_bounds__(threads_of(RW), RW == 2 ? 2 : 1) gemv_q_mma_kernel(const GemvParams p_in, const __grid_constant__ CUtensorMap tmap) {
   using G = Geom<DT, NT, CG>;
   constexpr int TN = G::TN;
   constexpr int MPA = 8 * MT;  // activation rows of the accumulator tile
-  // (RG is a template parameter so that the usual kernel keeps reading its parameters from
-  // the constant bank instead of holding an adjusted copy in registers.)
-  // With row groups the group index is the fastest-varying block index, so that the CTAs that
-  // stream the same weight range run next to one another and all but the first find it in L2.
-  const uint32_t cta = RG ? blockIdx.y : blockIdx.x, n_ctas = RG ? gridDim.y : gridDim.x, row_group = RG ? blockIdx.x : 0;
-  GemvParams p_rows;
-  if (RG) {
-    p_rows = p_in;
-    const uint32_t r0 = row_group * MPA;
-    p_rows.a += (uint64_t)r0 * p_in.lda;
-    p_rows.c += (uint64_t)r0 * p_in.ldc;
-    p_rows.m = min((uint32_t)MPA, p_in.m - r0);
-    p_rows.partials += (size_t)row_group * n_ctas * 2 * TN * MPA;
-    p_rows.tickets += (size_t)row_group * p_in.tiles * CONSUMER_WARPS;
-  }
-  const GemvParams& p = RG ? p_rows : p_in;
+  constexpr int MTW = MT / RW;  // groups of 8 rows per warp
+  constexpr int CONSUMER_WARPS = COL_WARPS * RW, CONSUMER_THREADS = CONSUMER_WARPS * 32;
+  static_assert(MT % RW == 0, "row groups divide over the row warps");
+  // RG: A has more than 8 * MT rows. The tile index then runs over (group of rows, column tile),
+  // group-major, and every group streams the weights again (the later ones find them in L2).
+  const GemvParams& p = p_in;
+  const uint32_t cta = blockIdx.x, n_ctas = gridDim.x;
   constexpr uint32_t MP2 = M1 ? 2 : 8 * MT;  // activation rows held in shared memory
   extern __shared__ __align__(128) uint8_t smem[];
   const uint32_t smem_base = ptx::smem_u32(smem);
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, j = lane & 3;
+  const int wc = warp % COL_WARPS, wr = warp / COL_WARPS;  // consumer warp: column position, row half
 
   const uint64_t U = p.units, NG = n_ctas;
   const uint32_t Sg = p.stages_per_tile;
@@ -319,13 +313,13 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_
     // into the stage's slot of the activation ring. The image comes from the previous kernel,
     // so those copies wait for it; the weight copies of the first NS stages do not, and start
     // at once.
-    const uint8_t* image = PREQ ? p.act_image + (size_t)row_group * p.act_image_bytes : nullptr;
-    auto issue_acts = [&](uint32_t slot_, uint32_t s_) {
+    auto issue_acts = [&](uint32_t slot_, uint32_t s_, uint32_t tile_) {
+      const uint8_t* image = p.act_image + (RG ? (size_t)(tile_ / p.col_tiles) * p.act_image_bytes : 0);
       const uint32_t dst = smem_base + G::OFF_ACT + slot_ * (AQ_SLICE + AS_SLICE), full = bar_full + 8 * slot_;
       ptx::bulk_g2s(dst, image + (size_t)s_ * AQ_SLICE, AQ_SLICE, full);
       ptx::bulk_g2s(dst + AQ_SLICE, image + (size_t)kb_pad * (MP2 * 32) + (size_t)s_ * AS_SLICE, AS_SLICE, full);
     };
-    uint32_t pend_s[NS];
+    uint32_t pend_s[NS], pend_tile[NS];
     uint32_t npend = 0;
     bool acts_open = !PREQ;
     for (uint64_t it = 0; it < n_units; it++) {
@@ -334,7 +328,7 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_
       if (PREQ && !acts_open && it == (uint64_t)NS) {
         ptx::pdl_wait();
         if (lane == 0)
-          for (uint32_t i = 0; i < npend; i++) issue_acts(i, pend_s[i]);
+          for (uint32_t i = 0; i < npend; i++) issue_acts(i, pend_s[i], pend_tile[i]);
         acts_open = true;
       }
       if (it >= (uint64_t)NS) {
@@ -353,12 +347,13 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_
         // Rows or columns past the tensor arrive as zeros (a zero scale), and the whole
         // box counts towards the barrier.
         ptx::mbar_arrive_expect_tx(full, G::STAGE_BYTES + (PREQ ? AQ_SLICE + AS_SLICE : 0));
-        if (!NT && DT == AION_CUDA_DTYPE_Q4_0 && CG == 1) ptx::tma_load_2d(stage, &tmap, (int32_t)(tile * (TN * G::BB / 8)), (int32_t)(s * KBT), full);
-        else if (!NT) ptx::tma_load_3d(stage, &tmap, 0, (int32_t)(tile * (TN / 8)), (int32_t)(s * KBT), full);
-        else ptx::tma_load_2d(stage, &tmap, (int32_t)(s * KBT * Q8_BYTES / 8), (int32_t)(tile * TN), full);
+        const uint32_t ct = RG ? tile % p.col_tiles : tile;  // column tile
+        if (!NT && DT == AION_CUDA_DTYPE_Q4_0 && CG == 1) ptx::tma_load_2d(stage, &tmap, (int32_t)(ct * (TN * G::BB / 8)), (int32_t)(s * KBT), full);
+        else if (!NT) ptx::tma_load_3d(stage, &tmap, 0, (int32_t)(ct * (TN / 8)), (int32_t)(s * KBT), full);
+        else ptx::tma_load_2d(stage, &tmap, (int32_t)(s * KBT * Q8_BYTES / 8), (int32_t)(ct * TN), full);
         if (PREQ) {
-          if (acts_open) issue_acts(slot, s);
-          else pend_s[npend] = s;
+          if (acts_open) issue_acts(slot, s, tile);
+          else pend_s[npend] = s, pend_tile[npend] = tile;
         }
       }
       if (PREQ && !acts_open) npend++;
@@ -373,7 +368,7 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_
     if (PREQ && !acts_open) {
       ptx::pdl_wait();
       if (lane == 0)
-        for (uint32_t i = 0; i < npend; i++) issue_acts(i, pend_s[i]);
+        for (uint32_t i = 0; i < npend; i++) issue_acts(i, pend_s[i], pend_tile[i]);
     }
     // After a failed wait nobody drains the ring: let the copies still in flight land
     // (bounded) before this CTA's shared memory can be handed to another CTA.
@@ -417,14 +412,15 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_
   // fragment) sit inside a stage, and where its activation fragments start.
   uint32_t off0, off1;
   if (!NT) {
-    off0 = (2 * warp + 8 * g) * G::BB;  // an even column: its codes start 2 bytes past a word boundary
-    off1 = off0 + G::BB;                // the odd column after it: codes word aligned
+    off0 = (2 * wc + 8 * g) * G::BB;  // an even column: its codes start 2 bytes past a word boundary
+    off1 = off0 + G::BB;              // the odd column after it: codes word aligned
   } else {
-    off0 = (16 * warp + g) * NT_ROW_PITCH;
+    off0 = (16 * wc + g) * NT_ROW_PITCH;
     off1 = off0 + 8 * NT_ROW_PITCH;
   }
-  const int col0 = NT ? 16 * warp + g : 2 * warp + 8 * g;
+  const int col0 = NT ? 16 * wc + g : 2 * wc + 8 * g;
   const int col1 = NT ? col0 + 8 : col0 + 1;
+  const int row_base = wr * MTW * 8;  // first activation row of this warp's row groups
   // Bytes per K block: MP2 rows of codes, MP2 scales. A lane supplies the codes of activation
   // row t*8+g (absent rows are zero codes with a zero scale) and applies the scales of rows
   // t*8+2j and t*8+2j+1. With a single activation row every lane reads row g % 2 and scale
@@ -432,12 +428,12 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_
   constexpr uint32_t AQ_STRIDE = MP2 * 32, AS_STRIDE = MP2 * 4;
   const uint32_t act_q_addr = smem_base + G::OFF_ACT;
   const uint32_t act_s_addr = act_q_addr + (PREQ ? KBT : kb_pad) * AQ_STRIDE;  // PREQ: inside a ring slot
-  const uint32_t aq_lane = act_q_addr + (g % MP2) * 32 + 8 * j;
-  const uint32_t as_lane = act_s_addr + (M1 ? 0 : j * 8);
+  const uint32_t aq_lane = act_q_addr + ((row_base + g) % MP2) * 32 + 8 * j;
+  const uint32_t as_lane = act_s_addr + (M1 ? 0 : (row_base + 2 * j) * 4);
 
-  uint64_t acc[MT][CG][2];
+  uint64_t acc[MTW][CG][2];
 #pragma unroll
-  for (int t = 0; t < MT; t++)
+  for (int t = 0; t < MTW; t++)
 #pragma unroll
     for (int c = 0; c < CG; c++) acc[t][c][0] = acc[t][c][1] = 0ull;
 
@@ -464,9 +460,20 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_
       // Ties every load below to this point: they cannot move above the wait.
       asm volatile("" : "+r"(w0), "+r"(w1), "+r"(b0), "+r"(b1), "+r"(aq), "+r"(as)::"memory");
       constexpr int STEP = NT ? Q8_BYTES : G::KM_PITCH;
-#define AION_BLOCK(K) block_step<DT, NT, MT, CG, K, STEP, G::CG_STRIDE, (int)AQ_STRIDE, (int)AS_STRIDE>(w0, w1, b0, b1, aq, as, acc)
-      AION_BLOCK(0); AION_BLOCK(1); AION_BLOCK(2); AION_BLOCK(3);
-      AION_BLOCK(4); AION_BLOCK(5); AION_BLOCK(6); AION_BLOCK(7);
+#define AION_BLOCK(K) block_step<DT, NT, MTW, CG, K, STEP, G::CG_STRIDE, (int)AQ_STRIDE, (int)AS_STRIDE>(w0, w1, b0, b1, aq, as, acc)
+      if (MTW * CG <= 2) {
+        AION_BLOCK(0); AION_BLOCK(1); AION_BLOCK(2); AION_BLOCK(3);
+        AION_BLOCK(4); AION_BLOCK(5); AION_BLOCK(6); AION_BLOCK(7);
+      } else {
+        // Many MMAs per K block: two blocks per trip of a real loop, so that the loop body stays
+        // inside the instruction cache closest to the schedulers (unrolled eight times it does not,
+        // and the warps then stall on instruction fetch more than on anything else).
+#pragma unroll 1
+        for (int kb2 = 0; kb2 < KBT; kb2 += 2) {
+          AION_BLOCK(0); AION_BLOCK(1);
+          w0 += 2 * STEP, w1 += 2 * STEP, b0 += 2 * STEP, b1 += 2 * STEP, aq += 2 * AQ_STRIDE, as += 2 * AS_STRIDE;
+        }
+      }
 #undef AION_BLOCK
       static_assert(KBT == 8, "eight K blocks per stage are spelled out above");
     }
@@ -477,11 +484,12 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_
       // ---------------- this CTA's share of `tile` is complete ----------------
       const uint64_t tile_u0 = (uint64_t)tile * Sg;
       const bool whole = (uu + 1 - tile_u0 == Sg) && (tile_u0 >= u_begin);
-      const uint32_t n0 = tile * TN;
+      const uint32_t grp = RG ? tile / p.col_tiles : 0;
+      const uint32_t n0 = (RG ? tile - grp * p.col_tiles : tile) * TN, r0 = grp * MPA;  // first column / row of the tile
       // v[t][c][0..3] = (col0, row 2j), (col0, row 2j+1), (col1, row 2j), (col1, row 2j+1)
-      float v[MT][CG][4];
+      float v[MTW][CG][4];
 #pragma unroll
-      for (int t = 0; t < MT; t++)
+      for (int t = 0; t < MTW; t++)
 #pragma unroll
         for (int c = 0; c < CG; c++) {
           unpack2(acc[t][c][0], v[t][c][0], v[t][c][1]);
@@ -494,11 +502,11 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_
         const uint32_t nparts = c_last - c_first + 1;
         float* mine = p.partials + ((size_t)cta * 2 + (tile == first_tile ? 0 : 1)) * (TN * MPA);
 #pragma unroll
-        for (int t = 0; t < MT; t++)
+        for (int t = 0; t < MTW; t++)
 #pragma unroll
           for (int c = 0; c < CG; c++) {
-            *reinterpret_cast<float2*>(mine + (col0 + 64 * c) * MPA + t * 8 + 2 * j) = make_float2(v[t][c][0], v[t][c][1]);
-            *reinterpret_cast<float2*>(mine + (col1 + 64 * c) * MPA + t * 8 + 2 * j) = make_float2(v[t][c][2], v[t][c][3]);
+            *reinterpret_cast<float2*>(mine + (col0 + 64 * c) * MPA + row_base + t * 8 + 2 * j) = make_float2(v[t][c][0], v[t][c][1]);
+            *reinterpret_cast<float2*>(mine + (col1 + 64 * c) * MPA + row_base + t * 8 + 2 * j) = make_float2(v[t][c][2], v[t][c][3]);
           }
         // The warp's stores are ordered before lane 0's release by the warp barrier; the
         // acquire side orders the last arriver's loads after every earlier release.
@@ -515,7 +523,7 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_
         if (last) {
           // The last part to arrive adds all of them in CTA order.
 #pragma unroll
-          for (int t = 0; t < MT; t++)
+          for (int t = 0; t < MTW; t++)
 #pragma unroll
             for (int c = 0; c < CG; c++) v[t][c][0] = v[t][c][1] = v[t][c][2] = v[t][c][3] = 0.0f;
           for (uint32_t part = 0; part < nparts; part++) {
@@ -523,11 +531,11 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_
             const uint32_t cc_first_tile = (uint32_t)((U * cc / NG) / Sg);
             const float* src = p.partials + ((size_t)cc * 2 + (tile == cc_first_tile ? 0 : 1)) * (TN * MPA);
 #pragma unroll
-            for (int t = 0; t < MT; t++)
+            for (int t = 0; t < MTW; t++)
 #pragma unroll
               for (int c = 0; c < CG; c++) {
-                const float2 x0 = __ldcg(reinterpret_cast<const float2*>(src + (col0 + 64 * c) * MPA + t * 8 + 2 * j));
-                const float2 x1 = __ldcg(reinterpret_cast<const float2*>(src + (col1 + 64 * c) * MPA + t * 8 + 2 * j));
+                const float2 x0 = __ldcg(reinterpret_cast<const float2*>(src + (col0 + 64 * c) * MPA + row_base + t * 8 + 2 * j));
+                const float2 x1 = __ldcg(reinterpret_cast<const float2*>(src + (col1 + 64 * c) * MPA + row_base + t * 8 + 2 * j));
                 v[t][c][0] += x0.x; v[t][c][1] += x0.y;
                 v[t][c][2] += x1.x; v[t][c][3] += x1.y;
               }
@@ -537,12 +545,12 @@ __global__ void __launch_bounds__(THREADS) gemv_q_mma_kernel(const GemvParams p_
       }
       if (store && !*abort_flag) {
 #pragma unroll
-        for (int t = 0; t < MT; t++)
+        for (int t = 0; t < MTW; t++)
 #pragma unroll
           for (int c = 0; c < CG; c++)
 #pragma unroll
             for (int rr = 0; rr < 2; rr++) {
-              const uint32_t mrow = t * 8 + 2 * j + rr;
+              const uint32_t mrow = r0 + row_base + t * 8 + 2 * j + rr;
               if (mrow >= p.m) continue;
               const uint32_t ca = n0 + col0 + 64 * c, cb = n0 + col1 + 64 * c;
               float* row = p.c + (uint64_t)mrow * p.ldc;
@@ -576,7 +584,7 @@ struct KernelSetup {
 };
 
 template <typename Kernel>
-int32_t kernel_occupancy(KernelSetup& ks, Kernel kernel, AionCudaDevice* dev, size_t smem, int* blocks_per_sm) {
+int32_t kernel_occupancy(KernelSetup& ks, Kernel kernel, AionCudaDevice* dev, int threads, size_t smem, int* blocks_per_sm) {
   if (dev->ordinal < 0 || dev->ordinal >= 64) return fail(AION_CUDA_UNSUPPORTED, "gemv: device ordinal %d is beyond the 64 this library keeps state for", dev->ordinal);
   std::lock_guard<std::mutex> lock(ks.mu);
   const int di = dev->ordinal;
@@ -586,7 +594,7 @@ int32_t kernel_occupancy(KernelSetup& ks, Kernel kernel, AionCudaDevice* dev, si
   }
   if (ks.occ_smem[di] != smem) {
     int nb = 0;
-    AION_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, kernel, THREADS, smem));
+    AION_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, kernel, threads, smem));
     if (nb < 1) return fail(AION_CUDA_INTERNAL_ERROR, "gemv: kernel does not fit an SM with %llu bytes of shared memory", (unsigned long long)smem);
     ks.occ_blocks[di] = nb;
     ks.occ_smem[di] = smem;
@@ -595,7 +603,7 @@ int32_t kernel_occupancy(KernelSetup& ks, Kernel kernel, AionCudaDevice* dev, si
   return AION_CUDA_OK;
 }
 
-template <int DT, bool NT, int MT, bool M1, bool RG, bool PREQ, int CG>
+template <int DT, bool NT, int MT, bool M1, bool RG, bool PREQ, int CG, int RW>
 KernelSetup& setup_of() {
   static KernelSetup ks;
   return ks;
@@ -633,15 +641,16 @@ int32_t encode_weight_map(const uint8_t* b, uint64_t ldb, uint32_t n, uint32_t k
   return AION_CUDA_OK;
 }
 
-template <int DT, bool NT, int MT, bool M1, bool RG, bool PREQ, int CG>
+template <int DT, bool NT, int MT, bool M1, bool RG, bool PREQ, int CG, int RW>
 int32_t launch(AionCudaDevice* dev, GemvParams p, const uint8_t* b, uint64_t ldb, const uint8_t* given_image) {
   using G = Geom<DT, NT, CG>;
   constexpr int TN = G::TN;
-  auto kernel = gemv_q_mma_kernel<DT, NT, MT, M1, RG, PREQ, CG>;
+  constexpr int THREADS = threads_of(RW);
+  auto kernel = gemv_q_mma_kernel<DT, NT, MT, M1, RG, PREQ, CG, RW>;
   constexpr uint32_t MP2 = M1 ? 2 : 8 * MT;
   const size_t smem = G::OFF_ACT + (PREQ ? (size_t)NS * act_bytes(KBT, MP2) : act_bytes(p.stages_per_tile * KBT, MP2));
   int per_sm = 0;
-  if (int32_t st = kernel_occupancy(setup_of<DT, NT, MT, M1, RG, PREQ, CG>(), kernel, dev, smem, &per_sm)) return st;
+  if (int32_t st = kernel_occupancy(setup_of<DT, NT, MT, M1, RG, PREQ, CG, RW>(), kernel, dev, THREADS, smem, &per_sm)) return st;
   uint64_t grid = (uint64_t)per_sm * dev->sm_count;
   if (dev->gemv_split_override) grid = (uint64_t)dev->gemv_split_override * dev->sm_count;  // CTAs per SM, tuning only
   if (grid > p.units) grid = p.units;
@@ -649,7 +658,7 @@ int32_t launch(AionCudaDevice* dev, GemvParams p, const uint8_t* b, uint64_t ldb
   // CTA per SM. Their launches are latency-bound, and independent ones recorded in
   // parallel lanes then share the GPU (measured on 9 MB q4 matrices: 148 CTAs in 8 lanes
   // stream 3.5 TB/s, 256 or 444 CTAs 2.6 to 3.0 TB/s).
-  if (!dev->gemv_split_override) {
+  if (!dev->gemv_split_override && MT <= 2) {
     const uint64_t sms = (uint64_t)dev->sm_count;
     uint64_t want = p.units / 8;
     if (want < sms) want = sms;
@@ -676,9 +685,8 @@ int32_t launch(AionCudaDevice* dev, GemvParams p, const uint8_t* b, uint64_t ldb
   // Scratch for tiles shared by several CTAs: two partial slots per CTA, one ticket per (tile, warp),
   // times the groups of 8 * MT rows.
   constexpr int MPA = 8 * MT;
-  const uint64_t groups = RG ? ceil_div((uint64_t)p.m, (uint64_t)MPA) : 1;
-  if (groups > 0x7FFFFFFFull || grid > 65535) return fail(AION_CUDA_UNSUPPORTED, "gemv: too many rows for one launch");
-  if (int32_t st = dev->reserve_gemv_fixup((size_t)groups * grid * 2 * TN * MPA * sizeof(float), (size_t)groups * p.tiles * CONSUMER_WARPS)) return st;
+  const uint64_t groups = p.tiles / p.col_tiles;
+  if (int32_t st = dev->reserve_gemv_fixup((size_t)grid * 2 * TN * MPA * sizeof(float), (size_t)p.tiles * COL_WARPS * RW)) return st;
   p.partials = dev->lane_gemv_partials();
   p.tickets = dev->lane_gemv_tickets();
 
@@ -713,7 +721,7 @@ int32_t launch(AionCudaDevice* dev, GemvParams p, const uint8_t* b, uint64_t ldb
   if (int32_t st = encode_weight_map<DT, NT, CG>(b, ldb, p.n, p.kblocks, dev, nullptr, &tm)) return st;
 
   cudaLaunchConfig_t cfg{};
-  cfg.gridDim = RG ? dim3((unsigned)groups, (unsigned)grid) : dim3((unsigned)grid);
+  cfg.gridDim = dim3((unsigned)grid);
   cfg.blockDim = dim3(THREADS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = dev->stream;
@@ -731,19 +739,19 @@ int32_t launch_m(AionCudaDevice* dev, const GemvParams& p, const uint8_t* b, uin
   // m >= 2: A is quantized once by a small kernel (or by the kernel that produced A) instead of
   // by every CTA. m = 1 quantizes its one row inside the kernel unless K is deep: past about
   // 3000 the small kernel is cheaper than 148 CTAs each quantizing the whole row.
-  if (p.m == 1) return (image || p.kblocks > 96) ? launch<DT, NT, 1, true, false, true, 1>(dev, p, b, ldb, image)
-                                                 : launch<DT, NT, 1, true, false, false, 1>(dev, p, b, ldb, nullptr);
-  if (p.m <= 8) return launch<DT, NT, 1, false, false, true, 1>(dev, p, b, ldb, image);
-  if (p.m <= 16) return launch<DT, NT, 2, false, false, true, 1>(dev, p, b, ldb, image);
-  if (p.m <= 32) return launch<DT, NT, 4, false, false, true, 2>(dev, p, b, ldb, image);
-  if (p.m <= 64) return launch<DT, NT, 8, false, false, true, 2>(dev, p, b, ldb, image);
-  return launch<DT, NT, 8, false, true, true, 2>(dev, p, b, ldb, image);  // groups of 64 rows
+  if (p.m == 1) return (image || p.kblocks > 96) ? launch<DT, NT, 1, true, false, true, 1, 1>(dev, p, b, ldb, image)
+                                                 : launch<DT, NT, 1, true, false, false, 1, 1>(dev, p, b, ldb, nullptr);
+  if (p.m <= 8) return launch<DT, NT, 1, false, false, true, 1, 1>(dev, p, b, ldb, image);
+  if (p.m <= 16) return launch<DT, NT, 2, false, false, true, 1, 1>(dev, p, b, ldb, image);
+  if (p.m <= 32) return launch<DT, NT, 4, false, false, true, 2, 2>(dev, p, b, ldb, image);
+  if (p.m <= 64) return launch<DT, NT, 8, false, false, true, 2, 2>(dev, p, b, ldb, image);
+  return launch<DT, NT, 8, false, true, true, 2, 2>(dev, p, b, ldb, image);  // groups of 64 rows
 }
 
 }  // namespace
 
 int32_t gemv_mma(AionCudaDevice* dev, const MatMulArgs& g, bool probe_only) {
-  if (g.m > 64ull * 65535 || g.k == 0) return AION_CUDA_UNSUPPORTED;
+  if (g.m > (1ull << 22) || g.k == 0) return AION_CUDA_UNSUPPORTED;
   if (g.n > 0x7FFFFFFFull - 128 || g.k / QK > 0x7FFFFFFFull) return AION_CUDA_UNSUPPORTED;
   const uint64_t kblocks = g.k / QK;
   const uintptr_t baddr = reinterpret_cast<uintptr_t>(g.b);
@@ -778,7 +786,10 @@ int32_t gemv_mma(AionCudaDevice* dev, const MatMulArgs& g, bool probe_only) {
     p.alpha = g.alpha;
     p.beta = kb0 == 0 ? g.beta : 1.0f;
     const uint32_t tn = g.m > 16 ? 128u : 64u;
-    p.tiles = (uint32_t)((g.n + tn - 1) / tn);
+    const uint64_t row_groups = g.m <= 64 ? 1 : ceil_div(g.m, (uint64_t)64);
+    p.col_tiles = (uint32_t)((g.n + tn - 1) / tn);
+    if ((uint64_t)p.col_tiles * row_groups > 0x7FFFFFFFull) return AION_CUDA_UNSUPPORTED;
+    p.tiles = (uint32_t)(p.col_tiles * row_groups);
     p.stages_per_tile = (uint32_t)((nkb + KBT - 1) / KBT);
     p.units = (uint64_t)p.tiles * p.stages_per_tile;
     p.fault = dev->fault_dev;
@@ -823,7 +834,7 @@ namespace {
 constexpr uint32_t STATIC_MAX_CTAS = 512;    // grid is clamped to this
 constexpr uint32_t STATIC_MAX_TILES = 8192;  // n <= 524288
 constexpr size_t STATIC_PARTIAL_BYTES = (size_t)STATIC_MAX_CTAS * 2 * 64 * 8 * sizeof(float);  // m <= 8
-constexpr size_t STATIC_TICKET_BYTES = (size_t)STATIC_MAX_TILES * CONSUMER_WARPS * sizeof(int);
+constexpr size_t STATIC_TICKET_BYTES = (size_t)STATIC_MAX_TILES * COL_WARPS * sizeof(int);
 
 static __device__ __align__(256) unsigned char g_static_scratch[STATIC_PARTIAL_BYTES + STATIC_TICKET_BYTES];
 
@@ -836,11 +847,12 @@ template <int DT, bool M1>
 int32_t launch_static(AionCudaDevice* dev, GemvParams p, const uint8_t* b, uint64_t ldb, unsigned char* scratch) {
   using G = Geom<DT, false, 1>;
   // The same instantiation aion_cuda_matmul uses for these shapes: they share its set-up state.
-  auto kernel = gemv_q_mma_kernel<DT, false, 1, M1, false, false, 1>;
+  auto kernel = gemv_q_mma_kernel<DT, false, 1, M1, false, false, 1, 1>;
   constexpr uint32_t MP2 = M1 ? 2 : 8;
+  constexpr int THREADS = threads_of(1);
   const size_t smem = G::OFF_ACT + act_bytes(p.stages_per_tile * KBT, MP2);
   int per_sm = 0;
-  if (int32_t st = kernel_occupancy(setup_of<DT, false, 1, M1, false, false, 1>(), kernel, dev, smem, &per_sm)) return st;
+  if (int32_t st = kernel_occupancy(setup_of<DT, false, 1, M1, false, false, 1, 1>(), kernel, dev, THREADS, smem, &per_sm)) return st;
   uint64_t grid = (uint64_t)per_sm * dev->sm_count;
   if (grid > p.units) grid = p.units;
   if (grid > STATIC_MAX_CTAS) grid = STATIC_MAX_CTAS;
@@ -848,7 +860,7 @@ int32_t launch_static(AionCudaDevice* dev, GemvParams p, const uint8_t* b, uint6
   p.partials = reinterpret_cast<float*>(scratch);
   p.tickets = reinterpret_cast<int*>(scratch + STATIC_PARTIAL_BYTES);
   // The counters must start at zero whatever an earlier call left behind.
-  AION_CUDA_TRY(cudaMemsetAsync(p.tickets, 0, (size_t)p.tiles * CONSUMER_WARPS * sizeof(int), dev->stream));
+  AION_CUDA_TRY(cudaMemsetAsync(p.tickets, 0, (size_t)p.tiles * COL_WARPS * sizeof(int), dev->stream));
   CUtensorMap local;
   const CUtensorMap* tm = nullptr;
   if (int32_t st = encode_weight_map<DT, false, 1>(b, ldb, p.n, p.kblocks, nullptr, &local, &tm)) return st;
@@ -905,7 +917,7 @@ int32_t gemv_mma_static_scratch(AionCudaDevice* dev, const MatMulArgs& g) {
   p.ldc = g.ldc;
   p.alpha = g.alpha;
   p.beta = g.beta;
-  p.tiles = (uint32_t)((g.n + 63) / 64);
+  p.tiles = p.col_tiles = (uint32_t)((g.n + 63) / 64);
   p.stages_per_tile = (uint32_t)((kblocks + KBT - 1) / KBT);
   p.units = (uint64_t)p.tiles * p.stages_per_tile;
   p.fault = dev->fault_dev;

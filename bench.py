@@ -382,7 +382,8 @@ def run_other(args):
         elif args.workload == "gemm":
             dt = capi.DTYPE_Q4_0 if args.gemm_dtype == "q4" else capi.DTYPE_Q8_0
             out = {"metric": "prefill GEMM TFLOP/s", "n_gpus": 1,
-                   **benchmarks.gemm_leg(torch, backend, local_rank, dt, args.gemm_m, 8192, 2048, iters=max(3, min(args.steps, 50)))}
+                   **benchmarks.gemm_leg(torch, backend, local_rank, dt, args.gemm_m, 8192, 2048, iters=max(3, min(args.steps, 50)),
+                                         kernel=args.gemm_kernel)}
         elif args.workload == "attention":
             out = {"metric": "decode attention GB/s", "n_gpus": 1,
                    **benchmarks.attention_leg(torch, backend, local_rank, args.attn_batch, args.attn_context,
@@ -501,6 +502,8 @@ def main():
     ap.add_argument("--decode-layers", type=int, default=30)
     ap.add_argument("--gemm-m", type=int, default=2048)
     ap.add_argument("--gemm-dtype", default="q4", choices=["q4", "q8"])
+    ap.add_argument("--gemm-kernel", default="gemm", choices=["gemm", "int8", "auto"],
+                    help="gemm workload: the tcgen05 kernel (bf16 operands), the int8-activation kernel, or the library's own choice")
     ap.add_argument("--attn-batch", type=int, default=64)
     ap.add_argument("--attn-context", type=int, default=4096)
     ap.add_argument("--colsplit-m", type=int, default=1)

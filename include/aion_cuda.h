@@ -158,18 +158,19 @@ AION_CUDA_API int32_t aion_cuda_memset(AionCudaDevice* dev, uint64_t handle, siz
  *   C f32, row stride ldc elements (0 = n).
  * The activation is quantized to int8 per 32-block exactly as the reference CPU
  * kernels do (aion src/aion/backend/cpu/kernels/matmul_q_i8.zig:187-203) for
- * m < AION_CUDA_GEMM_MIN_M — every decode batch size: one launch streams the weights once per
- * AION_CUDA_INT8_GROUP_ROWS rows of A, so a request's result does not depend on how many
- * requests share its step; larger m (prefill) runs the tensor-core GEMM, which dequantizes B
- * to bf16 and rounds A to bf16 (results within rel-L2 1e-2 of the int8-activation arithmetic
- * instead of 1e-3).
+ * m < AION_CUDA_GEMM_MIN_M (one launch streams the weights once per AION_CUDA_INT8_GROUP_ROWS rows
+ * of A); from there on the tensor-core GEMM runs: it quantizes A to int8 per 32-block in the
+ * same way, then multiplies the dequantized activation and the dequantized weights, both
+ * rounded to bf16 (results within rel-L2 1e-2 of the int8 arithmetic instead of 1e-3; about
+ * 2e-3 in practice). AION_CUDA_MATMUL_FORCE_GEMV keeps the int8 kernel at any m: exact
+ * integer dots, at a quarter to a third of the GEMM's speed once m reaches the hundreds.
  * f32 / f16 B return UNSUPPORTED.
  *   a_image (handle 0 = absent): the quantized image of A that the step producing A wrote
  *     (see aion_cuda_act_image_bytes); the int8 kernels then read it instead of quantizing A.
  *     Ignored by the tensor-core GEMM and the any-shape kernel, which read A itself.
  * --------------------------------------------------------------------------------- */
 #define AION_CUDA_INT8_GROUP_ROWS 64 /* rows of A that share one pass over the weights */
-#define AION_CUDA_GEMM_MIN_M 513     /* from this many rows on, the tensor-core GEMM (bf16 operands) runs */
+#define AION_CUDA_GEMM_MIN_M 33      /* from this many rows on, the tensor-core GEMM (bf16 operands) runs */
 
 typedef struct AionCudaMatMul {
   AionCudaOperand c, a, b;

@@ -30,6 +30,7 @@ class OracleDecoder:
         pos = np.asarray(positions, np.int32).reshape(R, 1)
         rms = lambda v, res=None: oracle.rms_norm(v, self.gamma, self.beta, cfg.eps, residual=res)
         x = oracle.gather_rows_q8(self.embed, cfg.vocab, cfg.hidden, np.asarray(tokens, np.int32)).reshape(R, cfg.hidden)
+        self.trace = []  # per layer: the intermediate tensors of the last step, for tests that localise a difference
         for l in range(cfg.layers):
             xn = rms(x)
             q = self._mm(xn, f"l{l}.wq", cfg.hidden, cfg.q_width).reshape(R, 1, cfg.heads, cfg.head_dim)
@@ -49,6 +50,7 @@ class OracleDecoder:
             act = oracle.elemwise(oracle.ELEMWISE_GATE_GELU, gate, up)
             down = self._mm(act, f"l{l}.wd", cfg.ffn, cfg.hidden)
             x = rms(down, res=x)
+            self.trace.append({"q": q, "k": k, "v": v, "attn": a, "o": o, "gate": gate, "up": up, "act": act, "down": down, "x": x})
         xf = rms(x)
         logits = self._mm(xf, "head", cfg.hidden, cfg.vocab)
         return x, logits, oracle.argmax(logits)

@@ -1,10 +1,12 @@
 """Prefill GEMM parity: the tcgen05 kernel through the C ABI against the oracle.
 
-The kernel rounds A to bf16 and dequantizes B to bf16, so the bound against the reference
-CPU arithmetic (int8 activations) is rel-L2 <= 1e-2, the tolerance stated for the path
-whose activations pass through bf16. Against f32-A x dequant(B) (the host reference of the
-reference's GPU tests, src/aion/backend/gpu/test_gpu_backend.zig:1325-1341) only the two
-bf16 roundings differ, so that distance is checked tighter (4e-3)."""
+The kernel quantizes A to int8 per 32-block exactly as the reference CPU kernels do, then
+multiplies dequantized A and dequantized B, both rounded to bf16. The stated bound for the path
+whose activations pass through bf16 is rel-L2 <= 1e-2 against the reference CPU arithmetic; with
+the int8 quantization shared, what is left is the two bf16 roundings (about 2e-3), so the tests
+hold it to 5e-3. Against f32-A x dequant(B) (the host reference of the reference's GPU tests,
+src/aion/backend/gpu/test_gpu_backend.zig:1325-1341) the int8 quantization of A is the whole
+distance (about 5e-3, as between the reference's own CPU and GPU kernels): bounded by 1e-2."""
 import numpy as np
 import pytest
 
@@ -14,8 +16,8 @@ from tests.gpu_util import matmul_plan, run_matmul
 
 pytestmark = pytest.mark.gpu
 
-TOL_INT8A = 1e-2
-TOL_DEQ = 4e-3
+TOL_INT8A = 5e-3   # against the reference CPU arithmetic (the stated bound is 1e-2)
+TOL_DEQ = 1e-2     # against f32 activations: the reference's own CPU-vs-device distance
 
 
 def rel_l2(got, want):
@@ -58,8 +60,8 @@ def test_gemm_alpha_beta_and_leading_dims(backend, dtype):
     c0 = np.random.default_rng(9).standard_normal(m * ldc).astype(np.float32)
     got = run_matmul(backend, dtype, a_wide, b, m, n, k, lda=lda, ldb=ldb, ldc=ldc, alpha=0.5, beta=-1.25, c=c0,
                      flags=capi.MATMUL_FORCE_GEMM)
-    want = oracle.matmul_deqf32(dtype, a_wide, b, m, n, k, lda=lda, ldb=ldb, ldc=ldc, alpha=0.5, beta=-1.25, c=c0).reshape(m, ldc)
-    assert rel_l2(got[:, :n], want[:, :n]) <= TOL_DEQ
+    want = oracle.matmul_q(dtype, a_wide, b, m, n, k, lda=lda, ldb=ldb, ldc=ldc, alpha=0.5, beta=-1.25, c=c0).reshape(m, ldc)
+    assert rel_l2(got[:, :n], want[:, :n]) <= TOL_INT8A
     # columns between n and ldc are not part of C and must be left alone
     assert np.array_equal(got[:, n:], c0.reshape(m, ldc)[:, n:])
 
@@ -121,8 +123,8 @@ def test_gemm_split_k_shapes(backend, dtype, m, n, k):
     a, b = make(dtype, m, n, k, seed=21)
     c0 = np.random.default_rng(3).standard_normal(m * n).astype(np.float32)
     got = run_matmul(backend, dtype, a, b, m, n, k, alpha=0.75, beta=0.5, c=c0, flags=capi.MATMUL_FORCE_GEMM)
-    want = oracle.matmul_deqf32(dtype, a, b, m, n, k, alpha=0.75, beta=0.5, c=c0).reshape(m, n)
-    assert rel_l2(got, want) <= TOL_DEQ
+    want = oracle.fast_matmul_q(dtype, a, b, m, n, k, alpha=0.75, beta=0.5, c=c0.copy()).reshape(m, n)
+    assert rel_l2(got, want) <= TOL_INT8A
     again = run_matmul(backend, dtype, a, b, m, n, k, alpha=0.75, beta=0.5, c=c0, flags=capi.MATMUL_FORCE_GEMM)
     assert np.array_equal(got, again)
 
@@ -168,5 +170,5 @@ def test_gemm_smallest_and_ragged_shapes(backend, m, n, k):
     # small m, a single K block, n far below a tile
     a, b = make(capi.DTYPE_Q8_0, m, n, k, seed=41)
     got = run_matmul(backend, capi.DTYPE_Q8_0, a, b, m, n, k, flags=capi.MATMUL_FORCE_GEMM)
-    want = oracle.matmul_deqf32(capi.DTYPE_Q8_0, a, b, m, n, k).reshape(m, n)
-    assert rel_l2(got, want) <= TOL_DEQ
+    want = oracle.matmul_q(capi.DTYPE_Q8_0, a, b, m, n, k).reshape(m, n)
+    assert rel_l2(got, want) <= TOL_INT8A

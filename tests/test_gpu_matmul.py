@@ -106,9 +106,11 @@ def test_decode_batches_keep_int8_arithmetic(backend, dtype, m):
     x = rd.synth_acts(m, k, seed=m)
     b = oracle.quantize(dtype, rd.synth_weights(k, n, seed=7), 0)
     want = oracle.fast_matmul_q(dtype, x, b, m, n, k)
-    plan = matmul_plan(backend, dtype, m, n, k)
+    # up to 32 rows the library picks this kernel itself; beyond, the flag keeps it (exact integer dots at any m)
+    flags = capi.MATMUL_AUTO if m < capi.GEMM_MIN_M else capi.MATMUL_FORCE_GEMV
+    plan = matmul_plan(backend, dtype, m, n, k, flags=flags)
     assert plan.kernel == capi.KERNEL_INT8 and plan.tile_cols == 128 and plan.tile_rows == (32 if m <= 32 else 64)
-    got = run_matmul(backend, dtype, x, b, m, n, k)
+    got = run_matmul(backend, dtype, x, b, m, n, k, flags=flags)
     assert rd.rel_l2(got, want) < TIGHT
 
 
@@ -118,7 +120,7 @@ def test_decode_batches_nt(backend, m):
     x = rd.synth_acts(m, k, seed=m)
     b = oracle.quantize(oracle.Q8_0, rd.synth_weights(n, k, seed=3), 1)
     want = oracle.fast_matmul_nt_q8(x, b, m, n, k)
-    assert rd.rel_l2(run_matmul_nt(backend, x, b, m, n, k), want) < TIGHT
+    assert rd.rel_l2(run_matmul_nt(backend, x, b, m, n, k, flags=capi.MATMUL_FORCE_GEMV), want) < TIGHT
 
 
 @pytest.mark.parametrize("dtype", [capi.DTYPE_Q8_0, capi.DTYPE_Q4_0])
@@ -129,22 +131,30 @@ def test_decode_batch_at_decoder_widths_alpha_beta_ldc(backend, dtype):
     b = oracle.quantize(dtype, rd.synth_weights(k, n, seed=2), 0)
     c0 = rd.synth_acts(m, ldc, seed=3)
     want = oracle.fast_matmul_q(dtype, x, b, m, n, k)
-    got = run_matmul(backend, dtype, x, b, m, n, k, ldc=ldc, alpha=0.5, beta=-2.0, c=c0)
+    got = run_matmul(backend, dtype, x, b, m, n, k, ldc=ldc, alpha=0.5, beta=-2.0, c=c0, flags=capi.MATMUL_FORCE_GEMV)
     assert rd.rel_l2(got[:, :n], 0.5 * want - 2.0 * c0[:, :n]) < TIGHT
     assert np.array_equal(got[:, n:], c0[:, n:])
 
 
-def test_a_request_does_not_depend_on_its_batch(backend):
-    """Rows decoded alone, in a batch of 8 and in a batch of 64 take different kernel variants
-    (8-, 64-row groups; different K splits) but the same arithmetic: equal to f32 summation order."""
+def test_a_row_does_not_depend_on_its_batch(backend):
+    """Rows multiplied alone, in a batch of 8, of 32 and of 64. Up to 32 rows the int8 kernel runs (different
+    tile variants and K splits, the same arithmetic: equal to f32 summation order). From 33 rows the tensor-core
+    GEMM takes over; it multiplies the same int8-quantized activation, rounded to bf16 like the weights, so a
+    row moves by the bf16 rounding only."""
     n, k = 1536, 2048
     x = rd.synth_acts(64, k, seed=9)
     b = oracle.quantize(oracle.Q4_0, rd.synth_weights(k, n, seed=10), 0)
-    full = run_matmul(backend, capi.DTYPE_Q4_0, x, b, 64, n, k)
-    eight = run_matmul(backend, capi.DTYPE_Q4_0, x[:8], b, 8, n, k)
     one = run_matmul(backend, capi.DTYPE_Q4_0, x[:1], b, 1, n, k)
-    assert rd.rel_l2(full[:8], eight) < TIGHT
-    assert rd.rel_l2(full[:1], one) < TIGHT
+    eight = run_matmul(backend, capi.DTYPE_Q4_0, x[:8], b, 8, n, k)
+    thirty_two = run_matmul(backend, capi.DTYPE_Q4_0, x[:32], b, 32, n, k)
+    forced = run_matmul(backend, capi.DTYPE_Q4_0, x, b, 64, n, k, flags=capi.MATMUL_FORCE_GEMV)
+    assert rd.rel_l2(thirty_two[:8], eight) < TIGHT and rd.rel_l2(thirty_two[:1], one) < TIGHT
+    assert rd.rel_l2(forced[:32], thirty_two) < TIGHT
+    assert matmul_plan(backend, capi.DTYPE_Q4_0, 64, n, k).kernel == capi.KERNEL_GEMM
+    gemm = run_matmul(backend, capi.DTYPE_Q4_0, x, b, 64, n, k)
+    d = rd.rel_l2(gemm[:32], thirty_two)
+    print(f"\nrows in a batch of 64 (tensor-core GEMM) against the same rows in a batch of 32 (int8 kernel): rel-L2 {d:.2e}")
+    assert d < 5e-3
 
 
 # ---- the quantized-activation image ---------------------------------------------------------
@@ -217,8 +227,9 @@ def test_matmul_with_image_equals_matmul_without(backend, dtype, m):
     n, k = 520, 1024
     x = rd.synth_acts(m, k, seed=m)
     b = oracle.quantize(dtype, rd.synth_weights(k, n, seed=5), 0)
-    plain = run_matmul(backend, dtype, x, b, m, n, k)
-    with_image = run_matmul(backend, dtype, x, b, m, n, k, image=True)
+    flags = capi.MATMUL_AUTO if m < capi.GEMM_MIN_M else capi.MATMUL_FORCE_GEMV  # the int8 kernel is the one that reads images
+    plain = run_matmul(backend, dtype, x, b, m, n, k, flags=flags)
+    with_image = run_matmul(backend, dtype, x, b, m, n, k, image=True, flags=flags)
     if m == 1:  # alone, a single row is quantized inside the matmul and K may be split differently
         assert rd.rel_l2(with_image, plain) < TIGHT
     else:
@@ -249,7 +260,9 @@ def test_image_operand_is_checked(backend):
 
 def test_plan_names_the_kernel(backend):
     assert matmul_plan(backend, capi.DTYPE_Q4_0, 1, 8192, 2048).kernel == capi.KERNEL_INT8
-    assert matmul_plan(backend, capi.DTYPE_Q4_0, 512, 8192, 2048).kernel == capi.KERNEL_INT8
+    assert matmul_plan(backend, capi.DTYPE_Q4_0, 32, 8192, 2048).kernel == capi.KERNEL_INT8
+    assert matmul_plan(backend, capi.DTYPE_Q4_0, 33, 8192, 2048).kernel == capi.KERNEL_GEMM
+    assert matmul_plan(backend, capi.DTYPE_Q4_0, 512, 8192, 2048, flags=capi.MATMUL_FORCE_GEMV).kernel == capi.KERNEL_INT8
     p = matmul_plan(backend, capi.DTYPE_Q4_0, 2048, 8192, 2048)
     assert p.kernel == capi.KERNEL_GEMM and p.tile_cols == 256
     assert matmul_plan(backend, capi.DTYPE_Q4_0, 3, 5, 64).kernel == capi.KERNEL_GENERIC  # n not a multiple of 8

@@ -46,10 +46,50 @@ def _max_over_ranks(torch, dist, world, value):
     return float(t.item())
 
 
+def _oracle_check_of_request0(dec, cfg, token0: int, position0: int, caches0, logits0, threads: int) -> dict:
+    """One request of the step just executed, recomputed by the CPU oracle (the checker: the reference's
+    arithmetic composed op by op) from the packed weights the device holds and the request's own cache rows.
+    Returns the distance of the device's logits from the oracle's and the oracle's speed."""
+    import time as _time
+
+    from oracle.decoder_ref import OracleDecoder
+
+    st = dec.store
+    packed = {}
+    for l, names in enumerate(dec.w):
+        for name, tid in names.items():
+            packed[f"l{l}.{name}"] = st.read(tid)
+    packed["head"] = st.read(dec.w_head)
+    row_bytes = cfg.hidden // 32 * 34
+    ech = st.acquire_const(dec.embed)
+    row = np.empty(row_bytes, dtype=np.uint8)
+    dec.backend.device_memory.copy_d2h(row, ech.handle, ech.offset + token0 * row_bytes)
+    ref = OracleDecoder.from_packed(cfg, 1, packed, row, fast=True)
+    for l in range(cfg.layers):
+        ref.k_cache[l][0], ref.v_cache[l][0] = caches0[l]
+    ref.threads = threads  # explicit: the launcher of several ranks pins the OpenMP default to 1
+    t0 = _time.perf_counter()
+    _, logits_ref, next_ref = ref.step(np.array([0], np.int32), np.array([position0], np.int32))
+    dt = _time.perf_counter() - t0
+    got = np.asarray(logits0, dtype=np.float64)
+    want = logits_ref.reshape(-1).astype(np.float64)
+    top2 = np.sort(want)[-2:]
+    return {"rel_l2_vs_oracle": float(np.linalg.norm(got - want) / max(np.linalg.norm(want), 1e-30)),
+            "argmax_device": int(np.argmax(logits0)), "argmax_oracle": int(next_ref[0]),
+            "oracle_top2_gap_over_max": float((top2[1] - top2[0]) / max(np.abs(want).max(), 1e-30)),
+            "what": "request 0 of rank 0, all layers and the full head, device logits against the CPU oracle's on the same "
+                    "packed weights and cache rows",
+            "cpu_baseline": {"value": round(1.0 / dt, 3), "unit": "tokens/s", "cores": threads, "kind": "port",
+                             "sample": "one request, one token step, through the oracle's decoder graph (threaded port of the "
+                                       "reference's CPU kernels for the matmuls)"}}
+
+
 def decode_leg(torch, dist, backend: CudaBackend, rank: int, world: int, local_rank: int, requests_total: int, steps: int,
-               warmup: int, lanes: int, cfg: DecoderConfig | None = None, peak_gbs: float = 6552.3) -> dict:
+               warmup: int, lanes: int, cfg: DecoderConfig | None = None, peak_gbs: float = 6552.3, check: bool = False,
+               threads: int = 1) -> dict:
     """Decode tokens/s of the synthetic q4 decoder: `requests_total` concurrent requests at the far
-    end of the context window, split evenly over the ranks (replicated weights, no exchange)."""
+    end of the context window, split evenly over the ranks (replicated weights, no exchange).
+    check: on rank 0, recompute request 0 of the first step with the CPU oracle and report the distance."""
     cfg = cfg or DecoderConfig()
     mine = request_shard(requests_total, world, rank)
     R = mine.stop - mine.start
@@ -85,9 +125,32 @@ def decode_leg(torch, dist, backend: CudaBackend, rank: int, world: int, local_r
     tokens = (np.arange(mine.start, mine.stop) * 7919 + 13) % cfg.vocab
     positions = np.full(R, cfg.ctx - 1, np.int32)
     dec.set_inputs(tokens, positions)
+    caches0 = None
+    if check and rank == 0:
+        # request 0's cache rows before the step appends to them (the oracle appends its own k, v)
+        caches0 = []
+        per_req = cfg.ctx * cfg.kv_width
+        for l in range(cfg.layers):
+            pair = []
+            for tid in (dec.k_cache[l], dec.v_cache[l]):
+                ch = dec.store.acquire_const(tid)
+                rows = np.empty((cfg.ctx, cfg.kv_heads, cfg.head_dim), dtype=np.float16)
+                backend.device_memory.copy_d2h(rows, ch.handle, ch.offset)
+                pair.append(rows)
+            caches0.append(tuple(pair))
     dec.execute()  # sizes scratch; also the un-recorded reference run
     backend.sync()
     first = dec.read_next_tokens().copy()
+    oracle_check = None
+    if caches0 is not None:
+        lch = dec.store.acquire_const(dec.logits)
+        logits0 = np.empty(cfg.vocab, dtype=np.float32)
+        backend.device_memory.copy_d2h(logits0, lch.handle, lch.offset)
+        try:
+            oracle_check = _oracle_check_of_request0(dec, cfg, int(tokens[0]), int(positions[0]), caches0, logits0, threads)
+        except Exception as e:  # the timing below must still run
+            oracle_check = {"error": f"{type(e).__name__}: {e}"}
+        caches0 = None
     dec.record(lanes=lanes)
     build_s = time.perf_counter() - t_build
 
@@ -134,9 +197,12 @@ def decode_leg(torch, dist, backend: CudaBackend, rank: int, world: int, local_r
         "hbm_gbs_per_gpu": round(step_bytes / (ms * 1e-3) / 1e9, 1),
         "hbm_frac_of_measured": round(step_bytes / (ms * 1e-3) / 1e9 / peak_gbs, 4),
         "launches_per_step": len(dec.steps), "replay_matches_eager": replay_same, "build_s": round(build_s, 1),
+        "matmul_kernel": "int8 (activation images written by the producing steps)" if dec.images else "tcgen05 GEMM (bf16 operands)",
         "config": {"layers": cfg.layers, "hidden": cfg.hidden, "ffn": cfg.ffn, "heads": cfg.heads, "kv_heads": cfg.kv_heads,
                    "head_dim": cfg.head_dim, "vocab": cfg.vocab, "ctx": cfg.ctx, "weights": "q4_0, N(0, 0.02), random init"},
     }
+    if oracle_check is not None:
+        out["oracle_check"] = oracle_check
     dec.deinit()
     return out
 
@@ -265,21 +331,32 @@ def attention_leg(torch, backend: CudaBackend, local_rank: int, batch: int, t_ct
 def colsplit_leg(torch, dist, backend: CudaBackend, rank: int, world: int, local_rank: int, m: int, iters: int = 50,
                  n: int = 28672, k: int = 8192) -> dict:
     """The one large q4 layer column-split over the ranks: each rank computes y[:, n0:n1] straight
-    into its slot of the gather buffer, then one NCCL all-gather (in place) assembles y on every rank."""
+    into its slot of the gather buffer, then one NCCL all-gather (in place) assembles y on every rank.
+    Every rank quantizes the SAME full weight (one seed) and keeps its column range of the packed blocks, so
+    the assembled y can be compared with the unsplit matmul on one GPU: `max_abs_diff` below."""
+    from .sharding import assemble_gathered
+
     lib, dev, mem = backend._lib, backend.handle, backend.device_memory
     n0, n1 = column_shard(n, world, rank)
     n_loc = n1 - n0
-    nb = (k // 32) * n_loc * 18
+    bb = 18
+    nb_full, nb = (k // 32) * n * bb, (k // 32) * n_loc * bb
     gen = torch.Generator(device="cuda")
-    gen.manual_seed(1234 + rank)
-    w = torch.randn((k, n_loc), generator=gen, device="cuda", dtype=torch.float32) * 0.02
+    gen.manual_seed(1234)  # the same weight on every rank
+    w = torch.randn((k, n), generator=gen, device="cuda", dtype=torch.float32) * 0.02
     torch.cuda.synchronize()
-    hw = mem.alloc(nb, 256)
-    shape = (C.c_uint64 * 2)(k, n_loc)
-    src, dst = capi.Operand(w.data_ptr(), 0, w.numel() * 4), capi.Operand(hw, 0, nb)
+    h_full = mem.alloc(nb_full, 256)
+    shape = (C.c_uint64 * 2)(k, n)
+    src, dst = capi.Operand(w.data_ptr(), 0, w.numel() * 4), capi.Operand(h_full, 0, nb_full)
     _chk(lib.aion_cuda_quantize(dev, capi.DTYPE_Q4_0, C.byref(src), shape, 2, 0, C.byref(dst)))
     backend.sync()
     del w
+    # this rank's columns of the packed [k/32][n] blocks: a strided copy on the device, block row by block row
+    hw = mem.alloc(nb, 256)
+    full_t = torch.as_tensor(_DevArray(h_full, nb_full, "|u1", 1), device="cuda").view(k // 32, n * bb)
+    loc_t = torch.as_tensor(_DevArray(hw, nb, "|u1", 1), device="cuda").view(k // 32, n_loc * bb)
+    loc_t.copy_(full_t[:, n0 * bb:n1 * bb])
+    torch.cuda.synchronize()
     x = torch.randn((m, k), generator=torch.Generator().manual_seed(5678), dtype=torch.float32)
     xd = x.cuda()
     # gather buffer [world][m][n_loc]; rank r's matmul writes slot r (ldc = n_loc)
@@ -300,7 +377,22 @@ def colsplit_leg(torch, dist, backend: CudaBackend, rank: int, world: int, local
         step()
     backend.sync()
     torch.cuda.synchronize()
+    # parity: the gathered y against the unsplit matmul over the full weight on this GPU
+    y_full = torch.zeros((m, n), device="cuda", dtype=torch.float32)
+    rec_full = capi.MatMul(c=capi.Operand(y_full.data_ptr(), 0, m * n * 4), a=capi.Operand(xd.data_ptr(), 0, xd.numel() * 4),
+                           b=capi.Operand(h_full, 0, nb_full), b_dtype=capi.DTYPE_Q4_0, flags=capi.MATMUL_AUTO, m=m, n=n, k=k,
+                           lda=0, ldb=0, ldc=0, alpha=1.0, beta=0.0)
+    _chk(lib.aion_cuda_matmul(dev, C.byref(rec_full)))
+    backend.sync()
+    torch.cuda.synchronize()
+    assembled = assemble_gathered(gather.cpu().numpy())
+    want = y_full.cpu().numpy()
+    max_abs = float(np.max(np.abs(assembled - want)))
+    rel = float(np.linalg.norm(assembled.astype(np.float64) - want) / max(np.linalg.norm(want.astype(np.float64)), 1e-30))
     if world > 1:
+        worst = torch.tensor([max_abs, rel], device="cuda", dtype=torch.float64)
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+        max_abs, rel = float(worst[0].item()), float(worst[1].item())
         dist.barrier()
     ev0.record(stream)
     for _ in range(iters):
@@ -309,12 +401,14 @@ def colsplit_leg(torch, dist, backend: CudaBackend, rank: int, world: int, local
     backend.sync()
     torch.cuda.synchronize()
     ms = _max_over_ranks(torch, dist, world, ev0.elapsed_time(ev1)) / iters
-    checksum = float(gather.double().sum().item())
     mem.free(hw)
+    mem.free(h_full)
     total_w = (k // 32) * n * 18
     return {"m": m, "n": n, "k": k, "n_gpus": world, "columns_per_gpu": n_loc, "ms": round(ms, 4),
             "aggregate_weight_gbs": round(total_w / (ms * 1e-3) / 1e9, 1),
-            "all_gather_bytes_per_rank": m * n_loc * 4, "checksum": checksum}
+            "all_gather_bytes_per_rank": m * n_loc * 4,
+            "parity": {"against": "the unsplit matmul over the full weight on one GPU, every rank checks the gathered y",
+                       "max_abs_diff": max_abs, "rel_l2": rel, "pass": bool(rel <= 2e-5)}}
 
 
 def matmul_leg(torch, backend: CudaBackend, local_rank: int, dtype: int, nt: bool, m: int, n: int, k: int, lanes: int = 8,
@@ -386,3 +480,50 @@ def matmul_leg(torch, backend: CudaBackend, local_rank: int, dtype: int, nt: boo
     for h in (arena, hx, hy):
         mem.free(h)
     return out
+
+
+def gemm_cpu_baseline(dtype: int, m: int, n: int, k: int, threads: int, sample_rows: int = 256, budget_s: float = 3.0) -> dict:
+    """The reference's CPU path for the prefill GEMM (threaded port of its packed int8 GEMM) on a bounded
+    sample: `sample_rows` of the m rows against the whole weight, repeated for about `budget_s`."""
+    import oracle
+
+    rows = min(m, sample_rows)
+    rng = np.random.default_rng(1234)
+    b = oracle.quantize(dtype, (rng.standard_normal((k, n)) * 0.02).astype(np.float32), 0)
+    a = rng.standard_normal((rows, k)).astype(np.float32)
+    c = np.zeros(rows * n, dtype=np.float32)
+    oracle.fast_matmul_q(dtype, a, b, rows, n, k, c=c, threads=threads)
+    t0, reps = time.perf_counter(), 0
+    while time.perf_counter() - t0 < budget_s:
+        oracle.fast_matmul_q(dtype, a, b, rows, n, k, c=c, threads=threads)
+        reps += 1
+    dt = time.perf_counter() - t0
+    return {"value": round(2.0 * rows * n * k * reps / dt / 1e12, 4), "unit": "TFLOP/s", "cores": threads, "kind": "port",
+            "sample": f"{rows} of the {m} rows against the whole {k}x{n} weight, {reps} passes, threaded port of the reference's "
+                      f"packed int8 GEMM (vnni={oracle.fast_has_vnni()})"}
+
+
+def attention_cpu_baseline(batch: int, t_ctx: int, threads: int, heads: int = 8, kv_heads: int = 1, d: int = 256,
+                           sample_requests: int = 16, budget_s: float = 3.0) -> dict:
+    """The reference's CPU path for decode attention with f16 q (its generic per-row executor, which streams K/V
+    once per query head), requests over the host threads, on a bounded sample of the batch."""
+    import oracle
+
+    B = min(batch, sample_requests)
+    rng = np.random.default_rng(12)
+    q = rng.standard_normal((B, 1, heads, d)).astype(np.float16)
+    kk = rng.standard_normal((B, t_ctx, kv_heads, d)).astype(np.float16)
+    vv = rng.standard_normal((B, t_ctx, kv_heads, d)).astype(np.float16)
+    pos = np.full((B, 1), t_ctx - 1, np.int32)
+    lens = np.full(B, t_ctx, np.int32)
+    kw = dict(scale=1.0 / float(np.sqrt(d)), positions=pos, kv_lengths=lens, right=0, threads=threads)
+    oracle.fast_attention(q, kk, vv, **kw)
+    t0, reps = time.perf_counter(), 0
+    while time.perf_counter() - t0 < budget_s:
+        oracle.fast_attention(q, kk, vv, **kw)
+        reps += 1
+    dt = time.perf_counter() - t0
+    alg = 2 * kk.nbytes + q.nbytes + B * heads * d * 4
+    return {"value": round(alg * reps / dt / 1e9, 3), "unit": "GB/s", "cores": threads, "kind": "port",
+            "sample": f"{B} of the {batch} requests at context {t_ctx}, {reps} passes, the oracle's per-row executor with the requests "
+                      "spread over the host threads"}

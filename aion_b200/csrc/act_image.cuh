@@ -9,7 +9,9 @@
 //   rows are cut into groups of `rows_per_group` (2 for m = 1 — one pad row —, then 8, 16, 32, 64;
 //   more than 64 rows: groups of 64); K blocks are padded to a multiple of 8 (`kb_pad`);
 //   one group = codes [kb_pad][rows_per_group][32 B], then scales [kb_pad][rows_per_group] f32.
-//   Pad rows and pad blocks hold zero codes and zero scales (they then contribute nothing).
+//   Pad rows and pad blocks hold zero codes and zero scales (they then contribute nothing); the
+//   one exception is the pad row of a single-row image, which repeats the row's scale (its codes
+//   are zero all the same): the single-row kernel reads the two scales as the pair (s, s).
 // The 32 code bytes of a block are the 8 words the MMA B fragments read (quad lane j finds its
 // two registers at bytes 8j..8j+7):
 //   q8: word 2j = codes 4j..4j+3, word 2j+1 = codes 16+4j..16+4j+3
@@ -89,10 +91,12 @@ __device__ __forceinline__ uint8_t* act_image_codes(uint8_t* image, const ActIma
   const uint32_t g = row / L.rows_per_group, r = row - g * L.rows_per_group;
   return image + (size_t)g * L.group_bytes + ((size_t)kb * L.rows_per_group + r) * 32;
 }
-__device__ __forceinline__ float* act_image_scale(uint8_t* image, const ActImageLayout& L, uint32_t row, uint32_t kb) {
+__device__ __forceinline__ void act_image_store_scale(uint8_t* image, const ActImageLayout& L, uint32_t row, uint32_t kb, float scale) {
   const uint32_t g = row / L.rows_per_group, r = row - g * L.rows_per_group;
-  return reinterpret_cast<float*>(image + (size_t)g * L.group_bytes + (size_t)L.kb_pad * L.rows_per_group * 32) +
-         ((size_t)kb * L.rows_per_group + r);
+  float* s = reinterpret_cast<float*>(image + (size_t)g * L.group_bytes + (size_t)L.kb_pad * L.rows_per_group * 32) +
+             ((size_t)kb * L.rows_per_group + r);
+  *s = scale;
+  if (L.rows_per_group == 2 && r == 0) s[1] = scale;  // single-row image: the pad row repeats the scale
 }
 
 // The same quantizer for a producer whose threads hold four consecutive elements each: eight
@@ -124,7 +128,7 @@ __device__ __forceinline__ void quantize_store_block_8lanes(float4 v, uint32_t i
   }
   if (store) {
     reinterpret_cast<uint32_t*>(act_image_codes(image, L, row, kb))[pos] = word;
-    if (i == 0) *act_image_scale(image, L, row, kb) = scale * ((DT == AION_CUDA_DTYPE_Q4_0) ? 0.0625f : 1.0f);
+    if (i == 0) act_image_store_scale(image, L, row, kb, scale * ((DT == AION_CUDA_DTYPE_Q4_0) ? 0.0625f : 1.0f));
   }
 }
 

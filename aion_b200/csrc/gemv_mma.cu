@@ -220,6 +220,68 @@ __device__ __forceinline__ void block_step(uint32_t w0, uint32_t w1, uint32_t b0
   }
 }
 
+// D(16x8, s32) = A(16x32, s8 row) * B(32x8, s8 col), fresh accumulator.
+__device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
+// ---- up to 16 activation rows, 16 columns per warp: one MMA (or two) per K block -----------------
+// Here the weight side is most of the work, and what matters is that the shared-memory loads of
+// several K blocks are in flight before the first block's arithmetic needs them: the loads of
+// four blocks are issued ahead, spelled out below.
+template <int MT>
+struct SmallRegs {
+  uint32_t a0, a1, a2, a3;  // weight codes: rows g / g+8, low / high half of K
+  float s0, s1;             // scales of rows g and g+8
+  uint2 bq[MT];             // activation codes
+  uint64_t sc[MT];          // activation scales of rows 2j, 2j+1 (a single row: (s, s))
+};
+template <int DT, bool NT, int MT, int KBL, int STEP, int AQ_STRIDE, int AS_STRIDE>
+__device__ __forceinline__ void load_small(SmallRegs<MT>& r, uint32_t w0, uint32_t w1, uint32_t b0, uint32_t b1, uint32_t aq, uint32_t as) {
+  constexpr bool AL0 = NT ? (KBL & 1) != 0 : false;
+  constexpr bool AL1 = NT ? (KBL & 1) != 0 : true;
+  load_codes<DT, AL0, KBL * STEP>(w0, r.a0, r.a2);
+  load_codes<DT, AL1, KBL * STEP>(w1, r.a1, r.a3);
+  r.s0 = lds_f16<KBL * STEP>(b0);
+  r.s1 = lds_f16<KBL * STEP>(b1);
+#pragma unroll
+  for (int t = 0; t < MT; t++) {
+    r.bq[t] = lds_u64<KBL * AQ_STRIDE>(aq + t * 256);
+    r.sc[t] = lds_b64<KBL * AS_STRIDE>(as + t * 32);
+  }
+}
+// M1 (a single activation row): acc[0][0][0] holds (column g, column g+8) of that row; VAR picks the
+// int32 -> f32 step (0: the biased accumulator and one fused multiply-add, 1: conversion instructions).
+template <int MT, bool M1, int VAR>
+__device__ __forceinline__ void compute_small(const SmallRegs<MT>& r, uint64_t (&acc)[MT][1][2]) {
+  if (M1) {
+    int d[4];
+    if (VAR == 1) {
+      mma_s8(d, r.a0, r.a1, r.a2, r.a3, r.bq[0].x, r.bq[0].y);
+      const uint64_t x = pack2((float)d[0], (float)d[2]);
+      uint64_t y;
+      asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(y) : "l"(x), "l"(pack2(r.s0, r.s1)));
+      acc[0][0][0] = fma2(y, r.sc[0], acc[0][0][0]);
+    } else {
+      mma_s8_biased(d, r.a0, r.a1, r.a2, r.a3, r.bq[0].x, r.bq[0].y);
+      const uint64_t ws = pack2(r.s0, r.s1), nm = pack2(r.s0 * -MAGIC, r.s1 * -MAGIC);
+      acc[0][0][0] = fma2(fma2(pack2i(d[0], d[2]), ws, nm), r.sc[0], acc[0][0][0]);
+    }
+    return;
+  }
+  const float m0 = r.s0 * -MAGIC, m1 = r.s1 * -MAGIC;  // exact: an f16 value times 3 * 2^22
+  const uint64_t s0 = pack2(r.s0, r.s0), s1 = pack2(r.s1, r.s1), n0 = pack2(m0, m0), n1 = pack2(m1, m1);
+#pragma unroll
+  for (int t = 0; t < MT; t++) {
+    int d[4];
+    mma_s8_biased(d, r.a0, r.a1, r.a2, r.a3, r.bq[t].x, r.bq[t].y);
+    acc[t][0][0] = fma2(fma2(pack2i(d[0], d[1]), s0, n0), r.sc[t], acc[t][0][0]);
+    acc[t][0][1] = fma2(fma2(pack2i(d[2], d[3]), s1, n1), r.sc[t], acc[t][0][1]);
+  }
+}
+
 // CTA that owns unit u when G CTAs split U units as [c*U/G, (c+1)*U/G).
 __device__ __forceinline__ uint32_t unit_owner(uint64_t u, uint64_t U, uint64_t G) { return (uint32_t)(((u + 1) * G - 1) / U); }
 
@@ -244,7 +306,7 @@ __global__ void gemv_act_image_kernel(const float* __restrict__ a, uint64_t lda,
   uint4* dst = reinterpret_cast<uint4*>(act_image_codes(image, L, row, kb));
   dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
   dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
-  *act_image_scale(image, L, row, kb) = sc;
+  if (row < m || L.rows_per_group != 2) act_image_store_scale(image, L, row, kb, sc);
 }
 
 // DT: weight dtype; NT: weights are [n,k] row-major (else K-major); MT: groups of 8 activation
@@ -253,7 +315,7 @@ __global__ void gemv_act_image_kernel(const float* __restrict__ a, uint64_t lda,
 // per warp; RW: consumer warps stacked over the activation rows (1: four warps take all MT row
 // groups, 2: eight warps, each MT / 2 of them — the warps a scheduler needs to hide the latency
 // of the MMA and shared-memory loads once there is this much arithmetic per weight byte).
-template <int DT, bool NT, int MT, bool M1, bool RG, bool PREQ, int CG, int RW>
+template <int DT, bool NT, int MT, bool M1, bool RG, bool PREQ, int CG, int RW, int VAR = 0>
 __global__ void __launch_bounds__(threads_of(RW), RW == 2 ? 2 : 1) gemv_q_mma_kernel(const GemvParams p_in, const __grid_constant__ CUtensorMap tmap) {
   using G = Geom<DT, NT, CG>;
   constexpr int TN = G::TN;
@@ -404,6 +466,7 @@ __global__ void __launch_bounds__(threads_of(RW), RW == 2 ? 2 : 1) gemv_q_mma_ke
       dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
       dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
       act_s[(size_t)kb * MP2 + r] = sc;
+      if (M1) act_s[(size_t)kb * MP2 + 1] = sc;  // the pad row's codes are zero; the lanes read the pair as (s, s)
     }
   }
   asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_THREADS) : "memory");
@@ -461,9 +524,19 @@ __global__ void __launch_bounds__(threads_of(RW), RW == 2 ? 2 : 1) gemv_q_mma_ke
       asm volatile("" : "+r"(w0), "+r"(w1), "+r"(b0), "+r"(b1), "+r"(aq), "+r"(as)::"memory");
       constexpr int STEP = NT ? Q8_BYTES : G::KM_PITCH;
 #define AION_BLOCK(K) block_step<DT, NT, MTW, CG, K, STEP, G::CG_STRIDE, (int)AQ_STRIDE, (int)AS_STRIDE>(w0, w1, b0, b1, aq, as, acc)
-      if (MTW * CG <= 2) {
-        AION_BLOCK(0); AION_BLOCK(1); AION_BLOCK(2); AION_BLOCK(3);
-        AION_BLOCK(4); AION_BLOCK(5); AION_BLOCK(6); AION_BLOCK(7);
+      if constexpr (MTW * CG <= 2 && RW == 1) {
+        SmallRegs<MTW> r[4];
+#define AION_LOAD(K, R) load_small<DT, NT, MTW, K, STEP, (int)AQ_STRIDE, (int)AS_STRIDE>(r[R], w0, w1, b0, b1, aq, as)
+        AION_LOAD(0, 0); AION_LOAD(1, 1); AION_LOAD(2, 2); AION_LOAD(3, 3);
+        compute_small<MTW, M1, VAR>(r[0], acc); AION_LOAD(4, 0);
+        compute_small<MTW, M1, VAR>(r[1], acc); AION_LOAD(5, 1);
+        compute_small<MTW, M1, VAR>(r[2], acc); AION_LOAD(6, 2);
+        compute_small<MTW, M1, VAR>(r[3], acc); AION_LOAD(7, 3);
+        compute_small<MTW, M1, VAR>(r[0], acc);
+        compute_small<MTW, M1, VAR>(r[1], acc);
+        compute_small<MTW, M1, VAR>(r[2], acc);
+        compute_small<MTW, M1, VAR>(r[3], acc);
+#undef AION_LOAD
       } else {
         // Many MMAs per K block: two blocks per trip of a real loop, so that the loop body stays
         // inside the instruction cache closest to the schedulers (unrolled eight times it does not,
@@ -492,8 +565,13 @@ __global__ void __launch_bounds__(threads_of(RW), RW == 2 ? 2 : 1) gemv_q_mma_ke
       for (int t = 0; t < MTW; t++)
 #pragma unroll
         for (int c = 0; c < CG; c++) {
-          unpack2(acc[t][c][0], v[t][c][0], v[t][c][1]);
-          unpack2(acc[t][c][1], v[t][c][2], v[t][c][3]);
+          if (M1) {  // a single row: (column g, column g+8) of row 0 in the first accumulator
+            unpack2(acc[t][c][0], v[t][c][0], v[t][c][2]);
+            v[t][c][1] = v[t][c][3] = 0.0f;
+          } else {
+            unpack2(acc[t][c][0], v[t][c][0], v[t][c][1]);
+            unpack2(acc[t][c][1], v[t][c][2], v[t][c][3]);
+          }
           acc[t][c][0] = acc[t][c][1] = 0ull;
         }
       bool store = whole;
@@ -603,7 +681,7 @@ int32_t kernel_occupancy(KernelSetup& ks, Kernel kernel, AionCudaDevice* dev, in
   return AION_CUDA_OK;
 }
 
-template <int DT, bool NT, int MT, bool M1, bool RG, bool PREQ, int CG, int RW>
+template <int DT, bool NT, int MT, bool M1, bool RG, bool PREQ, int CG, int RW, int VAR = 0>
 KernelSetup& setup_of() {
   static KernelSetup ks;
   return ks;
@@ -641,16 +719,16 @@ int32_t encode_weight_map(const uint8_t* b, uint64_t ldb, uint32_t n, uint32_t k
   return AION_CUDA_OK;
 }
 
-template <int DT, bool NT, int MT, bool M1, bool RG, bool PREQ, int CG, int RW>
+template <int DT, bool NT, int MT, bool M1, bool RG, bool PREQ, int CG, int RW, int VAR = 0>
 int32_t launch(AionCudaDevice* dev, GemvParams p, const uint8_t* b, uint64_t ldb, const uint8_t* given_image) {
   using G = Geom<DT, NT, CG>;
   constexpr int TN = G::TN;
   constexpr int THREADS = threads_of(RW);
-  auto kernel = gemv_q_mma_kernel<DT, NT, MT, M1, RG, PREQ, CG, RW>;
+  auto kernel = gemv_q_mma_kernel<DT, NT, MT, M1, RG, PREQ, CG, RW, VAR>;
   constexpr uint32_t MP2 = M1 ? 2 : 8 * MT;
   const size_t smem = G::OFF_ACT + (PREQ ? (size_t)NS * act_bytes(KBT, MP2) : act_bytes(p.stages_per_tile * KBT, MP2));
   int per_sm = 0;
-  if (int32_t st = kernel_occupancy(setup_of<DT, NT, MT, M1, RG, PREQ, CG, RW>(), kernel, dev, THREADS, smem, &per_sm)) return st;
+  if (int32_t st = kernel_occupancy(setup_of<DT, NT, MT, M1, RG, PREQ, CG, RW, VAR>(), kernel, dev, THREADS, smem, &per_sm)) return st;
   uint64_t grid = (uint64_t)per_sm * dev->sm_count;
   if (dev->gemv_split_override) grid = (uint64_t)dev->gemv_split_override * dev->sm_count;  // CTAs per SM, tuning only
   if (grid > p.units) grid = p.units;
@@ -739,8 +817,17 @@ int32_t launch_m(AionCudaDevice* dev, const GemvParams& p, const uint8_t* b, uin
   // m >= 2: A is quantized once by a small kernel (or by the kernel that produced A) instead of
   // by every CTA. m = 1 quantizes its one row inside the kernel unless K is deep: past about
   // 3000 the small kernel is cheaper than 148 CTAs each quantizing the whole row.
-  if (p.m == 1) return (image || p.kblocks > 96) ? launch<DT, NT, 1, true, false, true, 1, 1>(dev, p, b, ldb, image)
-                                                 : launch<DT, NT, 1, true, false, false, 1, 1>(dev, p, b, ldb, nullptr);
+  if (p.m == 1) {
+    static const int variant = [] {
+      const char* e = std::getenv("AION_CUDA_GEMV_VARIANT");  // tuning: int32 -> f32 step of the single-row kernel
+      return e ? std::atoi(e) : 0;
+    }();
+    if (variant == 1)
+      return (image || p.kblocks > 96) ? launch<DT, NT, 1, true, false, true, 1, 1, 1>(dev, p, b, ldb, image)
+                                       : launch<DT, NT, 1, true, false, false, 1, 1, 1>(dev, p, b, ldb, nullptr);
+    return (image || p.kblocks > 96) ? launch<DT, NT, 1, true, false, true, 1, 1>(dev, p, b, ldb, image)
+                                     : launch<DT, NT, 1, true, false, false, 1, 1>(dev, p, b, ldb, nullptr);
+  }
   if (p.m <= 8) return launch<DT, NT, 1, false, false, true, 1, 1>(dev, p, b, ldb, image);
   if (p.m <= 16) return launch<DT, NT, 2, false, false, true, 1, 1>(dev, p, b, ldb, image);
   if (p.m <= 32) return launch<DT, NT, 4, false, false, true, 2, 2>(dev, p, b, ldb, image);

@@ -43,6 +43,8 @@ COPIES = 256
 W_BYTES = (K // 32) * N * 18
 BYTES_PER_LAUNCH = W_BYTES + 4 * M * K + 4 * M * N
 WORKLOAD = f"q4_0 GEMV (MatMul step) M={M} N={N} K={K}, {COPIES} distinct weight matrices per step"
+# The same `config` in both arms (ours and --impl reference): the workload and how caches are kept out of it.
+CONFIG = {"workload": WORKLOAD, "l2": "inputs larger than L2: every GEMV of a step reads a weight matrix no cache holds"}
 METRIC = "q4 GEMV HBM GB/s"
 
 # DRAM bytes per launch of the GEMV kernel from an ncu capture of this workload
@@ -57,6 +59,17 @@ def measured_peak_gbs():
             return float(json.load(f)["hbm_gbs"]), "measured"
     except Exception:
         return 6650.0, "fallback"
+
+
+def measured_peak_tflops():
+    """(burst, sustained) bf16 TFLOP/s of this pool's B200s, and which figures they are."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["bf16_tflops"]), float(d["bf16_tflops_sustained"]), "measured"
+    except Exception:
+        return 1590.0, 1400.0, "fallback"
 
 
 class ClockSampler:
@@ -97,7 +110,7 @@ class ClockSampler:
                         self.reasons.add(name)
             except Exception:
                 pass
-            self._stop.wait(0.01)
+            self._stop.wait(0.002)
 
     def __enter__(self):
         if self._h is not None:
@@ -208,6 +221,29 @@ def run_ours(args):
     ms_per_step = max_ms / args.steps
     bytes_per_step = COPIES * BYTES_PER_LAUNCH
     value = world * bytes_per_step / (ms_per_step * 1e-3) / 1e9
+
+    # ---- the same pass held for about two seconds, with the clocks it ran at (sampling only) ------
+    sustained = None
+    if not args.no_sustained:
+        n_sust = max(args.steps, int(2000.0 / max(ms_per_step, 1e-3)))
+        barrier()
+        with ClockSampler(local_rank) as sclocks:
+            ev0.record(stream)
+            for _ in range(n_sust):
+                chk(lib.aion_cuda_program_launch(dev, prog))
+            ev1.record(stream)
+            backend.sync()
+            torch.cuda.synchronize()
+        s_ms = ev0.elapsed_time(ev1)
+        if world > 1:
+            t = torch.tensor([s_ms], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            s_ms = float(t.item())
+        s_val = world * bytes_per_step * n_sust / (s_ms * 1e-3) / 1e9
+        sc = sclocks.summary()
+        sustained = {"value": round(s_val, 2), "unit": "GB/s", "steps": n_sust, "seconds": round(s_ms * 1e-3, 3),
+                     "frac_of_peak_per_gpu": round(s_val / world / measured_peak_gbs()[0], 4), "clocks": sc,
+                     "ms_per_step_times_sm_mhz": round(s_ms / n_sust * sc["sm_mhz"], 2) if sc.get("sm_mhz") else None}
 
     # ---- end to end from host buffers through the C ABI -------------------------------------
     e2e_steps = max(3, min(args.steps, 200))
@@ -322,9 +358,10 @@ def run_ours(args):
         "metric": METRIC, "value": round(value, 2), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 5), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "int8 x int4 -> int32, f32 scale/accumulate", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "l2": "inputs larger than L2: 2.4 GB of distinct weights per step",
-                   "parallelism": "replicas only" if world > 1 else "single GPU",
-                   "program": f"one recorded program per step; its 256 independent steps sit in {args.lanes} parallel lanes", "outputs_finite_nonzero": finite},
+        "config": dict(CONFIG),
+        "run": {"parallelism": "replicas only" if world > 1 else "single GPU", "distinct_weight_bytes_per_step": COPIES * W_BYTES,
+                "program": f"one recorded program per step; its 256 independent steps sit in {args.lanes} parallel lanes",
+                "outputs_finite_nonzero": finite},
         "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d_bytes,
                 "d2h_bytes_per_step": d2h_bytes, "steps": e2e_steps, "sessions": len(sessions),
                 "how": "host threads, one per session; a step = aion_cuda_h2d + aion_cuda_program_launch + aion_cuda_d2h",
@@ -337,19 +374,60 @@ def run_ours(args):
     }
     if cpu_baseline is not None:
         out["cpu_baseline"] = cpu_baseline
+    if sustained is not None:
+        out["sustained"] = sustained
     lib.aion_cuda_program_destroy(dev, prog)
     for h in (w_arena, x_dev, y_dev):
         mem.free(h)
+    from aion_b200 import benchmarks
+    from aion_b200.decoder import DecoderConfig
+
+    def leg(name, fn):
+        try:
+            out[name] = fn()
+        except Exception as e:  # the headline line must still print
+            out[name] = {"error": f"{type(e).__name__}: {e}"}
+
+    threads = host_threads()
+    if not args.no_extra_legs and world == 1:
+        # The other kernels of the path, each beside its roofline and the reference's CPU path (bounded samples).
+        tf_burst, tf_sust, tf_kind = measured_peak_tflops()
+
+        def gemm_rows():
+            rows = []
+            for dt, m in ((capi.DTYPE_Q4_0, 512), (capi.DTYPE_Q4_0, 2048), (capi.DTYPE_Q8_0, 2048)):
+                r = benchmarks.gemm_leg(torch, backend, local_rank, dt, m, 8192, 2048, iters=30, peak_tflops=tf_burst)
+                r["roofline"] = {"bound": "tensor", "achieved": r["tflops"], "peak": tf_burst, "unit": "TFLOP/s",
+                                 "frac": round(r["tflops"] / tf_burst, 4), "peak_kind": f"of {tf_kind} (bf16 burst)"}
+                if not args.skip_cpu_baseline and dt == capi.DTYPE_Q4_0 and m == 2048:
+                    r["cpu_baseline"] = benchmarks.gemm_cpu_baseline(dt, m, 8192, 2048, threads)
+                rows.append(r)
+            return {"metric": "prefill GEMM TFLOP/s (q4_0 / q8_0 [k/32][n] weights, k=2048, n=8192)", "rows": rows}
+
+        def attention_rows():
+            rows = []
+            for b, t in ((64, 1024), (64, 4096), (8, 4096)):
+                r = benchmarks.attention_leg(torch, backend, local_rank, b, t, iters=20, peak_gbs=peak)
+                r["roofline"] = {"bound": "hbm", "achieved": r["gbs"], "peak": peak, "unit": "GB/s", "frac": r["frac_of_measured_hbm"],
+                                 "peak_kind": f"of {peak_kind}"}
+                if not args.skip_cpu_baseline and (b, t) == (64, 4096):
+                    r["cpu_baseline"] = benchmarks.attention_cpu_baseline(b, t, threads)
+                rows.append(r)
+            return {"metric": "decode attention GB/s (8 query heads / 1 kv head, head_dim 256, f16)", "rows": rows}
+
+        leg("gemm", gemm_rows)
+        leg("attention", attention_rows)
+    if not args.no_extra_legs and world > 1:
+        def colsplit():
+            return {"metric": "column-split q4 layer (k=8192, n=28672) + NCCL all-gather",
+                    **benchmarks.colsplit_leg(torch, dist, backend, rank, world, local_rank, 1, iters=50)}
+
+        leg("colsplit", colsplit)
     if not args.no_decode:
         # Second leg of the metric: decode tokens/s of the synthetic q4 decoder on the same GPUs.
-        from aion_b200 import benchmarks
-        from aion_b200.decoder import DecoderConfig
-
-        try:
-            out["decode"] = benchmarks.decode_leg(torch, dist, backend, rank, world, local_rank, args.decode_requests,
-                                                  args.decode_steps, 3, args.lanes, DecoderConfig(layers=args.decode_layers), peak)
-        except Exception as e:  # the headline line must still print
-            out["decode"] = {"error": f"{type(e).__name__}: {e}"}
+        leg("decode", lambda: benchmarks.decode_leg(torch, dist, backend, rank, world, local_rank, args.decode_requests,
+                                                    args.decode_steps, 3, args.lanes, DecoderConfig(layers=args.decode_layers), peak,
+                                                    check=not args.skip_cpu_baseline, threads=threads))
     if rank == 0:
         print(json.dumps(out), flush=True)
     backend.deinit()
@@ -475,7 +553,7 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": round(value, 3), "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(dt / args.steps * 1e3, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8 x int4 -> int32, f32 scale/accumulate",
-        "data": "synthetic", "config": {"workload": WORKLOAD, "sample": sample},
+        "data": "synthetic", "config": dict(CONFIG), "run": {"sample": sample, "distinct_weight_bytes": copies * W_BYTES},
         "cpu_baseline": {"value": round(value, 3), "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": round(value, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -495,6 +573,9 @@ def main():
                          "their own line: decode tokens/s, prefill GEMM TFLOP/s, decode attention GB/s, the "
                          "column-split layer with its all-gather")
     ap.add_argument("--no-decode", action="store_true", help="gemv workload: leave the decoder leg out")
+    ap.add_argument("--no-sustained", action="store_true", help="gemv workload: leave out the two-second run of the same pass")
+    ap.add_argument("--no-extra-legs", action="store_true",
+                    help="gemv workload: leave out the prefill GEMM / attention legs (1 GPU) and the column-split leg (several GPUs)")
     ap.add_argument("--e2e-sessions", type=int, default=2, choices=[1, 2],
                     help="sessions (device objects + host threads) the end-to-end leg drives concurrently")
     ap.add_argument("--decode-requests", type=int, default=512, help="concurrent requests in total, split over the GPUs")

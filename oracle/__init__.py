@@ -188,6 +188,27 @@ def fast_matmul_nt_q8(a, b, m, n, k, *, alpha=1.0, beta=0.0, c=None, threads=0):
     return c.reshape(m, n)
 
 
+def fast_attention(q, k, v, *, scale, positions=None, kv_lengths=None, left=UNBOUNDED, right=UNBOUNDED, chunk=0, soft_cap=0.0,
+                   rolling=False, threads=0):
+    """`attention` with the requests spread over host threads (same values)."""
+    q = np.ascontiguousarray(q)
+    k = np.ascontiguousarray(k)
+    v = np.ascontiguousarray(v)
+    B, L, Hq, Dk = q.shape
+    _, T, Hkv, _ = k.shape
+    Dv = v.shape[3]
+    out = np.zeros((B, L, Hq, Dv), dtype=np.float32)
+    pos = None if positions is None else np.ascontiguousarray(positions, dtype=np.int32)
+    lens = None if kv_lengths is None else np.ascontiguousarray(kv_lengths, dtype=np.int32)
+    rc = lib().aion_oracle_fast_attention(
+        _p(out), _p(q), _dt(q), _p(k), _dt(k), _p(v), _dt(v), _p(pos), _p(lens),
+        C.c_uint64(B), C.c_uint64(L), C.c_uint64(Hq), C.c_uint64(Hkv), C.c_uint64(Dk), C.c_uint64(Dv),
+        C.c_uint64(T), C.c_float(scale), C.c_uint32(left), C.c_uint32(right), C.c_uint32(chunk),
+        C.c_float(soft_cap), int(rolling), int(threads))
+    _check(rc, "fast_attention")
+    return out
+
+
 # ---- decoder glue steps -----------------------------------------------------------------
 ELEMWISE_ADD, ELEMWISE_MUL, ELEMWISE_GATE_GELU = 0, 1, 2
 

@@ -16,6 +16,9 @@
 //   * q8_0 NT row-major: 2x2 micro-tile over prepared rows
 //     (src/aion/backend/cpu/kernels/matmul_nt_q.zig:74-95, 389-461), rows of B split across
 //     threads (src/aion/backend/cpu/exec/matmul_nt.zig:132-134).
+//   * `Attention`: the generic per-row executor of the scalar oracle, one request per task
+//     (the reference threads its per-row executor over rows,
+//     src/aion/backend/cpu/exec/attention.zig:1025-1318); same values as the scalar oracle.
 // A CPU without AVX-512-VNNI/AVX-VNNI runs the scalar byte dot (same values).
 #include <omp.h>
 
@@ -360,4 +363,34 @@ ORC_API int aion_oracle_fast_matmul_nt_q8(uint64_t m, uint64_t n, uint64_t k, fl
       }
   }
   return 0;
+}
+
+
+// The scalar oracle's attention (aion_oracle.cpp, same shared object).
+extern "C" int aion_oracle_attention(float* out, const void* q, int q_dtype, const void* k, int k_dtype, const void* v, int v_dtype,
+                                     const int32_t* positions, const int32_t* kv_lengths, uint64_t B, uint64_t L, uint64_t Hq,
+                                     uint64_t Hkv, uint64_t Dk, uint64_t Dv, uint64_t T, float scale, uint32_t win_left,
+                                     uint32_t win_right, uint32_t win_chunk, float soft_cap, int rolling, int exact);
+
+// `Attention`, requests in parallel: each task runs the scalar executor on one request.
+ORC_API int aion_oracle_fast_attention(float* out, const void* q, int q_dtype, const void* k, int k_dtype, const void* v, int v_dtype,
+                                       const int32_t* positions, const int32_t* kv_lengths, uint64_t B, uint64_t L, uint64_t Hq,
+                                       uint64_t Hkv, uint64_t Dk, uint64_t Dv, uint64_t T, float scale, uint32_t win_left,
+                                       uint32_t win_right, uint32_t win_chunk, float soft_cap, int rolling, int threads) {
+  if (threads <= 0) threads = omp_get_max_threads();
+  const size_t qe = q_dtype == 0 ? 4 : 2, ke = k_dtype == 0 ? 4 : 2, ve = v_dtype == 0 ? 4 : 2;
+  int status = 0;
+#pragma omp parallel for num_threads(threads) schedule(dynamic, 1)
+  for (uint64_t b = 0; b < B; b++) {
+    const int rc = aion_oracle_attention(out + b * L * Hq * Dv, static_cast<const uint8_t*>(q) + b * L * Hq * Dk * qe, q_dtype,
+                                         static_cast<const uint8_t*>(k) + b * T * Hkv * Dk * ke, k_dtype,
+                                         static_cast<const uint8_t*>(v) + b * T * Hkv * Dv * ve, v_dtype,
+                                         positions ? positions + b * L : nullptr, kv_lengths ? kv_lengths + b : nullptr, 1, L, Hq, Hkv, Dk,
+                                         Dv, T, scale, win_left, win_right, win_chunk, soft_cap, rolling, 0);
+    if (rc != 0) {
+#pragma omp atomic write
+      status = rc;
+    }
+  }
+  return status;
 }

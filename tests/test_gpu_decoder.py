@@ -15,7 +15,7 @@ import pytest
 import oracle
 from aion_b200 import capi
 from aion_b200.decoder import DecoderConfig, SyntheticDecoder
-from tests.decoder_ref import OracleDecoder
+from oracle.decoder_ref import OracleDecoder
 
 pytestmark = pytest.mark.gpu
 

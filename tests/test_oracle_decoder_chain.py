@@ -12,7 +12,7 @@ import numpy as np
 
 import oracle
 from aion_b200.decoder import DecoderConfig
-from tests.decoder_ref import OracleDecoder
+from oracle.decoder_ref import OracleDecoder
 
 
 def rel_l2(a, b):

@@ -34,3 +34,15 @@ def test_fast_alpha_beta():
     want = oracle.matmul_q(oracle.Q4_0, a, b, m, n, k, alpha=0.5, beta=2.0, c=c0)
     got = oracle.fast_matmul_q(oracle.Q4_0, a, b, m, n, k, alpha=0.5, beta=2.0, c=c0.reshape(-1).copy())
     assert rd.rel_l2(got, want) < 2e-6
+
+
+def test_fast_attention_equals_the_scalar_oracle():
+    rng = np.random.default_rng(0)
+    B, T, Hq, D = 5, 96, 8, 64
+    q = rng.standard_normal((B, 1, Hq, D)).astype(np.float16)
+    k = rng.standard_normal((B, T, 1, D)).astype(np.float16)
+    v = rng.standard_normal((B, T, 1, D)).astype(np.float16)
+    lens = np.array([96, 1, 40, 77, 13], np.int32)
+    pos = (lens - 1).reshape(B, 1)
+    kw = dict(scale=0.125, positions=pos, kv_lengths=lens, right=0)
+    assert np.array_equal(oracle.fast_attention(q, k, v, threads=3, **kw), oracle.attention(q, k, v, **kw))

@@ -64,7 +64,7 @@ def _worker(rank: int, world: int, port: int, tmp: str):
     assert np.array_equal(torch.cat(parts).numpy(), whole)
     # the decoder itself: every op is row-wise, so a request decodes to the same tokens in any shard
     from aion_b200.decoder import DecoderConfig
-    from tests.decoder_ref import OracleDecoder
+    from oracle.decoder_ref import OracleDecoder
 
     cfg = DecoderConfig(layers=1, hidden=64, ffn=128, heads=2, kv_heads=1, head_dim=32, vocab=96, ctx=8)
     drng = np.random.default_rng(7)

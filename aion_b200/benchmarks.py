@@ -197,7 +197,8 @@ def decode_leg(torch, dist, backend: CudaBackend, rank: int, world: int, local_r
         "hbm_gbs_per_gpu": round(step_bytes / (ms * 1e-3) / 1e9, 1),
         "hbm_frac_of_measured": round(step_bytes / (ms * 1e-3) / 1e9 / peak_gbs, 4),
         "launches_per_step": len(dec.steps), "replay_matches_eager": replay_same, "build_s": round(build_s, 1),
-        "matmul_kernel": "int8 (activation images written by the producing steps)" if dec.images else "tcgen05 GEMM (bf16 operands)",
+        "matmul_kernel": ("int8 tensor-core kernel" if R < capi.GEMM_MIN_M else "tcgen05 GEMM (bf16 operands)") +
+                         (", activation images written by the producing steps" if dec.images else ""),
         "config": {"layers": cfg.layers, "hidden": cfg.hidden, "ffn": cfg.ffn, "heads": cfg.heads, "kv_heads": cfg.kv_heads,
                    "head_dim": cfg.head_dim, "vocab": cfg.vocab, "ctx": cfg.ctx, "weights": "q4_0, N(0, 0.02), random init"},
     }

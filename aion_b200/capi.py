@@ -156,6 +156,7 @@ SIGNATURES = {
     "aion_cuda_record_end": (C.c_int32, [_DEV, C.POINTER(C.c_void_p)]),
     "aion_cuda_program_launch": (C.c_int32, [_DEV, C.c_void_p]),
     "aion_cuda_program_destroy": (None, [_DEV, C.c_void_p]),
+    "aion_cuda_debug_expire_waits": (C.c_int32, [_DEV, C.c_int32]),
     "aion_cuda_last_error": (C.c_int32, [C.c_char_p, C.c_size_t, C.POINTER(C.c_size_t)]),
     "aion_cuda_memory_model": (C.c_int32, [_DEV]),
     "aion_cuda_max_binding_bytes": (C.c_uint64, [_DEV]),

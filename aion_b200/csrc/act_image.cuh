@@ -18,22 +18,55 @@
 //   q4: word 2j = elements 8j+{0,2,4,6}, word 2j+1 = elements 8j+{1,3,5,7} (the order in which a
 //       word of q4 weight nibbles splits into its low and high nibbles); the scale carries an
 //       exact 1/16, which undoes the weights' placement in the high nibble of a byte.
+//
+// From the number of rows at which the tensor-core GEMM takes over (gemm_min_m()), the image is
+// what THAT kernel reads instead: row-major bf16 [m][k], every value the bf16 rounding of
+// code * scale of the same int8 quantization; for q4 weights the order of K inside every group
+// of 8 is e0 e4 e1 e5 e2 e6 e3 e7, the order in which a word of q4 nibbles unpacks two at a time.
 #pragma once
+
+#include <cuda_bf16.h>
 
 #include "common.cuh"
 #include "quant_device.cuh"
 
 namespace aion {
 
+constexpr uint32_t ACT_IMAGE_INT8 = 0, ACT_IMAGE_BF16 = 1;
+
 struct ActImageLayout {
-  uint32_t rows_per_group;
+  uint32_t kind;            // ACT_IMAGE_INT8 | ACT_IMAGE_BF16
+  uint32_t rows_per_group;  // int8 kind
   uint32_t groups;
   uint32_t kb_pad;
-  uint32_t group_bytes;
+  uint32_t group_bytes;     // bf16 kind: the whole image, m * k * 2
+  uint32_t kblocks;
 };
 
-__host__ __device__ inline ActImageLayout act_image_layout(uint64_t m, uint64_t kblocks) {
+// Rows of A from which aion_cuda_matmul runs the tensor-core GEMM (AION_CUDA_GEMM_MIN_M, or the
+// tuning override from the environment); defined with the routing in api.cu.
+uint64_t gemm_min_m();
+
+// The int8 kind whatever m is (the int8 kernel quantizing for itself when it was asked for by flag).
+inline ActImageLayout act_image_layout_int8(uint64_t m, uint64_t kblocks);
+
+inline ActImageLayout act_image_layout(uint64_t m, uint64_t kblocks) {
   ActImageLayout L;
+  L.kblocks = (uint32_t)kblocks;
+  if (m >= gemm_min_m()) {
+    L.kind = ACT_IMAGE_BF16;
+    L.rows_per_group = 1;
+    L.groups = 1;
+    L.kb_pad = (uint32_t)kblocks;
+    L.group_bytes = (uint32_t)(m * kblocks * QK * 2);
+    return L;
+  }
+  return act_image_layout_int8(m, kblocks);
+}
+inline ActImageLayout act_image_layout_int8(uint64_t m, uint64_t kblocks) {
+  ActImageLayout L;
+  L.kblocks = (uint32_t)kblocks;
+  L.kind = ACT_IMAGE_INT8;
   L.rows_per_group = m <= 1 ? 2u : (m <= 8 ? 8u : (m <= 16 ? 16u : (m <= 32 ? 32u : 64u)));
   L.groups = m <= 64 ? 1u : (uint32_t)((m + 63) / 64);
   L.kb_pad = (uint32_t)((kblocks + 7) / 8 * 8);
@@ -112,6 +145,21 @@ __device__ __forceinline__ void quantize_store_block_8lanes(float4 v, uint32_t i
   amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 4));
   float scale, inv;
   activation_block_scales(amax, &scale, &inv);
+  if (L.kind == ACT_IMAGE_BF16) {
+    // code * scale, rounded to bf16: what the GEMM's own pre-pass writes.
+    const float d0 = __fmul_rn((float)quantize_activation_with_inv(v.x, inv), scale), d1 = __fmul_rn((float)quantize_activation_with_inv(v.y, inv), scale);
+    const float d2 = __fmul_rn((float)quantize_activation_with_inv(v.z, inv), scale), d3 = __fmul_rn((float)quantize_activation_with_inv(v.w, inv), scale);
+    __nv_bfloat162 lo = __floats2bfloat162_rn(d0, d1), hi = __floats2bfloat162_rn(d2, d3);
+    uint2 out = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+    if (DT == AION_CUDA_DTYPE_Q4_0) {
+      // lanes 2u / 2u+1 hold e0..e3 / e4..e7 of a group of 8; the group is stored e0 e4 e1 e5 | e2 e6 e3 e7
+      const uint32_t plo = __shfl_xor_sync(0xFFFFFFFFu, out.x, 1), phi = __shfl_xor_sync(0xFFFFFFFFu, out.y, 1);
+      if (i & 1) out = make_uint2(__byte_perm(phi, out.y, 0x5410), __byte_perm(phi, out.y, 0x7632));   // (e2,e6), (e3,e7)
+      else out = make_uint2(__byte_perm(out.x, plo, 0x5410), __byte_perm(out.x, plo, 0x7632));          // (e0,e4), (e1,e5)
+    }
+    if (store) *reinterpret_cast<uint2*>(image + ((size_t)row * L.kblocks * QK + (size_t)kb * QK + 4 * i) * 2) = out;
+    return;
+  }
   const uint32_t q0 = (uint32_t)quantize_activation_with_inv(v.x, inv) & 0xFF;
   const uint32_t q1 = (uint32_t)quantize_activation_with_inv(v.y, inv) & 0xFF;
   const uint32_t q2 = (uint32_t)quantize_activation_with_inv(v.z, inv) & 0xFF;

@@ -7,14 +7,7 @@
 
 using namespace aion;
 
-namespace {
-
-// Bytes a K-major quantized B of `kblocks` block-rows must hold
-// (src/aion/backend/cpu/kernels/matvec_q.zig:85).
-uint64_t kmajor_bytes(uint64_t kblocks, uint64_t ldb, uint64_t n, size_t bb) {
-  return kblocks == 0 ? 0 : ((kblocks - 1) * ldb + n) * bb;
-}
-
+namespace aion {
 // Rows of A from which the step is a dense contraction for the tensor cores (bf16 operands);
 // below, the int8 kernel streams the weights with the reference CPU kernels' arithmetic.
 uint64_t gemm_min_m() {
@@ -24,6 +17,16 @@ uint64_t gemm_min_m() {
     return x > 0 ? (uint64_t)x : (uint64_t)AION_CUDA_GEMM_MIN_M;
   }();
   return v;
+}
+
+}  // namespace aion
+
+namespace {
+
+// Bytes a K-major quantized B of `kblocks` block-rows must hold
+// (src/aion/backend/cpu/kernels/matvec_q.zig:85).
+uint64_t kmajor_bytes(uint64_t kblocks, uint64_t ldb, uint64_t n, size_t bb) {
+  return kblocks == 0 ? 0 : ((kblocks - 1) * ldb + n) * bb;
 }
 
 int32_t route(AionCudaDevice* dev, const MatMulArgs& g, uint32_t flags, const char* what) {
@@ -54,6 +57,7 @@ int32_t route(AionCudaDevice* dev, const MatMulArgs& g, uint32_t flags, const ch
 int32_t resolve_image(const AionCudaOperand& op, uint64_t m, uint64_t k, const char* name, const uint8_t** out) {
   *out = nullptr;
   if (op.handle == 0) return AION_CUDA_OK;
+  if (m * k >= (1ull << 31)) return fail(AION_CUDA_UNSUPPORTED, "%s: shape beyond what an activation image holds", name);
   const size_t need = act_image_total_bytes(act_image_layout(m, k / QK));
   if (int32_t st = resolve(op, need, name, out)) return st;
   if (reinterpret_cast<uintptr_t>(*out) & 15) return fail(AION_CUDA_INVALID_ARGUMENT, "%s: the image must be 16-byte aligned", name);
@@ -148,7 +152,7 @@ int32_t aion_cuda_matmul_plan(AionCudaDevice* dev, const AionCudaMatMul* s, Aion
 int32_t aion_cuda_act_image_bytes(uint64_t m, uint64_t k, uint64_t* out_bytes) {
   if (!out_bytes) return fail(AION_CUDA_INVALID_ARGUMENT, "act_image_bytes: null out");
   if (k % QK != 0) return fail(AION_CUDA_INVALID_ARGUMENT, "act_image_bytes: k = %llu is not a multiple of 32", (unsigned long long)k);
-  if (m > (1ull << 22) || k > (1ull << 26)) return fail(AION_CUDA_UNSUPPORTED, "act_image_bytes: shape beyond what the matmul kernels index");
+  if (m > (1ull << 22) || k > (1ull << 26) || m * k >= (1ull << 31)) return fail(AION_CUDA_UNSUPPORTED, "act_image_bytes: shape beyond what the matmul kernels index");
   *out_bytes = m == 0 ? 0 : act_image_total_bytes(act_image_layout(m, k / QK));
   return AION_CUDA_OK;
 }
@@ -159,7 +163,7 @@ int32_t aion_cuda_act_image(AionCudaDevice* dev, uint32_t b_dtype, const AionCud
   if (b_dtype != AION_CUDA_DTYPE_Q8_0 && b_dtype != AION_CUDA_DTYPE_Q4_0) return fail(AION_CUDA_INVALID_ARGUMENT, "act_image: weight dtype %u", b_dtype);
   if (k % QK != 0 || k == 0) return fail(AION_CUDA_INVALID_ARGUMENT, "act_image: k = %llu must be a positive multiple of 32", (unsigned long long)k);
   if (m == 0) return AION_CUDA_OK;
-  if (m > (1ull << 22) || k > (1ull << 26)) return fail(AION_CUDA_UNSUPPORTED, "act_image: shape beyond what the matmul kernels index");
+  if (m > (1ull << 22) || k > (1ull << 26) || m * k >= (1ull << 31)) return fail(AION_CUDA_UNSUPPORTED, "act_image: shape beyond what the matmul kernels index");
   const uint64_t ld = lda ? lda : k;
   if (ld < k) return fail(AION_CUDA_INVALID_ARGUMENT, "act_image: lda is shorter than a row");
   const float* ap;

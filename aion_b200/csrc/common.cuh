@@ -86,6 +86,9 @@ struct AionCudaDevice {
 
   // Between aion_cuda_record_begin and aion_cuda_record_end.
   bool recording = false;
+  // Test hook (aion_cuda_debug_expire_waits): matmul launches leave out a copy and poll briefly,
+  // so that a bounded wait runs out and the fault path can be observed.
+  bool debug_expire_waits = false;
 
   // Tensor maps (TMA descriptors) already encoded for this device, keyed by view geometry.
   struct TmapCache;
@@ -199,6 +202,8 @@ int32_t gemm_tcgen05(AionCudaDevice* dev, const MatMulArgs& g);
 int32_t gemv_mma_static_scratch(AionCudaDevice* dev, const MatMulArgs& g);
 // Quantizes f32 rows into an activation image (act_image.cuh) for weights of `dtype`.
 int32_t act_image_from_f32(AionCudaDevice* dev, uint32_t dtype, const float* a, uint64_t m, uint64_t k, uint64_t lda, uint8_t* image);
+// The bf16 kind of image (what the tensor-core GEMM reads), written by that kernel's own pre-pass.
+int32_t act_image_bf16_from_f32(AionCudaDevice* dev, uint32_t dtype, const float* a, uint64_t m, uint64_t k, uint64_t lda, uint8_t* image);
 // What the prefill GEMM would do with this shape: rows per tile (128 or 256), K splits, CTAs.
 struct GemmPlan {
   uint32_t tile_rows, splits, grid;

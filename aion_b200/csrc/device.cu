@@ -486,6 +486,12 @@ void aion_cuda_program_destroy(AionCudaDevice* dev, AionCudaProgram* prog) {
   delete prog;
 }
 
+int32_t aion_cuda_debug_expire_waits(AionCudaDevice* dev, int32_t on) {
+  if (!dev) return fail(AION_CUDA_INVALID_ARGUMENT, "debug_expire_waits: null device");
+  dev->debug_expire_waits = on != 0;
+  return AION_CUDA_OK;
+}
+
 int32_t aion_cuda_last_error(char* buf, size_t cap, size_t* len) {
   const std::string& s = g_last_error;
   if (len) *len = s.size();

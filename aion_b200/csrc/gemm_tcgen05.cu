@@ -30,6 +30,7 @@
 #include <algorithm>
 #include <mutex>
 
+#include "act_image.cuh"
 #include "common.cuh"
 #include "ptx.cuh"
 #include "quant_device.cuh"
@@ -741,7 +742,10 @@ int32_t gemm_tcgen05(AionCudaDevice* dev, const MatMulArgs& g_in) {
   }
   __nv_bfloat16* a_bf16 = reinterpret_cast<__nv_bfloat16*>(scratch + relaid_bytes);
   float* partial = reinterpret_cast<float*>(scratch + relaid_bytes + a_bytes);
-  {
+  if (g.a_image && act_image_layout(g.m, g.k / QK).kind == ACT_IMAGE_BF16) {
+    // The step that produced A already wrote what the pre-pass would write.
+    a_bf16 = reinterpret_cast<__nv_bfloat16*>(const_cast<uint8_t*>(g.a_image));
+  } else {
     const uint64_t groups = g.m * (g.k / 8);
     const unsigned blocks = (unsigned)std::min<uint64_t>(ceil_div(groups, (uint64_t)256), (uint64_t)dev->sm_count * 8);
     AION_CUDA_TRY(launch_pdl_main(convert_a_bf16_kernel, dim3(blocks), dim3(256), 0, dev->stream, g.a, g.lda, a_bf16, (uint32_t)g.m, (uint32_t)g.k,
@@ -752,6 +756,15 @@ int32_t gemm_tcgen05(AionCudaDevice* dev, const MatMulArgs& g_in) {
                    : launch_gemm<AION_CUDA_DTYPE_Q4_0, 1>(dev, g, a_bf16, (uint32_t)splits, partial);
   return mh == 2 ? launch_gemm<AION_CUDA_DTYPE_Q8_0, 2>(dev, g, a_bf16, (uint32_t)splits, partial)
                  : launch_gemm<AION_CUDA_DTYPE_Q8_0, 1>(dev, g, a_bf16, (uint32_t)splits, partial);
+}
+
+
+int32_t act_image_bf16_from_f32(AionCudaDevice* dev, uint32_t dtype, const float* a, uint64_t m, uint64_t k, uint64_t lda, uint8_t* image) {
+  const uint64_t groups = m * (k / 8);
+  const unsigned blocks = (unsigned)std::min<uint64_t>(ceil_div(groups, (uint64_t)256), (uint64_t)dev->sm_count * 8);
+  AION_CUDA_TRY(launch_pdl_main(convert_a_bf16_kernel, dim3(blocks), dim3(256), 0, dev->stream, a, lda, reinterpret_cast<__nv_bfloat16*>(image),
+                                (uint32_t)m, (uint32_t)k, dtype == AION_CUDA_DTYPE_Q4_0 ? 1 : 0));
+  return AION_CUDA_OK;
 }
 
 }  // namespace aion

@@ -604,7 +604,7 @@ int32_t resolve_out_image(const AionCudaOperand& op, uint32_t dtype, uint64_t ro
   if (op.handle == 0) return AION_CUDA_OK;
   if (dtype != AION_CUDA_DTYPE_Q8_0 && dtype != AION_CUDA_DTYPE_Q4_0) return fail(AION_CUDA_INVALID_ARGUMENT, "%s: image dtype %u", name, dtype);
   if (cols % QK != 0) return fail(AION_CUDA_INVALID_ARGUMENT, "%s: an image needs rows of whole 32-blocks, got %llu columns", name, (unsigned long long)cols);
-  if (rows > (1ull << 22) || cols > (1ull << 26)) return fail(AION_CUDA_UNSUPPORTED, "%s: shape beyond what the matmul kernels index", name);
+  if (rows > (1ull << 22) || cols > (1ull << 26) || rows * cols >= (1ull << 31)) return fail(AION_CUDA_UNSUPPORTED, "%s: shape beyond what the matmul kernels index", name);
   if (int32_t st = resolve(op, act_image_total_bytes(act_image_layout(rows, cols / QK)), name, out)) return st;
   if (reinterpret_cast<uintptr_t>(*out) & 15) return fail(AION_CUDA_INVALID_ARGUMENT, "%s: the image must be 16-byte aligned", name);
   return AION_CUDA_OK;

@@ -102,10 +102,9 @@ class SyntheticDecoder:
                  weight_values: Callable[[str, int, int], object], embedding_values: Callable[[int, int], object],
                  store: Optional[DeviceStore] = None, fused: bool = True, images: bool = True):
         self.backend, self.cfg, self.requests, self.fused = backend, cfg, requests, fused
-        # Images ride on the fused steps, on rows the register-resident norm kernel takes, and only
-        # where the int8 kernel (which reads them) runs.
+        # Images ride on the fused steps and on rows the register-resident norm kernel takes.
         self.images = bool(images and fused and cfg.hidden % 32 == 0 and cfg.hidden <= 4096 and cfg.ffn % 32 == 0
-                           and cfg.head_dim in (64, 128, 256) and requests < capi.GEMM_MIN_M)
+                           and cfg.head_dim in (64, 128, 256))
         self.store = store or DeviceStore(backend.device_memory)
         self.session: CudaSession = backend.create_session(self.store)
         self._build_weights(weight_values, embedding_values)

@@ -127,6 +127,13 @@ AION_CUDA_API int32_t aion_cuda_record_join(AionCudaDevice* dev);
 AION_CUDA_API int32_t aion_cuda_record_end(AionCudaDevice* dev, AionCudaProgram** out);
 AION_CUDA_API int32_t aion_cuda_program_launch(AionCudaDevice* dev, AionCudaProgram* prog);
 AION_CUDA_API void aion_cuda_program_destroy(AionCudaDevice* dev, AionCudaProgram* prog);
+/* Test hook, no counterpart in the reference. Every wait a kernel of this library makes on a copy
+ * barrier is bounded: when it runs out, the kernel records a fault, lets the copies still in flight
+ * land and returns, and the next aion_cuda_sync / aion_cuda_d2h reports INTERNAL_ERROR; the device
+ * stays usable. While this switch is on, the tiled matmul kernels leave out their first weight copy
+ * and poll a few hundred times instead of a million, so that exactly this happens within
+ * milliseconds (the result of such a matmul is meaningless). For tests of the fault path. */
+AION_CUDA_API int32_t aion_cuda_debug_expire_waits(AionCudaDevice* dev, int32_t on);
 /* Per-thread diagnostic text of the last failing call on this thread
  * (aion src/aion/diagnostic.zig:8-44; include/aion.h:117-140). Copies at most `cap`
  * bytes, NUL-terminates when cap > 0, stores the full length in *len when non-NULL. */
@@ -166,8 +173,9 @@ AION_CUDA_API int32_t aion_cuda_memset(AionCudaDevice* dev, uint64_t handle, siz
  * integer dots, at a quarter to a third of the GEMM's speed once m reaches the hundreds.
  * f32 / f16 B return UNSUPPORTED.
  *   a_image (handle 0 = absent): the quantized image of A that the step producing A wrote
- *     (see aion_cuda_act_image_bytes); the int8 kernels then read it instead of quantizing A.
- *     Ignored by the tensor-core GEMM and the any-shape kernel, which read A itself.
+ *     (see aion_cuda_act_image_bytes); the kernel then reads it instead of quantizing A.
+ *     Ignored by the any-shape kernel, and by a kernel forced through `flags` onto a number of
+ *     rows whose image is laid out for the other one: those read A itself.
  * --------------------------------------------------------------------------------- */
 #define AION_CUDA_INT8_GROUP_ROWS 64 /* rows of A that share one pass over the weights */
 #define AION_CUDA_GEMM_MIN_M 33      /* from this many rows on, the tensor-core GEMM (bf16 operands) runs */
@@ -214,7 +222,11 @@ AION_CUDA_API int32_t aion_cuda_matmul_plan(AionCudaDevice* dev, const AionCudaM
  * to its f32 output, the int8 codes and block scales of that output in the order the int8
  * matmul kernel reads them, and the matmul that consumes it takes the image through `a_image`.
  * A decode layer then runs without a quantization kernel between its steps. The codes and
- * scales are exactly those the matmul would compute from the f32 values.
+ * scales are exactly those the matmul would compute from the f32 values. What an image holds
+ * follows the kernel that will read it, which the number of rows decides: below
+ * AION_CUDA_GEMM_MIN_M rows the int8 codes and f32 block scales in the int8 kernel's fragment
+ * order; from there on the same quantization dequantized and rounded to bf16, row-major, which is
+ * what the tensor-core GEMM's own pre-pass produces.
  *   aion_cuda_act_image_bytes: size of the image of an [m, k] activation (k % 32 == 0).
  *   aion_cuda_act_image: writes the image of f32 rows (row stride lda elements, 0 = k) for
  *     weights of `b_dtype` (q4_0 and q8_0 weights read their codes in different orders).

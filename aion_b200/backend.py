@@ -328,6 +328,10 @@ class StepAttention:
     window: AttentionWindow = dataclasses.field(default_factory=AttentionWindow)
     attn_logits_soft_cap: float = 0.0
     image: Optional[int] = None       # also write the quantized image of `out` (see `ActImage`)
+    # Paged K / V: k and v are pools [pages, page_tokens, Hkv, D] and page_table is i32 [B, pages per request];
+    # key t of request b is row t % page_tokens of page page_table[b, t // page_tokens].
+    page_table: Optional[int] = None
+    flags: int = 0                    # capi.ATTENTION_*
 
 
 @dataclasses.dataclass
@@ -467,7 +471,7 @@ class CudaSession:
             return reads, {step.c}
         if isinstance(step, StepAttention):
             reads = {step.q, step.k, step.v}
-            reads |= {t for t in (step.query_positions, step.kv_lengths) if t is not None}
+            reads |= {t for t in (step.query_positions, step.kv_lengths, step.page_table) if t is not None}
             return reads, {step.out} | img(step.image)
         if isinstance(step, StepRMSNorm):
             reads = {step.x, step.gamma, step.beta} | ({step.residual} if step.residual is not None else set())
@@ -608,11 +612,21 @@ class CudaSession:
         B, L, Hq, Dk = qm.shape
         _, T, Hkv, _ = km.shape
         Dv = vm.shape[3]
-        if km.shape[0] != B or vm.shape[0] != B or km.shape[3] != Dk or vm.shape[1] != T or vm.shape[2] != Hkv:
+        none = capi.Operand(0, 0, 0)
+        table, page_tokens, pool_pages = none, 0, 0
+        if s.page_table is not None:
+            tm = st.meta(s.page_table)
+            if tm.dtype != capi.DTYPE_I32 or tm.rank != 2 or tm.shape[0] != B:
+                raise BackendError(capi.INVALID_ARGUMENT, "attention: page_table must be i32 [B, pages per request]")
+            if tuple(vm.shape[:3]) != tuple(km.shape[:3]) or km.shape[3] != Dk:
+                raise BackendError(capi.INVALID_ARGUMENT, "attention: q/k/v shapes do not agree")
+            pool_pages, page_tokens = km.shape[0], km.shape[1]
+            T = tm.shape[1] * page_tokens
+            table = st.acquire_const(s.page_table).operand()
+        elif km.shape[0] != B or vm.shape[0] != B or km.shape[3] != Dk or vm.shape[1] != T or vm.shape[2] != Hkv:
             raise BackendError(capi.INVALID_ARGUMENT, "attention: q/k/v shapes do not agree")
         if tuple(om.shape) != (B, L, Hq, Dv):
             raise BackendError(capi.INVALID_ARGUMENT, "attention: out shape")
-        none = capi.Operand(0, 0, 0)
         pos = none
         if s.query_positions is not None:
             pm = st.meta(s.query_positions)
@@ -633,7 +647,7 @@ class CudaSession:
                              v_dtype=vm.dtype, rolling=rolling, batch=B, l_q=L, h_q=Hq, h_kv=Hkv, d_k=Dk, d_v=Dv,
                              t_cap=T, scale=s.scale, soft_cap=s.attn_logits_soft_cap,
                              window_left=s.window.left, window_right=s.window.right, window_chunk=s.window.chunk,
-                             flags=0)
+                             flags=s.flags, page_table=table, page_tokens=page_tokens, pool_pages=pool_pages)
         _check(self._lib.aion_cuda_attention(self.backend._h, C.byref(rec)))
 
 
@@ -870,6 +884,23 @@ def relayout_q8(backend: CudaBackend, order: int, n: int, k: int, src: np.ndarra
         mem.copy_h2d(hs, 0, s)
         so, do = capi.Operand(hs, 0, s.nbytes), capi.Operand(hd, 0, s.nbytes)
         _check(backend._lib.aion_cuda_relayout_q8(backend._h, order, int(inverse), n, k, C.byref(so), C.byref(do)))
+        out = np.empty(s.nbytes, dtype=np.uint8)
+        mem.copy_d2h(out, hd, 0)
+        return out
+    finally:
+        mem.free(hs)
+        mem.free(hd)
+
+
+def derive_kmajor_q8(backend: CudaBackend, order: int, n: int, k: int, src: np.ndarray) -> np.ndarray:
+    """The K-major [k/32][n] derived weight of a q8_0 [n, k] tensor stored in `order` (bytes in, bytes out)."""
+    s = np.ascontiguousarray(src, dtype=np.uint8)
+    mem = backend.device_memory
+    hs, hd = mem.alloc(max(s.nbytes, 1)), mem.alloc(max(s.nbytes, 1))
+    try:
+        mem.copy_h2d(hs, 0, s)
+        so, do = capi.Operand(hs, 0, s.nbytes), capi.Operand(hd, 0, s.nbytes)
+        _check(backend._lib.aion_cuda_derive_kmajor_q8(backend._h, order, n, k, C.byref(so), C.byref(do)))
         out = np.empty(s.nbytes, dtype=np.uint8)
         mem.copy_d2h(out, hd, 0)
         return out

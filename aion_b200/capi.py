@@ -67,6 +67,10 @@ class MatMulNT(C.Structure):
     ]
 
 
+ATTENTION_GENERIC = 1
+ATTENTION_ROW_UNITS = 2
+
+
 class Attention(C.Structure):
     _fields_ = [
         ("out", Operand), ("q", Operand), ("k", Operand), ("v", Operand),
@@ -77,7 +81,8 @@ class Attention(C.Structure):
         ("scale", C.c_float), ("soft_cap", C.c_float),
         ("window_left", C.c_uint32), ("window_right", C.c_uint32), ("window_chunk", C.c_uint32),
         ("flags", C.c_uint32),
-        ("image", Operand), ("image_dtype", C.c_uint32), ("reserved", C.c_uint32),
+        ("image", Operand), ("image_dtype", C.c_uint32), ("page_tokens", C.c_uint32),
+        ("page_table", Operand), ("pool_pages", C.c_uint64),
     ]
 
 
@@ -185,6 +190,7 @@ SIGNATURES = {
     "aion_cuda_quantize": (C.c_int32, [_DEV, C.c_uint32, _OPP, C.POINTER(C.c_uint64), C.c_uint32, C.c_uint32, _OPP]),
     "aion_cuda_dequantize": (C.c_int32, [_DEV, C.c_uint32, _OPP, C.c_uint64, _OPP]),
     "aion_cuda_relayout_q8": (C.c_int32, [_DEV, C.c_uint32, C.c_uint32, C.c_uint64, C.c_uint64, _OPP, _OPP]),
+    "aion_cuda_derive_kmajor_q8": (C.c_int32, [_DEV, C.c_uint32, C.c_uint64, C.c_uint64, _OPP, _OPP]),
 }
 
 _lib = None

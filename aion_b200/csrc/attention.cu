@@ -10,7 +10,10 @@
 // Two kernels:
 //  * attn_decode_kernel — f16 K/V with Dk = Dv in {64, 128, 256}: the decode hot path.
 //    HBM-bound: K and V are read from global memory once per (b, l, kv head); the up to
-//    eight query heads of the group share them. A producer warp brings 64-key stages
+//    eight query heads of the group share them. With several query rows per request (prefill,
+//    the reference's 32-row block kernel, exec/attention.zig:546-963) a CTA takes a block of
+//    up to 64 (position, head) columns instead and streams K / V once for all of them, each
+//    column masked to its own key range. K / V may live in a pool of pages behind a page table. A producer warp brings 64-key stages
 //    of K and V rows into shared memory with 1-D bulk (TMA) copies (row pitch padded by
 //    16 bytes so ldmatrix is conflict free); four consumer warps take 16 keys each.
 //    Both contractions run on the tensor cores in transposed form so that no
@@ -53,7 +56,12 @@ struct AttnParams {
   float scale, soft_cap;
   uint32_t splits;
   uint32_t head_groups;  // ceil((Hq/Hkv) / 8)
-  float* partial;        // [unit][split][8 heads][Dv + 4]: sums, max, sum of weights, pad
+  uint32_t col_heads;    // query heads of a head group: min(Hq/Hkv, 8)
+  uint32_t pos_per_tile; // query positions sharing one 8-column MMA tile
+  uint32_t l_blocks;     // blocks of positions per request
+  const int32_t* page_table;  // [B][pages_per_request] page numbers, or null: K / V are [B, T, ...]
+  uint32_t page_tokens, pages_per_request, pool_pages;
+  float* partial;        // [unit][split][columns][Dv + 4]: sums, max, sum of weights, pad
   int* tickets;          // [unit]
   int* fault;
   // Optional: the quantized image of `out` as [B*L, Hq*Dv] rows (act_image.cuh), for the matmul
@@ -140,50 +148,73 @@ __device__ __forceinline__ uint32_t tile_off(uint32_t row, uint32_t chunk) {
   return row * (D * 2 + 16) + (chunk << 4);
 }
 
-template <int D>
+// A CTA serves COLS "query columns" of one kv head: column = (query position, query head of the
+// group). The MMAs run in transposed form, so a column is one of the 8 columns (n) of an MMA and
+// NTT is the number of such 8-column tiles per CTA.
+//  * decode (BLOCK = false): NT tiles, every consumer warp works on all of them and takes 16 of
+//    a stage's 64 keys; the four warps are folded at the end.
+//  * query blocks (BLOCK = true, l_q > 1): each warp owns NT tiles of its own and walks all 64
+//    keys of every stage, so K and V are read once per block of positions and nothing is folded.
+template <int D, bool QF32, bool BLOCK, int NT>
 struct DecodeGeom {
+  static constexpr int NTT = BLOCK ? CONSUMER_WARPS * NT : NT;
+  static constexpr int COLS = 8 * NTT;
   static constexpr int PITCH = D * 2 + 16;            // bytes per K / V row in shared memory (padded layout)
   static constexpr int TILE_BYTES = KT * PITCH;       // one of K, V
   static constexpr int STAGE_BYTES = 2 * TILE_BYTES;  // K then V
-  static constexpr int QFRAG_BYTES = (D / 16) * 32 * 8;  // one of hi, lo
-  static constexpr int MERGE_BYTES = CONSUMER_WARPS * (8 * D + 16) * 4;
-  static constexpr int NS_MAX = (220 * 1024 - 2 * QFRAG_BYTES - 256) / STAGE_BYTES;
+  static constexpr int QFRAG_BYTES = (D / 16) * 32 * 8;  // one tile, one of hi, lo
+  static constexpr int Q_BYTES = NTT * QFRAG_BYTES * (QF32 ? 2 : 1);
+  static constexpr int STAGING_BUFS = BLOCK ? 1 : CONSUMER_WARPS;
+  static constexpr int WS = COLS * D + 2 * COLS;      // floats per staging buffer: sums, then max and weight per column
+  static constexpr int MERGE_BYTES = STAGING_BUFS * WS * 4;
+  static constexpr int META_BYTES = COLS * 12;        // per column: output row, first key, key end
+  static constexpr int NS_MAX = (220 * 1024 - Q_BYTES - META_BYTES - 256) / STAGE_BYTES;
   static constexpr int NS = NS_MAX > 4 ? 4 : NS_MAX;
   static_assert(NS >= 2, "ring too small");
   static_assert(MERGE_BYTES <= NS * STAGE_BYTES, "merge buffer reuses the ring");
   static constexpr int OFF_QHI = NS * STAGE_BYTES;
-  static constexpr int OFF_QLO = OFF_QHI + QFRAG_BYTES;
-  static constexpr int OFF_BARS = OFF_QLO + QFRAG_BYTES;
+  static constexpr int OFF_QLO = OFF_QHI + NTT * QFRAG_BYTES;
+  static constexpr int OFF_META = OFF_QHI + Q_BYTES;
+  static constexpr int OFF_BARS = OFF_META + META_BYTES;
   static constexpr int SMEM_BYTES = OFF_BARS + 2 * NS * 8 + 32;
+  // The merge of split partials keeps (max, weight) of every column and split in the drained ring.
+  static constexpr int MAX_SPLITS = (NS * STAGE_BYTES / 4 - COLS) / (2 * COLS);
 };
 
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory"); }
 
-template <int D, bool QF32, bool TILED>
+constexpr uint32_t NO_ROW = 0xFFFFFFFFu;
+
+template <int D, bool QF32, bool TILED, bool BLOCK, int NT>
 __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tmap_k,
                                                                  const __grid_constant__ CUtensorMap tmap_v) {
-  using G = DecodeGeom<D>;
-  constexpr int NS = G::NS;
+  using G = DecodeGeom<D, QF32, BLOCK, NT>;
+  constexpr int NS = G::NS, COLS = G::COLS, NTT = G::NTT;
   extern __shared__ __align__(1024) uint8_t smem[];  // swizzled TMA tiles need 1024-byte alignment
   const uint32_t smem_base = ptx::smem_u32(smem);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, j = lane & 3;
 
-  // unit = (b, l, hkv, head group); split = blockIdx.y
-  uint32_t unit = blockIdx.x;
+  // unit = (b, block of positions, hkv, head group); split = blockIdx.y
+  const uint32_t unit = blockIdx.x;
   const uint32_t hg = unit % p.head_groups;
   const uint32_t hkv = (unit / p.head_groups) % p.Hkv;
   const uint32_t bl = unit / (p.head_groups * p.Hkv);
-  const uint32_t l = bl % p.L, b = bl / p.L;
+  const uint32_t lb = bl % p.l_blocks, b = bl / p.l_blocks;
   const uint32_t split = blockIdx.y;
   const uint32_t group = p.Hq / p.Hkv;
   const uint32_t h0 = hkv * group + hg * 8;
   const uint32_t nh = min(8u, group - hg * 8);
+  const uint32_t l0 = lb * (NTT * p.pos_per_tile);
 
   const uint32_t bar_full = smem_base + G::OFF_BARS;
   const uint32_t bar_empty = bar_full + NS * 8;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + G::OFF_BARS + 2 * NS * 8);
   int* last_flag = const_cast<int*>(abort_flag) + 1;
+  uint32_t* union_range = reinterpret_cast<uint32_t*>(const_cast<int*>(abort_flag) + 2);  // lo, hi, bad
+  uint32_t* col_row = reinterpret_cast<uint32_t*>(smem + G::OFF_META);  // (b*L + l)*Hq + head, NO_ROW for a column that is padding
+  uint32_t* col_lo = col_row + COLS;
+  uint32_t* col_hi = col_lo + COLS;
 
   if (tid == 0) {
     for (int s = 0; s < NS; s++) {
@@ -192,6 +223,9 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParam
     }
     *abort_flag = 0;
     *last_flag = 0;
+    union_range[0] = 0xFFFFFFFFu;
+    union_range[1] = 0;
+    union_range[2] = 0;
     ptx::fence_barrier_init();
   }
   __syncthreads();
@@ -199,24 +233,50 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParam
   // q, K, V, positions and lengths may all come from the previous kernel.
   ptx::pdl_wait();
 
-  const KeyRange kr = key_range(p, b, l);
-  if (kr.bad && tid == 0) atomicExch(p.fault, FAULT_INVALID_ARGUMENT);
-  const uint32_t nkeys = kr.hi - kr.lo;
-  uint32_t per = (nkeys + p.splits - 1) / p.splits;
-  per = (per + 15) & ~15u;
-  const uint32_t my_lo = min(kr.hi, kr.lo + split * per);
-  const uint32_t my_hi = min(kr.hi, my_lo + per);
-  const uint32_t my_n = my_hi - my_lo;
-  const uint32_t ntiles = (my_n + KT - 1) / KT;
+  // Every column's row and key range; the CTA walks the union of the ranges and masks per column.
+  for (uint32_t c = tid; c < (uint32_t)COLS; c += THREADS) {
+    const uint32_t tile = c >> 3, cc = c & 7;
+    const uint32_t pl = cc / p.col_heads, hh = cc - pl * p.col_heads;
+    const uint32_t l = l0 + tile * p.pos_per_tile + pl;
+    uint32_t row = NO_ROW, lo = 0, hi = 0;
+    if (pl < p.pos_per_tile && hh < nh && l < p.L) {
+      const KeyRange kr = key_range(p, b, l);
+      if (kr.bad) atomicOr(union_range + 2, 1u);
+      row = (b * p.L + l) * p.Hq + h0 + hh;
+      lo = kr.lo, hi = kr.hi;
+      if (hi > lo) {
+        atomicMin(union_range, lo);
+        atomicMax(union_range + 1, hi);
+      }
+    }
+    col_row[c] = row, col_lo[c] = lo, col_hi[c] = hi;
+  }
+  __syncthreads();
+  const bool bad = union_range[2] != 0;
+  if (bad && tid == 0) atomicExch(p.fault, FAULT_INVALID_ARGUMENT);
+  const uint32_t u_hi = union_range[1], u_lo = min(union_range[0], u_hi);
+  // Splits walk disjoint slices of the union. With a page table a stage must not straddle a
+  // page, so slices then start on multiples of a stage (the keys before a column's range are
+  // masked like any others).
+  const uint32_t base = p.page_tokens ? (u_lo / KT) * KT : u_lo;
+  uint32_t per = (u_hi - base + p.splits - 1) / p.splits;
+  per = p.page_tokens ? (per + KT - 1) / KT * KT : (per + 15) & ~15u;
+  const uint32_t my_lo = min(u_hi, base + split * per);
+  const uint32_t my_hi = min(u_hi, my_lo + per);
+  const uint32_t ntiles = (my_hi - my_lo + KT - 1) / KT;
 
-  // running state of this lane's two heads (2j, 2j+1), log2 domain
-  float m_run[2] = {-INFINITY, -INFINITY};
-  float l_run[2] = {0.0f, 0.0f};
-  float acc[D / 16][4];
+  // running state of this lane's two columns (2j, 2j+1) of every tile, log2 domain
+  float m_run[NT][2], l_run[NT][2];
+  float acc[D / 16][NT][4];
 #pragma unroll
-  for (int t = 0; t < D / 16; t++)
+  for (int nt = 0; nt < NT; nt++) {
+    m_run[nt][0] = m_run[nt][1] = -INFINITY;
+    l_run[nt][0] = l_run[nt][1] = 0.0f;
 #pragma unroll
-    for (int e = 0; e < 4; e++) acc[t][e] = 0.0f;
+    for (int t = 0; t < D / 16; t++)
+#pragma unroll
+      for (int e = 0; e < 4; e++) acc[t][nt][e] = 0.0f;
+  }
 
   if (warp == CONSUMER_WARPS) {
     // ---------------- producer ----------------
@@ -242,7 +302,14 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParam
         // rows or zeros past the tensor) and are cleared by the consumers before use.
         if (lane == 0) {
           ptx::mbar_arrive_expect_tx(full, 2u * KT * D * 2);
-          const int32_t y = (int32_t)(b * p.T + t0);
+          int32_t y;
+          if (p.page_tokens) {
+            // t0 is a multiple of a stage and a page is a whole number of stages.
+            const int32_t page = p.page_table[(uint64_t)b * p.pages_per_request + t0 / p.page_tokens];
+            y = (int32_t)((uint32_t)page * p.page_tokens + t0 % p.page_tokens);
+          } else {
+            y = (int32_t)(b * p.T + t0);
+          }
 #pragma unroll
           for (int cb = 0; cb < D / 64; cb++) {
             ptx::tma_load_2d(stage + cb * (KT * 128), &tmap_k, (int32_t)(hkv * D + cb * 64), y, full);
@@ -266,16 +333,17 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParam
         ptx::mbar_wait_bounded(bar_full + 8 * (it % NS), (it / NS) & 1, 1u << 16);
   } else {
     // ---------------- consumers ----------------
-    // Q^T fragments: for k-step s, lane (g, j) needs (q[g][16s+2j], q[g][16s+2j+1]) and
-    // the same at +8; rows g >= nh are zero. An f32 q is split hi + lo.
+    // Q^T fragments: for tile n and k-step s, lane (g, j) needs (q[column g][16s+2j], q[..][16s+2j+1])
+    // and the same at +8; padding columns are zero. An f32 q is split hi + lo.
     {
       uint2* qhi = reinterpret_cast<uint2*>(smem + G::OFF_QHI);
       uint2* qlo = reinterpret_cast<uint2*>(smem + G::OFF_QLO);
-      for (int i = tid; i < (D / 16) * 32; i += CONSUMER_WARPS * 32) {
-        const int s = i >> 5, ln = i & 31, gg = ln >> 2, jj = ln & 3;
+      for (int i = tid; i < NTT * (D / 16) * 32; i += CONSUMER_WARPS * 32) {
+        const int tile = i / ((D / 16) * 32), s = (i >> 5) % (D / 16), ln = i & 31, gg = ln >> 2, jj = ln & 3;
         float v[4] = {0, 0, 0, 0};
-        if ((uint32_t)gg < nh) {
-          const uint64_t off = (((uint64_t)b * p.L + l) * p.Hq + h0 + gg) * D + 16 * s + 2 * jj;
+        const uint32_t row = col_row[tile * 8 + gg];
+        if (row != NO_ROW) {
+          const uint64_t off = (uint64_t)row * D + 16 * s + 2 * jj;
           if (QF32) {
             const float* qp = static_cast<const float*>(p.q) + off;
             v[0] = qp[0]; v[1] = qp[1]; v[2] = qp[8]; v[3] = qp[9];
@@ -291,9 +359,23 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParam
                               pack_half2(v[2] - __half2float(h2a), v[3] - __half2float(h3a)));
       }
     }
+    // This lane's columns and their key ranges clipped to this CTA's slice (lo, length).
+    const uint32_t tile0 = BLOCK ? warp * NT : 0;
+    uint32_t c_lo[NT][2], c_len[NT][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+      for (int hh = 0; hh < 2; hh++) {
+        const uint32_t c = (tile0 + nt) * 8 + 2 * j + hh;
+        const uint32_t lo = max(col_lo[c], my_lo), hi = min(col_hi[c], my_hi);
+        c_lo[nt][hh] = lo;
+        c_len[nt][hh] = hi > lo ? hi - lo : 0;
+      }
     consumer_sync();
 
     const float sc = (p.soft_cap > 0.0f) ? p.scale : p.scale * LOG2E;
+    const uint2* qhi = reinterpret_cast<const uint2*>(smem + G::OFF_QHI) + tile0 * (D / 16) * 32;
+    const uint2* qlo = reinterpret_cast<const uint2*>(smem + G::OFF_QLO) + tile0 * (D / 16) * 32;
     bool ok = true;
     for (uint32_t it = 0; it < ntiles; it++) {
       const uint32_t slot = it % NS;
@@ -308,11 +390,13 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParam
       const uint32_t cnt = min((uint32_t)KT, my_hi - t0);
       const uint32_t kst = smem_base + slot * G::STAGE_BYTES;
       const uint32_t vst = kst + G::TILE_BYTES;
-      const uint32_t r0 = 16 * warp;
-      if (ok && r0 < cnt) {
+#pragma unroll 1
+      for (uint32_t r0 = BLOCK ? 0 : 16 * warp; r0 < (BLOCK ? (uint32_t)KT : 16 * warp + 16); r0 += 16) {
+        if (!ok || r0 >= cnt) break;
         const uint32_t valid = min(16u, cnt - r0);
         if (valid < 16) {
-          // Rows past the range were not copied: clear them so stale bits cannot reach an MMA.
+          // Rows past the slice were not copied (or hold other rows): clear them so stale bits cannot
+          // reach an MMA. (With query blocks every warp clears the same rows with the same zeros.)
           uint8_t* kt = smem + slot * G::STAGE_BYTES;
           for (uint32_t i = lane; i < (16 - valid) * (D * 2 / 16); i += 32) {
             const uint32_t rr = r0 + valid + i / (D * 2 / 16), cc = i % (D * 2 / 16);
@@ -321,149 +405,168 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParam
           }
           __syncwarp();
         }
-        // ---- S^T[16 keys x 8 heads] = K . Q^T ----
-        // Four accumulators (even / odd k-steps, high / low half of an f32 q) keep the chain of
-        // dependent MMAs a quarter as long; a CTA works on one tile at a time, so nothing else
-        // would hide that latency.
-        float s[4] = {0, 0, 0, 0};
+        // ---- S^T[16 keys x 8 columns] = K . Q^T per tile ----
+        // Separate accumulators (even / odd k-steps when there is one tile, high / low half of an
+        // f32 q) keep the chains of dependent MMAs short.
+        constexpr int CH = NT == 1 ? 2 : 1;
+        float s_hi[NT][CH][4], s_lo[NT][CH][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+          for (int c = 0; c < CH; c++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) s_hi[nt][c][e] = s_lo[nt][c][e] = 0.0f;
         {
-          float sa[4] = {0, 0, 0, 0}, sb[4] = {0, 0, 0, 0}, sc[4] = {0, 0, 0, 0}, sd[4] = {0, 0, 0, 0};
           const uint32_t a_row = r0 + (lane & 7) + 8 * ((lane >> 3) & 1);
           const uint32_t a_chunk = lane >> 4;
-          const uint2* qhi = reinterpret_cast<const uint2*>(smem + G::OFF_QHI);
-          const uint2* qlo = reinterpret_cast<const uint2*>(smem + G::OFF_QLO);
 #pragma unroll
           for (int ks = 0; ks < D / 16; ks++) {
             uint32_t a0, a1, a2, a3;
             ldmatrix_x4(kst + tile_off<D, TILED>(a_row, 2 * ks + a_chunk), a0, a1, a2, a3);
-            const uint2 bh = qhi[ks * 32 + lane];
-            mma_f16((ks & 1) ? sb : sa, a0, a1, a2, a3, bh.x, bh.y);
-            if (QF32) {
-              const uint2 bl2 = qlo[ks * 32 + lane];
-              mma_f16((ks & 1) ? sd : sc, a0, a1, a2, a3, bl2.x, bl2.y);
+#pragma unroll
+            for (int nt = 0; nt < NT; nt++) {
+              const uint2 bh = qhi[(nt * (D / 16) + ks) * 32 + lane];
+              mma_f16(s_hi[nt][ks % CH], a0, a1, a2, a3, bh.x, bh.y);
+              if (QF32) {
+                const uint2 bl2 = qlo[(nt * (D / 16) + ks) * 32 + lane];
+                mma_f16(s_lo[nt][ks % CH], a0, a1, a2, a3, bl2.x, bl2.y);
+              }
             }
           }
-#pragma unroll
-          for (int e = 0; e < 4; e++) s[e] = (sa[e] + sb[e]) + (sc[e] + sd[e]);
         }
-        // s[0], s[1]: key g, heads 2j, 2j+1;  s[2], s[3]: key g+8.
-        const bool in0 = (uint32_t)g < valid, in1 = (uint32_t)(g + 8) < valid;
-        float lg[4];
+        // s[0], s[1]: key g, columns 2j, 2j+1;  s[2], s[3]: key g+8.
+        const uint32_t key0 = t0 + r0 + g, key1 = key0 + 8;
+        float alpha[NT][2];
+        uint32_t pb0[NT], pb1[NT];
 #pragma unroll
-        for (int e = 0; e < 4; e++) {
-          float x = s[e] * sc;
-          if (p.soft_cap > 0.0f) x = soft_cap_logit(x, p.soft_cap) * LOG2E;
-          lg[e] = ((e < 2) ? in0 : in1) ? x : -INFINITY;
-        }
-        float mx[2] = {fmaxf(lg[0], lg[2]), fmaxf(lg[1], lg[3])};
+        for (int nt = 0; nt < NT; nt++) {
+          float lg[4];
 #pragma unroll
-        for (int o = 4; o < 32; o <<= 1) {
-          mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xFFFFFFFFu, mx[0], o));
-          mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xFFFFFFFFu, mx[1], o));
-        }
-        float alpha[2], pr[4];
+          for (int e = 0; e < 4; e++) {
+            float x = (CH == 2 ? (s_hi[nt][0][e] + s_hi[nt][CH - 1][e]) + (s_lo[nt][0][e] + s_lo[nt][CH - 1][e])
+                               : s_hi[nt][0][e] + s_lo[nt][0][e]) * sc;
+            if (p.soft_cap > 0.0f) x = soft_cap_logit(x, p.soft_cap) * LOG2E;
+            const uint32_t key = e < 2 ? key0 : key1;
+            lg[e] = (key - c_lo[nt][e & 1] < c_len[nt][e & 1]) ? x : -INFINITY;
+          }
+          float mx[2] = {fmaxf(lg[0], lg[2]), fmaxf(lg[1], lg[3])};
 #pragma unroll
-        for (int hh = 0; hh < 2; hh++) {
-          const float m_new = fmaxf(m_run[hh], mx[hh]);  // finite: at least one key of the slice is valid
-          alpha[hh] = exp2f(m_run[hh] - m_new);           // exp2(-inf) = 0 on the first slice
-          m_run[hh] = m_new;
+          for (int o = 4; o < 32; o <<= 1) {
+            mx[0] = fmaxf(mx[0], __shfl_xor_sync(0xFFFFFFFFu, mx[0], o));
+            mx[1] = fmaxf(mx[1], __shfl_xor_sync(0xFFFFFFFFu, mx[1], o));
+          }
+          float mu[2];
+#pragma unroll
+          for (int hh = 0; hh < 2; hh++) {
+            const float m_new = fmaxf(m_run[nt][hh], mx[hh]);
+            mu[hh] = m_new == -INFINITY ? 0.0f : m_new;   // a column that has seen no key yet
+            alpha[nt][hh] = exp2f(m_run[nt][hh] - mu[hh]);  // exp2(-inf) = 0 on the first keys
+            m_run[nt][hh] = m_new;
+          }
+          const float pr0 = exp2f(lg[0] - mu[0]), pr1 = exp2f(lg[1] - mu[1]), pr2 = exp2f(lg[2] - mu[0]), pr3 = exp2f(lg[3] - mu[1]);
+          l_run[nt][0] = l_run[nt][0] * alpha[nt][0] + pr0 + pr2;
+          l_run[nt][1] = l_run[nt][1] * alpha[nt][1] + pr1 + pr3;
+          // P^T fragments (k = key, n = column) from the S^T accumulator layout by an 8x8 transpose.
+          pb0[nt] = movmatrix_trans(pack_half2(pr0, pr1));
+          pb1[nt] = movmatrix_trans(pack_half2(pr2, pr3));
         }
-        pr[0] = exp2f(lg[0] - m_run[0]);
-        pr[1] = exp2f(lg[1] - m_run[1]);
-        pr[2] = exp2f(lg[2] - m_run[0]);
-        pr[3] = exp2f(lg[3] - m_run[1]);
-        l_run[0] = l_run[0] * alpha[0] + pr[0] + pr[2];
-        l_run[1] = l_run[1] * alpha[1] + pr[1] + pr[3];
-        // P^T fragments (k = key, n = head) from the S^T accumulator layout by an 8x8 transpose.
-        const uint32_t pb0 = movmatrix_trans(pack_half2(pr[0], pr[1]));
-        const uint32_t pb1 = movmatrix_trans(pack_half2(pr[2], pr[3]));
-        // ---- O^T[Dv x 8 heads] = alpha * O^T + V^T . P^T ----
+        // ---- O^T[Dv x 8 columns] = alpha * O^T + V^T . P^T per tile ----
         const uint32_t v_row = r0 + (lane & 7) + 8 * (lane >> 4);
         const uint32_t v_chunk = (lane >> 3) & 1;
 #pragma unroll
         for (int mt = 0; mt < D / 16; mt++) {
-          acc[mt][0] *= alpha[0];
-          acc[mt][1] *= alpha[1];
-          acc[mt][2] *= alpha[0];
-          acc[mt][3] *= alpha[1];
           uint32_t a0, a1, a2, a3;
           ldmatrix_x4_trans(vst + tile_off<D, TILED>(v_row, 2 * mt + v_chunk), a0, a1, a2, a3);
-          mma_f16(acc[mt], a0, a1, a2, a3, pb0, pb1);
+#pragma unroll
+          for (int nt = 0; nt < NT; nt++) {
+            acc[mt][nt][0] *= alpha[nt][0];
+            acc[mt][nt][1] *= alpha[nt][1];
+            acc[mt][nt][2] *= alpha[nt][0];
+            acc[mt][nt][3] *= alpha[nt][1];
+            mma_f16(acc[mt][nt], a0, a1, a2, a3, pb0[nt], pb1[nt]);
+          }
         }
       }
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(bar_empty + 8 * slot);
     }
 
-    // ---------------- fold the four warps (log-sum-exp), inside the drained ring ----------------
+    // ---------------- stage the warps' results in the drained ring; fold them (decode) ----------------
 #pragma unroll
-    for (int o = 4; o < 32; o <<= 1) {
-      l_run[0] += __shfl_xor_sync(0xFFFFFFFFu, l_run[0], o);
-      l_run[1] += __shfl_xor_sync(0xFFFFFFFFu, l_run[1], o);
-    }
+    for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+      for (int o = 4; o < 32; o <<= 1) {
+        l_run[nt][0] += __shfl_xor_sync(0xFFFFFFFFu, l_run[nt][0], o);
+        l_run[nt][1] += __shfl_xor_sync(0xFFFFFFFFu, l_run[nt][1], o);
+      }
     consumer_sync();
-    float* mb = reinterpret_cast<float*>(smem) + (size_t)warp * (8 * D + 16);  // [8 heads][D] then m[8], l[8]
+    constexpr int WS = G::WS, NB = G::STAGING_BUFS;
+    {
+      float* mb = reinterpret_cast<float*>(smem) + (BLOCK ? 0 : (size_t)warp * WS);  // [COLS][D], then max[COLS], weight[COLS]
 #pragma unroll
-    for (int mt = 0; mt < D / 16; mt++) {
-      mb[(2 * j) * D + mt * 16 + g] = acc[mt][0];
-      mb[(2 * j + 1) * D + mt * 16 + g] = acc[mt][1];
-      mb[(2 * j) * D + mt * 16 + g + 8] = acc[mt][2];
-      mb[(2 * j + 1) * D + mt * 16 + g + 8] = acc[mt][3];
-    }
-    if (g == 0) {
-      mb[8 * D + 2 * j] = m_run[0];
-      mb[8 * D + 2 * j + 1] = m_run[1];
-      mb[8 * D + 8 + 2 * j] = l_run[0];
-      mb[8 * D + 8 + 2 * j + 1] = l_run[1];
+      for (int nt = 0; nt < NT; nt++) {
+        const uint32_t c0 = (tile0 + nt) * 8 + 2 * j;
+#pragma unroll
+        for (int mt = 0; mt < D / 16; mt++) {
+          mb[c0 * D + mt * 16 + g] = acc[mt][nt][0];
+          mb[(c0 + 1) * D + mt * 16 + g] = acc[mt][nt][1];
+          mb[c0 * D + mt * 16 + g + 8] = acc[mt][nt][2];
+          mb[(c0 + 1) * D + mt * 16 + g + 8] = acc[mt][nt][3];
+        }
+        if (g == 0) {
+          mb[COLS * D + c0] = m_run[nt][0];
+          mb[COLS * D + c0 + 1] = m_run[nt][1];
+          mb[COLS * D + COLS + c0] = l_run[nt][0];
+          mb[COLS * D + COLS + c0 + 1] = l_run[nt][1];
+        }
+      }
     }
     consumer_sync();
     const float* all = reinterpret_cast<const float*>(smem);
-    constexpr int WS = 8 * D + 16;
     // A partial row is D sums, then (max, sum of weights), padded to a 16-byte multiple so
     // that the merge reads it in float4s.
     constexpr int PP = D + 4;
-    float* part = p.partial + ((uint64_t)unit * p.splits + split) * 8 * PP;
-    float* orow = p.out + (((uint64_t)b * p.L + l) * p.Hq + h0) * D;
+    float* part = p.partial + ((uint64_t)unit * p.splits + split) * COLS * PP;
     const bool direct = p.splits == 1;
-    // Thread t owns the float4 columns t, t + 128, ... of the row's [8 heads][D] outputs: eight
-    // consecutive lanes hold one 32-block of the output row.
-    constexpr int C4 = (8 * D / 4) / (CONSUMER_WARPS * 32);
-    static_assert(C4 >= 1 && C4 * CONSUMER_WARPS * 32 * 4 == 8 * D, "whole float4 columns per thread");
-    const uint32_t out_row = b * p.L + l;
-#pragma unroll
+    // Thread t owns the float4s t, t + 128, ... of the CTA's [COLS][D] outputs: eight consecutive
+    // lanes hold one 32-block of an output row.
+    constexpr int C4 = (COLS * D / 4) / (CONSUMER_WARPS * 32);
+    static_assert(C4 >= 1 && C4 * CONSUMER_WARPS * 32 * 4 == COLS * D, "whole float4 columns per thread");
+#pragma unroll 1
     for (int c = 0; c < C4; c++) {
-      const uint32_t idx4 = tid + c * (CONSUMER_WARPS * 32), h = idx4 / (D / 4), d = 4 * (idx4 % (D / 4));
-      const bool on = h < nh;
+      const uint32_t idx4 = tid + c * (CONSUMER_WARPS * 32), col = idx4 / (D / 4), d4 = idx4 % (D / 4);
+      const uint32_t row = col_row[col];
+      const bool on = row != NO_ROW;
       float M = -INFINITY;
 #pragma unroll
-      for (int w = 0; w < CONSUMER_WARPS; w++) M = fmaxf(M, all[w * WS + 8 * D + h]);
+      for (int w = 0; w < NB; w++) M = fmaxf(M, all[w * WS + COLS * D + col]);
       float4 o = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
       float lsum = 0.0f;
 #pragma unroll
-      for (int w = 0; w < CONSUMER_WARPS; w++) {
-        const float mw = all[w * WS + 8 * D + h];
+      for (int w = 0; w < NB; w++) {
+        const float mw = all[w * WS + COLS * D + col];
         const float f = (mw == -INFINITY) ? 0.0f : exp2f(mw - M);
         const float4 x = *reinterpret_cast<const float4*>(all + w * WS + 4 * idx4);
         o.x += x.x * f; o.y += x.y * f; o.z += x.z * f; o.w += x.w * f;
-        lsum += all[w * WS + 8 * D + 8 + h] * f;
+        lsum += all[w * WS + COLS * D + COLS + col] * f;
       }
       if (direct) {
         float4 r = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         if (lsum > 0.0f && isfinite(lsum)) r = make_float4(o.x / lsum, o.y / lsum, o.z / lsum, o.w / lsum);
-        else if (on && nkeys > 0 && !kr.bad && !*abort_flag) atomicExch(p.fault, FAULT_NONFINITE);
-        if (on) *reinterpret_cast<float4*>(orow + 4 * idx4) = r;
+        else if (on && col_hi[col] > col_lo[col] && !bad && !*abort_flag) atomicExch(p.fault, FAULT_NONFINITE);
+        if (on) *reinterpret_cast<float4*>(p.out + (uint64_t)row * D + 4 * d4) = r;
         if (p.image) {
-          const uint32_t col4 = (h0 * D) / 4 + idx4;
-          if (p.image_dtype == AION_CUDA_DTYPE_Q8_0) quantize_store_block_8lanes<AION_CUDA_DTYPE_Q8_0>(r, col4 & 7, on, p.image, p.image_layout, out_row, col4 >> 3);
-          else quantize_store_block_8lanes<AION_CUDA_DTYPE_Q4_0>(r, col4 & 7, on, p.image, p.image_layout, out_row, col4 >> 3);
+          const uint32_t out_row = on ? row / p.Hq : 0, col4 = on ? (row % p.Hq) * (D / 4) + d4 : 0;
+          if (p.image_dtype == AION_CUDA_DTYPE_Q8_0) quantize_store_block_8lanes<AION_CUDA_DTYPE_Q8_0>(r, d4 & 7, on, p.image, p.image_layout, out_row, col4 >> 3);
+          else quantize_store_block_8lanes<AION_CUDA_DTYPE_Q4_0>(r, d4 & 7, on, p.image, p.image_layout, out_row, col4 >> 3);
         }
       } else if (on) {
-        *reinterpret_cast<float4*>(part + h * PP + d) = o;
-        if (d == 0) *reinterpret_cast<float2*>(part + h * PP + D) = make_float2(M, lsum);
+        *reinterpret_cast<float4*>(part + col * PP + 4 * d4) = o;
+        if (d4 == 0) *reinterpret_cast<float2*>(part + col * PP + D) = make_float2(M, lsum);
       }
     }
     if (!direct) {
-      // The last CTA of this row to arrive merges every split's partial.
+      // The last CTA of this unit to arrive merges every split's partial.
       __threadfence();
       consumer_sync();
       if (tid == 0) {
@@ -479,19 +582,19 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParam
         // fetches every split's (max, sum) pair into shared memory (the ring is drained, its
         // space is free), the factors come from there, and the weighted sums then run over
         // float4 loads issued sixteen at a time per thread.
-        const float* pu = p.partial + (uint64_t)unit * p.splits * 8 * PP;
-        float* fac = reinterpret_cast<float*>(smem);  // [8][splits]: max, then factor
-        float* wsum = fac + 8 * p.splits;             // [8][splits]: sum of weights
-        float* lsums = wsum + 8 * p.splits;           // [8]
-        for (uint32_t idx = tid; idx < 8 * p.splits; idx += CONSUMER_WARPS * 32) {
+        const float* pu = p.partial + (uint64_t)unit * p.splits * COLS * PP;
+        float* fac = reinterpret_cast<float*>(smem);  // [COLS][splits]: max, then factor
+        float* wsum = fac + COLS * p.splits;          // [COLS][splits]: sum of weights
+        float* lsums = wsum + COLS * p.splits;        // [COLS]
+        for (uint32_t idx = tid; idx < COLS * p.splits; idx += CONSUMER_WARPS * 32) {
           const uint32_t h = idx / p.splits, s2 = idx % p.splits;
           float2 ml = make_float2(-INFINITY, 0.0f);
-          if (h < nh) ml = __ldcg(reinterpret_cast<const float2*>(pu + (size_t)(s2 * 8 + h) * PP + D));
+          if (col_row[h] != NO_ROW) ml = __ldcg(reinterpret_cast<const float2*>(pu + (size_t)(s2 * COLS + h) * PP + D));
           fac[idx] = ml.x;
           wsum[idx] = ml.y;
         }
         consumer_sync();
-        for (uint32_t h = warp; h < 8; h += CONSUMER_WARPS) {
+        for (uint32_t h = warp; h < (uint32_t)COLS; h += CONSUMER_WARPS) {
           float M = -INFINITY;
           for (uint32_t s2 = lane; s2 < p.splits; s2 += 32) M = fmaxf(M, fac[h * p.splits + s2]);
 #pragma unroll
@@ -508,52 +611,58 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParam
           if (lane == 0) lsums[h] = lsum;
         }
         consumer_sync();
-        const float* colp[C4];
-        const float* fh[C4];
-        bool live[C4];
-        float4 o[C4];
+        constexpr int CHK = C4 < 4 ? C4 : 4;
+        static_assert(C4 % CHK == 0, "whole chunks");
+#pragma unroll 1
+        for (int cb = 0; cb < C4; cb += CHK) {
+          const float* colp[CHK];
+          const float* fh[CHK];
+          bool live[CHK];
+          float4 o[CHK];
 #pragma unroll
-        for (int c = 0; c < C4; c++) {
-          const uint32_t idx4 = tid + c * (CONSUMER_WARPS * 32), h = idx4 / (D / 4), d4 = idx4 % (D / 4);
-          live[c] = h < nh;
-          colp[c] = pu + (size_t)h * PP + 4 * d4;
-          fh[c] = fac + h * p.splits;
-          o[c] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        }
-        for (uint32_t s2 = 0; s2 < p.splits; s2 += 4) {
-          float4 v[C4][4];
-          float f[C4][4];
+          for (int c = 0; c < CHK; c++) {
+            const uint32_t idx4 = tid + (cb + c) * (CONSUMER_WARPS * 32), col = idx4 / (D / 4), d4 = idx4 % (D / 4);
+            live[c] = col_row[col] != NO_ROW;
+            colp[c] = pu + (size_t)col * PP + 4 * d4;
+            fh[c] = fac + col * p.splits;
+            o[c] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+          }
+          for (uint32_t s2 = 0; s2 < p.splits; s2 += 4) {
+            float4 v[CHK][4];
+            float f[CHK][4];
 #pragma unroll
-          for (int c = 0; c < C4; c++)
+            for (int c = 0; c < CHK; c++)
 #pragma unroll
-            for (int k = 0; k < 4; k++) {
-              const uint32_t ss = s2 + k;
-              const bool on = live[c] && ss < p.splits;
-              v[c][k] = on ? __ldcg(reinterpret_cast<const float4*>(colp[c] + (size_t)ss * 8 * PP)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-              f[c][k] = on ? fh[c][ss] : 0.0f;
+              for (int k = 0; k < 4; k++) {
+                const uint32_t ss = s2 + k;
+                const bool on = live[c] && ss < p.splits;
+                v[c][k] = on ? __ldcg(reinterpret_cast<const float4*>(colp[c] + (size_t)ss * COLS * PP)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                f[c][k] = on ? fh[c][ss] : 0.0f;
+              }
+#pragma unroll
+            for (int c = 0; c < CHK; c++)
+#pragma unroll
+              for (int k = 0; k < 4; k++) {  // splits in order
+                o[c].x += v[c][k].x * f[c][k];
+                o[c].y += v[c][k].y * f[c][k];
+                o[c].z += v[c][k].z * f[c][k];
+                o[c].w += v[c][k].w * f[c][k];
+              }
+          }
+#pragma unroll
+          for (int c = 0; c < CHK; c++) {
+            const uint32_t idx4 = tid + (cb + c) * (CONSUMER_WARPS * 32), col = idx4 / (D / 4), d4 = idx4 % (D / 4);
+            const uint32_t row = col_row[col];
+            const float lsum = lsums[col];
+            float4 r = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (lsum > 0.0f && isfinite(lsum)) r = make_float4(o[c].x / lsum, o[c].y / lsum, o[c].z / lsum, o[c].w / lsum);
+            else if (live[c] && col_hi[col] > col_lo[col] && !bad) atomicExch(p.fault, FAULT_NONFINITE);
+            if (live[c]) *reinterpret_cast<float4*>(p.out + (uint64_t)row * D + 4 * d4) = r;
+            if (p.image) {
+              const uint32_t out_row = live[c] ? row / p.Hq : 0, col4 = live[c] ? (row % p.Hq) * (D / 4) + d4 : 0;
+              if (p.image_dtype == AION_CUDA_DTYPE_Q8_0) quantize_store_block_8lanes<AION_CUDA_DTYPE_Q8_0>(r, d4 & 7, live[c], p.image, p.image_layout, out_row, col4 >> 3);
+              else quantize_store_block_8lanes<AION_CUDA_DTYPE_Q4_0>(r, d4 & 7, live[c], p.image, p.image_layout, out_row, col4 >> 3);
             }
-#pragma unroll
-          for (int c = 0; c < C4; c++)
-#pragma unroll
-            for (int k = 0; k < 4; k++) {  // splits in order
-              o[c].x += v[c][k].x * f[c][k];
-              o[c].y += v[c][k].y * f[c][k];
-              o[c].z += v[c][k].z * f[c][k];
-              o[c].w += v[c][k].w * f[c][k];
-            }
-        }
-#pragma unroll
-        for (int c = 0; c < C4; c++) {
-          const uint32_t idx4 = tid + c * (CONSUMER_WARPS * 32), h = idx4 / (D / 4);
-          const float lsum = lsums[h & 7];
-          float4 r = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-          if (lsum > 0.0f && isfinite(lsum)) r = make_float4(o[c].x / lsum, o[c].y / lsum, o[c].z / lsum, o[c].w / lsum);
-          else if (live[c] && nkeys > 0 && !kr.bad) atomicExch(p.fault, FAULT_NONFINITE);
-          if (live[c]) *reinterpret_cast<float4*>(orow + 4 * idx4) = r;
-          if (p.image) {
-            const uint32_t col4 = (h0 * D) / 4 + idx4;
-            if (p.image_dtype == AION_CUDA_DTYPE_Q8_0) quantize_store_block_8lanes<AION_CUDA_DTYPE_Q8_0>(r, col4 & 7, live[c], p.image, p.image_layout, out_row, col4 >> 3);
-            else quantize_store_block_8lanes<AION_CUDA_DTYPE_Q4_0>(r, col4 & 7, live[c], p.image, p.image_layout, out_row, col4 >> 3);
           }
         }
       }
@@ -644,10 +753,10 @@ __global__ void __launch_bounds__(GEN_WARPS * 32) attn_generic_kernel(const Attn
   }
 }
 
-template <int D, bool QF32, bool TILED>
+template <int D, bool QF32, bool TILED, bool BLOCK, int NT>
 int32_t launch_decode_as(AionCudaDevice* dev, const AttnParams& p, uint32_t units, const CUtensorMap& tk, const CUtensorMap& tv) {
-  using G = DecodeGeom<D>;
-  auto kernel = attn_decode_kernel<D, QF32, TILED>;
+  using G = DecodeGeom<D, QF32, BLOCK, NT>;
+  auto kernel = attn_decode_kernel<D, QF32, TILED, BLOCK, NT>;
   {
     // Once per device and instantiation; several host threads may drive devices at once.
     static std::mutex mu;
@@ -658,6 +767,7 @@ int32_t launch_decode_as(AionCudaDevice* dev, const AttnParams& p, uint32_t unit
       if (dev->ordinal >= 0 && dev->ordinal < 64) configured[dev->ordinal] = true;
     }
   }
+  if (p.splits > (uint32_t)G::MAX_SPLITS) return fail(AION_CUDA_INTERNAL_ERROR, "attention: %u splits exceed the merge buffer", p.splits);
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(units, p.splits);
   cfg.blockDim = dim3(THREADS);
@@ -673,17 +783,20 @@ int32_t launch_decode_as(AionCudaDevice* dev, const AttnParams& p, uint32_t unit
   return AION_CUDA_OK;
 }
 
-template <int D, bool QF32>
+template <int D, bool QF32, bool BLOCK, int NT>
 int32_t launch_decode(AionCudaDevice* dev, const AttnParams& p, uint32_t units) {
   CUtensorMap tk{}, tv{};
-  // K and V as [B*T rows][Hkv*D columns] f16; a rolling cache's rows wrap, so it keeps row copies.
-  if (!p.rolling && (uint64_t)p.B * p.T < (1ull << 31)) {
-    const uint64_t rows = (uint64_t)p.B * p.T, cols = (uint64_t)p.Hkv * D;
+  // K and V as [rows][Hkv*D columns] f16, rows = B*T (or every row of the page pool); a rolling
+  // cache's rows wrap, so it keeps row copies.
+  const uint64_t rows = p.page_tokens ? (uint64_t)p.pool_pages * p.page_tokens : (uint64_t)p.B * p.T;
+  if (!p.rolling && rows < (1ull << 31)) {
+    const uint64_t cols = (uint64_t)p.Hkv * D;
     if (int32_t st = tensor_map_16bit_sw128(p.k, false, rows, cols, cols * 2, 64, KT, &tk)) return st;
     if (int32_t st = tensor_map_16bit_sw128(p.v, false, rows, cols, cols * 2, 64, KT, &tv)) return st;
-    return launch_decode_as<D, QF32, true>(dev, p, units, tk, tv);
+    return launch_decode_as<D, QF32, true, BLOCK, NT>(dev, p, units, tk, tv);
   }
-  return launch_decode_as<D, QF32, false>(dev, p, units, tk, tv);
+  if (p.page_tokens) return fail(AION_CUDA_UNSUPPORTED, "attention: a paged cache needs the tiled path (no rolling, fewer than 2^31 pool rows)");
+  return launch_decode_as<D, QF32, false, BLOCK, NT>(dev, p, units, tk, tv);
 }
 
 }  // namespace
@@ -694,11 +807,23 @@ int32_t attention_launch(AionCudaDevice* dev, const AionCudaAttention* s) {
   if (B > 0x7FFFFFFF || L > 0x7FFFFFFF || Hq > 65535 || Dk > 65535 || Dv > 65535 || T > 0x7FFFFFFF || B * L * Hq > 0x7FFFFFFF)
     return fail(AION_CUDA_UNSUPPORTED, "attention: a dimension is beyond what the kernels index");
   auto esz = [](uint32_t dt) { return dt == AION_CUDA_DTYPE_F32 ? 4u : 2u; };
+  const bool paged = s->page_table.handle != 0;
+  const uint64_t page_tokens = s->page_tokens, pool_pages = s->pool_pages;
+  uint64_t pages_per_request = 0;
+  if (paged) {
+    if (page_tokens == 0 || page_tokens % KT != 0 || page_tokens > (1u << 20))
+      return fail(AION_CUDA_INVALID_ARGUMENT, "attention: page_tokens %llu must be a positive multiple of %d", (unsigned long long)page_tokens, KT);
+    if (pool_pages == 0 || pool_pages * page_tokens > 0x7FFFFFFFull)
+      return fail(AION_CUDA_INVALID_ARGUMENT, "attention: pool of %llu pages", (unsigned long long)pool_pages);
+    if (s->rolling) return fail(AION_CUDA_UNSUPPORTED, "attention: a rolling cache cannot be paged");
+    pages_per_request = (T + page_tokens - 1) / page_tokens;
+  }
+  const uint64_t kv_rows = paged ? pool_pages * page_tokens : B * T;
   const uint8_t *q, *k, *v;
   float* out;
   if (int32_t st = resolve(s->q, B * L * Hq * Dk * esz(s->q_dtype), "attention.q", &q)) return st;
-  if (int32_t st = resolve(s->k, B * T * Hkv * Dk * esz(s->k_dtype), "attention.k", &k)) return st;
-  if (int32_t st = resolve(s->v, B * T * Hkv * Dv * esz(s->v_dtype), "attention.v", &v)) return st;
+  if (int32_t st = resolve(s->k, kv_rows * Hkv * Dk * esz(s->k_dtype), "attention.k", &k)) return st;
+  if (int32_t st = resolve(s->v, kv_rows * Hkv * Dv * esz(s->v_dtype), "attention.v", &v)) return st;
   if (int32_t st = resolve(s->out, B * L * Hq * Dv * sizeof(float), "attention.out", &out)) return st;
   p.q = q;
   p.k = k;
@@ -709,6 +834,12 @@ int32_t attention_launch(AionCudaDevice* dev, const AionCudaAttention* s) {
   }
   if (s->kv_lengths.handle) {
     if (int32_t st = resolve(s->kv_lengths, B * 4, "attention.kv_lengths", &p.lengths)) return st;
+  }
+  if (paged) {
+    if (int32_t st = resolve(s->page_table, B * pages_per_request * 4, "attention.page_table", &p.page_table)) return st;
+    p.page_tokens = (uint32_t)page_tokens;
+    p.pages_per_request = (uint32_t)pages_per_request;
+    p.pool_pages = (uint32_t)pool_pages;
   }
   p.B = (uint32_t)B; p.L = (uint32_t)L; p.Hq = (uint32_t)Hq; p.Hkv = (uint32_t)Hkv;
   p.Dk = (uint32_t)Dk; p.Dv = (uint32_t)Dv; p.T = (uint32_t)T;
@@ -722,7 +853,9 @@ int32_t attention_launch(AionCudaDevice* dev, const AionCudaAttention* s) {
   const bool f16kv = s->k_dtype == AION_CUDA_DTYPE_F16 && s->v_dtype == AION_CUDA_DTYPE_F16;
   const bool aligned = ((reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(out)) & 15) == 0 &&
                        (reinterpret_cast<uintptr_t>(q) & 3) == 0;
-  const bool tensor_path = f16kv && aligned && Dk == Dv && (Dk == 64 || Dk == 128 || Dk == 256) && !(s->flags & 1u);
+  const bool tensor_path = f16kv && aligned && Dk == Dv && (Dk == 64 || Dk == 128 || Dk == 256) && !(s->flags & AION_CUDA_ATTENTION_GENERIC);
+  if (paged && !tensor_path)
+    return fail(AION_CUDA_UNSUPPORTED, "attention: the page table is read by the f16 tensor-core kernel only (Dk = Dv in {64, 128, 256}, aligned operands)");
   if (s->image.handle) {
     if (!tensor_path) return fail(AION_CUDA_UNSUPPORTED, "attention: the output image is written by the f16 tensor-core kernel only (Dk = Dv in {64, 128, 256}, aligned operands)");
     if (s->image_dtype != AION_CUDA_DTYPE_Q8_0 && s->image_dtype != AION_CUDA_DTYPE_Q4_0)
@@ -735,8 +868,24 @@ int32_t attention_launch(AionCudaDevice* dev, const AionCudaAttention* s) {
   if (tensor_path) {
     const uint32_t group = p.Hq / p.Hkv;
     p.head_groups = (group + 7) / 8;
-    const uint64_t units = B * L * Hkv * p.head_groups;
+    p.col_heads = group < 8 ? group : 8;
+    // One query position per CTA (the four warps split the keys) for a single-row step; blocks of
+    // positions (each warp owns some, all walk every key) when a request brings several rows, so that
+    // K and V are streamed once per block instead of once per row.
+    const bool block = L > 1 && !(s->flags & AION_CUDA_ATTENTION_ROW_UNITS);
+    uint32_t nt = 1;
+    if (block) {
+      p.pos_per_tile = 8 / p.col_heads;
+      if (L > (uint64_t)CONSUMER_WARPS * p.pos_per_tile) nt = 2;
+      const uint64_t per_unit = (uint64_t)CONSUMER_WARPS * nt * p.pos_per_tile;
+      p.l_blocks = (uint32_t)((L + per_unit - 1) / per_unit);
+    } else {
+      p.pos_per_tile = 1;
+      p.l_blocks = (uint32_t)L;
+    }
+    const uint64_t units = B * p.l_blocks * Hkv * p.head_groups;
     if (units > 0x7FFFFFFF) return fail(AION_CUDA_UNSUPPORTED, "attention: too many rows");
+    const uint32_t cols = 8 * (block ? CONSUMER_WARPS * nt : 1);
     // Split the context until the grid covers the SMs about twice; a split is at least 64 keys.
     // Upper bound of any row's keys: the window span clipped to the cache (or ring) length.
     uint64_t max_keys = T;
@@ -754,12 +903,14 @@ int32_t attention_launch(AionCudaDevice* dev, const AionCudaAttention* s) {
     uint64_t cap = (uint64_t)std::sqrt(0.2 * (double)max_keys) + 1;
     if (cap > stages_total) cap = stages_total;
     if (cap > 256) cap = 256;
+    if (block && cap > 32) cap = 32;   // a block's partial is `cols` rows: keep the merge short
     if (cap < 1) cap = 1;
     uint64_t splits = 1;
     double best = 1e30;
+    const double stage_cost = block ? (double)(CONSUMER_WARPS * nt) : 1.0;  // a block's warps walk every key of a stage for their own tiles
     for (uint64_t sp = 1; sp <= cap; sp++) {
       const uint64_t waves = (units * sp + sms - 1) / sms;
-      const double per_cta = (double)((stages_total + sp - 1) / sp) + 4.0 + (sp > 1 ? 2.0 + 0.1 * (double)sp : 0.0);
+      const double per_cta = stage_cost * (double)((stages_total + sp - 1) / sp) + 4.0 + (sp > 1 ? 2.0 + 0.1 * (double)sp * (cols / 8) : 0.0);
       const double cost = (double)waves * per_cta;
       if (cost < best * 0.999) {
         best = cost;
@@ -769,18 +920,24 @@ int32_t attention_launch(AionCudaDevice* dev, const AionCudaAttention* s) {
     if (dev->attn_split_override) splits = dev->attn_split_override;
     p.splits = (uint32_t)splits;
     if (splits > 1) {
-      const size_t part_bytes = (size_t)units * splits * 8 * (Dk + 4) * sizeof(float);
+      const size_t part_bytes = (size_t)units * splits * cols * (Dk + 4) * sizeof(float);
       if (int32_t st = dev->reserve_scratch(part_bytes)) return st;
       if (int32_t st = dev->reserve_tickets(units)) return st;
       p.partial = static_cast<float*>(dev->lane_scratch());
       p.tickets = dev->lane_tickets();
     }
     const bool qf32 = s->q_dtype == AION_CUDA_DTYPE_F32;
+    const uint32_t u = (uint32_t)units;
+#define AION_ATTN(DD)                                                                                              \
+  if (!block) return qf32 ? launch_decode<DD, true, false, 1>(dev, p, u) : launch_decode<DD, false, false, 1>(dev, p, u); \
+  if (nt == 1) return qf32 ? launch_decode<DD, true, true, 1>(dev, p, u) : launch_decode<DD, false, true, 1>(dev, p, u);  \
+  return qf32 ? launch_decode<DD, true, true, 2>(dev, p, u) : launch_decode<DD, false, true, 2>(dev, p, u);
     switch (Dk) {
-      case 64: return qf32 ? launch_decode<64, true>(dev, p, (uint32_t)units) : launch_decode<64, false>(dev, p, (uint32_t)units);
-      case 128: return qf32 ? launch_decode<128, true>(dev, p, (uint32_t)units) : launch_decode<128, false>(dev, p, (uint32_t)units);
-      default: return qf32 ? launch_decode<256, true>(dev, p, (uint32_t)units) : launch_decode<256, false>(dev, p, (uint32_t)units);
+      case 64: AION_ATTN(64)
+      case 128: AION_ATTN(128)
+      default: AION_ATTN(256)
     }
+#undef AION_ATTN
   }
   if (Dv > 32 * GEN_MAX_DV_PER_LANE) return fail(AION_CUDA_UNSUPPORTED, "attention: Dv = %llu (any-shape kernel takes <= 1024)", (unsigned long long)Dv);
   const size_t smem = (Dk + GEN_WARPS * (Dv + 2)) * sizeof(float);

@@ -203,6 +203,7 @@ int32_t gemv_mma_static_scratch(AionCudaDevice* dev, const MatMulArgs& g);
 // Quantizes f32 rows into an activation image (act_image.cuh) for weights of `dtype`.
 int32_t act_image_from_f32(AionCudaDevice* dev, uint32_t dtype, const float* a, uint64_t m, uint64_t k, uint64_t lda, uint8_t* image);
 // The bf16 kind of image (what the tensor-core GEMM reads), written by that kernel's own pre-pass.
+int32_t nt_blocks_to_kmajor(AionCudaDevice* dev, uint32_t order, const uint8_t* src, uint8_t* dst, uint64_t n, uint64_t kblocks);
 int32_t act_image_bf16_from_f32(AionCudaDevice* dev, uint32_t dtype, const float* a, uint64_t m, uint64_t k, uint64_t lda, uint8_t* image);
 // What the prefill GEMM would do with this shape: rows per tile (128 or 256), K splits, CTAs.
 struct GemmPlan {

@@ -664,6 +664,23 @@ int32_t launch_gemm(AionCudaDevice* dev, const MatMulArgs& g, const __nv_bfloat1
 
 }  // namespace
 
+// q8_0 [n][k/32] blocks in `order` -> K-major [k/32][n] blocks (the layout `MatMul` reads).
+int32_t nt_blocks_to_kmajor(AionCudaDevice* dev, uint32_t order, const uint8_t* src, uint8_t* dst, uint64_t n, uint64_t kblocks) {
+  int group = 1, chunk = 4;
+  if (!block_order_info(order, &group, &chunk)) return AION_CUDA_INVALID_ARGUMENT;
+  if (n == 0 || kblocks == 0) return AION_CUDA_OK;
+  if (order == AION_CUDA_ORDER_ROW_MAJOR && ceil_div(kblocks, (uint64_t)RT_KB) <= 65535) {
+    const dim3 grid((unsigned)ceil_div(n, (uint64_t)RT_ROWS), (unsigned)ceil_div(kblocks, (uint64_t)RT_KB));
+    AION_CUDA_TRY(launch_pdl_main(nt_rowmajor_to_kmajor_kernel, grid, dim3(256), 0, dev->stream, reinterpret_cast<const uint16_t*>(src),
+                                  reinterpret_cast<uint16_t*>(dst), n, kblocks));
+  } else {
+    const uint64_t total = n * kblocks;
+    const unsigned blocks = (unsigned)std::min<uint64_t>(ceil_div(total, (uint64_t)256), (uint64_t)dev->sm_count * 16);
+    AION_CUDA_TRY(launch_pdl_main(nt_to_kmajor_kernel, dim3(blocks), dim3(256), 0, dev->stream, src, dst, n, kblocks, group, chunk));
+  }
+  return AION_CUDA_OK;
+}
+
 // Whether this kernel reads the step's operands, and how it would tile them.
 static bool plan_gemm(const AionCudaDevice* dev, const MatMulArgs& g, GemmPlan* out) {
   if (g.dtype != AION_CUDA_DTYPE_Q4_0 && g.dtype != AION_CUDA_DTYPE_Q8_0) return false;
@@ -716,9 +733,7 @@ int32_t gemm_tcgen05(AionCudaDevice* dev, const MatMulArgs& g_in) {
   // `MatMulNT`: the same kernel after a block permutation of the weights into lane scratch
   // (the reference's weight-layout pass does the equivalent once per model).
   size_t relaid_bytes = 0;
-  int nt_group = 1, nt_chunk = 4;
   if (g.nt) {
-    block_order_info(g.order, &nt_group, &nt_chunk);
     relaid_bytes = ((size_t)g.n * (g.k / QK) * Q8_BYTES + 1023) & ~size_t(1023);
     g.ldb = g.n;
   }
@@ -728,15 +743,7 @@ int32_t gemm_tcgen05(AionCudaDevice* dev, const MatMulArgs& g_in) {
   if (int32_t st = dev->reserve_scratch(relaid_bytes + a_bytes + part_bytes)) return st;
   uint8_t* scratch = static_cast<uint8_t*>(dev->lane_scratch());
   if (g.nt) {
-    const uint64_t kblocks = g.k / QK, total = g.n * kblocks;
-    if (g.order == AION_CUDA_ORDER_ROW_MAJOR && ceil_div(kblocks, (uint64_t)RT_KB) <= 65535) {
-      const dim3 grid((unsigned)ceil_div(g.n, (uint64_t)RT_ROWS), (unsigned)ceil_div(kblocks, (uint64_t)RT_KB));
-      AION_CUDA_TRY(launch_pdl_main(nt_rowmajor_to_kmajor_kernel, grid, dim3(256), 0, dev->stream, reinterpret_cast<const uint16_t*>(g.b),
-                               reinterpret_cast<uint16_t*>(scratch), g.n, kblocks));
-    } else {
-      const unsigned blocks = (unsigned)std::min<uint64_t>(ceil_div(total, (uint64_t)256), (uint64_t)dev->sm_count * 16);
-      AION_CUDA_TRY(launch_pdl_main(nt_to_kmajor_kernel, dim3(blocks), dim3(256), 0, dev->stream, g.b, scratch, g.n, kblocks, nt_group, nt_chunk));
-    }
+    if (int32_t st = nt_blocks_to_kmajor(dev, g.order, g.b, scratch, g.n, g.k / QK)) return st;
     g.b = scratch;
     g.nt = false;
   }

@@ -227,4 +227,25 @@ int32_t aion_cuda_relayout_q8(AionCudaDevice* dev, uint32_t order, uint32_t inve
   return AION_CUDA_OK;
 }
 
+
+int32_t aion_cuda_derive_kmajor_q8(AionCudaDevice* dev, uint32_t order, uint64_t n, uint64_t k, const AionCudaOperand* src,
+                                   const AionCudaOperand* dst) {
+  if (!dev || !src || !dst) return fail(AION_CUDA_INVALID_ARGUMENT, "derive_kmajor: null argument");
+  int group, chunk;
+  if (!block_order_info(order, &group, &chunk)) return fail(AION_CUDA_INVALID_ARGUMENT, "derive_kmajor: unknown block order %u", order);
+  if (k % QK != 0 || n % group != 0)
+    return fail(AION_CUDA_INVALID_ARGUMENT, "derive_kmajor: [%llu, %llu] does not tile into groups of %d rows of 32-blocks",
+                (unsigned long long)n, (unsigned long long)k, group);
+  const uint64_t bytes = n * (k / QK) * Q8_BYTES;
+  if (bytes == 0) return AION_CUDA_OK;
+  const uint8_t* s;
+  uint8_t* d;
+  if (int32_t st = resolve(*src, bytes, "derive_kmajor.src", &s)) return st;
+  if (int32_t st = resolve(*dst, bytes, "derive_kmajor.dst", &d)) return st;
+  if (s == d) return fail(AION_CUDA_INVALID_ARGUMENT, "derive_kmajor: src and dst alias");
+  if (((uintptr_t)s | (uintptr_t)d) & 1) return fail(AION_CUDA_INVALID_ARGUMENT, "derive_kmajor: blocks must be 2-byte aligned");
+  if (int32_t st = dev->make_current()) return st;
+  return aion::nt_blocks_to_kmajor(dev, order, s, d, n, k / QK);
+}
+
 }  // extern "C"

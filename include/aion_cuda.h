@@ -294,10 +294,15 @@ AION_CUDA_API int32_t aion_cuda_matmul_nt(AionCudaDevice* dev, const AionCudaMat
  *   window {left, right, chunk} (aion src/aion/graph/graph.zig:130-167), soft cap
  *   (0 = off), rolling: K/V are a ring of T rows addressed t % T and only the last T
  *   logical keys are visible (aion src/aion/backend/cpu/exec/attention.zig:1072-1075).
+ * With l_q > 1 (prefill, or several new rows per request) the f16 kernel works on blocks of up to
+ * 32 positions that share one pass over K / V, as the reference's block kernel does
+ * (aion src/aion/backend/cpu/exec/attention.zig:546-963).
  * Empty key range writes zeros. A negative position / length, or a length beyond T on
  * a non-rolling cache, is detected on the device and reported by the next
  * aion_cuda_sync / aion_cuda_d2h as INVALID_ARGUMENT.
  * --------------------------------------------------------------------------------- */
+#define AION_CUDA_ATTENTION_GENERIC 1u   /* flags: take the any-shape f32 kernel */
+#define AION_CUDA_ATTENTION_ROW_UNITS 2u /* flags: one CTA per query row even when l_q > 1 (measurement) */
 typedef struct AionCudaAttention {
   AionCudaOperand out, q, k, v;
   AionCudaOperand query_positions; /* handle 0 = absent */
@@ -314,7 +319,14 @@ typedef struct AionCudaAttention {
    * by the tensor-core decode kernel; other shapes return UNSUPPORTED when it is asked for. */
   AionCudaOperand image;
   uint32_t image_dtype;
-  uint32_t reserved;
+  /* Paged K / V (handle 0 = absent: K / V are the contiguous [B, T, ...] tensors above). With a
+   * page table, k and v are pools [pool_pages, page_tokens, Hkv, D] f16 and key t of request b is
+   * row t % page_tokens of page page_table[b][t / page_tokens]; page_table is i32
+   * [B, ceil(t_cap / page_tokens)], page_tokens a multiple of 64. Entries past a request's
+   * kv_length are not read. Tensor-core kernel only; not with `rolling`. */
+  uint32_t page_tokens;
+  AionCudaOperand page_table;
+  uint64_t pool_pages;
 } AionCudaAttention;
 
 AION_CUDA_API int32_t aion_cuda_attention(AionCudaDevice* dev, const AionCudaAttention* step);
@@ -476,6 +488,15 @@ AION_CUDA_API int32_t aion_cuda_dequantize(AionCudaDevice* dev, uint32_t dtype, 
  * which creates the derived tensor directly on the device (:270-275). */
 AION_CUDA_API int32_t aion_cuda_relayout_q8(AionCudaDevice* dev, uint32_t order, uint32_t inverse, uint64_t n,
                                             uint64_t k, const AionCudaOperand* src, const AionCudaOperand* dst);
+/* The derived weight of this backend: a q8_0 [n,k] tensor in `order` re-laid as K-major
+ * [k/32][n] blocks, the layout `aion_cuda_matmul` streams. Both layouts quantize along K, so
+ * this is a permutation of 34-byte blocks and C = A . B^T of the `MatMulNT` step equals
+ * `MatMul` over the derived tensor bit for bit. A binder calls it once per weight from its
+ * weight-layout pass (aion src/aion/graph/opt/weight_layout.zig:243-314 memoises the derived
+ * tensor per model) and then issues the step as `aion_cuda_matmul`; `aion_cuda_matmul_nt`
+ * stays available for weights that were not derived. */
+AION_CUDA_API int32_t aion_cuda_derive_kmajor_q8(AionCudaDevice* dev, uint32_t order, uint64_t n, uint64_t k,
+                                                 const AionCudaOperand* src, const AionCudaOperand* dst);
 
 #ifdef __cplusplus
 }

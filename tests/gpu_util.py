@@ -127,11 +127,17 @@ NP_DT = {np.dtype(np.float32): capi.DTYPE_F32, np.dtype(np.float16): capi.DTYPE_
 
 
 def run_attention(backend: CudaBackend, q, k, v, *, scale, positions=None, kv_lengths=None, left=capi.WINDOW_UNBOUNDED,
-                  right=capi.WINDOW_UNBOUNDED, chunk=0, soft_cap=0.0, rolling=False, sync=True):
+                  right=capi.WINDOW_UNBOUNDED, chunk=0, soft_cap=0.0, rolling=False, sync=True, flags=0, page_table=None):
+    """page_table (i32 [B, pages per request]): k and v are page pools [pages, page_tokens, Hkv, D]."""
     q, k, v = np.ascontiguousarray(q), np.ascontiguousarray(k), np.ascontiguousarray(v)
     B, L, Hq, Dk = q.shape
     _, T, Hkv, _ = k.shape
     Dv = v.shape[3]
+    table_op, page_tokens, pool_pages = capi.Operand(0, 0, 0), 0, 0
+    if page_table is not None:
+        page_table = np.ascontiguousarray(page_table, dtype=np.int32)
+        pool_pages, page_tokens = k.shape[0], k.shape[1]
+        T = page_table.shape[1] * page_tokens
     out_n = B * L * Hq * Dv
     tail = np.full(64, CANARY, dtype=np.float32)
     bufs = [DevBuf(backend, q), DevBuf(backend, k), DevBuf(backend, v),
@@ -144,12 +150,16 @@ def run_attention(backend: CudaBackend, q, k, v, *, scale, positions=None, kv_le
     if kv_lengths is not None:
         bufs.append(DevBuf(backend, np.ascontiguousarray(kv_lengths, dtype=np.int32)))
         len_op = bufs[-1].operand()
+    if page_table is not None:
+        bufs.append(DevBuf(backend, page_table))
+        table_op = bufs[-1].operand()
     try:
         rec = capi.Attention(out=bufs[3].operand(0, out_n * 4), q=bufs[0].operand(), k=bufs[1].operand(), v=bufs[2].operand(),
+                             page_table=table_op, page_tokens=page_tokens, pool_pages=pool_pages,
                              query_positions=pos_op, kv_lengths=len_op, q_dtype=NP_DT[q.dtype], k_dtype=NP_DT[k.dtype],
                              v_dtype=NP_DT[v.dtype], rolling=int(rolling), batch=B, l_q=L, h_q=Hq, h_kv=Hkv, d_k=Dk, d_v=Dv,
                              t_cap=T, scale=scale, soft_cap=soft_cap, window_left=left, window_right=right,
-                             window_chunk=chunk, flags=0)
+                             window_chunk=chunk, flags=flags)
         _raise(backend._lib.aion_cuda_attention(backend.handle, C.byref(rec)))
         out = bufs[3].read(np.float32)  # d2h waits and reports device-side input faults
         assert np.array_equal(out[out_n:], tail), "kernel wrote past the end of out"

@@ -79,6 +79,108 @@ def test_head_layouts_and_q_dtypes(backend, D, qdt, Hq, Hkv):
     assert rd.rel_l2(got, oracle.attention(q, k, v, **kw)) < TOL
 
 
+# ---- several query rows per request: blocks of positions share one pass over K / V ----------
+@pytest.mark.parametrize("Hq,Hkv,D", [(8, 4, 256), (8, 1, 256), (4, 4, 128), (6, 2, 64), (12, 1, 128), (2, 1, 64)])
+@pytest.mark.parametrize("qdt", [np.float16, np.float32])
+def test_prefill_blocks_causal(backend, Hq, Hkv, D, qdt):
+    """A whole prompt per request: row l sees keys 0..l. Lengths that leave ragged blocks, with the
+    per-row kernel of the same library as a second witness (same arithmetic, other tiling)."""
+    B, L = 2, 150
+    q, k, v = _qkv(B, L, Hq, Hkv, L, D, D, qdt, np.float16, seed=Hq * D)
+    kw = dict(scale=float(1 / np.sqrt(D)), right=0)
+    got = run_attention(backend, q, k, v, **kw)
+    want = oracle.attention(q, k, v, **kw)
+    assert rd.rel_l2(got, want) < TOL
+    rows = run_attention(backend, q, k, v, flags=capi.ATTENTION_ROW_UNITS, **kw)
+    assert rd.rel_l2(got, rows) < 5e-4   # f16 rounding of the weights against a different running maximum
+    for l in (0, 1, 63, 64, 149):   # every row on its own, the short ones too
+        assert rd.rel_l2(got[:, l], want[:, l]) < TOL
+
+
+@pytest.mark.parametrize("window", [dict(left=40, right=0), dict(left=64, right=0, chunk=32), dict(left=5, right=2), dict(right=0)])
+@pytest.mark.parametrize("soft_cap", [0.0, 4.0])
+def test_prefill_blocks_on_a_cache_with_windows(backend, window, soft_cap):
+    """A chunk of new rows appended to a cache that already holds a prefix: explicit positions, ragged
+    lengths per request, sliding and chunked windows whose key ranges differ inside one block."""
+    B, L, T, Hq, Hkv, D = 3, 70, 600, 8, 2, 128
+    q, k, v = _qkv(B, L, Hq, Hkv, T, D, D, np.float32, np.float16, seed=31)
+    q *= 2.0
+    starts = np.array([0, 311, 530], dtype=np.int32)
+    pos = (starts[:, None] + np.arange(L, dtype=np.int32)[None, :]).astype(np.int32)
+    lens = (starts + L).astype(np.int32)
+    kw = dict(scale=0.11, positions=pos, kv_lengths=lens, soft_cap=soft_cap, **window)
+    got = run_attention(backend, q, k, v, **kw)
+    assert rd.rel_l2(got, oracle.attention(q, k, v, **kw)) < TOL
+
+
+def test_prefill_block_with_split_context(backend):
+    """Few rows against a long cache: the block's context is split over CTAs and merged by the last one."""
+    B, L, T, Hq, Hkv, D = 1, 9, 6000, 8, 4, 256
+    q, k, v = _qkv(B, L, Hq, Hkv, T, D, D, np.float32, np.float16, seed=77)
+    pos = (T - L + np.arange(L, dtype=np.int32)).reshape(1, L)
+    kw = dict(scale=1 / 16.0, positions=pos, kv_lengths=np.array([T], dtype=np.int32), right=0)
+    want = oracle.attention(q, k, v, **kw)
+    for _ in range(2):
+        assert rd.rel_l2(run_attention(backend, q, k, v, **kw), want) < TOL
+
+
+def test_prefill_rows_with_no_keys_write_zeros(backend):
+    B, L, T, D = 1, 20, 64, 64
+    q, k, v = _qkv(B, L, 4, 2, T, D, D, np.float16, np.float16, seed=3)
+    pos = np.arange(L, dtype=np.int32).reshape(1, L)
+    kw = dict(scale=0.2, positions=pos, kv_lengths=np.array([7], dtype=np.int32), left=2, right=0)  # rows >= 10 see nothing
+    got = run_attention(backend, q, k, v, **kw)
+    assert rd.rel_l2(got, oracle.attention(q, k, v, **kw)) < TOL
+    assert not got[0, 10:].any() and got[0, :9].any()
+
+
+# ---- paged K / V -----------------------------------------------------------------------
+def _paged(k, v, page_tokens, seed):
+    """Scatter contiguous [B, T, H, D] caches over a shuffled pool of pages; returns pools and the table."""
+    B, T, H, D = k.shape
+    per = (T + page_tokens - 1) // page_tokens
+    rng = np.random.default_rng(seed)
+    pool = B * per + 3
+    ids = rng.permutation(pool)[: B * per].reshape(B, per).astype(np.int32)
+    kp = rng.standard_normal((pool, page_tokens, H, D)).astype(k.dtype)   # unused pages hold other data
+    vp = rng.standard_normal((pool, page_tokens, H, D)).astype(v.dtype)
+    for b in range(B):
+        for i in range(per):
+            n = min(page_tokens, T - i * page_tokens)
+            kp[ids[b, i], :n] = k[b, i * page_tokens: i * page_tokens + n]
+            vp[ids[b, i], :n] = v[b, i * page_tokens: i * page_tokens + n]
+    return kp, vp, ids
+
+
+@pytest.mark.parametrize("page_tokens", [64, 256])
+@pytest.mark.parametrize("B,L,T,window", [(5, 1, 1000, dict(right=0)), (2, 1, 4500, dict(left=700, right=0)),
+                                           (2, 40, 500, dict(right=0)), (64, 1, 300, dict(right=0))])
+def test_paged_cache_equals_contiguous(backend, page_tokens, B, L, T, window):
+    Hq, Hkv, D = 8, 2, 128
+    q, k, v = _qkv(B, L, Hq, Hkv, T, D, D, np.float16, np.float16, seed=T + page_tokens)
+    lens = np.random.default_rng(T).integers(L, T + 1, B).astype(np.int32)
+    pos = (lens[:, None] - L + np.arange(L, dtype=np.int32)[None, :]).astype(np.int32)
+    kw = dict(scale=0.09, positions=pos, kv_lengths=lens, **window)
+    kp, vp, table = _paged(k, v, page_tokens, seed=B)
+    got = run_attention(backend, q, kp, vp, page_table=table, **kw)
+    assert rd.rel_l2(got, oracle.attention(q, k, v, **kw)) < TOL
+    assert rd.rel_l2(got, run_attention(backend, q, k, v, **kw)) < 5e-4   # slices start on stage multiples with a table
+
+
+def test_paged_cache_argument_errors(backend):
+    q, k, v = _qkv(1, 1, 8, 1, 128, 64, 64, np.float16, np.float16)
+    kp, vp, table = _paged(k, v, 64, seed=0)
+    with pytest.raises(BackendError) as e:   # pages that a stage would straddle
+        run_attention(backend, q, kp.reshape(-1, 32, 1, 64), vp.reshape(-1, 32, 1, 64), page_table=np.zeros((1, 4), np.int32), scale=1.0)
+    assert e.value.name == "InvalidArgument"
+    with pytest.raises(BackendError) as e:
+        run_attention(backend, q, kp, vp, page_table=table, scale=1.0, rolling=True)
+    assert e.value.name == "Unsupported"
+    with pytest.raises(BackendError) as e:   # the f32 any-shape kernel does not read tables
+        run_attention(backend, q, kp.astype(np.float32), vp.astype(np.float32), page_table=table, scale=1.0)
+    assert e.value.name == "Unsupported"
+
+
 @pytest.mark.parametrize("length", [0, 1, 15, 16, 17, 63, 64, 65, 129, 1000])
 def test_ragged_lengths(backend, length):
     B, T, D = 3, 1000, 128

@@ -6,6 +6,7 @@ import oracle
 from aion_b200 import backend as ab
 from aion_b200 import capi
 from tests import refdata as rd
+from tests.gpu_util import run_matmul, run_matmul_nt
 
 pytestmark = pytest.mark.gpu
 
@@ -56,6 +57,23 @@ def test_relayout_matches_oracle_and_inverts(backend, order):
     got = ab.relayout_q8(backend, order, n, k, rows)
     assert np.array_equal(got, oracle.relayout_q8(order, n, k, rows))
     assert np.array_equal(ab.relayout_q8(backend, order, n, k, got, inverse=True), rows)
+
+
+@pytest.mark.parametrize("order", range(0, 6))
+@pytest.mark.parametrize("n,k", [(96, 256), (160, 2080)])
+def test_derived_kmajor_weight_is_the_block_transpose(backend, order, n, k):
+    """Any stored order -> the K-major layout `MatMul` reads: the same 34-byte blocks, [k/32][n]; both
+    steps then give the reference's int8 arithmetic over the same blocks."""
+    rows = oracle.quantize(oracle.Q8_0, rd.synth_weights(n, k), 1)
+    stored = rows if order == 0 else oracle.relayout_q8(order, n, k, rows)
+    got = ab.derive_kmajor_q8(backend, order, n, k, stored)
+    want = rows.reshape(n, k // 32, 34).transpose(1, 0, 2)
+    assert np.array_equal(got.reshape(k // 32, n, 34), want)
+    a = rd.synth_acts(3, k)
+    c_nt = run_matmul_nt(backend, a, stored, 3, n, k, order=order)
+    c_km = run_matmul(backend, capi.DTYPE_Q8_0, a, got, 3, n, k)
+    want_c = rd.int8_reference_f64(a, rows, 3, n, k, nt=True)
+    assert rd.rel_l2(c_km, want_c) < 2e-5 and rd.rel_l2(c_nt, want_c) < 2e-5
 
 
 def test_quantize_rejects_bad_arguments(backend):

@@ -412,6 +412,7 @@ class StepSequenceAppend:
     cache: int
     new_kv: int
     end_index: int
+    page_table: Optional[int] = None   # paged cache: `cache` is the pool [pages, page_tokens, H, D]
 
 
 @dataclasses.dataclass
@@ -490,7 +491,7 @@ class CudaSession:
         if isinstance(step, StepCast):
             return {step.x}, {step.out}
         if isinstance(step, StepSequenceAppend):
-            return {step.new_kv, step.end_index, step.cache}, {step.cache}
+            return {step.new_kv, step.end_index, step.cache} | img(step.page_table), {step.cache}
         if isinstance(step, StepGatherRows):
             return {step.table, step.indices}, {step.out}
         if isinstance(step, StepArgMax):
@@ -777,15 +778,25 @@ class CudaSession:
         # src/aion/backend/cpu/exec/sequence_append.zig:25-37
         if cm.rank != 4 or nm.rank != 4 or im.rank != 1 or cm.dtype != nm.dtype:
             raise BackendError(capi.INVALID_ARGUMENT, "sequence_append: ranks / dtypes")
-        if cm.shape[0] != nm.shape[0] or cm.shape[2] != nm.shape[2] or cm.shape[3] != nm.shape[3] or im.shape[0] != cm.shape[0]:
+        paged = s.page_table is not None
+        if (not paged and cm.shape[0] != nm.shape[0]) or cm.shape[2] != nm.shape[2] or cm.shape[3] != nm.shape[3] or im.shape[0] != nm.shape[0]:
             raise BackendError(capi.INVALID_ARGUMENT, "sequence_append: shapes do not agree")
         policy = st.sequence_cache_policy_info(s.cache)
         if policy == "growable":
             raise BackendError(capi.UNSUPPORTED, "sequence_append: growable caches are settled by the storage layer, not here")
         B, T, H, D = cm.shape
+        table, page_tokens, pool_pages = capi.Operand(0, 0, 0), 0, 0
+        if paged:
+            tm = self._need(s.page_table, capi.DTYPE_I32, "sequence_append.page_table")
+            if tm.rank != 2 or tm.shape[0] != nm.shape[0]:
+                raise BackendError(capi.INVALID_ARGUMENT, "sequence_append: page_table must be i32 [B, pages per request]")
+            pool_pages, page_tokens = cm.shape[0], cm.shape[1]
+            B, T = nm.shape[0], tm.shape[1] * page_tokens
+            table = st.acquire_const(s.page_table).operand()
         rec = capi.SequenceAppend(cache=st.acquire_mut(s.cache).operand(), new_kv=st.acquire_const(s.new_kv).operand(),
                                   end_index=st.acquire_const(s.end_index).operand(), batch=B, t_cap=T, heads=H, head_dim=D,
-                                  new_len=nm.shape[1], dtype=cm.dtype, rolling=1 if policy == "rolling" else 0)
+                                  new_len=nm.shape[1], dtype=cm.dtype, rolling=1 if policy == "rolling" else 0,
+                                  page_table=table, page_tokens=page_tokens, pool_pages=pool_pages)
         _check(self._lib.aion_cuda_sequence_append(self.backend._h, C.byref(rec)))
 
     def _gather_rows(self, s: StepGatherRows) -> None:

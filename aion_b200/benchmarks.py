@@ -329,6 +329,47 @@ def attention_leg(torch, backend: CudaBackend, local_rank: int, batch: int, t_ct
             "algorithmic_bytes": alg, "distinct_cache_sets": copies}
 
 
+def prefill_attention_leg(torch, backend: CudaBackend, local_rank: int, batch: int, rows: int, iters: int = 10, heads: int = 8,
+                          kv_heads: int = 4, d: int = 256, flags: int = 0, peak_tflops: float = 1622.7) -> dict:
+    """Causal attention of a whole prompt (l_q = rows, keys 0..l per row), TFLOP/s of the two contractions
+    over the visible keys only. flags: capi.ATTENTION_* (ROW_UNITS times the one-CTA-per-row tiling)."""
+    lib, dev, mem = backend._lib, backend.handle, backend.device_memory
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(21)
+    kv_bytes = batch * rows * kv_heads * d * 2
+    q_bytes = batch * rows * heads * d * 2
+    out_bytes = batch * rows * heads * d * 4
+    hk, hv, hq, ho = mem.alloc(kv_bytes, 256), mem.alloc(kv_bytes, 256), mem.alloc(q_bytes, 256), mem.alloc(out_bytes, 256)
+    for h, nb in ((hk, kv_bytes), (hv, kv_bytes), (hq, q_bytes)):
+        torch.as_tensor(_DevArray(h, nb, "<f2", 2), device="cuda").normal_(0.0, 1.0, generator=gen)
+    torch.cuda.synchronize()
+    none = capi.Operand(0, 0, 0)
+    rec = capi.Attention(out=capi.Operand(ho, 0, out_bytes), q=capi.Operand(hq, 0, q_bytes), k=capi.Operand(hk, 0, kv_bytes),
+                         v=capi.Operand(hv, 0, kv_bytes), query_positions=none, kv_lengths=none, q_dtype=capi.DTYPE_F16,
+                         k_dtype=capi.DTYPE_F16, v_dtype=capi.DTYPE_F16, rolling=0, batch=batch, l_q=rows, h_q=heads, h_kv=kv_heads,
+                         d_k=d, d_v=d, t_cap=rows, scale=1.0 / float(np.sqrt(d)), soft_cap=0.0, window_left=capi.WINDOW_UNBOUNDED,
+                         window_right=0, window_chunk=0, flags=flags)
+    for _ in range(3):
+        _chk(lib.aion_cuda_attention(dev, C.byref(rec)))
+    backend.sync()
+    stream, ev0, ev1 = _events(torch, backend, local_rank)
+    ev0.record(stream)
+    for _ in range(iters):
+        _chk(lib.aion_cuda_attention(dev, C.byref(rec)))
+    ev1.record(stream)
+    backend.sync()
+    torch.cuda.synchronize()
+    ms = ev0.elapsed_time(ev1) / iters
+    for h in (hk, hv, hq, ho):
+        mem.free(h)
+    flops = 4.0 * batch * heads * d * rows * (rows + 1) / 2
+    tf = flops / (ms * 1e-3) / 1e12
+    return {"batch": batch, "rows": rows, "heads": heads, "kv_heads": kv_heads, "d": d, "ms": round(ms, 4), "tflops": round(tf, 1),
+            "frac_of_measured_bf16_peak": round(tf / peak_tflops, 4),
+            "tiling": "one CTA per row" if flags & capi.ATTENTION_ROW_UNITS else "blocks of positions",
+            "kv_mb_streamed_once": round(2 * kv_bytes / 1e6, 1)}
+
+
 def colsplit_leg(torch, dist, backend: CudaBackend, rank: int, world: int, local_rank: int, m: int, iters: int = 50,
                  n: int = 28672, k: int = 8192) -> dict:
     """The one large q4 layer column-split over the ranks: each rank computes y[:, n0:n1] straight

@@ -69,6 +69,7 @@ class MatMulNT(C.Structure):
 
 ATTENTION_GENERIC = 1
 ATTENTION_ROW_UNITS = 2
+ATTENTION_BLOCKS = 4
 
 
 class Attention(C.Structure):
@@ -129,7 +130,8 @@ class Cast(C.Structure):
 class SequenceAppend(C.Structure):
     _fields_ = [("cache", Operand), ("new_kv", Operand), ("end_index", Operand),
                 ("batch", C.c_uint64), ("t_cap", C.c_uint64), ("heads", C.c_uint64), ("head_dim", C.c_uint64),
-                ("new_len", C.c_uint64), ("dtype", C.c_uint32), ("rolling", C.c_uint32)]
+                ("new_len", C.c_uint64), ("dtype", C.c_uint32), ("rolling", C.c_uint32),
+                ("page_table", Operand), ("page_tokens", C.c_uint64), ("pool_pages", C.c_uint64)]
 
 
 class GatherRows(C.Structure):

@@ -209,7 +209,8 @@ __global__ void cast_f16_f32_kernel(float* __restrict__ out, const __half* __res
 // ---- SequenceAppend: one block per (request, new step), 2-byte units ---------------------
 __global__ void sequence_append_kernel(uint16_t* __restrict__ cache, const uint16_t* __restrict__ new_kv,
                                        const int32_t* __restrict__ end_index, uint64_t t_cap, uint64_t row_units,
-                                       uint64_t new_len, int rolling, int* fault) {
+                                       uint64_t new_len, int rolling, int* fault, const int32_t* __restrict__ page_table,
+                                       uint64_t page_tokens, uint64_t pages_per_request, uint64_t pool_pages) {
   ptx::pdl_launch_dependents();
   ptx::pdl_wait();
   const uint64_t b = blockIdx.x / new_len, t = blockIdx.x % new_len;
@@ -223,7 +224,17 @@ __global__ void sequence_append_kernel(uint16_t* __restrict__ cache, const uint1
   const uint64_t logical = (uint64_t)e + t;
   const uint64_t dst = rolling ? logical % t_cap : logical;
   const uint16_t* src = new_kv + (b * new_len + t) * row_units;
-  uint16_t* dp = cache + (b * t_cap + dst) * row_units;
+  uint64_t cache_row = b * t_cap + dst;
+  if (page_table) {
+    // Paged cache: row dst of request b lives in the page its table names.
+    const int32_t page = page_table[b * pages_per_request + dst / page_tokens];
+    if (page < 0 || (uint64_t)page >= pool_pages) {
+      if (threadIdx.x == 0) atomicCAS(fault, FAULT_NONE, FAULT_INVALID_ARGUMENT);
+      return;
+    }
+    cache_row = (uint64_t)page * page_tokens + dst % page_tokens;
+  }
+  uint16_t* dp = cache + cache_row * row_units;
   for (uint64_t i = threadIdx.x; i < row_units; i += blockDim.x) dp[i] = src[i];
 }
 
@@ -768,12 +779,22 @@ int32_t aion_cuda_sequence_append(AionCudaDevice* dev, const AionCudaSequenceApp
   uint16_t* cache;
   const uint16_t* nk;
   const int32_t* idx;
-  if (int32_t st = resolve(s->cache, s->batch * s->t_cap * row, "sequence_append.cache", &cache)) return st;
+  const int32_t* table = nullptr;
+  uint64_t pages_per_request = 0, cache_rows = s->batch * s->t_cap;
+  if (s->page_table.handle) {
+    if (s->rolling) return fail(AION_CUDA_UNSUPPORTED, "sequence_append: a rolling cache cannot be paged");
+    if (s->page_tokens == 0 || s->pool_pages == 0) return fail(AION_CUDA_INVALID_ARGUMENT, "sequence_append: page_tokens and pool_pages must be positive");
+    pages_per_request = (s->t_cap + s->page_tokens - 1) / s->page_tokens;
+    cache_rows = s->pool_pages * s->page_tokens;
+    if (int32_t st = resolve(s->page_table, s->batch * pages_per_request * sizeof(int32_t), "sequence_append.page_table", &table)) return st;
+  }
+  if (int32_t st = resolve(s->cache, cache_rows * row, "sequence_append.cache", &cache)) return st;
   if (int32_t st = resolve(s->new_kv, s->batch * s->new_len * row, "sequence_append.new_kv", &nk)) return st;
   if (int32_t st = resolve(s->end_index, s->batch * sizeof(int32_t), "sequence_append.end_index", &idx)) return st;
   if (s->batch * s->new_len > 0x7FFFFFFFull) return fail(AION_CUDA_UNSUPPORTED, "sequence_append: too many rows for one launch");
   AION_CUDA_TRY(launch_pdl(sequence_append_kernel, dim3((unsigned)(s->batch * s->new_len)), dim3(128), 0, dev->stream, cache, nk, idx,
-                           s->t_cap, (uint64_t)(row / 2), s->new_len, s->rolling ? 1 : 0, dev->fault_dev));
+                           s->t_cap, (uint64_t)(row / 2), s->new_len, s->rolling ? 1 : 0, dev->fault_dev, table, (uint64_t)s->page_tokens,
+                           pages_per_request, (uint64_t)s->pool_pages));
   return AION_CUDA_OK;
 }
 

@@ -466,6 +466,12 @@ def run_other(args):
             out = {"metric": "decode attention GB/s", "n_gpus": 1,
                    **benchmarks.attention_leg(torch, backend, local_rank, args.attn_batch, args.attn_context,
                                               iters=max(3, min(args.steps, 50)), peak_gbs=peak)}
+        elif args.workload == "prefill-attention":
+            tf_peak = measured_peak_tflops()[0]
+            legs = [benchmarks.prefill_attention_leg(torch, backend, local_rank, args.attn_batch, args.attn_rows, kv_heads=args.attn_kv_heads,
+                                                     iters=max(3, min(args.steps, 20)), flags=fl, peak_tflops=tf_peak)
+                    for fl in (0, capi.ATTENTION_ROW_UNITS)]
+            out = {"metric": "prefill attention TFLOP/s", "n_gpus": 1, **legs[0], "one_cta_per_row": legs[1]}
         elif args.workload == "sweep":
             # The GEMV configurations of the benchmark: the single q8 NT op, then the q4 batch / shape sweep.
             rows = [benchmarks.matmul_leg(torch, backend, local_rank, capi.DTYPE_Q8_0, True, 1, 8192, 2048, lanes=args.lanes, peak_gbs=peak)]
@@ -568,7 +574,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--lanes", type=int, default=8, help="parallel lanes the independent steps are recorded into (1..8)")
     ap.add_argument("--skip-cpu-baseline", action="store_true", help="leave the CPU leg out (profiling runs)")
-    ap.add_argument("--workload", default="gemv", choices=["gemv", "decode", "gemm", "attention", "colsplit", "sweep"],
+    ap.add_argument("--workload", default="gemv", choices=["gemv", "decode", "gemm", "attention", "prefill-attention", "colsplit", "sweep"],
                     help="gemv: the headline pass (default; its line also carries the decode leg). The others print "
                          "their own line: decode tokens/s, prefill GEMM TFLOP/s, decode attention GB/s, the "
                          "column-split layer with its all-gather")
@@ -587,6 +593,8 @@ def main():
                     help="gemm workload: the tcgen05 kernel (bf16 operands), the int8-activation kernel, or the library's own choice")
     ap.add_argument("--attn-batch", type=int, default=64)
     ap.add_argument("--attn-context", type=int, default=4096)
+    ap.add_argument("--attn-rows", type=int, default=2048, help="prefill-attention workload: prompt rows per request (set --attn-batch too)")
+    ap.add_argument("--attn-kv-heads", type=int, default=4, help="prefill-attention workload: kv heads under the 8 query heads")
     ap.add_argument("--colsplit-m", type=int, default=1)
     args = ap.parse_args()
     if args.impl == "reference":

@@ -303,6 +303,7 @@ AION_CUDA_API int32_t aion_cuda_matmul_nt(AionCudaDevice* dev, const AionCudaMat
  * --------------------------------------------------------------------------------- */
 #define AION_CUDA_ATTENTION_GENERIC 1u   /* flags: take the any-shape f32 kernel */
 #define AION_CUDA_ATTENTION_ROW_UNITS 2u /* flags: one CTA per query row even when l_q > 1 (measurement) */
+#define AION_CUDA_ATTENTION_BLOCKS 4u    /* flags: blocks of positions whenever l_q > 1 (measurement) */
 typedef struct AionCudaAttention {
   AionCudaOperand out, q, k, v;
   AionCudaOperand query_positions; /* handle 0 = absent */
@@ -407,6 +408,11 @@ typedef struct AionCudaSequenceAppend {
   uint64_t batch, t_cap, heads, head_dim, new_len;
   uint32_t dtype;
   uint32_t rolling;
+  /* Paged cache (handle 0 = absent), as in AionCudaAttention: cache is the pool
+   * [pool_pages, page_tokens, H, D], page_table i32 [B, ceil(t_cap / page_tokens)]; a page number
+   * outside the pool is reported like a bad index. */
+  AionCudaOperand page_table;
+  uint64_t page_tokens, pool_pages;
 } AionCudaSequenceAppend;
 AION_CUDA_API int32_t aion_cuda_sequence_append(AionCudaDevice* dev, const AionCudaSequenceAppend* step);
 

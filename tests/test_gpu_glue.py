@@ -10,6 +10,7 @@ import oracle
 from aion_b200 import capi
 from aion_b200.backend import (BackendError, DeviceStore, StepArgMax, StepCast, StepElemwiseBinary, StepGatherRows,
                                StepRMSNorm, StepRMSNormPair, StepRoPE1D, StepSequenceAppend, TensorMeta, act_image_meta)
+from tests import refdata as rd
 from tests.gpu_util import DevBuf, make_image
 
 pytestmark = pytest.mark.gpu
@@ -169,6 +170,49 @@ def test_sequence_append(sess, rolling):
     tn, ti = put(store, new, F16), put(store, idx, I32)
     s.execute([StepSequenceAppend(cache=tc, new_kv=tn, end_index=ti)])
     assert np.array_equal(store.read(tc).view(np.uint16), oracle.sequence_append(cache, new, idx, rolling=rolling).view(np.uint16))
+
+
+def test_sequence_append_into_a_paged_cache_then_attention_reads_it(sess, backend):
+    """New rows go to the pages the table names (byte-equal to the contiguous append gathered page by
+    page), and the attention step then reads the same pool through the same table."""
+    from aion_b200.backend import AttentionWindow, StepAttention
+    s, store = sess
+    rng = np.random.default_rng(16)
+    B, T, H, D, PT, Ln = 3, 256, 2, 64, 64, 5
+    per = T // PT
+    pool = B * per + 2
+    table = rng.permutation(pool)[: B * per].reshape(B, per).astype(np.int32)
+    k0 = rng.standard_normal((B, T, H, D)).astype(np.float16)
+    v0 = rng.standard_normal((B, T, H, D)).astype(np.float16)
+    idx = np.array([0, 62, 200], dtype=np.int32)     # the second request's rows straddle two pages
+    knew = rng.standard_normal((B, Ln, H, D)).astype(np.float16)
+    vnew = rng.standard_normal((B, Ln, H, D)).astype(np.float16)
+
+    def to_pool(c):
+        p = np.zeros((pool, PT, H, D), dtype=np.float16)
+        for b in range(B):
+            for i in range(per):
+                p[table[b, i]] = c[b, i * PT:(i + 1) * PT]
+        return p
+
+    tk = store.add(TensorMeta(F16, (pool, PT, H, D)), to_pool(k0))
+    tv = store.add(TensorMeta(F16, (pool, PT, H, D)), to_pool(v0))
+    tt, ti = put(store, table, I32), put(store, idx, I32)
+    tkn, tvn = put(store, knew, F16), put(store, vnew, F16)
+    q = rng.standard_normal((B, Ln, 4, D)).astype(np.float16)
+    pos = (idx[:, None] + np.arange(Ln, dtype=np.int32)[None, :]).astype(np.int32)
+    lens = (idx + Ln).astype(np.int32)
+    tq, tp, tl = put(store, q, F16), put(store, pos, I32), put(store, lens, I32)
+    to = store.add(TensorMeta(F32, (B, Ln, 4, D)))
+    s.execute([StepSequenceAppend(cache=tk, new_kv=tkn, end_index=ti, page_table=tt),
+               StepSequenceAppend(cache=tv, new_kv=tvn, end_index=ti, page_table=tt),
+               StepAttention(out=to, q=tq, k=tk, v=tv, query_positions=tp, kv_lengths=tl, scale=0.125,
+                             window=AttentionWindow.causal(), page_table=tt)])
+    k1, v1 = oracle.sequence_append(k0, knew, idx), oracle.sequence_append(v0, vnew, idx)
+    assert np.array_equal(store.read(tk).view(np.uint16), to_pool(k1).view(np.uint16))
+    assert np.array_equal(store.read(tv).view(np.uint16), to_pool(v1).view(np.uint16))
+    want = oracle.attention(q, k1, v1, scale=0.125, positions=pos, kv_lengths=lens, right=0)
+    assert rd.rel_l2(store.read(to), want) < 1e-3
 
 
 def test_sequence_append_out_of_range_is_reported(sess, backend):

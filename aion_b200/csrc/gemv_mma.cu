@@ -313,8 +313,14 @@ __global__ void gemv_act_image_kernel(const float* __restrict__ a, uint64_t lda,
 // per warp; RW: consumer warps stacked over the activation rows (1: four warps take all MT row
 // groups, 2: eight warps, each MT / 2 of them — the warps a scheduler needs to hide the latency
 // of the MMA and shared-memory loads once there is this much arithmetic per weight byte).
+// Independent small matmuls overlap on an SM, and how many of their CTAs fit decides the
+// bandwidth they reach together: the one- and two-MMA variants are held to the registers that
+// leave room for seven CTAs per SM (fewer registers measured 4.9 - 5.3 TB/s on 9 MB matrices
+// in eight lanes, more 4.6 - 4.8).
+constexpr int min_ctas_per_sm(int mt, int cg, int rw) { return rw == 2 ? 2 : (mt * cg <= 2 ? 7 : 1); }
+
 template <int DT, bool NT, int MT, bool M1, bool RG, bool PREQ, int CG, int RW>
-__global__ void __launch_bounds__(threads_of(RW), RW == 2 ? 2 : 1) gemv_q_mma_kernel(const GemvParams p_in, const __grid_constant__ CUtensorMap tmap) {
+__global__ void __launch_bounds__(threads_of(RW), min_ctas_per_sm(MT, CG, RW)) gemv_q_mma_kernel(const GemvParams p_in, const __grid_constant__ CUtensorMap tmap) {
   using G = Geom<DT, NT, CG>;
   constexpr int TN = G::TN;
   constexpr int MPA = 8 * MT;  // activation rows of the accumulator tile

@@ -14,7 +14,7 @@ STATUS_NAMES = {0: "OK", 1: "INVALID_ARGUMENT", 2: "OUT_OF_MEMORY", 3: "UNSUPPOR
 DTYPE_F32, DTYPE_F16, DTYPE_I8, DTYPE_Q4_0, DTYPE_Q8_0, DTYPE_I32 = range(6)
 ORDER_ROW_MAJOR, ORDER_LANES4, ORDER_LANES8, ORDER_LANES16, ORDER_LANES32, ORDER_LANES32X16 = range(6)
 WINDOW_UNBOUNDED = 0xFFFFFFFF
-MATMUL_AUTO, MATMUL_FORCE_GENERIC, MATMUL_FORCE_GEMV, MATMUL_FORCE_GEMM = 0, 1, 2, 4
+MATMUL_AUTO, MATMUL_FORCE_GENERIC, MATMUL_FORCE_GEMV, MATMUL_FORCE_GEMM, MATMUL_ONE_SM = 0, 1, 2, 4, 8
 INT8_GROUP_ROWS = 64
 GEMM_MIN_M = 33
 KERNEL_GENERIC, KERNEL_INT8, KERNEL_GEMM = 1, 2, 3
@@ -53,7 +53,7 @@ class MatMul(C.Structure):
 
 class MatMulPlan(C.Structure):
     _fields_ = [("kernel", C.c_uint32), ("tile_rows", C.c_uint32), ("tile_cols", C.c_uint32), ("k_splits", C.c_uint32),
-                ("grid", C.c_uint32), ("reserved", C.c_uint32 * 3)]
+                ("grid", C.c_uint32), ("cta_pairs", C.c_uint32), ("reserved", C.c_uint32 * 2)]
 
 
 class MatMulNT(C.Structure):

@@ -88,6 +88,7 @@ int32_t matmul_args(const AionCudaMatMul* s, MatMulArgs* out, bool* empty) {
   g.ldb = s->ldb ? s->ldb : s->n;
   g.ldc = s->ldc ? s->ldc : s->n;
   g.alpha = s->alpha;
+  g.one_sm = (s->flags & AION_CUDA_MATMUL_ONE_SM) != 0;
   g.beta = s->beta;
   if (g.lda < g.k || g.ldb < g.n || g.ldc < g.n) return fail(AION_CUDA_INVALID_ARGUMENT, "matmul: a leading dimension is shorter than its row");
   const size_t bb = block_bytes_of(g.dtype);
@@ -138,6 +139,7 @@ int32_t aion_cuda_matmul_plan(AionCudaDevice* dev, const AionCudaMatMul* s, Aion
     out->tile_cols = 256;
     out->k_splits = gp.splits;
     out->grid = gp.grid;
+    out->cta_pairs = gp.pair ? 1u : 0u;
   } else if (!want_gemm && g.k > 0 && gemv_mma(dev, g, true) == AION_CUDA_OK) {
     out->kernel = AION_CUDA_KERNEL_INT8;
     out->tile_rows = g.m <= 8 ? 8u : (g.m <= 16 ? 16u : (g.m <= 32 ? 32u : (uint32_t)AION_CUDA_INT8_GROUP_ROWS));
@@ -222,6 +224,7 @@ int32_t aion_cuda_matmul_nt(AionCudaDevice* dev, const AionCudaMatMulNT* s) {
   MatMulArgs g{};
   g.dtype = s->b_dtype;
   g.nt = true;
+  g.one_sm = (s->flags & AION_CUDA_MATMUL_ONE_SM) != 0;
   g.order = s->block_order;
   g.m = s->m;
   g.n = s->n;

@@ -141,6 +141,10 @@ int32_t tensor_map_bf16_sw128(const void* base, uint64_t rows, uint64_t cols, ui
 int32_t tensor_map_16bit_sw128(const void* base, bool bf16, uint64_t rows, uint64_t cols, uint64_t pitch_bytes, uint32_t box_cols,
                                uint32_t box_rows, CUtensorMap* out);
 
+// Row-major f32 [rows, cols] view with a 128-byte swizzled box of 32 columns (bulk stores of output tiles).
+int32_t tensor_map_f32_sw128(const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_bytes, uint32_t box_cols, uint32_t box_rows,
+                             CUtensorMap* out);
+
 // Launch with programmatic stream serialization: the kernel may be scheduled while its
 // predecessor in the stream is still draining, which hides the launch latency of the chains
 // of small kernels a decode step is made of. Such a kernel calls ptx::pdl_wait() before it
@@ -193,6 +197,7 @@ struct MatMulArgs {
   // The quantized image of A written by the kernel that produced A (act_image.cuh), or null:
   // the int8 matmul then reads it instead of quantizing A itself.
   const uint8_t* a_image = nullptr;
+  bool one_sm = false;   // keep the prefill GEMM on its one-SM kernel (no CTA pairs)
 };
 int32_t matmul_generic(AionCudaDevice* dev, const MatMulArgs& g);
 // Returns AION_CUDA_UNSUPPORTED (without setting an error) when the shape or the
@@ -208,6 +213,7 @@ int32_t act_image_bf16_from_f32(AionCudaDevice* dev, uint32_t dtype, const float
 // What the prefill GEMM would do with this shape: rows per tile (128 or 256), K splits, CTAs.
 struct GemmPlan {
   uint32_t tile_rows, splits, grid;
+  bool pair;   // pairs of CTAs (two-SM MMAs); tile_rows is then the pair's
 };
 bool gemm_tcgen05_plan(const AionCudaDevice* dev, const MatMulArgs& g, GemmPlan* out);
 int32_t attention_launch(AionCudaDevice* dev, const AionCudaAttention* s);

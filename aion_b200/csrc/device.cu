@@ -154,8 +154,9 @@ int32_t tensor_map_bf16_sw128(const void* base, uint64_t rows, uint64_t cols, ui
   return tensor_map_16bit_sw128(base, true, rows, cols, pitch_bytes, box_cols, box_rows, out);
 }
 
-int32_t tensor_map_16bit_sw128(const void* base, bool bf16, uint64_t rows, uint64_t cols, uint64_t pitch_bytes, uint32_t box_cols,
-                               uint32_t box_rows, CUtensorMap* out) {
+// Row-major 2-D view with a 128-byte swizzled box: the box's inner extent is exactly one swizzle row.
+static int32_t tensor_map_2d_sw128(const void* base, CUtensorMapDataType type, uint32_t elem_bytes, uint64_t rows, uint64_t cols,
+                                   uint64_t pitch_bytes, uint32_t box_cols, uint32_t box_rows, CUtensorMap* out) {
   typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                     const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                     CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -167,17 +168,27 @@ int32_t tensor_map_16bit_sw128(const void* base, bool bf16, uint64_t rows, uint6
     if (!fn || qres != cudaDriverEntryPointSuccess) return fail(AION_CUDA_INTERNAL_ERROR, "cuTensorMapEncodeTiled is not available from this driver");
     encode = reinterpret_cast<EncodeTiledFn>(fn);
   }
-  if (((uintptr_t)base & 15) || (pitch_bytes & 15) || box_cols * 2 != 128 || box_rows > 256)
-    return fail(AION_CUDA_INTERNAL_ERROR, "tensor map: 16-bit view geometry is not TMA-addressable");
+  if (((uintptr_t)base & 15) || (pitch_bytes & 15) || box_cols * elem_bytes != 128 || box_rows > 256)
+    return fail(AION_CUDA_INTERNAL_ERROR, "tensor map: swizzled view geometry is not TMA-addressable");
   const cuuint64_t gdim[2] = {cols, rows};
   const cuuint64_t gstride[1] = {pitch_bytes};
   const cuuint32_t bx[2] = {box_cols, box_rows};
   const cuuint32_t estride[2] = {1, 1};
-  const CUresult r = encode(out, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), gdim, gstride, bx, estride,
-                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(AION_CUDA_INTERNAL_ERROR, "cuTensorMapEncodeTiled (16-bit, swizzled) failed with %d", (int)r);
+  const CUresult r = encode(out, type, 2, const_cast<void*>(base), gdim, gstride, bx, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(AION_CUDA_INTERNAL_ERROR, "cuTensorMapEncodeTiled (swizzled) failed with %d", (int)r);
   return AION_CUDA_OK;
+}
+
+int32_t tensor_map_16bit_sw128(const void* base, bool bf16, uint64_t rows, uint64_t cols, uint64_t pitch_bytes, uint32_t box_cols,
+                               uint32_t box_rows, CUtensorMap* out) {
+  return tensor_map_2d_sw128(base, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, rows, cols, pitch_bytes,
+                             box_cols, box_rows, out);
+}
+
+int32_t tensor_map_f32_sw128(const void* base, uint64_t rows, uint64_t cols, uint64_t pitch_bytes, uint32_t box_cols, uint32_t box_rows,
+                             CUtensorMap* out) {
+  return tensor_map_2d_sw128(base, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, rows, cols, pitch_bytes, box_cols, box_rows, out);
 }
 
 }  // namespace aion

@@ -529,6 +529,428 @@ gemm_q_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm
   }
 }
 
+// ---- two-SM variant: a pair of CTAs (a cluster of two) shares every MMA -----------------------
+// tcgen05.mma.cta_group::2 multiplies 256 tokens by 256 weight columns per instruction: each CTA
+// of the pair holds 128 of the tokens (its A rows, its accumulator lanes) and HALF of the weight
+// columns of the B operand. So each SM unpacks, stages and feeds the tensor core half as many
+// weight bytes per flop as the one-SM kernel; shared-memory bandwidth, not the tensor pipe, is what
+// limits that kernel. The even CTA of the pair (the leader) issues the MMAs for both.
+// Signals that cross the pair:
+//   * activation tiles: both CTAs' TMA loads complete on the leader's a_full barrier;
+//   * dequantized half tiles: the peer's dequantizers arrive on the leader's bready barrier;
+//   * MMA completion: one commit arrives on a_empty / bfree / acc_full of both CTAs;
+//   * drained accumulators: the peer's epilogue arrives on the leader's acc_empty barrier.
+constexpr int BNH = BN / 2;                  // weight columns unpacked per CTA
+constexpr int BH_TILE_BYTES = BNH * BK * 2;  // 16 KB
+constexpr int PAIR_B_STAGES = 2 * DEQ_GROUPS;
+
+template <int DT, int MH>
+struct PairGeom {
+  static constexpr int A_TILE_BYTES = MH * A_HALF_BYTES;
+  static constexpr int BB = (DT == AION_CUDA_DTYPE_Q8_0) ? Q8_BYTES : Q4_BYTES;
+  static constexpr int PACKED_ROW = BNH * BB;
+  static constexpr int PACKED_BYTES = KB_PER_STAGE * PACKED_ROW;   // 4608 (q4) / 8704 (q8)
+  static constexpr int PACKED_PAD = (PACKED_BYTES + 16 + 1023) / 1024 * 1024;
+  static constexpr int A_STAGES = MH == 1 ? 4 : 3;
+  static constexpr int P_STAGES = DT == AION_CUDA_DTYPE_Q8_0 ? 3 : 6;
+  // Two dequantized half tiles per dequantizer group where the MMAs of a stage are short (one per
+  // k-step); one where a stage carries two and the staging buffers below need the room.
+  static constexpr int B_STAGES = MH == 1 ? PAIR_B_STAGES : DEQ_GROUPS;
+  static_assert(P_STAGES % DEQ_GROUPS == 0 && B_STAGES % DEQ_GROUPS == 0, "a stage belongs to one dequantizer group");
+  // Output staging: every epilogue warp has two buffers of 32 rows x 32 columns f32 (one swizzle
+  // row per output row), filled from tensor memory and written out by bulk tensor stores.
+  static constexpr int OUT_BUF_BYTES = 32 * 128;
+  static constexpr int OUT_BYTES = 4 * 2 * OUT_BUF_BYTES;
+  static constexpr int OFF_BRING = 0;
+  static constexpr int OFF_ARING = OFF_BRING + B_STAGES * BH_TILE_BYTES;
+  static constexpr int OFF_PRING = OFF_ARING + A_STAGES * A_TILE_BYTES;
+  static constexpr int OFF_OUT = OFF_PRING + P_STAGES * PACKED_PAD;
+  static constexpr int OFF_BARS = OFF_OUT + OUT_BYTES;
+  static constexpr int SMEM_BYTES = OFF_BARS + 512 + 1024;  // barrier block + slack to align the base to 1024
+  static_assert(A_STAGES <= MAX_A_STAGES && P_STAGES <= MAX_P_STAGES && B_STAGES <= PAIR_B_STAGES, "barrier block");
+  static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
+};
+
+struct PairBars {
+  uint64_t a_full[MAX_A_STAGES];
+  uint64_t a_empty[MAX_A_STAGES];
+  uint64_t p_full[MAX_P_STAGES];
+  uint64_t p_empty[MAX_P_STAGES];
+  uint64_t bready[PAIR_B_STAGES];
+  uint64_t bfree[PAIR_B_STAGES];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  uint32_t abort;
+};
+static_assert(sizeof(PairBars) <= 512, "barrier block");
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// The address of this CTA's shared-memory location `addr` in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Arrive on a barrier that may live in the other CTA of the cluster. What the arrival publishes is
+// this CTA's own shared memory (read by this SM's half of the MMA) or its drained tensor memory, so
+// the default CTA-scope release is enough; a cluster-scope release measured about 1900 cycles per
+// arrival and made the dequantizers the bottleneck.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait on a barrier whose arrivals may come from the other CTA.
+__device__ __forceinline__ bool wait_cluster_or_abort(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
+  const uint32_t b = ptx::smem_u32(bar);
+  for (uint32_t i = 0; i < (1u << 24); i++) {
+    if (mbar_try_wait_cluster(b, parity)) return true;
+    if ((i & 63) == 63 && *abort_flag) return false;
+  }
+  return false;
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t smem_dst, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// One arrival on the barrier at this offset in BOTH CTAs once every MMA issued so far is done.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+               "h"((uint16_t)3)
+               : "memory");
+}
+// Tiled load whose completion bytes are counted on a barrier of the pair's leader.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst_smem, const void* tmap, int32_t x, int32_t y, uint32_t leader_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst_smem),
+      "l"(tmap), "r"(x), "r"(y), "r"(leader_bar)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,"
+      "%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+        "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]),
+        "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+// Bulk tensor store of one staged box (shared -> global); out-of-range rows and columns are clipped.
+__device__ __forceinline__ void tma_store_2d(const void* tmap, int32_t x, int32_t y, uint32_t src_smem) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(tmap), "r"(x), "r"(y), "r"(src_smem)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Until at most `N` of this thread's bulk groups still read their shared-memory source.
+template <int N>
+__device__ __forceinline__ void bulk_wait_group_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void bulk_wait_group_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+// Instruction descriptor of the pair's MMA: D f32, A and B bf16, both K-major, M = 256, N = 256.
+constexpr uint32_t kInstrDescPair = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+
+template <int DT, int MH>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_q_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                   const __grid_constant__ CUtensorMap tmap_c) {
+  using G = PairGeom<DT, MH>;
+  constexpr uint32_t ACC_COLS = MH * BN;   // all 512 columns when MH == 2: one accumulator set
+  constexpr uint32_t NACC = MH == 1 ? 2 : 1;
+  constexpr int A_TILE_BYTES = G::A_TILE_BYTES;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = ptx::smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* sm = smem_raw + (base - raw);
+  PairBars* bars = reinterpret_cast<PairBars*>(sm + G::OFF_BARS);
+  volatile uint32_t* abort_flag = &bars->abort;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();   // 0: leader
+  const bool leader = rank == 0;
+  constexpr uint32_t AS = G::A_STAGES, PS = G::P_STAGES, BS = G::B_STAGES;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < (int)AS; s++) {
+      ptx::mbar_init(ptx::smem_u32(&bars->a_full[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&bars->a_empty[s]), 1);
+    }
+    for (int s = 0; s < (int)PS; s++) {
+      ptx::mbar_init(ptx::smem_u32(&bars->p_full[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&bars->p_empty[s]), DEQ_WARPS / DEQ_GROUPS);
+    }
+    for (int s = 0; s < (int)BS; s++) {
+      ptx::mbar_init(ptx::smem_u32(&bars->bready[s]), 2 * (DEQ_WARPS / DEQ_GROUPS));   // both CTAs' warps
+      ptx::mbar_init(ptx::smem_u32(&bars->bfree[s]), 1);
+    }
+    for (int a = 0; a < 2; a++) {
+      ptx::mbar_init(ptx::smem_u32(&bars->acc_full[a]), 1);
+      ptx::mbar_init(ptx::smem_u32(&bars->acc_empty[a]), 8);   // four epilogue warps of each CTA
+    }
+    bars->abort = 0;
+    ptx::fence_barrier_init();
+    ptx::prefetch_tensormap(&tmap_a);
+    ptx::prefetch_tensormap(&tmap_b);
+    ptx::prefetch_tensormap(&tmap_c);
+  }
+  if (warp == 1) {
+    tmem_alloc2(ptx::smem_u32(&bars->tmem_base), TMEM_COLS);
+    tmem_relinquish2();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();   // the other CTA's barriers and tensor memory exist from here on
+  tc_fence_after();
+  ptx::pdl_launch_dependents();
+  ptx::pdl_wait();
+  const uint32_t tmem_base = bars->tmem_base;
+  const uint32_t units = p.m_tiles * p.n_tiles * p.splits;
+  const uint32_t pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+
+  if (warp == 0) {
+    // ---- TMA producer of this CTA's activation rows ----
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (uint32_t u = pair; u < units && ok; u += pairs) {
+        const Unit w = unit_of(p, u);
+        const int32_t m0 = (int32_t)((w.tile % p.m_tiles) * (2 * BM * MH) + rank * BM);
+        for (uint32_t ks = w.ks0; ks < w.ks1; ks++, it++) {
+          const uint32_t s = it % AS, use = it / AS;
+          if (use > 0 && !wait_or_abort<true>(&bars->a_empty[s], (use - 1) & 1, abort_flag)) {
+            raise_abort(p.fault, abort_flag);
+            ok = false;
+            break;
+          }
+          const uint32_t full_local = ptx::smem_u32(&bars->a_full[s]);
+          if (leader) ptx::mbar_arrive_expect_tx(full_local, 2 * A_TILE_BYTES);
+          const uint32_t full = map_to_cta(full_local, 0);
+#pragma unroll
+          for (int h = 0; h < MH; h++)
+            tma_load_2d_pair(base + G::OFF_ARING + s * A_TILE_BYTES + h * A_HALF_BYTES, &tmap_a, (int32_t)(ks * BK), m0 + h * 2 * BM, full);
+        }
+      }
+    }
+  } else if (warp == 2) {
+    // ---- TMA producer of this CTA's half of the packed weight blocks ----
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (uint32_t u = pair; u < units && ok; u += pairs) {
+        const Unit w = unit_of(p, u);
+        const int32_t n0 = (int32_t)((w.tile / p.m_tiles) * BN + rank * BNH);
+        for (uint32_t ks = w.ks0; ks < w.ks1; ks++, it++) {
+          const uint32_t s = it % PS, use = it / PS;
+          if (use > 0 && !wait_or_abort<true>(&bars->p_empty[s], (use - 1) & 1, abort_flag)) {
+            raise_abort(p.fault, abort_flag);
+            ok = false;
+            break;
+          }
+          const uint32_t full = ptx::smem_u32(&bars->p_full[s]);
+          ptx::mbar_arrive_expect_tx(full, G::PACKED_BYTES);
+          ptx::tma_load_3d(base + G::OFF_PRING + s * G::PACKED_PAD, &tmap_b, 0, n0 / 8, (int32_t)(ks * KB_PER_STAGE), full);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer: the leader's, for both CTAs ----
+    if (leader) {
+      uint32_t it = 0, tile_iter = 0;
+      bool ok = true;
+      for (uint32_t u = pair; u < units && ok; u += pairs, tile_iter++) {
+        const Unit w = unit_of(p, u);
+        const uint32_t acc = tile_iter % NACC, acc_use = tile_iter / NACC;
+        if (acc_use > 0 && !wait_cluster_or_abort(&bars->acc_empty[acc], (acc_use - 1) & 1, abort_flag)) {
+          if (lane == 0) raise_abort(p.fault, abort_flag);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * ACC_COLS;
+        for (uint32_t ks = w.ks0; ks < w.ks1; ks++, it++) {
+          const uint32_t sa = it % AS, pha = (it / AS) & 1, sb = it % BS, phb = (it / BS) & 1;
+          if (!wait_cluster_or_abort(&bars->a_full[sa], pha, abort_flag) || !wait_cluster_or_abort(&bars->bready[sb], phb, abort_flag)) {
+            if (lane == 0) raise_abort(p.fault, abort_flag);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          if (lane == 0) {
+            const uint64_t a_desc = smem_desc_sw128(base + G::OFF_ARING + sa * A_TILE_BYTES);
+            const uint64_t b_desc = smem_desc_sw128(base + G::OFF_BRING + sb * BH_TILE_BYTES);
+#pragma unroll
+            for (int kk = 0; kk < BK / UMMA_K; kk++)
+#pragma unroll
+              for (int h = 0; h < MH; h++)
+                umma_bf16_pair(d_tmem + h * BN, a_desc + (uint64_t)((h * A_HALF_BYTES + kk * UMMA_K * 2) / 16),
+                               b_desc + (uint64_t)(kk * UMMA_K * 2 / 16), kInstrDescPair, ((ks - w.ks0) | (uint32_t)kk) != 0);
+            umma_commit_pair(ptx::smem_u32(&bars->a_empty[sa]));
+            umma_commit_pair(ptx::smem_u32(&bars->bfree[sb]));
+          }
+          __syncwarp();
+        }
+        if (ok && lane == 0) umma_commit_pair(ptx::smem_u32(&bars->acc_full[acc]));
+        __syncwarp();
+      }
+    }
+  } else if (warp < EPI_WARP0) {
+    // ---- dequantizers: thread j of a group owns weight column j of this CTA's half ----
+    constexpr uint32_t GROUP_WARPS = DEQ_WARPS / DEQ_GROUPS, GROUP_THREADS = GROUP_WARPS * 32;
+    static_assert(GROUP_THREADS == BNH, "one weight column per dequantizer thread");
+    const uint32_t dw = warp - DEQ_WARP0, group = dw / GROUP_WARPS, row = (dw % GROUP_WARPS) * 32 + lane;
+    uint32_t it = 0;
+    bool ok = true;
+    for (uint32_t u = pair; u < units && ok; u += pairs) {
+      const Unit w = unit_of(p, u);
+      for (uint32_t ks = w.ks0; ks < w.ks1; ks++, it++) {
+        if (it % DEQ_GROUPS != group) continue;
+        const uint32_t sp = it % PS, php = (it / PS) & 1, sb = it % BS, buse = it / BS;
+        if (!wait_or_abort<true>(&bars->p_full[sp], php, abort_flag) ||
+            (buse > 0 && !wait_or_abort<true>(&bars->bfree[sb], (buse - 1) & 1, abort_flag))) {
+          if (lane == 0) raise_abort(p.fault, abort_flag);
+          ok = false;
+          break;
+        }
+        const uint32_t packed = base + G::OFF_PRING + sp * G::PACKED_PAD;
+        uint8_t* btile = sm + G::OFF_BRING + sb * BH_TILE_BYTES;
+#pragma unroll
+        for (int kbl = 0; kbl < KB_PER_STAGE; kbl++) {
+          const uint32_t blk = packed + kbl * G::PACKED_ROW + row * G::BB;
+          if (DT == AION_CUDA_DTYPE_Q4_0) dequant_q4_block(blk, btile, row, kbl * 4);
+          else dequant_q8_block(blk, btile, row, kbl * 4);
+        }
+        ptx::fence_proxy_async();  // the tensor core reads this tile through the async proxy
+        __syncwarp();
+        if (lane == 0) {
+          ptx::mbar_arrive(ptx::smem_u32(&bars->p_empty[sp]));
+          mbar_arrive_cluster(map_to_cta(ptx::smem_u32(&bars->bready[sb]), 0));
+        }
+      }
+    }
+  } else {
+    // ---- epilogue: this CTA's 128 accumulator lanes = its 128 tokens of every half ----
+    // Plain outputs (no beta, no K split) leave through shared memory: 32 columns of a warp's 32
+    // rows at a time are staged (128-byte swizzle, so the stores spread over the banks) and written
+    // by one bulk tensor store, which clips the rows past m and the columns past n. A thread
+    // storing its own row straight to global memory touches 32 separate sectors per instruction,
+    // and that made the epilogue a third of the kernel.
+    const uint32_t quarter = warp & 3;
+    const bool staged = p.splits == 1 && p.beta == 0.0f;
+    const uint32_t out_buf = base + G::OFF_OUT + quarter * 2 * G::OUT_BUF_BYTES;
+    uint8_t* out_ptr = sm + G::OFF_OUT + quarter * 2 * G::OUT_BUF_BYTES;
+    uint32_t chunk_iter = 0;
+    uint32_t tile_iter = 0;
+    for (uint32_t u = pair; u < units; u += pairs, tile_iter++) {
+      const Unit w = unit_of(p, u);
+      const uint32_t acc = tile_iter % NACC, acc_use = tile_iter / NACC;
+      if (!wait_or_abort(&bars->acc_full[acc], acc_use & 1, abort_flag)) {
+        if (lane == 0) raise_abort(p.fault, abort_flag);
+        break;
+      }
+      tc_fence_after();
+      const uint32_t m0 = (w.tile % p.m_tiles) * (2 * BM * MH), n0 = (w.tile / p.m_tiles) * BN;
+#pragma unroll 1
+      for (int h = 0; h < MH; h++) {
+        const uint32_t trow = h * 2 * BM + rank * BM + quarter * 32 + lane, row = m0 + trow;
+        const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + acc * ACC_COLS + h * BN;
+        if (staged) {
+          if (row - lane >= p.m) continue;   // none of this warp's rows exist (the same for the whole warp)
+#pragma unroll 1
+          for (uint32_t c0 = 0; c0 < BN; c0 += 32, chunk_iter++) {
+            if (n0 + c0 >= p.n) break;   // the same for the whole warp
+            uint32_t r[32];
+            tmem_ld32(taddr + c0, r);
+            // The buffer about to be filled was the source of the store two chunks ago.
+            if (lane == 0) bulk_wait_group_read<1>();
+            __syncwarp();
+            tmem_ld_wait();
+            uint8_t* buf = out_ptr + (chunk_iter & 1) * G::OUT_BUF_BYTES + lane * 128;
+#pragma unroll
+            for (int q = 0; q < 8; q++)
+              *reinterpret_cast<float4*>(buf + ((q ^ (lane & 7)) << 4)) =
+                  make_float4(__uint_as_float(r[4 * q]) * p.alpha, __uint_as_float(r[4 * q + 1]) * p.alpha, __uint_as_float(r[4 * q + 2]) * p.alpha,
+                              __uint_as_float(r[4 * q + 3]) * p.alpha);
+            ptx::fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&tmap_c, (int32_t)(n0 + c0), (int32_t)(row - lane), out_buf + (chunk_iter & 1) * G::OUT_BUF_BYTES);
+              bulk_commit_group();
+            }
+          }
+          continue;
+        }
+        float* crow = p.c + (uint64_t)row * p.ldc + n0;
+        float* slot = p.partial + ((size_t)w.tile * p.splits + w.split) * ((size_t)2 * BM * MH * BN) + (size_t)trow * BN;
+#pragma unroll 1
+        for (uint32_t c0 = 0; c0 < BN; c0 += 16) {
+          uint32_t r[16];
+          tmem_ld16(taddr + c0, r);
+          tmem_ld_wait();
+          if (row < p.m) {
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+              const uint32_t col = n0 + c0 + q * 4;
+              if (col >= p.n) continue;
+              float4 v = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]), __uint_as_float(r[4 * q + 2]),
+                                     __uint_as_float(r[4 * q + 3]));
+              if (p.splits > 1) {
+                __stcg(reinterpret_cast<float4*>(slot + c0 + q * 4), v);
+                continue;
+              }
+              v.x *= p.alpha, v.y *= p.alpha, v.z *= p.alpha, v.w *= p.alpha;
+              float4* dst = reinterpret_cast<float4*>(crow + c0 + q * 4);
+              if (p.beta != 0.0f) {
+                const float4 o = *dst;
+                v.x += p.beta * o.x, v.y += p.beta * o.y, v.z += p.beta * o.z, v.w += p.beta * o.w;
+              }
+              *dst = v;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(ptx::smem_u32(&bars->acc_empty[acc]), 0));
+    }
+    if (lane == 0) bulk_wait_group_all();   // this CTA's shared memory and its stores outlive nothing
+  }
+
+  // Neither CTA may leave (or free tensor memory) while the other can still signal it or read its
+  // shared memory through an MMA in flight: every role of both CTAs is past its last wait here.
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc2(tmem_base, TMEM_COLS);
+  }
+}
+
 // C = alpha * sum over splits (in split order) + beta * C for the split-K path; one thread per
 // four adjacent columns, so both the partial reads and the C accesses are coalesced.
 __global__ void splitk_reduce_kernel(const GemmParams p) {
@@ -662,6 +1084,101 @@ int32_t launch_gemm(AionCudaDevice* dev, const MatMulArgs& g, const __nv_bfloat1
   return AION_CUDA_OK;
 }
 
+
+// Clusters of two CTAs that fit the device at once, per instantiation (0: the launch is not possible).
+template <int DT, int MH>
+int32_t pair_capacity(AionCudaDevice* dev, int* pairs_out) {
+  using G = PairGeom<DT, MH>;
+  auto kernel = gemm_q_pair_kernel<DT, MH>;
+  static std::mutex mu;
+  static int pairs[64] = {};
+  static bool configured[64] = {};
+  if (dev->ordinal < 0 || dev->ordinal >= 64) {
+    *pairs_out = 0;
+    return AION_CUDA_OK;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (!configured[dev->ordinal]) {
+    AION_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM_BYTES));
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2 * (unsigned)dev->sm_count);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = G::SMEM_BYTES;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) {
+      cudaGetLastError();
+      n = 0;
+    }
+    pairs[dev->ordinal] = n;
+    configured[dev->ordinal] = true;
+  }
+  *pairs_out = pairs[dev->ordinal];
+  return AION_CUDA_OK;
+}
+
+template <int DT, int MH>
+int32_t launch_gemm_pair(AionCudaDevice* dev, const MatMulArgs& g, const __nv_bfloat16* a_bf16, uint32_t splits, float* partial, uint32_t pairs) {
+  using G = PairGeom<DT, MH>;
+  auto kernel = gemm_q_pair_kernel<DT, MH>;
+  const uint64_t kblocks = g.k / QK;
+  CUtensorMap tmap_a, tmap_b;
+  if (int32_t st = tensor_map_bf16_sw128(a_bf16, g.m, g.k, g.k * 2, BK, BM, &tmap_a)) return st;
+  {
+    // Packed weights as [K/32][ldb/8][8 blocks]: box = 2 block rows x 16 groups x 8 blocks (this CTA's 128 columns).
+    const uint64_t dims[3] = {8ull * G::BB, g.n / 8, kblocks};
+    const uint64_t strides[2] = {8ull * G::BB, g.ldb * G::BB};
+    const uint32_t box[3] = {8u * G::BB, BNH / 8, KB_PER_STAGE};
+    if (int32_t st = tensor_map_encode(g.b, 3, dims, strides, box, &tmap_b)) return st;
+  }
+  // C as [m][n] f32 with boxes of 32 x 32 for the staged stores (unused, but valid, when beta or a K split
+  // keeps the epilogue on plain stores).
+  CUtensorMap tmap_c;
+  if (int32_t st = tensor_map_f32_sw128(g.c, g.m, g.n, g.ldc * sizeof(float), 32, 32, &tmap_c)) return st;
+  GemmParams p{};
+  p.c = g.c;
+  p.m = (uint32_t)g.m, p.n = (uint32_t)g.n, p.k = (uint32_t)g.k;
+  p.ldc = g.ldc;
+  p.alpha = g.alpha, p.beta = g.beta;
+  p.tile_rows = 2 * BM * MH;
+  p.m_tiles = (uint32_t)ceil_div(g.m, (uint64_t)p.tile_rows);
+  p.n_tiles = (uint32_t)ceil_div(g.n, (uint64_t)BN);
+  p.k_stages = (uint32_t)ceil_div(g.k, (uint64_t)BK);
+  p.fault = dev->fault_dev;
+  p.splits = splits;
+  p.partial = partial;
+  const uint32_t units = p.m_tiles * p.n_tiles * splits;
+  const uint32_t grid = 2 * (units < pairs ? units : pairs);
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = G::SMEM_BYTES;
+  cfg.stream = dev->stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  static const bool overlap = std::getenv("AION_CUDA_NO_PDL_MAIN") == nullptr;  // tuning only
+  cfg.numAttrs = overlap ? 2 : 1;
+  AION_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, p, tmap_a, tmap_b, tmap_c));
+  if (splits > 1) {
+    const uint64_t quads = (uint64_t)g.m * (g.n / 4);
+    const unsigned blocks = (unsigned)std::min<uint64_t>(ceil_div(quads, (uint64_t)256), (uint64_t)dev->sm_count * 8);
+    AION_CUDA_TRY(launch_pdl_main(splitk_reduce_kernel, dim3(blocks), dim3(256), 0, dev->stream, p));
+  }
+  return AION_CUDA_OK;
+}
+
 }  // namespace
 
 // q8_0 [n][k/32] blocks in `order` -> K-major [k/32][n] blocks (the layout `MatMul` reads).
@@ -682,7 +1199,16 @@ int32_t nt_blocks_to_kmajor(AionCudaDevice* dev, uint32_t order, const uint8_t* 
 }
 
 // Whether this kernel reads the step's operands, and how it would tile them.
-static bool plan_gemm(const AionCudaDevice* dev, const MatMulArgs& g, GemmPlan* out) {
+// AION_CUDA_GEMM_PAIR=0 keeps every shape on the one-SM kernel (measurement).
+static bool pair_enabled() {
+  static const bool on = [] {
+    const char* e = std::getenv("AION_CUDA_GEMM_PAIR");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
+static bool plan_gemm(const AionCudaDevice* dev, const MatMulArgs& g, GemmPlan* out, bool allow_pair = true) {
   if (g.dtype != AION_CUDA_DTYPE_Q4_0 && g.dtype != AION_CUDA_DTYPE_Q8_0) return false;
   if (g.m == 0 || g.n == 0 || g.k == 0) return false;
   if (g.nt) {
@@ -694,30 +1220,40 @@ static bool plan_gemm(const AionCudaDevice* dev, const MatMulArgs& g, GemmPlan* 
   }
   if ((g.n & 7) || ((uintptr_t)g.c & 15) || (g.ldc & 3)) return false;
   if (g.m > (1u << 24) || g.n > (1u << 24) || g.k > (1u << 24)) return false;
-  // 256-token tiles (one dequantized weight tile feeds two MMAs) once there are enough of them
-  // to fill the SMs; 128-token tiles with a double-buffered accumulator otherwise.
+  // Above 128 rows: pairs of CTAs (two-SM MMAs). A pair's tile is 256 tokens, or 512 (two MMAs per
+  // dequantized weight tile) once there are enough of those to fill the pairs.
+  const bool pair = allow_pair && !g.one_sm && g.m > BM && pair_enabled();
+  const uint64_t workers = pair ? (uint64_t)dev->sm_count / 2 : (uint64_t)dev->sm_count;   // CTAs or pairs
+  const uint64_t base_rows = pair ? 2 * BM : BM;
+  // 1-SM kernel: 256-token tiles (one dequantized weight tile feeds two MMAs) once there are enough
+  // of them to fill the SMs; 128-token tiles with a double-buffered accumulator otherwise.
   // (fewer 256-token tiles with a K split to fill the SMs measured slower: m = 512 x 8192 columns
   // took 47 us that way against 39 us with 128-token tiles)
-  const uint64_t tiles256 = ceil_div(g.m, (uint64_t)(2 * BM)) * ceil_div(g.n, (uint64_t)BN);
-  const uint32_t mh = (g.m > BM && tiles256 >= (uint64_t)dev->sm_count) ? 2 : 1;
-  const uint64_t tiles = ceil_div(g.m, (uint64_t)(BM * mh)) * ceil_div(g.n, (uint64_t)BN), k_stages = ceil_div(g.k, (uint64_t)BK);
+  const uint64_t tiles2 = ceil_div(g.m, 2 * base_rows) * ceil_div(g.n, (uint64_t)BN);
+  uint32_t mh = (g.m > base_rows && tiles2 >= workers) ? 2 : 1;
+  {
+    static const int force = [] { const char* e = std::getenv("AION_CUDA_GEMM_MH"); return e ? atoi(e) : 0; }();   // measurement
+    if (force == 1 || (force == 2 && g.m > base_rows)) mh = (uint32_t)force;
+  }
+  const uint64_t tiles = ceil_div(g.m, base_rows * mh) * ceil_div(g.n, (uint64_t)BN), k_stages = ceil_div(g.k, (uint64_t)BK);
   // Few output tiles (narrow layers): split K so the SMs are covered. A split keeps at least
   // two k-stages; its raw accumulator goes through scratch.
   uint64_t splits = 1;
-  if (tiles * 2 <= (uint64_t)dev->sm_count) {
-    splits = (uint64_t)dev->sm_count / tiles;
+  if (tiles * 2 <= workers) {
+    splits = workers / tiles;
     if (splits > k_stages / 2) splits = k_stages / 2;
     if (splits > 16) splits = 16;
     if (splits < 1) splits = 1;
   }
-  out->tile_rows = BM * mh;
+  out->tile_rows = (uint32_t)(base_rows * mh);
   out->splits = (uint32_t)splits;
+  out->pair = pair;
   const uint64_t units = tiles * splits;
-  out->grid = (uint32_t)(units < (uint64_t)dev->sm_count ? units : (uint64_t)dev->sm_count);
+  out->grid = (uint32_t)((units < workers ? units : workers) * (pair ? 2 : 1));
   return true;
 }
 
-bool gemm_tcgen05_plan(const AionCudaDevice* dev, const MatMulArgs& g, GemmPlan* out) { return plan_gemm(dev, g, out); }
+bool gemm_tcgen05_plan(const AionCudaDevice* dev, const MatMulArgs& g, GemmPlan* out) { return plan_gemm(dev, g, out, true); }
 
 // Returns UNSUPPORTED (without setting a message) for shapes this kernel does not read, so
 // the caller can route them to the any-shape kernel.
@@ -727,7 +1263,18 @@ int32_t gemm_tcgen05(AionCudaDevice* dev, const MatMulArgs& g_in) {
   if (g.m == 0 || g.n == 0) return AION_CUDA_OK;
   GemmPlan plan{};
   if (!plan_gemm(dev, g, &plan)) return AION_CUDA_UNSUPPORTED;
-  const int mh = (int)(plan.tile_rows / BM);
+  int pairs = 0;
+  if (plan.pair) {
+    // Clusters of two that the device can hold at once; none (an SM partition without room for pairs)
+    // sends the shape to the one-SM kernel.
+    const bool two = plan.tile_rows == 4 * BM;
+    int32_t st;
+    if (g.dtype == AION_CUDA_DTYPE_Q4_0) st = two ? pair_capacity<AION_CUDA_DTYPE_Q4_0, 2>(dev, &pairs) : pair_capacity<AION_CUDA_DTYPE_Q4_0, 1>(dev, &pairs);
+    else st = two ? pair_capacity<AION_CUDA_DTYPE_Q8_0, 2>(dev, &pairs) : pair_capacity<AION_CUDA_DTYPE_Q8_0, 1>(dev, &pairs);
+    if (st) return st;
+    if (pairs < 1 && !plan_gemm(dev, g, &plan, false)) return AION_CUDA_UNSUPPORTED;
+  }
+  const int mh = (int)(plan.tile_rows / (plan.pair ? 2 * BM : BM));
   const uint64_t splits = plan.splits;
   const uint64_t tiles = ceil_div(g.m, (uint64_t)plan.tile_rows) * ceil_div(g.n, (uint64_t)BN);
   // `MatMulNT`: the same kernel after a block permutation of the weights into lane scratch
@@ -739,7 +1286,7 @@ int32_t gemm_tcgen05(AionCudaDevice* dev, const MatMulArgs& g_in) {
   }
   // Lane scratch: the bf16 copy of the activation, then the split partials.
   const size_t a_bytes = ((size_t)g.m * g.k * sizeof(__nv_bfloat16) + 1023) & ~size_t(1023);
-  const size_t part_bytes = splits > 1 ? (size_t)tiles * splits * BM * mh * BN * sizeof(float) : 0;
+  const size_t part_bytes = splits > 1 ? (size_t)tiles * splits * plan.tile_rows * BN * sizeof(float) : 0;
   if (int32_t st = dev->reserve_scratch(relaid_bytes + a_bytes + part_bytes)) return st;
   uint8_t* scratch = static_cast<uint8_t*>(dev->lane_scratch());
   if (g.nt) {
@@ -757,6 +1304,13 @@ int32_t gemm_tcgen05(AionCudaDevice* dev, const MatMulArgs& g_in) {
     const unsigned blocks = (unsigned)std::min<uint64_t>(ceil_div(groups, (uint64_t)256), (uint64_t)dev->sm_count * 8);
     AION_CUDA_TRY(launch_pdl_main(convert_a_bf16_kernel, dim3(blocks), dim3(256), 0, dev->stream, g.a, g.lda, a_bf16, (uint32_t)g.m, (uint32_t)g.k,
                              g.dtype == AION_CUDA_DTYPE_Q4_0 ? 1 : 0));
+  }
+  if (plan.pair) {
+    if (g.dtype == AION_CUDA_DTYPE_Q4_0)
+      return mh == 2 ? launch_gemm_pair<AION_CUDA_DTYPE_Q4_0, 2>(dev, g, a_bf16, (uint32_t)splits, partial, (uint32_t)pairs)
+                     : launch_gemm_pair<AION_CUDA_DTYPE_Q4_0, 1>(dev, g, a_bf16, (uint32_t)splits, partial, (uint32_t)pairs);
+    return mh == 2 ? launch_gemm_pair<AION_CUDA_DTYPE_Q8_0, 2>(dev, g, a_bf16, (uint32_t)splits, partial, (uint32_t)pairs)
+                   : launch_gemm_pair<AION_CUDA_DTYPE_Q8_0, 1>(dev, g, a_bf16, (uint32_t)splits, partial, (uint32_t)pairs);
   }
   if (g.dtype == AION_CUDA_DTYPE_Q4_0)
     return mh == 2 ? launch_gemm<AION_CUDA_DTYPE_Q4_0, 2>(dev, g, a_bf16, (uint32_t)splits, partial)

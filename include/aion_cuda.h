@@ -196,6 +196,7 @@ typedef struct AionCudaMatMul {
 #define AION_CUDA_MATMUL_FORCE_GENERIC 1u /* any-shape scalar kernel */
 #define AION_CUDA_MATMUL_FORCE_GEMV 2u    /* tiled int8 tensor-core kernel (decode) */
 #define AION_CUDA_MATMUL_FORCE_GEMM 4u    /* tcgen05 prefill GEMM */
+#define AION_CUDA_MATMUL_ONE_SM 8u        /* the prefill GEMM stays on its one-SM kernel (no pairs of CTAs sharing an MMA) */
 
 AION_CUDA_API int32_t aion_cuda_matmul(AionCudaDevice* dev, const AionCudaMatMul* step);
 
@@ -212,7 +213,8 @@ typedef struct AionCudaMatMulPlan {
   uint32_t tile_cols; /* output columns per tile */
   uint32_t k_splits;  /* GEMM: CTAs that share one tile's K range (1 = none) */
   uint32_t grid;      /* GEMM: CTAs launched; 0 where the choice is made at launch */
-  uint32_t reserved[3];
+  uint32_t cta_pairs; /* GEMM: 1 = clusters of two CTAs share every MMA (tile_rows is the pair's: 256 or 512) */
+  uint32_t reserved[2];
 } AionCudaMatMulPlan;
 AION_CUDA_API int32_t aion_cuda_matmul_plan(AionCudaDevice* dev, const AionCudaMatMul* step, AionCudaMatMulPlan* out);
 

@@ -20,6 +20,11 @@ TOL_INT8A = 5e-3   # against the reference CPU arithmetic (the stated bound is 1
 TOL_DEQ = 1e-2     # against f32 activations: the reference's own CPU-vs-device distance
 
 
+# Both tensor-core kernels: pairs of CTAs sharing every MMA (the default above 128 rows) and the one-SM kernel.
+PAIRS, ONE_SM = capi.MATMUL_FORCE_GEMM, capi.MATMUL_FORCE_GEMM | capi.MATMUL_ONE_SM
+KERNELS = [pytest.param(PAIRS, id="pairs"), pytest.param(ONE_SM, id="one_sm")]
+
+
 def rel_l2(got, want):
     return float(np.linalg.norm(got.astype(np.float64) - want.astype(np.float64)) / max(np.linalg.norm(want.astype(np.float64)), 1e-30))
 
@@ -41,10 +46,11 @@ def make(dtype, m, n, k, seed=0, ldb=0):
 
 @pytest.mark.parametrize("dtype", [capi.DTYPE_Q4_0, capi.DTYPE_Q8_0])
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (33, 256, 128), (128, 256, 96), (200, 264, 256), (130, 512, 2048),
-                                   (64, 8, 32), (257, 776, 160)])
-def test_gemm_matches_oracle(backend, dtype, m, n, k):
+                                   (64, 8, 32), (257, 776, 160), (513, 520, 320)])
+@pytest.mark.parametrize("gflags", KERNELS)
+def test_gemm_matches_oracle(backend, dtype, m, n, k, gflags):
     a, b = make(dtype, m, n, k)
-    got = run_matmul(backend, dtype, a, b, m, n, k, flags=capi.MATMUL_FORCE_GEMM)
+    got = run_matmul(backend, dtype, a, b, m, n, k, flags=gflags)
     want_deq = oracle.matmul_deqf32(dtype, a, b, m, n, k).reshape(m, n)
     want_i8 = oracle.matmul_q(dtype, a, b, m, n, k).reshape(m, n)
     assert rel_l2(got, want_deq) <= TOL_DEQ
@@ -52,14 +58,15 @@ def test_gemm_matches_oracle(backend, dtype, m, n, k):
 
 
 @pytest.mark.parametrize("dtype", [capi.DTYPE_Q4_0, capi.DTYPE_Q8_0])
-def test_gemm_alpha_beta_and_leading_dims(backend, dtype):
+@pytest.mark.parametrize("gflags", KERNELS)
+def test_gemm_alpha_beta_and_leading_dims(backend, dtype, gflags):
     m, n, k, lda, ldb, ldc = 150, 264, 192, 200, 272, 280
     a, b = make(dtype, m, n, k, seed=3, ldb=ldb)
     a_wide = np.zeros((m, lda), dtype=np.float32)
     a_wide[:, :k] = a
     c0 = np.random.default_rng(9).standard_normal(m * ldc).astype(np.float32)
     got = run_matmul(backend, dtype, a_wide, b, m, n, k, lda=lda, ldb=ldb, ldc=ldc, alpha=0.5, beta=-1.25, c=c0,
-                     flags=capi.MATMUL_FORCE_GEMM)
+                     flags=gflags)
     want = oracle.matmul_q(dtype, a_wide, b, m, n, k, lda=lda, ldb=ldb, ldc=ldc, alpha=0.5, beta=-1.25, c=c0).reshape(m, ldc)
     assert rel_l2(got[:, :n], want[:, :n]) <= TOL_INT8A
     # columns between n and ldc are not part of C and must be left alone
@@ -67,29 +74,34 @@ def test_gemm_alpha_beta_and_leading_dims(backend, dtype):
 
 
 @pytest.mark.parametrize("dtype", [capi.DTYPE_Q4_0, capi.DTYPE_Q8_0])
-def test_gemm_prefill_m512(backend, dtype):
-    # The prefill configuration with m = 512 on the tensor-core kernel (128-token tiles: 256 of them).
+@pytest.mark.parametrize("gflags", KERNELS)
+def test_gemm_prefill_m512(backend, dtype, gflags):
+    # The prefill configuration with m = 512: 256-token tiles of CTA pairs (64 of them), or 128-token tiles (256) on one SM.
     m, n, k = 512, 8192, 2048
     a, b = make(dtype, m, n, k, seed=7)
-    plan = matmul_plan(backend, dtype, m, n, k, flags=capi.MATMUL_FORCE_GEMM)
-    assert plan.kernel == capi.KERNEL_GEMM and plan.tile_rows == 128 and plan.k_splits == 1
-    got = run_matmul(backend, dtype, a, b, m, n, k, flags=capi.MATMUL_FORCE_GEMM)
+    plan = matmul_plan(backend, dtype, m, n, k, flags=gflags)
+    assert plan.kernel == capi.KERNEL_GEMM and plan.k_splits == 1
+    assert (plan.tile_rows, plan.cta_pairs) == ((256, 1) if gflags == PAIRS else (128, 0))
+    got = run_matmul(backend, dtype, a, b, m, n, k, flags=gflags)
     want_i8 = oracle.fast_matmul_q(dtype, a, b, m, n, k).reshape(m, n)
     assert rel_l2(got, want_i8) <= TOL_INT8A
     # linearity in alpha, exactly: the epilogue multiplies the same accumulators
-    got2 = run_matmul(backend, dtype, a, b, m, n, k, alpha=2.0, flags=capi.MATMUL_FORCE_GEMM)
+    got2 = run_matmul(backend, dtype, a, b, m, n, k, alpha=2.0, flags=gflags)
     assert np.array_equal(got2, 2.0 * got)
 
 
 @pytest.mark.parametrize("dtype", [capi.DTYPE_Q4_0, capi.DTYPE_Q8_0])
-def test_gemm_prefill_m2048_takes_256_token_tiles(backend, dtype):
-    """The prefill configuration with m = 2048, routed by m alone: 8 x 32 = 256 tiles of 256 tokens, at
-    least one per SM, so the kernel variant whose dequantized weight tile feeds two MMAs runs."""
+@pytest.mark.parametrize("gflags", [pytest.param(capi.MATMUL_AUTO, id="pairs"), pytest.param(capi.MATMUL_ONE_SM, id="one_sm")])
+def test_gemm_prefill_m2048_takes_two_mmas_per_weight_tile(backend, dtype, gflags):
+    """The prefill configuration with m = 2048, routed by m alone: enough tiles of twice the base height
+    (512 tokens for a pair, 256 for one SM) to fill the machine, so the variant whose dequantized weight
+    tile feeds two MMAs runs."""
     m, n, k = 2048, 8192, 2048
-    plan = matmul_plan(backend, dtype, m, n, k)
-    assert plan.kernel == capi.KERNEL_GEMM and plan.tile_rows == 256 and plan.k_splits == 1
+    plan = matmul_plan(backend, dtype, m, n, k, flags=gflags)
+    assert plan.kernel == capi.KERNEL_GEMM and plan.k_splits == 1
+    assert (plan.tile_rows, plan.cta_pairs) == ((512, 1) if gflags == capi.MATMUL_AUTO else (256, 0))
     a, b = make(dtype, m, n, k, seed=8)
-    got = run_matmul(backend, dtype, a, b, m, n, k)
+    got = run_matmul(backend, dtype, a, b, m, n, k, flags=gflags)
     want_i8 = oracle.fast_matmul_q(dtype, a, b, m, n, k).reshape(m, n)
     assert rel_l2(got, want_i8) <= TOL_INT8A
     # a slice of the f32-activation reference (the scalar oracle is slow at this size): rows from every tile row
@@ -99,14 +111,15 @@ def test_gemm_prefill_m2048_takes_256_token_tiles(backend, dtype):
 
 
 @pytest.mark.parametrize("dtype", [capi.DTYPE_Q4_0, capi.DTYPE_Q8_0])
-def test_gemm_256_token_tiles_ragged_alpha_beta_ldc(backend, dtype):
-    """256-token tiles with a ragged last tile row (m = 300 = 256 + 44), alpha / beta and a C wider than n."""
+@pytest.mark.parametrize("gflags", KERNELS)
+def test_gemm_two_mma_tiles_ragged_alpha_beta_ldc(backend, dtype, gflags):
+    """Two-MMA tiles with a ragged last tile row (m = 300 = 256 + 44), alpha / beta and a C wider than n."""
     m, n, k, ldc = 300, 38400, 256, 38400 + 8
-    plan = matmul_plan(backend, dtype, m, n, k, flags=capi.MATMUL_FORCE_GEMM)
-    assert plan.kernel == capi.KERNEL_GEMM and plan.tile_rows == 256
+    plan = matmul_plan(backend, dtype, m, n, k, flags=gflags)
+    assert plan.kernel == capi.KERNEL_GEMM and plan.tile_rows == (512 if gflags == PAIRS else 256)
     a, b = make(dtype, m, n, k, seed=9)
     c0 = np.random.default_rng(4).standard_normal(m * ldc).astype(np.float32)
-    got = run_matmul(backend, dtype, a, b, m, n, k, ldc=ldc, alpha=0.5, beta=-1.25, c=c0, flags=capi.MATMUL_FORCE_GEMM)
+    got = run_matmul(backend, dtype, a, b, m, n, k, ldc=ldc, alpha=0.5, beta=-1.25, c=c0, flags=gflags)
     c0m = c0.reshape(m, ldc)
     want_i8 = 0.5 * oracle.fast_matmul_q(dtype, a, b, m, n, k).reshape(m, n) - 1.25 * c0m[:, :n]
     assert rel_l2(got[:, :n], want_i8) <= TOL_INT8A
@@ -117,24 +130,38 @@ def test_gemm_256_token_tiles_ragged_alpha_beta_ldc(backend, dtype):
 
 
 @pytest.mark.parametrize("dtype", [capi.DTYPE_Q4_0, capi.DTYPE_Q8_0])
-@pytest.mark.parametrize("m,n,k", [(64, 256, 1536), (40, 1536, 2048), (512, 256, 1536), (130, 264, 8192)])
-def test_gemm_split_k_shapes(backend, dtype, m, n, k):
-    # few output tiles: K is split over CTAs and reduced in split order
+@pytest.mark.parametrize("m,n,k", [(64, 256, 1536), (40, 1536, 2048), (512, 256, 1536), (130, 264, 8192), (700, 520, 4096)])
+@pytest.mark.parametrize("gflags", KERNELS)
+def test_gemm_split_k_shapes(backend, dtype, m, n, k, gflags):
+    # few output tiles: K is split over CTAs (or pairs) and reduced in split order
     a, b = make(dtype, m, n, k, seed=21)
     c0 = np.random.default_rng(3).standard_normal(m * n).astype(np.float32)
-    got = run_matmul(backend, dtype, a, b, m, n, k, alpha=0.75, beta=0.5, c=c0, flags=capi.MATMUL_FORCE_GEMM)
+    if m > 128:
+        assert matmul_plan(backend, dtype, m, n, k, flags=gflags).k_splits > 1
+    got = run_matmul(backend, dtype, a, b, m, n, k, alpha=0.75, beta=0.5, c=c0, flags=gflags)
     want = oracle.fast_matmul_q(dtype, a, b, m, n, k, alpha=0.75, beta=0.5, c=c0.copy()).reshape(m, n)
     assert rel_l2(got, want) <= TOL_INT8A
-    again = run_matmul(backend, dtype, a, b, m, n, k, alpha=0.75, beta=0.5, c=c0, flags=capi.MATMUL_FORCE_GEMM)
+    again = run_matmul(backend, dtype, a, b, m, n, k, alpha=0.75, beta=0.5, c=c0, flags=gflags)
     assert np.array_equal(got, again)
 
 
-def test_gemm_is_deterministic(backend):
+@pytest.mark.parametrize("gflags", KERNELS)
+def test_gemm_is_deterministic(backend, gflags):
     m, n, k = 256, 1024, 512
     a, b = make(capi.DTYPE_Q4_0, m, n, k, seed=11)
-    x = run_matmul(backend, capi.DTYPE_Q4_0, a, b, m, n, k, flags=capi.MATMUL_FORCE_GEMM)
-    y = run_matmul(backend, capi.DTYPE_Q4_0, a, b, m, n, k, flags=capi.MATMUL_FORCE_GEMM)
+    x = run_matmul(backend, capi.DTYPE_Q4_0, a, b, m, n, k, flags=gflags)
+    y = run_matmul(backend, capi.DTYPE_Q4_0, a, b, m, n, k, flags=gflags)
     assert np.array_equal(x, y)
+
+
+def test_pairs_and_one_sm_kernels_agree(backend):
+    """The two kernels multiply the same bf16 operands and accumulate in f32: they differ only in the order
+    the tensor core adds, which the same K split keeps identical here."""
+    m, n, k = 640, 1024, 1024
+    a, b = make(capi.DTYPE_Q4_0, m, n, k, seed=12)
+    x = run_matmul(backend, capi.DTYPE_Q4_0, a, b, m, n, k, flags=PAIRS)
+    y = run_matmul(backend, capi.DTYPE_Q4_0, a, b, m, n, k, flags=ONE_SM)
+    assert rel_l2(x, y) < 1e-6
 
 
 @pytest.mark.parametrize("m", [17, 29, 32])

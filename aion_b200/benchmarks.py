@@ -524,6 +524,40 @@ def matmul_leg(torch, backend: CudaBackend, local_rank: int, dtype: int, nt: boo
     return out
 
 
+def gemv_cpu_baseline(dtype: int, nt: bool, m: int, n: int, k: int, threads: int, budget_s: float = 1.5) -> dict:
+    """The reference's CPU path for a decode matmul (threaded port), walking enough distinct weight copies
+    (random bytes with sane scales: the arithmetic does not care) that no cache holds them, for about `budget_s`."""
+    import oracle
+
+    bb = 18 if dtype == capi.DTYPE_Q4_0 else 34
+    wb = (k // 32) * n * bb
+    copies = int(max(2, min(64, (384 << 20) // wb + 1)))
+    rng = np.random.default_rng(99)
+    arena = rng.integers(0, 256, copies * wb, dtype=np.uint8)
+    blocks = arena.reshape(-1, bb)
+    blocks[:, 0] = rng.integers(0, 256, blocks.shape[0], dtype=np.uint8)
+    blocks[:, 1] = 0x1F   # f16 scales around 2^-8
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    c = np.zeros(m * n, dtype=np.float32)
+
+    def one(i):
+        w = arena[(i % copies) * wb:(i % copies + 1) * wb]
+        if nt:
+            oracle.fast_matmul_nt_q8(a, w, m, n, k, c=c, threads=threads)
+        else:
+            oracle.fast_matmul_q(dtype, a, w, m, n, k, c=c, threads=threads)
+
+    one(0)
+    t0, reps = time.perf_counter(), 0
+    while time.perf_counter() - t0 < budget_s:
+        one(reps)
+        reps += 1
+    dt = time.perf_counter() - t0
+    alg = wb + 4 * m * k + 4 * m * n
+    return {"value": round(alg * reps / dt / 1e9, 2), "unit": "GB/s", "cores": threads, "kind": "port",
+            "sample": f"{reps} launches over {copies} distinct weight copies"}
+
+
 def gemm_cpu_baseline(dtype: int, m: int, n: int, k: int, threads: int, sample_rows: int = 256, budget_s: float = 3.0) -> dict:
     """The reference's CPU path for the prefill GEMM (threaded port of its packed int8 GEMM) on a bounded
     sample: `sample_rows` of the m rows against the whole weight, repeated for about `budget_s`."""

@@ -49,7 +49,7 @@ METRIC = "q4 GEMV HBM GB/s"
 
 # DRAM bytes per launch of the GEMV kernel from an ncu capture of this workload
 # (dram__bytes_read.sum + dram__bytes_write.sum of one launch; summary under profiles/).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 9493248
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 9486336
 
 
 def measured_peak_gbs():
@@ -486,6 +486,14 @@ def run_other(args):
                     rows.append(benchmarks.gemm_leg(torch, backend, local_rank, dt, m, 8192, 2048))
             for m in (512, 2048):
                 rows.append(benchmarks.gemm_leg(torch, backend, local_rank, capi.DTYPE_Q8_0, m, 8192, 2048, nt=True))
+            if not args.skip_cpu_baseline:
+                threads = host_threads()
+                for r in rows:
+                    dt = capi.DTYPE_Q4_0 if r["dtype"] == "q4_0" else capi.DTYPE_Q8_0
+                    if "gbs_lanes" in r:
+                        r["cpu_baseline"] = benchmarks.gemv_cpu_baseline(dt, r["layout"].startswith("[N,K]"), r["m"], r["n"], r["k"], threads)
+                    elif r.get("step", "").startswith("MatMul ["):
+                        r["cpu_baseline"] = benchmarks.gemm_cpu_baseline(dt, r["m"], r["n"], r["k"], threads, budget_s=1.5)
             for r in rows:
                 print(json.dumps(r), flush=True)
             out = {"metric": "matmul sweep", "rows": len(rows)}

@@ -56,6 +56,10 @@ class MatMulPlan(C.Structure):
                 ("grid", C.c_uint32), ("cta_pairs", C.c_uint32), ("reserved", C.c_uint32 * 2)]
 
 
+class PeerFanout(C.Structure):
+    _fields_ = [("world", C.c_uint32), ("rank", C.c_uint32), ("c", Operand * 8), ("flags", Operand * 8), ("state", Operand)]
+
+
 class MatMulNT(C.Structure):
     _fields_ = [
         ("c", Operand), ("a", Operand), ("b", Operand),
@@ -192,6 +196,11 @@ SIGNATURES = {
     "aion_cuda_quantize": (C.c_int32, [_DEV, C.c_uint32, _OPP, C.POINTER(C.c_uint64), C.c_uint32, C.c_uint32, _OPP]),
     "aion_cuda_dequantize": (C.c_int32, [_DEV, C.c_uint32, _OPP, C.c_uint64, _OPP]),
     "aion_cuda_relayout_q8": (C.c_int32, [_DEV, C.c_uint32, C.c_uint32, C.c_uint64, C.c_uint64, _OPP, _OPP]),
+    "aion_cuda_matmul_peers": (C.c_int32, [_DEV, C.POINTER(MatMul), C.POINTER(PeerFanout)]),
+    "aion_cuda_peer_wait": (C.c_int32, [_DEV, _OPP, _OPP, C.c_uint32, C.c_uint32]),
+    "aion_cuda_ipc_export": (C.c_int32, [_DEV, C.c_uint64, C.POINTER(C.c_uint8 * 64)]),
+    "aion_cuda_ipc_import": (C.c_int32, [_DEV, C.POINTER(C.c_uint8 * 64), C.POINTER(C.c_uint64)]),
+    "aion_cuda_ipc_close": (C.c_int32, [_DEV, C.c_uint64]),
     "aion_cuda_derive_kmajor_q8": (C.c_int32, [_DEV, C.c_uint32, C.c_uint64, C.c_uint64, _OPP, _OPP]),
 }
 

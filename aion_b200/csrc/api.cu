@@ -3,6 +3,8 @@
 #include <cstdlib>
 
 #include "act_image.cuh"
+#include <cstring>
+
 #include "common.cuh"
 
 using namespace aion;
@@ -120,6 +122,75 @@ int32_t aion_cuda_matmul(AionCudaDevice* dev, const AionCudaMatMul* s) {
   if (empty) return AION_CUDA_OK;
   if (int32_t st = dev->make_current()) return st;
   return route(dev, g, s->flags, "matmul");
+}
+
+int32_t aion_cuda_matmul_peers(AionCudaDevice* dev, const AionCudaMatMul* s, const AionCudaPeerFanout* fan) {
+  if (!dev || !s || !fan) return fail(AION_CUDA_INVALID_ARGUMENT, "matmul_peers: null argument");
+  if (fan->world < 1 || fan->world > 8 || fan->rank >= fan->world)
+    return fail(AION_CUDA_INVALID_ARGUMENT, "matmul_peers: rank %u of %u (at most 8 ranks)", fan->rank, fan->world);
+  MatMulArgs g{};
+  bool empty = false;
+  if (int32_t st = matmul_args(s, &g, &empty)) return st;
+  if (empty) return fail(AION_CUDA_INVALID_ARGUMENT, "matmul_peers: an empty matmul has nothing to announce");
+  if (g.m > 32) return fail(AION_CUDA_UNSUPPORTED, "matmul_peers: m = %llu (the fan-out is part of the int8 kernel, m <= 32)", (unsigned long long)g.m);
+  PeerFanout pf{};
+  pf.world = fan->world;
+  pf.rank = fan->rank;
+  const uint64_t c_bytes = ((g.m - 1) * g.ldc + g.n) * sizeof(float);
+  for (uint32_t r = 0; r < fan->world; r++) {
+    if (int32_t st = resolve(fan->flags[r], 8 * sizeof(uint32_t), "matmul_peers.flags", &pf.flags[r])) return st;
+    if (r == fan->rank) continue;
+    if (int32_t st = resolve(fan->c[r], c_bytes, "matmul_peers.c", &pf.c[pf.count])) return st;
+    if (reinterpret_cast<uintptr_t>(pf.c[pf.count]) & 7) return fail(AION_CUDA_INVALID_ARGUMENT, "matmul_peers.c: 8-byte alignment");
+    pf.count++;
+  }
+  if (int32_t st = resolve(fan->state, 2 * sizeof(uint32_t), "matmul_peers.state", &pf.state)) return st;
+  g.peers = &pf;
+  if (int32_t st = dev->make_current()) return st;
+  const int32_t st = gemv_mma(dev, g, false);
+  if (st == AION_CUDA_UNSUPPORTED) return fail(AION_CUDA_UNSUPPORTED, "matmul_peers: this shape or alignment is outside the tiled int8 kernel");
+  return st;
+}
+
+int32_t aion_cuda_peer_wait(AionCudaDevice* dev, const AionCudaOperand* flags, const AionCudaOperand* state, uint32_t world,
+                            uint32_t poll_limit) {
+  if (!dev || !flags || !state) return fail(AION_CUDA_INVALID_ARGUMENT, "peer_wait: null argument");
+  if (world < 1 || world > 8) return fail(AION_CUDA_INVALID_ARGUMENT, "peer_wait: %u ranks", world);
+  const uint32_t* f;
+  uint32_t* st_ptr;
+  if (int32_t st = resolve(*flags, 8 * sizeof(uint32_t), "peer_wait.flags", &f)) return st;
+  if (int32_t st = resolve(*state, 2 * sizeof(uint32_t), "peer_wait.state", &st_ptr)) return st;
+  if (int32_t st = dev->make_current()) return st;
+  return peer_wait_launch(dev, f, st_ptr, world, poll_limit ? poll_limit : (1u << 23));
+}
+
+int32_t aion_cuda_ipc_export(AionCudaDevice* dev, uint64_t handle, uint8_t out[64]) {
+  if (!dev || !handle || !out) return fail(AION_CUDA_INVALID_ARGUMENT, "ipc_export: null argument");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  if (int32_t st = dev->make_current()) return st;
+  cudaIpcMemHandle_t h;
+  AION_CUDA_TRY(cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(static_cast<uintptr_t>(handle))));
+  memcpy(out, &h, 64);
+  return AION_CUDA_OK;
+}
+
+int32_t aion_cuda_ipc_import(AionCudaDevice* dev, const uint8_t in[64], uint64_t* handle) {
+  if (!dev || !in || !handle) return fail(AION_CUDA_INVALID_ARGUMENT, "ipc_import: null argument");
+  if (int32_t st = dev->make_current()) return st;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, in, 64);
+  void* p = nullptr;
+  AION_CUDA_TRY(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+  *handle = static_cast<uint64_t>(reinterpret_cast<uintptr_t>(p));
+  return AION_CUDA_OK;
+}
+
+int32_t aion_cuda_ipc_close(AionCudaDevice* dev, uint64_t handle) {
+  if (!dev || !handle) return fail(AION_CUDA_INVALID_ARGUMENT, "ipc_close: null argument");
+  if (int32_t st = dev->make_current()) return st;
+  AION_CUDA_TRY(cudaStreamSynchronize(dev->stream));
+  AION_CUDA_TRY(cudaIpcCloseMemHandle(reinterpret_cast<void*>(static_cast<uintptr_t>(handle))));
+  return AION_CUDA_OK;
 }
 
 int32_t aion_cuda_matmul_plan(AionCudaDevice* dev, const AionCudaMatMul* s, AionCudaMatMulPlan* out) {

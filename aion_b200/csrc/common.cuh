@@ -185,6 +185,16 @@ inline cudaError_t launch_pdl_main(void (*kernel)(KArgs...), dim3 grid, dim3 blo
 int32_t quantize_activation_rows(AionCudaDevice* dev, const float* a, uint64_t m, uint64_t k, uint64_t lda,
                                  int8_t* aq, float* ascale);
 
+// Column-split layers over several GPUs of a node: where a matmul also stores its outputs, and whom
+// it tells when they have landed (aion_cuda_matmul_peers).
+struct PeerFanout {
+  float* c[7];          // C of the other ranks, laid out like this rank's
+  uint32_t* flags[8];   // arrival words [8] of every rank, this one included
+  uint32_t* state;      // this rank's: [0] epoch, [1] CTAs done
+  uint32_t count;       // entries of c
+  uint32_t world, rank;
+};
+
 struct MatMulArgs {
   const float* a;
   const uint8_t* b;
@@ -198,6 +208,7 @@ struct MatMulArgs {
   // the int8 matmul then reads it instead of quantizing A itself.
   const uint8_t* a_image = nullptr;
   bool one_sm = false;   // keep the prefill GEMM on its one-SM kernel (no CTA pairs)
+  const PeerFanout* peers = nullptr;   // int8 kernel only
 };
 int32_t matmul_generic(AionCudaDevice* dev, const MatMulArgs& g);
 // Returns AION_CUDA_UNSUPPORTED (without setting an error) when the shape or the
@@ -217,5 +228,6 @@ struct GemmPlan {
 };
 bool gemm_tcgen05_plan(const AionCudaDevice* dev, const MatMulArgs& g, GemmPlan* out);
 int32_t attention_launch(AionCudaDevice* dev, const AionCudaAttention* s);
+int32_t peer_wait_launch(AionCudaDevice* dev, const uint32_t* flags, uint32_t* state, uint32_t world, uint32_t poll_limit);
 
 }  // namespace aion

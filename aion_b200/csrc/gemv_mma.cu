@@ -76,6 +76,9 @@ struct GemvParams {
   uint32_t act_image_bytes;
   uint32_t wait_limit;   // polls a barrier wait makes before it gives up and reports FAULT_WAIT_EXPIRED
   uint32_t drop_first;   // test hook: every CTA leaves out its first weight copy, so that wait runs out
+  // Column-split layers over several GPUs (PeerFanout): every output value is also stored into the C
+  // of the other ranks, and the last CTA to finish tells every rank that this rank's columns have landed.
+  PeerFanout peers;
 };
 
 // CG: groups of 16 columns per consumer warp (1: 64-column tiles, 2: 128-column tiles).
@@ -641,10 +644,20 @@ __global__ void __launch_bounds__(threads_of(RW), min_ctas_per_sm(MT, CG, RW)) g
               const float va = v[t][c][rr], vb = v[t][c][2 + rr];
               if (!NT && p.c_vec2 && p.beta == 0.0f && cb < p.n) {
                 // K-major tiles: the lane's two columns are neighbours, the first one even.
-                *reinterpret_cast<float2*>(row + ca) = make_float2(p.alpha * va, p.alpha * vb);
+                const float2 o = make_float2(p.alpha * va, p.alpha * vb);
+                *reinterpret_cast<float2*>(row + ca) = o;
+                for (uint32_t q = 0; q < p.peers.count; q++) *reinterpret_cast<float2*>(p.peers.c[q] + (uint64_t)mrow * p.ldc + ca) = o;
               } else {
-                if (ca < p.n) row[ca] = (p.beta == 0.0f) ? p.alpha * va : p.alpha * va + p.beta * row[ca];
-                if (cb < p.n) row[cb] = (p.beta == 0.0f) ? p.alpha * vb : p.alpha * vb + p.beta * row[cb];
+                if (ca < p.n) {
+                  const float o = (p.beta == 0.0f) ? p.alpha * va : p.alpha * va + p.beta * row[ca];
+                  row[ca] = o;
+                  for (uint32_t q = 0; q < p.peers.count; q++) p.peers.c[q][(uint64_t)mrow * p.ldc + ca] = o;
+                }
+                if (cb < p.n) {
+                  const float o = (p.beta == 0.0f) ? p.alpha * vb : p.alpha * vb + p.beta * row[cb];
+                  row[cb] = o;
+                  for (uint32_t q = 0; q < p.peers.count; q++) p.peers.c[q][(uint64_t)mrow * p.ldc + cb] = o;
+                }
               }
             }
       }
@@ -653,6 +666,50 @@ __global__ void __launch_bounds__(threads_of(RW), min_ctas_per_sm(MT, CG, RW)) g
       s = 0;
       tile++;
     }
+  }
+  if (p.peers.world > 1) {
+    // Every output of this CTA is stored, here and on the peers. The last CTA of the grid to get here
+    // publishes the arrival: flags[this rank] = epoch + 1 in every rank's flag array (the epoch is
+    // advanced by the wait kernel that follows in the stream). Stores, system-scope fence, counter;
+    // the last CTA's fence after the counter orders every CTA's stores before its flag stores.
+    __threadfence_system();
+    asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_THREADS) : "memory");
+    if (tid == 0) {
+      const uint32_t prev = atomicAdd(p.peers.state + 1, 1u);
+      if (prev == gridDim.x - 1) {
+        __threadfence_system();
+        p.peers.state[1] = 0;   // ready for the next launch
+        const uint32_t next = *reinterpret_cast<volatile uint32_t*>(p.peers.state) + 1;
+        for (uint32_t r = 0; r < p.peers.world; r++)
+          asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.peers.flags[r] + p.peers.rank), "r"(next) : "memory");
+      }
+    }
+  }
+}
+
+// Waits (bounded) until every rank's arrival word has reached epoch + 1, then advances the epoch.
+// One warp; lane r watches rank r. A wait that runs out reports FAULT_WAIT_EXPIRED and leaves the
+// epoch where it was.
+__global__ void peer_wait_kernel(const uint32_t* flags, uint32_t* state, uint32_t world, uint32_t poll_limit, int* fault) {
+  const uint32_t lane = threadIdx.x;
+  const uint32_t want = *reinterpret_cast<volatile uint32_t*>(state) + 1;
+  bool ok = true;
+  if (lane < world) {
+    ok = false;
+    for (uint32_t i = 0; i < poll_limit; i++) {
+      uint32_t v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + lane) : "memory");
+      if ((int32_t)(v - want) >= 0) {
+        ok = true;
+        break;
+      }
+      __nanosleep(64);
+    }
+  }
+  const bool all = __all_sync(0xFFFFFFFFu, ok);
+  if (lane == 0) {
+    if (all) *state = want;
+    else atomicCAS(fault, FAULT_NONE, FAULT_WAIT_EXPIRED);
   }
 }
 
@@ -859,6 +916,7 @@ int32_t gemv_mma(AionCudaDevice* dev, const MatMulArgs& g, bool probe_only) {
   const uint8_t* image = (g.a_image && act_image_layout(g.m, kblocks).kind == ACT_IMAGE_INT8) ? g.a_image : nullptr;
   uint64_t kb_max = (ACT_BUDGET_BYTES / 72) / KBT * KBT;
   if (g.m >= 2 || kblocks > 96 || image) kb_max = (kblocks + KBT - 1) / KBT * KBT;
+  if (g.peers && kblocks > kb_max) return AION_CUDA_UNSUPPORTED;   // the fan-out belongs to a single launch
 
   for (uint64_t kb0 = 0; kb0 < kblocks; kb0 += kb_max) {
     const uint64_t nkb = kblocks - kb0 < kb_max ? kblocks - kb0 : kb_max;
@@ -882,6 +940,7 @@ int32_t gemv_mma(AionCudaDevice* dev, const MatMulArgs& g, bool probe_only) {
     p.fault = dev->fault_dev;
     p.wait_limit = dev->debug_expire_waits ? (1u << 8) : (1u << 20);
     p.drop_first = dev->debug_expire_waits ? 1u : 0u;
+    if (g.peers) p.peers = *g.peers;
     p.a_vec4 = (g.a && (reinterpret_cast<uintptr_t>(p.a) & 15) == 0 && g.lda % 4 == 0) ? 1u : 0u;
     p.c_vec2 = ((reinterpret_cast<uintptr_t>(p.c) & 7) == 0 && g.ldc % 2 == 0) ? 1u : 0u;
     int32_t st;
@@ -894,6 +953,12 @@ int32_t gemv_mma(AionCudaDevice* dev, const MatMulArgs& g, bool probe_only) {
     }
     if (st != AION_CUDA_OK) return st;
   }
+  return AION_CUDA_OK;
+}
+
+int32_t peer_wait_launch(AionCudaDevice* dev, const uint32_t* flags, uint32_t* state, uint32_t world, uint32_t poll_limit) {
+  peer_wait_kernel<<<1, 32, 0, dev->stream>>>(flags, state, world, poll_limit, dev->fault_dev);
+  AION_CUDA_TRY(cudaGetLastError());
   return AION_CUDA_OK;
 }
 

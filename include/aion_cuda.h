@@ -496,6 +496,38 @@ AION_CUDA_API int32_t aion_cuda_dequantize(AionCudaDevice* dev, uint32_t dtype, 
  * which creates the derived tensor directly on the device (:270-275). */
 AION_CUDA_API int32_t aion_cuda_relayout_q8(AionCudaDevice* dev, uint32_t order, uint32_t inverse, uint64_t n,
                                             uint64_t k, const AionCudaOperand* src, const AionCudaOperand* dst);
+/* ---------------------------------------------------------------------------------
+ * Column-split layers over the GPUs of one node (one process per GPU). No counterpart in
+ * the reference, which runs on one device. Rank r holds the columns [n0_r, n1_r) of a K-major
+ * weight and computes y[:, n0_r:n1_r]; with a fan-out the int8 matmul kernel (m <= 32) stores
+ * every output value into the C of every other rank as well (plain peer stores over NVLink from
+ * the kernel's epilogue) and, when its last CTA is done, writes its arrival into every rank's
+ * flag array. aion_cuda_peer_wait, next in the stream, waits (bounded) until all ranks have
+ * arrived: y is then complete on this GPU without a collective call.
+ *   Buffers another rank writes (C, flags) come from aion_cuda_alloc, are exported with
+ *   aion_cuda_ipc_export, and opened in the other processes with aion_cuda_ipc_import.
+ *   flags: u32[8] per rank, zero-filled once; state: u32[2] per rank (epoch, CTA counter),
+ *   zero-filled once. Every rank must run the same sequence of fan-out matmuls and waits.
+ *   A rank may run one step ahead of a peer, so consecutive steps alternate between two C
+ *   buffers (a peer still reading step s is never overwritten by step s + 1).
+ *   A wait that runs out (a rank that never arrives) is reported by the next
+ *   aion_cuda_sync / aion_cuda_d2h as EXECUTION_FAILED; the device stays usable.
+ * --------------------------------------------------------------------------------- */
+typedef struct AionCudaPeerFanout {
+  uint32_t world, rank;
+  AionCudaOperand c[8];     /* C of every rank, laid out like the step's own c (entry `rank` is ignored) */
+  AionCudaOperand flags[8]; /* u32[8] arrival words of every rank (entry `rank`: this rank's own) */
+  AionCudaOperand state;    /* this rank's u32[2] */
+} AionCudaPeerFanout;
+AION_CUDA_API int32_t aion_cuda_matmul_peers(AionCudaDevice* dev, const AionCudaMatMul* step, const AionCudaPeerFanout* fan);
+/* poll_limit: polls (about 0.1 us apart) before the wait gives up; 0 = the default (about a second). */
+AION_CUDA_API int32_t aion_cuda_peer_wait(AionCudaDevice* dev, const AionCudaOperand* flags, const AionCudaOperand* state,
+                                          uint32_t world, uint32_t poll_limit);
+/* 64 opaque bytes that name an aion_cuda_alloc allocation to the other processes of the node, and back. */
+AION_CUDA_API int32_t aion_cuda_ipc_export(AionCudaDevice* dev, uint64_t handle, uint8_t out[64]);
+AION_CUDA_API int32_t aion_cuda_ipc_import(AionCudaDevice* dev, const uint8_t in[64], uint64_t* handle);
+AION_CUDA_API int32_t aion_cuda_ipc_close(AionCudaDevice* dev, uint64_t handle);
+
 /* The derived weight of this backend: a q8_0 [n,k] tensor in `order` re-laid as K-major
  * [k/32][n] blocks, the layout `aion_cuda_matmul` streams. Both layouts quantize along K, so
  * this is a permutation of 34-byte blocks and C = A . B^T of the `MatMulNT` step equals

@@ -32,7 +32,8 @@ STRUCTS = {"AionCudaOperand": capi.Operand, "AionCudaDeviceInfo": capi.DeviceInf
            "AionCudaMatMulPlan": capi.MatMulPlan, "AionCudaMatMulNT": capi.MatMulNT, "AionCudaAttention": capi.Attention,
            "AionCudaRMSNorm": capi.RMSNorm, "AionCudaElemwise": capi.Elemwise, "AionCudaRoPE": capi.RoPE,
            "AionCudaCast": capi.Cast, "AionCudaSequenceAppend": capi.SequenceAppend, "AionCudaGatherRows": capi.GatherRows,
-           "AionCudaArgMax": capi.ArgMax, "AionCudaRMSNormPair": capi.RMSNormPair, "AionCudaRopeKVAppend": capi.RopeKVAppend}
+           "AionCudaArgMax": capi.ArgMax, "AionCudaRMSNormPair": capi.RMSNormPair, "AionCudaRopeKVAppend": capi.RopeKVAppend,
+           "AionCudaPeerFanout": capi.PeerFanout}
 
 
 def test_struct_layouts_match_the_header(tmp_path):

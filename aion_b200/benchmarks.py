@@ -443,14 +443,108 @@ def colsplit_leg(torch, dist, backend: CudaBackend, rank: int, world: int, local
     backend.sync()
     torch.cuda.synchronize()
     ms = _max_over_ranks(torch, dist, world, ev0.elapsed_time(ev1)) / iters
+    total_w = (k // 32) * n * 18
+    out = {"m": m, "n": n, "k": k, "n_gpus": world, "columns_per_gpu": n_loc, "ms": round(ms, 4),
+           "aggregate_weight_gbs": round(total_w / (ms * 1e-3) / 1e9, 1),
+           "all_gather_bytes_per_rank": m * n_loc * 4,
+           "parity": {"against": "the unsplit matmul over the full weight on one GPU, every rank checks the gathered y",
+                      "max_abs_diff": max_abs, "rel_l2": rel, "pass": bool(rel <= 2e-5)}}
+    if world > 1 and m <= 32:
+        out["peer_stores"] = _colsplit_peer_stores(torch, dist, backend, rank, world, local_rank, m, n, k, n0, n1, hw, nb, xd, y_full, iters)
     mem.free(hw)
     mem.free(h_full)
+    return out
+
+
+def _colsplit_peer_stores(torch, dist, backend, rank, world, local_rank, m, n, k, n0, n1, hw, nb, xd, y_full, iters) -> dict:
+    """The same layer with the exchange inside the matmul kernel: every rank's kernel stores its columns into
+    every rank's y [m, n] over NVLink (peer stores from the epilogue) and announces them; a bounded wait kernel
+    then finds y complete. Two y buffers alternate, since a rank may run one step ahead of a peer. One recorded
+    program = two steps."""
+    lib, dev, mem = backend._lib, backend.handle, backend.device_memory
+    y_bytes = m * n * 4
+    mine = {"y0": mem.alloc(y_bytes, 256), "y1": mem.alloc(y_bytes, 256), "flags": mem.alloc(32, 256), "state": mem.alloc(8, 256)}
+    for h, nbytes in ((mine["y0"], y_bytes), (mine["y1"], y_bytes), (mine["flags"], 32), (mine["state"], 8)):
+        mem.memset(h, 0, 0, nbytes)
+    backend.sync()
+    exported = {}
+    for name, h in mine.items():
+        buf = (C.c_uint8 * 64)()
+        _chk(lib.aion_cuda_ipc_export(dev, h, C.byref(buf)))
+        exported[name] = bytes(buf)
+    everyone = [None] * world
+    dist.all_gather_object(everyone, exported)
+    peers = []   # per rank: name -> handle valid in this process
+    for r in range(world):
+        if r == rank:
+            peers.append(dict(mine))
+            continue
+        opened = {}
+        for name in ("y0", "y1", "flags"):
+            buf = (C.c_uint8 * 64).from_buffer_copy(everyone[r][name])
+            h = C.c_uint64()
+            _chk(lib.aion_cuda_ipc_import(dev, C.byref(buf), C.byref(h)))
+            opened[name] = h.value
+        peers.append(opened)
+    n_loc = n1 - n0
+
+    def fan_out(parity):
+        key = "y1" if parity else "y0"
+        c_of = lambda r: capi.Operand(peers[r][key], n0 * 4, y_bytes - n0 * 4)
+        rec = capi.MatMul(c=c_of(rank), a=capi.Operand(xd.data_ptr(), 0, xd.numel() * 4), b=capi.Operand(hw, 0, nb),
+                          b_dtype=capi.DTYPE_Q4_0, flags=capi.MATMUL_AUTO, m=m, n=n_loc, k=k, lda=0, ldb=0, ldc=n, alpha=1.0, beta=0.0)
+        fan = capi.PeerFanout(world=world, rank=rank, state=capi.Operand(mine["state"], 0, 8))
+        for r in range(world):
+            fan.c[r] = c_of(r)
+            fan.flags[r] = capi.Operand(peers[r]["flags"], 0, 32)
+        _chk(lib.aion_cuda_matmul_peers(dev, C.byref(rec), C.byref(fan)))
+        fl, st = capi.Operand(mine["flags"], 0, 32), capi.Operand(mine["state"], 0, 8)
+        _chk(lib.aion_cuda_peer_wait(dev, C.byref(fl), C.byref(st), world, 0))
+
+    dist.barrier()   # every rank's buffers are zeroed and opened everywhere before the first store
+    fan_out(0)
+    fan_out(1)
+    backend.sync()
+    got = [np.empty(m * n, np.float32), np.empty(m * n, np.float32)]
+    mem.copy_d2h(got[0], mine["y0"], 0)
+    mem.copy_d2h(got[1], mine["y1"], 0)
+    want = y_full.cpu().numpy().reshape(-1).astype(np.float64)
+    rel = max(float(np.linalg.norm(g.astype(np.float64) - want) / max(np.linalg.norm(want), 1e-30)) for g in got)
+    worst = torch.tensor([rel], device="cuda", dtype=torch.float64)
+    dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+    rel = float(worst[0].item())
+    _chk(lib.aion_cuda_record_begin(dev))
+    fan_out(0)
+    fan_out(1)
+    prog = C.c_void_p()
+    _chk(lib.aion_cuda_record_end(dev, C.byref(prog)))
+    for _ in range(3):
+        _chk(lib.aion_cuda_program_launch(dev, prog))
+    backend.sync()
+    dist.barrier()
+    stream, ev0, ev1 = _events(torch, backend, local_rank)
+    ev0.record(stream)
+    for _ in range(iters):
+        _chk(lib.aion_cuda_program_launch(dev, prog))
+    ev1.record(stream)
+    backend.sync()
+    torch.cuda.synchronize()
+    ms = _max_over_ranks(torch, dist, world, ev0.elapsed_time(ev1)) / (2 * iters)
+    lib.aion_cuda_program_destroy(dev, prog)
+    dist.barrier()   # nobody closes a mapping another rank may still store into
+    for r in range(world):
+        if r != rank:
+            for h in peers[r].values():
+                _chk(lib.aion_cuda_ipc_close(dev, h))
+    dist.barrier()
+    for h in mine.values():
+        mem.free(h)
     total_w = (k // 32) * n * 18
-    return {"m": m, "n": n, "k": k, "n_gpus": world, "columns_per_gpu": n_loc, "ms": round(ms, 4),
-            "aggregate_weight_gbs": round(total_w / (ms * 1e-3) / 1e9, 1),
-            "all_gather_bytes_per_rank": m * n_loc * 4,
-            "parity": {"against": "the unsplit matmul over the full weight on one GPU, every rank checks the gathered y",
-                       "max_abs_diff": max_abs, "rel_l2": rel, "pass": bool(rel <= 2e-5)}}
+    return {"ms": round(ms, 4), "aggregate_weight_gbs": round(total_w / (ms * 1e-3) / 1e9, 1),
+            "exchange": "peer stores from the matmul kernel's epilogue into every rank's y + arrival words + one bounded wait kernel",
+            "peer_bytes_per_rank": m * n_loc * 4 * (world - 1),
+            "parity": {"against": "the unsplit matmul over the full weight on this GPU, both y buffers, worst rank", "rel_l2": rel,
+                       "pass": bool(rel <= 2e-5)}}
 
 
 def matmul_leg(torch, backend: CudaBackend, local_rank: int, dtype: int, nt: bool, m: int, n: int, k: int, lanes: int = 8,

@@ -690,7 +690,12 @@ __global__ void __launch_bounds__(threads_of(RW), min_ctas_per_sm(MT, CG, RW)) g
 // Waits (bounded) until every rank's arrival word has reached epoch + 1, then advances the epoch.
 // One warp; lane r watches rank r. A wait that runs out reports FAULT_WAIT_EXPIRED and leaves the
 // epoch where it was.
+// Launched with programmatic stream serialization and without a wait for its predecessor: it may start
+// while the matmul that announces this rank's own columns is still running (that matmul does not depend on
+// it, and all of its CTAs have started by then), so the launch is off the critical path. The kernel after
+// it waits for its completion as usual, which is what keeps the epoch read by the next matmul current.
 __global__ void peer_wait_kernel(const uint32_t* flags, uint32_t* state, uint32_t world, uint32_t poll_limit, int* fault) {
+  ptx::pdl_launch_dependents();
   const uint32_t lane = threadIdx.x;
   const uint32_t want = *reinterpret_cast<volatile uint32_t*>(state) + 1;
   bool ok = true;
@@ -957,8 +962,7 @@ int32_t gemv_mma(AionCudaDevice* dev, const MatMulArgs& g, bool probe_only) {
 }
 
 int32_t peer_wait_launch(AionCudaDevice* dev, const uint32_t* flags, uint32_t* state, uint32_t world, uint32_t poll_limit) {
-  peer_wait_kernel<<<1, 32, 0, dev->stream>>>(flags, state, world, poll_limit, dev->fault_dev);
-  AION_CUDA_TRY(cudaGetLastError());
+  AION_CUDA_TRY(launch_pdl_main(peer_wait_kernel, dim3(1), dim3(32), 0, dev->stream, flags, state, world, poll_limit, dev->fault_dev));
   return AION_CUDA_OK;
 }
 

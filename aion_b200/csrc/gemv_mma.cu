@@ -670,11 +670,12 @@ __global__ void __launch_bounds__(threads_of(RW), min_ctas_per_sm(MT, CG, RW)) g
   if (p.peers.world > 1) {
     // Every output of this CTA is stored, here and on the peers. The last CTA of the grid to get here
     // publishes the arrival: flags[this rank] = epoch + 1 in every rank's flag array (the epoch is
-    // advanced by the wait kernel that follows in the stream). Stores, system-scope fence, counter;
+    // advanced by the wait kernel that follows in the stream). The CTA barrier orders every thread's
+    // stores before thread 0's system-scope fence (fences are cumulative), the fence before the counter;
     // the last CTA's fence after the counter orders every CTA's stores before its flag stores.
-    __threadfence_system();
     asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_THREADS) : "memory");
     if (tid == 0) {
+      __threadfence_system();
       const uint32_t prev = atomicAdd(p.peers.state + 1, 1u);
       if (prev == gridDim.x - 1) {
         __threadfence_system();

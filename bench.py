@@ -12,7 +12,7 @@ program of 256 `aion_cuda_matmul` steps = one pass over the batch.
 
 Metric: GB/s of algorithmic bytes (weights once + x + y per launch) — higher is better.
   value  : inputs resident in HBM, device-timed (CUDA events on the launching stream).
-  e2e    : the same pass driven through the C ABI from HOST buffers (two sessions on two host
+  e2e    : the same pass driven through the C ABI from HOST buffers (four sessions on four host
            threads, so one session's copies overlap the other's kernels): per step one
            aion_cuda_h2d of the batch's activations (pinned), the program, one
            aion_cuda_d2h of the results.
@@ -250,8 +250,8 @@ def run_ours(args):
     h2d_bytes = x_host.numel() * 4
     d2h_bytes = y_host.numel() * 4
 
-    # Two sessions (two device objects, each with its own stream, activation / result buffers
-    # and recorded program over the shared weights) driven by two host threads, the way a
+    # Several sessions (device objects, each with its own stream, activation / result buffers
+    # and recorded program over the shared weights) driven by one host thread each, the way a
     # server overlaps requests: one session's copies run under the other's kernels. Every step
     # of either session is h2d of its inputs, the program, d2h of its results.
     class E2ESession:
@@ -266,7 +266,7 @@ def run_ours(args):
             chk(lb.aion_cuda_d2h(dv, C.c_void_p(self.y.data_ptr()), self.yd, 0, d2h_bytes))
 
     sessions = [E2ESession(backend, x_dev, y_dev, prog, False)]
-    if args.e2e_sessions > 1:
+    for _extra in range(args.e2e_sessions - 1):
         be2 = CudaBackend(local_rank)
         x2 = be2.device_memory.alloc(COPIES * M * K * 4, 256)
         y2 = be2.device_memory.alloc(COPIES * M * N * 4, 256)
@@ -312,15 +312,13 @@ def run_ours(args):
     e2e_s = time.perf_counter() - t0
     if errors:
         raise errors[0]
-    if len(sessions) > 1:
-        same = bool(torch.equal(sessions[1].y, y_host))
-        sn = sessions[1]
+    same = True
+    for sn in sessions[1:]:
+        same = same and bool(torch.equal(sn.y, y_host))
         sn.be._lib.aion_cuda_program_destroy(sn.be.handle, sn.pg)
         sn.be.device_memory.free(sn.xd)
         sn.be.device_memory.free(sn.yd)
         sn.be.deinit()
-    else:
-        same = True
     if world > 1:
         t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -590,7 +588,7 @@ def main():
     ap.add_argument("--no-sustained", action="store_true", help="gemv workload: leave out the two-second run of the same pass")
     ap.add_argument("--no-extra-legs", action="store_true",
                     help="gemv workload: leave out the prefill GEMM / attention legs (1 GPU) and the column-split leg (several GPUs)")
-    ap.add_argument("--e2e-sessions", type=int, default=2, choices=[1, 2],
+    ap.add_argument("--e2e-sessions", type=int, default=4, choices=[1, 2, 3, 4],
                     help="sessions (device objects + host threads) the end-to-end leg drives concurrently")
     ap.add_argument("--decode-requests", type=int, default=512, help="concurrent requests in total, split over the GPUs")
     ap.add_argument("--decode-steps", type=int, default=20)

@@ -69,6 +69,8 @@ struct AttnParams {
   uint8_t* image;
   ActImageLayout image_layout;
   uint32_t image_dtype;
+  uint32_t wait_limit;   // polls a barrier wait makes before it gives up and reports FAULT_WAIT_EXPIRED
+  uint32_t drop_first;   // test hook: every CTA leaves out the copies of its first stage, so that wait runs out
 };
 
 struct KeyRange {
@@ -288,7 +290,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParam
     for (uint32_t it = 0; it < ntiles; it++) {
       const uint32_t slot = it % NS;
       if (*abort_flag) break;
-      if (it >= (uint32_t)NS && !ptx::mbar_wait_bounded(bar_empty + 8 * slot, ((it / NS) - 1) & 1)) {
+      if (it >= (uint32_t)NS && !ptx::mbar_wait_bounded(bar_empty + 8 * slot, ((it / NS) - 1) & 1, p.wait_limit)) {
         if (lane == 0) {
           atomicExch(p.fault, FAULT_WAIT_EXPIRED);
           *abort_flag = 1;
@@ -304,6 +306,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParam
         // rows or zeros past the tensor) and are cleared by the consumers before use.
         if (lane == 0) {
           ptx::mbar_arrive_expect_tx(full, 2u * KT * D * 2);
+          if (p.drop_first && it == 0) continue;   // (test hook: the bytes never arrive, the consumers' wait runs out)
           int32_t y;
           if (p.page_tokens) {
             // t0 is a multiple of a stage and a page is a whole number of stages.
@@ -332,7 +335,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParam
     }
     if (*abort_flag)
       for (uint32_t it = issued > (uint32_t)NS ? issued - NS : 0; it < issued; it++)
-        ptx::mbar_wait_bounded(bar_full + 8 * (it % NS), (it / NS) & 1, 1u << 16);
+        ptx::mbar_wait_bounded(bar_full + 8 * (it % NS), (it / NS) & 1, min(p.wait_limit, 1u << 16));
   } else {
     // ---------------- consumers ----------------
     // Q^T fragments: for tile n and k-step s, lane (g, j) needs (q[column g][16s+2j], q[..][16s+2j+1])
@@ -381,7 +384,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParam
     bool ok = true;
     for (uint32_t it = 0; it < ntiles; it++) {
       const uint32_t slot = it % NS;
-      if (ok && (*abort_flag || !ptx::mbar_wait_bounded(bar_full + 8 * slot, (it / NS) & 1))) {
+      if (ok && (*abort_flag || !ptx::mbar_wait_bounded(bar_full + 8 * slot, (it / NS) & 1, p.wait_limit))) {
         if (lane == 0 && !*abort_flag) {
           atomicExch(p.fault, FAULT_WAIT_EXPIRED);
           *abort_flag = 1;
@@ -555,7 +558,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParam
       if (direct) {
         float4 r = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         if (lsum > 0.0f && isfinite(lsum)) r = make_float4(o.x / lsum, o.y / lsum, o.z / lsum, o.w / lsum);
-        else if (on && col_hi[col] > col_lo[col] && !bad && !*abort_flag) atomicExch(p.fault, FAULT_NONFINITE);
+        else if (on && col_hi[col] > col_lo[col] && !bad && !*abort_flag) atomicCAS(p.fault, FAULT_NONE, FAULT_NONFINITE);
         if (on) *reinterpret_cast<float4*>(p.out + (uint64_t)row * D + 4 * d4) = r;
         if (p.image) {
           const uint32_t out_row = on ? row / p.Hq : 0, col4 = on ? (row % p.Hq) * (D / 4) + d4 : 0;
@@ -658,7 +661,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParam
             const float lsum = lsums[col];
             float4 r = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             if (lsum > 0.0f && isfinite(lsum)) r = make_float4(o[c].x / lsum, o[c].y / lsum, o[c].z / lsum, o[c].w / lsum);
-            else if (live[c] && col_hi[col] > col_lo[col] && !bad) atomicExch(p.fault, FAULT_NONFINITE);
+            else if (live[c] && col_hi[col] > col_lo[col] && !bad) atomicCAS(p.fault, FAULT_NONE, FAULT_NONFINITE);
             if (live[c]) *reinterpret_cast<float4*>(p.out + (uint64_t)row * D + 4 * d4) = r;
             if (p.image) {
               const uint32_t out_row = live[c] ? row / p.Hq : 0, col4 = live[c] ? (row % p.Hq) * (D / 4) + d4 : 0;
@@ -744,7 +747,7 @@ __global__ void __launch_bounds__(GEN_WARPS * 32) attn_generic_kernel(const Attn
     lsum += (mw == -INFINITY) ? 0.0f : base[(size_t)w * (p.Dv + 2) + p.Dv + 1] * exp2f(mw - M);
   }
   const bool good = lsum > 0.0f && isfinite(lsum);
-  if (!good && kr.hi > kr.lo && !kr.bad && tid == 0) atomicExch(p.fault, FAULT_NONFINITE);
+  if (!good && kr.hi > kr.lo && !kr.bad && tid == 0) atomicCAS(p.fault, FAULT_NONE, FAULT_NONFINITE);
   for (uint32_t d = tid; d < p.Dv; d += blockDim.x) {
     float o = 0.0f;
     for (int w = 0; w < GEN_WARPS; w++) {
@@ -851,6 +854,8 @@ int32_t attention_launch(AionCudaDevice* dev, const AionCudaAttention* s) {
   p.scale = s->scale;
   p.soft_cap = s->soft_cap;
   p.fault = dev->fault_dev;
+  p.wait_limit = dev->debug_expire_waits ? (1u << 6) : (1u << 20);
+  p.drop_first = dev->debug_expire_waits ? 1u : 0u;
 
   const bool f16kv = s->k_dtype == AION_CUDA_DTYPE_F16 && s->v_dtype == AION_CUDA_DTYPE_F16;
   const bool aligned = ((reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(out)) & 15) == 0 &&

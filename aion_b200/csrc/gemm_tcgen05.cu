@@ -64,6 +64,8 @@ struct GemmParams {
   float* partial;     // [tile][split][BM * MH][BN] raw accumulators
   uint32_t tile_rows; // BM * MH
   int* fault;
+  uint32_t wait_shift;  // poll limits of the bounded waits are shifted right by this much (test hook)
+  uint32_t drop_first;  // test hook: every CTA leaves out its first packed-weight copy, so a wait runs out
 };
 
 template <int DT, int MH>
@@ -210,13 +212,21 @@ struct Bars {
 };
 static_assert(sizeof(Bars) <= 256, "barrier block");
 
+// What a bounded wait needs: the CTA's abort flag, and by how many bits the poll limits are shortened
+// (0 in production; the test hook of aion_cuda_debug_expire_waits sets it so a wait that cannot complete
+// gives up within milliseconds).
+struct WaitCtx {
+  volatile uint32_t* abort_flag;
+  uint32_t shift;
+};
 // Bounded wait that also gives up as soon as another role has aborted.
 template <bool SPIN = false>
-__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, const WaitCtx& w) {
   const uint32_t b = ptx::smem_u32(bar);
-  for (uint32_t i = 0; i < (SPIN ? (1u << 24) : (1u << 18)); i++) {
+  const uint32_t limit = (SPIN ? (1u << 24) : (1u << 18)) >> w.shift;
+  for (uint32_t i = 0; i < limit; i++) {
     if (SPIN ? ptx::mbar_try_wait_spin(b, parity) : ptx::mbar_try_wait(b, parity)) return true;
-    if ((!SPIN || (i & 63) == 63) && *abort_flag) return false;
+    if ((!SPIN || (i & 63) == 63) && *w.abort_flag) return false;
   }
   return false;
 }
@@ -308,6 +318,7 @@ gemm_q_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm
   uint8_t* sm = smem_raw + (base - raw);
   Bars* bars = reinterpret_cast<Bars*>(sm + G::OFF_BARS);
   volatile uint32_t* abort_flag = &bars->abort;
+  const WaitCtx wctx{abort_flag, p.wait_shift};
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr uint32_t AS = G::A_STAGES, PS = G::P_STAGES, BS = G::B_STAGES;
@@ -357,7 +368,7 @@ gemm_q_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm
         const int32_t m0 = (int32_t)((w.tile % p.m_tiles) * (BM * MH));
         for (uint32_t ks = w.ks0; ks < w.ks1; ks++, it++) {
           const uint32_t s = it % AS, use = it / AS;
-          if (use > 0 && !wait_or_abort<true>(&bars->a_empty[s], (use - 1) & 1, abort_flag)) {
+          if (use > 0 && !wait_or_abort<true>(&bars->a_empty[s], (use - 1) & 1, wctx)) {
             raise_abort(p.fault, abort_flag);
             ok = false;
             break;
@@ -378,13 +389,14 @@ gemm_q_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm
         const int32_t n0 = (int32_t)((w.tile / p.m_tiles) * BN);
         for (uint32_t ks = w.ks0; ks < w.ks1; ks++, it++) {
           const uint32_t s = it % PS, use = it / PS;
-          if (use > 0 && !wait_or_abort<true>(&bars->p_empty[s], (use - 1) & 1, abort_flag)) {
+          if (use > 0 && !wait_or_abort<true>(&bars->p_empty[s], (use - 1) & 1, wctx)) {
             raise_abort(p.fault, abort_flag);
             ok = false;
             break;
           }
           const uint32_t full = ptx::smem_u32(&bars->p_full[s]);
           ptx::mbar_arrive_expect_tx(full, G::PACKED_BYTES);
+          if (p.drop_first && it == 0) continue;   // (test hook: the bytes never arrive, the dequantizers' wait runs out)
           ptx::tma_load_3d(base + G::OFF_PRING + s * G::PACKED_PAD, &tmap_b, 0, n0 / 8, (int32_t)(ks * KB_PER_STAGE), full);
         }
       }
@@ -396,7 +408,7 @@ gemm_q_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm
     for (uint32_t u = blockIdx.x; u < units && ok; u += gridDim.x, tile_iter++) {
       const Unit w = unit_of(p, u);
       const uint32_t acc = tile_iter % NACC, acc_use = tile_iter / NACC;
-      if (acc_use > 0 && !wait_or_abort<true>(&bars->acc_empty[acc], (acc_use - 1) & 1, abort_flag)) {
+      if (acc_use > 0 && !wait_or_abort<true>(&bars->acc_empty[acc], (acc_use - 1) & 1, wctx)) {
         if (lane == 0) raise_abort(p.fault, abort_flag);
         break;
       }
@@ -404,7 +416,7 @@ gemm_q_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm
       const uint32_t d_tmem = tmem_base + acc * ACC_COLS;
       for (uint32_t ks = w.ks0; ks < w.ks1; ks++, it++) {
         const uint32_t sa = it % AS, pha = (it / AS) & 1, sb = it % BS, phb = (it / BS) & 1;
-        if (!wait_or_abort<true>(&bars->a_full[sa], pha, abort_flag) || !wait_or_abort<true>(&bars->bready[sb], phb, abort_flag)) {
+        if (!wait_or_abort<true>(&bars->a_full[sa], pha, wctx) || !wait_or_abort<true>(&bars->bready[sb], phb, wctx)) {
           if (lane == 0) raise_abort(p.fault, abort_flag);
           ok = false;
           break;
@@ -441,8 +453,8 @@ gemm_q_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm
       for (uint32_t ks = w.ks0; ks < w.ks1; ks++, it++) {
         if (it % DEQ_GROUPS != group) continue;
         const uint32_t sp = it % PS, php = (it / PS) & 1, sb = it % BS, buse = it / BS;
-        if (!wait_or_abort<true>(&bars->p_full[sp], php, abort_flag) ||
-            (buse > 0 && !wait_or_abort<true>(&bars->bfree[sb], (buse - 1) & 1, abort_flag))) {
+        if (!wait_or_abort<true>(&bars->p_full[sp], php, wctx) ||
+            (buse > 0 && !wait_or_abort<true>(&bars->bfree[sb], (buse - 1) & 1, wctx))) {
           if (lane == 0) raise_abort(p.fault, abort_flag);
           ok = false;
           break;
@@ -474,7 +486,7 @@ gemm_q_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm
     for (uint32_t u = blockIdx.x; u < units; u += gridDim.x, tile_iter++) {
       const Unit w = unit_of(p, u);
       const uint32_t acc = tile_iter % NACC, acc_use = tile_iter / NACC;
-      if (!wait_or_abort(&bars->acc_full[acc], acc_use & 1, abort_flag)) {
+      if (!wait_or_abort(&bars->acc_full[acc], acc_use & 1, wctx)) {
         if (lane == 0) raise_abort(p.fault, abort_flag);
         break;
       }
@@ -618,11 +630,12 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
   return ok != 0;
 }
 // Bounded wait on a barrier whose arrivals may come from the other CTA.
-__device__ __forceinline__ bool wait_cluster_or_abort(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
+__device__ __forceinline__ bool wait_cluster_or_abort(uint64_t* bar, uint32_t parity, const WaitCtx& w) {
   const uint32_t b = ptx::smem_u32(bar);
-  for (uint32_t i = 0; i < (1u << 24); i++) {
+  const uint32_t limit = (1u << 24) >> w.shift;
+  for (uint32_t i = 0; i < limit; i++) {
     if (mbar_try_wait_cluster(b, parity)) return true;
-    if ((i & 63) == 63 && *abort_flag) return false;
+    if ((i & 63) == 63 && *w.abort_flag) return false;
   }
   return false;
 }
@@ -691,6 +704,7 @@ gemm_q_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_
   uint8_t* sm = smem_raw + (base - raw);
   PairBars* bars = reinterpret_cast<PairBars*>(sm + G::OFF_BARS);
   volatile uint32_t* abort_flag = &bars->abort;
+  const WaitCtx wctx{abort_flag, p.wait_shift};
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();   // 0: leader
@@ -743,7 +757,7 @@ gemm_q_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_
         const int32_t m0 = (int32_t)((w.tile % p.m_tiles) * (2 * BM * MH) + rank * BM);
         for (uint32_t ks = w.ks0; ks < w.ks1; ks++, it++) {
           const uint32_t s = it % AS, use = it / AS;
-          if (use > 0 && !wait_or_abort<true>(&bars->a_empty[s], (use - 1) & 1, abort_flag)) {
+          if (use > 0 && !wait_or_abort<true>(&bars->a_empty[s], (use - 1) & 1, wctx)) {
             raise_abort(p.fault, abort_flag);
             ok = false;
             break;
@@ -767,13 +781,14 @@ gemm_q_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_
         const int32_t n0 = (int32_t)((w.tile / p.m_tiles) * BN + rank * BNH);
         for (uint32_t ks = w.ks0; ks < w.ks1; ks++, it++) {
           const uint32_t s = it % PS, use = it / PS;
-          if (use > 0 && !wait_or_abort<true>(&bars->p_empty[s], (use - 1) & 1, abort_flag)) {
+          if (use > 0 && !wait_or_abort<true>(&bars->p_empty[s], (use - 1) & 1, wctx)) {
             raise_abort(p.fault, abort_flag);
             ok = false;
             break;
           }
           const uint32_t full = ptx::smem_u32(&bars->p_full[s]);
           ptx::mbar_arrive_expect_tx(full, G::PACKED_BYTES);
+          if (p.drop_first && it == 0) continue;   // (test hook: the bytes never arrive, the dequantizers' wait runs out)
           ptx::tma_load_3d(base + G::OFF_PRING + s * G::PACKED_PAD, &tmap_b, 0, n0 / 8, (int32_t)(ks * KB_PER_STAGE), full);
         }
       }
@@ -786,7 +801,7 @@ gemm_q_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_
       for (uint32_t u = pair; u < units && ok; u += pairs, tile_iter++) {
         const Unit w = unit_of(p, u);
         const uint32_t acc = tile_iter % NACC, acc_use = tile_iter / NACC;
-        if (acc_use > 0 && !wait_cluster_or_abort(&bars->acc_empty[acc], (acc_use - 1) & 1, abort_flag)) {
+        if (acc_use > 0 && !wait_cluster_or_abort(&bars->acc_empty[acc], (acc_use - 1) & 1, wctx)) {
           if (lane == 0) raise_abort(p.fault, abort_flag);
           break;
         }
@@ -794,7 +809,7 @@ gemm_q_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_
         const uint32_t d_tmem = tmem_base + acc * ACC_COLS;
         for (uint32_t ks = w.ks0; ks < w.ks1; ks++, it++) {
           const uint32_t sa = it % AS, pha = (it / AS) & 1, sb = it % BS, phb = (it / BS) & 1;
-          if (!wait_cluster_or_abort(&bars->a_full[sa], pha, abort_flag) || !wait_cluster_or_abort(&bars->bready[sb], phb, abort_flag)) {
+          if (!wait_cluster_or_abort(&bars->a_full[sa], pha, wctx) || !wait_cluster_or_abort(&bars->bready[sb], phb, wctx)) {
             if (lane == 0) raise_abort(p.fault, abort_flag);
             ok = false;
             break;
@@ -830,8 +845,8 @@ gemm_q_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_
       for (uint32_t ks = w.ks0; ks < w.ks1; ks++, it++) {
         if (it % DEQ_GROUPS != group) continue;
         const uint32_t sp = it % PS, php = (it / PS) & 1, sb = it % BS, buse = it / BS;
-        if (!wait_or_abort<true>(&bars->p_full[sp], php, abort_flag) ||
-            (buse > 0 && !wait_or_abort<true>(&bars->bfree[sb], (buse - 1) & 1, abort_flag))) {
+        if (!wait_or_abort<true>(&bars->p_full[sp], php, wctx) ||
+            (buse > 0 && !wait_or_abort<true>(&bars->bfree[sb], (buse - 1) & 1, wctx))) {
           if (lane == 0) raise_abort(p.fault, abort_flag);
           ok = false;
           break;
@@ -868,7 +883,7 @@ gemm_q_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_
     for (uint32_t u = pair; u < units; u += pairs, tile_iter++) {
       const Unit w = unit_of(p, u);
       const uint32_t acc = tile_iter % NACC, acc_use = tile_iter / NACC;
-      if (!wait_or_abort(&bars->acc_full[acc], acc_use & 1, abort_flag)) {
+      if (!wait_or_abort(&bars->acc_full[acc], acc_use & 1, wctx)) {
         if (lane == 0) raise_abort(p.fault, abort_flag);
         break;
       }
@@ -1071,6 +1086,8 @@ int32_t launch_gemm(AionCudaDevice* dev, const MatMulArgs& g, const __nv_bfloat1
   p.n_tiles = (uint32_t)ceil_div(g.n, (uint64_t)BN);
   p.k_stages = (uint32_t)ceil_div(g.k, (uint64_t)BK);
   p.fault = dev->fault_dev;
+  p.wait_shift = dev->debug_expire_waits ? 14u : 0u;
+  p.drop_first = dev->debug_expire_waits ? 1u : 0u;
   p.splits = splits;
   p.partial = partial;
   const uint32_t units = p.m_tiles * p.n_tiles * splits;
@@ -1151,6 +1168,8 @@ int32_t launch_gemm_pair(AionCudaDevice* dev, const MatMulArgs& g, const __nv_bf
   p.n_tiles = (uint32_t)ceil_div(g.n, (uint64_t)BN);
   p.k_stages = (uint32_t)ceil_div(g.k, (uint64_t)BK);
   p.fault = dev->fault_dev;
+  p.wait_shift = dev->debug_expire_waits ? 14u : 0u;
+  p.drop_first = dev->debug_expire_waits ? 1u : 0u;
   p.splits = splits;
   p.partial = partial;
   const uint32_t units = p.m_tiles * p.n_tiles * splits;

@@ -324,3 +324,25 @@ def test_attention_writes_the_image_of_its_output(backend, dtype, B, T, qdt):
             img.free()
     finally:
         store.deinit()
+
+
+@pytest.mark.parametrize("L", [1, 40], ids=["decode_rows", "query_blocks"])
+def test_an_expired_wait_in_attention_is_reported_and_the_device_stays_usable(L):
+    """With the test hook on, every CTA leaves out the K / V copies of its first stage and polls briefly: the
+    consumers' wait runs out, the kernel records the fault and returns, the next synchronization reports it,
+    and the same device object then computes correctly again."""
+    b2 = CudaBackend(0)
+    try:
+        q, k, v = _qkv(2, L, 8, 2, 300, 128, 128, np.float16, np.float16, seed=L)
+        pos = (300 - L + np.arange(L, dtype=np.int32))[None, :].repeat(2, 0).astype(np.int32)
+        kw = dict(scale=0.09, positions=pos, kv_lengths=np.full(2, 300, np.int32), right=0)
+        want = oracle.attention(q, k, v, **kw)
+        assert rd.rel_l2(run_attention(b2, q, k, v, **kw), want) < TOL
+        assert b2._lib.aion_cuda_debug_expire_waits(b2.handle, 1) == capi.OK
+        with pytest.raises(BackendError) as e:
+            run_attention(b2, q, k, v, **kw)
+        assert e.value.name == "ExecutionFailed" and "bounded wait" in str(e.value)
+        assert b2._lib.aion_cuda_debug_expire_waits(b2.handle, 0) == capi.OK
+        assert rd.rel_l2(run_attention(b2, q, k, v, **kw), want) < TOL
+    finally:
+        b2.deinit()

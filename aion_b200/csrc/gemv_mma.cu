@@ -884,10 +884,22 @@ int32_t launch(AionCudaDevice* dev, GemvParams p, const uint8_t* b, uint64_t ldb
 template <int DT, bool NT>
 int32_t launch_m(AionCudaDevice* dev, const GemvParams& p, const uint8_t* b, uint64_t ldb, const uint8_t* image) {
   // m >= 2: A is quantized once by a small kernel (or by the kernel that produced A) instead of
-  // by every CTA. m = 1 quantizes its one row inside the kernel unless K is deep: past about
-  // 3000 the small kernel is cheaper than 148 CTAs each quantizing the whole row.
-  if (p.m == 1) return (image || p.kblocks > 96) ? launch<DT, NT, 1, true, false, true, 1, 1>(dev, p, b, ldb, image)
-                                                 : launch<DT, NT, 1, true, false, false, 1, 1>(dev, p, b, ldb, nullptr);
+  // by every CTA. m = 1 quantizes its one row inside the kernel when the launch stands alone on a
+  // chain (one kernel less: 10.6 against 11.8 us for a lone 9 MB launch) and K is shallow (past
+  // about 3000 the small kernel is cheaper than 148 CTAs each quantizing the whole row). Independent
+  // launches recorded into parallel lanes are bound by how soon each CTA starts to consume its
+  // weights, and the quantization prologue is a seventh of a CTA's life there: with the small
+  // kernel the 9 MB bench shape streams 5.4 - 5.7 TB/s instead of 4.9 - 5.2 (row-major NT weights
+  // measured 3 % slower that way and keep the in-kernel prologue).
+  if (p.m == 1) {
+    bool overlapped = false;
+    if (dev->recording) {
+      overlapped = dev->cur_lane != 0;
+      for (int l = 1; l < AionCudaDevice::LANES; l++) overlapped = overlapped || dev->lane_forked[l];
+    }
+    return (image || p.kblocks > 96 || (overlapped && !NT)) ? launch<DT, NT, 1, true, false, true, 1, 1>(dev, p, b, ldb, image)
+                                                            : launch<DT, NT, 1, true, false, false, 1, 1>(dev, p, b, ldb, nullptr);
+  }
   if (p.m <= 8) return launch<DT, NT, 1, false, false, true, 1, 1>(dev, p, b, ldb, image);
   if (p.m <= 16) return launch<DT, NT, 2, false, false, true, 1, 1>(dev, p, b, ldb, image);
   if (p.m <= 32) return launch<DT, NT, 4, false, false, true, 2, 2>(dev, p, b, ldb, image);
@@ -921,7 +933,16 @@ int32_t gemv_mma(AionCudaDevice* dev, const MatMulArgs& g, bool probe_only) {
   // ours to read: A is quantized here instead.
   const uint8_t* image = (g.a_image && act_image_layout(g.m, kblocks).kind == ACT_IMAGE_INT8) ? g.a_image : nullptr;
   uint64_t kb_max = (ACT_BUDGET_BYTES / 72) / KBT * KBT;
-  if (g.m >= 2 || kblocks > 96 || image) kb_max = (kblocks + KBT - 1) / KBT * KBT;
+  bool lanes = false;
+  if (dev->recording) {
+    lanes = dev->cur_lane != 0;
+    for (int l = 1; l < AionCudaDevice::LANES; l++) lanes = lanes || dev->lane_forked[l];
+  }
+  if (g.m >= 2 || kblocks > 96 || image || (lanes && !g.nt)) kb_max = (kblocks + KBT - 1) / KBT * KBT;
+  // A single row takes the image kernel only when recorded into parallel lanes: the run before the
+  // recording (which quantizes in the kernel) reserves the image's scratch for it.
+  if (g.m == 1 && !g.nt && !image && !dev->recording)
+    if (int32_t st = dev->reserve_scratch(act_image_total_bytes(act_image_layout_int8(1, kblocks)))) return st;
   if (g.peers && kblocks > kb_max) return AION_CUDA_UNSUPPORTED;   // the fan-out belongs to a single launch
 
   for (uint64_t kb0 = 0; kb0 < kblocks; kb0 += kb_max) {

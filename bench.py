@@ -359,12 +359,14 @@ def run_ours(args):
         "config": dict(CONFIG),
         "run": {"parallelism": "replicas only" if world > 1 else "single GPU", "distinct_weight_bytes_per_step": COPIES * W_BYTES,
                 "program": f"one recorded program per step; its 256 independent steps sit in {args.lanes} parallel lanes",
+                "kernels_per_gemv": ("gemv_act_image_kernel + gemv_q_mma_kernel" if args.lanes > 1 else "gemv_q_mma_kernel"),
                 "outputs_finite_nonzero": finite},
         "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d_bytes,
                 "d2h_bytes_per_step": d2h_bytes, "steps": e2e_steps, "sessions": len(sessions),
                 "how": "host threads, one per session; a step = aion_cuda_h2d + aion_cuda_program_launch + aion_cuda_d2h",
                 "sessions_agree": same},
-        "gpu_launches": args.steps * COPIES,
+        # per GEMV of the pass: the activation-image kernel (A quantized once per launch) and the matmul kernel
+        "gpu_launches": args.steps * COPIES * (2 if args.lanes > 1 else 1),
         "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
                      "frac": round(achieved / peak, 4), "peak_kind": f"of {peak_kind}",
                      "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "algorithmic_bytes_per_launch": BYTES_PER_LAUNCH},

@@ -460,33 +460,63 @@ def _colsplit_peer_stores(torch, dist, backend, rank, world, local_rank, m, n, k
     """The same layer with the exchange inside the matmul kernel: every rank's kernel stores its columns into
     every rank's y [m, n] over NVLink (peer stores from the epilogue) and announces them; a bounded wait kernel
     then finds y complete. Two y buffers alternate, since a rank may run one step ahead of a peer. One recorded
-    program = two steps."""
+    program = two steps.
+
+    Every rank makes the same collective calls in the same order whatever happens locally: a phase that fails
+    on one rank is agreed on by all (an all-reduce of a flag after each phase), the rest of the leg is skipped
+    everywhere, and the error is reported instead of a number."""
     lib, dev, mem = backend._lib, backend.handle, backend.device_memory
     y_bytes = m * n * 4
-    mine = {"y0": mem.alloc(y_bytes, 256), "y1": mem.alloc(y_bytes, 256), "flags": mem.alloc(32, 256), "state": mem.alloc(8, 256)}
-    for h, nbytes in ((mine["y0"], y_bytes), (mine["y1"], y_bytes), (mine["flags"], 32), (mine["state"], 8)):
-        mem.memset(h, 0, 0, nbytes)
-    backend.sync()
-    exported = {}
-    for name, h in mine.items():
-        buf = (C.c_uint8 * 64)()
-        _chk(lib.aion_cuda_ipc_export(dev, h, C.byref(buf)))
-        exported[name] = bytes(buf)
-    everyone = [None] * world
-    dist.all_gather_object(everyone, exported)
-    peers = []   # per rank: name -> handle valid in this process
-    for r in range(world):
-        if r == rank:
-            peers.append(dict(mine))
-            continue
-        opened = {}
-        for name in ("y0", "y1", "flags"):
-            buf = (C.c_uint8 * 64).from_buffer_copy(everyone[r][name])
-            h = C.c_uint64()
-            _chk(lib.aion_cuda_ipc_import(dev, C.byref(buf), C.byref(h)))
-            opened[name] = h.value
-        peers.append(opened)
     n_loc = n1 - n0
+    state = {"error": None}
+
+    def phase(fn):
+        """Runs fn on this rank unless an earlier phase failed somewhere; returns True when it worked everywhere."""
+        if state["error"] is None:
+            try:
+                fn()
+            except Exception as ex:  # noqa: BLE001 - reported in the leg's result
+                state["error"] = f"{type(ex).__name__}: {ex}"[:300]
+        bad = torch.tensor([0 if state["error"] is None else 1], device="cuda", dtype=torch.int32)
+        dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+        if int(bad.item()) and state["error"] is None:
+            state["error"] = "another rank failed in this phase"
+        return state["error"] is None
+
+    mine, peers, opened, prog = {}, [], [], [None]
+    everyone = [None] * world
+
+    def allocate():
+        for name, nbytes in (("y0", y_bytes), ("y1", y_bytes), ("flags", 32), ("state", 8)):
+            mine[name] = mem.alloc(nbytes, 256)
+            mem.memset(mine[name], 0, 0, nbytes)
+        backend.sync()
+
+    def export():
+        exported = {}
+        for name, h in mine.items():
+            buf = (C.c_uint8 * 64)()
+            _chk(lib.aion_cuda_ipc_export(dev, h, C.byref(buf)))
+            exported[name] = bytes(buf)
+        state["exported"] = exported
+
+    phase(allocate)
+    phase(export)
+    dist.all_gather_object(everyone, state.get("exported"))
+
+    def open_peers():
+        for r in range(world):
+            if r == rank:
+                peers.append(dict(mine))
+                continue
+            got = {}
+            for name in ("y0", "y1", "flags"):
+                buf = (C.c_uint8 * 64).from_buffer_copy(everyone[r][name])
+                h = C.c_uint64()
+                _chk(lib.aion_cuda_ipc_import(dev, C.byref(buf), C.byref(h)))
+                got[name] = h.value
+                opened.append(h.value)
+            peers.append(got)
 
     def fan_out(parity):
         key = "y1" if parity else "y0"
@@ -501,50 +531,70 @@ def _colsplit_peer_stores(torch, dist, backend, rank, world, local_rank, m, n, k
         fl, st = capi.Operand(mine["flags"], 0, 32), capi.Operand(mine["state"], 0, 8)
         _chk(lib.aion_cuda_peer_wait(dev, C.byref(fl), C.byref(st), world, 0))
 
-    dist.barrier()   # every rank's buffers are zeroed and opened everywhere before the first store
-    fan_out(0)
-    fan_out(1)
-    backend.sync()
-    got = [np.empty(m * n, np.float32), np.empty(m * n, np.float32)]
-    mem.copy_d2h(got[0], mine["y0"], 0)
-    mem.copy_d2h(got[1], mine["y1"], 0)
-    want = y_full.cpu().numpy().reshape(-1).astype(np.float64)
-    rel = max(float(np.linalg.norm(g.astype(np.float64) - want) / max(np.linalg.norm(want), 1e-30)) for g in got)
-    worst = torch.tensor([rel], device="cuda", dtype=torch.float64)
-    dist.all_reduce(worst, op=dist.ReduceOp.MAX)
-    rel = float(worst[0].item())
-    _chk(lib.aion_cuda_record_begin(dev))
-    fan_out(0)
-    fan_out(1)
-    prog = C.c_void_p()
-    _chk(lib.aion_cuda_record_end(dev, C.byref(prog)))
-    for _ in range(3):
-        _chk(lib.aion_cuda_program_launch(dev, prog))
-    backend.sync()
+    result = {}
+
+    def first_steps():
+        fan_out(0)
+        fan_out(1)
+        backend.sync()
+        got = [np.empty(m * n, np.float32), np.empty(m * n, np.float32)]
+        mem.copy_d2h(got[0], mine["y0"], 0)
+        mem.copy_d2h(got[1], mine["y1"], 0)
+        want = y_full.cpu().numpy().reshape(-1).astype(np.float64)
+        result["rel"] = max(float(np.linalg.norm(g.astype(np.float64) - want) / max(np.linalg.norm(want), 1e-30)) for g in got)
+
+    def record():
+        _chk(lib.aion_cuda_record_begin(dev))
+        fan_out(0)
+        fan_out(1)
+        pg = C.c_void_p()
+        _chk(lib.aion_cuda_record_end(dev, C.byref(pg)))
+        prog[0] = pg
+        for _ in range(3):
+            _chk(lib.aion_cuda_program_launch(dev, pg))
+        backend.sync()
+
+    def timed():
+        stream, ev0, ev1 = _events(torch, backend, local_rank)
+        ev0.record(stream)
+        for _ in range(iters):
+            _chk(lib.aion_cuda_program_launch(dev, prog[0]))
+        ev1.record(stream)
+        backend.sync()
+        torch.cuda.synchronize()
+        result["ms_local"] = ev0.elapsed_time(ev1)
+
+    # (each phase ends in an all-reduce: every rank's buffers are zeroed and opened everywhere before the first store)
+    ok = phase(open_peers) and phase(first_steps)
+    if ok:
+        worst = torch.tensor([result["rel"]], device="cuda", dtype=torch.float64)
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+        result["rel"] = float(worst[0].item())
+    ok = ok and phase(record) and phase(timed)
+    if ok:
+        result["ms"] = _max_over_ranks(torch, dist, world, result["ms_local"]) / (2 * iters)
+    # Tear down in lockstep too: nobody closes a mapping another rank may still store into.
+    try:
+        backend.sync()
+    except Exception:  # noqa: BLE001 - a fault recorded by a failed phase; already in the result
+        pass
     dist.barrier()
-    stream, ev0, ev1 = _events(torch, backend, local_rank)
-    ev0.record(stream)
-    for _ in range(iters):
-        _chk(lib.aion_cuda_program_launch(dev, prog))
-    ev1.record(stream)
-    backend.sync()
-    torch.cuda.synchronize()
-    ms = _max_over_ranks(torch, dist, world, ev0.elapsed_time(ev1)) / (2 * iters)
-    lib.aion_cuda_program_destroy(dev, prog)
-    dist.barrier()   # nobody closes a mapping another rank may still store into
-    for r in range(world):
-        if r != rank:
-            for h in peers[r].values():
-                _chk(lib.aion_cuda_ipc_close(dev, h))
+    if prog[0] is not None:
+        lib.aion_cuda_program_destroy(dev, prog[0])
+    for h in opened:
+        lib.aion_cuda_ipc_close(dev, h)
     dist.barrier()
     for h in mine.values():
         mem.free(h)
+    what = "peer stores from the matmul kernel's epilogue into every rank's y + arrival words + one bounded wait kernel"
+    if not ok:
+        return {"error": state["error"], "exchange": what}
     total_w = (k // 32) * n * 18
-    return {"ms": round(ms, 4), "aggregate_weight_gbs": round(total_w / (ms * 1e-3) / 1e9, 1),
-            "exchange": "peer stores from the matmul kernel's epilogue into every rank's y + arrival words + one bounded wait kernel",
+    ms = result["ms"]
+    return {"ms": round(ms, 4), "aggregate_weight_gbs": round(total_w / (ms * 1e-3) / 1e9, 1), "exchange": what,
             "peer_bytes_per_rank": m * n_loc * 4 * (world - 1),
-            "parity": {"against": "the unsplit matmul over the full weight on this GPU, both y buffers, worst rank", "rel_l2": rel,
-                       "pass": bool(rel <= 2e-5)}}
+            "parity": {"against": "the unsplit matmul over the full weight on this GPU, both y buffers, worst rank", "rel_l2": result["rel"],
+                       "pass": bool(result["rel"] <= 2e-5)}}
 
 
 def matmul_leg(torch, backend: CudaBackend, local_rank: int, dtype: int, nt: bool, m: int, n: int, k: int, lanes: int = 8,

@@ -886,9 +886,10 @@ int32_t attention_launch(AionCudaDevice* dev, const AionCudaAttention* s) {
       if (L > (uint64_t)CONSUMER_WARPS * p.pos_per_tile) nt = 2;
       const uint64_t per_unit = (uint64_t)CONSUMER_WARPS * nt * p.pos_per_tile;
       p.l_blocks = (uint32_t)((L + per_unit - 1) / per_unit);
-      // Eight heads already share a row's keys; blocks of eight such rows pay only once they
-      // fill the SMs twice (2048 rows of one request measured 0.29 ms in blocks, 0.26 ms as rows).
-      if (p.col_heads == 8 && B * p.l_blocks * Hkv * p.head_groups < 2ull * (uint64_t)dev->sm_count && !(s->flags & AION_CUDA_ATTENTION_BLOCKS))
+      // Eight heads already share a row's keys; blocks of eight such rows pay once they cover half the
+      // SMs (one kv head: 2048 rows 0.130 ms in blocks against 0.233 ms as rows, 8 x 256 rows 0.061
+      // against 0.091; 512 rows, 64 blocks: 0.049 against 0.033).
+      if (p.col_heads == 8 && 2 * B * p.l_blocks * Hkv * p.head_groups < (uint64_t)dev->sm_count && !(s->flags & AION_CUDA_ATTENTION_BLOCKS))
         block = false;
     }
     if (!block) {
@@ -929,6 +930,14 @@ int32_t attention_launch(AionCudaDevice* dev, const AionCudaAttention* s) {
         best = cost;
         splits = sp;
       }
+    }
+    // Blocks of positions: a split leaves a partial of every column of the block behind (64 rows of Dv floats)
+    // and a causal prompt's blocks are uneven anyway, so the context is split only while the blocks alone
+    // cannot cover the SMs (2048 causal rows of one request: 0.133 ms unsplit against 0.28 ms in four splits).
+    if (block) {
+      splits = 1;
+      if (units < sms) splits = std::min<uint64_t>(cap, sms / units);
+      if (splits < 1) splits = 1;
     }
     if (dev->attn_split_override) splits = dev->attn_split_override;
     p.splits = (uint32_t)splits;

@@ -343,25 +343,42 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParam
     {
       uint2* qhi = reinterpret_cast<uint2*>(smem + G::OFF_QHI);
       uint2* qlo = reinterpret_cast<uint2*>(smem + G::OFF_QLO);
-      for (int i = tid; i < NTT * (D / 16) * 32; i += CONSUMER_WARPS * 32) {
-        const int tile = i / ((D / 16) * 32), s = (i >> 5) % (D / 16), ln = i & 31, gg = ln >> 2, jj = ln & 3;
-        float v[4] = {0, 0, 0, 0};
-        const uint32_t row = col_row[tile * 8 + gg];
-        if (row != NO_ROW) {
-          const uint64_t off = (uint64_t)row * D + 16 * s + 2 * jj;
-          if (QF32) {
-            const float* qp = static_cast<const float*>(p.q) + off;
-            v[0] = qp[0]; v[1] = qp[1]; v[2] = qp[8]; v[3] = qp[9];
-          } else {
-            const __half* qp = static_cast<const __half*>(p.q) + off;
-            v[0] = __half2float(qp[0]); v[1] = __half2float(qp[1]); v[2] = __half2float(qp[8]); v[3] = __half2float(qp[9]);
+      // Every thread builds ITEMS fragment words. The loads of a batch of them are all issued before the
+      // first is used: taken one item at a time, each item's loads were a separate trip to L2 and this loop
+      // was a quarter of a short kernel.
+      constexpr int ITEMS = NTT * (D / 16) * 32 / (CONSUMER_WARPS * 32);
+      constexpr int BATCH = ITEMS < 8 ? ITEMS : 8;
+      static_assert(ITEMS >= 1 && ITEMS % BATCH == 0, "whole batches of fragment words per thread");
+#pragma unroll 1
+      for (int i0 = 0; i0 < ITEMS; i0 += BATCH) {
+        float v[BATCH][4];
+#pragma unroll
+        for (int u = 0; u < BATCH; u++) {
+          const int i = tid + (i0 + u) * (CONSUMER_WARPS * 32);
+          const int tile = i / ((D / 16) * 32), s = (i >> 5) % (D / 16), ln = i & 31, gg = ln >> 2, jj = ln & 3;
+          v[u][0] = v[u][1] = v[u][2] = v[u][3] = 0.0f;
+          const uint32_t row = col_row[tile * 8 + gg];
+          if (row != NO_ROW) {
+            const uint64_t off = (uint64_t)row * D + 16 * s + 2 * jj;
+            if (QF32) {
+              const float* qp = static_cast<const float*>(p.q) + off;
+              v[u][0] = qp[0]; v[u][1] = qp[1]; v[u][2] = qp[8]; v[u][3] = qp[9];
+            } else {
+              const __half* qp = static_cast<const __half*>(p.q) + off;
+              v[u][0] = __half2float(qp[0]); v[u][1] = __half2float(qp[1]);
+              v[u][2] = __half2float(qp[8]); v[u][3] = __half2float(qp[9]);
+            }
           }
         }
-        const __half h0a = __float2half_rn(v[0]), h1a = __float2half_rn(v[1]), h2a = __float2half_rn(v[2]), h3a = __float2half_rn(v[3]);
-        qhi[i] = make_uint2(pack_half2(__half2float(h0a), __half2float(h1a)), pack_half2(__half2float(h2a), __half2float(h3a)));
-        if (QF32)
-          qlo[i] = make_uint2(pack_half2(v[0] - __half2float(h0a), v[1] - __half2float(h1a)),
-                              pack_half2(v[2] - __half2float(h2a), v[3] - __half2float(h3a)));
+#pragma unroll
+        for (int u = 0; u < BATCH; u++) {
+          const int i = tid + (i0 + u) * (CONSUMER_WARPS * 32);
+          const __half h0a = __float2half_rn(v[u][0]), h1a = __float2half_rn(v[u][1]), h2a = __float2half_rn(v[u][2]), h3a = __float2half_rn(v[u][3]);
+          qhi[i] = make_uint2(pack_half2(__half2float(h0a), __half2float(h1a)), pack_half2(__half2float(h2a), __half2float(h3a)));
+          if (QF32)
+            qlo[i] = make_uint2(pack_half2(v[u][0] - __half2float(h0a), v[u][1] - __half2float(h1a)),
+                                pack_half2(v[u][2] - __half2float(h2a), v[u][3] - __half2float(h3a)));
+        }
       }
     }
     // This lane's columns and their key ranges clipped to this CTA's slice (lo, length).

@@ -613,19 +613,36 @@ __global__ void __launch_bounds__(threads_of(RW), min_ctas_per_sm(MT, CG, RW)) g
           for (int t = 0; t < MTW; t++)
 #pragma unroll
             for (int c = 0; c < CG; c++) v[t][c][0] = v[t][c][1] = v[t][c][2] = v[t][c][3] = 0.0f;
-          for (uint32_t part = 0; part < nparts; part++) {
-            const uint32_t cc = c_first + part;
-            const uint32_t cc_first_tile = (uint32_t)((U * cc / NG) / Sg);
-            const float* src = p.partials + ((size_t)cc * 2 + (tile == cc_first_tile ? 0 : 1)) * (TN * MPA);
+          // The loads of several parts are issued before the first is added: taken one part at a time each
+          // was a separate trip to L2 (about 0.4 us), and this loop is the tail of the kernel's critical path
+          // (a tile of a narrow layer is shared by six or seven CTAs). The sums stay in CTA order.
+          constexpr int PB = (MTW * CG == 1) ? 4 : 1;   // parts in flight (the wider variants have no registers to spare: 16 requests ran 2.55 -> 3.16 ms with two in flight)
+          for (uint32_t part0 = 0; part0 < nparts; part0 += PB) {
+            float2 x0[PB][MTW][CG], x1[PB][MTW][CG];
 #pragma unroll
-            for (int t = 0; t < MTW; t++)
+            for (int q = 0; q < PB; q++) {
+              const uint32_t cc = min(c_first + part0 + q, c_last);
+              const uint32_t cc_first_tile = (uint32_t)((U * cc / NG) / Sg);
+              const float* src = p.partials + ((size_t)cc * 2 + (tile == cc_first_tile ? 0 : 1)) * (TN * MPA);
 #pragma unroll
-              for (int c = 0; c < CG; c++) {
-                const float2 x0 = __ldcg(reinterpret_cast<const float2*>(src + (col0 + 64 * c) * MPA + row_base + t * 8 + 2 * j));
-                const float2 x1 = __ldcg(reinterpret_cast<const float2*>(src + (col1 + 64 * c) * MPA + row_base + t * 8 + 2 * j));
-                v[t][c][0] += x0.x; v[t][c][1] += x0.y;
-                v[t][c][2] += x1.x; v[t][c][3] += x1.y;
-              }
+              for (int t = 0; t < MTW; t++)
+#pragma unroll
+                for (int c = 0; c < CG; c++) {
+                  x0[q][t][c] = __ldcg(reinterpret_cast<const float2*>(src + (col0 + 64 * c) * MPA + row_base + t * 8 + 2 * j));
+                  x1[q][t][c] = __ldcg(reinterpret_cast<const float2*>(src + (col1 + 64 * c) * MPA + row_base + t * 8 + 2 * j));
+                }
+            }
+#pragma unroll
+            for (int q = 0; q < PB; q++) {
+              if (part0 + q >= nparts) break;
+#pragma unroll
+              for (int t = 0; t < MTW; t++)
+#pragma unroll
+                for (int c = 0; c < CG; c++) {
+                  v[t][c][0] += x0[q][t][c].x; v[t][c][1] += x0[q][t][c].y;
+                  v[t][c][2] += x1[q][t][c].x; v[t][c][3] += x1[q][t][c].y;
+                }
+            }
           }
           store = true;
         }

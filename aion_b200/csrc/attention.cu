@@ -169,7 +169,7 @@ struct DecodeGeom {
   static constexpr int STAGING_BUFS = BLOCK ? 1 : CONSUMER_WARPS;
   static constexpr int WS = COLS * D + 2 * COLS;      // floats per staging buffer: sums, then max and weight per column
   static constexpr int MERGE_BYTES = STAGING_BUFS * WS * 4;
-  static constexpr int META_BYTES = COLS * 12;        // per column: output row, first key, key end
+  static constexpr int META_BYTES = COLS * 20;        // per column: output row x head, first key, key end, row of the [B*L] view, head
   static constexpr int NS_MAX = (220 * 1024 - Q_BYTES - META_BYTES - 256) / STAGE_BYTES;
   static constexpr int NS = NS_MAX > 4 ? 4 : NS_MAX;
   static_assert(NS >= 2, "ring too small");
@@ -186,6 +186,38 @@ struct DecodeGeom {
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory"); }
 
 constexpr uint32_t NO_ROW = 0xFFFFFFFFu;
+
+// The last step of a thread's N float4 columns: o / lsum (zeros for a column without keys), the stores,
+// and the quantized image of the output. Written across the N columns, so their divisions, roundings and
+// shuffles overlap: the kernel has four warps on its SM, and column after column this tail was 4 us.
+// All 32 lanes call with the same N (columns that do not exist pass on = false).
+template <int D, int N>
+__device__ __forceinline__ void finish_columns(const AttnParams& p, const float4 (&o)[N], const float (&lsum)[N], const bool (&on)[N],
+                                               const bool (&has_keys)[N], const uint32_t (&col)[N], uint32_t d4, const uint32_t* col_row,
+                                               const uint32_t* col_orow, const uint32_t* col_head, bool report) {
+  float4 r[N];
+#pragma unroll
+  for (int c = 0; c < N; c++) {
+    const bool good = lsum[c] > 0.0f && isfinite(lsum[c]);
+    const float inv = good ? __frcp_rn(lsum[c]) : 0.0f;
+    r[c] = make_float4(o[c].x * inv, o[c].y * inv, o[c].z * inv, o[c].w * inv);
+    if (!good) r[c] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (!good && on[c] && has_keys[c] && report) atomicCAS(p.fault, FAULT_NONE, FAULT_NONFINITE);
+  }
+#pragma unroll
+  for (int c = 0; c < N; c++)
+    if (on[c]) *reinterpret_cast<float4*>(p.out + (uint64_t)col_row[col[c]] * D + 4 * d4) = r[c];
+  if (p.image) {
+    uint32_t irow[N], kb[N];
+#pragma unroll
+    for (int c = 0; c < N; c++) {
+      irow[c] = on[c] ? col_orow[col[c]] : 0;
+      kb[c] = on[c] ? (col_head[col[c]] * (D / 4) + d4) >> 3 : 0;
+    }
+    if (p.image_dtype == AION_CUDA_DTYPE_Q8_0) quantize_store_blocks_8lanes<AION_CUDA_DTYPE_Q8_0, N>(r, d4 & 7, on, p.image, p.image_layout, irow, kb);
+    else quantize_store_blocks_8lanes<AION_CUDA_DTYPE_Q4_0, N>(r, d4 & 7, on, p.image, p.image_layout, irow, kb);
+  }
+}
 
 template <int D, bool QF32, bool TILED, bool BLOCK, int NT>
 __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParams p, const __grid_constant__ CUtensorMap tmap_k,
@@ -219,6 +251,8 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParam
   uint32_t* col_row = reinterpret_cast<uint32_t*>(smem + G::OFF_META);  // (b*L + l)*Hq + head, NO_ROW for a column that is padding
   uint32_t* col_lo = col_row + COLS;
   uint32_t* col_hi = col_lo + COLS;
+  uint32_t* col_orow = col_hi + COLS;   // b*L + l: the row of the output seen as [B*L, Hq*Dv]
+  uint32_t* col_head = col_orow + COLS;
 
   if (tid == 0) {
     for (int s = 0; s < NS; s++) {
@@ -254,6 +288,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParam
       }
     }
     col_row[c] = row, col_lo[c] = lo, col_hi[c] = hi;
+    col_orow[c] = b * p.L + l, col_head[c] = h0 + hh;
   }
   __syncthreads();
   const bool bad = union_range[2] != 0;
@@ -554,37 +589,44 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParam
     // lanes hold one 32-block of an output row.
     constexpr int C4 = (COLS * D / 4) / (CONSUMER_WARPS * 32);
     static_assert(C4 >= 1 && C4 * CONSUMER_WARPS * 32 * 4 == COLS * D, "whole float4 columns per thread");
+    constexpr int CHK = C4 < 4 ? C4 : 4;
+    static_assert(C4 % CHK == 0, "whole chunks");
+    const uint32_t d4 = tid % (D / 4);   // the same for every column of this thread: 128 threads are a multiple of D/4
 #pragma unroll 1
-    for (int c = 0; c < C4; c++) {
-      const uint32_t idx4 = tid + c * (CONSUMER_WARPS * 32), col = idx4 / (D / 4), d4 = idx4 % (D / 4);
-      const uint32_t row = col_row[col];
-      const bool on = row != NO_ROW;
-      float M = -INFINITY;
+    for (int cb = 0; cb < C4; cb += CHK) {
+      float4 o[CHK];
+      float lsum[CHK], M[CHK];
+      uint32_t col[CHK];
+      bool on[CHK], has_keys[CHK];
 #pragma unroll
-      for (int w = 0; w < NB; w++) M = fmaxf(M, all[w * WS + COLS * D + col]);
-      float4 o = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-      float lsum = 0.0f;
+      for (int c = 0; c < CHK; c++) {
+        const uint32_t idx4 = tid + (cb + c) * (CONSUMER_WARPS * 32);
+        col[c] = idx4 / (D / 4);
+        on[c] = col_row[col[c]] != NO_ROW;
+        has_keys[c] = col_hi[col[c]] > col_lo[col[c]];
+        M[c] = -INFINITY;
 #pragma unroll
-      for (int w = 0; w < NB; w++) {
-        const float mw = all[w * WS + COLS * D + col];
-        const float f = (mw == -INFINITY) ? 0.0f : exp2f(mw - M);
-        const float4 x = *reinterpret_cast<const float4*>(all + w * WS + 4 * idx4);
-        o.x += x.x * f; o.y += x.y * f; o.z += x.z * f; o.w += x.w * f;
-        lsum += all[w * WS + COLS * D + COLS + col] * f;
+        for (int w = 0; w < NB; w++) M[c] = fmaxf(M[c], all[w * WS + COLS * D + col[c]]);
+        o[c] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        lsum[c] = 0.0f;
+#pragma unroll
+        for (int w = 0; w < NB; w++) {
+          const float mw = all[w * WS + COLS * D + col[c]];
+          const float f = (mw == -INFINITY) ? 0.0f : exp2f(mw - M[c]);
+          const float4 x = *reinterpret_cast<const float4*>(all + w * WS + 4 * idx4);
+          o[c].x += x.x * f; o[c].y += x.y * f; o[c].z += x.z * f; o[c].w += x.w * f;
+          lsum[c] += all[w * WS + COLS * D + COLS + col[c]] * f;
+        }
       }
       if (direct) {
-        float4 r = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        if (lsum > 0.0f && isfinite(lsum)) r = make_float4(o.x / lsum, o.y / lsum, o.z / lsum, o.w / lsum);
-        else if (on && col_hi[col] > col_lo[col] && !bad && !*abort_flag) atomicCAS(p.fault, FAULT_NONE, FAULT_NONFINITE);
-        if (on) *reinterpret_cast<float4*>(p.out + (uint64_t)row * D + 4 * d4) = r;
-        if (p.image) {
-          const uint32_t out_row = on ? row / p.Hq : 0, col4 = on ? (row % p.Hq) * (D / 4) + d4 : 0;
-          if (p.image_dtype == AION_CUDA_DTYPE_Q8_0) quantize_store_block_8lanes<AION_CUDA_DTYPE_Q8_0>(r, d4 & 7, on, p.image, p.image_layout, out_row, col4 >> 3);
-          else quantize_store_block_8lanes<AION_CUDA_DTYPE_Q4_0>(r, d4 & 7, on, p.image, p.image_layout, out_row, col4 >> 3);
-        }
-      } else if (on) {
-        *reinterpret_cast<float4*>(part + col * PP + 4 * d4) = o;
-        if (d4 == 0) *reinterpret_cast<float2*>(part + col * PP + D) = make_float2(M, lsum);
+        finish_columns<D, CHK>(p, o, lsum, on, has_keys, col, d4, col_row, col_orow, col_head, !bad && !*abort_flag);
+      } else {
+#pragma unroll
+        for (int c = 0; c < CHK; c++)
+          if (on[c]) {
+            *reinterpret_cast<float4*>(part + col[c] * PP + 4 * d4) = o[c];
+            if (d4 == 0) *reinterpret_cast<float2*>(part + col[c] * PP + D) = make_float2(M[c], lsum[c]);
+          }
       }
     }
     if (!direct) {
@@ -633,20 +675,23 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParam
           if (lane == 0) lsums[h] = lsum;
         }
         consumer_sync();
-        constexpr int CHK = C4 < 4 ? C4 : 4;
-        static_assert(C4 % CHK == 0, "whole chunks");
 #pragma unroll 1
         for (int cb = 0; cb < C4; cb += CHK) {
           const float* colp[CHK];
           const float* fh[CHK];
-          bool live[CHK];
+          bool live[CHK], has_keys[CHK];
+          uint32_t col[CHK];
           float4 o[CHK];
+          float lsum[CHK];
 #pragma unroll
           for (int c = 0; c < CHK; c++) {
-            const uint32_t idx4 = tid + (cb + c) * (CONSUMER_WARPS * 32), col = idx4 / (D / 4), d4 = idx4 % (D / 4);
-            live[c] = col_row[col] != NO_ROW;
-            colp[c] = pu + (size_t)col * PP + 4 * d4;
-            fh[c] = fac + col * p.splits;
+            const uint32_t idx4 = tid + (cb + c) * (CONSUMER_WARPS * 32);
+            col[c] = idx4 / (D / 4);
+            live[c] = col_row[col[c]] != NO_ROW;
+            has_keys[c] = col_hi[col[c]] > col_lo[col[c]];
+            colp[c] = pu + (size_t)col[c] * PP + 4 * d4;
+            fh[c] = fac + col[c] * p.splits;
+            lsum[c] = lsums[col[c]];
             o[c] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
           }
           for (uint32_t s2 = 0; s2 < p.splits; s2 += 4) {
@@ -671,21 +716,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParam
                 o[c].w += v[c][k].w * f[c][k];
               }
           }
-#pragma unroll
-          for (int c = 0; c < CHK; c++) {
-            const uint32_t idx4 = tid + (cb + c) * (CONSUMER_WARPS * 32), col = idx4 / (D / 4), d4 = idx4 % (D / 4);
-            const uint32_t row = col_row[col];
-            const float lsum = lsums[col];
-            float4 r = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-            if (lsum > 0.0f && isfinite(lsum)) r = make_float4(o[c].x / lsum, o[c].y / lsum, o[c].z / lsum, o[c].w / lsum);
-            else if (live[c] && col_hi[col] > col_lo[col] && !bad) atomicCAS(p.fault, FAULT_NONE, FAULT_NONFINITE);
-            if (live[c]) *reinterpret_cast<float4*>(p.out + (uint64_t)row * D + 4 * d4) = r;
-            if (p.image) {
-              const uint32_t out_row = live[c] ? row / p.Hq : 0, col4 = live[c] ? (row % p.Hq) * (D / 4) + d4 : 0;
-              if (p.image_dtype == AION_CUDA_DTYPE_Q8_0) quantize_store_block_8lanes<AION_CUDA_DTYPE_Q8_0>(r, d4 & 7, live[c], p.image, p.image_layout, out_row, col4 >> 3);
-              else quantize_store_block_8lanes<AION_CUDA_DTYPE_Q4_0>(r, d4 & 7, live[c], p.image, p.image_layout, out_row, col4 >> 3);
-            }
-          }
+          finish_columns<D, CHK>(p, o, lsum, live, has_keys, col, d4, col_row, col_orow, col_head, !bad);
         }
       }
     }

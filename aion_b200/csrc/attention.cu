@@ -179,43 +179,35 @@ struct DecodeGeom {
   static constexpr int OFF_META = OFF_QHI + Q_BYTES;
   static constexpr int OFF_BARS = OFF_META + META_BYTES;
   static constexpr int SMEM_BYTES = OFF_BARS + 2 * NS * 8 + 32;
-  // The merge of split partials keeps (max, weight) of every column and split in the drained ring.
-  static constexpr int MAX_SPLITS = (NS * STAGE_BYTES / 4 - COLS) / (2 * COLS);
+  // The merge of split partials keeps (max, weight) of every column and split at the start of the drained
+  // ring and the merged sums ([COLS][D] floats) at its end.
+  static constexpr int OFF_SUMS = NS * STAGE_BYTES - COLS * D * 4;
+  static constexpr int MAX_SPLITS = (OFF_SUMS / 4 - COLS) / (2 * COLS);
+  static_assert(OFF_SUMS % 16 == 0 && MAX_SPLITS >= 16, "room for the merge");
 };
 
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_WARPS * 32) : "memory"); }
 
 constexpr uint32_t NO_ROW = 0xFFFFFFFFu;
 
-// The last step of a thread's N float4 columns: o / lsum (zeros for a column without keys), the stores,
-// and the quantized image of the output. Written across the N columns, so their divisions, roundings and
-// shuffles overlap: the kernel has four warps on its SM, and column after column this tail was 4 us.
-// All 32 lanes call with the same N (columns that do not exist pass on = false).
-template <int D, int N>
-__device__ __forceinline__ void finish_columns(const AttnParams& p, const float4 (&o)[N], const float (&lsum)[N], const bool (&on)[N],
-                                               const bool (&has_keys)[N], const uint32_t (&col)[N], uint32_t d4, const uint32_t* col_row,
-                                               const uint32_t* col_orow, const uint32_t* col_head, bool report) {
-  float4 r[N];
-#pragma unroll
-  for (int c = 0; c < N; c++) {
-    const bool good = lsum[c] > 0.0f && isfinite(lsum[c]);
-    const float inv = good ? __frcp_rn(lsum[c]) : 0.0f;
-    r[c] = make_float4(o[c].x * inv, o[c].y * inv, o[c].z * inv, o[c].w * inv);
-    if (!good) r[c] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    if (!good && on[c] && has_keys[c] && report) atomicCAS(p.fault, FAULT_NONE, FAULT_NONFINITE);
-  }
-#pragma unroll
-  for (int c = 0; c < N; c++)
-    if (on[c]) *reinterpret_cast<float4*>(p.out + (uint64_t)col_row[col[c]] * D + 4 * d4) = r[c];
+// The last step of one float4 of an output column: o / lsum (zeros for a column without keys), the store, and
+// the quantized image of the output. All 32 lanes of a warp call it together (a column that does not exist
+// passes on = false). Callers run it in a loop that is NOT unrolled: this code runs once per CTA, at the very
+// end, on the CTA every other one is waiting for, and run once it costs what fetching its instructions costs
+// (four columns spelled out side by side took 4 to 5 us, most of it in the quantizer).
+template <int D>
+__device__ __forceinline__ void finish_column(const AttnParams& p, float4 o, float lsum, bool on, bool has_keys, uint32_t col, uint32_t d4,
+                                              const uint32_t* col_row, const uint32_t* col_orow, const uint32_t* col_head, bool report) {
+  const bool good = lsum > 0.0f && isfinite(lsum);
+  const float inv = good ? __frcp_rn(lsum) : 0.0f;
+  float4 r = make_float4(o.x * inv, o.y * inv, o.z * inv, o.w * inv);
+  if (!good) r = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  if (!good && on && has_keys && report) atomicCAS(p.fault, FAULT_NONE, FAULT_NONFINITE);
+  if (on) *reinterpret_cast<float4*>(p.out + (uint64_t)col_row[col] * D + 4 * d4) = r;
   if (p.image) {
-    uint32_t irow[N], kb[N];
-#pragma unroll
-    for (int c = 0; c < N; c++) {
-      irow[c] = on[c] ? col_orow[col[c]] : 0;
-      kb[c] = on[c] ? (col_head[col[c]] * (D / 4) + d4) >> 3 : 0;
-    }
-    if (p.image_dtype == AION_CUDA_DTYPE_Q8_0) quantize_store_blocks_8lanes<AION_CUDA_DTYPE_Q8_0, N>(r, d4 & 7, on, p.image, p.image_layout, irow, kb);
-    else quantize_store_blocks_8lanes<AION_CUDA_DTYPE_Q4_0, N>(r, d4 & 7, on, p.image, p.image_layout, irow, kb);
+    const uint32_t irow = on ? col_orow[col] : 0, kb = on ? (col_head[col] * (D / 4) + d4) >> 3 : 0;
+    if (p.image_dtype == AION_CUDA_DTYPE_Q8_0) quantize_store_block_8lanes<AION_CUDA_DTYPE_Q8_0>(r, d4 & 7, on, p.image, p.image_layout, irow, kb);
+    else quantize_store_block_8lanes<AION_CUDA_DTYPE_Q4_0>(r, d4 & 7, on, p.image, p.image_layout, irow, kb);
   }
 }
 
@@ -593,40 +585,27 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParam
     static_assert(C4 % CHK == 0, "whole chunks");
     const uint32_t d4 = tid % (D / 4);   // the same for every column of this thread: 128 threads are a multiple of D/4
 #pragma unroll 1
-    for (int cb = 0; cb < C4; cb += CHK) {
-      float4 o[CHK];
-      float lsum[CHK], M[CHK];
-      uint32_t col[CHK];
-      bool on[CHK], has_keys[CHK];
+    for (int c = 0; c < C4; c++) {
+      const uint32_t idx4 = tid + c * (CONSUMER_WARPS * 32), col = idx4 / (D / 4);
+      const bool on = col_row[col] != NO_ROW;
+      float M = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < CHK; c++) {
-        const uint32_t idx4 = tid + (cb + c) * (CONSUMER_WARPS * 32);
-        col[c] = idx4 / (D / 4);
-        on[c] = col_row[col[c]] != NO_ROW;
-        has_keys[c] = col_hi[col[c]] > col_lo[col[c]];
-        M[c] = -INFINITY;
+      for (int w = 0; w < NB; w++) M = fmaxf(M, all[w * WS + COLS * D + col]);
+      float4 o = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      float lsum = 0.0f;
 #pragma unroll
-        for (int w = 0; w < NB; w++) M[c] = fmaxf(M[c], all[w * WS + COLS * D + col[c]]);
-        o[c] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        lsum[c] = 0.0f;
-#pragma unroll
-        for (int w = 0; w < NB; w++) {
-          const float mw = all[w * WS + COLS * D + col[c]];
-          const float f = (mw == -INFINITY) ? 0.0f : exp2f(mw - M[c]);
-          const float4 x = *reinterpret_cast<const float4*>(all + w * WS + 4 * idx4);
-          o[c].x += x.x * f; o[c].y += x.y * f; o[c].z += x.z * f; o[c].w += x.w * f;
-          lsum[c] += all[w * WS + COLS * D + COLS + col[c]] * f;
-        }
+      for (int w = 0; w < NB; w++) {
+        const float mw = all[w * WS + COLS * D + col];
+        const float f = (mw == -INFINITY) ? 0.0f : exp2f(mw - M);
+        const float4 x = *reinterpret_cast<const float4*>(all + w * WS + 4 * idx4);
+        o.x += x.x * f; o.y += x.y * f; o.z += x.z * f; o.w += x.w * f;
+        lsum += all[w * WS + COLS * D + COLS + col] * f;
       }
       if (direct) {
-        finish_columns<D, CHK>(p, o, lsum, on, has_keys, col, d4, col_row, col_orow, col_head, !bad && !*abort_flag);
-      } else {
-#pragma unroll
-        for (int c = 0; c < CHK; c++)
-          if (on[c]) {
-            *reinterpret_cast<float4*>(part + col[c] * PP + 4 * d4) = o[c];
-            if (d4 == 0) *reinterpret_cast<float2*>(part + col[c] * PP + D) = make_float2(M[c], lsum[c]);
-          }
+        finish_column<D>(p, o, lsum, on, col_hi[col] > col_lo[col], col, d4, col_row, col_orow, col_head, !bad && !*abort_flag);
+      } else if (on) {
+        *reinterpret_cast<float4*>(part + col * PP + 4 * d4) = o;
+        if (d4 == 0) *reinterpret_cast<float2*>(part + col * PP + D) = make_float2(M, lsum);
       }
     }
     if (!direct) {
@@ -650,6 +629,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParam
         float* fac = reinterpret_cast<float*>(smem);  // [COLS][splits]: max, then factor
         float* wsum = fac + COLS * p.splits;          // [COLS][splits]: sum of weights
         float* lsums = wsum + COLS * p.splits;        // [COLS]
+        float4* sums = reinterpret_cast<float4*>(smem + G::OFF_SUMS);   // [C4][128]: the merged sums
         for (uint32_t idx = tid; idx < COLS * p.splits; idx += CONSUMER_WARPS * 32) {
           const uint32_t h = idx / p.splits, s2 = idx % p.splits;
           float2 ml = make_float2(-INFINITY, 0.0f);
@@ -716,7 +696,15 @@ __global__ void __launch_bounds__(THREADS, 1) attn_decode_kernel(const AttnParam
                 o[c].w += v[c][k].w * f[c][k];
               }
           }
-          finish_columns<D, CHK>(p, o, lsum, live, has_keys, col, d4, col_row, col_orow, col_head, !bad);
+          // The sums go through shared memory (this thread's own slots) so that the loop below can stay rolled.
+#pragma unroll
+          for (int c = 0; c < CHK; c++) sums[(cb + c) * (CONSUMER_WARPS * 32) + tid] = o[c];
+        }
+#pragma unroll 1
+        for (int c = 0; c < C4; c++) {
+          const uint32_t col = (tid + c * (CONSUMER_WARPS * 32)) / (D / 4);
+          finish_column<D>(p, sums[c * (CONSUMER_WARPS * 32) + tid], lsums[col], col_row[col] != NO_ROW, col_hi[col] > col_lo[col], col, d4,
+                           col_row, col_orow, col_head, !bad);
         }
       }
     }

@@ -50,6 +50,7 @@ namespace {
 
 constexpr int KBT = 8;             // K blocks per stage
 constexpr int NS = 2;              // stages in the ring: shallow, so that more CTAs (of concurrent launches) fit an SM
+constexpr int NS_DEEP = 8;         // the ring of the variant that holds a whole tile (up to 64 K blocks) per CTA
 constexpr int COL_WARPS = 4;                    // consumer warps side by side over a tile's columns
 constexpr int threads_of(int rw) { return (COL_WARPS * rw + 1) * 32; }
 constexpr int NT_ROW_PITCH = KBT * Q8_BYTES;  // 272: 16-byte multiple, 4 words mod 32 banks
@@ -82,15 +83,15 @@ struct GemvParams {
 };
 
 // CG: groups of 16 columns per consumer warp (1: 64-column tiles, 2: 128-column tiles).
-template <int DT, bool NT, int CG>
+template <int DT, bool NT, int CG, int NSK = NS>
 struct Geom {
   static constexpr int BB = (DT == AION_CUDA_DTYPE_Q8_0) ? Q8_BYTES : Q4_BYTES;
   static constexpr int TN = 64 * CG;
   static constexpr int KM_PITCH = TN * BB;
   static constexpr int STAGE_BYTES = NT ? TN * NT_ROW_PITCH : KBT * KM_PITCH;
-  static constexpr int RING_BYTES = NS * STAGE_BYTES;
+  static constexpr int RING_BYTES = NSK * STAGE_BYTES;
   static constexpr int OFF_BARS = RING_BYTES;
-  static constexpr int OFF_ACT = OFF_BARS + 128;
+  static constexpr int OFF_ACT = OFF_BARS + (2 * NSK * 8 + 16 + 127) / 128 * 128;   // full / empty barriers, abort flag
   // Distance between a warp's first and second group of 16 columns inside a stage.
   static constexpr int CG_STRIDE = NT ? 64 * NT_ROW_PITCH : 64 * BB;
   static_assert(STAGE_BYTES % 128 == 0, "TMA destinations are 128-byte aligned");
@@ -322,9 +323,9 @@ __global__ void gemv_act_image_kernel(const float* __restrict__ a, uint64_t lda,
 // in eight lanes, more 4.6 - 4.8).
 constexpr int min_ctas_per_sm(int mt, int cg, int rw) { return rw == 2 ? 2 : (mt * cg <= 2 ? 7 : 1); }
 
-template <int DT, bool NT, int MT, bool M1, bool RG, bool PREQ, int CG, int RW>
+template <int DT, bool NT, int MT, bool M1, bool RG, bool PREQ, int CG, int RW, int NSK = NS>
 __global__ void __launch_bounds__(threads_of(RW), min_ctas_per_sm(MT, CG, RW)) gemv_q_mma_kernel(const GemvParams p_in, const __grid_constant__ CUtensorMap tmap) {
-  using G = Geom<DT, NT, CG>;
+  using G = Geom<DT, NT, CG, NSK>;
   constexpr int TN = G::TN;
   constexpr int MPA = 8 * MT;  // activation rows of the accumulator tile
   constexpr int MTW = MT / RW;  // groups of 8 rows per warp
@@ -354,8 +355,8 @@ __global__ void __launch_bounds__(threads_of(RW), min_ctas_per_sm(MT, CG, RW)) g
   }
 
   const uint32_t bar_full = smem_base + G::OFF_BARS;
-  const uint32_t bar_empty = bar_full + NS * 8;
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + G::OFF_BARS + 2 * NS * 8);
+  const uint32_t bar_empty = bar_full + NSK * 8;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + G::OFF_BARS + 2 * NSK * 8);
   const uint32_t kb_pad = p.stages_per_tile * KBT;  // K blocks rounded up to whole stages
   uint8_t* act_q = smem + G::OFF_ACT;
   float* act_s = reinterpret_cast<float*>(act_q + (size_t)kb_pad * MP2 * 32);  // [kb][MP2] (when the CTA quantizes A itself)
@@ -367,7 +368,7 @@ __global__ void __launch_bounds__(threads_of(RW), min_ctas_per_sm(MT, CG, RW)) g
     // the CTA barrier below before they first wait on one.
     if (lane == 0) {
       ptx::prefetch_tensormap(&tmap);
-      for (int s = 0; s < NS; s++) {
+      for (int s = 0; s < NSK; s++) {
         ptx::mbar_init(bar_full + 8 * s, 1);
         ptx::mbar_init(bar_empty + 8 * s, CONSUMER_WARPS);
       }
@@ -380,7 +381,7 @@ __global__ void __launch_bounds__(threads_of(RW), min_ctas_per_sm(MT, CG, RW)) g
     uint32_t tile = (uint32_t)(u_begin / Sg), s = (uint32_t)(u_begin - (uint64_t)tile * Sg);
     // PREQ: every stage also brings its 8 K blocks of the activation image (codes, then scales)
     // into the stage's slot of the activation ring. The image comes from the previous kernel,
-    // so those copies wait for it; the weight copies of the first NS stages do not, and start
+    // so those copies wait for it; the weight copies of the first NSK stages do not, and start
     // at once.
     auto issue_acts = [&](uint32_t slot_, uint32_t s_, uint32_t tile_) {
       const uint8_t* image = p.act_image + (RG ? (size_t)(tile_ / p.col_tiles) * p.act_image_bytes : 0);
@@ -388,21 +389,21 @@ __global__ void __launch_bounds__(threads_of(RW), min_ctas_per_sm(MT, CG, RW)) g
       ptx::bulk_g2s(dst, image + (size_t)s_ * AQ_SLICE, AQ_SLICE, full);
       ptx::bulk_g2s(dst + AQ_SLICE, image + (size_t)kb_pad * (MP2 * 32) + (size_t)s_ * AS_SLICE, AS_SLICE, full);
     };
-    uint32_t pend_s[NS], pend_tile[NS];
+    uint32_t pend_s[NSK], pend_tile[NSK];
     uint32_t npend = 0;
     bool acts_open = !PREQ;
     for (uint64_t it = 0; it < n_units; it++) {
-      const uint32_t slot = (uint32_t)(it % NS);
-      if (it == (uint64_t)NS) __syncthreads();  // CTA barrier #1 (see the consumers)
-      if (PREQ && !acts_open && it == (uint64_t)NS) {
+      const uint32_t slot = (uint32_t)(it % NSK);
+      if (it == (uint64_t)NSK) __syncthreads();  // CTA barrier #1 (see the consumers)
+      if (PREQ && !acts_open && it == (uint64_t)NSK) {
         ptx::pdl_wait();
         if (lane == 0)
           for (uint32_t i = 0; i < npend; i++) issue_acts(i, pend_s[i], pend_tile[i]);
         acts_open = true;
       }
-      if (it >= (uint64_t)NS) {
+      if (it >= (uint64_t)NSK) {
         if (*abort_flag) break;
-        if (!ptx::mbar_wait_bounded(bar_empty + 8 * slot, (uint32_t)((it / NS) - 1) & 1, p.wait_limit)) {
+        if (!ptx::mbar_wait_bounded(bar_empty + 8 * slot, (uint32_t)((it / NSK) - 1) & 1, p.wait_limit)) {
           if (lane == 0) {
             atomicExch(p.fault, FAULT_WAIT_EXPIRED);
             *abort_flag = 1;
@@ -435,7 +436,7 @@ __global__ void __launch_bounds__(threads_of(RW), min_ctas_per_sm(MT, CG, RW)) g
         tile++;
       }
     }
-    if (n_units <= (uint64_t)NS) __syncthreads();  // CTA barrier #1 when the whole range fit the ring
+    if (n_units <= (uint64_t)NSK) __syncthreads();  // CTA barrier #1 when the whole range fit the ring
     if (PREQ && !acts_open) {
       ptx::pdl_wait();
       if (lane == 0)
@@ -444,8 +445,8 @@ __global__ void __launch_bounds__(threads_of(RW), min_ctas_per_sm(MT, CG, RW)) g
     // After a failed wait nobody drains the ring: let the copies still in flight land
     // (bounded) before this CTA's shared memory can be handed to another CTA.
     if (*abort_flag)
-      for (uint64_t it = issued > (uint64_t)NS ? issued - NS : 0; it < issued; it++)
-        ptx::mbar_wait_bounded(bar_full + 8 * (uint32_t)(it % NS), (uint32_t)(it / NS) & 1, min(p.wait_limit, 1u << 16));
+      for (uint64_t it = issued > (uint64_t)NSK ? issued - NSK : 0; it < issued; it++)
+        ptx::mbar_wait_bounded(bar_full + 8 * (uint32_t)(it % NSK), (uint32_t)(it / NSK) & 1, min(p.wait_limit, 1u << 16));
     return;
   }
 
@@ -514,8 +515,8 @@ __global__ void __launch_bounds__(threads_of(RW), min_ctas_per_sm(MT, CG, RW)) g
   bool ok = true;
   uint64_t it = 0;
   for (uint64_t uu = u_begin; uu < u_end; uu++, it++) {
-    const uint32_t slot = (uint32_t)(it % NS);
-    if (ok && (*abort_flag || !ptx::mbar_wait_bounded(bar_full + 8 * slot, (uint32_t)(it / NS) & 1, p.wait_limit))) {
+    const uint32_t slot = (uint32_t)(it % NSK);
+    if (ok && (*abort_flag || !ptx::mbar_wait_bounded(bar_full + 8 * slot, (uint32_t)(it / NSK) & 1, p.wait_limit))) {
       if (lane == 0 && !*abort_flag) {
         atomicExch(p.fault, FAULT_WAIT_EXPIRED);
         *abort_flag = 1;
@@ -767,7 +768,7 @@ int32_t kernel_occupancy(KernelSetup& ks, Kernel kernel, AionCudaDevice* dev, in
   return AION_CUDA_OK;
 }
 
-template <int DT, bool NT, int MT, bool M1, bool RG, bool PREQ, int CG, int RW>
+template <int DT, bool NT, int MT, bool M1, bool RG, bool PREQ, int CG, int RW, int NSK = NS>
 KernelSetup& setup_of() {
   static KernelSetup ks;
   return ks;
@@ -805,24 +806,32 @@ int32_t encode_weight_map(const uint8_t* b, uint64_t ldb, uint32_t n, uint32_t k
   return AION_CUDA_OK;
 }
 
-template <int DT, bool NT, int MT, bool M1, bool RG, bool PREQ, int CG, int RW>
+// Returned by the whole-tile variant when the shape does not suit it; the caller then takes the streaming one.
+constexpr int32_t DECLINED = -0x7A11;
+
+template <int DT, bool NT, int MT, bool M1, bool RG, bool PREQ, int CG, int RW, int NSK = NS>
 int32_t launch(AionCudaDevice* dev, GemvParams p, const uint8_t* b, uint64_t ldb, const uint8_t* given_image) {
-  using G = Geom<DT, NT, CG>;
+  using G = Geom<DT, NT, CG, NSK>;
   constexpr int TN = G::TN;
   constexpr int THREADS = threads_of(RW);
-  auto kernel = gemv_q_mma_kernel<DT, NT, MT, M1, RG, PREQ, CG, RW>;
+  constexpr bool WHOLE = NSK != NS;   // one whole tile per CTA, every stage of it in the ring at once
+  auto kernel = gemv_q_mma_kernel<DT, NT, MT, M1, RG, PREQ, CG, RW, NSK>;
   constexpr uint32_t MP2 = M1 ? 2 : 8 * MT;
-  const size_t smem = G::OFF_ACT + (PREQ ? (size_t)NS * act_bytes(KBT, MP2) : act_bytes(p.stages_per_tile * KBT, MP2));
+  const size_t smem = G::OFF_ACT + (PREQ ? (size_t)NSK * act_bytes(KBT, MP2) : act_bytes(p.stages_per_tile * KBT, MP2));
   int per_sm = 0;
-  if (int32_t st = kernel_occupancy(setup_of<DT, NT, MT, M1, RG, PREQ, CG, RW>(), kernel, dev, THREADS, smem, &per_sm)) return st;
+  if (int32_t st = kernel_occupancy(setup_of<DT, NT, MT, M1, RG, PREQ, CG, RW, NSK>(), kernel, dev, THREADS, smem, &per_sm)) return st;
   uint64_t grid = (uint64_t)per_sm * dev->sm_count;
-  if (dev->gemv_split_override) grid = (uint64_t)dev->gemv_split_override * dev->sm_count;  // CTAs per SM, tuning only
+  if (WHOLE) {
+    if (p.stages_per_tile > (uint32_t)NSK || (uint64_t)p.tiles > grid) return DECLINED;
+    grid = p.tiles;
+  }
+  if (dev->gemv_split_override && !WHOLE) grid = (uint64_t)dev->gemv_split_override * dev->sm_count;  // CTAs per SM, tuning only
   if (grid > p.units) grid = p.units;
   // Small problems: fewer, fuller CTAs — about eight stages each, but never fewer than one
   // CTA per SM. Their launches are latency-bound, and independent ones recorded in
   // parallel lanes then share the GPU (measured on 9 MB q4 matrices: 148 CTAs in 8 lanes
   // stream 3.5 TB/s, 256 or 444 CTAs 2.6 to 3.0 TB/s).
-  if (!dev->gemv_split_override && MT <= 2) {
+  if (!dev->gemv_split_override && MT <= 2 && !WHOLE) {
     const uint64_t sms = (uint64_t)dev->sm_count;
     uint64_t want = p.units / 8;
     if (want < sms) want = sms;
@@ -908,12 +917,28 @@ int32_t launch_m(AionCudaDevice* dev, const GemvParams& p, const uint8_t* b, uin
   // weights, and the quantization prologue is a seventh of a CTA's life there: with the small
   // kernel the 9 MB bench shape streams 5.4 - 5.7 TB/s instead of 4.9 - 5.2 (row-major NT weights
   // measured 3 % slower that way and keep the in-kernel prologue).
+  bool overlapped = false;
+  if (dev->recording) {
+    overlapped = dev->cur_lane != 0;
+    for (int l = 1; l < AionCudaDevice::LANES; l++) overlapped = overlapped || dev->lane_forked[l];
+  }
+  // A launch on a dependent chain (a decode step) with a shallow K: one whole tile per CTA and a ring that holds
+  // all of its stages. The weights do not depend on the previous kernel, so all of them are on their way (or
+  // already in shared memory) before that kernel has finished, and once it has, what is left is the activation
+  // image's copy, the arithmetic and the store: no tile is shared, so no partial sums, tickets or second pass.
+  // Measured inside a decode step of 8 requests (1536-wide layers): 5.8 to 10 us per matmul after its
+  // predecessor has finished with the streaming variant.
+  static const bool no_whole = std::getenv("AION_CUDA_GEMV_NO_WHOLE") != nullptr;   // tuning only
+  const bool whole = !no_whole && !overlapped && !dev->gemv_split_override && p.stages_per_tile <= (uint32_t)NS_DEEP && p.m <= 16 &&
+                     (p.m > 1 || image != nullptr);
+  if (whole) {
+    int32_t st;
+    if (p.m == 1) st = launch<DT, NT, 1, true, false, true, 1, 1, NS_DEEP>(dev, p, b, ldb, image);
+    else if (p.m <= 8) st = launch<DT, NT, 1, false, false, true, 1, 1, NS_DEEP>(dev, p, b, ldb, image);
+    else st = launch<DT, NT, 2, false, false, true, 1, 1, NS_DEEP>(dev, p, b, ldb, image);
+    if (st != DECLINED) return st;
+  }
   if (p.m == 1) {
-    bool overlapped = false;
-    if (dev->recording) {
-      overlapped = dev->cur_lane != 0;
-      for (int l = 1; l < AionCudaDevice::LANES; l++) overlapped = overlapped || dev->lane_forked[l];
-    }
     return (image || p.kblocks > 96 || (overlapped && !NT)) ? launch<DT, NT, 1, true, false, true, 1, 1>(dev, p, b, ldb, image)
                                                             : launch<DT, NT, 1, true, false, false, 1, 1>(dev, p, b, ldb, nullptr);
   }

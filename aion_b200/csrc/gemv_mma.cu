@@ -822,8 +822,11 @@ int32_t launch(AionCudaDevice* dev, GemvParams p, const uint8_t* b, uint64_t ldb
   if (int32_t st = kernel_occupancy(setup_of<DT, NT, MT, M1, RG, PREQ, CG, RW, NSK>(), kernel, dev, THREADS, smem, &per_sm)) return st;
   uint64_t grid = (uint64_t)per_sm * dev->sm_count;
   if (WHOLE) {
-    if (p.stages_per_tile > (uint32_t)NSK || (uint64_t)p.tiles > grid) return DECLINED;
-    grid = p.tiles;
+    // A deeper K is cut into ranges of NSK stages: still every weight byte of a CTA in flight at once, and the
+    // few CTAs that share a tile add their parts up as in the streaming variant.
+    const uint64_t want = p.stages_per_tile <= (uint32_t)NSK ? (uint64_t)p.tiles : ceil_div(p.units, (uint64_t)NSK);
+    if (want > grid) return DECLINED;
+    grid = want;
   }
   if (dev->gemv_split_override && !WHOLE) grid = (uint64_t)dev->gemv_split_override * dev->sm_count;  // CTAs per SM, tuning only
   if (grid > p.units) grid = p.units;
@@ -929,7 +932,7 @@ int32_t launch_m(AionCudaDevice* dev, const GemvParams& p, const uint8_t* b, uin
   // Measured inside a decode step of 8 requests (1536-wide layers): 5.8 to 10 us per matmul after its
   // predecessor has finished with the streaming variant.
   static const bool no_whole = std::getenv("AION_CUDA_GEMV_NO_WHOLE") != nullptr;   // tuning only
-  const bool whole = !no_whole && !overlapped && !dev->gemv_split_override && p.stages_per_tile <= (uint32_t)NS_DEEP && p.m <= 16 &&
+  const bool whole = !no_whole && !overlapped && !dev->gemv_split_override && p.m <= 16 &&
                      (p.m > 1 || image != nullptr);
   if (whole) {
     int32_t st;

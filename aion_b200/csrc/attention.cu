@@ -820,6 +820,7 @@ int32_t launch_decode_as(AionCudaDevice* dev, const AttnParams& p, uint32_t unit
   cfg.attrs = attr;
   static const bool no_pdl_main = std::getenv("AION_CUDA_NO_PDL_MAIN") != nullptr;  // tuning only
   cfg.numAttrs = no_pdl_main ? 0 : 1;
+  prefer_max_shared(reinterpret_cast<const void*>(kernel));
   AION_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, p, tk, tv));
   return AION_CUDA_OK;
 }

@@ -10,6 +10,9 @@
 #include <stdint.h>
 
 #include <cstdarg>
+#include <mutex>
+#include <set>
+#include <utility>
 #include <cstdio>
 
 #include "../../include/aion_cuda.h"
@@ -151,8 +154,24 @@ int32_t tensor_map_f32_sw128(const void* base, uint64_t rows, uint64_t cols, uin
 // reads anything an earlier kernel wrote (the wait returns when the predecessors have
 // completed and their writes are visible) and ptx::pdl_launch_dependents() to let its own
 // successor start early.
+// Every kernel of the library asks for the largest shared-memory carve-out, whatever it uses itself. An SM
+// changes its split between L1 and shared memory only while no CTA runs on it, so a kernel that needs a
+// different split from the one running cannot start under it: with programmatic dependent launch that cost
+// a matmul its head start (its CTAs, and with them its weight copies, began only when the small kernel before
+// it had finished: measured 3 us later). Once per kernel and device.
+inline void prefer_max_shared(const void* func) {
+  static std::mutex mu;
+  static std::set<std::pair<int, const void*>> done;
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) return;
+  std::lock_guard<std::mutex> lock(mu);
+  if (done.insert({device, func}).second)
+    cudaFuncSetAttribute(func, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
+}
+
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl_if(bool overlap, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  prefer_max_shared(reinterpret_cast<const void*>(kernel));
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = grid;
   cfg.blockDim = block;

@@ -1189,6 +1189,7 @@ int32_t launch_gemm_pair(AionCudaDevice* dev, const MatMulArgs& g, const __nv_bf
   cfg.attrs = attr;
   static const bool overlap = std::getenv("AION_CUDA_NO_PDL_MAIN") == nullptr;  // tuning only
   cfg.numAttrs = overlap ? 2 : 1;
+  prefer_max_shared(reinterpret_cast<const void*>(kernel));
   AION_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, p, tmap_a, tmap_b, tmap_c));
   if (splits > 1) {
     const uint64_t quads = (uint64_t)g.m * (g.n / 4);

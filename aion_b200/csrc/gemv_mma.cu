@@ -51,6 +51,7 @@ namespace {
 constexpr int KBT = 8;             // K blocks per stage
 constexpr int NS = 2;              // stages in the ring: shallow, so that more CTAs (of concurrent launches) fit an SM
 constexpr int NS_DEEP = 8;         // the ring of the variant that holds a whole tile (up to 64 K blocks) per CTA
+constexpr int KW_DEEP = 4;         // and its groups of consumer warps, which take the tile's stages in turn
 constexpr int COL_WARPS = 4;                    // consumer warps side by side over a tile's columns
 constexpr int threads_of(int rw) { return (COL_WARPS * rw + 1) * 32; }
 constexpr int NT_ROW_PITCH = KBT * Q8_BYTES;  // 272: 16-byte multiple, 4 words mod 32 banks
@@ -321,16 +322,22 @@ __global__ void gemv_act_image_kernel(const float* __restrict__ a, uint64_t lda,
 // bandwidth they reach together: the one- and two-MMA variants are held to the registers that
 // leave room for seven CTAs per SM (fewer registers measured 4.9 - 5.3 TB/s on 9 MB matrices
 // in eight lanes, more 4.6 - 4.8).
-constexpr int min_ctas_per_sm(int mt, int cg, int rw) { return rw == 2 ? 2 : (mt * cg <= 2 ? 7 : 1); }
+constexpr int min_ctas_per_sm(int mt, int cg, int rw, int kw = 1) { return kw > 1 ? 2 : (rw == 2 ? 2 : (mt * cg <= 2 ? 7 : 1)); }
 
-template <int DT, bool NT, int MT, bool M1, bool RG, bool PREQ, int CG, int RW, int NSK = NS>
-__global__ void __launch_bounds__(threads_of(RW), min_ctas_per_sm(MT, CG, RW)) gemv_q_mma_kernel(const GemvParams p_in, const __grid_constant__ CUtensorMap tmap) {
+// KW: groups of consumer warps that share a tile's columns and take its stages in turn (stage i goes to group
+// i % KW); the groups' sums are added through shared memory when the tile ends. One CTA alone on its tile is
+// bound by the latency of a warp's own instruction stream (about 0.6 us per stage with four warps on the SM),
+// so the whole-tile variant spreads the stages of a tile over four groups.
+template <int DT, bool NT, int MT, bool M1, bool RG, bool PREQ, int CG, int RW, int NSK = NS, int KW = 1>
+__global__ void __launch_bounds__(threads_of(RW * KW), min_ctas_per_sm(MT, CG, RW, KW)) gemv_q_mma_kernel(const GemvParams p_in, const __grid_constant__ CUtensorMap tmap) {
   using G = Geom<DT, NT, CG, NSK>;
   constexpr int TN = G::TN;
   constexpr int MPA = 8 * MT;  // activation rows of the accumulator tile
   constexpr int MTW = MT / RW;  // groups of 8 rows per warp
-  constexpr int CONSUMER_WARPS = COL_WARPS * RW, CONSUMER_THREADS = CONSUMER_WARPS * 32;
+  constexpr int GROUP_WARPS = COL_WARPS * RW;   // the warps that consume one stage together
+  constexpr int CONSUMER_WARPS = GROUP_WARPS * KW, CONSUMER_THREADS = CONSUMER_WARPS * 32;
   static_assert(MT % RW == 0, "row groups divide over the row warps");
+  static_assert(KW == 1 || (RW == 1 && PREQ && !RG), "stage groups exist for the single-row-group variants that read an activation image");
   // RG: A has more than 8 * MT rows. The tile index then runs over (group of rows, column tile),
   // group-major, and every group streams the weights again (the later ones find them in L2).
   const GemvParams& p = p_in;
@@ -341,7 +348,8 @@ __global__ void __launch_bounds__(threads_of(RW), min_ctas_per_sm(MT, CG, RW)) g
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, j = lane & 3;
-  const int wc = warp % COL_WARPS, wr = warp / COL_WARPS;  // consumer warp: column position, row half
+  const int wc = warp % COL_WARPS, wr = (warp / COL_WARPS) % RW;  // consumer warp: column position, row half
+  const int wk = warp / GROUP_WARPS;                              // its stage group
 
   const uint64_t U = p.units, NG = n_ctas;
   const uint32_t Sg = p.stages_per_tile;
@@ -370,7 +378,7 @@ __global__ void __launch_bounds__(threads_of(RW), min_ctas_per_sm(MT, CG, RW)) g
       ptx::prefetch_tensormap(&tmap);
       for (int s = 0; s < NSK; s++) {
         ptx::mbar_init(bar_full + 8 * s, 1);
-        ptx::mbar_init(bar_empty + 8 * s, CONSUMER_WARPS);
+        ptx::mbar_init(bar_empty + 8 * s, GROUP_WARPS);
       }
       *abort_flag = 0;
       ptx::fence_barrier_init();
@@ -516,14 +524,15 @@ __global__ void __launch_bounds__(threads_of(RW), min_ctas_per_sm(MT, CG, RW)) g
   uint64_t it = 0;
   for (uint64_t uu = u_begin; uu < u_end; uu++, it++) {
     const uint32_t slot = (uint32_t)(it % NSK);
-    if (ok && (*abort_flag || !ptx::mbar_wait_bounded(bar_full + 8 * slot, (uint32_t)(it / NSK) & 1, p.wait_limit))) {
+    const bool my_stage = KW == 1 || (uint32_t)(it % KW) == (uint32_t)wk;
+    if (my_stage && ok && (*abort_flag || !ptx::mbar_wait_bounded(bar_full + 8 * slot, (uint32_t)(it / NSK) & 1, p.wait_limit))) {
       if (lane == 0 && !*abort_flag) {
         atomicExch(p.fault, FAULT_WAIT_EXPIRED);
         *abort_flag = 1;
       }
       ok = false;
     }
-    if (ok) {
+    if (my_stage && ok) {
       // K blocks past the end of K arrive as zero-filled weights against zero-scaled
       // activations, so all 8 blocks of a stage are always processed.
       uint32_t b0 = smem_base + slot * G::STAGE_BYTES + off0, b1 = smem_base + slot * G::STAGE_BYTES + off1;  // block starts
@@ -561,9 +570,39 @@ __global__ void __launch_bounds__(threads_of(RW), min_ctas_per_sm(MT, CG, RW)) g
       static_assert(KBT == 8, "eight K blocks per stage are spelled out above");
     }
     __syncwarp();
-    if (lane == 0) ptx::mbar_arrive(bar_empty + 8 * slot);
+    if (my_stage && lane == 0) ptx::mbar_arrive(bar_empty + 8 * slot);
 
     if (s == Sg - 1 || uu == u_end - 1) {
+      if (KW > 1) {
+        // The stage groups' sums meet in shared memory; group 0 adds them in group order and carries on alone.
+        uint64_t* red = reinterpret_cast<uint64_t*>(smem + G::OFF_ACT + (size_t)NSK * act_bytes(KBT, MP2));
+        constexpr int PER = MTW * CG * 2;
+        if (wk > 0) {
+#pragma unroll
+          for (int t = 0; t < MTW; t++)
+#pragma unroll
+            for (int c = 0; c < CG; c++) {
+              red[((size_t)(wk - 1) * (GROUP_WARPS * 32) + (tid % (GROUP_WARPS * 32))) * PER + (t * CG + c) * 2] = acc[t][c][0];
+              red[((size_t)(wk - 1) * (GROUP_WARPS * 32) + (tid % (GROUP_WARPS * 32))) * PER + (t * CG + c) * 2 + 1] = acc[t][c][1];
+              acc[t][c][0] = acc[t][c][1] = 0ull;
+            }
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_THREADS) : "memory");
+        if (wk == 0) {
+          for (int k2 = 0; k2 < KW - 1; k2++)
+#pragma unroll
+            for (int t = 0; t < MTW; t++)
+#pragma unroll
+              for (int c = 0; c < CG; c++) {
+                const uint64_t x0 = red[((size_t)k2 * (GROUP_WARPS * 32) + tid) * PER + (t * CG + c) * 2];
+                const uint64_t x1 = red[((size_t)k2 * (GROUP_WARPS * 32) + tid) * PER + (t * CG + c) * 2 + 1];
+                asm("add.rn.f32x2 %0, %0, %1;" : "+l"(acc[t][c][0]) : "l"(x0));
+                asm("add.rn.f32x2 %0, %0, %1;" : "+l"(acc[t][c][1]) : "l"(x1));
+              }
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_THREADS) : "memory");   // the buffer is free for the CTA's next tile
+      }
+      if (KW == 1 || wk == 0) {
       // ---------------- this CTA's share of `tile` is complete ----------------
       const uint64_t tile_u0 = (uint64_t)tile * Sg;
       const bool whole = (uu + 1 - tile_u0 == Sg) && (tile_u0 >= u_begin);
@@ -601,7 +640,7 @@ __global__ void __launch_bounds__(threads_of(RW), min_ctas_per_sm(MT, CG, RW)) g
         __syncwarp();
         int last = 0;
         if (lane == 0) {
-          int* tk = p.tickets + (size_t)tile * CONSUMER_WARPS + warp;
+          int* tk = p.tickets + (size_t)tile * GROUP_WARPS + warp;
           int prev;
           asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(prev) : "l"(tk) : "memory");
           last = (prev == (int)nparts - 1);
@@ -678,6 +717,7 @@ __global__ void __launch_bounds__(threads_of(RW), min_ctas_per_sm(MT, CG, RW)) g
                 }
               }
             }
+      }
       }
     }
     if (++s == Sg) {
@@ -768,7 +808,7 @@ int32_t kernel_occupancy(KernelSetup& ks, Kernel kernel, AionCudaDevice* dev, in
   return AION_CUDA_OK;
 }
 
-template <int DT, bool NT, int MT, bool M1, bool RG, bool PREQ, int CG, int RW, int NSK = NS>
+template <int DT, bool NT, int MT, bool M1, bool RG, bool PREQ, int CG, int RW, int NSK = NS, int KW = 1>
 KernelSetup& setup_of() {
   static KernelSetup ks;
   return ks;
@@ -809,17 +849,18 @@ int32_t encode_weight_map(const uint8_t* b, uint64_t ldb, uint32_t n, uint32_t k
 // Returned by the whole-tile variant when the shape does not suit it; the caller then takes the streaming one.
 constexpr int32_t DECLINED = -0x7A11;
 
-template <int DT, bool NT, int MT, bool M1, bool RG, bool PREQ, int CG, int RW, int NSK = NS>
+template <int DT, bool NT, int MT, bool M1, bool RG, bool PREQ, int CG, int RW, int NSK = NS, int KW = 1>
 int32_t launch(AionCudaDevice* dev, GemvParams p, const uint8_t* b, uint64_t ldb, const uint8_t* given_image) {
   using G = Geom<DT, NT, CG, NSK>;
   constexpr int TN = G::TN;
-  constexpr int THREADS = threads_of(RW);
+  constexpr int THREADS = threads_of(RW * KW);
   constexpr bool WHOLE = NSK != NS;   // one whole tile per CTA, every stage of it in the ring at once
-  auto kernel = gemv_q_mma_kernel<DT, NT, MT, M1, RG, PREQ, CG, RW, NSK>;
+  auto kernel = gemv_q_mma_kernel<DT, NT, MT, M1, RG, PREQ, CG, RW, NSK, KW>;
   constexpr uint32_t MP2 = M1 ? 2 : 8 * MT;
-  const size_t smem = G::OFF_ACT + (PREQ ? (size_t)NSK * act_bytes(KBT, MP2) : act_bytes(p.stages_per_tile * KBT, MP2));
+  constexpr size_t RED_BYTES = (size_t)(KW - 1) * COL_WARPS * RW * 32 * (MT / RW) * CG * 2 * sizeof(uint64_t);   // the stage groups' sums
+  const size_t smem = G::OFF_ACT + (PREQ ? (size_t)NSK * act_bytes(KBT, MP2) : act_bytes(p.stages_per_tile * KBT, MP2)) + RED_BYTES;
   int per_sm = 0;
-  if (int32_t st = kernel_occupancy(setup_of<DT, NT, MT, M1, RG, PREQ, CG, RW, NSK>(), kernel, dev, THREADS, smem, &per_sm)) return st;
+  if (int32_t st = kernel_occupancy(setup_of<DT, NT, MT, M1, RG, PREQ, CG, RW, NSK, KW>(), kernel, dev, THREADS, smem, &per_sm)) return st;
   uint64_t grid = (uint64_t)per_sm * dev->sm_count;
   if (WHOLE) {
     // A deeper K is cut into ranges of NSK stages: still every weight byte of a CTA in flight at once, and the
@@ -887,6 +928,7 @@ int32_t launch(AionCudaDevice* dev, GemvParams p, const uint8_t* b, uint64_t ldb
       iattrs[0].val.programmaticStreamSerializationAllowed = 1;
       icfg.attrs = iattrs;
       icfg.numAttrs = no_pdl_main ? 0 : 1;
+      prefer_max_shared(reinterpret_cast<const void*>(gemv_act_image_kernel<DT>));
       AION_CUDA_TRY(cudaLaunchKernelEx(&icfg, gemv_act_image_kernel<DT>, p.a, p.lda, p.m, p.kblocks, L, image, p.a_vec4));
       p.act_image = image;
     }
@@ -906,6 +948,7 @@ int32_t launch(AionCudaDevice* dev, GemvParams p, const uint8_t* b, uint64_t ldb
   attrs[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attrs;
   cfg.numAttrs = no_pdl_main ? 0 : 1;
+  prefer_max_shared(reinterpret_cast<const void*>(kernel));
   AION_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, p, *tm));
   return AION_CUDA_OK;
 }
@@ -936,9 +979,9 @@ int32_t launch_m(AionCudaDevice* dev, const GemvParams& p, const uint8_t* b, uin
                      (p.m > 1 || image != nullptr);
   if (whole) {
     int32_t st;
-    if (p.m == 1) st = launch<DT, NT, 1, true, false, true, 1, 1, NS_DEEP>(dev, p, b, ldb, image);
-    else if (p.m <= 8) st = launch<DT, NT, 1, false, false, true, 1, 1, NS_DEEP>(dev, p, b, ldb, image);
-    else st = launch<DT, NT, 2, false, false, true, 1, 1, NS_DEEP>(dev, p, b, ldb, image);
+    if (p.m == 1) st = launch<DT, NT, 1, true, false, true, 1, 1, NS_DEEP, KW_DEEP>(dev, p, b, ldb, image);
+    else if (p.m <= 8) st = launch<DT, NT, 1, false, false, true, 1, 1, NS_DEEP, KW_DEEP>(dev, p, b, ldb, image);
+    else st = launch<DT, NT, 2, false, false, true, 1, 1, NS_DEEP, KW_DEEP>(dev, p, b, ldb, image);
     if (st != DECLINED) return st;
   }
   if (p.m == 1) {
@@ -1095,6 +1138,7 @@ int32_t launch_static(AionCudaDevice* dev, GemvParams p, const uint8_t* b, uint6
   cfg.blockDim = dim3(THREADS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = dev->stream;
+  prefer_max_shared(reinterpret_cast<const void*>(kernel));
   AION_CUDA_TRY(cudaLaunchKernelEx(&cfg, kernel, p, *tm));
   return AION_CUDA_OK;
 }

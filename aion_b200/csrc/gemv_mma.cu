@@ -975,8 +975,7 @@ int32_t launch_m(AionCudaDevice* dev, const GemvParams& p, const uint8_t* b, uin
   // Measured inside a decode step of 8 requests (1536-wide layers): 5.8 to 10 us per matmul after its
   // predecessor has finished with the streaming variant.
   static const bool no_whole = std::getenv("AION_CUDA_GEMV_NO_WHOLE") != nullptr;   // tuning only
-  const bool whole = !no_whole && !overlapped && !dev->gemv_split_override && p.m <= 16 &&
-                     (p.m > 1 || image != nullptr);
+  const bool whole = !no_whole && !overlapped && !dev->gemv_split_override && p.m <= 16;
   if (whole) {
     int32_t st;
     if (p.m == 1) st = launch<DT, NT, 1, true, false, true, 1, 1, NS_DEEP, KW_DEEP>(dev, p, b, ldb, image);

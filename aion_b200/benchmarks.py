@@ -476,7 +476,7 @@ def _colsplit_peer_stores(torch, dist, backend, rank, world, local_rank, m, n, k
             try:
                 fn()
             except Exception as ex:  # noqa: BLE001 - reported in the leg's result
-                state["error"] = f"{type(ex).__name__}: {ex}"[:300]
+                state["error"] = f"{fn.__name__}: {type(ex).__name__}: {ex}"[:300]
         bad = torch.tensor([0 if state["error"] is None else 1], device="cuda", dtype=torch.int32)
         dist.all_reduce(bad, op=dist.ReduceOp.MAX)
         if int(bad.item()) and state["error"] is None:
@@ -588,7 +588,10 @@ def _colsplit_peer_stores(torch, dist, backend, rank, world, local_rank, m, n, k
         mem.free(h)
     what = "peer stores from the matmul kernel's epilogue into every rank's y + arrival words + one bounded wait kernel"
     if not ok:
-        return {"error": state["error"], "exchange": what}
+        # every rank's own account, so that the rank that failed first can be told from those that waited for it
+        errors = [None] * world
+        dist.all_gather_object(errors, state["error"])
+        return {"error": state["error"], "errors_by_rank": errors, "exchange": what}
     total_w = (k // 32) * n * 18
     ms = result["ms"]
     return {"ms": round(ms, 4), "aggregate_weight_gbs": round(total_w / (ms * 1e-3) / 1e9, 1), "exchange": what,

@@ -775,12 +775,16 @@ __global__ void __launch_bounds__(threads_of(RW * KW), min_ctas_per_sm(MT, CG, R
 // Waits (bounded) until every rank's arrival word has reached epoch + 1, then advances the epoch.
 // One warp; lane r watches rank r. A wait that runs out reports FAULT_WAIT_EXPIRED and leaves the
 // epoch where it was.
-// Launched with programmatic stream serialization and without a wait for its predecessor: it may start
-// while the matmul that announces this rank's own columns is still running (that matmul does not depend on
-// it, and all of its CTAs have started by then), so the launch is off the critical path. The kernel after
-// it waits for its completion as usual, which is what keeps the epoch read by the next matmul current.
+// Launched with programmatic stream serialization, so its one CTA is resident and its launch off the critical
+// path while the matmul that announces this rank's own columns runs; but it reads the epoch only after that
+// matmul has completed (griddepcontrol.wait). The matmul's CTAs let their dependents start before they wait
+// for their own predecessors, so without that wait this kernel could start while the wait kernel of the step
+// before was still polling, read the epoch that kernel was about to advance, pass at once and leave the epoch
+// one step behind for good: the peers then wait for an arrival word that never comes (seen on 8 GPUs, where a
+// step's wait lasts longest; 2 and 4 GPUs happened to stay clear of it).
 __global__ void peer_wait_kernel(const uint32_t* flags, uint32_t* state, uint32_t world, uint32_t poll_limit, int* fault) {
   ptx::pdl_launch_dependents();
+  ptx::pdl_wait();
   const uint32_t lane = threadIdx.x;
   const uint32_t want = *reinterpret_cast<volatile uint32_t*>(state) + 1;
   bool ok = true;

@@ -37,6 +37,7 @@
 //     adds the parts in CTA order (so results do not depend on timing) and stores C.
 //   * With programmatic dependent launch the next kernel's weight stream starts as this
 //     one's CTAs retire; only the activation read waits for the previous kernel.
+#include <algorithm>
 #include <mutex>
 
 #include "act_image.cuh"
@@ -933,7 +934,14 @@ int32_t launch(AionCudaDevice* dev, GemvParams p, const uint8_t* b, uint64_t ldb
   // times the groups of 8 * MT rows.
   constexpr int MPA = 8 * MT;
   const uint64_t groups = p.tiles / p.col_tiles;
-  if (int32_t st = dev->reserve_gemv_fixup((size_t)grid * 2 * TN * MPA * sizeof(float), (size_t)p.tiles * COL_WARPS * RW)) return st;
+  // (The whole-tile variant also reserves what the streaming variant of the same step would ask for: a step
+  // run once on its own and then recorded into parallel lanes takes that variant, and a recording cannot grow scratch.)
+  uint64_t fix_ctas = grid;
+  if (WHOLE) {
+    const uint64_t streaming = std::min<uint64_t>(p.units, 7ull * (uint64_t)dev->sm_count);
+    if (streaming > fix_ctas) fix_ctas = streaming;
+  }
+  if (int32_t st = dev->reserve_gemv_fixup((size_t)fix_ctas * 2 * TN * MPA * sizeof(float), (size_t)p.tiles * COL_WARPS * RW)) return st;
   p.partials = dev->lane_gemv_partials();
   p.tickets = dev->lane_gemv_tickets();
 

@@ -409,6 +409,51 @@ def test_repeated_launches_are_bitwise_reproducible(backend):
         assert np.array_equal(run_matmul(backend, capi.DTYPE_Q4_0, x, b, m, n, k), first)
 
 
+@pytest.mark.parametrize("dtype", [capi.DTYPE_Q8_0, capi.DTYPE_Q4_0])
+@pytest.mark.parametrize("m", [1, 8, 16])
+@pytest.mark.parametrize("nk", [(520, 1536), (328, 8192)])
+def test_whole_tile_and_streaming_variants_agree_with_the_oracle(backend, dtype, m, nk):
+    """A launch on a chain takes one whole tile per CTA (a deep K: ranges of eight stages); the same step
+    recorded into parallel lanes takes the streaming variant. Both against the reference arithmetic."""
+    n, k = nk
+    lib, dev = backend._lib, backend.handle
+    odt = oracle.Q8_0 if dtype == capi.DTYPE_Q8_0 else oracle.Q4_0
+    xs = [rd.synth_acts(m, k, seed=11 + i) for i in range(2)]
+    b = oracle.quantize(odt, rd.synth_weights(k, n), 0)
+    want = [oracle.matmul_q(odt, x, b, m, n, k) for x in xs]
+    for x, w in zip(xs, want):   # on a chain (not being recorded): whole tiles
+        assert rd.rel_l2(run_matmul(backend, dtype, x, b, m, n, k), w) < TIGHT
+    bufs = [DevBuf(backend, np.ascontiguousarray(b, dtype=np.uint8))]
+    try:
+        recs = []
+        for x in xs:
+            a_buf, c_buf = DevBuf(backend, x), DevBuf(backend, np.zeros(m * n, dtype=np.float32))
+            bufs += [a_buf, c_buf]
+            recs.append((capi.MatMul(c=c_buf.operand(), a=a_buf.operand(), b=bufs[0].operand(), b_dtype=dtype, flags=capi.MATMUL_AUTO,
+                                     m=m, n=n, k=k, lda=0, ldb=0, ldc=0, alpha=1.0, beta=0.0), c_buf))
+        for r, _ in recs:   # the run before the recording reserves scratch
+            assert lib.aion_cuda_matmul(dev, C.byref(r)) == capi.OK
+        assert lib.aion_cuda_record_begin(dev) == capi.OK
+        for i, (r, _) in enumerate(recs):
+            assert lib.aion_cuda_record_lane(dev, 1 + i) == capi.OK   # two parallel lanes: the streaming variant
+            assert lib.aion_cuda_matmul(dev, C.byref(r)) == capi.OK
+        prog = C.c_void_p()
+        assert lib.aion_cuda_record_end(dev, C.byref(prog)) == capi.OK
+        for _, c_buf in recs:
+            backend.device_memory.memset(c_buf.handle, 0, 0, m * n * 4)
+        assert lib.aion_cuda_program_launch(dev, prog) == capi.OK
+        backend.sync()
+        for (_, c_buf), w in zip(recs, want):
+            assert rd.rel_l2(c_buf.read(np.float32).reshape(m, n), w) < TIGHT
+        lib.aion_cuda_program_destroy(dev, prog)
+    finally:
+        for x in bufs:
+            try:
+                x.free()
+            except BackendError:
+                pass   # a failure inside the recording is the one to report
+
+
 # ---- the session interface (reference: Backend / Session / DeviceStore) -----------------
 def test_session_executes_a_program(backend):
     m, n, k = 2, 128, 256

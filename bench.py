@@ -110,7 +110,7 @@ class ClockSampler:
                         self.reasons.add(name)
             except Exception:
                 pass
-            self._stop.wait(0.002)
+            self._stop.wait(0.0005)
 
     def __enter__(self):
         if self._h is not None:

@@ -1013,7 +1013,11 @@ int32_t launch_m(AionCudaDevice* dev, const GemvParams& p, const uint8_t* b, uin
   // Measured inside a decode step of 8 requests (1536-wide layers): 5.8 to 10 us per matmul after its
   // predecessor has finished with the streaming variant.
   static const bool no_whole = std::getenv("AION_CUDA_GEMV_NO_WHOLE") != nullptr;   // tuning only
-  const bool whole = !no_whole && !overlapped && !dev->gemv_split_override && p.m <= 16;
+  // Recorded into parallel lanes, the streaming variant is the faster one (more CTAs of more launches per SM)
+  // except for a small matrix, whose few tiles leave most SMs to the other lanes anyway: 2048 x 2048 q4 in
+  // 8 lanes measured 1.04 us per launch with whole tiles against 1.59 us, 8192 x 2048 2.98 against 1.92 us.
+  const bool few_tiles = p.stages_per_tile <= (uint32_t)NS_DEEP && (uint64_t)p.tiles * 4 <= (uint64_t)dev->sm_count;
+  const bool whole = !no_whole && (!overlapped || few_tiles) && !dev->gemv_split_override && p.m <= 16;
   if (whole) {
     int32_t st;
     if (p.m == 1) st = launch<DT, NT, 1, true, false, true, 1, 1, NS_DEEP, KW_DEEP>(dev, p, b, ldb, image);

@@ -601,10 +601,11 @@ def _colsplit_peer_stores(torch, dist, backend, rank, world, local_rank, m, n, k
 
 
 def matmul_leg(torch, backend: CudaBackend, local_rank: int, dtype: int, nt: bool, m: int, n: int, k: int, lanes: int = 8,
-               iters: int = 20, min_bytes: int = 512 << 20, peak_gbs: float = 6552.3) -> dict:
+               iters: int = 20, min_bytes: int = 2400 << 20, peak_gbs: float = 6552.3) -> dict:
     """Decode-sized matmul (`MatMul` K-major or `MatMulNT` row-major q8) GB/s of algorithmic bytes over
-    enough distinct weight copies (>= 512 MB) that no launch finds its weights in L2; one recorded
-    program per pass, its independent steps spread over `lanes` parallel lanes."""
+    enough distinct weight copies (2.4 GB like the headline pass, at most 256 copies) that no launch finds its
+    weights in L2 and that the lanes' drain at the end of a pass is a small part of it; one recorded program
+    per pass, its independent steps spread over `lanes` parallel lanes."""
     lib, dev, mem = backend._lib, backend.handle, backend.device_memory
     bb = 18 if dtype == capi.DTYPE_Q4_0 else 34
     w_bytes = (k // 32) * n * bb

@@ -920,6 +920,17 @@ int32_t launch(AionCudaDevice* dev, GemvParams p, const uint8_t* b, uint64_t ldb
       for (int l = 1; l < AionCudaDevice::LANES; l++) overlapped = overlapped || dev->lane_forked[l];
     }
     if (overlapped && (uint64_t)p.tiles <= grid && (uint64_t)p.tiles * 5 >= grid * 4) grid = p.tiles;
+    // Tiles shared by several CTAs: a grid that cuts every tile into the same number of equal parts, so that
+    // no CTA straddles two tiles (one set of partial sums and one ticket per CTA, and the parts of a tile end
+    // together). 2048 x 8192 q4 in 8 lanes: 2.16 us per launch with 256 CTAs against 2.47 with 148.
+    if (!WHOLE && (uint64_t)p.tiles < grid) {
+      const uint64_t cap = (uint64_t)per_sm * dev->sm_count;
+      for (uint64_t d = 1; d <= p.stages_per_tile; d++)
+        if (p.stages_per_tile % d == 0 && (uint64_t)p.tiles * d >= grid) {
+          if ((uint64_t)p.tiles * d <= cap) grid = (uint64_t)p.tiles * d;
+          break;
+        }
+    }
   }
   // At least as many tiles as CTAs: hand out whole tiles, so that no tile is shared and the
   // partial-sum fix-up (two more L2 round trips at the end of a short kernel) is skipped —

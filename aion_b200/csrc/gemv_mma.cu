@@ -338,7 +338,7 @@ __global__ void __launch_bounds__(threads_of(RW * KW), min_ctas_per_sm(MT, CG, R
   constexpr int GROUP_WARPS = COL_WARPS * RW;   // the warps that consume one stage together
   constexpr int CONSUMER_WARPS = GROUP_WARPS * KW, CONSUMER_THREADS = CONSUMER_WARPS * 32;
   static_assert(MT % RW == 0, "row groups divide over the row warps");
-  static_assert(KW == 1 || (RW == 1 && PREQ && !RG), "stage groups exist for the single-row-group variants that read an activation image");
+  static_assert(KW == 1 || (RW == 1 && !RG), "stage groups exist for the variants with a single group of rows");
   // RG: A has more than 8 * MT rows. The tile index then runs over (group of rows, column tile),
   // group-major, and every group streams the weights again (the later ones find them in L2).
   const GemvParams& p = p_in;
@@ -602,7 +602,7 @@ __global__ void __launch_bounds__(threads_of(RW * KW), min_ctas_per_sm(MT, CG, R
     if (s == Sg - 1 || uu == u_end - 1) {
       if (KW > 1) {
         // The stage groups' sums meet in shared memory; group 0 adds them in group order and carries on alone.
-        uint64_t* red = reinterpret_cast<uint64_t*>(smem + G::OFF_ACT + (size_t)NSK * act_bytes(KBT, MP2));
+        uint64_t* red = reinterpret_cast<uint64_t*>(smem + G::OFF_ACT + (PREQ ? (size_t)NSK * act_bytes(KBT, MP2) : act_bytes(kb_pad, MP2)));
         constexpr int PER = MTW * CG * 2;
         if (wk > 0) {
 #pragma unroll
@@ -1031,7 +1031,10 @@ int32_t launch_m(AionCudaDevice* dev, const GemvParams& p, const uint8_t* b, uin
   const bool whole = !no_whole && (!overlapped || few_tiles) && !dev->gemv_split_override && p.m <= 16;
   if (whole) {
     int32_t st;
-    if (p.m == 1) st = launch<DT, NT, 1, true, false, true, 1, 1, NS_DEEP, KW_DEEP>(dev, p, b, ldb, image);
+    // A single row without an image and a K of at most eight stages: the CTA quantizes the row itself while its
+    // weights are on their way (one kernel less on the chain than with the image kernel in front).
+    if (p.m == 1 && !image && p.stages_per_tile <= (uint32_t)NS_DEEP) st = launch<DT, NT, 1, true, false, false, 1, 1, NS_DEEP, KW_DEEP>(dev, p, b, ldb, nullptr);
+    else if (p.m == 1) st = launch<DT, NT, 1, true, false, true, 1, 1, NS_DEEP, KW_DEEP>(dev, p, b, ldb, image);
     else if (p.m <= 8) st = launch<DT, NT, 1, false, false, true, 1, 1, NS_DEEP, KW_DEEP>(dev, p, b, ldb, image);
     else st = launch<DT, NT, 2, false, false, true, 1, 1, NS_DEEP, KW_DEEP>(dev, p, b, ldb, image);
     if (st != DECLINED) return st;

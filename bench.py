@@ -80,6 +80,8 @@ class ClockSampler:
 
     def __init__(self, torch_device_index: int):
         self.samples = []
+        self.stamped = []     # (time, MHz, reason mask) of every sample
+        self.window = None    # (begin, end) of the timed region, when the sampler was started ahead of it
         self.reasons = set()
         self.max_mhz = None
         self._stop = threading.Event()
@@ -103,8 +105,10 @@ class ClockSampler:
         nv = self._nv
         while not self._stop.is_set():
             try:
-                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
+                mhz = int(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
                 mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self._h))
+                self.samples.append(mhz)
+                self.stamped.append((time.perf_counter(), mhz, mask))
                 for bit, name in self.REASONS.items():
                     if mask & bit:
                         self.reasons.add(name)
@@ -123,7 +127,20 @@ class ClockSampler:
         if self._thread:
             self._thread.join()
 
+    def begin_window(self):
+        """The timed region starts now (the sampler thread is already running: its first reading takes a few ms)."""
+        self.window = (time.perf_counter(), None)
+
+    def end_window(self):
+        self.window = (self.window[0], time.perf_counter())
+
     def summary(self):
+        if self.window and self.window[1] is not None:
+            inside = [(m, k) for t, m, k in self.stamped if self.window[0] <= t <= self.window[1]]
+            if inside:
+                reasons = sorted({name for _, k in inside for bit, name in self.REASONS.items() if k & bit})
+                return {"sm_mhz": int(np.median([m for m, _ in inside])), "sm_max_mhz": self.max_mhz, "reasons": reasons,
+                        "samples": len(inside), "over": "the timed steps"}
         if not self.samples:
             return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": 0}
         return {"sm_mhz": int(np.median(self.samples)), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
@@ -201,16 +218,18 @@ def run_ours(args):
         if world > 1:
             dist.barrier()
 
-    for _ in range(max(args.warmup, 3)):
-        chk(lib.aion_cuda_program_launch(dev, prog))
-    barrier()
-    with ClockSampler(local_rank) as clocks:
+    with ClockSampler(local_rank) as clocks:   # started ahead of the warm-up; only readings inside the timed region count
+        for _ in range(max(args.warmup, 3)):
+            chk(lib.aion_cuda_program_launch(dev, prog))
+        barrier()
+        clocks.begin_window()
         ev0.record(stream)
         for _ in range(args.steps):
             chk(lib.aion_cuda_program_launch(dev, prog))
         ev1.record(stream)
         backend.sync()
         torch.cuda.synchronize()
+        clocks.end_window()
     elapsed_ms = ev0.elapsed_time(ev1)
     if world > 1:
         t = torch.tensor([elapsed_ms], device="cuda", dtype=torch.float64)

@@ -351,16 +351,18 @@ gemm_q_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  // Everything above touched only this CTA's shared and tensor memory; the activation (and,
-  // in a recorded program, possibly C) comes from earlier kernels.
+  // Everything above touched only this CTA's shared and tensor memory. The activation (and C, and the scratch
+  // of the split partials) belong to earlier kernels: the warp that loads activation tiles and the epilogue
+  // warps wait for those (griddepcontrol.wait). The packed weights do not, so their loads and their unpacking
+  // start at once: on a decode chain the first dequantized tiles are ready before the activation exists.
   ptx::pdl_launch_dependents();
-  ptx::pdl_wait();
   const uint32_t tmem_base = bars->tmem_base;
   const uint32_t units = p.m_tiles * p.n_tiles * p.splits;
 
   if (warp == 0) {
     // ---- TMA producer of activation tiles ----
     if (lane == 0) {
+      ptx::pdl_wait();
       uint32_t it = 0;
       bool ok = true;
       for (uint32_t u = blockIdx.x; u < units && ok; u += gridDim.x) {
@@ -481,6 +483,7 @@ gemm_q_tcgen05_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tm
     }
   } else {
     // ---- epilogue: warp w may touch TMEM lanes 32*(w%4) .. +31 ----
+    ptx::pdl_wait();
     const uint32_t quarter = warp & 3;
     uint32_t tile_iter = 0;
     for (uint32_t u = blockIdx.x; u < units; u += gridDim.x, tile_iter++) {
@@ -741,8 +744,8 @@ gemm_q_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_
   __syncthreads();
   cluster_sync_all();   // the other CTA's barriers and tensor memory exist from here on
   tc_fence_after();
+  // (as in the one-SM kernel: only the activation loads and the epilogue wait for the earlier kernels)
   ptx::pdl_launch_dependents();
-  ptx::pdl_wait();
   const uint32_t tmem_base = bars->tmem_base;
   const uint32_t units = p.m_tiles * p.n_tiles * p.splits;
   const uint32_t pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
@@ -750,6 +753,7 @@ gemm_q_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_
   if (warp == 0) {
     // ---- TMA producer of this CTA's activation rows ----
     if (lane == 0) {
+      ptx::pdl_wait();
       uint32_t it = 0;
       bool ok = true;
       for (uint32_t u = pair; u < units && ok; u += pairs) {
@@ -869,6 +873,7 @@ gemm_q_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_
     }
   } else {
     // ---- epilogue: this CTA's 128 accumulator lanes = its 128 tokens of every half ----
+    ptx::pdl_wait();
     // Plain outputs (no beta, no K split) leave through shared memory: 32 columns of a warp's 32
     // rows at a time are staged (128-byte swizzle, so the stores spread over the banks) and written
     // by one bulk tensor store, which clips the rows past m and the columns past n. A thread

@@ -1012,9 +1012,10 @@ __global__ void splitk_reduce_kernel(const GemmParams p) {
 // re-laid as K-major [k/32][n] blocks for the GEMM. Both layouts quantize along K, so a block
 // holds the same 34 bytes either way: this is a permutation of blocks. One thread per block,
 // n fastest, so the K-major writes are contiguous.
+// (It does not release its dependents early: what it writes are WEIGHTS, and the matmul kernels start their
+// weight loads without waiting for the kernel before them. Its dependents therefore start when it has completed.)
 __global__ void nt_to_kmajor_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, uint64_t n, uint64_t kblocks,
                                     int group, int chunk) {
-  ptx::pdl_launch_dependents();
   ptx::pdl_wait();
   const uint64_t total = n * kblocks;
   for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
@@ -1038,8 +1039,7 @@ __global__ void nt_to_kmajor_kernel(const uint8_t* __restrict__ src, uint8_t* __
 constexpr int RT_ROWS = 64, RT_KB = 16, RT_UNITS = Q8_BYTES / 2, RT_PITCH = RT_KB * RT_UNITS + 1;
 __global__ void __launch_bounds__(256) nt_rowmajor_to_kmajor_kernel(const uint16_t* __restrict__ src, uint16_t* __restrict__ dst,
                                                                     uint64_t n, uint64_t kblocks) {
-  ptx::pdl_launch_dependents();
-  ptx::pdl_wait();
+  ptx::pdl_wait();   // (no early release of its dependents, for the same reason)
   __shared__ uint16_t tile[RT_ROWS * RT_PITCH];
   const uint64_t r0 = (uint64_t)blockIdx.x * RT_ROWS, kb0 = (uint64_t)blockIdx.y * RT_KB;
   const uint32_t rows = (uint32_t)min((uint64_t)RT_ROWS, n - r0), kbs = (uint32_t)min((uint64_t)RT_KB, kblocks - kb0);

@@ -76,6 +76,44 @@ def test_derived_kmajor_weight_is_the_block_transpose(backend, order, n, k):
     assert rd.rel_l2(c_km, want_c) < 2e-5 and rd.rel_l2(c_nt, want_c) < 2e-5
 
 
+@pytest.mark.parametrize("m", [4, 64])
+@pytest.mark.parametrize("order", [0, 3])
+def test_a_matmul_issued_right_after_the_derivation_reads_the_finished_weight(backend, order, m):
+    """The matmul kernels start their weight loads without waiting for the kernel before them, so a kernel that
+    writes weights must not let its successors start early: derive, then multiply, with nothing in between,
+    over a matrix large enough that the derivation is still running when the matmul is issued."""
+    import ctypes as C
+    n, k = 8192, 2048
+    rows = oracle.quantize(oracle.Q8_0, rd.synth_weights(n, k), 1)
+    stored = rows if order == 0 else oracle.relayout_q8(order, n, k, rows)
+    a = rd.synth_acts(m, k)
+    mem, lib, dev = backend.device_memory, backend._lib, backend.handle
+    nb = stored.nbytes
+    hs, hd, ha, hc = mem.alloc(nb), mem.alloc(nb), mem.alloc(a.nbytes), mem.alloc(m * n * 4)
+    try:
+        mem.copy_h2d(hs, 0, np.ascontiguousarray(stored, dtype=np.uint8))
+        mem.copy_h2d(ha, 0, a)
+        mem.memset(hd, 0, 0, nb)
+        backend.sync()
+        so, do = capi.Operand(hs, 0, nb), capi.Operand(hd, 0, nb)
+        rec = capi.MatMul(c=capi.Operand(hc, 0, m * n * 4), a=capi.Operand(ha, 0, a.nbytes), b=do, b_dtype=capi.DTYPE_Q8_0,
+                          flags=capi.MATMUL_AUTO, m=m, n=n, k=k, lda=0, ldb=0, ldc=0, alpha=1.0, beta=0.0)
+        for rnd in range(3):   # the first round sizes scratch (and may synchronize); the later ones run back to back
+            if rnd:
+                mem.memset(hd, 0, 0, nb)   # a matmul that read too early would see zero weights
+            assert lib.aion_cuda_derive_kmajor_q8(dev, order, n, k, C.byref(so), C.byref(do)) == capi.OK
+            assert lib.aion_cuda_matmul(dev, C.byref(rec)) == capi.OK
+        backend.sync()
+        got = np.empty(m * n, dtype=np.float32)
+        mem.copy_d2h(got, hc, 0)
+        want = oracle.matmul_nt_q8(a, rows, m, n, k)   # the reference's int8 arithmetic over the same blocks
+        tol = 2e-5 if m <= 32 else 1e-2
+        assert rd.rel_l2(got.reshape(m, n), want) < tol
+    finally:
+        for h in (hs, hd, ha, hc):
+            mem.free(h)
+
+
 def test_quantize_rejects_bad_arguments(backend):
     with pytest.raises(ab.BackendError) as e:
         ab.quantize(backend, capi.DTYPE_Q8_0, np.zeros((33, 4), dtype=np.float32), 0)

@@ -37,6 +37,13 @@
 //     adds the parts in CTA order (so results do not depend on timing) and stores C.
 //   * With programmatic dependent launch the next kernel's weight stream starts as this
 //     one's CTAs retire; only the activation read waits for the previous kernel.
+//   * Launches on a dependent chain (a decode step; up to 16 rows) take the whole-tile variant:
+//     one tile per CTA (a deep K: a range of eight stages), a ring that holds all of its stages,
+//     the producer warp's lanes issuing them side by side, and four groups of consumer warps
+//     taking the stages in turn and adding their sums through shared memory. Every weight byte of
+//     the CTA is under way before the previous kernel has finished, and no tile is shared, so
+//     there are no partial sums to exchange. Launches recorded into parallel lanes keep the
+//     streaming variant above (more CTAs of more launches per SM), except for small matrices.
 #include <algorithm>
 #include <mutex>
 

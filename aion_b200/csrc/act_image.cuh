@@ -183,70 +183,4 @@ __device__ __forceinline__ void quantize_store_block_8lanes(float4 v, uint32_t i
   }
 }
 
-// The same for N blocks at once (a thread that owns N float4 columns of N different rows): every step
-// is written across the N blocks, so that the N dependent chains (shuffles, the two divisions, the
-// roundings) overlap instead of running one after the other — which is what a kernel with four warps
-// on its SM needs; block after block this was 1600 cycles per block at the tail of the attention kernel.
-template <int DT, int N>
-__device__ __forceinline__ void quantize_store_blocks_8lanes(const float4 (&v)[N], uint32_t i, const bool (&store)[N], uint8_t* image,
-                                                             const ActImageLayout& L, const uint32_t (&row)[N], const uint32_t (&kb)[N]) {
-  float amax[N], scale[N], inv[N];
-#pragma unroll
-  for (int c = 0; c < N; c++) amax[c] = fmaxf(fmaxf(fabsf(v[c].x), fabsf(v[c].y)), fmaxf(fabsf(v[c].z), fabsf(v[c].w)));
-#pragma unroll
-  for (int o = 1; o < 8; o <<= 1)
-#pragma unroll
-    for (int c = 0; c < N; c++) amax[c] = fmaxf(amax[c], __shfl_xor_sync(0xFFFFFFFFu, amax[c], o));
-#pragma unroll
-  for (int c = 0; c < N; c++) activation_block_scales(amax[c], &scale[c], &inv[c]);
-  int q[N][4];
-#pragma unroll
-  for (int c = 0; c < N; c++) {
-    q[c][0] = quantize_activation_with_inv(v[c].x, inv[c]);
-    q[c][1] = quantize_activation_with_inv(v[c].y, inv[c]);
-    q[c][2] = quantize_activation_with_inv(v[c].z, inv[c]);
-    q[c][3] = quantize_activation_with_inv(v[c].w, inv[c]);
-  }
-  if (L.kind == ACT_IMAGE_BF16) {
-    uint2 out[N];
-#pragma unroll
-    for (int c = 0; c < N; c++) {
-      __nv_bfloat162 lo = __floats2bfloat162_rn(__fmul_rn((float)q[c][0], scale[c]), __fmul_rn((float)q[c][1], scale[c]));
-      __nv_bfloat162 hi = __floats2bfloat162_rn(__fmul_rn((float)q[c][2], scale[c]), __fmul_rn((float)q[c][3], scale[c]));
-      out[c] = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
-    }
-    if (DT == AION_CUDA_DTYPE_Q4_0) {
-#pragma unroll
-      for (int c = 0; c < N; c++) {
-        const uint32_t plo = __shfl_xor_sync(0xFFFFFFFFu, out[c].x, 1), phi = __shfl_xor_sync(0xFFFFFFFFu, out[c].y, 1);
-        if (i & 1) out[c] = make_uint2(__byte_perm(phi, out[c].y, 0x5410), __byte_perm(phi, out[c].y, 0x7632));
-        else out[c] = make_uint2(__byte_perm(out[c].x, plo, 0x5410), __byte_perm(out[c].x, plo, 0x7632));
-      }
-    }
-#pragma unroll
-    for (int c = 0; c < N; c++)
-      if (store[c]) *reinterpret_cast<uint2*>(image + ((size_t)row[c] * L.kblocks * QK + (size_t)kb[c] * QK + 4 * i) * 2) = out[c];
-    return;
-  }
-  uint32_t word[N];
-#pragma unroll
-  for (int c = 0; c < N; c++) {
-    const uint32_t q0 = (uint32_t)q[c][0] & 0xFF, q1 = (uint32_t)q[c][1] & 0xFF, q2 = (uint32_t)q[c][2] & 0xFF, q3 = (uint32_t)q[c][3] & 0xFF;
-    if (DT == AION_CUDA_DTYPE_Q8_0) {
-      word[c] = q0 | (q1 << 8) | (q2 << 16) | (q3 << 24);
-    } else {
-      const uint32_t w = q0 | (q2 << 8) | (q1 << 16) | (q3 << 24);
-      const uint32_t other = __shfl_xor_sync(0xFFFFFFFFu, w, 1);
-      word[c] = (i & 1) ? ((other >> 16) | (w & 0xFFFF0000u)) : ((w & 0xFFFFu) | (other << 16));
-    }
-  }
-  const uint32_t pos = (DT == AION_CUDA_DTYPE_Q8_0) ? (i < 4 ? 2 * i : 2 * (i - 4) + 1) : i;
-#pragma unroll
-  for (int c = 0; c < N; c++)
-    if (store[c]) {
-      reinterpret_cast<uint32_t*>(act_image_codes(image, L, row[c], kb[c]))[pos] = word[c];
-      if (i == 0) act_image_store_scale(image, L, row[c], kb[c], scale[c] * ((DT == AION_CUDA_DTYPE_Q4_0) ? 0.0625f : 1.0f));
-    }
-}
-
 }  // namespace aion

@@ -1011,6 +1011,7 @@ int32_t launch(AionCudaDevice* dev, GemvParams p, const uint8_t* b, uint64_t ldb
 
 template <int DT, bool NT>
 int32_t launch_m(AionCudaDevice* dev, const GemvParams& p, const uint8_t* b, uint64_t ldb, const uint8_t* image) {
+  // (The streaming variants, which a launch takes when the whole-tile variant below does not apply.)
   // m >= 2: A is quantized once by a small kernel (or by the kernel that produced A) instead of
   // by every CTA. m = 1 quantizes its one row inside the kernel when the launch stands alone on a
   // chain (one kernel less: 10.6 against 11.8 us for a lone 9 MB launch) and K is shallow (past
